@@ -1,0 +1,431 @@
+// Persistent warp-specialised bf16 GEMM for sm_100a:  C[M,N] = epilogue(A[M,K] * B[N,K]^T)
+//
+//   warp 0      TMA producer: cp.async.bulk.tensor tiles (128-byte swizzle) into a STAGES-deep ring
+//   warp 1      UMMA issuer: tcgen05.mma (M=128, N=BN, K=16) from shared memory into TMEM;
+//               tcgen05.commit releases ring slots and publishes finished accumulators
+//   warps 2-5   epilogue: tcgen05.ld the fp32 accumulator (two TMEM buffers, so tile i drains
+//               while tile i+1 accumulates), apply the fused epilogue, store bf16
+//
+// Fused epilogue (all optional): alpha, bias[N], GELU(tanh)/SiLU with the pre-activation kept
+// for backward, activation backward (multiply by f'(pre)), adaLN gate + residual
+// (out = R + gate[batch] * y), and a column split that routes columns >= n_split (with the
+// activation) to a second destination, which removes the split/cat copies around FLUX
+// single-stream blocks.
+//
+// LoRA: Y = X W^T + (s X A^T) B^T is one launch of this kernel for the rank-r product
+// H = s X A^T followed by the main launch, which appends one extra K step whose operands are
+// H[M,r] and B[N,r]; the low-rank update lands in the same TMEM accumulator before the epilogue,
+// so no [M,N] delta tensor is ever written. (Reference: two library GEMMs, a scale and an add per
+// site, crates/training/src/flux/lora.rs:47-63, crates/training/src/flux/runtime.rs:555-600.)
+//
+// No cluster launch and no multicast: every CTA loads its own operand tiles.
+#include "ptx.cuh"
+#include "tma_host.h"
+
+using namespace eri;
+typedef __nv_bfloat16 bf16;
+
+namespace {
+
+struct GemmParams {
+  int M, N, K, num_k;
+  int lora_r;          // 0, 16, 32 or 64
+  int act;             // 0 none, 1 GELU(tanh) fwd, 2 SiLU fwd, 3 GELU bwd, 4 SiLU bwd
+  int n_split;         // columns >= n_split take the activation and go to out2 (tile aligned)
+  int ldc, ldc2, ld_pre, ldr;
+  int rows_per_batch, gate_stride;
+  float alpha;
+  const bf16* bias;
+  const bf16* residual;
+  const bf16* gate;
+  const bf16* pre_in;   // indexed with (col - n_split)
+  bf16* out;
+  bf16* out2;           // indexed with (col - n_split)
+  bf16* pre_out;        // indexed with (col - n_split)
+  int* err;
+};
+
+constexpr int BM = 128, BK = 64;
+constexpr int kGroupN = 8;
+
+__host__ __device__ constexpr int tmem_cols_for(int bn) {
+  return 2 * bn <= 32 ? 32 : 2 * bn <= 64 ? 64 : 2 * bn <= 128 ? 128 : 2 * bn <= 256 ? 256 : 512;
+}
+
+__device__ __forceinline__ void tile_coords(int t, int num_m, int num_n, int& m_blk, int& n_blk) {
+  const int group_sz = kGroupN * num_m;
+  const int g = t / group_sz;
+  const int first_n = g * kGroupN;
+  const int gw = min(num_n - first_n, kGroupN);
+  const int r = t - g * group_sz;
+  n_blk = first_n + r % gw;
+  m_blk = r / gw;
+}
+
+__device__ __forceinline__ float apply_act(float v, int act) {
+  return act == 1 ? gelu_tanh_f(v) : act == 2 ? silu_f(v) : v;
+}
+__device__ __forceinline__ float apply_act_grad(float pre, int act) {
+  return act == 3 ? gelu_tanh_grad_f(pre) : silu_grad_f(pre);
+}
+
+template <int BN, int STAGES>
+__global__ void __launch_bounds__(192, 1)
+gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                 const __grid_constant__ CUtensorMap tmA2, const __grid_constant__ CUtensorMap tmB2,
+                 const GemmParams p) {
+  constexpr int A_BYTES = BM * BK * 2;
+  constexpr int B_BYTES = BN * BK * 2;
+  constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  constexpr int TMEM_COLS = tmem_cols_for(BN);
+  constexpr int CH = BN >= 32 ? 32 : 16;  // accumulator columns per TMEM load
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~uintptr_t(1023));
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
+  uint64_t* empty = full + STAGES;
+  uint64_t* acc_full = empty + STAGES;
+  uint64_t* acc_empty = acc_full + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&acc_full[b], 1);
+      mbar_init(&acc_empty[b], 4);
+    }
+    mbar_fence_init();
+    tma_prefetch_desc(&tmA);
+    tma_prefetch_desc(&tmB);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int num_m = (p.M + BM - 1) / BM;
+  const int num_n = (p.N + BN - 1) / BN;
+  const int tiles = num_m * num_n;
+  const int k_iters = p.num_k + (p.lora_r > 0 ? 1 : 0);
+  const uint32_t idesc = umma_idesc_bf16(BM, BN);
+
+  if (warp == 0) {
+    if (elect_one()) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < tiles && ok; t += gridDim.x) {
+        int m_blk, n_blk;
+        tile_coords(t, num_m, num_n, m_blk, n_blk);
+        const int m0 = m_blk * BM, n0 = n_blk * BN;
+        for (int k = 0; k < k_iters; ++k) {
+          if (!mbar_wait(&empty[stage], phase ^ 1)) {
+            atomicExch(p.err, 1);
+            ok = false;
+            break;
+          }
+          uint8_t* sA = smem + stage * STAGE_BYTES;
+          uint8_t* sB = sA + A_BYTES;
+          if (k < p.num_k) {
+            mbar_expect_tx(&full[stage], STAGE_BYTES);
+            tma_load_2d(sA, &tmA, &full[stage], k * BK, m0);
+            tma_load_2d(sB, &tmB, &full[stage], k * BK, n0);
+          } else {
+            mbar_expect_tx(&full[stage], (BM + BN) * p.lora_r * 2);
+            tma_load_2d(sA, &tmA2, &full[stage], 0, m0);
+            tma_load_2d(sB, &tmB2, &full[stage], 0, n0);
+          }
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (elect_one()) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      int it = 0;
+      for (int t = blockIdx.x; t < tiles && ok; t += gridDim.x, ++it) {
+        const int buf = it & 1;
+        const uint32_t use = (uint32_t)(it >> 1);
+        if (!mbar_wait(&acc_empty[buf], (use & 1) ^ 1)) {
+          atomicExch(p.err, 2);
+          break;
+        }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + buf * BN;
+        for (int k = 0; k < k_iters; ++k) {
+          if (!mbar_wait(&full[stage], phase)) {
+            atomicExch(p.err, 3);
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t sA = smem_u32(smem + stage * STAGE_BYTES);
+          const uint32_t sB = sA + A_BYTES;
+          if (k < p.num_k) {
+            const uint64_t da = umma_desc_kmajor(sA, 128), db = umma_desc_kmajor(sB, 128);
+#pragma unroll
+            for (int kk = 0; kk < BK / 16; ++kk)
+              umma_bf16(d_tmem, da + kk * 2, db + kk * 2, idesc, (k | kk) != 0);
+          } else {
+            const uint32_t sw = p.lora_r * 2;
+            const uint64_t da = umma_desc_kmajor(sA, sw), db = umma_desc_kmajor(sB, sw);
+            for (int kk = 0; kk < p.lora_r / 16; ++kk)
+              umma_bf16(d_tmem, da + kk * 2, db + kk * 2, idesc, (k | kk) != 0);
+          }
+          umma_commit(&empty[stage]);
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+        if (ok) umma_commit(&acc_full[buf]);
+      }
+    }
+  } else {
+    const int q = warp & 3;  // TMEM lane quarter this warp may read
+    int it = 0;
+    for (int t = blockIdx.x; t < tiles; t += gridDim.x, ++it) {
+      int m_blk, n_blk;
+      tile_coords(t, num_m, num_n, m_blk, n_blk);
+      const int m0 = m_blk * BM, n0 = n_blk * BN;
+      const int buf = it & 1;
+      const uint32_t use = (uint32_t)(it >> 1);
+      if (!mbar_wait(&acc_full[buf], use & 1)) {
+        if (lane == 0) atomicExch(p.err, 4);
+        break;
+      }
+      tc_fence_after();
+      const int row = m0 + q * 32 + lane;
+      const bool row_ok = row < p.M;
+      const bool second = p.n_split >= 0 && n0 >= p.n_split;
+      const int act = second || p.n_split < 0 ? p.act : 0;
+      const int coff = second ? p.n_split : 0;
+      bf16* dst = second && p.out2 ? p.out2 + (size_t)row * p.ldc2 : p.out + (size_t)row * p.ldc;
+      const int dcol_off = second && p.out2 ? coff : 0;
+      const bf16* gate = p.gate ? p.gate + (size_t)(row_ok ? row / p.rows_per_batch : 0) * p.gate_stride
+                                : nullptr;
+#pragma unroll 1
+      for (int c = 0; c < BN / CH; ++c) {
+        const int col0 = n0 + c * CH;
+        if (col0 >= p.N) break;
+        uint32_t r[CH];
+        const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + buf * BN + c * CH;
+        if constexpr (CH == 32) tmem_ld32(taddr, r); else tmem_ld16(taddr, r);
+        tmem_ld_wait();
+        if (row_ok) {
+#pragma unroll
+          for (int g = 0; g < CH / 8; ++g) {
+            const int col = col0 + g * 8;
+            if (col < p.N) {
+              float v[8];
+#pragma unroll
+              for (int j = 0; j < 8; ++j) v[j] = __uint_as_float(r[g * 8 + j]) * p.alpha;
+              if (p.bias) {
+                float b[8];
+                unpack8(*reinterpret_cast<const bf16x8*>(p.bias + col), b);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) v[j] += b[j];
+              }
+              if (act == 1 || act == 2) {
+                if (p.pre_out)
+                  *reinterpret_cast<bf16x8*>(p.pre_out + (size_t)row * p.ld_pre + (col - coff)) =
+                      pack8(v);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) v[j] = apply_act(v[j], act);
+              } else if (act == 3 || act == 4) {
+                float pr[8];
+                unpack8(*reinterpret_cast<const bf16x8*>(p.pre_in + (size_t)row * p.ld_pre +
+                                                         (col - coff)),
+                        pr);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) v[j] *= apply_act_grad(pr[j], act);
+              }
+              if (gate) {
+                float gt[8];
+                unpack8(*reinterpret_cast<const bf16x8*>(gate + col), gt);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) v[j] *= gt[j];
+              }
+              if (p.residual) {
+                float rs[8];
+                unpack8(*reinterpret_cast<const bf16x8*>(p.residual + (size_t)row * p.ldr + col),
+                        rs);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) v[j] += rs[j];
+              }
+              *reinterpret_cast<bf16x8*>(dst + (col - dcol_off)) = pack8(v);
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&acc_empty[buf]);
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    __syncwarp();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+template <int BN, int STAGES>
+int launch(const CUtensorMap& a, const CUtensorMap& b, const CUtensorMap& a2, const CUtensorMap& b2,
+           const GemmParams& p, int max_ctas, cudaStream_t stream) {
+  constexpr int SMEM = STAGES * (BM * BK * 2 + BN * BK * 2) + 1024 + 256;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_bf16_kernel<BN, STAGES>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  const int tiles = ((p.M + BM - 1) / BM) * ((p.N + BN - 1) / BN);
+  const int grid = tiles < max_ctas ? tiles : max_ctas;
+  gemm_bf16_kernel<BN, STAGES><<<grid, 192, SMEM, stream>>>(a, b, a2, b2, p);
+  return (int)cudaGetLastError();
+}
+
+int g_num_sms = 0;
+int* g_err_flag = nullptr;  // device word; non-zero after a wait inside a kernel ran out
+
+}  // namespace
+
+extern "C" {
+
+struct EriGemmArgs {
+  const void* a;        // [M, K] bf16, row stride lda
+  const void* b;        // [N, K] bf16, row stride ldb
+  const void* lora_h;   // [M, r] bf16 (row stride ld_h) or null
+  const void* lora_b;   // [N, r] bf16 (row stride ld_lb) or null
+  const void* bias;
+  const void* residual;
+  const void* gate;
+  const void* pre_in;
+  void* out;
+  void* out2;
+  void* pre_out;
+  long long lda, ldb, ld_h, ld_lb;
+  int M, N, K, lora_r;
+  int act, n_split;
+  int ldc, ldc2, ld_pre, ldr;
+  int rows_per_batch, gate_stride;
+  int force_bn;
+  float alpha;
+};
+
+// One-time set-up of the device error word (allocates 4 bytes). Returns 0 on success.
+int eri_gemm_init() {
+  if (g_err_flag) return 0;
+  int dev = 0;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&g_num_sms, cudaDevAttrMultiProcessorCount, dev);
+  cudaError_t e = cudaMalloc(&g_err_flag, sizeof(int));
+  if (e != cudaSuccess) return (int)e;
+  return (int)cudaMemset(g_err_flag, 0, sizeof(int));
+}
+
+// Reads (and clears) the error word. Synchronises the device: meant for tests and for the
+// trainer's per-step health check, not for the hot path.
+int eri_gemm_check_error() {
+  if (!g_err_flag) return 0;
+  int h = 0;
+  cudaMemcpy(&h, g_err_flag, sizeof(int), cudaMemcpyDeviceToHost);
+  if (h) cudaMemset(g_err_flag, 0, sizeof(int));
+  return h;
+}
+
+int eri_gemm_bf16(const EriGemmArgs* g, void* stream) {
+  if (!g_err_flag) {
+    int e = eri_gemm_init();
+    if (e) return e;
+  }
+  if (g->M < 1 || g->N < 16 || g->K < 8) return -10;
+  if (g->K % 8 || g->N % 8 || g->lda % 8 || g->ldb % 8 || g->ldc % 8) return -11;
+  if (g->lora_r && g->lora_r != 16 && g->lora_r != 32 && g->lora_r != 64) return -12;
+  int bn = g->force_bn;
+  if (!bn) {
+    if (g->N <= 16) bn = 16;
+    else if (g->N <= 32) bn = 32;
+    else if (g->N <= 64) bn = 64;
+    else {
+      const long long t256 = (long long)((g->M + BM - 1) / BM) * ((g->N + 255) / 256);
+      bn = (g->N >= 256 && t256 >= g_num_sms) ? 256 : 128;
+      if (g->N < 128) bn = 64;
+    }
+  }
+  if (bn > g->N) return -13;
+  if (g->n_split > 0 && g->n_split % bn) {
+    if (g->n_split % 128 == 0) bn = 128; else if (g->n_split % 64 == 0) bn = 64; else return -14;
+  }
+  if (g->M < BM) return -15;  // box taller than the tensor: use the small-M path instead
+
+  GemmParams p;
+  p.M = g->M; p.N = g->N; p.K = g->K; p.num_k = (g->K + BK - 1) / BK;
+  p.lora_r = g->lora_r; p.act = g->act; p.n_split = g->n_split > 0 ? g->n_split : -1;
+  if (g->n_split == 0 && g->out2) p.n_split = 0;
+  p.ldc = g->ldc; p.ldc2 = g->ldc2; p.ld_pre = g->ld_pre; p.ldr = g->ldr;
+  p.rows_per_batch = g->rows_per_batch > 0 ? g->rows_per_batch : g->M;
+  p.gate_stride = g->gate_stride; p.alpha = g->alpha;
+  p.bias = (const bf16*)g->bias; p.residual = (const bf16*)g->residual;
+  p.gate = (const bf16*)g->gate; p.pre_in = (const bf16*)g->pre_in;
+  p.out = (bf16*)g->out; p.out2 = (bf16*)g->out2; p.pre_out = (bf16*)g->pre_out;
+  p.err = g_err_flag;
+
+  CUtensorMap ta, tb, ta2, tb2;
+  {
+    uint64_t d[2] = {(uint64_t)g->K, (uint64_t)g->M};
+    uint64_t s[1] = {(uint64_t)g->lda * 2};
+    uint32_t bx[2] = {BK, BM};
+    if (make_tensor_map(&ta, g->a, 2, d, s, bx, 128)) return -20;
+  }
+  {
+    uint64_t d[2] = {(uint64_t)g->K, (uint64_t)g->N};
+    uint64_t s[1] = {(uint64_t)g->ldb * 2};
+    uint32_t bx[2] = {BK, (uint32_t)bn};
+    if (make_tensor_map(&tb, g->b, 2, d, s, bx, 128)) return -21;
+  }
+  if (g->lora_r) {
+    uint64_t d[2] = {(uint64_t)g->lora_r, (uint64_t)g->M};
+    uint64_t s[1] = {(uint64_t)g->ld_h * 2};
+    uint32_t bx[2] = {(uint32_t)g->lora_r, BM};
+    if (make_tensor_map(&ta2, g->lora_h, 2, d, s, bx, g->lora_r * 2)) return -22;
+    uint64_t d2[2] = {(uint64_t)g->lora_r, (uint64_t)g->N};
+    uint64_t s2[1] = {(uint64_t)g->ld_lb * 2};
+    uint32_t bx2[2] = {(uint32_t)g->lora_r, (uint32_t)bn};
+    if (make_tensor_map(&tb2, g->lora_b, 2, d2, s2, bx2, g->lora_r * 2)) return -23;
+  } else {
+    ta2 = ta;
+    tb2 = tb;
+  }
+  cudaStream_t st = (cudaStream_t)stream;
+  switch (bn) {
+    case 256: return launch<256, 4>(ta, tb, ta2, tb2, p, g_num_sms, st);
+    case 128: return launch<128, 6>(ta, tb, ta2, tb2, p, g_num_sms, st);
+    case 64: return launch<64, 8>(ta, tb, ta2, tb2, p, g_num_sms, st);
+    case 32: return launch<32, 8>(ta, tb, ta2, tb2, p, g_num_sms, st);
+    case 16: return launch<16, 8>(ta, tb, ta2, tb2, p, g_num_sms, st);
+  }
+  return -16;
+}
+
+}  // extern "C"

@@ -1,0 +1,126 @@
+"""Building blocks shared by the transformer model families.
+
+``Linear`` owns a bf16 weight and routes through the fused linear op; an adapter (LoRA family)
+can be attached to it, and a frozen weight can keep a transposed copy so that the input-gradient
+GEMM reads a K-major operand (a deliberate HBM-for-speed trade on a 180 GB part).
+"""
+from __future__ import annotations
+
+import math
+
+import torch
+import torch.nn as nn
+
+from ..ops import functional as F
+
+
+class Linear(nn.Module):
+    def __init__(self, in_features, out_features, bias=True, dtype=torch.bfloat16, device=None):
+        super().__init__()
+        self.in_features, self.out_features = in_features, out_features
+        self.weight = nn.Parameter(torch.empty(out_features, in_features, dtype=dtype, device=device))
+        self.bias = nn.Parameter(torch.empty(out_features, dtype=dtype, device=device)) if bias else None
+        self.adapter = None          # set by adapters.inject()
+        self._wt = None              # cached transpose of a frozen weight
+        self.reset_parameters()
+
+    def reset_parameters(self, gen: torch.Generator | None = None):
+        std = 1.0 / math.sqrt(self.in_features)
+        with torch.no_grad():
+            w = torch.empty(self.weight.shape, dtype=torch.float32, device=self.weight.device)
+            w.normal_(0.0, std, generator=gen)
+            self.weight.copy_(w)
+            if self.bias is not None:
+                self.bias.zero_()
+
+    def frozen_transpose(self):
+        """[in, out] copy of a weight that does not require grad (built once, on demand)."""
+        if self.weight.requires_grad or not self.weight.is_cuda:
+            return None
+        if self._wt is None or self._wt.device != self.weight.device:
+            self._wt = self.weight.detach().t().contiguous()
+        return self._wt
+
+    def drop_transpose(self):
+        self._wt = None
+
+    def forward(self, x, act=None, residual=None, gate=None):
+        if self.adapter is not None:
+            return self.adapter(self, x, act=act, residual=residual, gate=gate)
+        return F.linear(x, self.weight, self.bias, act=act, residual=residual, gate=gate,
+                        wt=self.frozen_transpose() if torch.is_grad_enabled() else None)
+
+    def extra_repr(self):
+        return f"in={self.in_features}, out={self.out_features}, bias={self.bias is not None}"
+
+
+class SmallLinear(Linear):
+    """Linear applied to a few conditioning rows (adaLN modulation, embedders)."""
+
+    def forward(self, x, silu_in=False):
+        return F.small_linear(x, self.weight, self.bias, silu_in=silu_in)
+
+
+def timestep_embedding(t, dim, max_period=10000.0, time_factor=1000.0):
+    """Sinusoidal embedding [B, dim] of t in [0, 1] scaled by ``time_factor``."""
+    t = t.float() * time_factor
+    half = dim // 2
+    freqs = torch.exp(-math.log(max_period) * torch.arange(half, dtype=torch.float32, device=t.device) / half)
+    args = t[:, None] * freqs[None]
+    emb = torch.cat([torch.cos(args), torch.sin(args)], dim=-1)
+    if dim % 2:
+        emb = torch.cat([emb, torch.zeros_like(emb[:, :1])], dim=-1)
+    return emb
+
+
+class MLPEmbedder(nn.Module):
+    def __init__(self, in_dim, hidden, dtype=torch.bfloat16, device=None):
+        super().__init__()
+        self.in_layer = SmallLinear(in_dim, hidden, dtype=dtype, device=device)
+        self.out_layer = SmallLinear(hidden, hidden, dtype=dtype, device=device)
+
+    def forward(self, x):
+        return self.out_layer(self.in_layer(x), silu_in=True)
+
+
+class Modulation(nn.Module):
+    """adaLN modulation: Linear(SiLU(vec)) split into ``n`` chunks of width ``dim``."""
+
+    def __init__(self, dim, n, dtype=torch.bfloat16, device=None, cond_dim=None):
+        super().__init__()
+        self.n, self.dim = n, dim
+        self.lin = SmallLinear(cond_dim or dim, n * dim, dtype=dtype, device=device)
+
+    def forward(self, vec):
+        out = self.lin(vec, silu_in=True)          # [B, n*dim]
+        return out.split(self.dim, dim=-1)          # strided views, consumed without copies
+
+
+def rope_table(ids, axes_dim, theta=10000.0):
+    """cos/sin tables [L, sum(axes_dim)/2] (fp32) for N-axis rotary embedding of interleaved
+    pairs; ``ids`` is [L, n_axes] (FLUX: (type, row, col) with axes_dim (16, 56, 56);
+    reference layout: src/kernels/rope.cu:49-57)."""
+    cos, sin = [], []
+    for i, d in enumerate(axes_dim):
+        scale = torch.arange(0, d, 2, dtype=torch.float64, device=ids.device) / d
+        omega = 1.0 / (theta ** scale)
+        ang = ids[:, i].double()[:, None] * omega[None]
+        cos.append(torch.cos(ang))
+        sin.append(torch.sin(ang))
+    return torch.cat(cos, -1).float(), torch.cat(sin, -1).float()
+
+
+def image_ids(h, w, device=None, t=0):
+    ids = torch.zeros(h, w, 3, device=device)
+    ids[..., 0] = t
+    ids[..., 1] = torch.arange(h, device=device)[:, None]
+    ids[..., 2] = torch.arange(w, device=device)[None, :]
+    return ids.view(h * w, 3)
+
+
+class RMSNormScale(nn.Module):
+    """Learned per-head scale used by RMS QK-norm (the normalisation itself is fused downstream)."""
+
+    def __init__(self, dim, dtype=torch.bfloat16, device=None):
+        super().__init__()
+        self.scale = nn.Parameter(torch.ones(dim, dtype=dtype, device=device))

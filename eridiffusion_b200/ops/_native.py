@@ -1,0 +1,141 @@
+"""ctypes binding of the in-tree CUDA library.
+
+The kernels are exported as plain C functions taking raw device pointers and a CUDA stream, so the
+binding layer is a table of argument types. ``lib()`` loads ``lib/liberi_b200_kernels.so`` (building
+it when the sources are newer and a compiler is present). On a machine with a GPU a missing
+library is an error, never a silent fallback: ``require()`` raises ``NativeLibraryError``.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+import threading
+from pathlib import Path
+
+import torch
+
+_PKG = Path(__file__).resolve().parent.parent
+_LIB_PATH = _PKG / "lib" / "liberi_b200_kernels.so"
+_lock = threading.Lock()
+_lib = None
+_launches = 0  # number of kernel launches issued through this module (for bench accounting)
+
+
+class NativeLibraryError(RuntimeError):
+    pass
+
+
+class GemmArgs(C.Structure):
+    _fields_ = [
+        ("a", C.c_void_p), ("b", C.c_void_p), ("lora_h", C.c_void_p), ("lora_b", C.c_void_p),
+        ("bias", C.c_void_p), ("residual", C.c_void_p), ("gate", C.c_void_p),
+        ("pre_in", C.c_void_p), ("out", C.c_void_p), ("out2", C.c_void_p),
+        ("pre_out", C.c_void_p),
+        ("lda", C.c_longlong), ("ldb", C.c_longlong), ("ld_h", C.c_longlong),
+        ("ld_lb", C.c_longlong),
+        ("M", C.c_int), ("N", C.c_int), ("K", C.c_int), ("lora_r", C.c_int),
+        ("act", C.c_int), ("n_split", C.c_int),
+        ("ldc", C.c_int), ("ldc2", C.c_int), ("ld_pre", C.c_int), ("ldr", C.c_int),
+        ("rows_per_batch", C.c_int), ("gate_stride", C.c_int),
+        ("force_bn", C.c_int), ("alpha", C.c_float),
+    ]
+
+
+_P, _I, _L, _F, _U64, _U32 = C.c_void_p, C.c_int, C.c_longlong, C.c_float, C.c_ulonglong, C.c_uint
+
+_SIGNATURES = {
+    "eri_norm_modulate_fwd": [_P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _F, _I, _P],
+    "eri_norm_modulate_bwd": [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P],
+    "eri_qknorm_rope_fwd": [_P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _I, _I, _P],
+    "eri_qknorm_rope_bwd": [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F,
+                            _I, _I, _I, _P],
+    "eri_gate_residual": [_P, _P, _P, _P, _L, _I, _I, _I, _P],
+    "eri_gate_grad": [_P, _P, _P, _I, _I, _I, _P],
+    "eri_act_fwd": [_P, _P, _L, _I, _P],
+    "eri_act_bwd": [_P, _P, _P, _L, _I, _P],
+    "eri_glu_fwd": [_P, _P, _I, _I, _I, _I, _P],
+    "eri_glu_bwd": [_P, _P, _P, _I, _I, _I, _I, _P],
+    "eri_noise_mix": [_P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _U64, _U64, _P],
+    "eri_randn_bf16": [_P, _L, _U64, _U64, _F, _F, _P],
+    "eri_mse_fwd_bwd": [_P, _P, _P, _P, _P, _L, _L, _F, _P],
+    "eri_sumsq_bf16": [_P, _L, _P, _P],
+    "eri_post_clamp_u8": [_P, _P, _L, _P],
+    "eri_poison_fill": [_P, _L, _U32, _P],
+    "eri_adamw8bit_step": [_P, _P, _P, _P, _P, _P, _P, _L, _F, _F, _F, _F, _F, _I, _F, _F, _U32, _I, _P],
+    "eri_adamw32_step": [_P, _P, _P, _P, _P, _L, _I, _F, _F, _F, _F, _F, _I, _F, _F, _U32, _I, _P],
+    "eri_ema_update": [_P, _P, _L, _F, _P],
+    "eri_scale_bf16": [_P, _L, _P, _F, _F, _P],
+    "eri_gemm_init": [],
+    "eri_gemm_check_error": [],
+    "eri_gemm_bf16": [C.POINTER(GemmArgs), _P],
+    "eri_gemv_bf16": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P],
+}
+
+
+def _maybe_build() -> None:
+    if os.environ.get("ERI_B200_NO_BUILD") == "1":
+        return
+    try:
+        from ..csrc import build as _b
+        _b.build_kernels()
+    except Exception:
+        if not _LIB_PATH.exists():
+            raise
+
+
+def lib():
+    """Return the loaded kernel library, or ``None`` when it cannot be loaded here (CPU-only box
+    without the CUDA runtime)."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    with _lock:
+        if _lib is not None:
+            return _lib
+        try:
+            if not _LIB_PATH.exists():
+                _maybe_build()
+            handle = C.CDLL(str(_LIB_PATH))
+        except Exception:
+            return None
+        for name, argtypes in _SIGNATURES.items():
+            try:
+                fn = getattr(handle, name)
+            except AttributeError:
+                continue
+            fn.argtypes = argtypes
+            fn.restype = C.c_int
+        _lib = handle
+    return _lib
+
+
+def available() -> bool:
+    return torch.cuda.is_available() and lib() is not None
+
+
+def require():
+    h = lib()
+    if h is None:
+        raise NativeLibraryError(
+            f"native kernel library {_LIB_PATH} is missing or failed to load; run "
+            "`python -m eridiffusion_b200.csrc.build` (needs nvcc) before using CUDA tensors")
+    return h
+
+
+def stream_ptr() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def ptr(t) -> int | None:
+    return None if t is None else t.data_ptr()
+
+
+def check(code: int, what: str) -> None:
+    global _launches
+    _launches += 1
+    if code != 0:
+        raise RuntimeError(f"{what} failed with code {code}")
+
+
+def launch_count() -> int:
+    return _launches

@@ -1,0 +1,666 @@
+"""Public op surface. CUDA bf16 tensors run the hand-written sm_100a kernels (through autograd
+Functions that call the in-tree library); everything else runs the PyTorch statements in
+``reference``. ``set_backend("eager")`` forces the PyTorch path on CUDA too — that is the
+library baseline the fused path is measured against.
+"""
+from __future__ import annotations
+
+import math
+import os
+
+import torch
+
+from . import _native as N
+from . import reference as R
+
+_BACKEND = os.environ.get("ERI_B200_BACKEND", "fused")  # "fused" | "eager"
+_GEMM_NATIVE = os.environ.get("ERI_B200_GEMM", "native")  # "native" | "library"
+_ATTN_NATIVE = os.environ.get("ERI_B200_ATTN", "native")  # "native" | "library"
+
+
+def set_backend(name: str) -> None:
+    global _BACKEND
+    if name not in ("fused", "eager"):
+        raise ValueError(name)
+    _BACKEND = name
+
+
+def get_backend() -> str:
+    return _BACKEND
+
+
+def set_gemm_impl(name: str) -> None:
+    global _GEMM_NATIVE
+    _GEMM_NATIVE = name
+
+
+def set_attention_impl(name: str) -> None:
+    global _ATTN_NATIVE
+    _ATTN_NATIVE = name
+
+
+def _native_ok(*ts) -> bool:
+    if _BACKEND != "fused":
+        return False
+    for t in ts:
+        if t is None:
+            continue
+        if not t.is_cuda or t.dtype != torch.bfloat16:
+            return False
+    N.require()
+    return True
+
+
+def _c(t):
+    return None if t is None else (t if t.is_contiguous() else t.contiguous())
+
+
+def _tokmajor(t):
+    """[B, L, W] whose tokens may be row-strided (a column slice of a wider buffer)."""
+    if t.stride(2) == 1 and t.stride(0) == t.shape[1] * t.stride(1) and t.stride(1) % 8 == 0 \
+            and t.data_ptr() % 16 == 0:
+        return t
+    return t.contiguous()
+
+
+def _mod_view(t, D):
+    """A [B, D] modulation tensor whose rows may be strided (a chunk of a wider tensor)."""
+    if t is None:
+        return None, 0
+    assert t.dim() == 2 and t.shape[1] == D
+    if t.stride(1) != 1 or t.stride(0) % 8 != 0 or t.data_ptr() % 16 != 0:
+        t = t.contiguous()
+    return t, t.stride(0)
+
+
+# ---------------------------------------------------------------------------- norm + modulation
+class _NormModulate(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, scale, shift, weight, bias, eps, rms):
+        B, L, D = x.shape
+        x = _c(x)
+        scale_v, s1 = _mod_view(scale, D)
+        shift_v, s2 = _mod_view(shift, D)
+        if scale_v is not None and shift_v is not None and s1 != s2:
+            scale_v, shift_v = scale_v.contiguous(), shift_v.contiguous()
+            s1 = s2 = D
+        stride = s1 or s2 or D
+        y = torch.empty_like(x)
+        mean = torch.empty(B * L, dtype=torch.float32, device=x.device)
+        rstd = torch.empty(B * L, dtype=torch.float32, device=x.device)
+        lib = N.require()
+        N.check(lib.eri_norm_modulate_fwd(
+            x.data_ptr(), N.ptr(scale_v), N.ptr(shift_v), N.ptr(weight), N.ptr(bias),
+            y.data_ptr(), mean.data_ptr(), rstd.data_ptr(), B * L, D, L, stride, eps,
+            1 if rms else 0, N.stream_ptr()), "norm_modulate_fwd")
+        ctx.save_for_backward(x, scale_v, weight, bias, mean, rstd)
+        ctx.meta = (B, L, D, stride, rms, scale is not None, shift is not None)
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, scale_v, weight, bias, mean, rstd = ctx.saved_tensors
+        B, L, D, stride, rms, has_scale, has_shift = ctx.meta
+        dy = _c(dy)
+        dx = torch.empty_like(x)
+        need = ctx.needs_input_grad
+        f32 = dict(dtype=torch.float32, device=x.device)
+        dscale = torch.zeros(B, D, **f32) if (has_scale and need[1]) else None
+        dshift = torch.zeros(B, D, **f32) if (has_shift and need[2]) else None
+        dweight = torch.zeros(D, **f32) if (weight is not None and need[3]) else None
+        dbias = torch.zeros(D, **f32) if (bias is not None and need[4]) else None
+        lib = N.require()
+        N.check(lib.eri_norm_modulate_bwd(
+            dy.data_ptr(), x.data_ptr(), N.ptr(scale_v), N.ptr(weight), N.ptr(bias),
+            mean.data_ptr(), rstd.data_ptr(), dx.data_ptr(), N.ptr(dscale), N.ptr(dshift),
+            N.ptr(dweight), N.ptr(dbias), B * L, D, L, stride, 1 if rms else 0, N.stream_ptr()),
+            "norm_modulate_bwd")
+        cv = lambda t: None if t is None else t.to(torch.bfloat16)
+        return dx, cv(dscale), cv(dshift), cv(dweight), cv(dbias), None, None
+
+
+def norm_modulate(x, scale=None, shift=None, weight=None, bias=None, eps=1e-6, rms=False):
+    if _native_ok(x, scale, shift, weight, bias) and x.dim() == 3 and x.shape[-1] % 8 == 0 \
+            and x.shape[-1] <= 16384:
+        return _NormModulate.apply(x, scale, shift, weight, bias, eps, rms)
+    return R.norm_modulate(x, scale, shift, weight, bias, eps, rms)
+
+
+# ---------------------------------------------------------------------------- QK-norm + RoPE
+def qknorm_rope(qkv, q_scale, k_scale, cos, sin, num_heads, eps=1e-6):
+    """qkv [B, L, 3*H*Dh] -> q, k, v [B, L, H, Dh] (norm + rotary on q, k)."""
+    return qknorm_rope_joint([(qkv, q_scale, k_scale)], cos, sin, num_heads, eps)
+
+
+class _QKNormRopeJoint(torch.autograd.Function):
+    """Several token streams (e.g. text and image) -> one joint q, k, v of shape
+    [B, sum(L_i), H, Dh]; each stream has its own QK-norm scales, the rotary table covers the
+    joint sequence. One kernel launch per stream writes straight into the joint tensors, so no
+    concatenation copy exists in forward, and backward splits the gradient the same way."""
+
+    @staticmethod
+    def forward(ctx, cos, sin, H, eps, width, *flat):
+        n = len(flat) // 3
+        qkvs = [_tokmajor(flat[3 * i]) for i in range(n)]
+        B = qkvs[0].shape[0]
+        Dh = width // (3 * H)
+        Ls = [t.shape[1] for t in qkvs]
+        Ltot = sum(Ls)
+        q = torch.empty(B, Ltot, H, Dh, dtype=qkvs[0].dtype, device=qkvs[0].device)
+        k, v = torch.empty_like(q), torch.empty_like(q)
+        lib = N.require()
+        off = 0
+        for i in range(n):
+            qs, ks = flat[3 * i + 1], flat[3 * i + 2]
+            tok_stride = qkvs[i].stride(1)
+            N.check(lib.eri_qknorm_rope_fwd(
+                qkvs[i].data_ptr(), N.ptr(qs), N.ptr(ks), N.ptr(cos), N.ptr(sin), q.data_ptr(),
+                k.data_ptr(), v.data_ptr(), B, Ls[i], H, Dh, Ltot, off, eps, tok_stride, H * Dh,
+                N.stream_ptr()), "qknorm_rope_fwd")
+            off += Ls[i]
+        ctx.save_for_backward(cos, sin, *qkvs, *[flat[3 * i + 1] for i in range(n)],
+                              *[flat[3 * i + 2] for i in range(n)])
+        ctx.meta = (n, B, H, Dh, Ls, Ltot, eps)
+        return q, k, v
+
+    @staticmethod
+    def backward(ctx, dq, dk, dv):
+        n, B, H, Dh, Ls, Ltot, eps = ctx.meta
+        sv = ctx.saved_tensors
+        cos, sin = sv[0], sv[1]
+        qkvs, qss, kss = sv[2:2 + n], sv[2 + n:2 + 2 * n], sv[2 + 2 * n:2 + 3 * n]
+        dq, dk, dv = _c(dq), _c(dk), _c(dv)
+        lib = N.require()
+        grads = []
+        off = 0
+        f32 = dict(dtype=torch.float32, device=dq.device)
+        for i in range(n):
+            dqkv = torch.empty(qkvs[i].shape, dtype=qkvs[i].dtype, device=qkvs[i].device)
+            need_q = qss[i] is not None and ctx.needs_input_grad[5 + 3 * i + 1]
+            need_k = kss[i] is not None and ctx.needs_input_grad[5 + 3 * i + 2]
+            dqs = torch.zeros(Dh, **f32) if need_q else None
+            dks = torch.zeros(Dh, **f32) if need_k else None
+            N.check(lib.eri_qknorm_rope_bwd(
+                dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), qkvs[i].data_ptr(), N.ptr(qss[i]),
+                N.ptr(kss[i]), N.ptr(cos), N.ptr(sin), dqkv.data_ptr(), N.ptr(dqs), N.ptr(dks),
+                B, Ls[i], H, Dh, Ltot, off, eps, qkvs[i].stride(1), H * Dh, dqkv.stride(1),
+                N.stream_ptr()), "qknorm_rope_bwd")
+            off += Ls[i]
+            cv = lambda t: None if t is None else t.to(torch.bfloat16)
+            grads += [dqkv, cv(dqs), cv(dks)]
+        return (None, None, None, None, None, *grads)
+
+
+def qknorm_rope_joint(streams, cos, sin, num_heads, eps=1e-6):
+    """streams: list of (qkv [B, L_i, 3*H*Dh], q_scale [Dh] | None, k_scale [Dh] | None).
+    Returns joint q, k, v [B, sum L_i, H, Dh]; cos/sin [sum L_i, Dh/2] or None."""
+    W = streams[0][0].shape[-1]
+    Dh = W // (3 * num_heads)
+    tens = [t for s in streams for t in s]
+    if _native_ok(*tens) and Dh in (64, 128) and (cos is None or cos.is_cuda):
+        cosf = None if cos is None else cos.float().contiguous()
+        sinf = None if sin is None else sin.float().contiguous()
+        return _QKNormRopeJoint.apply(cosf, sinf, num_heads, eps, W, *tens)
+    outs, off = [], 0
+    for qkv, qs, ks in streams:
+        L = qkv.shape[1]
+        c = None if cos is None else cos[off:off + L]
+        s_ = None if sin is None else sin[off:off + L]
+        outs.append(R.qknorm_rope(qkv, qs, ks, c, s_, num_heads, eps))
+        off += L
+    if len(outs) == 1:
+        return outs[0]
+    return tuple(torch.cat([o[j] for o in outs], dim=1) for j in range(3))
+
+
+# ---------------------------------------------------------------------------- gate + residual
+class _GateResidual(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, y, gate):
+        B, L, D = y.shape
+        y = _c(y)
+        x = _c(x)
+        gate_v, gs = _mod_view(gate, D)
+        out = torch.empty_like(y)
+        lib = N.require()
+        N.check(lib.eri_gate_residual(N.ptr(x), y.data_ptr(), N.ptr(gate_v), out.data_ptr(),
+                                      B * L, D, L, gs, N.stream_ptr()), "gate_residual")
+        ctx.save_for_backward(y if (gate is not None and ctx.needs_input_grad[2]) else None, gate_v)
+        ctx.meta = (B, L, D, gs, x is not None)
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        y, gate_v = ctx.saved_tensors
+        B, L, D, gs, has_x = ctx.meta
+        dout = _c(dout)
+        lib = N.require()
+        dx = dout if has_x else None
+        if gate_v is None:
+            return dx, dout, None
+        dy = torch.empty_like(dout)
+        N.check(lib.eri_gate_residual(None, dout.data_ptr(), gate_v.data_ptr(), dy.data_ptr(),
+                                      B * L, D, L, gs, N.stream_ptr()), "gate_residual_bwd")
+        dgate = None
+        if ctx.needs_input_grad[2]:
+            dg = torch.zeros(B, D, dtype=torch.float32, device=dout.device)
+            N.check(lib.eri_gate_grad(dout.data_ptr(), y.data_ptr(), dg.data_ptr(), B * L, D, L,
+                                      N.stream_ptr()), "gate_grad")
+            dgate = dg.to(torch.bfloat16)
+        return dx, dy, dgate
+
+
+def gate_residual(x, y, gate=None):
+    if _native_ok(x, y, gate) and y.dim() == 3 and y.shape[-1] % 8 == 0:
+        return _GateResidual.apply(x, y, gate)
+    return R.gate_residual(x, y, gate)
+
+
+# ---------------------------------------------------------------------------- activations
+class _Act(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, mode):
+        x = _c(x)
+        y = torch.empty_like(x)
+        N.check(N.require().eri_act_fwd(x.data_ptr(), y.data_ptr(), x.numel(), mode,
+                                        N.stream_ptr()), "act_fwd")
+        ctx.save_for_backward(x)
+        ctx.mode = mode
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        (x,) = ctx.saved_tensors
+        dy = _c(dy)
+        dx = torch.empty_like(x)
+        N.check(N.require().eri_act_bwd(dy.data_ptr(), x.data_ptr(), dx.data_ptr(), x.numel(),
+                                        ctx.mode, N.stream_ptr()), "act_bwd")
+        return dx, None
+
+
+def gelu_tanh(x):
+    if _native_ok(x) and x.numel() % 8 == 0:
+        return _Act.apply(x, 0)
+    return R.gelu_tanh(x)
+
+
+def silu(x):
+    if _native_ok(x) and x.numel() % 8 == 0:
+        return _Act.apply(x, 1)
+    return R.silu(x)
+
+
+class _Glu(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, h, mode, act_first):
+        h = _c(h)
+        F2 = h.shape[-1]
+        rows = h.numel() // F2
+        out = torch.empty(*h.shape[:-1], F2 // 2, dtype=h.dtype, device=h.device)
+        N.check(N.require().eri_glu_fwd(h.data_ptr(), out.data_ptr(), rows, F2 // 2, mode,
+                                        1 if act_first else 0, N.stream_ptr()), "glu_fwd")
+        ctx.save_for_backward(h)
+        ctx.meta = (rows, F2 // 2, mode, act_first)
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        (h,) = ctx.saved_tensors
+        rows, Fh, mode, act_first = ctx.meta
+        dout = _c(dout)
+        dh = torch.empty_like(h)
+        N.check(N.require().eri_glu_bwd(dout.data_ptr(), h.data_ptr(), dh.data_ptr(), rows, Fh,
+                                        mode, 1 if act_first else 0, N.stream_ptr()), "glu_bwd")
+        return dh, None, None
+
+
+def glu(h, mode="gelu", act_first=True):
+    if _native_ok(h) and h.shape[-1] % 16 == 0:
+        return _Glu.apply(h, 0 if mode == "gelu" else 1, act_first)
+    return R.glu(h, mode, act_first)
+
+
+# ---------------------------------------------------------------------------- GEMM family
+_ACT_CODE = {None: 0, "gelu": 1, "silu": 2, "gelu_bwd": 3, "silu_bwd": 4}
+
+
+def gemm_native(a, b, *, out=None, alpha=1.0, bias=None, lora_h=None, lora_b=None, act=None,
+                pre_out=None, pre_in=None, residual=None, gate=None, rows_per_batch=0,
+                n_split=0, out2=None, force_bn=0):
+    """out[M,N] = epilogue(a[M,K] @ b[N,K]^T (+ lora_h[M,r] @ lora_b[N,r]^T)) on the tcgen05 kernel.
+
+    ``a``/``b``/``out`` may be row-strided views (last dim contiguous). Returns ``out``.
+    """
+    lib = N.require()
+    M, K = a.shape
+    Nn = b.shape[0]
+    assert b.shape[1] == K and a.stride(1) == 1 and b.stride(1) == 1
+    if out is None:
+        out = torch.empty(M, Nn if not n_split else n_split, dtype=torch.bfloat16, device=a.device)
+    g = N.GemmArgs()
+    g.a, g.b = a.data_ptr(), b.data_ptr()
+    g.lda, g.ldb = a.stride(0), b.stride(0)
+    g.M, g.N, g.K = M, Nn, K
+    g.alpha = alpha
+    g.out, g.ldc = out.data_ptr(), out.stride(0)
+    g.bias = N.ptr(bias)
+    if lora_h is not None:
+        g.lora_h, g.lora_b = lora_h.data_ptr(), lora_b.data_ptr()
+        g.ld_h, g.ld_lb = lora_h.stride(0), lora_b.stride(0)
+        g.lora_r = lora_h.shape[1]
+    g.act = _ACT_CODE[act]
+    if pre_out is not None:
+        g.pre_out, g.ld_pre = pre_out.data_ptr(), pre_out.stride(0)
+    if pre_in is not None:
+        g.pre_in, g.ld_pre = pre_in.data_ptr(), pre_in.stride(0)
+    if residual is not None:
+        g.residual, g.ldr = residual.data_ptr(), residual.stride(0)
+    if gate is not None:
+        g.gate, g.gate_stride = gate.data_ptr(), gate.stride(0)
+    g.rows_per_batch = rows_per_batch
+    g.n_split = n_split
+    if out2 is not None:
+        g.out2, g.ldc2 = out2.data_ptr(), out2.stride(0)
+    g.force_bn = force_bn
+    code = lib.eri_gemm_bf16(g, N.stream_ptr())
+    N.check(code, "gemm_bf16")
+    return out
+
+
+def gemm_supported(M, Nn, K) -> bool:
+    return M >= 128 and Nn >= 16 and K >= 8 and K % 8 == 0 and Nn % 8 == 0
+
+
+def gemm_error_check() -> int:
+    """Synchronise and return the device error word of the GEMM kernels (0 = clean)."""
+    return N.require().eri_gemm_check_error()
+
+
+def _mm(a, b_nk, **kw):
+    """a[M,K] @ b_nk[N,K]^T with the native kernel when the shape qualifies."""
+    if _GEMM_NATIVE == "native" and gemm_supported(a.shape[0], b_nk.shape[0], a.shape[1]) \
+            and a.stride(0) % 8 == 0 and b_nk.stride(0) % 8 == 0 \
+            and a.data_ptr() % 16 == 0 and b_nk.data_ptr() % 16 == 0:
+        return gemm_native(a, b_nk, **kw)
+    y = torch.matmul(a, b_nk.t())
+    if kw.get("alpha", 1.0) != 1.0:
+        y = y * kw["alpha"]
+    return y
+
+
+class _FusedLinear(torch.autograd.Function):
+    """y = [residual + gate *] act(x W^T + b + s (x A^T) B^T), M = B*L rows.
+
+    Saved for backward: x, the rank-r product H, the pre-activation (when act) — never a
+    materialised LoRA delta. ``wt`` is an optional cached transpose of a frozen W ([K, N]) that
+    lets the input-gradient GEMM read a K-major operand.
+    """
+
+    @staticmethod
+    def forward(ctx, x, w, bias, lora_a, lora_b, lora_scale, act, residual, gate, wt):
+        shp = x.shape
+        K = shp[-1]
+        x2 = _c(x).view(-1, K)
+        M, Nn = x2.shape[0], w.shape[0]
+        L = shp[-2] if x.dim() >= 2 else 1
+        native = _GEMM_NATIVE == "native" and gemm_supported(M, Nn, K)
+        r = 0 if lora_a is None else lora_a.shape[0]
+        lora_fused = native and r in (16, 32, 64)
+        h = None
+        pre = None
+        res2 = None if residual is None else _c(residual).view(-1, Nn)
+        gate_v = None
+        if gate is not None:
+            gate_v, _ = _mod_view(gate, Nn)
+        if native:
+            if r and lora_fused:
+                h = gemm_native(x2, lora_a, alpha=lora_scale)
+            elif r:
+                h = (x2 @ lora_a.t()) * lora_scale
+            need_pre = act is not None and any(ctx.needs_input_grad[:5])
+            if need_pre:
+                pre = torch.empty(M, Nn, dtype=x.dtype, device=x.device)
+            if r and not lora_fused:
+                y = gemm_native(x2, w, bias=bias)
+                y = y + h @ lora_b.t()
+                if act is not None:
+                    pre = y
+                    y = R.gelu_tanh(y) if act == "gelu" else R.silu(y)
+                if gate_v is not None or res2 is not None:
+                    y = R.gate_residual(None if res2 is None else res2.view(-1, L, Nn),
+                                        y.view(-1, L, Nn), gate_v).view(M, Nn)
+            else:
+                y = gemm_native(x2, w, bias=bias, lora_h=h, lora_b=lora_b if r else None,
+                                act=act, pre_out=pre, residual=res2, gate=gate_v,
+                                rows_per_batch=L)
+        else:
+            y = torch.nn.functional.linear(x2, w, bias)
+            if r:
+                h = (x2 @ lora_a.t()) * lora_scale
+                y = y + h @ lora_b.t()
+            if act is not None:
+                pre = y
+                y = R.gelu_tanh(y) if act == "gelu" else R.silu(y)
+            if gate_v is not None or res2 is not None:
+                y = R.gate_residual(None if res2 is None else res2.view(-1, L, Nn),
+                                    y.view(-1, L, Nn), gate_v).view(M, Nn)
+        ctx.save_for_backward(x2, w, lora_a, lora_b, h, pre, gate_v, wt)
+        ctx.meta = (shp, Nn, L, lora_scale, act, residual is not None, bias is not None)
+        return y.view(*shp[:-1], Nn)
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2, w, lora_a, lora_b, h, pre, gate_v, wt = ctx.saved_tensors
+        shp, Nn, L, s, act, has_res, has_bias = ctx.meta
+        need = ctx.needs_input_grad
+        M, K = x2.shape
+        dy2 = _c(dy).view(M, Nn)
+        d_res = dy.reshape(*shp[:-1], Nn) if has_res else None
+        lib = N.require() if dy2.is_cuda and _BACKEND == "fused" else None
+        # undo gate / activation on the incoming gradient
+        dgate = None
+        if gate_v is not None:
+            if lib is not None:
+                g = torch.empty_like(dy2)
+                N.check(lib.eri_gate_residual(None, dy2.data_ptr(), gate_v.data_ptr(),
+                                              g.data_ptr(), M, Nn, L, gate_v.stride(0),
+                                              N.stream_ptr()), "gate_bwd")
+            else:
+                g = R.gate_residual(None, dy2.view(-1, L, Nn), gate_v).view(M, Nn)
+            dy2 = g
+        if act is not None:
+            if lib is not None:
+                g = torch.empty_like(dy2)
+                N.check(lib.eri_act_bwd(dy2.data_ptr(), pre.data_ptr(), g.data_ptr(), dy2.numel(),
+                                        0 if act == "gelu" else 1, N.stream_ptr()), "act_bwd")
+                dy2 = g
+            else:
+                pf = pre.float().requires_grad_(True)
+                with torch.enable_grad():
+                    a = torch.nn.functional.gelu(pf, approximate="tanh") if act == "gelu" \
+                        else torch.nn.functional.silu(pf)
+                dy2 = torch.autograd.grad(a, pf, dy2.float())[0].to(dy2.dtype)
+        dx = dw = dbias = da = db = None
+        r = 0 if lora_a is None else lora_a.shape[0]
+        native = lib is not None and _GEMM_NATIVE == "native" and gemm_supported(M, K, Nn)
+        ts = None
+        if r:
+            # Ts = s * dY B  [M, r]
+            if native and r in (16, 32, 64):
+                ts = gemm_native(dy2, lora_b.t().contiguous(), alpha=s)
+            else:
+                ts = (dy2 @ lora_b) * s
+        if need[0]:
+            if native:
+                wt_ = wt if wt is not None else w.t().contiguous()
+                if r in (16, 32, 64):
+                    dx = gemm_native(dy2, wt_, lora_h=ts, lora_b=lora_a.t().contiguous())
+                else:
+                    dx = gemm_native(dy2, wt_)
+                    if r:
+                        dx = dx + ts @ lora_a
+            else:
+                dx = dy2 @ w
+                if r:
+                    dx = dx + ts @ lora_a
+            dx = dx.view(shp)
+        if need[1]:
+            dw = dy2.t() @ x2
+        if has_bias and need[2]:
+            dbias = dy2.sum(0)
+        if r and need[3]:
+            da = ts.t() @ x2
+        if r and need[4]:
+            db = dy2.t() @ h
+        return dx, dw, dbias, da, db, None, None, d_res, dgate, None
+
+
+def linear(x, w, bias=None, lora=None, act=None, residual=None, gate=None, wt=None):
+    """Fused linear. lora = (A [r,K], B [N,r], scale) or None; act in {None,"gelu","silu"};
+    residual [.., N] and gate [B, N] give ``residual + gate * y``."""
+    if _native_ok(x, w, bias) and x.shape[-1] % 8 == 0:
+        a, b, s = lora if lora is not None else (None, None, 1.0)
+        if gate is not None and gate.requires_grad:
+            # trainable modulation: keep the gate outside so that its gradient is produced
+            y = _FusedLinear.apply(x, w, bias, a, b, float(s), act, None, None, wt)
+            return gate_residual(residual, y, gate)
+        return _FusedLinear.apply(x, w, bias, a, b, float(s), act, residual, gate, wt)
+    y = R.linear(x, w, bias, lora, act, None, None)
+    if gate is not None or residual is not None:
+        y = R.gate_residual(residual, y, gate)
+    return y
+
+
+class _SmallLinear(torch.autograd.Function):
+    """Conditioning-vector linear (M <= 8 rows): y = f_out(silu_in?(x) W^T + b)."""
+
+    @staticmethod
+    def forward(ctx, x, w, bias, silu_in):
+        x2 = _c(x).view(-1, x.shape[-1])
+        M, K = x2.shape
+        Nn = w.shape[0]
+        y = torch.empty(M, Nn, dtype=x.dtype, device=x.device)
+        N.check(N.require().eri_gemv_bf16(x2.data_ptr(), w.data_ptr(), N.ptr(bias), y.data_ptr(),
+                                          M, Nn, K, x2.stride(0), w.stride(0), Nn,
+                                          1 if silu_in else 0, 0, N.stream_ptr()), "gemv")
+        ctx.save_for_backward(x2, w)
+        ctx.meta = (x.shape, silu_in, bias is not None)
+        return y.view(*x.shape[:-1], Nn)
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2, w = ctx.saved_tensors
+        shp, silu_in, has_bias = ctx.meta
+        dy2 = dy.reshape(-1, dy.shape[-1])
+        xin = torch.nn.functional.silu(x2.float()).to(x2.dtype) if silu_in else x2
+        dx = dw = db = None
+        if ctx.needs_input_grad[0]:
+            dx = dy2 @ w
+            if silu_in:
+                xf = x2.float()
+                sg = torch.sigmoid(xf)
+                dx = (dx.float() * (sg * (1 + xf * (1 - sg)))).to(x2.dtype)
+            dx = dx.view(shp)
+        if ctx.needs_input_grad[1]:
+            dw = dy2.t() @ xin
+        if has_bias and ctx.needs_input_grad[2]:
+            db = dy2.sum(0)
+        return dx, dw, db, None
+
+
+def small_linear(x, w, bias=None, silu_in=False):
+    """Linear on a handful of rows (adaLN modulation and embedders); SiLU on the input optional."""
+    rows = x.numel() // x.shape[-1]
+    if _native_ok(x, w, bias) and rows <= 8 and x.shape[-1] % 8 == 0 and x.shape[-1] * rows <= 50000:
+        return _SmallLinear.apply(x, w, bias, silu_in)
+    xin = torch.nn.functional.silu(x) if silu_in else x
+    return torch.nn.functional.linear(xin, w, bias)
+
+
+# ---------------------------------------------------------------------------- attention
+def attention(q, k, v, scale=None, mask=None):
+    """Non-causal attention over token-major [B, L, H, Dh] tensors."""
+    if _ATTN_NATIVE == "native" and mask is None and _native_ok(q, k, v):
+        from . import flash_attn as FA
+        if FA.supported(q, k, v):
+            return FA.flash_attention(q, k, v, scale)
+    return R.attention(q, k, v, scale, mask)
+
+
+# ---------------------------------------------------------------------------- losses / noise
+class _MseLoss(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, pred, target, weight):
+        pred, target = _c(pred), _c(target)
+        n = pred.numel()
+        npb = n // pred.shape[0]
+        loss = torch.zeros((), dtype=torch.float32, device=pred.device)
+        dpred = torch.empty_like(pred)
+        w = None if weight is None else weight.float().contiguous()
+        N.check(N.require().eri_mse_fwd_bwd(pred.data_ptr(), target.data_ptr(), N.ptr(w),
+                                            loss.data_ptr(), dpred.data_ptr(), n, npb, 1.0,
+                                            N.stream_ptr()), "mse")
+        ctx.save_for_backward(dpred)
+        return loss
+
+    @staticmethod
+    def backward(ctx, g):
+        (dpred,) = ctx.saved_tensors
+        return dpred * g.to(dpred.dtype), None, None
+
+
+def mse_loss(pred, target, weight=None):
+    """mean(weight[b] * (pred - target)^2) with the gradient produced in the same pass."""
+    if _native_ok(pred, target) and pred.numel() % 8 == 0 and (pred.numel() // pred.shape[0]) % 8 == 0:
+        return _MseLoss.apply(pred, target, weight)
+    return R.mse(pred, target, weight)
+
+
+def noise_mix(x0, coef, seed: int, offset: int = 0, eps=None, patch=2, want_eps=False):
+    """Build x_t and the regression target from clean latents in one pass.
+
+    x0 [B, C, H, W]; coef [4, B] fp32 rows (a, s, ca, cb): x_t = a*x0 + s*eps,
+    target = ca*eps + cb*x0. Noise comes from a Philox counter stream (seed, offset) unless
+    ``eps`` is given. Returns token-major (x_t, target[, eps]) of shape [B, HW/p^2, C*p*p].
+    """
+    B, C, H, W = x0.shape
+    if _native_ok(x0, eps) and (B * C * H * W) % 4 == 0:
+        x0 = _c(x0)
+        L, D = (H // patch) * (W // patch), C * patch * patch
+        xt = torch.empty(B, L, D, dtype=x0.dtype, device=x0.device)
+        tg = torch.empty_like(xt)
+        eo = torch.empty_like(xt) if want_eps else None
+        cf = coef.float().contiguous()
+        N.check(N.require().eri_noise_mix(x0.data_ptr(), N.ptr(_c(eps)), cf.data_ptr(),
+                                          xt.data_ptr(), tg.data_ptr(), N.ptr(eo), B, C, H, W,
+                                          patch, seed, offset, N.stream_ptr()), "noise_mix")
+        return (xt, tg, eo) if want_eps else (xt, tg)
+    if eps is None:
+        gen = torch.Generator(device=x0.device).manual_seed(seed + offset)
+        eps = torch.randn(x0.shape, generator=gen, device=x0.device, dtype=torch.float32).to(x0.dtype)
+    xt, tg = R.noise_mix(x0, eps, coef, patch)
+    return (xt, tg, R.patchify(eps, patch)) if want_eps else (xt, tg)
+
+
+def randn_bf16(shape, seed: int, offset: int = 0, device="cuda", mean=0.0, std=1.0):
+    out = torch.empty(shape, dtype=torch.bfloat16, device=device)
+    if out.is_cuda and _BACKEND == "fused":
+        N.check(N.require().eri_randn_bf16(out.data_ptr(), out.numel(), seed, offset, mean, std,
+                                           N.stream_ptr()), "randn")
+        return out
+    gen = torch.Generator(device=out.device).manual_seed(seed + offset)
+    return (torch.randn(shape, generator=gen, device=out.device) * std + mean).to(torch.bfloat16)
+
+
+def sumsq(flat, out=None):
+    """Sum of squares of a flat bf16 buffer into a device fp32 scalar (no host sync)."""
+    if out is None:
+        out = torch.zeros((), dtype=torch.float32, device=flat.device)
+    else:
+        out.zero_()
+    if _native_ok(flat):
+        N.check(N.require().eri_sumsq_bf16(flat.data_ptr(), flat.numel(), out.data_ptr(),
+                                           N.stream_ptr()), "sumsq")
+    else:
+        out.add_(flat.float().pow(2).sum())
+    return out

@@ -1,0 +1,58 @@
+"""Flat parameter arena.
+
+All trainable parameters of a run live in ONE contiguous buffer (and their gradients in a second
+one); each ``nn.Parameter`` is re-pointed to a view. Every per-tensor loop of the reference
+(global-norm clipping with one device->host copy per tensor, crates/training/src/optimizer.rs:88-123;
+per-parameter optimizer updates, src/trainers/pipeline_flux_lora_sequential.rs:749-794; DDP bucket
+flattening, crates/training/src/distributed.rs:284-319) becomes a single launch over the arena,
+and the data-parallel reduce-scatter operates on the same buffer without a flatten copy.
+
+Each parameter is padded to a multiple of ``align`` elements (256 = the optimizer's quantisation
+block), so quantisation blocks never straddle two tensors and shards can be cut on block edges.
+"""
+from __future__ import annotations
+
+import torch
+
+
+class ParamArena:
+    def __init__(self, params, align: int = 256, shard_multiple: int = 1):
+        params = [p for p in params if p.requires_grad]
+        if not params:
+            raise ValueError("no trainable parameters")
+        dt, dev = params[0].dtype, params[0].device
+        for p in params:
+            if p.dtype != dt or p.device != dev:
+                raise ValueError("arena parameters must share dtype and device")
+        self.params = params
+        self.align = align
+        self.offsets, off = [], 0
+        for p in params:
+            self.offsets.append(off)
+            off += (p.numel() + align - 1) // align * align
+        unit = align * max(1, shard_multiple)
+        self.numel = (off + unit - 1) // unit * unit
+        self.data = torch.zeros(self.numel, dtype=dt, device=dev)
+        self.grad = torch.zeros(self.numel, dtype=dt, device=dev)
+        with torch.no_grad():
+            for p, o in zip(params, self.offsets):
+                n = p.numel()
+                self.data[o:o + n].copy_(p.detach().reshape(-1))
+                p.data = self.data[o:o + n].view(p.shape)
+                p.grad = self.grad[o:o + n].view(p.shape)
+
+    def zero_grad(self):
+        self.grad.zero_()
+
+    def rebind_grads(self):
+        """Re-attach ``.grad`` views (after something set them to None)."""
+        for p, o in zip(self.params, self.offsets):
+            if p.grad is None or p.grad.data_ptr() != self.grad[o:].data_ptr():
+                p.grad = self.grad[o:o + p.numel()].view(p.shape)
+
+    def shard(self, rank: int, world: int):
+        n = self.numel // world
+        return self.data[rank * n:(rank + 1) * n], self.grad[rank * n:(rank + 1) * n]
+
+    def named_slices(self, names):
+        return {n: (o, p.numel(), tuple(p.shape)) for n, p, o in zip(names, self.params, self.offsets)}

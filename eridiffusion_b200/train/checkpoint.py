@@ -1,0 +1,167 @@
+"""Checkpoint layouts (kept from the reference so that its files and tools keep working).
+
+* LoRA, primary:  ``{root}/step_{step:06}/lora.safetensors`` — bf16 tensors keyed
+  ``lora.{module}.lora.{A,B}``, metadata ``step``, ``seed``, ``dtype_policy``; optional
+  ``ema.safetensors`` (keys ``ema.{name}``, metadata + ``ema_decay``); ``meta.json`` with
+  ``step, seed, time, param_names, lora_file, ema_file``
+  (crates/training/src/flux_trainer.rs:416-439, 633-666). Resume picks the highest ``step_*``.
+* Full / generic: ``{root}/checkpoint-{step:06}/model.safetensors`` (keys ``model.{name}``),
+  ``optimizer.safetensors`` (keys ``optimizer.{name}``), ``metadata.json``; keep-last-N cleanup
+  (src/trainers/checkpoint_saver.rs:63-118, 329-371).
+* Adapter: ``{root}/checkpoint-{step}/adapter_model.safetensors`` + ``checkpoint-latest`` symlink,
+  metadata ``format, network_type, rank, alpha`` (crates/training/src/checkpoint_manager.rs:51-108).
+* kohya / ComfyUI export: ``lora_unet_{module}.lora_down.weight`` etc.
+* Sharded optimizer state: ``optimizer.rank{r}.safetensors`` with the 8-bit codes and block scales,
+  and the world size / shard map in ``meta.json``.
+"""
+from __future__ import annotations
+
+import json
+import os
+import re
+import shutil
+import time
+from pathlib import Path
+
+import torch
+
+from ..adapters import adapter_state_dict, load_adapter_state_dict
+from ..io import safetensors as st
+
+
+def _rank_world(trainer):
+    gs = trainer.grad_sync
+    return (gs.rank, gs.world_size) if gs is not None else (0, 1)
+
+
+def _optimizer_tensors(opt):
+    sd = opt.state_dict() if hasattr(opt, "state_dict") else {}
+    tensors, scalars = {}, {}
+    for k, v in sd.items():
+        if torch.is_tensor(v):
+            tensors[f"optimizer.{k}"] = v
+        elif isinstance(v, (int, float, str)):
+            scalars[k] = v
+        elif isinstance(v, (tuple, list)) and all(isinstance(x, (int, float)) for x in v):
+            scalars[k] = list(v)
+    return tensors, scalars
+
+
+def save_training_checkpoint(trainer, root):
+    root = Path(root)
+    rank, world = _rank_world(trainer)
+    step, cfg = trainer.step, trainer.cfg
+    if trainer.adapters is not None:
+        d = root / f"step_{step:06d}"
+        d.mkdir(parents=True, exist_ok=True)
+        meta = {"step": step, "seed": cfg.seed, "time": time.time(),
+                "param_names": trainer.param_names, "lora_file": "lora.safetensors",
+                "ema_file": None, "world_size": world,
+                "optimizer_files": [f"optimizer.rank{r}.safetensors" for r in range(world)]}
+        if rank == 0:
+            sd = adapter_state_dict(trainer.adapters, "eri")
+            st.save_file({k: v.to(torch.bfloat16) for k, v in sd.items()}, d / "lora.safetensors",
+                         {"step": step, "seed": cfg.seed, "dtype_policy": "storage=bf16,compute=fp32"})
+            if trainer.ema is not None:
+                st.save_file(trainer.ema.state_dict(trainer.param_names), d / "ema.safetensors",
+                             {"step": step, "seed": cfg.seed, "ema_decay": trainer.ema.decay})
+                meta["ema_file"] = "ema.safetensors"
+        tensors, scalars = _optimizer_tensors(trainer.optimizer)
+        if tensors:
+            st.save_file(tensors, d / f"optimizer.rank{rank}.safetensors",
+                         {"step": step, "rank": rank, "world_size": world, **{k: json.dumps(v) for k, v in scalars.items()}})
+        if rank == 0:
+            (d / "meta.json").write_text(json.dumps(meta, indent=1))
+            _cleanup(root, r"step_(\d+)$", cfg.keep_last)
+        return d
+    d = root / f"checkpoint-{step:06d}"
+    d.mkdir(parents=True, exist_ok=True)
+    if rank == 0:
+        sd = {f"model.{n}": p.detach() for n, p in trainer.model.named_parameters()}
+        st.save_file(sd, d / "model.safetensors", {"format": "pt", "step": step})
+    tensors, scalars = _optimizer_tensors(trainer.optimizer)
+    name = "optimizer.safetensors" if world == 1 else f"optimizer.rank{rank}.safetensors"
+    if tensors:
+        st.save_file(tensors, d / name, {"step": step, "rank": rank, "world_size": world})
+    if rank == 0:
+        (d / "metadata.json").write_text(json.dumps(
+            {"step": step, "seed": cfg.seed, "time": time.time(), "world_size": world,
+             "optimizer": scalars, "lr": trainer.optimizer.param_groups[0]["lr"]}, indent=1))
+        _cleanup(root, r"checkpoint-(\d+)$", cfg.keep_last)
+        latest = root / "checkpoint-latest"
+        try:
+            if latest.is_symlink() or latest.exists():
+                latest.unlink()
+            latest.symlink_to(d.name)
+        except OSError:
+            pass
+    return d
+
+
+def _cleanup(root, pattern, keep_last):
+    if not keep_last:
+        return
+    found = sorted((int(m.group(1)), p) for p in Path(root).iterdir()
+                   if (m := re.match(pattern, p.name)) and p.is_dir())
+    for _, p in found[:-keep_last]:
+        shutil.rmtree(p, ignore_errors=True)
+
+
+def find_latest(root, pattern=r"(?:step_|checkpoint-)(\d+)$"):
+    root = Path(root)
+    if not root.is_dir():
+        return None
+    found = sorted((int(m.group(1)), p) for p in root.iterdir()
+                   if (m := re.match(pattern, p.name)) and p.is_dir())
+    return found[-1][1] if found else None
+
+
+def load_latest_training_checkpoint(trainer, root):
+    """Restore parameters (+EMA, + optimizer state when its world size matches). Returns
+    ``(step, seed)`` or ``None`` when there is nothing to resume from."""
+    d = find_latest(root)
+    if d is None:
+        return None
+    rank, world = _rank_world(trainer)
+    dev = trainer.arena.data.device
+    if trainer.adapters is not None:
+        meta = json.loads((d / "meta.json").read_text())
+        sd = st.load_file(d / meta["lora_file"], device=dev)
+        load_adapter_state_dict(trainer.adapters, sd, strict=True)
+        if trainer.ema is not None and meta.get("ema_file"):
+            trainer.ema.load_state_dict(st.load_file(d / meta["ema_file"], device=dev), trainer.param_names)
+        step, seed = int(meta["step"]), int(meta["seed"])
+        saved_world = int(meta.get("world_size", 1))
+    else:
+        meta = json.loads((d / "metadata.json").read_text())
+        sd = st.load_file(d / "model.safetensors", device=dev)
+        own = dict(trainer.model.named_parameters())
+        with torch.no_grad():
+            for k, v in sd.items():
+                own[k[len("model."):]].copy_(v)
+        step, seed = int(meta["step"]), int(meta["seed"])
+        saved_world = int(meta.get("world_size", 1))
+    opt_file = d / (f"optimizer.rank{rank}.safetensors" if (saved_world > 1 or trainer.adapters is not None)
+                    else "optimizer.safetensors")
+    if saved_world == world and opt_file.exists() and hasattr(trainer.optimizer, "load_state_dict"):
+        t = st.load_file(opt_file, device=dev)
+        md = st.read_metadata(opt_file)
+        sdict = {k[len("optimizer."):]: v for k, v in t.items()}
+        sdict["step"] = int(md.get("step", step))
+        sdict["lr"] = trainer.optimizer.param_groups[0]["lr"]
+        try:
+            trainer.optimizer.load_state_dict(sdict)
+        except (KeyError, RuntimeError):
+            pass  # different optimizer kind: moments restart, as in the reference's Flux path
+    trainer.step = step
+    trainer.micro = step * trainer.cfg.grad_accum
+    return step, seed
+
+
+def export_lora(trainer, path, layout="kohya"):
+    """Single-file export for other tools (kohya / ComfyUI / PEFT key conventions)."""
+    sd = adapter_state_dict(trainer.adapters, layout)
+    acfg = trainer.cfg.adapter
+    st.save_file({k: v.to(torch.bfloat16) if v.dim() else v.float() for k, v in sd.items()}, path,
+                 {"format": "eridiffusion", "network_type": acfg.kind if acfg else "lora",
+                  "rank": acfg.rank if acfg else "", "alpha": (acfg.alpha if acfg and acfg.alpha else "")})

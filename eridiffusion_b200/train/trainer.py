@@ -1,0 +1,211 @@
+"""Training loop for all model families.
+
+One ``Trainer`` drives: timestep sampling -> fused noise-mix/patchify -> model forward ->
+fused weighted-MSE (loss + gradient in one pass) -> backward -> gradient synchronisation
+(``parallel.GradSync``: NCCL or the fused reduce-scatter + 8-bit AdamW + all-gather kernel) ->
+device-side clip + optimizer -> EMA. Nothing in the step reads a scalar back to the host; the
+loss tensor is returned and read only where the caller logs it.
+
+Reference loop being covered: crates/training/src/flux_trainer.rs:286-414
+(``train_step_precomputed``: noise, sigma, forward, MSE, accumulate, clip, step, EMA),
+crates/training/src/run.rs:208-308 (per-step console/CSV line, periodic checkpoint),
+crates/training/src/chroma/train.rs:1262-1378 (non-finite loss/grad -> skip + back-off),
+crates/training/src/gradient_accumulator.rs:107-146.
+"""
+from __future__ import annotations
+
+import json
+import math
+import os
+import time
+from dataclasses import dataclass, field
+from pathlib import Path
+
+import torch
+
+from ..adapters import (AdapterConfig, adapter_parameters, adapter_state_dict, inject_adapters,
+                        load_adapter_state_dict)
+from ..io import safetensors as st
+from ..objectives import DDPM, FlowMatching, loss_fn
+from ..ops import functional as F
+from ..optim import EMA, GradScaler, LRSchedule, ParamArena, create_optimizer
+
+
+@dataclass
+class TrainerConfig:
+    mode: str = "lora"                      # lora | full
+    adapter: AdapterConfig | None = None
+    objective: str = "flow"                 # flow | eps | v | sample
+    timestep_sampler: str = "logit_normal"
+    timestep_kw: dict = field(default_factory=dict)
+    guidance: float | None = 3.5            # value fed to the guidance embedder (None: 1.0)
+    optimizer: str = "adamw8bit"
+    lr: float = 1e-4
+    weight_decay: float = 0.01
+    betas: tuple = (0.9, 0.999)
+    eps: float = 1e-8
+    lr_schedule: str = "constant"
+    warmup_steps: int = 0
+    total_steps: int = 0
+    grad_accum: int = 1
+    max_grad_norm: float = 1.0
+    loss: str = "mse"
+    min_snr_gamma: float | None = None
+    ema_decay: float | None = None
+    stochastic_rounding: bool = True
+    patch: int = 2
+    seed: int = 0
+    out_dir: str | None = None
+    ckpt_every: int = 0
+    keep_last: int = 0
+    log_csv: str | None = None
+    nan_policy: str = "skip"                # skip | raise
+    lr_backoff: float = 0.5
+    activation_checkpointing: bool = False
+
+
+class Trainer:
+    def __init__(self, model, cfg: TrainerConfig, grad_sync=None, forward_fn=None):
+        self.model, self.cfg = model, cfg
+        self.forward_fn = forward_fn or default_forward
+        self.adapters = None
+        if cfg.mode == "lora":
+            acfg = cfg.adapter or AdapterConfig()
+            if acfg.target == [r".*"] and hasattr(model, "lora_targets"):
+                acfg.target = model.lora_targets()
+            self.adapters = inject_adapters(model, acfg, seed=cfg.seed)
+            params = adapter_parameters(self.adapters)
+            self.param_names = [f"{path}.{n}" for path in sorted(self.adapters)
+                                for n, _ in self.adapters[path].named_parameters()]
+        else:
+            named = [(n, p) for n, p in model.named_parameters() if p.requires_grad]
+            params = [p for _, p in named]
+            self.param_names = [n for n, _ in named]
+        world = grad_sync.world_size if grad_sync is not None else 1
+        self.arena = ParamArena(params, shard_multiple=world)
+        self.grad_sync = grad_sync
+        shard = grad_sync.optimizer_shard() if grad_sync is not None else None
+        kw = dict(lr=cfg.lr, weight_decay=cfg.weight_decay, betas=cfg.betas, eps=cfg.eps)
+        if cfg.optimizer.lower().replace("_", "") in ("adamw8bit", "adam8bit", "adamw"):
+            kw.update(stochastic_rounding=cfg.stochastic_rounding, seed=cfg.seed, shard=shard)
+        self.optimizer = create_optimizer(cfg.optimizer, self.arena, **kw)
+        if grad_sync is not None:
+            grad_sync.attach(self.arena, self.optimizer)
+        self.schedule = LRSchedule(cfg.lr, cfg.lr_schedule, cfg.warmup_steps, cfg.total_steps)
+        self.scaler = GradScaler(enabled=False)
+        self.ema = EMA(self.arena, cfg.ema_decay) if cfg.ema_decay else None
+        if cfg.objective == "flow":
+            self.objective = FlowMatching(cfg.timestep_sampler, cfg.timestep_kw)
+        else:
+            pred = {"eps": "epsilon", "v": "v", "sample": "sample"}[cfg.objective]
+            self.objective = DDPM(prediction=pred, min_snr_gamma=cfg.min_snr_gamma)
+        self.step = 0
+        self.micro = 0
+        self.nan_skips = 0
+        self._gen = None
+        self._sumsq = None
+        self._csv = None
+
+    # ------------------------------------------------------------------ one micro-step
+    def _generator(self, device):
+        if self._gen is None or self._gen.device != torch.device(device):
+            rank = self.grad_sync.rank if self.grad_sync is not None else 0
+            self._gen = torch.Generator(device=device).manual_seed(self.cfg.seed * 1000003 + rank)
+        return self._gen
+
+    def train_step(self, batch: dict):
+        """batch: ``latents`` [B, C, H, W] plus the conditioning tensors the model's forward
+        function consumes. Returns the (device) loss tensor of this micro-batch."""
+        cfg = self.cfg
+        x0 = batch["latents"]
+        B = x0.shape[0]
+        dev = x0.device
+        t = self.objective.sample_t(B, self._generator(dev), dev)
+        coef = self.objective.coefficients(t)
+        rank = self.grad_sync.rank if self.grad_sync is not None else 0
+        xt, target = F.noise_mix(x0, coef, seed=cfg.seed + 7919 * rank, offset=self.micro << 24,
+                                 eps=batch.get("noise"), patch=cfg.patch)
+        pred = self.forward_fn(self.model, xt, self.objective.model_time(t), batch, cfg)
+        loss = loss_fn(cfg.loss, pred, target, self.objective.loss_weight(t))
+        (loss / cfg.grad_accum).backward()
+        self.micro += 1
+        if self.micro % cfg.grad_accum == 0:
+            self._optimizer_step()
+        return loss.detach()
+
+    def _optimizer_step(self):
+        cfg = self.cfg
+        lr = self.schedule.apply(self.optimizer, self.step)
+        if self.grad_sync is not None and self.grad_sync.fused_optimizer:
+            # reduce-scatter + clip + 8-bit AdamW + all-gather in the communication kernel
+            self.grad_sync.reduce_and_step(lr=lr, max_grad_norm=cfg.max_grad_norm, step=self.step + 1)
+        else:
+            if self.grad_sync is not None:
+                self.grad_sync.reduce_grads()
+            if hasattr(self.optimizer, "arena"):
+                sumsq = None
+                if cfg.max_grad_norm > 0 or cfg.nan_policy == "skip":
+                    if self.grad_sync is not None:
+                        self._sumsq = self.grad_sync.grad_sumsq(self._sumsq)
+                    else:
+                        self._sumsq = F.sumsq(self.arena.grad, self._sumsq)
+                    sumsq = self._sumsq
+                self.optimizer.step(grad_sumsq=sumsq, max_grad_norm=cfg.max_grad_norm)
+            else:
+                if cfg.max_grad_norm > 0:
+                    torch.nn.utils.clip_grad_norm_(self.arena.params, cfg.max_grad_norm)
+                self.optimizer.step()
+                self.arena.rebind_grads()
+            if self.grad_sync is not None:
+                self.grad_sync.gather_params()
+        self.arena.zero_grad()
+        if self.ema is not None:
+            self.ema.update()
+        self.step += 1
+        if cfg.ckpt_every and cfg.out_dir and self.step % cfg.ckpt_every == 0:
+            self.save_checkpoint()
+
+    def grad_norm(self):
+        """Last global gradient norm (device tensor) when clipping or NaN checks are on."""
+        return None if self._sumsq is None else self._sumsq.sqrt()
+
+    # ------------------------------------------------------------------ logging
+    def log_row(self, loss, sec_per_it, ckpt_path=""):
+        """Append ``step,loss,grad_norm,sec_per_it,alloc_mb,ckpt_path`` (the reference's
+        TRAIN_LOG_CSV columns, crates/training/src/run.rs:181-188)."""
+        path = self.cfg.log_csv or os.environ.get("TRAIN_LOG_CSV")
+        if not path:
+            return
+        new = not os.path.exists(path)
+        with open(path, "a") as f:
+            if new:
+                f.write("step,loss,grad_norm,sec_per_it,alloc_mb,ckpt_path\n")
+            gn = self.grad_norm()
+            alloc = torch.cuda.memory_allocated() / 2 ** 20 if torch.cuda.is_available() else 0.0
+            f.write(f"{self.step},{float(loss):.6f},{float(gn) if gn is not None else float('nan'):.6f},"
+                    f"{sec_per_it:.6f},{alloc:.1f},{ckpt_path}\n")
+
+    # ------------------------------------------------------------------ checkpoints
+    def save_checkpoint(self, root=None):
+        """LoRA: ``{root}/step_{step:06}/lora.safetensors`` (+ ``ema.safetensors``, ``meta.json``),
+        the phase-4 layout (crates/training/src/flux_trainer.rs:416-439, 633-666). Full fine-tune:
+        ``{root}/checkpoint-{step:06}/model.safetensors`` with ``model.`` key prefix plus
+        ``optimizer.safetensors`` and ``metadata.json`` (src/trainers/checkpoint_saver.rs:63-118)."""
+        from .checkpoint import save_training_checkpoint
+        return save_training_checkpoint(self, root or self.cfg.out_dir)
+
+    def load_latest_checkpoint(self, root=None):
+        from .checkpoint import load_latest_training_checkpoint
+        return load_latest_training_checkpoint(self, root or self.cfg.out_dir)
+
+
+def default_forward(model, xt, t, batch, cfg):
+    """MMDiT-style call: model(img_tokens, txt, t, pooled, guidance)."""
+    g = None
+    if getattr(getattr(model, "cfg", None), "guidance_embed", False):
+        gv = 1.0 if cfg.guidance is None else cfg.guidance
+        g = torch.full((xt.shape[0],), float(gv), device=xt.device)
+    if cfg.activation_checkpointing:
+        from .act_checkpoint import checkpointed_forward
+        return checkpointed_forward(model, xt, batch["txt"], t, batch["pooled"], g)
+    return model(xt, batch["txt"], t, batch["pooled"], g, grid_hw=batch.get("grid_hw"))

@@ -1,0 +1,230 @@
+"""Numerics of every CUDA kernel against the plain PyTorch fp32 statement of the same op."""
+import math
+
+import pytest
+import torch
+
+from eridiffusion_b200.ops import functional as F
+from eridiffusion_b200.ops import reference as R
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+BF = torch.bfloat16
+
+
+def rnd(*s, scale=1.0, seed=0):
+    g = torch.Generator(device=DEV).manual_seed(seed + sum(s))
+    return (torch.randn(*s, device=DEV, generator=g) * scale).to(BF)
+
+
+def close(a, b, atol, rtol=2e-2):
+    a, b = a.float(), b.float()
+    assert a.shape == b.shape
+    err = (a - b).abs()
+    tol = atol + rtol * b.abs()
+    assert bool((err <= tol).all()), f"max err {err.max().item():.4g} (allowed {tol.max().item():.4g})"
+
+
+@pytest.mark.parametrize("rms", [False, True])
+@pytest.mark.parametrize("D", [256, 3072, 4096 + 8])
+def test_norm_modulate_fwd_bwd(rms, D):
+    B, L = 2, 67
+    x = rnd(B, L, D).requires_grad_()
+    mod = rnd(B, 3 * D, scale=0.3).requires_grad_()
+    w = rnd(D, scale=0.5).requires_grad_()
+    sh, sc, _ = mod.split(D, dim=-1)
+    y = F.norm_modulate(x, sc, sh, w, None, 1e-6, rms)
+    xr, modr, wr = (t.detach().float().requires_grad_() for t in (x, mod, w))
+    shr, scr, _ = modr.split(D, dim=-1)
+    yr = R.norm_modulate(xr, scr, shr, wr, None, 1e-6, rms)
+    close(y, yr, 3e-2)
+    g = rnd(B, L, D, seed=5)
+    y.backward(g)
+    yr.backward(g.float())
+    close(x.grad, xr.grad, 3e-2, 3e-2)
+    close(mod.grad, modr.grad, 0.15, 3e-2)
+    close(w.grad, wr.grad, 0.3, 3e-2)
+
+
+@pytest.mark.parametrize("Dh", [64, 128])
+def test_qknorm_rope_joint(Dh):
+    B, H, Lt, Li = 2, 4, 24, 40
+    D = H * Dh
+    cos = torch.cos(torch.rand(Lt + Li, Dh // 2, device=DEV) * 6)
+    sin = torch.sin(torch.rand(Lt + Li, Dh // 2, device=DEV) * 6)
+    ins = [rnd(B, Lt, 3 * D).requires_grad_(), rnd(B, Li, 3 * D, seed=1).requires_grad_()]
+    scales = [rnd(Dh, scale=0.5, seed=i).add(1).requires_grad_() for i in range(4)]
+    q, k, v = F.qknorm_rope_joint([(ins[0], scales[0], scales[1]), (ins[1], scales[2], scales[3])], cos, sin, H)
+    insr = [t.detach().float().requires_grad_() for t in ins]
+    scr = [t.detach().float().requires_grad_() for t in scales]
+    o0 = R.qknorm_rope(insr[0], scr[0], scr[1], cos[:Lt], sin[:Lt], H)
+    o1 = R.qknorm_rope(insr[1], scr[2], scr[3], cos[Lt:], sin[Lt:], H)
+    qr, kr, vr = (torch.cat([a, b], 1) for a, b in zip(o0, o1))
+    close(q, qr, 3e-2); close(k, kr, 3e-2); close(v, vr, 1e-6)
+    gq, gk, gv = rnd(*q.shape, seed=7), rnd(*q.shape, seed=8), rnd(*q.shape, seed=9)
+    torch.autograd.backward([q, k, v], [gq, gk, gv])
+    torch.autograd.backward([qr, kr, vr], [gq.float(), gk.float(), gv.float()])
+    for a, b in zip(ins, insr):
+        close(a.grad, b.grad, 4e-2, 3e-2)
+    for a, b in zip(scales, scr):
+        close(a.grad, b.grad, 0.5, 3e-2)
+
+
+def test_gate_residual_and_acts():
+    B, L, D = 2, 33, 512
+    x, y = rnd(B, L, D).requires_grad_(), rnd(B, L, D, seed=1).requires_grad_()
+    gate = rnd(B, D, scale=0.5).requires_grad_()
+    out = F.gate_residual(x, y, gate)
+    xr, yr, gr = (t.detach().float().requires_grad_() for t in (x, y, gate))
+    outr = R.gate_residual(xr, yr, gr)
+    close(out, outr, 2e-2)
+    g = rnd(B, L, D, seed=3)
+    out.backward(g); outr.backward(g.float())
+    close(x.grad, xr.grad, 1e-2); close(y.grad, yr.grad, 2e-2); close(gate.grad, gr.grad, 0.2, 3e-2)
+    for fn, rf in ((F.gelu_tanh, R.gelu_tanh), (F.silu, R.silu)):
+        a = rnd(4, 1024).requires_grad_()
+        ar = a.detach().float().requires_grad_()
+        o, orf = fn(a), rf(ar)
+        close(o, orf, 1e-2)
+        o.backward(g.view(-1)[:4096].view(4, 1024)); orf.backward(g.view(-1)[:4096].view(4, 1024).float())
+        close(a.grad, ar.grad, 2e-2)
+    for mode in ("gelu", "silu"):
+        for af in (True, False):
+            h = rnd(5, 7, 256).requires_grad_()
+            hr = h.detach().float().requires_grad_()
+            o, orf = F.glu(h, mode, af), R.glu(hr, mode, af)
+            close(o, orf, 2e-2)
+            gg = rnd(5, 7, 128, seed=4)
+            o.backward(gg); orf.backward(gg.float())
+            close(h.grad, hr.grad, 3e-2)
+
+
+def test_noise_mix_and_mse():
+    B, C, H, W = 2, 16, 32, 32
+    x0 = rnd(B, C, H, W)
+    eps = rnd(B, C, H, W, seed=3)
+    t = torch.tensor([0.3, 0.8], device=DEV)
+    coef = torch.stack([1 - t, t, torch.ones_like(t), -torch.ones_like(t)])
+    xt, tg = F.noise_mix(x0, coef, seed=1, eps=eps)
+    xtr, tgr = R.noise_mix(x0, eps, coef)
+    close(xt, xtr, 1e-2); close(tg, tgr, 1e-2)
+    xt2, tg2, e2 = F.noise_mix(x0, coef, seed=11, offset=5, want_eps=True)
+    e = e2.float()
+    assert abs(e.mean().item()) < 0.02 and abs(e.std().item() - 1.0) < 0.02
+    xt3, _, e3 = F.noise_mix(x0, coef, seed=11, offset=5, want_eps=True)
+    assert torch.equal(e2, e3)
+    pred = rnd(B, 256, 64).requires_grad_()
+    w = torch.tensor([0.5, 2.0], device=DEV)
+    loss = F.mse_loss(pred, tg, w)
+    pr = pred.detach().float().requires_grad_()
+    lr_ = R.mse(pr, tg, w)
+    assert abs(loss.item() - lr_.item()) < 1e-3 * max(1.0, lr_.item())
+    loss.backward(); lr_.backward()
+    close(pred.grad, pr.grad, 1e-6, 2e-2)
+
+
+def _gemm_ref(a, b, **kw):
+    return a.float() @ b.float().t()
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 256, 64), (256, 512, 256), (512, 3072, 3072), (300, 384, 136),
+                                   (4096, 256, 1024), (256, 64, 128), (384, 16, 512)])
+def test_gemm_plain(M, N, K):
+    a, b = rnd(M, K), rnd(N, K, seed=1)
+    out = F.gemm_native(a, b)
+    torch.cuda.synchronize()
+    assert F.gemm_error_check() == 0
+    close(out, _gemm_ref(a, b), 0.05 * math.sqrt(K / 64), 2e-2)
+
+
+@pytest.mark.parametrize("bn", [256, 128, 64])
+def test_gemm_tile_variants(bn):
+    M, N, K = 640, 1024, 512
+    a, b = rnd(M, K), rnd(N, K, seed=1)
+    out = F.gemm_native(a, b, force_bn=bn)
+    assert F.gemm_error_check() == 0
+    close(out, _gemm_ref(a, b), 0.15, 2e-2)
+
+
+@pytest.mark.parametrize("r", [16, 32, 64])
+def test_gemm_lora_epilogues(r):
+    B, L, K, N = 2, 192, 512, 768
+    M = B * L
+    x, w, bias = rnd(M, K), rnd(N, K, scale=K ** -0.5, seed=1), rnd(N, seed=2)
+    A, Bm = rnd(r, K, scale=K ** -0.5, seed=3), rnd(N, r, scale=0.1, seed=4)
+    res, gate = rnd(M, N, seed=5), rnd(B, N, seed=6)
+    s = 0.5
+    h = F.gemm_native(x, A, alpha=s)
+    close(h, (x.float() @ A.float().t()) * s, 0.03)
+    pre = torch.empty(M, N, device=DEV, dtype=BF)
+    y = F.gemm_native(x, w, bias=bias, lora_h=h, lora_b=Bm, act="gelu", pre_out=pre, residual=res,
+                      gate=gate, rows_per_batch=L)
+    assert F.gemm_error_check() == 0
+    pre_ref = x.float() @ w.float().t() + bias.float() + h.float() @ Bm.float().t()
+    close(pre, pre_ref, 0.05)
+    y_ref = res.float() + gate.float().repeat_interleave(L, 0) * torch.nn.functional.gelu(pre_ref, approximate="tanh")
+    close(y, y_ref, 0.06)
+    # activation backward epilogue + column split
+    dy = rnd(M, N, seed=8)
+    wt = rnd(K, N, scale=N ** -0.5, seed=9)
+    n_split = 256
+    out1 = torch.empty(M, n_split, device=DEV, dtype=BF)
+    out2 = torch.empty(M, K - n_split, device=DEV, dtype=BF)
+    pre2 = rnd(M, K - n_split, seed=10)
+    F.gemm_native(dy, wt, out=out1, out2=out2, n_split=n_split, act="gelu_bwd", pre_in=pre2)
+    assert F.gemm_error_check() == 0
+    full = dy.float() @ wt.float().t()
+    close(out1, full[:, :n_split], 0.06)
+    pf = pre2.float().requires_grad_()
+    gd = torch.autograd.grad(torch.nn.functional.gelu(pf, approximate="tanh").sum(), pf)[0]
+    close(out2, full[:, n_split:] * gd, 0.06)
+
+
+def test_fused_linear_autograd_matches_reference():
+    B, L, K, N, r = 2, 128, 256, 384, 16
+    x = rnd(B, L, K).requires_grad_()
+    w, bias = rnd(N, K, scale=K ** -0.5, seed=1), rnd(N, seed=2)
+    A = rnd(r, K, scale=K ** -0.5, seed=3).requires_grad_()
+    Bm = rnd(N, r, scale=0.2, seed=4).requires_grad_()
+    res, gate = rnd(B, L, N, seed=5).requires_grad_(), rnd(B, N, seed=6)
+    y = F.linear(x, w, bias, lora=(A, Bm, 2.0), act="gelu", residual=res, gate=gate, wt=w.t().contiguous())
+    xr, Ar, Br, rr = (t.detach().float().requires_grad_() for t in (x, A, Bm, res))
+    yr = R.linear(xr, w.float(), bias.float(), (Ar, Br, 2.0), "gelu", rr, gate.float())
+    close(y, yr, 0.06)
+    g = rnd(B, L, N, seed=7)
+    y.backward(g); yr.backward(g.float())
+    assert F.gemm_error_check() == 0
+    close(x.grad, xr.grad, 0.08, 3e-2)
+    close(res.grad, rr.grad, 1e-2)
+    close(A.grad, Ar.grad, 0.6, 5e-2)
+    close(Bm.grad, Br.grad, 0.6, 5e-2)
+
+
+def test_small_linear():
+    x, w, b = rnd(2, 3072), rnd(1024, 3072, scale=0.02, seed=1), rnd(1024, seed=2)
+    y = F.small_linear(x, w, b, silu_in=True)
+    yr = torch.nn.functional.linear(torch.nn.functional.silu(x.float()), w.float(), b.float())
+    close(y, yr, 0.03)
+
+
+def test_adamw8bit_kernel_matches_reference():
+    from eridiffusion_b200.optim import AdamW8bit
+    torch.manual_seed(0)
+    p1 = [torch.nn.Parameter(rnd(1000, 33)), torch.nn.Parameter(rnd(4099, seed=1))]
+    p2 = [torch.nn.Parameter(p.detach().clone()) for p in p1]
+    o1 = AdamW8bit(p1, lr=1e-2, stochastic_rounding=False)
+    o2 = AdamW8bit(p2, lr=1e-2, stochastic_rounding=False)
+    for s in range(5):
+        g = rnd(o1.arena.numel, seed=100 + s)
+        o1.arena.grad.copy_(g); o2.arena.grad.copy_(g)
+        ss = F.sumsq(o1.arena.grad)
+        o1.step(grad_sumsq=ss, max_grad_norm=1.0)
+        F.set_backend("eager")
+        try:
+            o2.step(grad_sumsq=ss, max_grad_norm=1.0)
+        finally:
+            F.set_backend("fused")
+    close(o1.arena.data, o2.arena.data, 2e-2, 2e-2)
+    m1, v1 = o1.export_moments(); m2, v2 = o2.export_moments()
+    close(m1, m2, 1e-4, 5e-2); close(v1, v2, 1e-7, 0.1)
+    assert abs(ss.sqrt().item() - o1.arena.grad.float().norm().item()) < 1e-2 * ss.sqrt().item()
