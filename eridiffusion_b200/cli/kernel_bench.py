@@ -1,0 +1,145 @@
+"""Per-kernel timing against the library equivalents and the measured roofline.
+
+    python -m eridiffusion_b200.cli.kernel_bench [--what gemm,attn,elementwise,optim] [--small]
+
+Timing: CUDA events on the launching stream, >= 3 warm-up launches, L2 flushed between timed
+launches by writing a 256 MB buffer, median of the timed launches. Roofline denominators come from
+``MEASURED_PEAKS.json`` at the repository root when present (copy bandwidth and cuBLAS bf16
+throughput measured on this pool), otherwise the documented fallback (6.65 TB/s, 1.59 PFLOP/s).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import statistics
+from pathlib import Path
+
+import torch
+
+from ..ops import functional as F
+from ..ops import reference as R
+
+
+def peaks():
+    p = Path(__file__).resolve().parents[2] / "MEASURED_PEAKS.json"
+    if p.exists():
+        d = json.loads(p.read_text())
+        return d["hbm_gbs"] * 1e9, d["bf16_tflops"] * 1e12, "of measured"
+    return 6.65e12, 1.59e15, "of fallback"
+
+
+_flush = None
+
+
+def timeit(fn, iters=10, warm=3, flush=True):
+    global _flush
+    if _flush is None:
+        _flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device="cuda")
+    for _ in range(warm):
+        fn()
+    ts = []
+    for _ in range(iters):
+        if flush:
+            _flush.zero_()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        fn()
+        e1.record()
+        torch.cuda.synchronize()
+        ts.append(e0.elapsed_time(e1) * 1e-3)
+    return statistics.median(ts)
+
+
+def bench_gemm(small):
+    bw, fl, tag = peaks()
+    shapes = [(4096, 9216, 3072), (4096, 3072, 3072), (4096, 12288, 3072), (4096, 3072, 12288),
+              (512, 9216, 3072), (4608, 21504, 3072), (4608, 3072, 15360), (8192, 8192, 8192)]
+    if small:
+        shapes = [(1024, 2048, 1024), (4096, 3072, 3072)]
+    print(f"{'M':>6} {'N':>6} {'K':>6} | {'ours us':>9} {'TF/s':>7} {'frac':>6} | {'cuBLAS us':>9} {'TF/s':>7} | lora16 us")
+    for M, N, K in shapes:
+        a = torch.randn(M, K, device="cuda").bfloat16()
+        b = torch.randn(N, K, device="cuda").bfloat16()
+        out = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+        t_ours = timeit(lambda: F.gemm_native(a, b, out=out))
+        t_lib = timeit(lambda: torch.matmul(a, b.t(), out=out))
+        h = torch.randn(M, 16, device="cuda").bfloat16()
+        lb = torch.randn(N, 16, device="cuda").bfloat16()
+        la = torch.randn(16, K, device="cuda").bfloat16()
+        t_lora = timeit(lambda: F.gemm_native(a, b, out=out, lora_h=F.gemm_native(a, la, alpha=0.5), lora_b=lb))
+        fl_ = 2.0 * M * N * K
+        print(f"{M:6d} {N:6d} {K:6d} | {t_ours*1e6:9.1f} {fl_/t_ours/1e12:7.1f} {fl_/t_ours/fl:6.2f} | "
+              f"{t_lib*1e6:9.1f} {fl_/t_lib/1e12:7.1f} | {t_lora*1e6:9.1f}   ({tag})")
+    assert F.gemm_error_check() == 0
+
+
+def bench_elementwise(small):
+    bw, fl, tag = peaks()
+    B, L, D = 1, 4608, 3072
+    x = torch.randn(B, L, D, device="cuda").bfloat16()
+    mod = torch.randn(B, 3 * D, device="cuda").bfloat16()
+    sh, sc, g = mod.split(D, -1)
+    t = timeit(lambda: F.norm_modulate(x, sc, sh))
+    nb = 2 * x.numel() * 2
+    print(f"norm_modulate fwd [{L}x{D}]: {t*1e6:.1f} us  {nb/t/1e9:.0f} GB/s  {nb/t/bw:.2f} {tag}")
+    F.set_backend("eager")
+    t2 = timeit(lambda: R.norm_modulate(x, sc, sh))
+    F.set_backend("fused")
+    print(f"   eager composition: {t2*1e6:.1f} us")
+    y = torch.randn_like(x)
+    t = timeit(lambda: F.gate_residual(x, y, g))
+    print(f"gate_residual [{L}x{D}]: {t*1e6:.1f} us  {3*x.numel()*2/t/1e9:.0f} GB/s  {3*x.numel()*2/t/bw:.2f} {tag}")
+    qkv = torch.randn(B, L, 3 * D, device="cuda").bfloat16()
+    qs = torch.ones(128, device="cuda").bfloat16()
+    cos = torch.rand(L, 64, device="cuda"); sin = torch.rand(L, 64, device="cuda")
+    t = timeit(lambda: F.qknorm_rope_joint([(qkv, qs, qs)], cos, sin, 24))
+    print(f"qknorm_rope [{L}x{3*D}]: {t*1e6:.1f} us  {2*qkv.numel()*2/t/1e9:.0f} GB/s  {2*qkv.numel()*2/t/bw:.2f} {tag}")
+    h = torch.randn(L, 12288, device="cuda").bfloat16()
+    t = timeit(lambda: F.gelu_tanh(h))
+    print(f"gelu [{L}x12288]: {t*1e6:.1f} us  {2*h.numel()*2/t/1e9:.0f} GB/s  {2*h.numel()*2/t/bw:.2f} {tag}")
+
+
+def bench_optim(small):
+    from ..optim import AdamW8bit
+    bw, fl, tag = peaks()
+    n = 56_000_000 if not small else 4_000_000
+    p = torch.nn.Parameter(torch.randn(n, device="cuda").bfloat16())
+    opt = AdamW8bit([p])
+    opt.arena.grad.normal_()
+    ss = F.sumsq(opt.arena.grad)
+    t = timeit(lambda: opt.step(grad_sumsq=ss, max_grad_norm=1.0))
+    nb = opt.arena.numel * (2 + 2 + 2 + 1 + 1 + 1 + 1)
+    print(f"adamw8bit [{n/1e6:.0f}M params]: {t*1e6:.1f} us  {nb/t/1e9:.0f} GB/s  {nb/t/bw:.2f} {tag}")
+    t = timeit(lambda: F.sumsq(opt.arena.grad, ss))
+    print(f"sumsq: {t*1e6:.1f} us  {opt.arena.numel*2/t/1e9:.0f} GB/s")
+
+
+def bench_attn(small):
+    bw, fl, tag = peaks()
+    for (B, L, H, D) in ([(1, 4608, 24, 128)] if not small else [(1, 1024, 8, 128)]):
+        q, k, v = (torch.randn(B, L, H, D, device="cuda").bfloat16() for _ in range(3))
+        fl_ = 4.0 * B * H * L * L * D
+        t_lib = timeit(lambda: R.attention(q, k, v))
+        print(f"attention fwd B{B} L{L} H{H} D{D}: library SDPA {t_lib*1e6:.1f} us {fl_/t_lib/1e12:.0f} TF/s")
+        from ..ops import flash_attn as FA
+        if FA.supported(q, k, v):
+            t = timeit(lambda: FA.flash_attention(q, k, v))
+            print(f"   ours {t*1e6:.1f} us {fl_/t/1e12:.0f} TF/s  {fl_/t/fl:.2f} {tag}")
+        qg, kg, vg = (t_.clone().requires_grad_() for t_ in (q, k, v))
+        o = R.attention(qg, kg, vg)
+        go = torch.randn_like(o)
+        t_b = timeit(lambda: torch.autograd.grad(o, (qg, kg, vg), go, retain_graph=True))
+        print(f"   library SDPA bwd {t_b*1e6:.1f} us {2.5*fl_/t_b/1e12:.0f} TF/s")
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--what", default="gemm,elementwise,optim,attn")
+    ap.add_argument("--small", action="store_true")
+    a = ap.parse_args()
+    for w in a.what.split(","):
+        {"gemm": bench_gemm, "elementwise": bench_elementwise, "optim": bench_optim, "attn": bench_attn}[w](a.small)
+
+
+if __name__ == "__main__":
+    main()

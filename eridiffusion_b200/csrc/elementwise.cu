@@ -37,7 +37,7 @@ __device__ __forceinline__ float block_sum(float v, float* red) {
 // ------------------------------------------------------------------ norm + modulation
 // y = (xhat * w + b) * (1 + scale[batch]) + shift[batch]; xhat = (x - mean) * rstd (LayerNorm)
 // or x * rstd (RMSNorm). w, b, scale, shift are each optional.
-__global__ void norm_modulate_fwd_kernel(const bf16* __restrict__ x, const bf16* __restrict__ scale,
+__global__ void __launch_bounds__(1024) norm_modulate_fwd_kernel(const bf16* __restrict__ x, const bf16* __restrict__ scale,
                                          const bf16* __restrict__ shift,
                                          const bf16* __restrict__ weight,
                                          const bf16* __restrict__ bias, bf16* __restrict__ y,
@@ -126,7 +126,7 @@ __global__ void norm_modulate_fwd_kernel(const bf16* __restrict__ x, const bf16*
 // Backward. One CTA walks `rows_per_cta` consecutive rows so that the column sums that feed
 // d_scale / d_shift / d_weight / d_bias are accumulated in registers and flushed with one
 // fp32 atomicAdd per column per CTA (or when the batch index changes).
-__global__ void norm_modulate_bwd_kernel(
+__global__ void __launch_bounds__(512) norm_modulate_bwd_kernel(
     const bf16* __restrict__ dy, const bf16* __restrict__ x, const bf16* __restrict__ scale,
     const bf16* __restrict__ weight, const bf16* __restrict__ bias,
     const float* __restrict__ mean_in, const float* __restrict__ rstd_in, bf16* __restrict__ dx,
@@ -693,10 +693,10 @@ inline int grid_for(size_t n, int block) {
   size_t cap = 148 * 16;
   return (int)(g < 1 ? 1 : (g > cap ? cap : g));
 }
-inline int row_threads(int D) {
+inline int row_threads(int D, int max_threads) {
   int nvec = D >> 3;
   int t = ((nvec + 31) / 32) * 32;
-  if (t > 1024) t = ((nvec / kMaxVec + 31) / 32) * 32;
+  if (t > max_threads) t = (((nvec + kMaxVec - 1) / kMaxVec + 31) / 32) * 32;
   return t < 32 ? 32 : t;
 }
 
@@ -708,7 +708,7 @@ int eri_norm_modulate_fwd(const void* x, const void* scale, const void* shift, c
                           const void* bias, void* y, float* mean, float* rstd, int rows, int D,
                           int rows_per_batch, int mod_stride, float eps, int rms, void* stream) {
   if (D % 8 != 0 || D > 8 * 1024 * kMaxVec) return -1;
-  norm_modulate_fwd_kernel<<<rows, row_threads(D), 0, (cudaStream_t)stream>>>(
+  norm_modulate_fwd_kernel<<<rows, row_threads(D, 1024), 0, (cudaStream_t)stream>>>(
       (const bf16*)x, (const bf16*)scale, (const bf16*)shift, (const bf16*)weight,
       (const bf16*)bias, (bf16*)y, mean, rstd, rows, D, rows_per_batch, mod_stride, eps, rms);
   ERI_LAUNCH_CHECK();
@@ -718,10 +718,10 @@ int eri_norm_modulate_bwd(const void* dy, const void* x, const void* scale, cons
                           const void* bias, const float* mean, const float* rstd, void* dx,
                           float* dscale, float* dshift, float* dweight, float* dbias, int rows,
                           int D, int rows_per_batch, int mod_stride, int rms, void* stream) {
-  if (D % 8 != 0 || D > 8 * 1024 * kMaxVec) return -1;
+  if (D % 8 != 0 || D > 8 * 512 * kMaxVec) return -1;
   const bool reduce = dscale || dshift || dweight || dbias;
   const int rpc = reduce ? 8 : 1;
-  norm_modulate_bwd_kernel<<<(rows + rpc - 1) / rpc, row_threads(D), 0, (cudaStream_t)stream>>>(
+  norm_modulate_bwd_kernel<<<(rows + rpc - 1) / rpc, row_threads(D, 512), 0, (cudaStream_t)stream>>>(
       (const bf16*)dy, (const bf16*)x, (const bf16*)scale, (const bf16*)weight, (const bf16*)bias,
       mean, rstd, (bf16*)dx, dscale, dshift, dweight, dbias, rows, D, rows_per_batch, mod_stride,
       rms, rpc);

@@ -1,0 +1,322 @@
+// Flash attention forward for sm_100a (non-causal, head_dim 64 or 128, bf16 in / bf16 out, fp32
+// softmax state), token-major tensors [B, L, H, Dh] so that the QKV projection's output and the
+// output projection's input need no transposes.
+//
+// One CTA per (128-query tile, head, batch), two CTAs resident per SM so that one CTA's softmax
+// overlaps the other's tensor-core work:
+//   warp 0     TMA loads: Q once, then one K tile and one V tile (128 keys) per iteration
+//   warp 1     tcgen05.mma issue:  S = Q K^T  (smem x smem -> TMEM, fp32)
+//                                  O += P V   (P read from TMEM as packed bf16, V from smem as an
+//                                              MN-major operand, accumulator O in TMEM)
+//   warps 2-5  softmax: one thread per query row reads S from TMEM, keeps the running max / sum in
+//              registers, writes P back over S in TMEM as packed bf16, rescales O in TMEM only when
+//              the running max moved by more than 2^8 (lazy rescale), and writes O / l and the
+//              log-sum-exp at the end.
+// The reference reaches attention through an external flame-core SDPA or a chunked online-softmax
+// composition of bmm + elementwise ops (crates/training/src/sdxl/runtime.rs:2814-3025,
+// crates/training/src/flux/runtime.rs:707-745); the softmax recurrence is the same.
+#include "ptx.cuh"
+#include "tma_host.h"
+
+using namespace eri;
+typedef __nv_bfloat16 bf16;
+
+namespace {
+
+struct FaParams {
+  int B, H, Lq, Lk;
+  float scale_log2;  // softmax scale * log2(e)
+  bf16* out;         // [B, Lq, H, DH]
+  float* lse;        // [B, H, Lq] natural-log log-sum-exp (may be null)
+  int* err;
+};
+
+constexpr int BQ = 128, BKV = 128;
+constexpr float kRescaleThreshold = 8.0f;  // log2 units
+
+template <int DH>
+__global__ void __launch_bounds__(192, 2)
+fa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+              const __grid_constant__ CUtensorMap tmV, const FaParams p) {
+  constexpr int CHUNKS = DH / 64;
+  constexpr int TILE_BYTES = 128 * 128 * CHUNKS;  // 128 rows x DH bf16
+  constexpr int CHUNK_BYTES = 128 * 128;          // 128 rows x 64 bf16
+  constexpr int TMEM_COLS = 256;                  // S/P: 128 columns, O: DH columns
+  constexpr uint32_t S_COL = 0, O_COL = 128;
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~uintptr_t(1023));
+  uint8_t* sQ = smem;
+  uint8_t* sK = sQ + TILE_BYTES;
+  uint8_t* sV = sK + TILE_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sV + TILE_BYTES);
+  uint64_t* q_full = bars + 0;
+  uint64_t* k_full = bars + 1;
+  uint64_t* k_empty = bars + 2;
+  uint64_t* v_full = bars + 3;
+  uint64_t* v_empty = bars + 4;
+  uint64_t* s_full = bars + 5;
+  uint64_t* p_full = bars + 6;
+  uint64_t* o_done = bars + 7;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 8);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int q0 = blockIdx.x * BQ, h = blockIdx.y, b = blockIdx.z;
+  const int nkv = (p.Lk + BKV - 1) / BKV;
+
+  if (threadIdx.x == 0) {
+    mbar_init(q_full, 1);
+    mbar_init(k_full, 1);
+    mbar_init(k_empty, 1);
+    mbar_init(v_full, 1);
+    mbar_init(v_empty, 1);
+    mbar_init(s_full, 1);
+    mbar_init(p_full, 4);
+    mbar_init(o_done, 1);
+    mbar_fence_init();
+    tma_prefetch_desc(&tmQ);
+    tma_prefetch_desc(&tmK);
+    tma_prefetch_desc(&tmV);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (elect_one()) {
+      mbar_expect_tx(q_full, TILE_BYTES);
+#pragma unroll
+      for (int c = 0; c < CHUNKS; ++c)
+        tma_load_3d(sQ + c * CHUNK_BYTES, &tmQ, q_full, h * DH + c * 64, q0, b);
+      for (int j = 0; j < nkv; ++j) {
+        const uint32_t par = (uint32_t)(j & 1);
+        if (!mbar_wait(k_empty, par ^ 1)) { atomicExch(p.err, 11); break; }
+        mbar_expect_tx(k_full, TILE_BYTES);
+#pragma unroll
+        for (int c = 0; c < CHUNKS; ++c)
+          tma_load_3d(sK + c * CHUNK_BYTES, &tmK, k_full, h * DH + c * 64, j * BKV, b);
+        if (!mbar_wait(v_empty, par ^ 1)) { atomicExch(p.err, 12); break; }
+        mbar_expect_tx(v_full, TILE_BYTES);
+#pragma unroll
+        for (int c = 0; c < CHUNKS; ++c)
+          tma_load_3d(sV + c * CHUNK_BYTES, &tmV, v_full, h * DH + c * 64, j * BKV, b);
+      }
+    }
+  } else if (warp == 1) {
+    if (elect_one()) {
+      const uint32_t idesc_s = umma_idesc_bf16(BQ, BKV, 0, 0);
+      const uint32_t idesc_o = umma_idesc_bf16(BQ, DH, 0, 1);  // B (V) is MN-major
+      const uint32_t aQ = smem_u32(sQ), aK = smem_u32(sK), aV = smem_u32(sV);
+      bool ok = mbar_wait(q_full, 0);
+      if (!ok) atomicExch(p.err, 13);
+      for (int j = 0; j < nkv && ok; ++j) {
+        const uint32_t par = (uint32_t)(j & 1);
+        if (!mbar_wait(k_full, par)) { atomicExch(p.err, 14); break; }
+        tc_fence_after();
+#pragma unroll
+        for (int c = 0; c < CHUNKS; ++c) {
+          const uint64_t dq = umma_desc_kmajor(aQ + c * CHUNK_BYTES, 128);
+          const uint64_t dk = umma_desc_kmajor(aK + c * CHUNK_BYTES, 128);
+#pragma unroll
+          for (int kk = 0; kk < 4; ++kk)
+            umma_bf16(tmem_base + S_COL, dq + kk * 2, dk + kk * 2, idesc_s, (c | kk) != 0);
+        }
+        umma_commit(s_full);
+        umma_commit(k_empty);
+        if (!mbar_wait(p_full, par)) { atomicExch(p.err, 15); break; }
+        if (!mbar_wait(v_full, par)) { atomicExch(p.err, 16); break; }
+        tc_fence_after();
+#pragma unroll
+        for (int kk = 0; kk < BKV / 16; ++kk) {
+          const uint64_t dv = umma_desc_mn128(aV + kk * 2048, CHUNK_BYTES);
+          umma_bf16_ts(tmem_base + O_COL, tmem_base + S_COL + kk * 8, dv, idesc_o, (j | kk) != 0);
+        }
+        umma_commit(o_done);
+        umma_commit(v_empty);
+      }
+    }
+  } else {
+    const int qd = warp & 3;
+    const int row = q0 + qd * 32 + lane;
+    const uint32_t lane_addr = tmem_base + ((uint32_t)(qd * 32) << 16);
+    float m_used = -INFINITY, l = 0.f;
+    bool ok = true;
+    for (int j = 0; j < nkv; ++j) {
+      const uint32_t par = (uint32_t)(j & 1);
+      if (!mbar_wait(s_full, par)) {
+        if (lane == 0) atomicExch(p.err, 17);
+        ok = false;
+        break;
+      }
+      tc_fence_after();
+      const int kv_left = p.Lk - j * BKV;  // valid key columns in this tile
+      float mx = -INFINITY;
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t r[32];
+        tmem_ld32(lane_addr + S_COL + c * 32, r);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          float s = __uint_as_float(r[i]);
+          if (c * 32 + i < kv_left) mx = fmaxf(mx, s);
+        }
+      }
+      const float m_new = mx * p.scale_log2;
+      if (j == 0) {
+        m_used = m_new;
+      } else {
+        const bool need = (m_new - m_used) > kRescaleThreshold;
+        if (__any_sync(0xffffffffu, need)) {
+          // s_full of this tile was committed after PV of the previous tile, so O is complete.
+          const float m_t = need ? m_new : m_used;
+          const float alpha = exp2f(m_used - m_t);
+#pragma unroll 1
+          for (int c = 0; c < DH / 32; ++c) {
+            uint32_t r[32];
+            tmem_ld32(lane_addr + O_COL + c * 32, r);
+            tmem_ld_wait();
+            uint32_t a0[16], a1[16];
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+              a0[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
+              a1[i] = __float_as_uint(__uint_as_float(r[16 + i]) * alpha);
+            }
+            tmem_st16(lane_addr + O_COL + c * 32, a0);
+            tmem_st16(lane_addr + O_COL + c * 32 + 16, a1);
+          }
+          tmem_st_wait();
+          l *= alpha;
+          m_used = m_t;
+        }
+      }
+      float lsum = 0.f;
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t r[32];
+        tmem_ld32(lane_addr + S_COL + c * 32, r);
+        tmem_ld_wait();
+        uint32_t pk[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          float p0 = exp2f(fmaf(__uint_as_float(r[2 * i]), p.scale_log2, -m_used));
+          float p1 = exp2f(fmaf(__uint_as_float(r[2 * i + 1]), p.scale_log2, -m_used));
+          if (c * 32 + 2 * i >= kv_left) p0 = 0.f;
+          if (c * 32 + 2 * i + 1 >= kv_left) p1 = 0.f;
+          __nv_bfloat162 pb = __floats2bfloat162_rn(p0, p1);
+          // the sum uses the rounded values, matching what the PV product sees
+          float2 pr = __bfloat1622float2(pb);
+          lsum += pr.x + pr.y;
+          pk[i] = *reinterpret_cast<uint32_t*>(&pb);
+        }
+        tmem_st16(lane_addr + S_COL + c * 16, pk);
+      }
+      l += lsum;
+      tmem_st_wait();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(p_full);
+    }
+    if (ok) {
+      if (!mbar_wait(o_done, (uint32_t)((nkv - 1) & 1))) {
+        if (lane == 0) atomicExch(p.err, 18);
+        ok = false;
+      }
+    }
+    if (ok) {
+      tc_fence_after();
+      const float inv_l = 1.f / l;
+      bf16* orow = p.out + (((size_t)b * p.Lq + row) * p.H + h) * DH;
+#pragma unroll 1
+      for (int c = 0; c < DH / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld32(lane_addr + O_COL + c * 32, r);
+        tmem_ld_wait();
+        if (row < p.Lq) {
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            float v[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) v[i] = __uint_as_float(r[g * 8 + i]) * inv_l;
+            *reinterpret_cast<bf16x8*>(orow + c * 32 + g * 8) = pack8(v);
+          }
+        }
+      }
+      if (p.lse && row < p.Lq)
+        p.lse[((size_t)b * p.H + h) * p.Lq + row] = (m_used + log2f(l)) * 0.6931471805599453f;
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    __syncwarp();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+int* g_fa_err = nullptr;
+
+template <int DH>
+int launch_fwd(const CUtensorMap& q, const CUtensorMap& k, const CUtensorMap& v, const FaParams& p,
+               cudaStream_t st) {
+  constexpr int SMEM = 3 * 128 * 128 * (DH / 64) + 1024 + 128;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(fa_fwd_kernel<DH>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  dim3 grid((p.Lq + BQ - 1) / BQ, p.H, p.B);
+  fa_fwd_kernel<DH><<<grid, 192, SMEM, st>>>(q, k, v, p);
+  return (int)cudaGetLastError();
+}
+
+int make_qkv_map(CUtensorMap* m, const void* ptr, int B, int L, int H, int DH) {
+  uint64_t dims[3] = {(uint64_t)H * DH, (uint64_t)L, (uint64_t)B};
+  uint64_t strides[2] = {(uint64_t)H * DH * 2, (uint64_t)L * H * DH * 2};
+  uint32_t box[3] = {64, 128, 1};
+  return make_tensor_map(m, ptr, 3, dims, strides, box, 128);
+}
+
+}  // namespace
+
+extern "C" {
+
+int eri_fa_check_error() {
+  if (!g_fa_err) return 0;
+  int h = 0;
+  cudaMemcpy(&h, g_fa_err, sizeof(int), cudaMemcpyDeviceToHost);
+  if (h) cudaMemset(g_fa_err, 0, sizeof(int));
+  return h;
+}
+
+// q [B, Lq, H, DH], k/v [B, Lk, H, DH], out [B, Lq, H, DH] (all contiguous bf16), lse [B, H, Lq].
+int eri_flash_attn_fwd(const void* q, const void* k, const void* v, void* out, float* lse, int B,
+                       int H, int Lq, int Lk, int DH, float scale, void* stream) {
+  if (DH != 64 && DH != 128) return -1;
+  if (Lq < 128 || Lk < 128) return -2;
+  if (!g_fa_err) {
+    if (cudaMalloc(&g_fa_err, sizeof(int)) != cudaSuccess) return -3;
+    cudaMemset(g_fa_err, 0, sizeof(int));
+  }
+  CUtensorMap tq, tk, tv;
+  if (make_qkv_map(&tq, q, B, Lq, H, DH) || make_qkv_map(&tk, k, B, Lk, H, DH) ||
+      make_qkv_map(&tv, v, B, Lk, H, DH))
+    return -4;
+  FaParams p;
+  p.B = B; p.H = H; p.Lq = Lq; p.Lk = Lk;
+  p.scale_log2 = scale * 1.4426950408889634f;
+  p.out = (bf16*)out; p.lse = lse; p.err = g_fa_err;
+  cudaStream_t st = (cudaStream_t)stream;
+  return DH == 128 ? launch_fwd<128>(tq, tk, tv, p, st) : launch_fwd<64>(tq, tk, tv, p, st);
+}
+
+}  // extern "C"

@@ -121,7 +121,7 @@ class _NormModulate(torch.autograd.Function):
 
 def norm_modulate(x, scale=None, shift=None, weight=None, bias=None, eps=1e-6, rms=False):
     if _native_ok(x, scale, shift, weight, bias) and x.dim() == 3 and x.shape[-1] % 8 == 0 \
-            and x.shape[-1] <= 16384:
+            and x.shape[-1] <= 8192:
         return _NormModulate.apply(x, scale, shift, weight, bias, eps, rms)
     return R.norm_modulate(x, scale, shift, weight, bias, eps, rms)
 

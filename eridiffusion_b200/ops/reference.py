@@ -107,7 +107,15 @@ def attention(q, k, v, scale=None, mask=None):
     ``mask``: optional additive or boolean mask broadcastable to [B, H, Lq, Lk].
     """
     qh, kh, vh = (t.transpose(1, 2) for t in (q, k, v))
-    o = F.scaled_dot_product_attention(qh, kh, vh, attn_mask=mask, scale=scale)
+    if q.is_cuda and torch.is_grad_enabled() and (q.requires_grad or k.requires_grad or v.requires_grad):
+        # The cuDNN attention backward of this torch build rejects the graph for these strided
+        # layouts ("mha_graph.execute ... is_good()"), so training uses the flash / efficient
+        # library kernels; cuDNN stays available for no-grad calls.
+        from torch.nn.attention import SDPBackend, sdpa_kernel
+        with sdpa_kernel([SDPBackend.FLASH_ATTENTION, SDPBackend.EFFICIENT_ATTENTION, SDPBackend.MATH]):
+            o = F.scaled_dot_product_attention(qh, kh, vh, attn_mask=mask, scale=scale)
+    else:
+        o = F.scaled_dot_product_attention(qh, kh, vh, attn_mask=mask, scale=scale)
     return o.transpose(1, 2).contiguous()
 
 

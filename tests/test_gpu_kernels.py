@@ -17,11 +17,13 @@ def rnd(*s, scale=1.0, seed=0):
     return (torch.randn(*s, device=DEV, generator=g) * scale).to(BF)
 
 
-def close(a, b, atol, rtol=2e-2):
+def close(a, b, atol, rtol=2e-2, rel_to_max=0.0):
+    """|a-b| <= atol + rel_to_max*max|b| + rtol*|b| elementwise (bf16 pipelines carry an absolute
+    error proportional to the tensor's scale, not to each element)."""
     a, b = a.float(), b.float()
     assert a.shape == b.shape
     err = (a - b).abs()
-    tol = atol + rtol * b.abs()
+    tol = atol + rel_to_max * b.abs().max() + rtol * b.abs()
     assert bool((err <= tol).all()), f"max err {err.max().item():.4g} (allowed {tol.max().item():.4g})"
 
 
@@ -194,10 +196,10 @@ def test_fused_linear_autograd_matches_reference():
     g = rnd(B, L, N, seed=7)
     y.backward(g); yr.backward(g.float())
     assert F.gemm_error_check() == 0
-    close(x.grad, xr.grad, 0.08, 3e-2)
+    close(x.grad, xr.grad, 0.02, 3e-2, rel_to_max=0.02)
     close(res.grad, rr.grad, 1e-2)
-    close(A.grad, Ar.grad, 0.6, 5e-2)
-    close(Bm.grad, Br.grad, 0.6, 5e-2)
+    close(A.grad, Ar.grad, 0.05, 3e-2, rel_to_max=0.02)
+    close(Bm.grad, Br.grad, 0.05, 3e-2, rel_to_max=0.02)
 
 
 def test_small_linear():
