@@ -125,6 +125,13 @@ def bench_attn(small):
         if FA.supported(q, k, v):
             t = timeit(lambda: FA.flash_attention(q, k, v))
             print(f"   ours {t*1e6:.1f} us {fl_/t/1e12:.0f} TF/s  {fl_/t/fl:.2f} {tag}")
+        if FA.supported(q, k, v) and FA.has_backward():
+            o_, lse_ = FA.fwd(q, k, v)
+            go_ = torch.randn_like(o_)
+            t = timeit(lambda: FA.bwd(go_, q, k, v, o_, lse_))
+            print(f"   ours bwd {t*1e6:.1f} us {2.5*fl_/t/1e12:.0f} TF/s (algorithmic 2.5x fwd flops; "
+                  f"3.5x executed)  {2.5*fl_/t/fl:.2f} {tag}")
+            assert FA.check_error() == 0
         qg, kg, vg = (t_.clone().requires_grad_() for t_ in (q, k, v))
         o = R.attention(qg, kg, vg)
         go = torch.randn_like(o)

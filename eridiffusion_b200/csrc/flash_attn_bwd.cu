@@ -1,0 +1,534 @@
+// Flash attention backward for sm_100a (non-causal, head_dim 64 / 128, token-major [B, L, H, Dh]).
+//
+// Three launches, no atomics, deterministic:
+//   prep   delta[b,h,q] = sum_d O * dO, and the log-sum-exp converted to log2 units, both written
+//          to buffers padded to a multiple of 128 queries (padding: lse = +inf, so P = 0 there)
+//   dkdv   one CTA per 128-key tile, loop over 128-query tiles:
+//              S^T  = K Q^T,  dP^T = V dO^T            (smem x smem -> TMEM, keys on TMEM lanes)
+//              P^T  = exp2(S^T c - lse2[q]),  dS^T = P^T * (dP^T - delta[q])   (one thread per key)
+//              dV  += P^T dO,  dK += dS^T Q            (A operand read from TMEM as packed bf16,
+//                                                       dO / Q tiles re-read as MN-major B operands)
+//   dq     one CTA per 128-query tile, loop over 128-key tiles:
+//              S = Q K^T, dP = dO V^T, dS = P * (dP - delta), dQ += dS K
+// Recomputing S and dP in the dq pass costs two extra MMAs per tile pair and removes the global
+// fp32 dQ accumulation (atomics or reduce-adds) that a single-pass backward needs.
+// The reference's only attention gradient is a recompute through tensor ops
+// (crates/core/src/autograd_ops.rs:10-75, attention_backward_recompute).
+#include "ptx.cuh"
+#include "tma_host.h"
+
+using namespace eri;
+typedef __nv_bfloat16 bf16;
+
+namespace {
+
+struct FaBwdParams {
+  int B, H, Lq, Lk, Lp;  // Lp: padded query length of lse2 / delta
+  float scale, scale_log2;
+  const float* lse2;     // [B, H, Lp]
+  const float* delta;    // [B, H, Lp]
+  bf16* dq;              // [B, Lq, H, DH]
+  bf16* dk;              // [B, Lk, H, DH]
+  bf16* dv;
+  int* err;
+};
+
+constexpr int T = 128;  // tile edge (queries and keys)
+
+__global__ void fa_bwd_prep_kernel(const bf16* __restrict__ o, const bf16* __restrict__ dout,
+                                   const float* __restrict__ lse, float* __restrict__ lse2,
+                                   float* __restrict__ delta, int B, int H, int Lq, int Lp, int DH) {
+  const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+  const int total = B * H * Lp;
+  if (warp >= total) return;
+  const int l = warp % Lp, h = (warp / Lp) % H, b = warp / (Lp * H);
+  if (l >= Lq) {
+    if (lane == 0) {
+      lse2[warp] = INFINITY;
+      delta[warp] = 0.f;
+    }
+    return;
+  }
+  const size_t base = (((size_t)b * Lq + l) * H + h) * DH;
+  float acc = 0.f;
+  for (int d = lane * 2; d < DH; d += 64) {
+    float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(o + base + d));
+    float2 g = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(dout + base + d));
+    acc += a.x * g.x + a.y * g.y;
+  }
+  acc = warp_sum(acc);
+  if (lane == 0) {
+    delta[warp] = acc;
+    lse2[warp] = lse[((size_t)b * H + h) * Lq + l] * 1.4426950408889634f;
+  }
+}
+
+__device__ __forceinline__ void named_bar_sync(int id, int nthreads) {
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
+}
+
+// ------------------------------------------------------------------------------------- dK, dV
+template <int DH>
+__global__ void __launch_bounds__(192, 1)
+fa_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                   const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmDO,
+                   const FaBwdParams p) {
+  constexpr int CHUNKS = DH / 64;
+  constexpr int CHUNK_BYTES = T * 128;
+  constexpr int TILE_BYTES = CHUNK_BYTES * CHUNKS;
+  constexpr uint32_t S_COL = 0, DP_COL = 128, DV_COL = 256, DK_COL = 384;
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~uintptr_t(1023));
+  uint8_t* sK = smem;
+  uint8_t* sV = sK + TILE_BYTES;
+  uint8_t* sQ = sV + TILE_BYTES;        // 2 stages
+  uint8_t* sDO = sQ + 2 * TILE_BYTES;   // 2 stages
+  float* s_lse = reinterpret_cast<float*>(sDO + 2 * TILE_BYTES);  // [2][128]
+  float* s_delta = s_lse + 2 * T;                                 // [2][128]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(s_delta + 2 * T);
+  uint64_t* kv_full = bars + 0;
+  uint64_t* qdo_full = bars + 1;   // [2]
+  uint64_t* qdo_empty = bars + 3;  // [2]
+  uint64_t* sp_full = bars + 5;
+  uint64_t* pds_ready = bars + 6;
+  uint64_t* acc_done = bars + 7;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 8);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int k0 = blockIdx.x * T, h = blockIdx.y, b = blockIdx.z;
+  const int nq = (p.Lq + T - 1) / T;
+
+  if (threadIdx.x == 0) {
+    mbar_init(kv_full, 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&qdo_full[s], 1);
+      mbar_init(&qdo_empty[s], 1);
+    }
+    mbar_init(sp_full, 1);
+    mbar_init(pds_ready, 4);
+    mbar_init(acc_done, 1);
+    mbar_fence_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (elect_one()) {
+      mbar_expect_tx(kv_full, 2 * TILE_BYTES);
+#pragma unroll
+      for (int c = 0; c < CHUNKS; ++c) {
+        tma_load_3d(sK + c * CHUNK_BYTES, &tmK, kv_full, h * DH + c * 64, k0, b);
+        tma_load_3d(sV + c * CHUNK_BYTES, &tmV, kv_full, h * DH + c * 64, k0, b);
+      }
+      for (int i = 0; i < nq; ++i) {
+        const int s = i & 1;
+        const uint32_t par = (uint32_t)((i >> 1) & 1);
+        if (!mbar_wait(&qdo_empty[s], par ^ 1)) { atomicExch(p.err, 21); break; }
+        mbar_expect_tx(&qdo_full[s], 2 * TILE_BYTES);
+#pragma unroll
+        for (int c = 0; c < CHUNKS; ++c) {
+          tma_load_3d(sQ + s * TILE_BYTES + c * CHUNK_BYTES, &tmQ, &qdo_full[s], h * DH + c * 64,
+                      i * T, b);
+          tma_load_3d(sDO + s * TILE_BYTES + c * CHUNK_BYTES, &tmDO, &qdo_full[s],
+                      h * DH + c * 64, i * T, b);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (elect_one()) {
+      const uint32_t idesc_s = umma_idesc_bf16(T, T, 0, 0);
+      const uint32_t idesc_g = umma_idesc_bf16(T, DH, 0, 1);
+      const uint32_t aK = smem_u32(sK), aV = smem_u32(sV);
+      bool ok = mbar_wait(kv_full, 0);
+      if (!ok) atomicExch(p.err, 22);
+      for (int i = 0; i < nq && ok; ++i) {
+        const int s = i & 1;
+        if (!mbar_wait(&qdo_full[s], (uint32_t)((i >> 1) & 1))) { atomicExch(p.err, 23); break; }
+        tc_fence_after();
+        const uint32_t aQ = smem_u32(sQ + s * TILE_BYTES), aDO = smem_u32(sDO + s * TILE_BYTES);
+#pragma unroll
+        for (int c = 0; c < CHUNKS; ++c) {
+          const uint64_t da = umma_desc_kmajor(aK + c * CHUNK_BYTES, 128);
+          const uint64_t db = umma_desc_kmajor(aQ + c * CHUNK_BYTES, 128);
+#pragma unroll
+          for (int kk = 0; kk < 4; ++kk)
+            umma_bf16(tmem_base + S_COL, da + kk * 2, db + kk * 2, idesc_s, (c | kk) != 0);
+        }
+#pragma unroll
+        for (int c = 0; c < CHUNKS; ++c) {
+          const uint64_t da = umma_desc_kmajor(aV + c * CHUNK_BYTES, 128);
+          const uint64_t db = umma_desc_kmajor(aDO + c * CHUNK_BYTES, 128);
+#pragma unroll
+          for (int kk = 0; kk < 4; ++kk)
+            umma_bf16(tmem_base + DP_COL, da + kk * 2, db + kk * 2, idesc_s, (c | kk) != 0);
+        }
+        umma_commit(sp_full);
+        if (!mbar_wait(pds_ready, (uint32_t)(i & 1))) { atomicExch(p.err, 24); break; }
+        tc_fence_after();
+#pragma unroll
+        for (int kk = 0; kk < T / 16; ++kk) {
+          const uint64_t dbo = umma_desc_mn128(aDO + kk * 2048, CHUNK_BYTES);
+          umma_bf16_ts(tmem_base + DV_COL, tmem_base + S_COL + kk * 8, dbo, idesc_g, (i | kk) != 0);
+        }
+#pragma unroll
+        for (int kk = 0; kk < T / 16; ++kk) {
+          const uint64_t dbq = umma_desc_mn128(aQ + kk * 2048, CHUNK_BYTES);
+          umma_bf16_ts(tmem_base + DK_COL, tmem_base + DP_COL + kk * 8, dbq, idesc_g, (i | kk) != 0);
+        }
+        umma_commit(&qdo_empty[s]);
+      }
+      if (ok) umma_commit(acc_done);
+    }
+  } else {
+    const int qd = warp & 3;
+    const int tid = threadIdx.x - 64;  // 0..127
+    const uint32_t lane_addr = tmem_base + ((uint32_t)(qd * 32) << 16);
+    const size_t stat_base = ((size_t)b * p.H + h) * p.Lp;
+    bool ok = true;
+    for (int i = 0; i < nq; ++i) {
+      const int s = i & 1;
+      s_lse[s * T + tid] = p.lse2[stat_base + i * T + tid];
+      s_delta[s * T + tid] = p.delta[stat_base + i * T + tid];
+      named_bar_sync(1, 128);
+      if (!mbar_wait(sp_full, (uint32_t)(i & 1))) {
+        if (lane == 0) atomicExch(p.err, 25);
+        ok = false;
+        break;
+      }
+      tc_fence_after();
+      const float* ls = s_lse + s * T;
+      const float* dl = s_delta + s * T;
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t r[32], g[32];
+        tmem_ld32(lane_addr + S_COL + c * 32, r);
+        tmem_ld32(lane_addr + DP_COL + c * 32, g);
+        tmem_ld_wait();
+        uint32_t pk[16], dk_[16];
+#pragma unroll
+        for (int x = 0; x < 16; ++x) {
+          const int q = c * 32 + 2 * x;
+          float p0 = exp2f(fmaf(__uint_as_float(r[2 * x]), p.scale_log2, -ls[q]));
+          float p1 = exp2f(fmaf(__uint_as_float(r[2 * x + 1]), p.scale_log2, -ls[q + 1]));
+          float d0 = p0 * (__uint_as_float(g[2 * x]) - dl[q]);
+          float d1 = p1 * (__uint_as_float(g[2 * x + 1]) - dl[q + 1]);
+          __nv_bfloat162 pb = __floats2bfloat162_rn(p0, p1);
+          __nv_bfloat162 db = __floats2bfloat162_rn(d0, d1);
+          pk[x] = *reinterpret_cast<uint32_t*>(&pb);
+          dk_[x] = *reinterpret_cast<uint32_t*>(&db);
+        }
+        tmem_st16(lane_addr + S_COL + c * 16, pk);
+        tmem_st16(lane_addr + DP_COL + c * 16, dk_);
+      }
+      tmem_st_wait();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(pds_ready);
+    }
+    if (ok && !mbar_wait(acc_done, 0)) {
+      if (lane == 0) atomicExch(p.err, 26);
+      ok = false;
+    }
+    if (ok) {
+      tc_fence_after();
+      const int kv = k0 + qd * 32 + lane;
+      const size_t obase = (((size_t)b * p.Lk + kv) * p.H + h) * DH;
+#pragma unroll 1
+      for (int c = 0; c < DH / 32; ++c) {
+        uint32_t rv[32], rk[32];
+        tmem_ld32(lane_addr + DV_COL + c * 32, rv);
+        tmem_ld32(lane_addr + DK_COL + c * 32, rk);
+        tmem_ld_wait();
+        if (kv < p.Lk) {
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            float a[8], bb[8];
+#pragma unroll
+            for (int x = 0; x < 8; ++x) {
+              a[x] = __uint_as_float(rv[g * 8 + x]);
+              bb[x] = __uint_as_float(rk[g * 8 + x]) * p.scale;
+            }
+            *reinterpret_cast<bf16x8*>(p.dv + obase + c * 32 + g * 8) = pack8(a);
+            *reinterpret_cast<bf16x8*>(p.dk + obase + c * 32 + g * 8) = pack8(bb);
+          }
+        }
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    __syncwarp();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+// ------------------------------------------------------------------------------------- dQ
+template <int DH>
+__global__ void __launch_bounds__(192, 1)
+fa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                 const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmDO,
+                 const FaBwdParams p) {
+  constexpr int CHUNKS = DH / 64;
+  constexpr int CHUNK_BYTES = T * 128;
+  constexpr int TILE_BYTES = CHUNK_BYTES * CHUNKS;
+  constexpr uint32_t S_COL = 0, DP_COL = 128, DQ_COL = 256;
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~uintptr_t(1023));
+  uint8_t* sQ = smem;
+  uint8_t* sDO = sQ + TILE_BYTES;
+  uint8_t* sK = sDO + TILE_BYTES;      // 2 stages
+  uint8_t* sV = sK + 2 * TILE_BYTES;   // 2 stages
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sV + 2 * TILE_BYTES);
+  uint64_t* qdo_full = bars + 0;
+  uint64_t* kv_full = bars + 1;   // [2]
+  uint64_t* kv_empty = bars + 3;  // [2]
+  uint64_t* sp_full = bars + 5;
+  uint64_t* ds_ready = bars + 6;
+  uint64_t* acc_done = bars + 7;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 8);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int q0 = blockIdx.x * T, h = blockIdx.y, b = blockIdx.z;
+  const int nkv = (p.Lk + T - 1) / T;
+
+  if (threadIdx.x == 0) {
+    mbar_init(qdo_full, 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&kv_full[s], 1);
+      mbar_init(&kv_empty[s], 1);
+    }
+    mbar_init(sp_full, 1);
+    mbar_init(ds_ready, 4);
+    mbar_init(acc_done, 1);
+    mbar_fence_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (elect_one()) {
+      mbar_expect_tx(qdo_full, 2 * TILE_BYTES);
+#pragma unroll
+      for (int c = 0; c < CHUNKS; ++c) {
+        tma_load_3d(sQ + c * CHUNK_BYTES, &tmQ, qdo_full, h * DH + c * 64, q0, b);
+        tma_load_3d(sDO + c * CHUNK_BYTES, &tmDO, qdo_full, h * DH + c * 64, q0, b);
+      }
+      for (int j = 0; j < nkv; ++j) {
+        const int s = j & 1;
+        if (!mbar_wait(&kv_empty[s], (uint32_t)(((j >> 1) & 1) ^ 1))) { atomicExch(p.err, 31); break; }
+        mbar_expect_tx(&kv_full[s], 2 * TILE_BYTES);
+#pragma unroll
+        for (int c = 0; c < CHUNKS; ++c) {
+          tma_load_3d(sK + s * TILE_BYTES + c * CHUNK_BYTES, &tmK, &kv_full[s], h * DH + c * 64,
+                      j * T, b);
+          tma_load_3d(sV + s * TILE_BYTES + c * CHUNK_BYTES, &tmV, &kv_full[s], h * DH + c * 64,
+                      j * T, b);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (elect_one()) {
+      const uint32_t idesc_s = umma_idesc_bf16(T, T, 0, 0);
+      const uint32_t idesc_g = umma_idesc_bf16(T, DH, 0, 1);
+      const uint32_t aQ = smem_u32(sQ), aDO = smem_u32(sDO);
+      bool ok = mbar_wait(qdo_full, 0);
+      if (!ok) atomicExch(p.err, 32);
+      for (int j = 0; j < nkv && ok; ++j) {
+        const int s = j & 1;
+        if (!mbar_wait(&kv_full[s], (uint32_t)((j >> 1) & 1))) { atomicExch(p.err, 33); break; }
+        tc_fence_after();
+        const uint32_t aK = smem_u32(sK + s * TILE_BYTES), aV = smem_u32(sV + s * TILE_BYTES);
+#pragma unroll
+        for (int c = 0; c < CHUNKS; ++c) {
+          const uint64_t da = umma_desc_kmajor(aQ + c * CHUNK_BYTES, 128);
+          const uint64_t db = umma_desc_kmajor(aK + c * CHUNK_BYTES, 128);
+#pragma unroll
+          for (int kk = 0; kk < 4; ++kk)
+            umma_bf16(tmem_base + S_COL, da + kk * 2, db + kk * 2, idesc_s, (c | kk) != 0);
+        }
+#pragma unroll
+        for (int c = 0; c < CHUNKS; ++c) {
+          const uint64_t da = umma_desc_kmajor(aDO + c * CHUNK_BYTES, 128);
+          const uint64_t db = umma_desc_kmajor(aV + c * CHUNK_BYTES, 128);
+#pragma unroll
+          for (int kk = 0; kk < 4; ++kk)
+            umma_bf16(tmem_base + DP_COL, da + kk * 2, db + kk * 2, idesc_s, (c | kk) != 0);
+        }
+        umma_commit(sp_full);
+        if (!mbar_wait(ds_ready, (uint32_t)(j & 1))) { atomicExch(p.err, 34); break; }
+        tc_fence_after();
+#pragma unroll
+        for (int kk = 0; kk < T / 16; ++kk) {
+          const uint64_t dbk = umma_desc_mn128(aK + kk * 2048, CHUNK_BYTES);
+          umma_bf16_ts(tmem_base + DQ_COL, tmem_base + DP_COL + kk * 8, dbk, idesc_g, (j | kk) != 0);
+        }
+        umma_commit(&kv_empty[s]);
+      }
+      if (ok) umma_commit(acc_done);
+    }
+  } else {
+    const int qd = warp & 3;
+    const int row = q0 + qd * 32 + lane;
+    const uint32_t lane_addr = tmem_base + ((uint32_t)(qd * 32) << 16);
+    const size_t stat = ((size_t)b * p.H + h) * p.Lp + row;  // row < Lp always
+    const float lse2 = p.lse2[stat], delta = p.delta[stat];
+    bool ok = true;
+    for (int j = 0; j < nkv; ++j) {
+      if (!mbar_wait(sp_full, (uint32_t)(j & 1))) {
+        if (lane == 0) atomicExch(p.err, 35);
+        ok = false;
+        break;
+      }
+      tc_fence_after();
+      const int kv_left = p.Lk - j * T;
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t r[32], g[32];
+        tmem_ld32(lane_addr + S_COL + c * 32, r);
+        tmem_ld32(lane_addr + DP_COL + c * 32, g);
+        tmem_ld_wait();
+        uint32_t dk_[16];
+#pragma unroll
+        for (int x = 0; x < 16; ++x) {
+          float p0 = exp2f(fmaf(__uint_as_float(r[2 * x]), p.scale_log2, -lse2));
+          float p1 = exp2f(fmaf(__uint_as_float(r[2 * x + 1]), p.scale_log2, -lse2));
+          if (c * 32 + 2 * x >= kv_left) p0 = 0.f;
+          if (c * 32 + 2 * x + 1 >= kv_left) p1 = 0.f;
+          float d0 = p0 * (__uint_as_float(g[2 * x]) - delta);
+          float d1 = p1 * (__uint_as_float(g[2 * x + 1]) - delta);
+          __nv_bfloat162 db = __floats2bfloat162_rn(d0, d1);
+          dk_[x] = *reinterpret_cast<uint32_t*>(&db);
+        }
+        tmem_st16(lane_addr + DP_COL + c * 16, dk_);
+      }
+      tmem_st_wait();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(ds_ready);
+    }
+    if (ok && !mbar_wait(acc_done, 0)) {
+      if (lane == 0) atomicExch(p.err, 36);
+      ok = false;
+    }
+    if (ok) {
+      tc_fence_after();
+      const size_t obase = (((size_t)b * p.Lq + row) * p.H + h) * DH;
+#pragma unroll 1
+      for (int c = 0; c < DH / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld32(lane_addr + DQ_COL + c * 32, r);
+        tmem_ld_wait();
+        if (row < p.Lq) {
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            float a[8];
+#pragma unroll
+            for (int x = 0; x < 8; ++x) a[x] = __uint_as_float(r[g * 8 + x]) * p.scale;
+            *reinterpret_cast<bf16x8*>(p.dq + obase + c * 32 + g * 8) = pack8(a);
+          }
+        }
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    __syncwarp();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+int* g_fab_err = nullptr;
+
+int make_map(CUtensorMap* m, const void* ptr, int B, int L, int H, int DH) {
+  uint64_t dims[3] = {(uint64_t)H * DH, (uint64_t)L, (uint64_t)B};
+  uint64_t strides[2] = {(uint64_t)H * DH * 2, (uint64_t)L * H * DH * 2};
+  uint32_t box[3] = {64, 128, 1};
+  return make_tensor_map(m, ptr, 3, dims, strides, box, 128);
+}
+
+template <int DH>
+int launch_bwd(const CUtensorMap& q, const CUtensorMap& k, const CUtensorMap& v,
+               const CUtensorMap& d, const FaBwdParams& p, cudaStream_t st) {
+  constexpr int SMEM = 6 * 128 * 128 * (DH / 64) + 2048 + 1024 + 128;
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(fa_bwd_dkdv_kernel<DH>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             SMEM) != cudaSuccess)
+      return -5;
+    if (cudaFuncSetAttribute(fa_bwd_dq_kernel<DH>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             SMEM) != cudaSuccess)
+      return -5;
+    configured = true;
+  }
+  dim3 g1((p.Lk + T - 1) / T, p.H, p.B), g2((p.Lq + T - 1) / T, p.H, p.B);
+  fa_bwd_dkdv_kernel<DH><<<g1, 192, SMEM, st>>>(q, k, v, d, p);
+  fa_bwd_dq_kernel<DH><<<g2, 192, SMEM, st>>>(q, k, v, d, p);
+  return (int)cudaGetLastError();
+}
+
+}  // namespace
+
+extern "C" {
+
+int eri_fa_bwd_check_error() {
+  if (!g_fab_err) return 0;
+  int h = 0;
+  cudaMemcpy(&h, g_fab_err, sizeof(int), cudaMemcpyDeviceToHost);
+  if (h) cudaMemset(g_fab_err, 0, sizeof(int));
+  return h;
+}
+
+// All tensors contiguous bf16 [B, L, H, DH]; lse [B, H, Lq] fp32 from the forward.
+// Scratch supplied by the caller: lse2 and delta, each [B, H, Lp] fp32 with Lp = ceil(Lq/128)*128.
+int eri_flash_attn_bwd(const void* dout, const void* q, const void* k, const void* v,
+                       const void* out, const float* lse, float* lse2, float* delta, void* dq,
+                       void* dk, void* dv, int B, int H, int Lq, int Lk, int DH, float scale,
+                       void* stream) {
+  if (DH != 64 && DH != 128) return -1;
+  if (Lq < 128 || Lk < 128) return -2;
+  if (!g_fab_err) {
+    if (cudaMalloc(&g_fab_err, sizeof(int)) != cudaSuccess) return -3;
+    cudaMemset(g_fab_err, 0, sizeof(int));
+  }
+  cudaStream_t st = (cudaStream_t)stream;
+  const int Lp = (Lq + T - 1) / T * T;
+  {
+    const long long warps = (long long)B * H * Lp;
+    const int block = 256;
+    const long long grid = (warps * 32 + block - 1) / block;
+    fa_bwd_prep_kernel<<<(unsigned)grid, block, 0, st>>>((const bf16*)out, (const bf16*)dout, lse,
+                                                         lse2, delta, B, H, Lq, Lp, DH);
+  }
+  CUtensorMap tq, tk, tv, td;
+  if (make_map(&tq, q, B, Lq, H, DH) || make_map(&tk, k, B, Lk, H, DH) ||
+      make_map(&tv, v, B, Lk, H, DH) || make_map(&td, dout, B, Lq, H, DH))
+    return -4;
+  FaBwdParams p;
+  p.B = B; p.H = H; p.Lq = Lq; p.Lk = Lk; p.Lp = Lp;
+  p.scale = scale; p.scale_log2 = scale * 1.4426950408889634f;
+  p.lse2 = lse2; p.delta = delta;
+  p.dq = (bf16*)dq; p.dk = (bf16*)dk; p.dv = (bf16*)dv; p.err = g_fab_err;
+  return DH == 128 ? launch_bwd<128>(tq, tk, tv, td, p, st) : launch_bwd<64>(tq, tk, tv, td, p, st);
+}
+
+}  // extern "C"

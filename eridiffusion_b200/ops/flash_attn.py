@@ -16,11 +16,13 @@ N._SIGNATURES.update({
     "eri_flash_attn_fwd": [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _P],
     "eri_flash_attn_bwd": [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _P],
     "eri_fa_check_error": [],
+    "eri_fa_bwd_check_error": [],
 })
 
 
 def _bind(lib):
-    for name in ("eri_flash_attn_fwd", "eri_flash_attn_bwd", "eri_fa_check_error"):
+    for name in ("eri_flash_attn_fwd", "eri_flash_attn_bwd", "eri_fa_check_error",
+                 "eri_fa_bwd_check_error"):
         if hasattr(lib, name):
             fn = getattr(lib, name)
             fn.argtypes = N._SIGNATURES[name]
@@ -67,21 +69,24 @@ def bwd(do, q, k, v, out, lse, scale=None):
     B, Lq, H, D = q.shape
     Lk = k.shape[1]
     scale = scale if scale is not None else 1.0 / math.sqrt(D)
-    dq = torch.zeros(B, Lq, H, D, dtype=torch.float32, device=q.device)
-    dk, dv = torch.empty_like(k), torch.empty_like(v)
-    delta = torch.empty(B, H, Lq, dtype=torch.float32, device=q.device)
-    dq_out = torch.empty_like(q)
+    Lp = (Lq + 127) // 128 * 128
+    dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+    lse2 = torch.empty(B, H, Lp, dtype=torch.float32, device=q.device)
+    delta = torch.empty_like(lse2)
     N.check(lib.eri_flash_attn_bwd(do.data_ptr(), q.data_ptr(), k.data_ptr(), v.data_ptr(),
-                                   out.data_ptr(), lse.data_ptr(), delta.data_ptr(),
-                                   dq.data_ptr(), dq_out.data_ptr(), dk.data_ptr(), dv.data_ptr(),
+                                   out.data_ptr(), lse.data_ptr(), lse2.data_ptr(),
+                                   delta.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(),
                                    B, H, Lq, Lk, D, scale, N.stream_ptr()), "flash_attn_bwd")
-    return dq_out, dk, dv
+    return dq, dk, dv
 
 
 def check_error() -> int:
     lib = N.require()
     _bind(lib)
-    return lib.eri_fa_check_error()
+    e = lib.eri_fa_check_error()
+    if not e and hasattr(lib, "eri_fa_bwd_check_error"):
+        e = lib.eri_fa_bwd_check_error()
+    return e
 
 
 class _FlashAttention(torch.autograd.Function):
