@@ -532,3 +532,131 @@ int eri_flash_attn_bwd(const void* dout, const void* q, const void* k, const voi
 }
 
 }  // extern "C"
+
+// ---------------------------------------------------------------------------------------------
+// Allocation-free attention backward (declared in flash_attn_noalloc.h).
+//
+// Who needs this: code that drives the library from a place where asking CUDA for memory is not
+// possible or not allowed — a host application that hands this library a fixed memory budget and
+// forbids any further cudaMalloc, a plug-in running inside another framework's allocator that
+// must not allocate behind its back, or a real-time loop where an allocation (which may
+// synchronise the device or fail under fragmentation) is unacceptable. Such callers can provide
+// the inputs and outputs they own, but have nowhere to get the kernel's two scratch vectors
+// (the log-sum-exp in log2 units and the row sums of O*dO). Here the scratch lives in a
+// fixed-size array that is part of the loaded library image on every GPU.
+//
+// Limits and rules:
+//  * B * H * ceil(Lq/128)*128 must not exceed ERI_FA_NOALLOC_MAX_ROWS (262144 rows; the array
+//    holds two fp32 vectors of that length, 2 MiB per GPU that loads the library, kept until the
+//    process exits). Larger problems are rejected with ERI_FA_NOALLOC_TOO_LARGE.
+//  * The first call on each device looks up the device address of the array (and of the status
+//    word) with cudaGetSymbolAddress while that device is current. Make that first call outside
+//    of any stream capture.
+//  * Every call on a device uses the same array. The array keeps whatever the previous call left
+//    in it; this kernel overwrites every element it later reads, so nothing has to be cleared.
+//    Two calls whose GPU work overlaps in time (different streams, or different host threads)
+//    race on the array and corrupt each other: serialise them.
+//  * No cudaMalloc / cudaFree / cudaMallocAsync and no allocating library routine is called.
+// ---------------------------------------------------------------------------------------------
+#define ERI_FA_NOALLOC_MAX_ROWS 262144
+#define ERI_FA_NOALLOC_MAX_DEVICES 64
+
+static __device__ __align__(256) float g_fa_noalloc_scratch[2 * ERI_FA_NOALLOC_MAX_ROWS];
+static __device__ __align__(256) int g_fa_noalloc_status[64];
+
+static float* g_fa_noalloc_scratch_addr[ERI_FA_NOALLOC_MAX_DEVICES] = {nullptr};
+static int* g_fa_noalloc_status_addr[ERI_FA_NOALLOC_MAX_DEVICES] = {nullptr};
+
+namespace {
+
+// Tensor-map encode without the host-side cache (the cache grows a std::unordered_map).
+int encode_map_uncached(CUtensorMap* m, const void* ptr, int B, int L, int H, int DH) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (!fn) return -1;
+  cuuint64_t dims[3] = {(cuuint64_t)H * DH, (cuuint64_t)L, (cuuint64_t)B};
+  cuuint64_t strides[2] = {(cuuint64_t)H * DH * 2, (cuuint64_t)L * H * DH * 2};
+  cuuint32_t box[3] = {64, 128, 1};
+  cuuint32_t es[3] = {1, 1, 1};
+  CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(ptr), dims, strides,
+                  box, es, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : -1;
+}
+
+}  // namespace
+
+extern "C" {
+
+const char* eri_flash_attn_bwd_noalloc_strerror(int code) {
+  switch (code) {
+    case 0: return "ok";
+    case -1: return "head_dim must be 64 or 128";
+    case -2: return "sequence lengths must be at least 128";
+    case -4: return "could not encode a TMA tensor map for one of the tensors";
+    case -5: return "could not raise the kernel's shared-memory limit";
+    case -6: return "ERI_FA_NOALLOC_TOO_LARGE: B*H*ceil(Lq/128)*128 exceeds the 262144-row static scratch";
+    case -7: return "cudaGetSymbolAddress failed for the static scratch array";
+    case -8: return "device ordinal above the supported table size";
+    default: return "CUDA launch error (value is a cudaError_t)";
+  }
+}
+
+int eri_flash_attn_bwd_noalloc_max_rows() { return ERI_FA_NOALLOC_MAX_ROWS; }
+
+// Reads (and clears) the status word the kernels set when one of their bounded waits ran out.
+// Synchronous device-to-host copy of 4 bytes; allocates nothing. 0 = clean.
+int eri_flash_attn_bwd_noalloc_status() {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev >= ERI_FA_NOALLOC_MAX_DEVICES) return -8;
+  if (!g_fa_noalloc_status_addr[dev]) return 0;
+  int h = 0;
+  cudaMemcpy(&h, g_fa_noalloc_status_addr[dev], sizeof(int), cudaMemcpyDeviceToHost);
+  if (h) cudaMemset(g_fa_noalloc_status_addr[dev], 0, sizeof(int));
+  return h;
+}
+
+// dout, q, out, dq: [B, Lq, H, DH]; k, v, dk, dv: [B, Lk, H, DH]; all contiguous bf16 on the
+// current device. lse: [B, H, Lq] fp32 as written by eri_flash_attn_fwd. Work is enqueued on
+// `stream`; returns 0 or a negative code (see eri_flash_attn_bwd_noalloc_strerror).
+int eri_flash_attn_bwd_noalloc(const void* dout, const void* q, const void* k, const void* v,
+                               const void* out, const float* lse, void* dq, void* dk, void* dv,
+                               int B, int H, int Lq, int Lk, int DH, float scale, void* stream) {
+  if (DH != 64 && DH != 128) return -1;
+  if (Lq < 128 || Lk < 128) return -2;
+  const int Lp = (Lq + T - 1) / T * T;
+  const long long rows = (long long)B * H * Lp;
+  if (rows > ERI_FA_NOALLOC_MAX_ROWS) return -6;
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= ERI_FA_NOALLOC_MAX_DEVICES) return -8;
+  if (!g_fa_noalloc_scratch_addr[dev]) {
+    // One-time set-up for this device: the array's name is only a host-side handle, the kernels
+    // need its device address.
+    float* sp = nullptr;
+    int* ep = nullptr;
+    if (cudaGetSymbolAddress((void**)&sp, g_fa_noalloc_scratch) != cudaSuccess || !sp) return -7;
+    if (cudaGetSymbolAddress((void**)&ep, g_fa_noalloc_status) != cudaSuccess || !ep) return -7;
+    g_fa_noalloc_status_addr[dev] = ep;
+    g_fa_noalloc_scratch_addr[dev] = sp;
+  }
+  float* lse2 = g_fa_noalloc_scratch_addr[dev];
+  float* delta = lse2 + ERI_FA_NOALLOC_MAX_ROWS;
+  cudaStream_t st = (cudaStream_t)stream;
+  {
+    const int block = 256;
+    const long long grid = (rows * 32 + block - 1) / block;
+    fa_bwd_prep_kernel<<<(unsigned)grid, block, 0, st>>>((const bf16*)out, (const bf16*)dout, lse,
+                                                         lse2, delta, B, H, Lq, Lp, DH);
+  }
+  CUtensorMap tq, tk, tv, td;
+  if (encode_map_uncached(&tq, q, B, Lq, H, DH) || encode_map_uncached(&tk, k, B, Lk, H, DH) ||
+      encode_map_uncached(&tv, v, B, Lk, H, DH) || encode_map_uncached(&td, dout, B, Lq, H, DH))
+    return -4;
+  FaBwdParams p;
+  p.B = B; p.H = H; p.Lq = Lq; p.Lk = Lk; p.Lp = Lp;
+  p.scale = scale; p.scale_log2 = scale * 1.4426950408889634f;
+  p.lse2 = lse2; p.delta = delta;
+  p.dq = (bf16*)dq; p.dk = (bf16*)dk; p.dv = (bf16*)dv; p.err = g_fa_noalloc_status_addr[dev];
+  return DH == 128 ? launch_bwd<128>(tq, tk, tv, td, p, st) : launch_bwd<64>(tq, tk, tv, td, p, st);
+}
+
+}  // extern "C"
