@@ -41,6 +41,19 @@ class ParamArena:
                 p.data = self.data[o:o + n].view(p.shape)
                 p.grad = self.grad[o:o + n].view(p.shape)
 
+    def rebase(self, new_data: torch.Tensor, new_grad: torch.Tensor):
+        """Move the arena into caller-provided buffers (e.g. symmetric peer-mapped memory) and
+        re-point every parameter and gradient view."""
+        assert new_data.numel() == self.numel and new_grad.numel() == self.numel
+        with torch.no_grad():
+            new_data.copy_(self.data)
+            new_grad.copy_(self.grad)
+            self.data, self.grad = new_data, new_grad
+            for p, o in zip(self.params, self.offsets):
+                n = p.numel()
+                p.data = self.data[o:o + n].view(p.shape)
+                p.grad = self.grad[o:o + n].view(p.shape)
+
     def zero_grad(self):
         self.grad.zero_()
 
