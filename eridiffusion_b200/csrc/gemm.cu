@@ -1,4 +1,4 @@
-// Persistent warp-specialised bf16 GEMM for sm_100a:  C[M,N] = epilogue(A[M,K] * B[N,K]^T)
+// Persistent warp-specialised bf16 GEMM for sm_100a:  C[M,N] = epilogue(A[M,K] * op(B))
 //
 //   warp 0      TMA producer: cp.async.bulk.tensor tiles (128-byte swizzle) into a STAGES-deep ring
 //   warp 1      UMMA issuer: tcgen05.mma (M=128, N=BN, K=16) from shared memory into TMEM;
@@ -6,11 +6,16 @@
 //   warps 2-5   epilogue: tcgen05.ld the fp32 accumulator (two TMEM buffers, so tile i drains
 //               while tile i+1 accumulates), apply the fused epilogue, store bf16
 //
+// B is either [N, K] row-major (K-major operand, a weight used as y = x W^T) or [K, N] row-major
+// (MN-major operand: the same weight tensor W[N_out, K_in] read as dX = dY W without a transposed
+// copy).
+//
 // Fused epilogue (all optional): alpha, bias[N], GELU(tanh)/SiLU with the pre-activation kept
 // for backward, activation backward (multiply by f'(pre)), adaLN gate + residual
-// (out = R + gate[batch] * y), and a column split that routes columns >= n_split (with the
-// activation) to a second destination, which removes the split/cat copies around FLUX
-// single-stream blocks.
+// (out = R + gate[batch] * y), a column split that routes columns >= n_split (with the
+// activation) to a second destination, and a peer scatter that stores each head group's columns
+// straight into the owning rank's buffer over NVLink (Ulysses all-to-all folded into the QKV
+// projection).
 //
 // LoRA: Y = X W^T + (s X A^T) B^T is one launch of this kernel for the rank-r product
 // H = s X A^T followed by the main launch, which appends one extra K step whose operands are
@@ -18,7 +23,13 @@
 // so no [M,N] delta tensor is ever written. (Reference: two library GEMMs, a scale and an add per
 // site, crates/training/src/flux/lora.rs:47-63, crates/training/src/flux/runtime.rs:555-600.)
 //
-// No cluster launch and no multicast: every CTA loads its own operand tiles.
+// Gather mode (ZeRO-3 parameter all-gather / Ulysses reverse all-to-all fused with the GEMM):
+// the first `n_copy` CTAs of the same launch do not compute; they pull slabs of an operand from
+// peer GPUs (plain 16-byte peer loads) into a local landing buffer and bump a per-slab counter.
+// The TMA producer of every compute CTA waits (bounded) on the counter of the slab it is about to
+// load, and tile / K order start at this rank's own slab, so the math on slabs that have landed
+// overlaps the transfer of the rest. The launch is cooperative, which guarantees the copy CTAs are
+// resident. Remote data is always read from local memory by TMA, never with a multicast load.
 #include "ptx.cuh"
 #include "tma_host.h"
 
@@ -27,6 +38,18 @@ typedef __nv_bfloat16 bf16;
 
 namespace {
 
+constexpr int kMaxPeers = 16;
+
+struct GatherJob {
+  const void* src;   // peer (or local) source, 16-byte aligned
+  void* dst;         // local landing address
+  int rows;
+  int row_bytes;     // multiple of 16
+  long long src_stride, dst_stride;  // bytes
+  int flag;          // counter bumped when the job is done
+  int pad;
+};
+
 struct GemmParams {
   int M, N, K, num_k;
   int lora_r;          // 0, 16, 32 or 64
@@ -34,6 +57,7 @@ struct GemmParams {
   int n_split;         // columns >= n_split take the activation and go to out2 (tile aligned)
   int ldc, ldc2, ld_pre, ldr;
   int rows_per_batch, gate_stride;
+  int b_mn;            // B given as [K, N] (MN-major operand)
   float alpha;
   const bf16* bias;
   const bf16* residual;
@@ -43,6 +67,22 @@ struct GemmParams {
   bf16* out2;           // indexed with (col - n_split)
   bf16* pre_out;        // indexed with (col - n_split)
   int* err;
+  // gather mode
+  int n_copy;                 // leading CTAs that run copy jobs
+  int n_jobs;
+  const GatherJob* jobs;
+  unsigned int* flags;        // per-slab counters (zeroed before the launch)
+  const unsigned int* flag_target;
+  int b_flag_rows;            // rows of B per slab (0: B is not gathered)
+  int a_flag_cols;            // K columns of A per slab (0: A is not gathered)
+  int rot_n, rot_k;           // rotation of tile order / K order towards the local slab
+  // peer scatter epilogue
+  int scatter_world;          // 0: off
+  int scatter_rank;
+  int scatter_part_cols;      // columns of one part (q, k or v) = H * Dh
+  int scatter_group_cols;     // columns of one rank's head group = (H / world) * Dh
+  int scatter_local_rows;     // tokens per batch element on this rank
+  bf16* scatter_out[kMaxPeers];
 };
 
 constexpr int BM = 128, BK = 64;
@@ -52,7 +92,8 @@ __host__ __device__ constexpr int tmem_cols_for(int bn) {
   return 2 * bn <= 32 ? 32 : 2 * bn <= 64 ? 64 : 2 * bn <= 128 ? 128 : 2 * bn <= 256 ? 256 : 512;
 }
 
-__device__ __forceinline__ void tile_coords(int t, int num_m, int num_n, int& m_blk, int& n_blk) {
+__device__ __forceinline__ void tile_coords(int t, int num_m, int num_n, int rot_n, int& m_blk,
+                                            int& n_blk) {
   const int group_sz = kGroupN * num_m;
   const int g = t / group_sz;
   const int first_n = g * kGroupN;
@@ -60,6 +101,10 @@ __device__ __forceinline__ void tile_coords(int t, int num_m, int num_n, int& m_
   const int r = t - g * group_sz;
   n_blk = first_n + r % gw;
   m_blk = r / gw;
+  if (rot_n) {
+    n_blk += rot_n;
+    if (n_blk >= num_n) n_blk -= num_n;
+  }
 }
 
 __device__ __forceinline__ float apply_act(float v, int act) {
@@ -69,16 +114,66 @@ __device__ __forceinline__ float apply_act_grad(float pre, int act) {
   return act == 3 ? gelu_tanh_grad_f(pre) : silu_grad_f(pre);
 }
 
+__device__ __forceinline__ unsigned int ld_acquire_gpu(const unsigned int* p) {
+  unsigned int v;
+  asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void fence_proxy_async_all() {
+  asm volatile("fence.proxy.async;" ::: "memory");
+}
+
+// Bounded wait for a landing-slab counter. Returns false when the wait ran out.
+__device__ __forceinline__ bool wait_slab(const GemmParams& p, int f) {
+  const unsigned int want = p.flag_target[f];
+  if (ld_acquire_gpu(p.flags + f) >= want) return true;
+  const uint64_t t0 = globaltimer_ns();
+  for (uint32_t i = 0; i < (1u << 28); ++i) {
+    if (ld_acquire_gpu(p.flags + f) >= want) return true;
+    if ((i & 63u) == 63u && globaltimer_ns() - t0 > ERI_WAIT_LIMIT_NS) return false;
+  }
+  return false;
+}
+
+__device__ void copy_role(const GemmParams& p) {
+  for (int j = blockIdx.x; j < p.n_jobs; j += p.n_copy) {
+    const GatherJob job = p.jobs[j];
+    const int vec_per_row = job.row_bytes >> 4;
+    const long long total = (long long)job.rows * vec_per_row;
+    for (long long i = threadIdx.x; i < total; i += blockDim.x) {
+      const long long r = i / vec_per_row;
+      const int c = (int)(i - r * vec_per_row);
+      const uint4 v = *reinterpret_cast<const uint4*>(reinterpret_cast<const char*>(job.src) +
+                                                      r * job.src_stride + (size_t)c * 16);
+      *reinterpret_cast<uint4*>(reinterpret_cast<char*>(job.dst) + r * job.dst_stride +
+                                (size_t)c * 16) = v;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      __threadfence();
+      fence_proxy_async_all();
+      atomicAdd(p.flags + job.flag, 1u);
+    }
+  }
+}
+
 template <int BN, int STAGES>
 __global__ void __launch_bounds__(192, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                  const __grid_constant__ CUtensorMap tmA2, const __grid_constant__ CUtensorMap tmB2,
-                 const GemmParams p) {
+                 const __grid_constant__ GemmParams p) {
   constexpr int A_BYTES = BM * BK * 2;
   constexpr int B_BYTES = BN * BK * 2;
   constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   constexpr int TMEM_COLS = tmem_cols_for(BN);
   constexpr int CH = BN >= 32 ? 32 : 16;  // accumulator columns per TMEM load
+
+  if ((int)blockIdx.x < p.n_copy) {
+    copy_role(p);
+    return;
+  }
+  const int worker = blockIdx.x - p.n_copy;
+  const int nworkers = gridDim.x - p.n_copy;
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
@@ -118,17 +213,29 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   const int num_n = (p.N + BN - 1) / BN;
   const int tiles = num_m * num_n;
   const int k_iters = p.num_k + (p.lora_r > 0 ? 1 : 0);
-  const uint32_t idesc = umma_idesc_bf16(BM, BN);
+  const uint32_t idesc = umma_idesc_bf16(BM, BN, 0, p.b_mn);
 
   if (warp == 0) {
     if (elect_one()) {
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int t = blockIdx.x; t < tiles && ok; t += gridDim.x) {
+      for (int t = worker; t < tiles && ok; t += nworkers) {
         int m_blk, n_blk;
-        tile_coords(t, num_m, num_n, m_blk, n_blk);
+        tile_coords(t, num_m, num_n, p.rot_n, m_blk, n_blk);
         const int m0 = m_blk * BM, n0 = n_blk * BN;
+        if (p.b_flag_rows) {
+          // every slab this tile's B rows touch must have landed
+          const int f0 = n0 / p.b_flag_rows, f1 = (min(n0 + BN, p.N) - 1) / p.b_flag_rows;
+          for (int f = f0; f <= f1 && ok; ++f)
+            if (!wait_slab(p, f)) {
+              atomicExch(p.err, 5);
+              ok = false;
+            }
+          if (!ok) break;
+          fence_proxy_async_all();
+        }
+        int a_ready = -1;
         for (int k = 0; k < k_iters; ++k) {
           if (!mbar_wait(&empty[stage], phase ^ 1)) {
             atomicExch(p.err, 1);
@@ -138,9 +245,29 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           uint8_t* sA = smem + stage * STAGE_BYTES;
           uint8_t* sB = sA + A_BYTES;
           if (k < p.num_k) {
+            int kk = k + p.rot_k;
+            if (kk >= p.num_k) kk -= p.num_k;
+            if (p.a_flag_cols) {
+              const int f = (kk * BK) / p.a_flag_cols;
+              if (f != a_ready) {
+                if (!wait_slab(p, f)) {
+                  atomicExch(p.err, 6);
+                  ok = false;
+                  break;
+                }
+                fence_proxy_async_all();
+                a_ready = f;
+              }
+            }
             mbar_expect_tx(&full[stage], STAGE_BYTES);
-            tma_load_2d(sA, &tmA, &full[stage], k * BK, m0);
-            tma_load_2d(sB, &tmB, &full[stage], k * BK, n0);
+            tma_load_2d(sA, &tmA, &full[stage], kk * BK, m0);
+            if (!p.b_mn) {
+              tma_load_2d(sB, &tmB, &full[stage], kk * BK, n0);
+            } else {
+#pragma unroll
+              for (int c = 0; c < (BN >= 64 ? BN / 64 : 1); ++c)
+                tma_load_2d(sB + c * (BK * 128), &tmB, &full[stage], n0 + c * 64, kk * BK);
+            }
           } else {
             mbar_expect_tx(&full[stage], (BM + BN) * p.lora_r * 2);
             tma_load_2d(sA, &tmA2, &full[stage], 0, m0);
@@ -159,7 +286,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       uint32_t phase = 0;
       bool ok = true;
       int it = 0;
-      for (int t = blockIdx.x; t < tiles && ok; t += gridDim.x, ++it) {
+      const uint32_t idesc_lora = umma_idesc_bf16(BM, BN, 0, 0);
+      for (int t = worker; t < tiles && ok; t += nworkers, ++it) {
         const int buf = it & 1;
         const uint32_t use = (uint32_t)(it >> 1);
         if (!mbar_wait(&acc_empty[buf], (use & 1) ^ 1)) {
@@ -178,15 +306,23 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           const uint32_t sA = smem_u32(smem + stage * STAGE_BYTES);
           const uint32_t sB = sA + A_BYTES;
           if (k < p.num_k) {
-            const uint64_t da = umma_desc_kmajor(sA, 128), db = umma_desc_kmajor(sB, 128);
+            const uint64_t da = umma_desc_kmajor(sA, 128);
+            if (!p.b_mn) {
+              const uint64_t db = umma_desc_kmajor(sB, 128);
 #pragma unroll
-            for (int kk = 0; kk < BK / 16; ++kk)
-              umma_bf16(d_tmem, da + kk * 2, db + kk * 2, idesc, (k | kk) != 0);
+              for (int kk = 0; kk < BK / 16; ++kk)
+                umma_bf16(d_tmem, da + kk * 2, db + kk * 2, idesc, (k | kk) != 0);
+            } else {
+#pragma unroll
+              for (int kk = 0; kk < BK / 16; ++kk)
+                umma_bf16(d_tmem, da + kk * 2, umma_desc_mn128(sB + kk * 2048, BK * 128), idesc,
+                          (k | kk) != 0);
+            }
           } else {
             const uint32_t sw = p.lora_r * 2;
             const uint64_t da = umma_desc_kmajor(sA, sw), db = umma_desc_kmajor(sB, sw);
             for (int kk = 0; kk < p.lora_r / 16; ++kk)
-              umma_bf16(d_tmem, da + kk * 2, db + kk * 2, idesc, (k | kk) != 0);
+              umma_bf16(d_tmem, da + kk * 2, db + kk * 2, idesc_lora, (k | kk) != 0);
           }
           umma_commit(&empty[stage]);
           if (++stage == STAGES) {
@@ -200,9 +336,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   } else {
     const int q = warp & 3;  // TMEM lane quarter this warp may read
     int it = 0;
-    for (int t = blockIdx.x; t < tiles; t += gridDim.x, ++it) {
+    for (int t = worker; t < tiles; t += nworkers, ++it) {
       int m_blk, n_blk;
-      tile_coords(t, num_m, num_n, m_blk, n_blk);
+      tile_coords(t, num_m, num_n, p.rot_n, m_blk, n_blk);
       const int m0 = m_blk * BM, n0 = n_blk * BN;
       const int buf = it & 1;
       const uint32_t use = (uint32_t)(it >> 1);
@@ -217,7 +353,20 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       const int act = second || p.n_split < 0 ? p.act : 0;
       const int coff = second ? p.n_split : 0;
       bf16* dst = second && p.out2 ? p.out2 + (size_t)row * p.ldc2 : p.out + (size_t)row * p.ldc;
-      const int dcol_off = second && p.out2 ? coff : 0;
+      int dcol_off = second && p.out2 ? coff : 0;
+      if (p.scatter_world) {
+        // all columns of a tile belong to one (part, rank) group
+        const int part = n0 / p.scatter_part_cols;
+        const int within = n0 - part * p.scatter_part_cols;
+        const int dest = within / p.scatter_group_cols;
+        const int bidx = row_ok ? row / p.scatter_local_rows : 0;
+        const int lrow = row - bidx * p.scatter_local_rows;
+        const size_t drow = (size_t)bidx * p.scatter_world * p.scatter_local_rows +
+                            (size_t)p.scatter_rank * p.scatter_local_rows + lrow;
+        dst = p.scatter_out[dest] + drow * p.ldc;
+        // destination column = part * group_cols + (col % group_cols)
+        dcol_off = n0 - (part * p.scatter_group_cols + (within - dest * p.scatter_group_cols));
+      }
       const bf16* gate = p.gate ? p.gate + (size_t)(row_ok ? row / p.rows_per_batch : 0) * p.gate_stride
                                 : nullptr;
 #pragma unroll 1
@@ -300,7 +449,14 @@ int launch(const CUtensorMap& a, const CUtensorMap& b, const CUtensorMap& a2, co
     configured = true;
   }
   const int tiles = ((p.M + BM - 1) / BM) * ((p.N + BN - 1) / BN);
-  const int grid = tiles < max_ctas ? tiles : max_ctas;
+  const int room = max_ctas - p.n_copy;
+  const int grid = p.n_copy + (tiles < room ? tiles : room);
+  if (p.n_copy > 0) {
+    // the compute CTAs spin on counters that the copy CTAs bump: all must be resident
+    void* args[] = {(void*)&a, (void*)&b, (void*)&a2, (void*)&b2, (void*)&p};
+    return (int)cudaLaunchCooperativeKernel((const void*)gemm_bf16_kernel<BN, STAGES>, dim3(grid),
+                                            dim3(192), args, SMEM, stream);
+  }
   gemm_bf16_kernel<BN, STAGES><<<grid, 192, SMEM, stream>>>(a, b, a2, b2, p);
   return (int)cudaGetLastError();
 }
@@ -314,7 +470,7 @@ extern "C" {
 
 struct EriGemmArgs {
   const void* a;        // [M, K] bf16, row stride lda
-  const void* b;        // [N, K] bf16, row stride ldb
+  const void* b;        // [N, K] bf16 (or [K, N] when b_mn), row stride ldb
   const void* lora_h;   // [M, r] bf16 (row stride ld_h) or null
   const void* lora_b;   // [N, r] bf16 (row stride ld_lb) or null
   const void* bias;
@@ -331,6 +487,16 @@ struct EriGemmArgs {
   int rows_per_batch, gate_stride;
   int force_bn;
   float alpha;
+  int b_mn;
+  // gather mode (all zero / null when unused)
+  int n_copy, n_jobs;
+  const void* jobs;
+  void* flags;
+  const void* flag_target;
+  int b_flag_rows, a_flag_cols, rot_n_rows, rot_k_cols;
+  // peer scatter
+  int scatter_world, scatter_rank, scatter_part_cols, scatter_group_cols, scatter_local_rows;
+  void* scatter_out[kMaxPeers];
 };
 
 // One-time set-up of the device error word (allocates 4 bytes). Returns 0 on success.
@@ -353,6 +519,8 @@ int eri_gemm_check_error() {
   if (h) cudaMemset(g_err_flag, 0, sizeof(int));
   return h;
 }
+
+int eri_gemm_job_size() { return (int)sizeof(GatherJob); }
 
 int eri_gemm_bf16(const EriGemmArgs* g, void* stream) {
   if (!g_err_flag) {
@@ -377,19 +545,36 @@ int eri_gemm_bf16(const EriGemmArgs* g, void* stream) {
   if (g->n_split > 0 && g->n_split % bn) {
     if (g->n_split % 128 == 0) bn = 128; else if (g->n_split % 64 == 0) bn = 64; else return -14;
   }
+  if (g->scatter_world) {
+    while (bn > 16 && (g->scatter_group_cols % bn)) bn >>= 1;
+    if (g->scatter_group_cols % bn) return -17;
+  }
+  if (g->b_mn && bn < 64) return -18;
   if (g->M < BM) return -15;  // box taller than the tensor: use the small-M path instead
 
   GemmParams p;
+  memset(&p, 0, sizeof(p));
   p.M = g->M; p.N = g->N; p.K = g->K; p.num_k = (g->K + BK - 1) / BK;
   p.lora_r = g->lora_r; p.act = g->act; p.n_split = g->n_split > 0 ? g->n_split : -1;
   if (g->n_split == 0 && g->out2) p.n_split = 0;
   p.ldc = g->ldc; p.ldc2 = g->ldc2; p.ld_pre = g->ld_pre; p.ldr = g->ldr;
   p.rows_per_batch = g->rows_per_batch > 0 ? g->rows_per_batch : g->M;
-  p.gate_stride = g->gate_stride; p.alpha = g->alpha;
+  p.gate_stride = g->gate_stride; p.alpha = g->alpha; p.b_mn = g->b_mn;
   p.bias = (const bf16*)g->bias; p.residual = (const bf16*)g->residual;
   p.gate = (const bf16*)g->gate; p.pre_in = (const bf16*)g->pre_in;
   p.out = (bf16*)g->out; p.out2 = (bf16*)g->out2; p.pre_out = (bf16*)g->pre_out;
   p.err = g_err_flag;
+  p.n_copy = g->n_copy; p.n_jobs = g->n_jobs; p.jobs = (const GatherJob*)g->jobs;
+  p.flags = (unsigned int*)g->flags; p.flag_target = (const unsigned int*)g->flag_target;
+  p.b_flag_rows = g->b_flag_rows; p.a_flag_cols = g->a_flag_cols;
+  p.rot_n = g->rot_n_rows / bn;
+  p.rot_k = g->rot_k_cols / BK;
+  if (p.n_copy < 0 || p.n_copy > g_num_sms / 2) return -19;
+  if (p.a_flag_cols % BK) return -19;
+  p.scatter_world = g->scatter_world; p.scatter_rank = g->scatter_rank;
+  p.scatter_part_cols = g->scatter_part_cols; p.scatter_group_cols = g->scatter_group_cols;
+  p.scatter_local_rows = g->scatter_local_rows > 0 ? g->scatter_local_rows : g->M;
+  for (int i = 0; i < kMaxPeers; ++i) p.scatter_out[i] = (bf16*)g->scatter_out[i];
 
   CUtensorMap ta, tb, ta2, tb2;
   {
@@ -398,10 +583,15 @@ int eri_gemm_bf16(const EriGemmArgs* g, void* stream) {
     uint32_t bx[2] = {BK, BM};
     if (make_tensor_map(&ta, g->a, 2, d, s, bx, 128)) return -20;
   }
-  {
+  if (!g->b_mn) {
     uint64_t d[2] = {(uint64_t)g->K, (uint64_t)g->N};
     uint64_t s[1] = {(uint64_t)g->ldb * 2};
     uint32_t bx[2] = {BK, (uint32_t)bn};
+    if (make_tensor_map(&tb, g->b, 2, d, s, bx, 128)) return -21;
+  } else {
+    uint64_t d[2] = {(uint64_t)g->N, (uint64_t)g->K};
+    uint64_t s[1] = {(uint64_t)g->ldb * 2};
+    uint32_t bx[2] = {64, BK};
     if (make_tensor_map(&tb, g->b, 2, d, s, bx, 128)) return -21;
   }
   if (g->lora_r) {

@@ -37,8 +37,22 @@ class GemmArgs(C.Structure):
         ("act", C.c_int), ("n_split", C.c_int),
         ("ldc", C.c_int), ("ldc2", C.c_int), ("ld_pre", C.c_int), ("ldr", C.c_int),
         ("rows_per_batch", C.c_int), ("gate_stride", C.c_int),
-        ("force_bn", C.c_int), ("alpha", C.c_float),
+        ("force_bn", C.c_int), ("alpha", C.c_float), ("b_mn", C.c_int),
+        ("n_copy", C.c_int), ("n_jobs", C.c_int),
+        ("jobs", C.c_void_p), ("flags", C.c_void_p), ("flag_target", C.c_void_p),
+        ("b_flag_rows", C.c_int), ("a_flag_cols", C.c_int), ("rot_n_rows", C.c_int),
+        ("rot_k_cols", C.c_int),
+        ("scatter_world", C.c_int), ("scatter_rank", C.c_int), ("scatter_part_cols", C.c_int),
+        ("scatter_group_cols", C.c_int), ("scatter_local_rows", C.c_int),
+        ("scatter_out", C.c_void_p * 16),
     ]
+
+
+class GatherJob(C.Structure):
+    """One copy job of the gather-fused GEMM (mirrors ``GatherJob`` in csrc/gemm.cu)."""
+    _fields_ = [("src", C.c_void_p), ("dst", C.c_void_p), ("rows", C.c_int), ("row_bytes", C.c_int),
+                ("src_stride", C.c_longlong), ("dst_stride", C.c_longlong), ("flag", C.c_int),
+                ("pad", C.c_int)]
 
 
 _P, _I, _L, _F, _U64, _U32 = C.c_void_p, C.c_int, C.c_longlong, C.c_float, C.c_ulonglong, C.c_uint

@@ -326,15 +326,19 @@ _ACT_CODE = {None: 0, "gelu": 1, "silu": 2, "gelu_bwd": 3, "silu_bwd": 4}
 
 def gemm_native(a, b, *, out=None, alpha=1.0, bias=None, lora_h=None, lora_b=None, act=None,
                 pre_out=None, pre_in=None, residual=None, gate=None, rows_per_batch=0,
-                n_split=0, out2=None, force_bn=0):
-    """out[M,N] = epilogue(a[M,K] @ b[N,K]^T (+ lora_h[M,r] @ lora_b[N,r]^T)) on the tcgen05 kernel.
+                n_split=0, out2=None, force_bn=0, b_mn=False, gather=None, scatter=None):
+    """out[M,N] = epilogue(a[M,K] @ op(b) (+ lora_h[M,r] @ lora_b[N,r]^T)) on the tcgen05 kernel.
 
-    ``a``/``b``/``out`` may be row-strided views (last dim contiguous). Returns ``out``.
+    ``b`` is [N, K] (``op`` = transpose) or, with ``b_mn=True``, [K, N] used as is. ``a``/``b``/
+    ``out`` may be row-strided views (last dim contiguous). ``gather``: dict built by
+    ``parallel.gather_gemm`` (copy jobs + slab counters, fuses an operand gather into the launch).
+    ``scatter``: dict(world, rank, part_cols, group_cols, local_rows, ptrs) routing column groups
+    to peer buffers (``out`` is then only used for its row stride). Returns ``out``.
     """
     lib = N.require()
     M, K = a.shape
-    Nn = b.shape[0]
-    assert b.shape[1] == K and a.stride(1) == 1 and b.stride(1) == 1
+    Nn = b.shape[1] if b_mn else b.shape[0]
+    assert (b.shape[0] if b_mn else b.shape[1]) == K and a.stride(1) == 1 and b.stride(1) == 1
     if out is None:
         out = torch.empty(M, Nn if not n_split else n_split, dtype=torch.bfloat16, device=a.device)
     g = N.GemmArgs()
@@ -362,6 +366,18 @@ def gemm_native(a, b, *, out=None, alpha=1.0, bias=None, lora_h=None, lora_b=Non
     if out2 is not None:
         g.out2, g.ldc2 = out2.data_ptr(), out2.stride(0)
     g.force_bn = force_bn
+    g.b_mn = 1 if b_mn else 0
+    if gather is not None:
+        g.n_copy, g.n_jobs = gather["n_copy"], gather["n_jobs"]
+        g.jobs, g.flags, g.flag_target = gather["jobs"], gather["flags"], gather["flag_target"]
+        g.b_flag_rows, g.a_flag_cols = gather.get("b_flag_rows", 0), gather.get("a_flag_cols", 0)
+        g.rot_n_rows, g.rot_k_cols = gather.get("rot_n_rows", 0), gather.get("rot_k_cols", 0)
+    if scatter is not None:
+        g.scatter_world, g.scatter_rank = scatter["world"], scatter["rank"]
+        g.scatter_part_cols, g.scatter_group_cols = scatter["part_cols"], scatter["group_cols"]
+        g.scatter_local_rows = scatter["local_rows"]
+        for i, ptr_ in enumerate(scatter["ptrs"]):
+            g.scatter_out[i] = ptr_
     code = lib.eri_gemm_bf16(g, N.stream_ptr())
     N.check(code, "gemm_bf16")
     return out

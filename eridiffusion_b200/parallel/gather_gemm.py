@@ -1,0 +1,106 @@
+"""Operand gathers fused into the GEMM launch.
+
+``GatherPlan`` describes how an operand is assembled in a local landing buffer from slabs that
+live on peer GPUs: a device array of copy jobs (source pointer, destination pointer, rows, row
+bytes, strides, slab id) plus one counter per slab. The GEMM launch (``csrc/gemm.cu``) reserves
+its first ``n_copy`` CTAs to execute the jobs with plain 16-byte peer loads; compute CTAs wait on
+the counter of the slab they are about to read and start with this rank's own slab, so the tensor
+cores work on data that has landed while the remaining slabs are still crossing NVLink.
+
+Two layouts are provided:
+  * ``rows``  — the operand's rows are sharded (ZeRO-3 weight [N, K] sharded along N): slab p =
+    rows [p*N/W, (p+1)*N/W). Used as B ([N, K], y = x W^T; waits per output-column tile) or,
+    with ``along_k=True``, as the MN-major B of dX = dY W (waits per K block).
+  * ``cols``  — the operand's columns come from different peers (Ulysses reverse all-to-all: the
+    out-projection input [L_local, H*Dh] takes column block p from peer p's attention output);
+    waits per K block.
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import torch
+
+from ..ops import _native as N
+
+
+class GatherPlan:
+    def __init__(self, rank: int, world: int, n_copy: int = 16, device=None):
+        self.rank, self.world, self.n_copy = rank, world, n_copy
+        self.device = device or torch.device("cuda", torch.cuda.current_device())
+        self.jobs = []
+        self.targets = [0] * world
+        self._dev_jobs = None
+        self.flags = torch.zeros(world, dtype=torch.int32, device=self.device)
+        self._targets_dev = None
+        self.kw = {}
+
+    def _add(self, src, dst, rows, row_bytes, src_stride, dst_stride, flag):
+        assert row_bytes % 16 == 0 and src % 16 == 0 and dst % 16 == 0
+        j = N.GatherJob()
+        j.src, j.dst, j.rows, j.row_bytes = src, dst, rows, row_bytes
+        j.src_stride, j.dst_stride, j.flag = src_stride, dst_stride, flag
+        self.jobs.append(j)
+        self.targets[flag] += 1
+
+    @classmethod
+    def rows(cls, rank, world, shard_ptrs, landing: torch.Tensor, along_k=False, n_copy=16,
+             rows_per_job=64):
+        """landing [N, K]; shard_ptrs[p] -> peer p's [N/W, K] contiguous shard."""
+        Nn, K = landing.shape
+        assert Nn % world == 0
+        per = Nn // world
+        pl = cls(rank, world, n_copy, landing.device)
+        rb = K * landing.element_size()
+        # interleave peers so that every slab makes progress; own slab first
+        order = [(rank + i) % world for i in range(world)]
+        r0 = 0
+        while r0 < per:
+            nr = min(rows_per_job, per - r0)
+            for p in order:
+                pl._add(shard_ptrs[p] + r0 * rb, landing.data_ptr() + (p * per + r0) * landing.stride(0) * landing.element_size(),
+                        nr, rb, rb, landing.stride(0) * landing.element_size(), p)
+            r0 += nr
+        if along_k:
+            pl.kw = dict(a_flag_cols=per, rot_k_cols=rank * per)
+        else:
+            pl.kw = dict(b_flag_rows=per, rot_n_rows=rank * per)
+        return pl._finish()
+
+    @classmethod
+    def cols(cls, rank, world, src_ptrs, src_row_offset, src_stride_bytes, landing: torch.Tensor,
+             n_copy=16, rows_per_job=128):
+        """landing [L, W*C]: column block p <- peer p's rows [src_row_offset, +L) of a [*, C]
+        matrix with row stride ``src_stride_bytes``."""
+        L, WC = landing.shape
+        Cc = WC // world
+        es = landing.element_size()
+        pl = cls(rank, world, n_copy, landing.device)
+        order = [(rank + i) % world for i in range(world)]
+        r0 = 0
+        while r0 < L:
+            nr = min(rows_per_job, L - r0)
+            for p in order:
+                pl._add(src_ptrs[p] + (src_row_offset + r0) * src_stride_bytes,
+                        landing.data_ptr() + (r0 * landing.stride(0) + p * Cc) * es,
+                        nr, Cc * es, src_stride_bytes, landing.stride(0) * es, p)
+            r0 += nr
+        pl.kw = dict(a_flag_cols=Cc, rot_k_cols=rank * Cc)
+        return pl._finish()
+
+    def _finish(self):
+        arr = (N.GatherJob * len(self.jobs))(*self.jobs)
+        raw = bytes(arr)
+        self._dev_jobs = torch.frombuffer(bytearray(raw), dtype=torch.uint8).to(self.device)
+        self._targets_dev = torch.tensor(self.targets, dtype=torch.int32, device=self.device)
+        return self
+
+    def launch_args(self):
+        """Zero the slab counters (stream-ordered) and return the ``gather=`` dict for
+        ``ops.functional.gemm_native``."""
+        self.flags.zero_()
+        return dict(n_copy=self.n_copy, n_jobs=len(self.jobs), jobs=self._dev_jobs.data_ptr(),
+                    flags=self.flags.data_ptr(), flag_target=self._targets_dev.data_ptr(), **self.kw)
+
+    def bytes_from_peers(self):
+        return sum(j.rows * j.row_bytes for j in self.jobs if j.flag != self.rank)

@@ -1,0 +1,88 @@
+"""GEMM operand modes that carry the fused-communication paths: MN-major B, gathers executed by
+copy CTAs inside the launch (peers emulated by local buffers on one GPU), peer scatter epilogue."""
+import pytest
+import torch
+
+from eridiffusion_b200.ops import functional as F
+from eridiffusion_b200.parallel.gather_gemm import GatherPlan
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def rnd(*s, seed=0, scale=1.0):
+    g = torch.Generator(device=DEV).manual_seed(seed + sum(s))
+    return (torch.randn(*s, device=DEV, generator=g) * scale).bfloat16()
+
+
+def close(a, b, atol):
+    err = (a.float() - b.float()).abs().max().item()
+    assert err <= atol + 0.02 * b.float().abs().max().item(), err
+
+
+@pytest.mark.parametrize("M,N,K", [(256, 256, 128), (512, 1024, 320), (384, 192, 256)])
+def test_b_mn(M, N, K):
+    a, bt = rnd(M, K), rnd(K, N, seed=1)
+    out = F.gemm_native(a, bt, b_mn=True)
+    assert F.gemm_error_check() == 0
+    close(out, a.float() @ bt.float(), 0.05)
+
+
+@pytest.mark.parametrize("rank", [0, 2])
+def test_gather_rows_forward(rank):
+    W, M, N, K = 4, 512, 1024, 512
+    x = rnd(M, K)
+    shards = [rnd(N // W, K, seed=10 + p, scale=K ** -0.5) for p in range(W)]
+    landing = torch.full((N, K), float("nan"), device=DEV, dtype=torch.bfloat16)
+    plan = GatherPlan.rows(rank, W, [s.data_ptr() for s in shards], landing, n_copy=4)
+    out = F.gemm_native(x, landing, gather=plan.launch_args())
+    assert F.gemm_error_check() == 0
+    w = torch.cat(shards, 0)
+    assert torch.equal(landing, w)
+    close(out, x.float() @ w.float().t(), 0.05)
+
+
+@pytest.mark.parametrize("rank", [1, 3])
+def test_gather_rows_along_k_for_input_grad(rank):
+    W, M, N, K = 4, 384, 1024, 512          # dX[M, K] = dY[M, N] @ W[N, K]
+    dy = rnd(M, N)
+    shards = [rnd(N // W, K, seed=20 + p, scale=N ** -0.5) for p in range(W)]
+    landing = torch.full((N, K), float("nan"), device=DEV, dtype=torch.bfloat16)
+    plan = GatherPlan.rows(rank, W, [s.data_ptr() for s in shards], landing, along_k=True, n_copy=4)
+    out = F.gemm_native(dy, landing, b_mn=True, gather=plan.launch_args())
+    assert F.gemm_error_check() == 0
+    w = torch.cat(shards, 0)
+    close(out, dy.float() @ w.float(), 0.05)
+
+
+def test_gather_cols_reverse_all_to_all():
+    W, L, Cc, N = 4, 256, 128, 512            # out-proj input [L, W*Cc] from W peers
+    rank = 1
+    srcs = [rnd(W * L, Cc, seed=30 + p) for p in range(W)]       # peer p's attention output
+    wo = rnd(N, W * Cc, seed=50, scale=(W * Cc) ** -0.5)
+    landing = torch.full((L, W * Cc), float("nan"), device=DEV, dtype=torch.bfloat16)
+    plan = GatherPlan.cols(rank, W, [s.data_ptr() for s in srcs], rank * L, Cc * 2, landing, n_copy=4)
+    out = F.gemm_native(landing, wo, gather=plan.launch_args())
+    assert F.gemm_error_check() == 0
+    a = torch.cat([s[rank * L:(rank + 1) * L] for s in srcs], 1)
+    assert torch.equal(landing, a)
+    close(out, a.float() @ wo.float().t(), 0.05)
+
+
+def test_scatter_epilogue_routes_head_groups():
+    W, rank, B, Ll, H, Dh, K = 2, 1, 2, 128, 4, 64, 256
+    part = H * Dh                  # 256 columns per q / k / v part
+    group = part // W              # 128 columns per rank
+    x = rnd(B * Ll, K)
+    wqkv = rnd(3 * part, K, seed=1, scale=K ** -0.5)
+    bias = rnd(3 * part, seed=2)
+    dests = [torch.zeros(B * W * Ll, 3 * group, device=DEV, dtype=torch.bfloat16) for _ in range(W)]
+    F.gemm_native(x, wqkv, bias=bias, out=dests[0],
+                  scatter=dict(world=W, rank=rank, part_cols=part, group_cols=group, local_rows=Ll,
+                               ptrs=[d.data_ptr() for d in dests]))
+    assert F.gemm_error_check() == 0
+    y = (x.float() @ wqkv.float().t() + bias.float()).view(B, Ll, 3, W, group)
+    for d in range(W):
+        got = dests[d].view(B, W, Ll, 3, group)
+        close(got[:, rank], y[:, :, :, d], 0.05)
+        assert got[:, 1 - rank].abs().max().item() == 0.0
