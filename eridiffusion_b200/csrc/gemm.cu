@@ -83,6 +83,8 @@ struct GemmParams {
   int scatter_group_cols;     // columns of one rank's head group = (H / world) * Dh
   int scatter_local_rows;     // tokens per batch element on this rank
   bf16* scatter_out[kMaxPeers];
+  float* rowsq;               // optional [rowsq_parts][M]: sum of squares of each output row over
+  int rowsq_parts;            // the columns of part 0..rowsq_parts-1 (QK-norm across heads)
 };
 
 constexpr int BM = 128, BK = 64;
@@ -369,6 +371,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       }
       const bf16* gate = p.gate ? p.gate + (size_t)(row_ok ? row / p.rows_per_batch : 0) * p.gate_stride
                                 : nullptr;
+      float sq = 0.f;
 #pragma unroll 1
       for (int c = 0; c < BN / CH; ++c) {
         const int col0 = n0 + c * CH;
@@ -418,10 +421,18 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 #pragma unroll
                 for (int j = 0; j < 8; ++j) v[j] += rs[j];
               }
+              if (p.rowsq) {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) sq += v[j] * v[j];
+              }
               *reinterpret_cast<bf16x8*>(dst + (col - dcol_off)) = pack8(v);
             }
           }
         }
+      }
+      if (p.rowsq && row_ok) {
+        const int part = n0 / p.scatter_part_cols;
+        if (part < p.rowsq_parts) atomicAdd(p.rowsq + (size_t)part * p.M + row, sq);
       }
       tc_fence_before();
       __syncwarp();
@@ -497,6 +508,8 @@ struct EriGemmArgs {
   // peer scatter
   int scatter_world, scatter_rank, scatter_part_cols, scatter_group_cols, scatter_local_rows;
   void* scatter_out[kMaxPeers];
+  void* rowsq;
+  int rowsq_parts;
 };
 
 // One-time set-up of the device error word (allocates 4 bytes). Returns 0 on success.
@@ -575,6 +588,8 @@ int eri_gemm_bf16(const EriGemmArgs* g, void* stream) {
   p.scatter_part_cols = g->scatter_part_cols; p.scatter_group_cols = g->scatter_group_cols;
   p.scatter_local_rows = g->scatter_local_rows > 0 ? g->scatter_local_rows : g->M;
   for (int i = 0; i < kMaxPeers; ++i) p.scatter_out[i] = (bf16*)g->scatter_out[i];
+  p.rowsq = (float*)g->rowsq; p.rowsq_parts = g->rowsq_parts;
+  if (p.rowsq && p.scatter_part_cols <= 0) return -17;
 
   CUtensorMap ta, tb, ta2, tb2;
   {

@@ -44,6 +44,7 @@ class MMDiTConfig:
     axes_dim: tuple = (16, 56, 56)
     theta: float = 10000.0
     time_embed_dim: int = 256
+    txt_rmsnorm: bool = False        # RMSNorm on the text embeddings before txt_in (Qwen-Image)
 
     @property
     def head_dim(self):
@@ -143,7 +144,8 @@ class MMDiT(nn.Module):
         self.img_in = Linear(cfg.in_channels, D, dtype=dtype, device=device)
         self.txt_in = Linear(cfg.context_dim, D, dtype=dtype, device=device)
         self.time_in = MLPEmbedder(cfg.time_embed_dim, D, dtype=dtype, device=device)
-        self.vector_in = MLPEmbedder(cfg.vec_dim, D, dtype=dtype, device=device)
+        self.vector_in = MLPEmbedder(cfg.vec_dim, D, dtype=dtype, device=device) if cfg.vec_dim else None
+        self.txt_norm = RMSNormScale(cfg.context_dim, dtype=dtype, device=device) if cfg.txt_rmsnorm else None
         self.guidance_in = MLPEmbedder(cfg.time_embed_dim, D, dtype=dtype, device=device) \
             if cfg.guidance_embed else None
         self.double_blocks = nn.ModuleList(DoubleStreamBlock(cfg, dtype, device)
@@ -174,12 +176,17 @@ class MMDiT(nn.Module):
         if self.guidance_in is not None:
             g = guidance if guidance is not None else torch.ones_like(t)
             vec = vec + self.guidance_in(timestep_embedding(g, cfg.time_embed_dim).to(dt))
-        vec = vec + self.vector_in(y.to(dt))
+        if self.vector_in is not None:
+            vec = vec + self.vector_in(y.to(dt))
         cos, sin = self.rope(Lt, grid_hw[0], grid_hw[1], img.device)
         img = self.img_in(img)
+        if self.txt_norm is not None:
+            txt = F.norm_modulate(txt, weight=self.txt_norm.scale, rms=True)
         txt = self.txt_in(txt)
         for blk in self.double_blocks:
             img, txt = blk(img, txt, vec, cos, sin)
+        if len(self.single_blocks) == 0:
+            return self.final_layer(img, vec)
         x = torch.cat((txt, img), dim=1)
         for blk in self.single_blocks:
             x = blk(x, vec, cos, sin)
@@ -198,6 +205,27 @@ class MMDiT(nn.Module):
 @register_model("flux")
 def build_flux(dtype=torch.bfloat16, device=None, **overrides):
     cfg = MMDiTConfig(**{**FLUX_DEV.__dict__, **overrides})
+    return MMDiT(cfg, dtype=dtype, device=device)
+
+
+QWEN_IMAGE = MMDiTConfig(in_channels=64, hidden=3072, num_heads=24, depth_double=60, depth_single=0,
+                         context_dim=3584, vec_dim=0, guidance_embed=False, txt_rmsnorm=True)
+
+
+@register_model("qwen_image")
+def build_qwen_image(dtype=torch.bfloat16, device=None, **overrides):
+    """Qwen-Image-architecture MMDiT: 60 dual-stream blocks, hidden 3072, 24 x 128 heads, MLP 12288,
+    text width 3584, 16-channel latents patchified 2x2 (the reference's entry is a placeholder:
+    src/inference/qwen_image.rs:9-21, 85-90; crates/models/qwen_image/src/lib.rs:7-12)."""
+    cfg = MMDiTConfig(**{**QWEN_IMAGE.__dict__, **overrides})
+    return MMDiT(cfg, dtype=dtype, device=device)
+
+
+@register_model("chroma")
+def build_chroma(dtype=torch.bfloat16, device=None, **overrides):
+    """Chroma is FLUX-derived (crates/training/src/chroma/registry.rs:36, 147-221): same blocks,
+    no guidance / pooled-vector embedders."""
+    cfg = MMDiTConfig(**{**FLUX_DEV.__dict__, "guidance_embed": False, "vec_dim": 0, **overrides})
     return MMDiT(cfg, dtype=dtype, device=device)
 
 

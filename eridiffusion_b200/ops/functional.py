@@ -378,6 +378,8 @@ def gemm_native(a, b, *, out=None, alpha=1.0, bias=None, lora_h=None, lora_b=Non
         g.scatter_local_rows = scatter["local_rows"]
         for i, ptr_ in enumerate(scatter["ptrs"]):
             g.scatter_out[i] = ptr_
+        if scatter.get("rowsq") is not None:
+            g.rowsq, g.rowsq_parts = scatter["rowsq"].data_ptr(), scatter["rowsq"].shape[0]
     code = lib.eri_gemm_bf16(g, N.stream_ptr())
     N.check(code, "gemm_bf16")
     return out

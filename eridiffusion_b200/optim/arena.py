@@ -16,7 +16,9 @@ import torch
 
 
 class ParamArena:
-    def __init__(self, params, align: int = 256, shard_multiple: int = 1):
+    def __init__(self, params, align: int = 256, shard_multiple: int = 1, alloc=None):
+        """``alloc(numel, dtype, device) -> 1-D tensor`` lets the caller place the two buffers
+        (e.g. in symmetric peer-mapped memory); default is ``torch.zeros``."""
         params = [p for p in params if p.requires_grad]
         if not params:
             raise ValueError("no trainable parameters")
@@ -32,8 +34,11 @@ class ParamArena:
             off += (p.numel() + align - 1) // align * align
         unit = align * max(1, shard_multiple)
         self.numel = (off + unit - 1) // unit * unit
-        self.data = torch.zeros(self.numel, dtype=dt, device=dev)
-        self.grad = torch.zeros(self.numel, dtype=dt, device=dev)
+        mk = alloc or (lambda n, dtype, device: torch.zeros(n, dtype=dtype, device=device))
+        self.data = mk(self.numel, dt, dev)
+        self.grad = mk(self.numel, dt, dev)
+        self.data.zero_()
+        self.grad.zero_()
         with torch.no_grad():
             for p, o in zip(params, self.offsets):
                 n = p.numel()

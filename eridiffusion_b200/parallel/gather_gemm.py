@@ -25,13 +25,14 @@ from ..ops import _native as N
 
 
 class GatherPlan:
-    def __init__(self, rank: int, world: int, n_copy: int = 16, device=None):
+    def __init__(self, rank: int, world: int, n_copy: int = 16, device=None, n_flags: int | None = None):
         self.rank, self.world, self.n_copy = rank, world, n_copy
         self.device = device or torch.device("cuda", torch.cuda.current_device())
         self.jobs = []
-        self.targets = [0] * world
+        n_flags = n_flags or world
+        self.targets = [0] * n_flags
         self._dev_jobs = None
-        self.flags = torch.zeros(world, dtype=torch.int32, device=self.device)
+        self.flags = torch.zeros(n_flags, dtype=torch.int32, device=self.device)
         self._targets_dev = None
         self.kw = {}
 
@@ -103,4 +104,4 @@ class GatherPlan:
                     flags=self.flags.data_ptr(), flag_target=self._targets_dev.data_ptr(), **self.kw)
 
     def bytes_from_peers(self):
-        return sum(j.rows * j.row_bytes for j in self.jobs if j.flag != self.rank)
+        return sum(j.rows * j.row_bytes for j in self.jobs if (j.flag % self.world) != self.rank)

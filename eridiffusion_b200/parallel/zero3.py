@@ -1,0 +1,297 @@
+"""ZeRO-3 style parameter sharding with the all-gather fused into the consuming GEMM.
+
+Every large ``Linear`` keeps only rows ``[rank*N/W, (rank+1)*N/W)`` of its weight, stored in
+symmetric (peer-mapped) memory. Nothing is gathered ahead of time:
+
+* forward  ``y = x W^T``: one launch of the tcgen05 GEMM whose first CTAs pull the peers' row
+  slabs into a local landing buffer while the compute CTAs start on this rank's own slab and wait
+  per output-column tile on the slab counters (``GatherPlan.rows``);
+* backward ``dX = dY W``: the same landing data is the MN-major B operand, gathered again along
+  the reduction dimension (``along_k=True``), no transposed copy;
+* ``dW``: local GEMM into a symmetric staging buffer, then a pull-based reduce-scatter kernel
+  delivers this rank's averaged slab (no NCCL);
+* conditioning-vector linears (adaLN modulation) are sharded too: every rank applies its row
+  slab to the vectors of all ranks (tiny all-gather in, all-to-all out), so a third of a
+  Qwen-Image block's weights never crosses NVLink at all.
+
+The single-GPU analogue in the reference is weight streaming
+(``WeightProvider::{load_block_to_gpu, prefetch_block, release_block}``,
+crates/training/src/streaming.rs:12-17): materialise -> run -> release per block.
+"""
+from __future__ import annotations
+
+import torch
+import torch.distributed as dist
+import torch.nn as nn
+
+from ..models.layers import Linear, SmallLinear
+from ..ops import functional as F
+from ..ops import reference as R
+from .dist import ProcessGroup, ReduceOp
+from .gather_gemm import GatherPlan
+from .symm import Communicator, SymmetricHeap
+
+
+class Zero3Context:
+    def __init__(self, pg: ProcessGroup | None = None, heap_bytes: int = 1 << 30,
+                 max_weight_elems: int = 64 << 20, n_copy: int = 16, wait_ms: float = 2000.0):
+        self.pg = pg or ProcessGroup()
+        self.rank, self.world = self.pg.rank, self.pg.world_size
+        self.heap = SymmetricHeap(heap_bytes + max_weight_elems * 2 + (1 << 20), group=self.pg.group)
+        self.comm = Communicator(self.heap, wait_ms)
+        dev = torch.device("cuda", torch.cuda.current_device())
+        self.landing = [torch.empty(max_weight_elems, dtype=torch.bfloat16, device=dev) for _ in range(2)]
+        self.stage = self.heap.tensor((max_weight_elems,), torch.bfloat16)
+        self.n_copy = n_copy
+        self._flip = 0
+        self._plans = {}
+        self.gathered_bytes = 0
+
+    # allocator handed to ParamArena so that the shards live in peer-mapped memory
+    def arena_alloc(self, n, dtype, device):
+        return self.heap.tensor((n,), dtype).local
+
+    def peer_ptrs_of(self, t: torch.Tensor):
+        off = t.data_ptr() - self.heap.local_ptr
+        assert 0 <= off < self.heap.nbytes, "tensor is not inside the symmetric heap"
+        return [p + off for p in self.heap.peer_ptrs]
+
+    def next_landing(self, n, k):
+        i = self._flip
+        self._flip ^= 1
+        return self.landing[i][: n * k].view(n, k), i
+
+    def plan(self, shard: torch.Tensor, n, k, along_k: bool):
+        landing, li = self.next_landing(n, k)
+        key = (shard.data_ptr(), n, k, along_k, li)
+        pl = self._plans.get(key)
+        if pl is None:
+            pl = GatherPlan.rows(self.rank, self.world, self.peer_ptrs_of(shard), landing,
+                                 along_k=along_k, n_copy=self.n_copy)
+            self._plans[key] = pl
+        self.gathered_bytes += pl.bytes_from_peers()
+        return pl, landing
+
+    def barrier(self):
+        """Cross-GPU barrier on the current stream (a kernel; no host synchronisation)."""
+        if self.world > 1:
+            self.comm.collective("barrier", self.stage, count=0)
+
+
+class _Zero3LinearFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, shard, bias, z3, n_out, act, residual, gate):
+        shp = x.shape
+        K = shp[-1]
+        x2 = x.contiguous().view(-1, K)
+        M = x2.shape[0]
+        L = shp[-2]
+        pl, landing = z3.plan(shard, n_out, K, along_k=False)
+        pre = torch.empty(M, n_out, dtype=x.dtype, device=x.device) if act is not None else None
+        res2 = None if residual is None else residual.contiguous().view(-1, n_out)
+        gate_v = None
+        if gate is not None:
+            gate_v, _ = F._mod_view(gate, n_out)
+        y = F.gemm_native(x2, landing, bias=bias, act=act, pre_out=pre, residual=res2, gate=gate_v,
+                          rows_per_batch=L, gather=pl.launch_args())
+        ctx.save_for_backward(x2, shard, pre, gate_v)
+        ctx.meta = (shp, n_out, L, act, residual is not None, bias is not None)
+        ctx.z3 = z3
+        return y.view(*shp[:-1], n_out)
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2, shard, pre, gate_v = ctx.saved_tensors
+        shp, n_out, L, act, has_res, has_bias = ctx.meta
+        z3 = ctx.z3
+        M, K = x2.shape
+        dy2 = dy.contiguous().view(M, n_out)
+        d_res = dy.reshape(*shp[:-1], n_out) if has_res else None
+        if gate_v is not None:
+            dy2 = F.gate_residual(None, dy2.view(-1, L, n_out), gate_v).view(M, n_out)
+        if act is not None:
+            g = torch.empty_like(dy2)
+            F.N.check(F.N.require().eri_act_bwd(dy2.data_ptr(), pre.data_ptr(), g.data_ptr(),
+                                                dy2.numel(), 0 if act == "gelu" else 1,
+                                                F.N.stream_ptr()), "act_bwd")
+            dy2 = g
+        dx = None
+        if ctx.needs_input_grad[0]:
+            pl, landing = z3.plan(shard, n_out, K, along_k=True)
+            dx = F.gemm_native(dy2, landing, b_mn=True, gather=pl.launch_args()).view(shp)
+        dshard = None
+        if ctx.needs_input_grad[1]:
+            per = n_out // z3.world
+            stage = z3.stage.local[: n_out * K].view(n_out, K)
+            torch.mm(dy2.t(), x2, out=stage)
+            if z3.world > 1:
+                dshard = torch.empty(per, K, dtype=dy2.dtype, device=dy2.device)
+                z3.comm.collective("reduce_scatter", z3.stage, dst=dshard, count=per * K, avg=True)
+            else:
+                dshard = stage.clone()
+        dbias = dy2.sum(0) if (has_bias and ctx.needs_input_grad[2]) else None
+        return dx, dshard, dbias, None, None, None, d_res, None
+
+
+class Zero3Linear(nn.Module):
+    def __init__(self, lin: Linear, z3: Zero3Context):
+        super().__init__()
+        self.in_features, self.out_features = lin.in_features, lin.out_features
+        per = lin.out_features // z3.world
+        self.weight = nn.Parameter(lin.weight.detach()[z3.rank * per:(z3.rank + 1) * per].clone())
+        self.bias = lin.bias
+        self.z3 = z3
+        self.adapter = None
+
+    def forward(self, x, act=None, residual=None, gate=None):
+        if gate is not None and gate.requires_grad:
+            y = _Zero3LinearFn.apply(x, self.weight, self.bias, self.z3, self.out_features, act, None, None)
+            return F.gate_residual(residual, y, gate)
+        return _Zero3LinearFn.apply(x, self.weight, self.bias, self.z3, self.out_features, act,
+                                    residual, gate)
+
+
+class _Zero3SmallFn(torch.autograd.Function):
+    """Row-sharded linear on conditioning vectors: all ranks' vectors visit every shard."""
+
+    @staticmethod
+    def forward(ctx, x, shard, bias_shard, z3, silu_in):
+        W = z3.world
+        B, K = x.shape
+        xs = torch.empty(W * B, K, dtype=x.dtype, device=x.device)
+        if W > 1:
+            dist.all_gather_into_tensor(xs, x.contiguous(), group=z3.pg.group)
+        else:
+            xs.copy_(x)
+        ys = F.small_linear(xs, shard, bias_shard, silu_in=silu_in) if W * B <= 8 else \
+            torch.nn.functional.linear(torch.nn.functional.silu(xs) if silu_in else xs, shard, bias_shard)
+        per = shard.shape[0]
+        out = torch.empty(W, B, per, dtype=x.dtype, device=x.device)
+        if W > 1:
+            dist.all_to_all_single(out, ys.view(W, B, per).contiguous(), group=z3.pg.group)
+        else:
+            out.copy_(ys.view(W, B, per))
+        ctx.save_for_backward(xs, shard)
+        ctx.meta = (W, B, K, per, silu_in, bias_shard is not None)
+        ctx.z3 = z3
+        return out.permute(1, 0, 2).reshape(B, W * per)
+
+    @staticmethod
+    def backward(ctx, dy):
+        xs, shard = ctx.saved_tensors
+        W, B, K, per, silu_in, has_bias = ctx.meta
+        z3 = ctx.z3
+        dyw = dy.reshape(B, W, per).permute(1, 0, 2).contiguous()
+        dys = torch.empty_like(dyw)
+        if W > 1:
+            dist.all_to_all_single(dys, dyw, group=z3.pg.group)
+        else:
+            dys.copy_(dyw)
+        dys = dys.view(W * B, per)
+        xin = torch.nn.functional.silu(xs.float()).to(xs.dtype) if silu_in else xs
+        dshard = (dys.t() @ xin) / W if ctx.needs_input_grad[1] else None     # already summed over ranks
+        dbias = dys.sum(0) / W if (has_bias and ctx.needs_input_grad[2]) else None
+        dx = None
+        if ctx.needs_input_grad[0]:
+            dxs = dys @ shard
+            if silu_in:
+                xf = xs.float()
+                sg = torch.sigmoid(xf)
+                dxs = (dxs.float() * (sg * (1 + xf * (1 - sg)))).to(xs.dtype)
+            dx = torch.empty(B, K, dtype=dxs.dtype, device=dxs.device)
+            if W > 1:
+                dist.reduce_scatter_tensor(dx, dxs.contiguous(), group=z3.pg.group)
+            else:
+                dx.copy_(dxs)
+        return dx, dshard, dbias, None, None
+
+
+class Zero3SmallLinear(nn.Module):
+    def __init__(self, lin: SmallLinear, z3: Zero3Context):
+        super().__init__()
+        per = lin.out_features // z3.world
+        sl = slice(z3.rank * per, (z3.rank + 1) * per)
+        self.weight = nn.Parameter(lin.weight.detach()[sl].clone())
+        self.bias = nn.Parameter(lin.bias.detach()[sl].clone()) if lin.bias is not None else None
+        self.z3 = z3
+        self.in_features, self.out_features = lin.in_features, lin.out_features
+
+    def forward(self, x, silu_in=False):
+        shp = x.shape
+        y = _Zero3SmallFn.apply(x.reshape(-1, shp[-1]), self.weight, self.bias, self.z3, silu_in)
+        return y.view(*shp[:-1], self.out_features)
+
+
+def shard_model(model: nn.Module, z3: Zero3Context, min_numel: int = 1 << 16):
+    """Replace every large Linear / SmallLinear of ``model`` by its row-sharded version.
+    Returns (sharded parameter list, replicated parameter list), shards first."""
+    W = z3.world
+    for name, mod in list(model.named_modules()):
+        for cname, child in list(mod.named_children()):
+            if isinstance(child, SmallLinear):
+                if child.weight.numel() >= min_numel and child.out_features % W == 0:
+                    setattr(mod, cname, Zero3SmallLinear(child, z3))
+            elif isinstance(child, Linear):
+                if (child.weight.numel() >= min_numel and child.out_features % (W * 64) == 0
+                        and child.in_features % 64 == 0 and child.adapter is None):
+                    setattr(mod, cname, Zero3Linear(child, z3))
+    sharded, replicated = [], []
+    for mod in model.modules():
+        if isinstance(mod, (Zero3Linear, Zero3SmallLinear)):
+            sharded.append(mod.weight)
+            if isinstance(mod, Zero3SmallLinear) and mod.bias is not None:
+                sharded.append(mod.bias)
+    ids = {id(p) for p in sharded}
+    replicated = [p for p in model.parameters() if id(p) not in ids and p.requires_grad]
+    return sharded, replicated
+
+
+class Zero3Sync:
+    """``grad_sync`` object for ``Trainer`` in ZeRO-3 mode: shards are updated locally, replicated
+    parameters (norm scales, biases, small embedders) get an averaged gradient."""
+
+    fused_optimizer = False
+    mode = "zero3"
+
+    def __init__(self, z3: Zero3Context, sharded, replicated):
+        self.z3, self.pg = z3, z3.pg
+        self.rank, self.world_size = z3.rank, z3.world
+        self.sharded, self.replicated = sharded, replicated
+        self.arena = self.optimizer = None
+        self.n_shard = 0
+
+    arena_alloc = property(lambda self: self.z3.arena_alloc)
+
+    def ordered_params(self):
+        return list(self.sharded) + list(self.replicated)
+
+    def optimizer_shard(self):
+        return None
+
+    def attach(self, arena, optimizer):
+        self.arena, self.optimizer = arena, optimizer
+        k = len(self.sharded)
+        self.n_shard = arena.offsets[k] if k < len(arena.offsets) else arena.numel
+        if self.world_size > 1 and self.n_shard < arena.numel:
+            self.pg.broadcast(arena.data[self.n_shard:], 0)
+        self.z3.barrier()
+
+    def reduce_grads(self):
+        if self.world_size > 1 and self.n_shard < self.arena.numel:
+            self.pg.all_reduce(self.arena.grad[self.n_shard:], ReduceOp.AVG)
+        self.z3.barrier()          # every rank has finished gathering for its backward
+
+    def grad_sumsq(self, out=None):
+        g = self.arena.grad
+        ss = F.sumsq(g[: self.n_shard]) if self.n_shard else torch.zeros((), device=g.device)
+        if self.world_size > 1:
+            self.pg.all_reduce(ss, ReduceOp.SUM)
+        if self.n_shard < g.numel():
+            ss = ss + F.sumsq(g[self.n_shard:])
+        if out is not None:
+            out.copy_(ss)
+            return out
+        return ss
+
+    def gather_params(self):
+        self.z3.barrier()          # all shards updated before anyone gathers for the next forward

@@ -79,10 +79,14 @@ class Trainer:
                                 for n, _ in self.adapters[path].named_parameters()]
         else:
             named = [(n, p) for n, p in model.named_parameters() if p.requires_grad]
+            if grad_sync is not None and hasattr(grad_sync, "ordered_params"):
+                order = {id(p): i for i, p in enumerate(grad_sync.ordered_params())}
+                named.sort(key=lambda kv: order.get(id(kv[1]), len(order)))
             params = [p for _, p in named]
             self.param_names = [n for n, _ in named]
         world = grad_sync.world_size if grad_sync is not None else 1
-        self.arena = ParamArena(params, shard_multiple=world)
+        self.arena = ParamArena(params, shard_multiple=world,
+                                alloc=getattr(grad_sync, "arena_alloc", None))
         self.grad_sync = grad_sync
         shard = grad_sync.optimizer_shard() if grad_sync is not None else None
         kw = dict(lr=cfg.lr, weight_decay=cfg.weight_decay, betas=cfg.betas, eps=cfg.eps)
@@ -207,5 +211,10 @@ def default_forward(model, xt, t, batch, cfg):
         g = torch.full((xt.shape[0],), float(gv), device=xt.device)
     if cfg.activation_checkpointing:
         from .act_checkpoint import checkpointed_forward
-        return checkpointed_forward(model, xt, batch["txt"], t, batch["pooled"], g)
-    return model(xt, batch["txt"], t, batch["pooled"], g, grid_hw=batch.get("grid_hw"))
+        return checkpointed_forward(model, xt, batch["txt"], t, batch.get("pooled"), g)
+    return model(xt, batch["txt"], t, batch.get("pooled"), g, grid_hw=batch.get("grid_hw"))
+
+
+def ltx_forward(model, xt, t, batch, cfg):
+    """LTX-style call: model(tokens, text, t, (frames, h, w))."""
+    return model(xt, batch["txt"], t, batch["grid_fhw"])
