@@ -68,8 +68,10 @@ def bench_gemm(small):
         la = torch.randn(16, K, device="cuda").bfloat16()
         t_lora = timeit(lambda: F.gemm_native(a, b, out=out, lora_h=F.gemm_native(a, la, alpha=0.5), lora_b=lb))
         fl_ = 2.0 * M * N * K
+        bt = b.t().contiguous()
+        t_mn = timeit(lambda: F.gemm_native(a, bt, out=out, b_mn=True))
         print(f"{M:6d} {N:6d} {K:6d} | {t_ours*1e6:9.1f} {fl_/t_ours/1e12:7.1f} {fl_/t_ours/fl:6.2f} | "
-              f"{t_lib*1e6:9.1f} {fl_/t_lib/1e12:7.1f} | {t_lora*1e6:9.1f}   ({tag})")
+              f"{t_lib*1e6:9.1f} {fl_/t_lib/1e12:7.1f} | {t_lora*1e6:9.1f} | B[K,N]: {t_mn*1e6:9.1f}   ({tag})")
     assert F.gemm_error_check() == 0
 
 

@@ -1,0 +1,73 @@
+"""Small single-kernel workloads for profiler captures (inputs larger than L2, a few hundred MB on
+the device, a handful of launches), one per hot kernel:
+
+    python -m eridiffusion_b200.cli.profile_target gemm|gemm_lora|attn_fwd|attn_bwd|norm|qknorm|adamw|gemv
+
+Meant to be run as ``ncu --set full --clock-control none -k regex:<kernel> -s 2 -c 1 ... python -m
+eridiffusion_b200.cli.profile_target <what>`` after the same command line exited 0 without ncu.
+"""
+from __future__ import annotations
+
+import sys
+
+import torch
+
+from ..ops import flash_attn as FA
+from ..ops import functional as F
+
+
+def main():
+    what = sys.argv[1] if len(sys.argv) > 1 else "gemm"
+    iters = 4
+    dev = "cuda"
+    r = lambda *s: torch.randn(*s, device=dev).bfloat16()
+    if what in ("gemm", "gemm_lora"):
+        M, N, K = 4096, 9216, 3072
+        a, b = r(M, K), r(N, K)
+        out = torch.empty(M, N, device=dev, dtype=torch.bfloat16)
+        h, lb = r(M, 16), r(N, 16)
+        for _ in range(iters):
+            F.gemm_native(a, b, out=out, lora_h=h if what == "gemm_lora" else None,
+                          lora_b=lb if what == "gemm_lora" else None)
+        assert F.gemm_error_check() == 0
+    elif what in ("attn_fwd", "attn_bwd"):
+        B, L, H, D = 1, 4608, 24, 128
+        q, k, v = r(B, L, H, D), r(B, L, H, D), r(B, L, H, D)
+        for _ in range(iters):
+            o, lse = FA.fwd(q, k, v)
+        if what == "attn_bwd":
+            do = torch.randn_like(o)
+            for _ in range(iters):
+                FA.bwd(do, q, k, v, o, lse)
+        assert FA.check_error() == 0
+    elif what == "norm":
+        x, mod = r(8, 4608, 3072), r(8, 3 * 3072)
+        sh, sc, _ = mod.split(3072, -1)
+        for _ in range(iters):
+            F.norm_modulate(x, sc, sh)
+    elif what == "qknorm":
+        qkv = r(4, 4608, 9216)
+        s = torch.ones(128, device=dev).bfloat16()
+        cos, sin = torch.rand(4608, 64, device=dev), torch.rand(4608, 64, device=dev)
+        for _ in range(iters):
+            F.qknorm_rope_joint([(qkv, s, s)], cos, sin, 24)
+    elif what == "adamw":
+        from ..optim import AdamW8bit
+        p = torch.nn.Parameter(r(112_000_000))
+        opt = AdamW8bit([p])
+        opt.arena.grad.normal_()
+        ss = F.sumsq(opt.arena.grad)
+        for _ in range(iters):
+            opt.step(grad_sumsq=ss, max_grad_norm=1.0)
+    elif what == "gemv":
+        x, w, b = r(1, 3072), r(18432, 3072), r(18432)
+        for _ in range(iters):
+            F.small_linear(x, w, b, silu_in=True)
+    else:
+        raise SystemExit(f"unknown target {what}")
+    torch.cuda.synchronize()
+    print("ok", what)
+
+
+if __name__ == "__main__":
+    main()

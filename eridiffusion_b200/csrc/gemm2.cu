@@ -1,0 +1,466 @@
+// Two-CTA (cta_group::2) variant of the bf16 GEMM: a pair of CTAs on one TPC computes a 256x256
+// output tile with tcgen05.mma M=256. Each CTA stages its own 128 rows of A and ONE HALF of the B
+// tile (128 of the 256 columns), so a K step costs 32 KB of shared-memory fill per SM instead of
+// 48 KB for the single-CTA 128x256 tile — the single-CTA kernel is bound by the latency x
+// bandwidth product of its operand ring (tensor pipe ~52 % active in its profile), and the pair
+// tile cuts the bytes per flop by a third and deepens the ring to six stages.
+//
+// Roles per CTA: warp 0 TMA producer (both CTAs; completion bytes of both land on the leader's
+// `full` barrier), warp 1 UMMA issuer (leader CTA only; tcgen05.commit arrives on the `empty` /
+// `acc_full` barriers of BOTH CTAs with two plain commits), warps 2-5 epilogue for the CTA's own
+// 128 accumulator rows (peer epilogue warps arrive remotely on the leader's `acc_empty`).
+// No multicast of any kind is used: every CTA issues its own loads.
+//
+// Same fused epilogue family and LoRA K step as gemm.cu (bias, GELU/SiLU + saved pre-activation,
+// activation backward, gate + residual, column split, MN-major B); operand gathers and the peer
+// scatter stay in the single-CTA kernel.
+#include "ptx.cuh"
+#include "tma_host.h"
+
+using namespace eri;
+typedef __nv_bfloat16 bf16;
+
+namespace {
+
+struct Gemm2Params {
+  int M, N, K, num_k;
+  int lora_r, act, n_split;
+  int ldc, ldc2, ld_pre, ldr;
+  int rows_per_batch, gate_stride;
+  int b_mn;
+  float alpha;
+  const bf16* bias;
+  const bf16* residual;
+  const bf16* gate;
+  const bf16* pre_in;
+  bf16* out;
+  bf16* out2;
+  bf16* pre_out;
+  int* err;
+};
+
+constexpr int BM = 128;       // rows per CTA (256 per pair)
+constexpr int BN = 256;       // columns per pair tile
+constexpr int BNH = 128;      // B rows staged per CTA
+constexpr int BK = 64;
+constexpr int STAGES = 6;
+constexpr int A_BYTES = BM * BK * 2, B_BYTES = BNH * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
+constexpr int kGroupN = 8;
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t saddr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(saddr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr)
+               : "memory");
+}
+// TMA load whose completion bytes are credited to the barrier at `bar_cluster_addr`
+// (a shared::cluster address, here always the leader CTA's barrier).
+__device__ __forceinline__ void tma_load_2d_pair(void* smem_dst, const void* desc,
+                                                 uint32_t bar_cluster_addr, int32_t x, int32_t y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(desc)), "r"(bar_cluster_addr),
+      "r"(x), "r"(y)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_alloc2(uint32_t* smem_dst, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                   smem_u32(smem_dst)),
+               "r"(ncols)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish2() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc2(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols)
+               : "memory");
+}
+__device__ __forceinline__ void umma2_bf16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b,
+                                           uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}\n"
+      ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// Arrive (once all prior UMMAs of this thread are done) on a barrier given by its shared::cluster
+// address: used for the local CTA's barrier and, with the mapped address, for the peer's.
+__device__ __forceinline__ void umma2_commit_addr(uint32_t bar_cluster_addr) {
+  asm volatile(
+      "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
+          bar_cluster_addr)
+      : "memory");
+}
+
+__device__ __forceinline__ void tile_coords(int t, int num_m, int num_n, int& m_blk, int& n_blk) {
+  const int group_sz = kGroupN * num_m;
+  const int g = t / group_sz;
+  const int first_n = g * kGroupN;
+  const int gw = min(num_n - first_n, kGroupN);
+  const int r = t - g * group_sz;
+  n_blk = first_n + r % gw;
+  m_blk = r / gw;
+}
+__device__ __forceinline__ float apply_act(float v, int act) {
+  return act == 1 ? gelu_tanh_f(v) : act == 2 ? silu_f(v) : v;
+}
+__device__ __forceinline__ float apply_act_grad(float pre, int act) {
+  return act == 3 ? gelu_tanh_grad_f(pre) : silu_grad_f(pre);
+}
+
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(192, 1)
+gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                  const __grid_constant__ CUtensorMap tmA2, const __grid_constant__ CUtensorMap tmB2,
+                  const __grid_constant__ Gemm2Params p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~uintptr_t(1023));
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
+  uint64_t* empty = full + STAGES;
+  uint64_t* acc_full = empty + STAGES;
+  uint64_t* acc_empty = acc_full + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();
+  const bool leader = rank == 0;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full[s], 1);    // leader: one arrive.expect_tx per phase (+ bytes of both CTAs)
+      mbar_init(&empty[s], 1);   // one commit arrival per phase
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&acc_full[b], 1);
+      mbar_init(&acc_empty[b], 8);  // 4 epilogue warps x 2 CTAs (used on the leader only)
+    }
+    mbar_fence_init();
+  }
+  if (warp == 1) {
+    tmem_alloc2(tmem_slot, 512);
+    tmem_relinquish2();
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();            // both CTAs' barriers are initialised before any remote use
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int num_m = (p.M + 2 * BM - 1) / (2 * BM);
+  const int num_n = (p.N + BN - 1) / BN;
+  const int tiles = num_m * num_n;
+  const int k_iters = p.num_k + (p.lora_r > 0 ? 1 : 0);
+  const int cluster_id = blockIdx.x >> 1, num_clusters = gridDim.x >> 1;
+
+  if (warp == 0) {
+    if (elect_one()) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int t = cluster_id; t < tiles && ok; t += num_clusters) {
+        int m_blk, n_blk;
+        tile_coords(t, num_m, num_n, m_blk, n_blk);
+        const int m0 = m_blk * 2 * BM + (int)rank * BM;
+        const int n0 = n_blk * BN + (int)rank * BNH;
+        for (int k = 0; k < k_iters; ++k) {
+          if (!mbar_wait(&empty[stage], phase ^ 1)) {
+            atomicExch(p.err, 41);
+            ok = false;
+            break;
+          }
+          uint8_t* sA = smem + stage * STAGE_BYTES;
+          uint8_t* sB = sA + A_BYTES;
+          const uint32_t bar = map_to_cta(smem_u32(&full[stage]), 0);
+          if (k < p.num_k) {
+            if (leader) mbar_expect_tx(&full[stage], 2 * STAGE_BYTES);
+            tma_load_2d_pair(sA, &tmA, bar, k * BK, m0);
+            if (!p.b_mn) {
+              tma_load_2d_pair(sB, &tmB, bar, k * BK, n0);
+            } else {
+              tma_load_2d_pair(sB, &tmB, bar, n0, k * BK);
+              tma_load_2d_pair(sB + BK * 128, &tmB, bar, n0 + 64, k * BK);
+            }
+          } else {
+            if (leader) mbar_expect_tx(&full[stage], 2 * (BM + BNH) * p.lora_r * 2);
+            tma_load_2d_pair(sA, &tmA2, bar, 0, m0);
+            tma_load_2d_pair(sB, &tmB2, bar, 0, n0);
+          }
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (leader && elect_one()) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      int it = 0;
+      const uint32_t idesc = umma_idesc_bf16(256, BN, 0, p.b_mn);
+      const uint32_t idesc_lora = umma_idesc_bf16(256, BN, 0, 0);
+      for (int t = cluster_id; t < tiles && ok; t += num_clusters, ++it) {
+        const int buf = it & 1;
+        const uint32_t use = (uint32_t)(it >> 1);
+        if (!mbar_wait(&acc_empty[buf], (use & 1) ^ 1)) {
+          atomicExch(p.err, 42);
+          break;
+        }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + buf * BN;
+        for (int k = 0; k < k_iters; ++k) {
+          if (!mbar_wait(&full[stage], phase)) {
+            atomicExch(p.err, 43);
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t sA = smem_u32(smem + stage * STAGE_BYTES);
+          const uint32_t sB = sA + A_BYTES;
+          if (k < p.num_k) {
+            const uint64_t da = umma_desc_kmajor(sA, 128);
+            if (!p.b_mn) {
+              const uint64_t db = umma_desc_kmajor(sB, 128);
+#pragma unroll
+              for (int kk = 0; kk < BK / 16; ++kk)
+                umma2_bf16(d_tmem, da + kk * 2, db + kk * 2, idesc, (k | kk) != 0);
+            } else {
+#pragma unroll
+              for (int kk = 0; kk < BK / 16; ++kk)
+                umma2_bf16(d_tmem, da + kk * 2, umma_desc_mn128(sB + kk * 2048, BK * 128), idesc,
+                           (k | kk) != 0);
+            }
+          } else {
+            const uint32_t sw = p.lora_r * 2;
+            const uint64_t da = umma_desc_kmajor(sA, sw), db = umma_desc_kmajor(sB, sw);
+            for (int kk = 0; kk < p.lora_r / 16; ++kk)
+              umma2_bf16(d_tmem, da + kk * 2, db + kk * 2, idesc_lora, (k | kk) != 0);
+          }
+          const uint32_t e = smem_u32(&empty[stage]);
+          umma2_commit_addr(e);
+          umma2_commit_addr(map_to_cta(e, 1));
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+        if (ok) {
+          const uint32_t a = smem_u32(&acc_full[buf]);
+          umma2_commit_addr(a);
+          umma2_commit_addr(map_to_cta(a, 1));
+        }
+      }
+    }
+  } else {
+    const int q = warp & 3;
+    int it = 0;
+    for (int t = cluster_id; t < tiles; t += num_clusters, ++it) {
+      int m_blk, n_blk;
+      tile_coords(t, num_m, num_n, m_blk, n_blk);
+      const int m0 = m_blk * 2 * BM + (int)rank * BM, n0 = n_blk * BN;
+      const int buf = it & 1;
+      const uint32_t use = (uint32_t)(it >> 1);
+      if (!mbar_wait(&acc_full[buf], use & 1)) {
+        if (lane == 0) atomicExch(p.err, 44);
+        break;
+      }
+      tc_fence_after();
+      const int row = m0 + q * 32 + lane;
+      const bool row_ok = row < p.M;
+      const bool second = p.n_split >= 0 && n0 >= p.n_split;
+      const int act = second || p.n_split < 0 ? p.act : 0;
+      const int coff = second ? p.n_split : 0;
+      bf16* dst = second && p.out2 ? p.out2 + (size_t)row * p.ldc2 : p.out + (size_t)row * p.ldc;
+      const int dcol_off = second && p.out2 ? coff : 0;
+      const bf16* gate = p.gate ? p.gate + (size_t)(row_ok ? row / p.rows_per_batch : 0) * p.gate_stride
+                                : nullptr;
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        const int col0 = n0 + c * 32;
+        if (col0 >= p.N) break;
+        uint32_t r[32];
+        tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + buf * BN + c * 32, r);
+        tmem_ld_wait();
+        if (row_ok) {
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            const int col = col0 + g * 8;
+            if (col < p.N) {
+              float v[8];
+#pragma unroll
+              for (int j = 0; j < 8; ++j) v[j] = __uint_as_float(r[g * 8 + j]) * p.alpha;
+              if (p.bias) {
+                float b[8];
+                unpack8(*reinterpret_cast<const bf16x8*>(p.bias + col), b);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) v[j] += b[j];
+              }
+              if (act == 1 || act == 2) {
+                if (p.pre_out)
+                  *reinterpret_cast<bf16x8*>(p.pre_out + (size_t)row * p.ld_pre + (col - coff)) =
+                      pack8(v);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) v[j] = apply_act(v[j], act);
+              } else if (act == 3 || act == 4) {
+                float pr[8];
+                unpack8(*reinterpret_cast<const bf16x8*>(p.pre_in + (size_t)row * p.ld_pre +
+                                                         (col - coff)),
+                        pr);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) v[j] *= apply_act_grad(pr[j], act);
+              }
+              if (gate) {
+                float gt[8];
+                unpack8(*reinterpret_cast<const bf16x8*>(gate + col), gt);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) v[j] *= gt[j];
+              }
+              if (p.residual) {
+                float rs[8];
+                unpack8(*reinterpret_cast<const bf16x8*>(p.residual + (size_t)row * p.ldr + col),
+                        rs);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) v[j] += rs[j];
+              }
+              *reinterpret_cast<bf16x8*>(dst + (col - dcol_off)) = pack8(v);
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&acc_empty[buf]), 0));
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();   // the peer may still read this CTA's shared memory / signal its barriers
+  if (warp == 1) {
+    __syncwarp();
+    tmem_dealloc2(tmem_base, 512);
+  }
+}
+
+int g2_num_sms = 0;
+int* g2_err = nullptr;
+
+}  // namespace
+
+extern "C" {
+
+struct EriGemmArgs2 {   // same leading layout as EriGemmArgs in gemm.cu (fields used here only)
+  const void* a; const void* b; const void* lora_h; const void* lora_b;
+  const void* bias; const void* residual; const void* gate; const void* pre_in;
+  void* out; void* out2; void* pre_out;
+  long long lda, ldb, ld_h, ld_lb;
+  int M, N, K, lora_r;
+  int act, n_split;
+  int ldc, ldc2, ld_pre, ldr;
+  int rows_per_batch, gate_stride;
+  int force_bn;
+  float alpha;
+  int b_mn;
+  int n_copy, n_jobs;
+  const void* jobs; void* flags; const void* flag_target;
+  int b_flag_rows, a_flag_cols, rot_n_rows, rot_k_cols;
+  int scatter_world;
+};
+
+int eri_gemm2_check_error() {
+  if (!g2_err) return 0;
+  int h = 0;
+  cudaMemcpy(&h, g2_err, sizeof(int), cudaMemcpyDeviceToHost);
+  if (h) cudaMemset(g2_err, 0, sizeof(int));
+  return h;
+}
+
+// Returns -30 when the problem does not fit this kernel (caller falls back to eri_gemm_bf16).
+int eri_gemm2_bf16(const EriGemmArgs2* g, void* stream) {
+  if (g->n_copy || g->scatter_world) return -30;
+  if (g->M < 256 || g->N < 256 || g->K < 64) return -30;
+  if (g->K % 8 || g->N % 8 || g->lda % 8 || g->ldb % 8 || g->ldc % 8) return -30;
+  if (g->lora_r && g->lora_r != 16 && g->lora_r != 32 && g->lora_r != 64) return -30;
+  if (g->n_split > 0 && g->n_split % BN) return -30;
+  if (!g2_err) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&g2_num_sms, cudaDevAttrMultiProcessorCount, dev);
+    if (cudaMalloc(&g2_err, sizeof(int)) != cudaSuccess) return -31;
+    cudaMemset(g2_err, 0, sizeof(int));
+  }
+  Gemm2Params p;
+  memset(&p, 0, sizeof(p));
+  p.M = g->M; p.N = g->N; p.K = g->K; p.num_k = (g->K + BK - 1) / BK;
+  p.lora_r = g->lora_r; p.act = g->act; p.n_split = g->n_split > 0 ? g->n_split : -1;
+  p.ldc = g->ldc; p.ldc2 = g->ldc2; p.ld_pre = g->ld_pre; p.ldr = g->ldr;
+  p.rows_per_batch = g->rows_per_batch > 0 ? g->rows_per_batch : g->M;
+  p.gate_stride = g->gate_stride; p.alpha = g->alpha; p.b_mn = g->b_mn;
+  p.bias = (const bf16*)g->bias; p.residual = (const bf16*)g->residual;
+  p.gate = (const bf16*)g->gate; p.pre_in = (const bf16*)g->pre_in;
+  p.out = (bf16*)g->out; p.out2 = (bf16*)g->out2; p.pre_out = (bf16*)g->pre_out;
+  p.err = g2_err;
+
+  CUtensorMap ta, tb, ta2, tb2;
+  {
+    uint64_t d[2] = {(uint64_t)g->K, (uint64_t)g->M};
+    uint64_t s[1] = {(uint64_t)g->lda * 2};
+    uint32_t bx[2] = {BK, BM};
+    if (make_tensor_map(&ta, g->a, 2, d, s, bx, 128)) return -32;
+  }
+  if (!g->b_mn) {
+    uint64_t d[2] = {(uint64_t)g->K, (uint64_t)g->N};
+    uint64_t s[1] = {(uint64_t)g->ldb * 2};
+    uint32_t bx[2] = {BK, BNH};
+    if (make_tensor_map(&tb, g->b, 2, d, s, bx, 128)) return -33;
+  } else {
+    uint64_t d[2] = {(uint64_t)g->N, (uint64_t)g->K};
+    uint64_t s[1] = {(uint64_t)g->ldb * 2};
+    uint32_t bx[2] = {64, BK};
+    if (make_tensor_map(&tb, g->b, 2, d, s, bx, 128)) return -33;
+  }
+  if (g->lora_r) {
+    uint64_t d[2] = {(uint64_t)g->lora_r, (uint64_t)g->M};
+    uint64_t s[1] = {(uint64_t)g->ld_h * 2};
+    uint32_t bx[2] = {(uint32_t)g->lora_r, BM};
+    if (make_tensor_map(&ta2, g->lora_h, 2, d, s, bx, g->lora_r * 2)) return -34;
+    uint64_t d2[2] = {(uint64_t)g->lora_r, (uint64_t)g->N};
+    uint64_t s2[1] = {(uint64_t)g->ld_lb * 2};
+    uint32_t bx2[2] = {(uint32_t)g->lora_r, BNH};
+    if (make_tensor_map(&tb2, g->lora_b, 2, d2, s2, bx2, g->lora_r * 2)) return -35;
+  } else {
+    ta2 = ta;
+    tb2 = tb;
+  }
+  constexpr int SMEM = STAGES * STAGE_BYTES + 1024 + 256;
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(gemm2_bf16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) !=
+        cudaSuccess)
+      return -36;
+    configured = true;
+  }
+  const int tiles = ((g->M + 2 * BM - 1) / (2 * BM)) * ((g->N + BN - 1) / BN);
+  const int max_clusters = g2_num_sms / 2;
+  const int clusters = tiles < max_clusters ? tiles : max_clusters;
+  gemm2_bf16_kernel<<<clusters * 2, 192, SMEM, (cudaStream_t)stream>>>(ta, tb, ta2, tb2, p);
+  return (int)cudaGetLastError();
+}
+
+}  // extern "C"

@@ -1,3 +1,6 @@
 from .registry import build_model, known_models, register_model  # noqa: F401
 from . import mmdit  # noqa: F401  (registers "flux", "tiny_mmdit")
 from . import ltx_video  # noqa: F401  (registers "ltx_video")
+from . import sdxl_unet  # noqa: F401  (registers "sdxl")
+from . import nextdit  # noqa: F401  (registers "zimage", "wan22")
+from . import sd35_klein  # noqa: F401  (registers "sd35", "klein")

@@ -13,6 +13,10 @@ import torch.nn as nn
 
 from ..ops import functional as F
 
+import os as _os
+
+_KEEP_TRANSPOSE = _os.environ.get("ERI_B200_FROZEN_TRANSPOSE") == "1"
+
 
 class Linear(nn.Module):
     def __init__(self, in_features, out_features, bias=True, dtype=torch.bfloat16, device=None):
@@ -34,8 +38,12 @@ class Linear(nn.Module):
                 self.bias.zero_()
 
     def frozen_transpose(self):
-        """[in, out] copy of a weight that does not require grad (built once, on demand)."""
-        if self.weight.requires_grad or not self.weight.is_cuda:
+        """[in, out] copy of a weight that does not require grad (built once, on demand).
+
+        Off unless ``ERI_B200_FROZEN_TRANSPOSE=1``: the GEMM reads W as an MN-major operand for
+        dX = dY W at the same speed as a K-major transposed copy (measured), so the copy only
+        costs memory."""
+        if not _KEEP_TRANSPOSE or self.weight.requires_grad or not self.weight.is_cuda:
             return None
         if self._wt is None or self._wt.device != self.weight.device:
             self._wt = self.weight.detach().t().contiguous()

@@ -115,7 +115,12 @@ class SingleStreamBlock(nn.Module):
 
     def forward(self, x, vec, cos, sin):
         shift, scale, gate = self.modulation(vec)
-        h = self.linear1(F.norm_modulate(x, scale, shift))            # [B, L, 3D + mlp]
+        from ..ops import fused_blocks as FB
+        xm = F.norm_modulate(x, scale, shift)
+        if FB.single_stream_supported(xm, gate, self.linear1, self.linear2, self.heads):
+            return FB.single_stream(xm, x, gate, self.linear1, self.linear2, self.q_norm.scale,
+                                    self.k_norm.scale, cos, sin, self.heads)
+        h = self.linear1(xm)                                          # [B, L, 3D + mlp]
         qkv, mlp = h[..., : 3 * self.dim], h[..., 3 * self.dim:]
         q, k, v = F.qknorm_rope_joint([(qkv, self.q_norm.scale, self.k_norm.scale)], cos, sin,
                                       self.heads)

@@ -16,6 +16,7 @@ from . import reference as R
 _BACKEND = os.environ.get("ERI_B200_BACKEND", "fused")  # "fused" | "eager"
 _GEMM_NATIVE = os.environ.get("ERI_B200_GEMM", "native")  # "native" | "library"
 _ATTN_NATIVE = os.environ.get("ERI_B200_ATTN", "native")  # "native" | "library"
+_GEMM_PAIR = os.environ.get("ERI_B200_GEMM2", "1") == "1"  # two-CTA tiles for large problems
 
 
 def set_backend(name: str) -> None:
@@ -380,6 +381,11 @@ def gemm_native(a, b, *, out=None, alpha=1.0, bias=None, lora_h=None, lora_b=Non
             g.scatter_out[i] = ptr_
         if scatter.get("rowsq") is not None:
             g.rowsq, g.rowsq_parts = scatter["rowsq"].data_ptr(), scatter["rowsq"].shape[0]
+    if _GEMM_PAIR and gather is None and scatter is None and force_bn in (0, 256) and M >= 256 and Nn >= 256:
+        code = lib.eri_gemm2_bf16(g, N.stream_ptr())       # two-CTA 256x256 tiles
+        if code != -30:
+            N.check(code, "gemm2_bf16")
+            return out
     code = lib.eri_gemm_bf16(g, N.stream_ptr())
     N.check(code, "gemm_bf16")
     return out
@@ -389,9 +395,18 @@ def gemm_supported(M, Nn, K) -> bool:
     return M >= 128 and Nn >= 16 and K >= 8 and K % 8 == 0 and Nn % 8 == 0
 
 
+def set_gemm_pair(on: bool) -> None:
+    global _GEMM_PAIR
+    _GEMM_PAIR = bool(on)
+
+
 def gemm_error_check() -> int:
     """Synchronise and return the device error word of the GEMM kernels (0 = clean)."""
-    return N.require().eri_gemm_check_error()
+    lib = N.require()
+    e = lib.eri_gemm_check_error()
+    if not e and hasattr(lib, "eri_gemm2_check_error"):
+        e = lib.eri_gemm2_check_error()
+    return e
 
 
 def _mm(a, b_nk, **kw):
@@ -510,11 +525,15 @@ class _FusedLinear(torch.autograd.Function):
                 ts = (dy2 @ lora_b) * s
         if need[0]:
             if native:
-                wt_ = wt if wt is not None else w.t().contiguous()
+                # dX = dY W: with a cached transpose W^T is a K-major operand, otherwise W itself
+                # is read as the MN-major operand (no copy).
+                b_op, mn = (wt, False) if wt is not None else (w, True)
+                if mn and K < 64:
+                    b_op, mn = w.t().contiguous(), False
                 if r in (16, 32, 64):
-                    dx = gemm_native(dy2, wt_, lora_h=ts, lora_b=lora_a.t().contiguous())
+                    dx = gemm_native(dy2, b_op, b_mn=mn, lora_h=ts, lora_b=lora_a.t().contiguous())
                 else:
-                    dx = gemm_native(dy2, wt_)
+                    dx = gemm_native(dy2, b_op, b_mn=mn)
                     if r:
                         dx = dx + ts @ lora_a
             else:

@@ -1,0 +1,134 @@
+"""Block-level fusions: the FLUX single-stream block as one autograd node.
+
+The block computes ``x + gate * linear2(cat(attn(qkv), gelu(mlp)))`` where ``qkv`` and ``mlp`` are
+column ranges of one projection ``linear1``. Written with separate ops this needs a split, an
+activation pass and a concatenation in forward and zero-fill / copy / add passes for the slice
+gradients in backward. Here the column-split epilogue of the GEMM writes the qkv columns and
+``gelu(mlp)`` straight to where the next op reads them (the activation output lands inside the
+concatenated buffer), and backward produces the gradient of the wide projection output in place:
+the attention-gradient columns come from the QK-norm/RoPE backward with a row stride, the MLP
+columns from linear2's input-gradient GEMM with the GELU-derivative epilogue.
+
+Reference block: single blocks of src/models/flux_model_complete.rs:830-956 (linear1
+[3D+4D, D], linear2 [D, D+4D], QK-norm, 3-way modulation).
+"""
+from __future__ import annotations
+
+import torch
+
+from . import _native as N
+from . import flash_attn as FA
+from . import functional as F
+
+
+def _t(x):
+    return x.t().contiguous()
+
+
+class _SingleStream(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, xm, x, gate, w1, b1, w2, b2, a1, bb1, s1, a2, bb2, s2, qs, ks, cos, sin, heads):
+        B, L, D = xm.shape
+        M = B * L
+        Fm = w1.shape[0] - 3 * D
+        Dh = D // heads
+        dev, dt = xm.device, xm.dtype
+        lib = N.require()
+        xm2 = xm.contiguous().view(M, D)
+        h1 = F.gemm_native(xm2, a1, alpha=s1) if a1 is not None else None
+        qkv = torch.empty(M, 3 * D, dtype=dt, device=dev)
+        cat = torch.empty(M, D + Fm, dtype=dt, device=dev)
+        pre = torch.empty(M, Fm, dtype=dt, device=dev)
+        F.gemm_native(xm2, w1, bias=b1, lora_h=h1, lora_b=bb1, out=qkv, n_split=3 * D,
+                      out2=cat[:, D:], act="gelu", pre_out=pre)
+        q = torch.empty(B, L, heads, Dh, dtype=dt, device=dev)
+        k, v = torch.empty_like(q), torch.empty_like(q)
+        N.check(lib.eri_qknorm_rope_fwd(qkv.data_ptr(), N.ptr(qs), N.ptr(ks), N.ptr(cos), N.ptr(sin),
+                                        q.data_ptr(), k.data_ptr(), v.data_ptr(), B, L, heads, Dh, L, 0,
+                                        1e-6, 3 * D, D, N.stream_ptr()), "qknorm_rope_fwd")
+        o, lse = FA.fwd(q, k, v)
+        cat[:, :D].copy_(o.view(M, D))
+        h2 = F.gemm_native(cat, a2, alpha=s2) if a2 is not None else None
+        gate_v, _ = F._mod_view(gate, D)
+        y = F.gemm_native(cat, w2, bias=b2, lora_h=h2, lora_b=bb2, residual=x.contiguous().view(M, D),
+                          gate=gate_v, rows_per_batch=L)
+        ctx.save_for_backward(xm2, qkv, pre, cat, q, k, v, o, lse, h1, h2, gate_v, w1, w2, a1, bb1, a2,
+                              bb2, qs, ks, cos, sin)
+        ctx.meta = (B, L, D, Fm, heads, Dh, s1, s2)
+        return y.view(B, L, D)
+
+    @staticmethod
+    def backward(ctx, dy):
+        (xm2, qkv, pre, cat, q, k, v, o, lse, h1, h2, gate_v, w1, w2, a1, bb1, a2, bb2, qs, ks, cos,
+         sin) = ctx.saved_tensors
+        B, L, D, Fm, heads, Dh, s1, s2 = ctx.meta
+        M = B * L
+        dev, dt = dy.device, dy.dtype
+        lib = N.require()
+        need = ctx.needs_input_grad
+        dy2 = dy.contiguous().view(M, D)
+        g = torch.empty_like(dy2)
+        N.check(lib.eri_gate_residual(None, dy2.data_ptr(), gate_v.data_ptr(), g.data_ptr(), M, D, L,
+                                      gate_v.stride(0), N.stream_ptr()), "gate_bwd")
+        ts2 = F.gemm_native(g, _t(bb2), alpha=s2) if a2 is not None else None
+        d_attn = torch.empty(M, D, dtype=dt, device=dev)
+        d_h = torch.empty(M, 3 * D + Fm, dtype=dt, device=dev)
+        F.gemm_native(g, w2, b_mn=True, lora_h=ts2, lora_b=_t(a2) if a2 is not None else None,
+                      out=d_attn, n_split=D, out2=d_h[:, 3 * D:], act="gelu_bwd", pre_in=pre)
+        da2 = (ts2.t() @ cat) if (a2 is not None and need[10]) else None
+        db2 = (g.t() @ h2) if (a2 is not None and need[11]) else None
+        dq, dk, dv = FA.bwd(d_attn.view(B, L, heads, Dh), q, k, v, o, lse)
+        f32 = dict(dtype=torch.float32, device=dev)
+        dqs = torch.zeros(Dh, **f32) if (qs is not None and need[13]) else None
+        dks = torch.zeros(Dh, **f32) if (ks is not None and need[14]) else None
+        N.check(lib.eri_qknorm_rope_bwd(dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), qkv.data_ptr(),
+                                        N.ptr(qs), N.ptr(ks), N.ptr(cos), N.ptr(sin), d_h.data_ptr(),
+                                        N.ptr(dqs), N.ptr(dks), B, L, heads, Dh, L, 0, 1e-6, 3 * D, D,
+                                        3 * D + Fm, N.stream_ptr()), "qknorm_rope_bwd")
+        ts1 = F.gemm_native(d_h, _t(bb1), alpha=s1) if a1 is not None else None
+        dxm = None
+        if need[0]:
+            dxm = F.gemm_native(d_h, w1, b_mn=True, lora_h=ts1,
+                                lora_b=_t(a1) if a1 is not None else None).view(B, L, D)
+        da1 = (ts1.t() @ xm2) if (a1 is not None and need[7]) else None
+        db1 = (d_h.t() @ h1) if (a1 is not None and need[8]) else None
+        dw1 = (d_h.t() @ xm2) if need[3] else None
+        dw2 = (g.t() @ cat) if need[5] else None
+        dgate = None
+        if need[2]:
+            raise NotImplementedError("trainable modulation uses the unfused single-stream path")
+        cv = lambda t: None if t is None else t.to(dt)
+        return (dxm, dy if need[1] else None, dgate, dw1, d_h.sum(0) if need[4] else None, dw2,
+                g.sum(0) if need[6] else None, da1, db1, None, da2, db2, None, cv(dqs), cv(dks), None,
+                None, None)
+
+
+def single_stream_supported(xm, gate, lin1, lin2, heads) -> bool:
+    if not (xm.is_cuda and xm.dtype == torch.bfloat16 and F.get_backend() == "fused"):
+        return False
+    if F._GEMM_NATIVE != "native" or F._ATTN_NATIVE != "native" or not FA.has_backward():
+        return False
+    B, L, D = xm.shape
+    if B * L < 128 or L < 128 or D // heads not in (64, 128) or D % 256 or gate.requires_grad:
+        return False
+    for lin in (lin1, lin2):
+        ad = getattr(lin, "adapter", None)
+        if type(lin).__name__ != "Linear":
+            return False
+        if ad is not None and not (getattr(ad, "kind", "") == "lora" and ad.rank in (16, 32, 64)
+                                   and not (ad.dropout > 0 and ad.training)):
+            return False
+    return True
+
+
+def single_stream(xm, x, gate, lin1, lin2, q_scale, k_scale, cos, sin, heads):
+    """xm: modulated/normalised input [B, L, D]; x: residual stream; gate [B, D]."""
+    def lora(lin):
+        ad = getattr(lin, "adapter", None)
+        return (None, None, 1.0) if ad is None else (ad.lora_A, ad.lora_B, float(ad.scale))
+    a1, bb1, s1 = lora(lin1)
+    a2, bb2, s2 = lora(lin2)
+    cosf = None if cos is None else cos.float().contiguous()
+    sinf = None if sin is None else sin.float().contiguous()
+    return _SingleStream.apply(xm, x, gate, lin1.weight, lin1.bias, lin2.weight, lin2.bias, a1, bb1, s1,
+                               a2, bb2, s2, q_scale, k_scale, cosf, sinf, heads)

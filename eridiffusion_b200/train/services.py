@@ -1,0 +1,339 @@
+"""Training services around the step: callbacks, metrics, telemetry CSV, NaN-safety policy,
+step watchdog, retry helper, graceful interrupt, run driver.
+
+Reference parts: ``Callback`` + ``EarlyStopping`` / ``CSVLogger`` / ``TensorBoardCallback``
+(crates/training/src/callbacks.rs:31-158), ``MetricsTracker`` with moving averages
+(crates/training/src/metrics.rs:12-196), ``MetricsLogger`` JSONL (metrics_logger.rs),
+``TelemetryCsv`` columns and ``EXPECT_STEP_SEC`` (telemetry.rs:15-62), ``NanSafetyCfg`` skip /
+scale back-off / LR back-off (crates/training/src/chroma/train.rs:268-290, 1262-1378), SIGINT ->
+graceful checkpoint (:669-681), ``ErrorRecovery::retry`` with exponential back-off
+(src/trainers/pipeline_progress_tracker.rs:280-315), ``TrainingVerifier`` / ``TrainingHealth``
+(src/training_verifier.rs:40-307), per-step console line (crates/training/src/run.rs:278).
+"""
+from __future__ import annotations
+
+import json
+import math
+import os
+import signal
+import threading
+import time
+from collections import deque
+from dataclasses import dataclass, field
+
+import torch
+
+
+# ------------------------------------------------------------------------- callbacks
+class Callback:
+    def on_train_begin(self, trainer): ...
+    def on_step_end(self, trainer, step, logs): ...
+    def on_checkpoint(self, trainer, path): ...
+    def on_train_end(self, trainer): ...
+    stop_training = False
+
+
+class EarlyStopping(Callback):
+    def __init__(self, monitor="loss", patience=100, min_delta=0.0, mode="min"):
+        self.monitor, self.patience, self.min_delta, self.mode = monitor, patience, min_delta, mode
+        self.best, self.bad = None, 0
+
+    def on_step_end(self, trainer, step, logs):
+        v = logs.get(self.monitor)
+        if v is None or not math.isfinite(v):
+            return
+        better = self.best is None or (v < self.best - self.min_delta if self.mode == "min"
+                                       else v > self.best + self.min_delta)
+        if better:
+            self.best, self.bad = v, 0
+        else:
+            self.bad += 1
+            if self.bad >= self.patience:
+                self.stop_training = True
+
+
+class CSVLogger(Callback):
+    def __init__(self, path, fields=("step", "loss", "grad_norm", "lr", "sec_per_it", "samples_per_s")):
+        self.path, self.fields = path, fields
+        self._wrote_header = os.path.exists(path)
+
+    def on_step_end(self, trainer, step, logs):
+        with open(self.path, "a") as f:
+            if not self._wrote_header:
+                f.write(",".join(self.fields) + "\n")
+                self._wrote_header = True
+            f.write(",".join(str(logs.get(k, "")) for k in self.fields) + "\n")
+
+
+class JSONLLogger(Callback):
+    def __init__(self, path):
+        self.path = path
+
+    def on_step_end(self, trainer, step, logs):
+        with open(self.path, "a") as f:
+            f.write(json.dumps({"step": step, **{k: v for k, v in logs.items() if isinstance(v, (int, float, str))}}) + "\n")
+
+
+class TensorBoardCallback(Callback):
+    """Writes scalars through ``torch.utils.tensorboard`` when it is importable; otherwise keeps
+    the scalars in ``.history`` (the reference's writer is a stub too)."""
+
+    def __init__(self, logdir):
+        self.history = []
+        try:
+            from torch.utils.tensorboard import SummaryWriter
+            self.writer = SummaryWriter(logdir)
+        except Exception:
+            self.writer = None
+
+    def on_step_end(self, trainer, step, logs):
+        for k, v in logs.items():
+            if isinstance(v, (int, float)):
+                if self.writer:
+                    self.writer.add_scalar(k, v, step)
+                else:
+                    self.history.append((step, k, v))
+
+
+# ------------------------------------------------------------------------- metrics
+class MetricsTracker:
+    def __init__(self, window=100):
+        self.window = window
+        self.series: dict[str, deque] = {}
+        self.totals: dict[str, float] = {}
+        self.counts: dict[str, int] = {}
+
+    def update(self, **kv):
+        for k, v in kv.items():
+            if v is None:
+                continue
+            self.series.setdefault(k, deque(maxlen=self.window)).append(float(v))
+            self.totals[k] = self.totals.get(k, 0.0) + float(v)
+            self.counts[k] = self.counts.get(k, 0) + 1
+
+    def moving_average(self, k):
+        s = self.series.get(k)
+        return sum(s) / len(s) if s else float("nan")
+
+    def mean(self, k):
+        return self.totals.get(k, 0.0) / max(1, self.counts.get(k, 0))
+
+    def summary(self):
+        return {k: {"ma": self.moving_average(k), "mean": self.mean(k), "n": self.counts[k]} for k in self.series}
+
+
+TELEMETRY_COLUMNS = ("step", "fw_sec", "bw_sec", "h2d_mb_s", "d2h_mb_s", "gpu_mem_peak", "tokens_per_s",
+                     "grad_norm", "loss", "fused", "samples_per_s_box", "step_ms_device_max")
+
+
+class TelemetryCsv:
+    def __init__(self, path):
+        self.path = path
+        if not os.path.exists(path):
+            with open(path, "w") as f:
+                f.write(",".join(TELEMETRY_COLUMNS) + "\n")
+
+    def row(self, **kv):
+        with open(self.path, "a") as f:
+            f.write(",".join(str(kv.get(c, "")) for c in TELEMETRY_COLUMNS) + "\n")
+
+
+class StepTimeoutError(RuntimeError):
+    pass
+
+
+class StepWatchdog:
+    """Host-side watchdog around each step: ``EXPECT_STEP_SEC`` (or ``limit_s``) bounds the wall
+    time; a step that exceeds it raises ``StepTimeoutError`` at its end, and a background thread
+    calls ``on_stall`` if a step never ends (so a rank waiting on a dead peer is noticed on the
+    host, not by hanging a GPU)."""
+
+    def __init__(self, limit_s=None, on_stall=None, hard_factor=10.0):
+        env = os.environ.get("EXPECT_STEP_SEC")
+        self.limit = limit_s if limit_s is not None else (float(env) if env else None)
+        self.on_stall, self.hard = on_stall, hard_factor
+        self._t0 = None
+        self._stop = threading.Event()
+        self.stalled = False
+        if self.limit and on_stall:
+            threading.Thread(target=self._watch, daemon=True).start()
+
+    def _watch(self):
+        while not self._stop.wait(min(1.0, self.limit)):
+            t0 = self._t0
+            if t0 is not None and time.time() - t0 > self.limit * self.hard:
+                self.stalled = True
+                self.on_stall()
+                self._t0 = None
+
+    def begin(self):
+        self._t0 = time.time()
+
+    def end(self):
+        dt = time.time() - self._t0 if self._t0 else 0.0
+        self._t0 = None
+        if self.limit and dt > self.limit:
+            raise StepTimeoutError(f"step took {dt:.2f}s, expected <= {self.limit}s")
+        return dt
+
+    def close(self):
+        self._stop.set()
+
+
+# ------------------------------------------------------------------------- NaN safety
+@dataclass
+class NanSafetyConfig:
+    max_skips: int = 50
+    lr_backoff: float = 0.5
+    scale_backoff: float = 0.5
+    reset_optimizer_after: int = 0          # consecutive skips before the optimizer state is reset
+    group_grad_norm_budget: float | None = None
+    zero_bad_grads: bool = True
+
+
+class NanGuard:
+    """Decides what to do with a non-finite loss / gradient norm: skip the step (the optimizer
+    kernels already leave parameters and state untouched when the squared norm is not finite),
+    back the learning rate off, count, and give up after ``max_skips``."""
+
+    def __init__(self, cfg: NanSafetyConfig | None = None):
+        self.cfg = cfg or NanSafetyConfig()
+        self.skips = 0
+        self.consecutive = 0
+
+    def check(self, trainer, loss_value: float, grad_norm: float | None = None) -> bool:
+        ok = math.isfinite(loss_value) and (grad_norm is None or math.isfinite(grad_norm))
+        if ok:
+            self.consecutive = 0
+            return True
+        self.skips += 1
+        self.consecutive += 1
+        trainer.nan_skips = self.skips
+        trainer.schedule.backoff(self.cfg.lr_backoff)
+        trainer.scaler.found_inf = True
+        trainer.scaler.update()
+        if self.cfg.zero_bad_grads:
+            trainer.arena.zero_grad()
+        if self.cfg.reset_optimizer_after and self.consecutive >= self.cfg.reset_optimizer_after:
+            opt = trainer.optimizer
+            for name in ("m_q", "v_q", "m_absmax", "v_absmax", "m", "v"):
+                t = getattr(opt, name, None)
+                if torch.is_tensor(t):
+                    t.zero_()
+        if self.skips > self.cfg.max_skips:
+            raise FloatingPointError(f"{self.skips} non-finite steps: giving up")
+        return False
+
+
+def retry(fn, attempts=3, base_delay=0.5, exceptions=(Exception,), sleep=time.sleep):
+    """Exponential back-off retry (3 attempts by default, like ``ErrorRecovery::retry``)."""
+    for i in range(attempts):
+        try:
+            return fn()
+        except exceptions:
+            if i == attempts - 1:
+                raise
+            sleep(base_delay * (2 ** i))
+
+
+class GracefulInterrupt:
+    """SIGINT / SIGTERM set a flag; the loop checkpoints and leaves at the next step boundary."""
+
+    def __init__(self):
+        self.flag = False
+        self._old = {}
+
+    def __enter__(self):
+        for s in (signal.SIGINT, signal.SIGTERM):
+            try:
+                self._old[s] = signal.signal(s, self._handler)
+            except ValueError:      # not the main thread
+                pass
+        return self
+
+    def _handler(self, *_):
+        self.flag = True
+
+    def __exit__(self, *a):
+        for s, h in self._old.items():
+            signal.signal(s, h)
+
+
+# ------------------------------------------------------------------------- verifier
+class TrainingVerifier:
+    """Checks that gradients are non-zero / finite and that parameters move
+    (``GradientInspector`` / ``ParameterTracker``, src/training_verifier.rs:80-307)."""
+
+    def __init__(self, arena):
+        self.arena = arena
+        self._snap = arena.data.detach().float().clone()
+
+    def gradients(self):
+        g = self.arena.grad.float()
+        return {"finite": bool(torch.isfinite(g).all()), "nonzero_frac": float((g != 0).float().mean()),
+                "norm": float(g.norm())}
+
+    def parameters_changed(self):
+        d = (self.arena.data.float() - self._snap).abs().max().item()
+        self._snap.copy_(self.arena.data.float())
+        return d
+
+    def health(self):
+        g = self.gradients()
+        if not g["finite"]:
+            return "diverged"
+        if g["nonzero_frac"] == 0:
+            return "dead_gradients"
+        return "healthy"
+
+
+# ------------------------------------------------------------------------- run driver
+def run_training(trainer, batches, steps, callbacks=(), log_every=10, world=1, batch_size=1, nan_guard=None,
+                 watchdog=None, print_fn=print):
+    """Drive ``trainer`` for ``steps`` optimizer steps over the iterator ``batches``.
+    Prints the reference's per-step line (loss, grad_norm, sec/it, alloc_MB, samples/s) every
+    ``log_every`` steps; reading the loss is the only host synchronisation."""
+    cbs = list(callbacks)
+    guard = nan_guard or NanGuard()
+    for cb in cbs:
+        cb.on_train_begin(trainer)
+    it = iter(batches)
+    t_last = time.time()
+    with GracefulInterrupt() as intr:
+        while trainer.step < steps:
+            if watchdog:
+                watchdog.begin()
+            step_before = trainer.step
+            loss = trainer.train_step(next(it))
+            if watchdog:
+                watchdog.end()
+            if trainer.step == step_before:
+                continue                                   # still accumulating
+            s = trainer.step
+            if s % log_every == 0 or s == steps or cbs:
+                lv = float(loss)
+                gn = trainer.grad_norm()
+                gnv = float(gn) if gn is not None else None
+                now = time.time()
+                sec_it = (now - t_last) / (log_every if s % log_every == 0 else 1)
+                t_last = now
+                guard.check(trainer, lv, gnv)
+                logs = {"step": s, "loss": lv, "grad_norm": gnv, "lr": trainer.optimizer.param_groups[0]["lr"],
+                        "sec_per_it": sec_it, "samples_per_s": batch_size * world / max(sec_it, 1e-9),
+                        "alloc_mb": torch.cuda.memory_allocated() / 2 ** 20 if torch.cuda.is_available() else 0.0,
+                        "nan_skips": guard.skips}
+                if s % log_every == 0 or s == steps:
+                    print_fn(f"step {s}/{steps} loss {lv:.4f} grad_norm {gnv if gnv is None else round(gnv, 4)} "
+                             f"sec/it {sec_it:.3f} alloc_MB {logs['alloc_mb']:.0f} samples/s {logs['samples_per_s']:.2f}")
+                    trainer.log_row(lv, sec_it)
+                for cb in cbs:
+                    cb.on_step_end(trainer, s, logs)
+                if any(cb.stop_training for cb in cbs):
+                    break
+            if intr.flag:
+                if trainer.cfg.out_dir:
+                    trainer.save_checkpoint()
+                break
+    for cb in cbs:
+        cb.on_train_end(trainer)
+    return trainer
