@@ -306,21 +306,33 @@ __device__ __forceinline__ float silu_grad_f(float x) {
   return s * (1.f + x * (1.f - s));
 }
 
+// Eight bf16 values moved as ONE 128-bit access. The payload is a uint4 so that copying the
+// struct through a pointer compiles to a single LDG.128 / STG.128; with four __nv_bfloat162
+// members the compiler emitted four 32-bit accesses (4 useful bytes per 32-byte sector in the
+// row-per-thread GEMM epilogue).
 struct alignas(16) bf16x8 {
-  __nv_bfloat162 v[4];
+  uint4 u;
 };
+__device__ __forceinline__ float2 bf162_bits_to_float2(uint32_t w) {
+  // bf16 -> fp32 is a 16-bit shift
+  return make_float2(__uint_as_float(w << 16), __uint_as_float(w & 0xffff0000u));
+}
 __device__ __forceinline__ void unpack8(const bf16x8& p, float (&f)[8]) {
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    float2 t = __bfloat1622float2(p.v[i]);
-    f[2 * i] = t.x;
-    f[2 * i + 1] = t.y;
-  }
+  const uint4 u = p.u;
+  float2 t;
+  t = bf162_bits_to_float2(u.x); f[0] = t.x; f[1] = t.y;
+  t = bf162_bits_to_float2(u.y); f[2] = t.x; f[3] = t.y;
+  t = bf162_bits_to_float2(u.z); f[4] = t.x; f[5] = t.y;
+  t = bf162_bits_to_float2(u.w); f[6] = t.x; f[7] = t.y;
+}
+__device__ __forceinline__ uint32_t pack_bf162(float a, float b) {
+  __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&h);
 }
 __device__ __forceinline__ bf16x8 pack8(const float (&f)[8]) {
   bf16x8 p;
-#pragma unroll
-  for (int i = 0; i < 4; ++i) p.v[i] = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+  p.u = make_uint4(pack_bf162(f[0], f[1]), pack_bf162(f[2], f[3]), pack_bf162(f[4], f[5]),
+                   pack_bf162(f[6], f[7]));
   return p;
 }
 

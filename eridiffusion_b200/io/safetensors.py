@@ -58,6 +58,7 @@ def save_file(tensors: dict, path, metadata: dict | None = None):
         for t in blobs:
             if t.numel() == 0:
                 continue
+            t = t.reshape(-1)
             raw = t.view(torch.uint8) if t.dtype != torch.bool else t.to(torch.uint8)
             f.write(raw.reshape(-1).numpy().tobytes())
     os.replace(tmp, path)

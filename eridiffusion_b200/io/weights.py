@@ -1,0 +1,62 @@
+"""Weight loading: safetensors checkpoints -> model parameters with strict key accounting, plus
+the key canonicalisation the reference applies to FLUX / SDXL files
+(crates/training/src/flux/registry.rs:102-161 canonical key map + strict audit;
+crates/common/weights/src/strict_loader.rs:21-92; src/loaders/weight_loader.rs)."""
+from __future__ import annotations
+
+import re
+from pathlib import Path
+
+import torch
+
+from . import safetensors as st
+
+_FLUX_RENAMES = [
+    (r"^model\.diffusion_model\.", ""),
+    (r"\.img_mlp\.0\.", ".img_mlp_0."), (r"\.img_mlp\.2\.", ".img_mlp_2."),
+    (r"\.txt_mlp\.0\.", ".txt_mlp_0."), (r"\.txt_mlp\.2\.", ".txt_mlp_2."),
+    (r"\.norm\.query_norm\.scale$", ".q_norm.scale"), (r"\.norm\.key_norm\.scale$", ".k_norm.scale"),
+    (r"^(single_blocks\.\d+)\.norm\.query_norm\.scale$", r"\1.q_norm.scale"),
+    (r"\.adaLN_modulation\.1\.", ".adaLN.lin."),
+]
+
+
+def canonical_key(key: str, kind: str) -> str:
+    if kind in ("flux", "chroma"):
+        for pat, rep in _FLUX_RENAMES:
+            key = re.sub(pat, rep, key)
+    return key
+
+
+def infer_num_blocks(keys, prefix="double_blocks."):
+    """Number of blocks present in a checkpoint (crates/training/src/flux/weights.rs:44-58)."""
+    idx = {int(m.group(1)) for k in keys if (m := re.match(re.escape(prefix) + r"(\d+)\.", k))}
+    return max(idx) + 1 if idx else 0
+
+
+def load_model_weights(model, path, kind="flux", strict=True, device=None):
+    """Copy tensors of a safetensors file (or a directory of shards) into ``model``. With ``strict``
+    every model parameter must be found and every file key used."""
+    path = Path(path)
+    files = sorted(path.glob("*.safetensors")) if path.is_dir() else [path]
+    own = dict(model.named_parameters())
+    used, seen = set(), set()
+    for f in files:
+        with st.SafeFile(f) as sf:
+            st.assert_not_text_encoder(sf.keys())
+            for k in sf.keys():
+                ck = canonical_key(k, kind)
+                seen.add(ck)
+                if ck in own:
+                    p = own[ck]
+                    t = sf.get(k, device=device or p.device, dtype=p.dtype)
+                    if tuple(t.shape) != tuple(p.shape):
+                        raise ValueError(f"{k}: shape {tuple(t.shape)} != parameter {tuple(p.shape)}")
+                    with torch.no_grad():
+                        p.copy_(t)
+                    used.add(ck)
+    if strict:
+        missing, unused = set(own) - used, seen - used
+        if missing or unused:
+            raise KeyError(f"strict weight load: missing={sorted(missing)[:5]} unused={sorted(unused)[:5]}")
+    return used

@@ -79,6 +79,9 @@ class BlockSwapManager:
                     self.stats["bytes_h2d"] += src.numel() * src.element_size()
                 ev = torch.cuda.Event()
                 ev.record(self.copy_stream)
+        else:
+            for n, p in self.blocks[i].named_parameters():
+                p.data = self.host[i][n]
         self.resident[i] = ev
         self.stats["loads"] += 1
 

@@ -1,0 +1,100 @@
+"""From a loaded ``TrainCfg`` to a running job: model, adapters / full fine-tune, parallel engine,
+data source, trainer. This is the dispatch the reference's unified CLI advertises but leaves
+disabled for every family (src/trainers/mod.rs:356-430 returns "temporarily disabled").
+"""
+from __future__ import annotations
+
+import torch
+
+from ..adapters import AdapterConfig
+from ..config import TrainCfg
+from ..data import CachedEmbeddingLoader, synthetic_batch
+from ..models import build_model
+from ..parallel.dist import GradSync, init_from_env
+from .trainer import Trainer, TrainerConfig, default_forward, ltx_forward
+
+_KIND_TO_MODEL = {"flux": "flux", "chroma": "chroma", "qwen_image": "qwen_image", "sdxl": "sdxl",
+                  "sd3": "sd35", "sd35": "sd35", "ltx": "ltx_video", "wan22": "wan22", "klein": "klein",
+                  "zimage": "zimage", "tiny_mmdit": "tiny_mmdit"}
+_UNIMPLEMENTED = {"hunyuan", "lumina", "hidream_i1", "omnigen2"}
+
+
+def build_job(cfg: TrainCfg, device=None):
+    """Returns (trainer, batch_iterator, info)."""
+    if cfg.model.kind in _UNIMPLEMENTED:
+        raise NotImplementedError(
+            f"model kind {cfg.model.kind!r}: the reference registers this family with a forward that "
+            "returns zeros (crates/models/*/src/lib.rs); no architecture is defined to train")
+    rank, world, local = init_from_env()
+    cuda = torch.cuda.is_available() and not cfg.device.startswith("cpu")
+    dev = torch.device(device) if device else (torch.device("cuda", local) if cuda else torch.device("cpu"))
+    dtype = torch.bfloat16 if cuda else torch.float32
+    model_id = _KIND_TO_MODEL[cfg.model.kind]
+    model = build_model(model_id, device=dev, dtype=dtype, **cfg.model.overrides)
+    if cfg.model.name_or_path:
+        from ..io.weights import load_model_weights
+        load_model_weights(model, cfg.model.name_or_path, cfg.model.kind)
+    if cfg.model.quantize and cfg.train_mode == "lora":
+        from ..memory import quantize_model
+        quantize_model(model, "int8")
+
+    par = cfg.parallel
+    grad_sync = None
+    if world > 1:
+        if par.zero_stage == 3:
+            from ..parallel.zero3 import Zero3Context, Zero3Sync, shard_model
+            z3 = Zero3Context()
+            sharded, replicated = shard_model(model, z3)
+            grad_sync = Zero3Sync(z3, sharded, replicated)
+        else:
+            mode = "allreduce" if par.zero_stage == 0 and par.fused_comm != "on" else \
+                ("fused" if par.fused_comm == "on" and cfg.train_mode == "lora" or
+                 (par.fused_comm == "on" and cfg.optimizer.lower().startswith("adamw8")) else "zero1")
+            grad_sync = GradSync(mode)
+
+    objective = {"flowmatch": "flow", "flow": "flow", "ddpm": "eps", "eps": "eps", "v": "v"}.get(
+        cfg.noise_scheduler, "flow" if cfg.model.kind != "sdxl" else "eps")
+    if cfg.model.kind == "sdxl":
+        objective = "eps" if objective == "flow" else objective
+    acfg = None
+    if cfg.train_mode == "lora":
+        n = cfg.network
+        acfg = AdapterConfig(kind=n.type if n.type in ("lora", "loha", "lokr", "dora", "ia3", "glora") else "lora",
+                             rank=n.linear, alpha=n.linear_alpha, dropout=n.dropout, dtype=dtype)
+    tcfg = TrainerConfig(
+        mode=cfg.train_mode, adapter=acfg, objective=objective,
+        timestep_sampler="uniform" if cfg.linear_timesteps else cfg.timestep_sampler,
+        guidance=1.0 if cfg.bypass_guidance_embedding and cfg.guidance is None else (cfg.guidance or 3.5),
+        optimizer=cfg.optimizer, lr=cfg.lr, weight_decay=cfg.weight_decay, lr_schedule=cfg.lr_schedule,
+        warmup_steps=cfg.warmup_steps, total_steps=cfg.steps, grad_accum=cfg.grad_accum_steps,
+        max_grad_norm=cfg.max_grad_norm, ema_decay=cfg.ema_decay, seed=cfg.seed,
+        out_dir=cfg.training_folder, ckpt_every=cfg.ckpt_every, keep_last=cfg.save.max_step_saves_to_keep,
+        activation_checkpointing=cfg.gradient_checkpointing and not cuda, stochastic_rounding=cuda,
+        patch=1 if cfg.model.kind in ("sdxl", "ltx", "wan22") else 2)
+    fwd = default_forward
+    if cfg.model.kind == "ltx":
+        fwd = ltx_forward
+    elif cfg.model.kind == "sdxl":
+        from ..models.sdxl_unet import sdxl_forward
+        fwd = sdxl_forward
+    trainer = Trainer(model, tcfg, grad_sync=grad_sync, forward_fn=fwd)
+
+    ds = cfg.datasets[0] if cfg.datasets else None
+    if ds is not None and ds.manifest and not ds.synthetic:
+        loader = CachedEmbeddingLoader(ds.manifest, kind="sdxl" if cfg.model.kind == "sdxl" else "flux",
+                                       batch_size=cfg.batch_size, root_dir=ds.manifest_root,
+                                       index_path=ds.manifest_index, shuffle=ds.manifest_shuffle,
+                                       repeat=ds.manifest_repeat, seed=cfg.seed, device=dev, rank=rank,
+                                       world=world, validate=ds.manifest_validate)
+        batches = iter(loader)
+    else:
+        res = (ds.resolution[0] if ds and ds.resolution else 1024)
+
+        def gen():
+            i = 0
+            while True:
+                yield synthetic_batch(model_id if model_id != "ltx_video" else "ltx", cfg.batch_size, dev, dtype,
+                                      seed=cfg.seed + i * world + rank, height=res, width=res)
+                i += 1
+        batches = gen()
+    return trainer, batches, {"rank": rank, "world": world, "device": str(dev), "model": model_id}

@@ -27,8 +27,11 @@ def _run(backend, depth_double, depth_single):
         out = m(img, txt, t, y, torch.tensor([3.5], device=dev))
         w = torch.randn(out.shape, device=dev, generator=g).bfloat16()
         (out.float() * w.float()).mean().backward()
-        grads = {n: p.grad.float().clone() for n, a in sorted(ads.items()) for p_n, p in a.named_parameters()
-                 for n in [f"{n}.{p_n}"]}
+        grads = {}
+        for path, a in sorted(ads.items()):
+            for p_n, p in a.named_parameters():
+                if p.grad is not None:
+                    grads[f"{path}.{p_n}"] = p.grad.float().clone()
         return out.float(), grads
     finally:
         F.set_backend("fused")
