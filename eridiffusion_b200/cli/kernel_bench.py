@@ -41,6 +41,9 @@ def timeit(fn, iters=10, warm=3, flush=True):
     for _ in range(iters):
         if flush:
             _flush.zero_()
+        # a device-side delay lets the host enqueue fn's launches before the start event fires, so
+        # host launch overhead (tens of microseconds in Python) is not measured as kernel time
+        torch.cuda._sleep(600_000)
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
         fn()
@@ -84,6 +87,12 @@ def bench_elementwise(small):
     t = timeit(lambda: F.norm_modulate(x, sc, sh))
     nb = 2 * x.numel() * 2
     print(f"norm_modulate fwd [{L}x{D}]: {t*1e6:.1f} us  {nb/t/1e9:.0f} GB/s  {nb/t/bw:.2f} {tag}")
+    xg = x.clone().requires_grad_()
+    yg = F.norm_modulate(xg, sc, sh)
+    go = torch.randn_like(yg)
+    t = timeit(lambda: torch.autograd.grad(yg, xg, go, retain_graph=True))
+    nb = 3 * x.numel() * 2
+    print(f"norm_modulate bwd (dx only) [{L}x{D}]: {t*1e6:.1f} us  {nb/t/1e9:.0f} GB/s  {nb/t/bw:.2f} {tag}")
     F.set_backend("eager")
     t2 = timeit(lambda: R.norm_modulate(x, sc, sh))
     F.set_backend("fused")

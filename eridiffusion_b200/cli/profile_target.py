@@ -43,8 +43,13 @@ def main():
     elif what == "norm":
         x, mod = r(8, 4608, 3072), r(8, 3 * 3072)
         sh, sc, _ = mod.split(3072, -1)
+        x.requires_grad_()
+        g = torch.randn_like(x)
         for _ in range(iters):
-            F.norm_modulate(x, sc, sh)
+            y = F.norm_modulate(x, sc, sh)
+            y.backward(g)
+            x.grad = None
+        assert F.kernel_error_check() == {}
     elif what == "qknorm":
         qkv = r(4, 4608, 9216)
         s = torch.ones(128, device=dev).bfloat16()

@@ -15,6 +15,8 @@
 // The reference reaches attention through an external flame-core SDPA or a chunked online-softmax
 // composition of bmm + elementwise ops (crates/training/src/sdxl/runtime.rs:2814-3025,
 // crates/training/src/flux/runtime.rs:707-745); the softmax recurrence is the same.
+#include <cstdlib>
+
 #include "ptx.cuh"
 #include "tma_host.h"
 
@@ -34,7 +36,7 @@ struct FaParams {
 constexpr int BQ = 128, BKV = 128;
 constexpr float kRescaleThreshold = 8.0f;  // log2 units
 
-template <int DH>
+template <int DH, int POLY>
 __global__ void __launch_bounds__(192, 2)
 fa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
               const __grid_constant__ CUtensorMap tmV, const FaParams p) {
@@ -156,16 +158,32 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
       }
       tc_fence_after();
       const int kv_left = p.Lk - j * BKV;  // valid key columns in this tile
+      const bool full_tile = kv_left >= BKV;
       float mx = -INFINITY;
+      if (full_tile) {
 #pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t r[32];
-        tmem_ld32(lane_addr + S_COL + c * 32, r);
-        tmem_ld_wait();
+        for (int c = 0; c < 2; ++c) {
+          uint32_t r[32], r2[32];
+          tmem_ld32(lane_addr + S_COL + c * 64, r);
+          tmem_ld32(lane_addr + S_COL + c * 64 + 32, r2);
+          tmem_ld_wait();
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          float s = __uint_as_float(r[i]);
-          if (c * 32 + i < kv_left) mx = fmaxf(mx, s);
+          for (int i = 0; i < 32; i += 2) {
+            mx = fmax3(mx, __uint_as_float(r[i]), __uint_as_float(r[i + 1]));
+            mx = fmax3(mx, __uint_as_float(r2[i]), __uint_as_float(r2[i + 1]));
+          }
+        }
+      } else {
+#pragma unroll 1
+        for (int c = 0; c < 4; ++c) {
+          uint32_t r[32];
+          tmem_ld32(lane_addr + S_COL + c * 32, r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            float s = __uint_as_float(r[i]);
+            if (c * 32 + i < kv_left) mx = fmaxf(mx, s);
+          }
         }
       }
       const float m_new = mx * p.scale_log2;
@@ -197,25 +215,55 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
         }
       }
       float lsum = 0.f;
+      if (full_tile) {
+        // Hot path: packed fp32 pairs (one fma / add per two scores), 2^x split between the
+        // special-function unit and a polynomial on the FMA pipe (POLY of every 16 pairs), the
+        // row sum taken from the unrounded fp32 values.
+        const f32x2 sc2 = f2_pack(p.scale_log2, p.scale_log2);
+        const f32x2 nm2 = f2_pack(-m_used, -m_used);
+        f32x2 acc2 = f2_pack(0.f, 0.f);
 #pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t r[32];
-        tmem_ld32(lane_addr + S_COL + c * 32, r);
-        tmem_ld_wait();
-        uint32_t pk[16];
+        for (int c = 0; c < 4; ++c) {
+          uint32_t r[32];
+          tmem_ld32(lane_addr + S_COL + c * 32, r);
+          tmem_ld_wait();
+          uint32_t pk[16];
 #pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          float p0 = exp2f(fmaf(__uint_as_float(r[2 * i]), p.scale_log2, -m_used));
-          float p1 = exp2f(fmaf(__uint_as_float(r[2 * i + 1]), p.scale_log2, -m_used));
-          if (c * 32 + 2 * i >= kv_left) p0 = 0.f;
-          if (c * 32 + 2 * i + 1 >= kv_left) p1 = 0.f;
-          __nv_bfloat162 pb = __floats2bfloat162_rn(p0, p1);
-          // the sum uses the rounded values, matching what the PV product sees
-          float2 pr = __bfloat1622float2(pb);
-          lsum += pr.x + pr.y;
-          pk[i] = *reinterpret_cast<uint32_t*>(&pb);
+          for (int i = 0; i < 16; ++i) {
+            f32x2 v = f2_fma(f2_pack_bits(r[2 * i], r[2 * i + 1]), sc2, nm2);
+            if (i < 16 - POLY) {
+              float lo, hi;
+              f2_unpack(v, lo, hi);
+              v = f2_pack(ex2_mufu(lo), ex2_mufu(hi));
+            } else {
+              v = ex2_poly2(v);
+            }
+            acc2 = f2_add(acc2, v);
+            pk[i] = f2_to_bf162(v);
+          }
+          tmem_st16(lane_addr + S_COL + c * 16, pk);
         }
-        tmem_st16(lane_addr + S_COL + c * 16, pk);
+        float a_lo, a_hi;
+        f2_unpack(acc2, a_lo, a_hi);
+        lsum = a_lo + a_hi;
+      } else {
+#pragma unroll 1
+        for (int c = 0; c < 4; ++c) {
+          uint32_t r[32];
+          tmem_ld32(lane_addr + S_COL + c * 32, r);
+          tmem_ld_wait();
+          uint32_t pk[16];
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            float p0 = exp2f(fmaf(__uint_as_float(r[2 * i]), p.scale_log2, -m_used));
+            float p1 = exp2f(fmaf(__uint_as_float(r[2 * i + 1]), p.scale_log2, -m_used));
+            if (c * 32 + 2 * i >= kv_left) p0 = 0.f;
+            if (c * 32 + 2 * i + 1 >= kv_left) p1 = 0.f;
+            lsum += p0 + p1;
+            pk[i] = pack_bf162(p0, p1);
+          }
+          tmem_st16(lane_addr + S_COL + c * 16, pk);
+        }
       }
       l += lsum;
       tmem_st_wait();
@@ -263,20 +311,32 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
 
 int* g_fa_err = nullptr;
 
-template <int DH>
+template <int DH, int POLY>
 int launch_fwd(const CUtensorMap& q, const CUtensorMap& k, const CUtensorMap& v, const FaParams& p,
                cudaStream_t st) {
   constexpr int SMEM = 3 * 128 * 128 * (DH / 64) + 1024 + 128;
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(fa_fwd_kernel<DH>,
+    cudaError_t e = cudaFuncSetAttribute(fa_fwd_kernel<DH, POLY>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
   dim3 grid((p.Lq + BQ - 1) / BQ, p.H, p.B);
-  fa_fwd_kernel<DH><<<grid, 192, SMEM, st>>>(q, k, v, p);
+  fa_fwd_kernel<DH, POLY><<<grid, 192, SMEM, st>>>(q, k, v, p);
   return (int)cudaGetLastError();
+}
+
+// Pairs (of every 16) whose 2^x runs on the FMA pipe instead of the special-function unit.
+// ERI_B200_FA_POLY = 0, 4 or 8 selects the variant (read once).
+int poly_pairs() {
+  static int v = -1;
+  if (v < 0) {
+    const char* e = getenv("ERI_B200_FA_POLY");
+    v = e ? atoi(e) : 8;
+    if (v != 0 && v != 4 && v != 8) v = 8;
+  }
+  return v;
 }
 
 int make_qkv_map(CUtensorMap* m, const void* ptr, int B, int L, int H, int DH) {
@@ -316,7 +376,15 @@ int eri_flash_attn_fwd(const void* q, const void* k, const void* v, void* out, f
   p.scale_log2 = scale * 1.4426950408889634f;
   p.out = (bf16*)out; p.lse = lse; p.err = g_fa_err;
   cudaStream_t st = (cudaStream_t)stream;
-  return DH == 128 ? launch_fwd<128>(tq, tk, tv, p, st) : launch_fwd<64>(tq, tk, tv, p, st);
+  const int poly = poly_pairs();
+  if (DH == 128) {
+    if (poly == 0) return launch_fwd<128, 0>(tq, tk, tv, p, st);
+    if (poly == 8) return launch_fwd<128, 8>(tq, tk, tv, p, st);
+    return launch_fwd<128, 4>(tq, tk, tv, p, st);
+  }
+  if (poly == 0) return launch_fwd<64, 0>(tq, tk, tv, p, st);
+  if (poly == 8) return launch_fwd<64, 8>(tq, tk, tv, p, st);
+  return launch_fwd<64, 4>(tq, tk, tv, p, st);
 }
 
 }  // extern "C"

@@ -14,6 +14,8 @@
 // fp32 dQ accumulation (atomics or reduce-adds) that a single-pass backward needs.
 // The reference's only attention gradient is a recompute through tensor ops
 // (crates/core/src/autograd_ops.rs:10-75, attention_backward_recompute).
+#include <cstdlib>
+
 #include "ptx.cuh"
 #include "tma_host.h"
 
@@ -68,7 +70,7 @@ __device__ __forceinline__ void named_bar_sync(int id, int nthreads) {
 }
 
 // ------------------------------------------------------------------------------------- dK, dV
-template <int DH>
+template <int DH, int POLY>
 __global__ void __launch_bounds__(192, 1)
 fa_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                    const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmDO,
@@ -91,10 +93,10 @@ fa_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   uint64_t* kv_full = bars + 0;
   uint64_t* qdo_full = bars + 1;   // [2]
   uint64_t* qdo_empty = bars + 3;  // [2]
-  uint64_t* sp_full = bars + 5;
-  uint64_t* pds_ready = bars + 6;
-  uint64_t* acc_done = bars + 7;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 8);
+  uint64_t* sp_full = bars + 5;    // [2] one per 64-query half
+  uint64_t* pds_ready = bars + 7;  // [2]
+  uint64_t* acc_done = bars + 9;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 10);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int k0 = blockIdx.x * T, h = blockIdx.y, b = blockIdx.z;
@@ -106,8 +108,10 @@ fa_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       mbar_init(&qdo_full[s], 1);
       mbar_init(&qdo_empty[s], 1);
     }
-    mbar_init(sp_full, 1);
-    mbar_init(pds_ready, 4);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&sp_full[s], 1);
+      mbar_init(&pds_ready[s], 4);
+    }
     mbar_init(acc_done, 1);
     mbar_fence_init();
   }
@@ -144,23 +148,22 @@ fa_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     }
   } else if (warp == 1) {
     if (elect_one()) {
-      const uint32_t idesc_s = umma_idesc_bf16(T, T, 0, 0);
+      // Software pipeline over 64-query halves: while the softmax warps turn one half of
+      // S^T / dP^T into P^T / dS^T, the tensor pipe runs the other half's products, and the
+      // next tile's first half is issued before this tile's second half is consumed.
+      const uint32_t idesc_s = umma_idesc_bf16(T, 64, 0, 0);
       const uint32_t idesc_g = umma_idesc_bf16(T, DH, 0, 1);
       const uint32_t aK = smem_u32(sK), aV = smem_u32(sV);
-      bool ok = mbar_wait(kv_full, 0);
-      if (!ok) atomicExch(p.err, 22);
-      for (int i = 0; i < nq && ok; ++i) {
-        const int s = i & 1;
-        if (!mbar_wait(&qdo_full[s], (uint32_t)((i >> 1) & 1))) { atomicExch(p.err, 23); break; }
-        tc_fence_after();
-        const uint32_t aQ = smem_u32(sQ + s * TILE_BYTES), aDO = smem_u32(sDO + s * TILE_BYTES);
+      const uint32_t aQ0 = smem_u32(sQ), aDO0 = smem_u32(sDO);
+      auto issue_sdp = [&](int st, int hf) {  // S^T and dP^T for queries [64 hf, 64 hf + 64)
+        const uint32_t aQ = aQ0 + st * TILE_BYTES + hf * 8192, aDO = aDO0 + st * TILE_BYTES + hf * 8192;
 #pragma unroll
         for (int c = 0; c < CHUNKS; ++c) {
           const uint64_t da = umma_desc_kmajor(aK + c * CHUNK_BYTES, 128);
           const uint64_t db = umma_desc_kmajor(aQ + c * CHUNK_BYTES, 128);
 #pragma unroll
           for (int kk = 0; kk < 4; ++kk)
-            umma_bf16(tmem_base + S_COL, da + kk * 2, db + kk * 2, idesc_s, (c | kk) != 0);
+            umma_bf16(tmem_base + S_COL + hf * 64, da + kk * 2, db + kk * 2, idesc_s, (c | kk) != 0);
         }
 #pragma unroll
         for (int c = 0; c < CHUNKS; ++c) {
@@ -168,22 +171,54 @@ fa_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
           const uint64_t db = umma_desc_kmajor(aDO + c * CHUNK_BYTES, 128);
 #pragma unroll
           for (int kk = 0; kk < 4; ++kk)
-            umma_bf16(tmem_base + DP_COL, da + kk * 2, db + kk * 2, idesc_s, (c | kk) != 0);
+            umma_bf16(tmem_base + DP_COL + hf * 64, da + kk * 2, db + kk * 2, idesc_s, (c | kk) != 0);
         }
-        umma_commit(sp_full);
-        if (!mbar_wait(pds_ready, (uint32_t)(i & 1))) { atomicExch(p.err, 24); break; }
+        umma_commit(&sp_full[hf]);
+      };
+      auto issue_dvdk = [&](int st, int hf, bool first) {
+        const uint32_t aQ = aQ0 + st * TILE_BYTES, aDO = aDO0 + st * TILE_BYTES;
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk) {
+          const uint64_t dbo = umma_desc_mn128(aDO + (hf * 4 + kk) * 2048, CHUNK_BYTES);
+          umma_bf16_ts(tmem_base + DV_COL, tmem_base + S_COL + hf * 64 + kk * 8, dbo, idesc_g,
+                       !first || kk != 0);
+        }
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk) {
+          const uint64_t dbq = umma_desc_mn128(aQ + (hf * 4 + kk) * 2048, CHUNK_BYTES);
+          umma_bf16_ts(tmem_base + DK_COL, tmem_base + DP_COL + hf * 64 + kk * 8, dbq, idesc_g,
+                       !first || kk != 0);
+        }
+      };
+      bool ok = mbar_wait(kv_full, 0);
+      if (!ok) atomicExch(p.err, 22);
+      if (ok && !mbar_wait(&qdo_full[0], 0)) { atomicExch(p.err, 23); ok = false; }
+      if (ok) {
         tc_fence_after();
-#pragma unroll
-        for (int kk = 0; kk < T / 16; ++kk) {
-          const uint64_t dbo = umma_desc_mn128(aDO + kk * 2048, CHUNK_BYTES);
-          umma_bf16_ts(tmem_base + DV_COL, tmem_base + S_COL + kk * 8, dbo, idesc_g, (i | kk) != 0);
+        issue_sdp(0, 0);
+        issue_sdp(0, 1);
+      }
+      for (int i = 0; i < nq && ok; ++i) {
+        const int s = i & 1;
+        const uint32_t par = (uint32_t)(i & 1);
+        const bool more = i + 1 < nq;
+        if (!mbar_wait(&pds_ready[0], par)) { atomicExch(p.err, 24); ok = false; break; }
+        tc_fence_after();
+        issue_dvdk(s, 0, i == 0);
+        if (more) {
+          if (!mbar_wait(&qdo_full[s ^ 1], (uint32_t)(((i + 1) >> 1) & 1))) {
+            atomicExch(p.err, 23);
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          issue_sdp(s ^ 1, 0);
         }
-#pragma unroll
-        for (int kk = 0; kk < T / 16; ++kk) {
-          const uint64_t dbq = umma_desc_mn128(aQ + kk * 2048, CHUNK_BYTES);
-          umma_bf16_ts(tmem_base + DK_COL, tmem_base + DP_COL + kk * 8, dbq, idesc_g, (i | kk) != 0);
-        }
+        if (!mbar_wait(&pds_ready[1], par)) { atomicExch(p.err, 27); ok = false; break; }
+        tc_fence_after();
+        issue_dvdk(s, 1, false);
         umma_commit(&qdo_empty[s]);
+        if (more) issue_sdp(s ^ 1, 1);
       }
       if (ok) umma_commit(acc_done);
     }
@@ -195,43 +230,61 @@ fa_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     bool ok = true;
     for (int i = 0; i < nq; ++i) {
       const int s = i & 1;
-      s_lse[s * T + tid] = p.lse2[stat_base + i * T + tid];
+      s_lse[s * T + tid] = -p.lse2[stat_base + i * T + tid];
       s_delta[s * T + tid] = p.delta[stat_base + i * T + tid];
       named_bar_sync(1, 128);
-      if (!mbar_wait(sp_full, (uint32_t)(i & 1))) {
-        if (lane == 0) atomicExch(p.err, 25);
-        ok = false;
-        break;
-      }
-      tc_fence_after();
-      const float* ls = s_lse + s * T;
-      const float* dl = s_delta + s * T;
+      // s_lse holds -lse2 so that one packed fma gives s * c - lse2 for two queries
+      const float4* ls4 = reinterpret_cast<const float4*>(s_lse + s * T);
+      const float4* dl4 = reinterpret_cast<const float4*>(s_delta + s * T);
+      const f32x2 sc2 = f2_pack(p.scale_log2, p.scale_log2);
 #pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t r[32], g[32];
-        tmem_ld32(lane_addr + S_COL + c * 32, r);
-        tmem_ld32(lane_addr + DP_COL + c * 32, g);
-        tmem_ld_wait();
-        uint32_t pk[16], dk_[16];
-#pragma unroll
-        for (int x = 0; x < 16; ++x) {
-          const int q = c * 32 + 2 * x;
-          float p0 = exp2f(fmaf(__uint_as_float(r[2 * x]), p.scale_log2, -ls[q]));
-          float p1 = exp2f(fmaf(__uint_as_float(r[2 * x + 1]), p.scale_log2, -ls[q + 1]));
-          float d0 = p0 * (__uint_as_float(g[2 * x]) - dl[q]);
-          float d1 = p1 * (__uint_as_float(g[2 * x + 1]) - dl[q + 1]);
-          __nv_bfloat162 pb = __floats2bfloat162_rn(p0, p1);
-          __nv_bfloat162 db = __floats2bfloat162_rn(d0, d1);
-          pk[x] = *reinterpret_cast<uint32_t*>(&pb);
-          dk_[x] = *reinterpret_cast<uint32_t*>(&db);
+      for (int hf = 0; hf < 2 && ok; ++hf) {
+        if (!mbar_wait(&sp_full[hf], (uint32_t)(i & 1))) {
+          if (lane == 0) atomicExch(p.err, 25);
+          ok = false;
+          break;
         }
-        tmem_st16(lane_addr + S_COL + c * 16, pk);
-        tmem_st16(lane_addr + DP_COL + c * 16, dk_);
+        tc_fence_after();
+#pragma unroll 1
+        for (int cc = 0; cc < 2; ++cc) {
+          const int c = hf * 2 + cc;  // 32-query chunk
+          uint32_t r[32], g[32];
+          tmem_ld32(lane_addr + S_COL + c * 32, r);
+          tmem_ld32(lane_addr + DP_COL + c * 32, g);
+          tmem_ld_wait();
+          uint32_t pk[16], dk_[16];
+#pragma unroll
+          for (int x4 = 0; x4 < 8; ++x4) {
+            const float4 nl = ls4[c * 8 + x4];
+            const float4 dl = dl4[c * 8 + x4];
+#pragma unroll
+            for (int hh = 0; hh < 2; ++hh) {
+              const int x = 2 * x4 + hh;
+              const f32x2 nl2 = hh ? f2_pack(nl.z, nl.w) : f2_pack(nl.x, nl.y);
+              const f32x2 dl2 = hh ? f2_pack(dl.z, dl.w) : f2_pack(dl.x, dl.y);
+              f32x2 v = f2_fma(f2_pack_bits(r[2 * x], r[2 * x + 1]), sc2, nl2);
+              if (x < 16 - POLY) {
+                float lo, hi;
+                f2_unpack(v, lo, hi);
+                v = f2_pack(ex2_mufu(lo), ex2_mufu(hi));
+              } else {
+                v = ex2_poly2(v);
+              }
+              const f32x2 d = f2_mul(v, f2_sub(f2_pack_bits(g[2 * x], g[2 * x + 1]), dl2));
+              pk[x] = f2_to_bf162(v);
+              dk_[x] = f2_to_bf162(d);
+            }
+          }
+          // packed bf16 P^T / dS^T of this half start at the half's own first column
+          tmem_st16(lane_addr + S_COL + hf * 64 + cc * 16, pk);
+          tmem_st16(lane_addr + DP_COL + hf * 64 + cc * 16, dk_);
+        }
+        tmem_st_wait();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&pds_ready[hf]);
       }
-      tmem_st_wait();
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(pds_ready);
+      if (!ok) break;
     }
     if (ok && !mbar_wait(acc_done, 0)) {
       if (lane == 0) atomicExch(p.err, 26);
@@ -273,7 +326,7 @@ fa_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
 }
 
 // ------------------------------------------------------------------------------------- dQ
-template <int DH>
+template <int DH, int POLY>
 __global__ void __launch_bounds__(192, 1)
 fa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                  const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmDO,
@@ -294,10 +347,10 @@ fa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   uint64_t* qdo_full = bars + 0;
   uint64_t* kv_full = bars + 1;   // [2]
   uint64_t* kv_empty = bars + 3;  // [2]
-  uint64_t* sp_full = bars + 5;
-  uint64_t* ds_ready = bars + 6;
-  uint64_t* acc_done = bars + 7;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 8);
+  uint64_t* sp_full = bars + 5;   // [2] one per 64-key half
+  uint64_t* ds_ready = bars + 7;  // [2]
+  uint64_t* acc_done = bars + 9;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 10);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int q0 = blockIdx.x * T, h = blockIdx.y, b = blockIdx.z;
@@ -309,8 +362,10 @@ fa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       mbar_init(&kv_full[s], 1);
       mbar_init(&kv_empty[s], 1);
     }
-    mbar_init(sp_full, 1);
-    mbar_init(ds_ready, 4);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&sp_full[s], 1);
+      mbar_init(&ds_ready[s], 4);
+    }
     mbar_init(acc_done, 1);
     mbar_fence_init();
   }
@@ -346,23 +401,20 @@ fa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     }
   } else if (warp == 1) {
     if (elect_one()) {
-      const uint32_t idesc_s = umma_idesc_bf16(T, T, 0, 0);
+      // Same half-tile software pipeline as the dK/dV kernel, split over 64-key halves.
+      const uint32_t idesc_s = umma_idesc_bf16(T, 64, 0, 0);
       const uint32_t idesc_g = umma_idesc_bf16(T, DH, 0, 1);
       const uint32_t aQ = smem_u32(sQ), aDO = smem_u32(sDO);
-      bool ok = mbar_wait(qdo_full, 0);
-      if (!ok) atomicExch(p.err, 32);
-      for (int j = 0; j < nkv && ok; ++j) {
-        const int s = j & 1;
-        if (!mbar_wait(&kv_full[s], (uint32_t)((j >> 1) & 1))) { atomicExch(p.err, 33); break; }
-        tc_fence_after();
-        const uint32_t aK = smem_u32(sK + s * TILE_BYTES), aV = smem_u32(sV + s * TILE_BYTES);
+      const uint32_t aK0 = smem_u32(sK), aV0 = smem_u32(sV);
+      auto issue_sdp = [&](int st, int hf) {  // S and dP for keys [64 hf, 64 hf + 64)
+        const uint32_t aK = aK0 + st * TILE_BYTES + hf * 8192, aV = aV0 + st * TILE_BYTES + hf * 8192;
 #pragma unroll
         for (int c = 0; c < CHUNKS; ++c) {
           const uint64_t da = umma_desc_kmajor(aQ + c * CHUNK_BYTES, 128);
           const uint64_t db = umma_desc_kmajor(aK + c * CHUNK_BYTES, 128);
 #pragma unroll
           for (int kk = 0; kk < 4; ++kk)
-            umma_bf16(tmem_base + S_COL, da + kk * 2, db + kk * 2, idesc_s, (c | kk) != 0);
+            umma_bf16(tmem_base + S_COL + hf * 64, da + kk * 2, db + kk * 2, idesc_s, (c | kk) != 0);
         }
 #pragma unroll
         for (int c = 0; c < CHUNKS; ++c) {
@@ -370,17 +422,48 @@ fa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           const uint64_t db = umma_desc_kmajor(aV + c * CHUNK_BYTES, 128);
 #pragma unroll
           for (int kk = 0; kk < 4; ++kk)
-            umma_bf16(tmem_base + DP_COL, da + kk * 2, db + kk * 2, idesc_s, (c | kk) != 0);
+            umma_bf16(tmem_base + DP_COL + hf * 64, da + kk * 2, db + kk * 2, idesc_s, (c | kk) != 0);
         }
-        umma_commit(sp_full);
-        if (!mbar_wait(ds_ready, (uint32_t)(j & 1))) { atomicExch(p.err, 34); break; }
-        tc_fence_after();
+        umma_commit(&sp_full[hf]);
+      };
+      auto issue_dq = [&](int st, int hf, bool first) {
+        const uint32_t aK = aK0 + st * TILE_BYTES;
 #pragma unroll
-        for (int kk = 0; kk < T / 16; ++kk) {
-          const uint64_t dbk = umma_desc_mn128(aK + kk * 2048, CHUNK_BYTES);
-          umma_bf16_ts(tmem_base + DQ_COL, tmem_base + DP_COL + kk * 8, dbk, idesc_g, (j | kk) != 0);
+        for (int kk = 0; kk < 4; ++kk) {
+          const uint64_t dbk = umma_desc_mn128(aK + (hf * 4 + kk) * 2048, CHUNK_BYTES);
+          umma_bf16_ts(tmem_base + DQ_COL, tmem_base + DP_COL + hf * 64 + kk * 8, dbk, idesc_g,
+                       !first || kk != 0);
         }
+      };
+      bool ok = mbar_wait(qdo_full, 0);
+      if (!ok) atomicExch(p.err, 32);
+      if (ok && !mbar_wait(&kv_full[0], 0)) { atomicExch(p.err, 33); ok = false; }
+      if (ok) {
+        tc_fence_after();
+        issue_sdp(0, 0);
+        issue_sdp(0, 1);
+      }
+      for (int j = 0; j < nkv && ok; ++j) {
+        const int s = j & 1;
+        const uint32_t par = (uint32_t)(j & 1);
+        const bool more = j + 1 < nkv;
+        if (!mbar_wait(&ds_ready[0], par)) { atomicExch(p.err, 34); ok = false; break; }
+        tc_fence_after();
+        issue_dq(s, 0, j == 0);
+        if (more) {
+          if (!mbar_wait(&kv_full[s ^ 1], (uint32_t)(((j + 1) >> 1) & 1))) {
+            atomicExch(p.err, 33);
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          issue_sdp(s ^ 1, 0);
+        }
+        if (!mbar_wait(&ds_ready[1], par)) { atomicExch(p.err, 37); ok = false; break; }
+        tc_fence_after();
+        issue_dq(s, 1, false);
         umma_commit(&kv_empty[s]);
+        if (more) issue_sdp(s ^ 1, 1);
       }
       if (ok) umma_commit(acc_done);
     }
@@ -391,38 +474,69 @@ fa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     const size_t stat = ((size_t)b * p.H + h) * p.Lp + row;  // row < Lp always
     const float lse2 = p.lse2[stat], delta = p.delta[stat];
     bool ok = true;
-    for (int j = 0; j < nkv; ++j) {
-      if (!mbar_wait(sp_full, (uint32_t)(j & 1))) {
-        if (lane == 0) atomicExch(p.err, 35);
-        ok = false;
-        break;
-      }
-      tc_fence_after();
+    const f32x2 sc2 = f2_pack(p.scale_log2, p.scale_log2);
+    const f32x2 nl2 = f2_pack(-lse2, -lse2);
+    const f32x2 dl2 = f2_pack(delta, delta);
+    for (int j = 0; j < nkv && ok; ++j) {
       const int kv_left = p.Lk - j * T;
 #pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t r[32], g[32];
-        tmem_ld32(lane_addr + S_COL + c * 32, r);
-        tmem_ld32(lane_addr + DP_COL + c * 32, g);
-        tmem_ld_wait();
-        uint32_t dk_[16];
-#pragma unroll
-        for (int x = 0; x < 16; ++x) {
-          float p0 = exp2f(fmaf(__uint_as_float(r[2 * x]), p.scale_log2, -lse2));
-          float p1 = exp2f(fmaf(__uint_as_float(r[2 * x + 1]), p.scale_log2, -lse2));
-          if (c * 32 + 2 * x >= kv_left) p0 = 0.f;
-          if (c * 32 + 2 * x + 1 >= kv_left) p1 = 0.f;
-          float d0 = p0 * (__uint_as_float(g[2 * x]) - delta);
-          float d1 = p1 * (__uint_as_float(g[2 * x + 1]) - delta);
-          __nv_bfloat162 db = __floats2bfloat162_rn(d0, d1);
-          dk_[x] = *reinterpret_cast<uint32_t*>(&db);
+      for (int hf = 0; hf < 2; ++hf) {
+        if (!mbar_wait(&sp_full[hf], (uint32_t)(j & 1))) {
+          if (lane == 0) atomicExch(p.err, 35);
+          ok = false;
+          break;
         }
-        tmem_st16(lane_addr + DP_COL + c * 16, dk_);
+        tc_fence_after();
+        if (kv_left >= T) {
+#pragma unroll 1
+          for (int cc = 0; cc < 2; ++cc) {
+            const int c = hf * 2 + cc;
+            uint32_t r[32], g[32];
+            tmem_ld32(lane_addr + S_COL + c * 32, r);
+            tmem_ld32(lane_addr + DP_COL + c * 32, g);
+            tmem_ld_wait();
+            uint32_t dk_[16];
+#pragma unroll
+            for (int x = 0; x < 16; ++x) {
+              f32x2 v = f2_fma(f2_pack_bits(r[2 * x], r[2 * x + 1]), sc2, nl2);
+              if (x < 16 - POLY) {
+                float lo, hi;
+                f2_unpack(v, lo, hi);
+                v = f2_pack(ex2_mufu(lo), ex2_mufu(hi));
+              } else {
+                v = ex2_poly2(v);
+              }
+              dk_[x] = f2_to_bf162(f2_mul(v, f2_sub(f2_pack_bits(g[2 * x], g[2 * x + 1]), dl2)));
+            }
+            tmem_st16(lane_addr + DP_COL + hf * 64 + cc * 16, dk_);
+          }
+        } else {
+#pragma unroll 1
+          for (int cc = 0; cc < 2; ++cc) {
+            const int c = hf * 2 + cc;
+            uint32_t r[32], g[32];
+            tmem_ld32(lane_addr + S_COL + c * 32, r);
+            tmem_ld32(lane_addr + DP_COL + c * 32, g);
+            tmem_ld_wait();
+            uint32_t dk_[16];
+#pragma unroll
+            for (int x = 0; x < 16; ++x) {
+              float p0 = exp2f(fmaf(__uint_as_float(r[2 * x]), p.scale_log2, -lse2));
+              float p1 = exp2f(fmaf(__uint_as_float(r[2 * x + 1]), p.scale_log2, -lse2));
+              if (c * 32 + 2 * x >= kv_left) p0 = 0.f;
+              if (c * 32 + 2 * x + 1 >= kv_left) p1 = 0.f;
+              float d0 = p0 * (__uint_as_float(g[2 * x]) - delta);
+              float d1 = p1 * (__uint_as_float(g[2 * x + 1]) - delta);
+              dk_[x] = pack_bf162(d0, d1);
+            }
+            tmem_st16(lane_addr + DP_COL + hf * 64 + cc * 16, dk_);
+          }
+        }
+        tmem_st_wait();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&ds_ready[hf]);
       }
-      tmem_st_wait();
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(ds_ready);
     }
     if (ok && !mbar_wait(acc_done, 0)) {
       if (lane == 0) atomicExch(p.err, 36);
@@ -466,24 +580,45 @@ int make_map(CUtensorMap* m, const void* ptr, int B, int L, int H, int DH) {
   return make_tensor_map(m, ptr, 3, dims, strides, box, 128);
 }
 
-template <int DH>
-int launch_bwd(const CUtensorMap& q, const CUtensorMap& k, const CUtensorMap& v,
-               const CUtensorMap& d, const FaBwdParams& p, cudaStream_t st) {
+template <int DH, int POLY>
+int launch_bwd_v(const CUtensorMap& q, const CUtensorMap& k, const CUtensorMap& v,
+                 const CUtensorMap& d, const FaBwdParams& p, cudaStream_t st) {
   constexpr int SMEM = 6 * 128 * 128 * (DH / 64) + 2048 + 1024 + 128;
   static bool configured = false;
   if (!configured) {
-    if (cudaFuncSetAttribute(fa_bwd_dkdv_kernel<DH>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             SMEM) != cudaSuccess)
+    if (cudaFuncSetAttribute(fa_bwd_dkdv_kernel<DH, POLY>,
+                             cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess)
       return -5;
-    if (cudaFuncSetAttribute(fa_bwd_dq_kernel<DH>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             SMEM) != cudaSuccess)
+    if (cudaFuncSetAttribute(fa_bwd_dq_kernel<DH, POLY>,
+                             cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess)
       return -5;
     configured = true;
   }
   dim3 g1((p.Lk + T - 1) / T, p.H, p.B), g2((p.Lq + T - 1) / T, p.H, p.B);
-  fa_bwd_dkdv_kernel<DH><<<g1, 192, SMEM, st>>>(q, k, v, d, p);
-  fa_bwd_dq_kernel<DH><<<g2, 192, SMEM, st>>>(q, k, v, d, p);
+  fa_bwd_dkdv_kernel<DH, POLY><<<g1, 192, SMEM, st>>>(q, k, v, d, p);
+  fa_bwd_dq_kernel<DH, POLY><<<g2, 192, SMEM, st>>>(q, k, v, d, p);
   return (int)cudaGetLastError();
+}
+
+// Pairs (of every 16) whose 2^x runs on the FMA pipe instead of the special-function unit;
+// ERI_B200_FA_BWD_POLY = 0, 4 or 8 (read once, no allocation).
+int bwd_poly_pairs() {
+  static int v = -1;
+  if (v < 0) {
+    const char* e = getenv("ERI_B200_FA_BWD_POLY");
+    v = e ? atoi(e) : 8;
+    if (v != 0 && v != 4 && v != 8) v = 8;
+  }
+  return v;
+}
+
+template <int DH>
+int launch_bwd(const CUtensorMap& q, const CUtensorMap& k, const CUtensorMap& v,
+               const CUtensorMap& d, const FaBwdParams& p, cudaStream_t st) {
+  const int poly = bwd_poly_pairs();
+  if (poly == 0) return launch_bwd_v<DH, 0>(q, k, v, d, p, st);
+  if (poly == 8) return launch_bwd_v<DH, 8>(q, k, v, d, p, st);
+  return launch_bwd_v<DH, 4>(q, k, v, d, p, st);
 }
 
 }  // namespace

@@ -1,0 +1,312 @@
+// Warp-per-row LayerNorm / RMSNorm + adaLN modulation (forward and input-gradient backward),
+// persistent and fed by bulk asynchronous copies.
+//
+// Each warp owns a two-stage ring in shared memory. One lane issues `cp.async.bulk` row copies
+// (global -> shared, completion on an mbarrier) two rows ahead; the warp waits for a row, moves it
+// into registers as packed bf16 (one 16-byte shared load per lane per 256 columns), hands the
+// stage straight back to the copy engine, and then does its passes over registers: reductions are
+// warp shuffles, no block barrier anywhere. With 8-16 warps per SM that keeps 100-190 KB of loads
+// in flight per SM, which is what the HBM pipe needs; the CTA-per-row kernels in elementwise.cu
+// had only a few rows outstanding per SM and reached a quarter of the copy bandwidth.
+// Used when D is a multiple of 8 in [256, 4096] and (backward) no parameter gradients are
+// requested; other cases run the kernels in elementwise.cu (same math).
+// Reference counterpart: layer_norm / rms_norm followed by separate modulate ops
+// (crates/training/src/flux/runtime.rs:2153-2278); its backward is composed from tensor ops.
+#include "ptx.cuh"
+
+using namespace eri;
+typedef __nv_bfloat16 bf16;
+
+namespace {
+
+struct NormArgs {
+  const bf16 *x, *dy, *scale, *shift, *weight, *bias;
+  bf16* out;  // y (forward) or dx (backward)
+  float *mean, *rstd;
+  int rows, D, rows_per_batch, mod_stride;
+  float eps;
+  int rms;
+  int* err;
+};
+
+__device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+          smem_u32(dst)),
+      "l"(src), "r"(bytes), "r"(smem_u32(bar))
+      : "memory");
+}
+
+constexpr int kBarBytes = 1024;  // room for 32 warps x 2 stages of mbarriers
+
+template <int VPL, bool BWD>
+__global__ void __launch_bounds__(BWD ? 256 : 512, 1) norm_rows_kernel(const NormArgs a) {
+  extern __shared__ __align__(128) uint8_t smem[];
+  constexpr int NT = BWD ? 2 : 1;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
+  const int D = a.D, nvec = D >> 3;
+  const uint32_t row_bytes = (uint32_t)D * 2u;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem) + warp * 2;
+  uint8_t* ring = smem + kBarBytes + (size_t)warp * 2 * NT * row_bytes;
+  if (lane == 0) {
+    mbar_init(&bars[0], 1);
+    mbar_init(&bars[1], 1);
+    mbar_fence_init();
+  }
+  __syncwarp();
+  const int stride = gridDim.x * nwarps;
+  const int row0 = blockIdx.x * nwarps + warp;
+  auto issue = [&](int row, int st) {
+    mbar_expect_tx(&bars[st], NT * row_bytes);
+    bulk_g2s(ring + (size_t)st * NT * row_bytes, a.x + (size_t)row * D, row_bytes, &bars[st]);
+    if (BWD)
+      bulk_g2s(ring + (size_t)st * NT * row_bytes + row_bytes, a.dy + (size_t)row * D, row_bytes,
+               &bars[st]);
+  };
+  if (lane == 0) {
+    if (row0 < a.rows) issue(row0, 0);
+    if (row0 + stride < a.rows) issue(row0 + stride, 1);
+  }
+  const bf16x8* wv = a.weight ? reinterpret_cast<const bf16x8*>(a.weight) : nullptr;
+  const bf16x8* bv = a.bias ? reinterpret_cast<const bf16x8*>(a.bias) : nullptr;
+  const float inv_d = 1.f / (float)D;
+  int it = 0;
+  for (int row = row0; row < a.rows; row += stride, ++it) {
+    const int st = it & 1;
+    if (!mbar_wait(&bars[st], (uint32_t)((it >> 1) & 1))) {
+      if (lane == 0) atomicExch(a.err, 1);
+      break;
+    }
+    const bf16x8* sx = reinterpret_cast<const bf16x8*>(ring + (size_t)st * NT * row_bytes);
+    bf16x8 rx[VPL], rg[BWD ? VPL : 1];
+#pragma unroll
+    for (int i = 0; i < VPL; ++i) {
+      const int v = lane + 32 * i;
+      if (v < nvec) {
+        rx[i] = sx[v];
+        if (BWD) rg[i] = sx[nvec + v];
+      }
+    }
+    __syncwarp();
+    if (lane == 0 && row + 2 * stride < a.rows) {
+      fence_proxy_async_smem();  // the warp's reads of this stage precede the copy engine's writes
+      issue(row + 2 * stride, st);
+    }
+    const int b = row / a.rows_per_batch;
+    const bf16x8* sc =
+        a.scale ? reinterpret_cast<const bf16x8*>(a.scale + (size_t)b * a.mod_stride) : nullptr;
+    bf16x8* orow = reinterpret_cast<bf16x8*>(a.out + (size_t)row * D);
+
+    if (!BWD) {
+      const bf16x8* sh =
+          a.shift ? reinterpret_cast<const bf16x8*>(a.shift + (size_t)b * a.mod_stride) : nullptr;
+      float s = 0.f;
+#pragma unroll
+      for (int i = 0; i < VPL; ++i)
+        if (lane + 32 * i < nvec) {
+          float f[8];
+          unpack8(rx[i], f);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) s += a.rms ? f[j] * f[j] : f[j];
+        }
+      s = warp_sum(s);
+      float mean = 0.f, rstd;
+      if (a.rms) {
+        rstd = rsqrtf(s * inv_d + a.eps);
+      } else {
+        mean = s * inv_d;
+        float q = 0.f;
+#pragma unroll
+        for (int i = 0; i < VPL; ++i)
+          if (lane + 32 * i < nvec) {
+            float f[8];
+            unpack8(rx[i], f);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              const float d = f[j] - mean;
+              q += d * d;
+            }
+          }
+        rstd = rsqrtf(warp_sum(q) * inv_d + a.eps);
+      }
+      if (lane == 0) {
+        if (a.mean) a.mean[row] = mean;
+        if (a.rstd) a.rstd[row] = rstd;
+      }
+#pragma unroll
+      for (int i = 0; i < VPL; ++i) {
+        const int v = lane + 32 * i;
+        if (v < nvec) {
+          float o[8], t[8];
+          unpack8(rx[i], o);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) o[j] = (o[j] - mean) * rstd;
+          if (wv) {
+            unpack8(wv[v], t);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) o[j] *= t[j];
+          }
+          if (bv) {
+            unpack8(bv[v], t);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) o[j] += t[j];
+          }
+          if (sc) {
+            unpack8(sc[v], t);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) o[j] = fmaf(o[j], t[j], o[j]);
+          }
+          if (sh) {
+            unpack8(sh[v], t);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) o[j] += t[j];
+          }
+          orow[v] = pack8(o);
+        }
+      }
+    } else {
+      const float mean = a.rms ? 0.f : a.mean[row];
+      const float rstd = a.rstd[row];
+      // g = dy * (1 + scale) * weight, kept packed in rg (bf16 would lose bits: keep fp32 sums
+      // from the exact products and recompute the products in the output pass)
+      float s1 = 0.f, s2 = 0.f;
+#pragma unroll
+      for (int i = 0; i < VPL; ++i) {
+        const int v = lane + 32 * i;
+        if (v < nvec) {
+          float xx[8], g[8], t[8];
+          unpack8(rx[i], xx);
+          unpack8(rg[i], g);
+          if (sc) {
+            unpack8(sc[v], t);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) g[j] = fmaf(g[j], t[j], g[j]);
+          }
+          if (wv) {
+            unpack8(wv[v], t);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) g[j] *= t[j];
+          }
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            s1 += g[j];
+            s2 = fmaf(g[j], (xx[j] - mean) * rstd, s2);
+          }
+        }
+      }
+      const float c1 = a.rms ? 0.f : warp_sum(s1) * inv_d;
+      const float c2 = warp_sum(s2) * inv_d;
+#pragma unroll
+      for (int i = 0; i < VPL; ++i) {
+        const int v = lane + 32 * i;
+        if (v < nvec) {
+          float xx[8], g[8], t[8], o[8];
+          unpack8(rx[i], xx);
+          unpack8(rg[i], g);
+          if (sc) {
+            unpack8(sc[v], t);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) g[j] = fmaf(g[j], t[j], g[j]);
+          }
+          if (wv) {
+            unpack8(wv[v], t);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) g[j] *= t[j];
+          }
+#pragma unroll
+          for (int j = 0; j < 8; ++j) o[j] = rstd * (g[j] - c1 - (xx[j] - mean) * rstd * c2);
+          orow[v] = pack8(o);
+        }
+      }
+    }
+  }
+}
+
+int* g_norm_err = nullptr;
+int g_norm_sms = 0;
+
+template <bool BWD>
+int launch_rows(const NormArgs& a, cudaStream_t st) {
+  constexpr int NT = BWD ? 2 : 1;
+  const int D = a.D;
+  const int per_warp = 2 * NT * D * 2;
+  int warps = (200 * 1024 - kBarBytes) / per_warp;
+  if (warps > (BWD ? 8 : 16)) warps = BWD ? 8 : 16;
+  if (warps < 1) return -100;
+  const int smem = kBarBytes + warps * per_warp;
+  const int vpl = ((D >> 3) + 31) / 32;
+  int grid = (a.rows + warps - 1) / warps;
+  if (grid > g_norm_sms) grid = g_norm_sms;
+#define ERI_CASE(V)                                                                             \
+  do {                                                                                          \
+    static bool configured = false;                                                             \
+    if (!configured) {                                                                          \
+      if (cudaFuncSetAttribute(norm_rows_kernel<V, BWD>,                                        \
+                               cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) !=      \
+          cudaSuccess)                                                                          \
+        return -101;                                                                            \
+      configured = true;                                                                        \
+    }                                                                                           \
+    norm_rows_kernel<V, BWD><<<grid, warps * 32, smem, st>>>(a);                                \
+  } while (0)
+  if (vpl <= 4) ERI_CASE(4); else if (vpl <= 8) ERI_CASE(8); else if (vpl <= 12) ERI_CASE(12); else ERI_CASE(16);
+#undef ERI_CASE
+  return (int)cudaGetLastError();
+}
+
+int norm_setup() {
+  if (!g_norm_err) {
+    if (cudaMalloc(&g_norm_err, sizeof(int)) != cudaSuccess) return -3;
+    cudaMemset(g_norm_err, 0, sizeof(int));
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&g_norm_sms, cudaDevAttrMultiProcessorCount, dev);
+    if (g_norm_sms <= 0) g_norm_sms = 148;
+  }
+  return 0;
+}
+
+}  // namespace
+
+extern "C" {
+
+// 0, or 1 when a bounded wait for a row copy ran out (the word is cleared by the read).
+int eri_norm_check_error() {
+  if (!g_norm_err) return 0;
+  int h = 0;
+  cudaMemcpy(&h, g_norm_err, sizeof(int), cudaMemcpyDeviceToHost);
+  if (h) cudaMemset(g_norm_err, 0, sizeof(int));
+  return h;
+}
+
+// Returns -100 when the shape is outside this kernel's range (caller uses the general kernel).
+int eri_norm_modulate_fwd_warp(const void* x, const void* scale, const void* shift, const void* weight,
+                               const void* bias, void* y, float* mean, float* rstd, int rows, int D,
+                               int rows_per_batch, int mod_stride, float eps, int rms, void* stream) {
+  if (D % 8 || D > 4096 || D < 256) return -100;
+  if ((reinterpret_cast<uintptr_t>(x) & 15) != 0) return -100;
+  if (norm_setup()) return -3;
+  NormArgs a;
+  a.x = (const bf16*)x; a.dy = nullptr; a.scale = (const bf16*)scale; a.shift = (const bf16*)shift;
+  a.weight = (const bf16*)weight; a.bias = (const bf16*)bias; a.out = (bf16*)y;
+  a.mean = mean; a.rstd = rstd; a.rows = rows; a.D = D; a.rows_per_batch = rows_per_batch;
+  a.mod_stride = mod_stride; a.eps = eps; a.rms = rms; a.err = g_norm_err;
+  return launch_rows<false>(a, (cudaStream_t)stream);
+}
+
+int eri_norm_modulate_bwd_warp(const void* dy, const void* x, const void* scale, const void* weight,
+                               const float* mean, const float* rstd, void* dx, int rows, int D,
+                               int rows_per_batch, int mod_stride, int rms, void* stream) {
+  if (D % 8 || D > 4096 || D < 256) return -100;
+  if (((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(dy)) & 15) != 0) return -100;
+  if (norm_setup()) return -3;
+  NormArgs a;
+  a.x = (const bf16*)x; a.dy = (const bf16*)dy; a.scale = (const bf16*)scale; a.shift = nullptr;
+  a.weight = (const bf16*)weight; a.bias = nullptr; a.out = (bf16*)dx;
+  a.mean = const_cast<float*>(mean); a.rstd = const_cast<float*>(rstd); a.rows = rows; a.D = D;
+  a.rows_per_batch = rows_per_batch; a.mod_stride = mod_stride; a.eps = 0.f; a.rms = rms;
+  a.err = g_norm_err;
+  return launch_rows<true>(a, (cudaStream_t)stream);
+}
+
+}  // extern "C"

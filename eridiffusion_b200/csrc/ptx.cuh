@@ -336,4 +336,86 @@ __device__ __forceinline__ bf16x8 pack8(const float (&f)[8]) {
   return p;
 }
 
+// ---- packed fp32 pairs (two fp32 lanes per 64-bit register; sm_100 executes add / mul / fma on
+// both lanes in one instruction, which halves the issue slots of softmax-style loops)
+typedef uint64_t f32x2;
+__device__ __forceinline__ f32x2 f2_pack(float lo, float hi) {
+  f32x2 r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ f32x2 f2_pack_bits(uint32_t lo, uint32_t hi) {
+  f32x2 r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "r"(lo), "r"(hi));
+  return r;
+}
+__device__ __forceinline__ void f2_unpack(f32x2 v, float& lo, float& hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ f32x2 f2_fma(f32x2 a, f32x2 b, f32x2 c) {
+  f32x2 d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
+}
+__device__ __forceinline__ f32x2 f2_add(f32x2 a, f32x2 b) {
+  f32x2 d;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+__device__ __forceinline__ f32x2 f2_sub(f32x2 a, f32x2 b) {
+  f32x2 d;
+  asm("sub.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+__device__ __forceinline__ f32x2 f2_mul(f32x2 a, f32x2 b) {
+  f32x2 d;
+  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+__device__ __forceinline__ float fmax3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+// 2^x on the special-function unit: one instruction, flushes denormal results to zero.
+__device__ __forceinline__ float ex2_mufu(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+// 2^x for a pair on the FMA pipe (no special-function unit): round-to-nearest split x = n + f with
+// f in [-0.5, 0.5] by the 1.5*2^23 trick, cubic minimax polynomial for 2^f (max relative error
+// 7.5e-5, well under bf16 rounding), exponent added by an integer multiply-add. x is clamped at
+// -126 so the result stays normal; the caller guarantees x <= 127.
+__device__ __forceinline__ f32x2 ex2_poly2(f32x2 x) {
+  float x0, x1;
+  f2_unpack(x, x0, x1);
+  x0 = fmaxf(x0, -126.f);
+  x1 = fmaxf(x1, -126.f);
+  x = f2_pack(x0, x1);
+  const f32x2 magic = f2_pack(12582912.f, 12582912.f);
+  const f32x2 t = f2_add(x, magic);
+  const f32x2 f = f2_sub(x, f2_sub(t, magic));
+  f32x2 p = f2_pack(0.0551716685f, 0.0551716685f);
+  p = f2_fma(p, f, f2_pack(0.2426111251f, 0.2426111251f));
+  p = f2_fma(p, f, f2_pack(0.6932609677f, 0.6932609677f));
+  p = f2_fma(p, f, f2_pack(0.9999280572f, 0.9999280572f));
+  uint32_t t0, t1, p0, p1;
+  asm("mov.b64 {%0, %1}, %2;" : "=r"(t0), "=r"(t1) : "l"(t));
+  asm("mov.b64 {%0, %1}, %2;" : "=r"(p0), "=r"(p1) : "l"(p));
+  // the low mantissa bits of t hold n (two's complement in the 23-bit field); n << 23 added to
+  // the bits of p scales it by 2^n
+  p0 += t0 << 23;
+  p1 += t1 << 23;
+  return f2_pack_bits(p0, p1);
+}
+// round a pair to packed bf16 (low half = lo)
+__device__ __forceinline__ uint32_t f2_to_bf162(f32x2 v) {
+  float lo, hi;
+  f2_unpack(v, lo, hi);
+  uint32_t d;
+  asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(d) : "f"(hi), "f"(lo));
+  return d;
+}
+
 }  // namespace eri

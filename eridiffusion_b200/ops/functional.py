@@ -90,10 +90,13 @@ class _NormModulate(torch.autograd.Function):
         mean = torch.empty(B * L, dtype=torch.float32, device=x.device)
         rstd = torch.empty(B * L, dtype=torch.float32, device=x.device)
         lib = N.require()
-        N.check(lib.eri_norm_modulate_fwd(
-            x.data_ptr(), N.ptr(scale_v), N.ptr(shift_v), N.ptr(weight), N.ptr(bias),
-            y.data_ptr(), mean.data_ptr(), rstd.data_ptr(), B * L, D, L, stride, eps,
-            1 if rms else 0, N.stream_ptr()), "norm_modulate_fwd")
+        args = (x.data_ptr(), N.ptr(scale_v), N.ptr(shift_v), N.ptr(weight), N.ptr(bias),
+                y.data_ptr(), mean.data_ptr(), rstd.data_ptr(), B * L, D, L, stride, eps,
+                1 if rms else 0, N.stream_ptr())
+        code = lib.eri_norm_modulate_fwd_warp(*args) if hasattr(lib, "eri_norm_modulate_fwd_warp") else -100
+        if code == -100:
+            code = lib.eri_norm_modulate_fwd(*args)
+        N.check(code, "norm_modulate_fwd")
         ctx.save_for_backward(x, scale_v, weight, bias, mean, rstd)
         ctx.meta = (B, L, D, stride, rms, scale is not None, shift is not None)
         return y
@@ -111,11 +114,18 @@ class _NormModulate(torch.autograd.Function):
         dweight = torch.zeros(D, **f32) if (weight is not None and need[3]) else None
         dbias = torch.zeros(D, **f32) if (bias is not None and need[4]) else None
         lib = N.require()
-        N.check(lib.eri_norm_modulate_bwd(
-            dy.data_ptr(), x.data_ptr(), N.ptr(scale_v), N.ptr(weight), N.ptr(bias),
-            mean.data_ptr(), rstd.data_ptr(), dx.data_ptr(), N.ptr(dscale), N.ptr(dshift),
-            N.ptr(dweight), N.ptr(dbias), B * L, D, L, stride, 1 if rms else 0, N.stream_ptr()),
-            "norm_modulate_bwd")
+        code = -100
+        if dscale is None and dshift is None and dweight is None and dbias is None \
+                and hasattr(lib, "eri_norm_modulate_bwd_warp"):
+            code = lib.eri_norm_modulate_bwd_warp(
+                dy.data_ptr(), x.data_ptr(), N.ptr(scale_v), N.ptr(weight), mean.data_ptr(),
+                rstd.data_ptr(), dx.data_ptr(), B * L, D, L, stride, 1 if rms else 0, N.stream_ptr())
+        if code == -100:
+            code = lib.eri_norm_modulate_bwd(
+                dy.data_ptr(), x.data_ptr(), N.ptr(scale_v), N.ptr(weight), N.ptr(bias),
+                mean.data_ptr(), rstd.data_ptr(), dx.data_ptr(), N.ptr(dscale), N.ptr(dshift),
+                N.ptr(dweight), N.ptr(dbias), B * L, D, L, stride, 1 if rms else 0, N.stream_ptr())
+        N.check(code, "norm_modulate_bwd")
         cv = lambda t: None if t is None else t.to(torch.bfloat16)
         return dx, cv(dscale), cv(dshift), cv(dweight), cv(dbias), None, None
 
@@ -407,6 +417,20 @@ def gemm_error_check() -> int:
     if not e and hasattr(lib, "eri_gemm2_check_error"):
         e = lib.eri_gemm2_check_error()
     return e
+
+
+def kernel_error_check() -> dict:
+    """Synchronise and read every kernel family's device error word (each is set when one of that
+    family's bounded waits ran out, and cleared by the read). Empty dict = clean."""
+    lib = N.require()
+    out = {}
+    for name in ("gemm", "gemm2", "fa", "fa_bwd", "norm"):
+        fn = getattr(lib, f"eri_{name}_check_error", None)
+        if fn is not None:
+            v = fn()
+            if v:
+                out[name] = v
+    return out
 
 
 def _mm(a, b_nk, **kw):

@@ -48,6 +48,27 @@ def test_norm_modulate_fwd_bwd(rms, D):
     close(w.grad, wr.grad, 0.3, 3e-2)
 
 
+@pytest.mark.parametrize("rms", [False, True])
+@pytest.mark.parametrize("L,D", [(67, 256), (2500, 3072), (5000, 264), (700, 4096)])
+def test_norm_modulate_row_kernels(rms, L, D):
+    """Input-gradient-only case (frozen modulation and weight): the persistent warp-per-row
+    kernels fed by bulk copies; the long cases make every warp cycle its two-stage ring."""
+    B = 2
+    x = rnd(B, L, D).requires_grad_()
+    mod = rnd(B, 2 * D, scale=0.3)
+    w = rnd(D, scale=0.5)
+    sh, sc = mod.split(D, dim=-1)
+    y = F.norm_modulate(x, sc, sh, w, None, 1e-6, rms)
+    xr = x.detach().float().requires_grad_()
+    yr = R.norm_modulate(xr, sc.float(), sh.float(), w.float(), None, 1e-6, rms)
+    close(y, yr, 3e-2)
+    g = rnd(B, L, D, seed=5)
+    y.backward(g)
+    yr.backward(g.float())
+    close(x.grad, xr.grad, 3e-2, 3e-2)
+    assert F.kernel_error_check() == {}
+
+
 @pytest.mark.parametrize("Dh", [64, 128])
 def test_qknorm_rope_joint(Dh):
     B, H, Lt, Li = 2, 4, 24, 40

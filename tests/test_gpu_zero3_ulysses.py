@@ -18,6 +18,15 @@ def _rel(a, b):
 
 
 def _worker(rank, world, port, q):
+    try:
+        _worker_body(rank, world, port, q)
+    except BaseException as e:                      # report instead of leaving the parent waiting
+        import traceback
+        q.put({"error": f"rank {rank}: {e!r}\n{traceback.format_exc()}"})
+        raise
+
+
+def _worker_body(rank, world, port, q):
     os.environ.update(WORLD_SIZE=str(world), RANK=str(rank), LOCAL_RANK=str(rank),
                       MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
     import torch
@@ -56,8 +65,9 @@ def _worker(rank, world, port, q):
     # reference: full weights, every rank's data
     xr = [t.clone().float().requires_grad_() for t in xs]
     vr = [t.clone().float().requires_grad_() for t in vs]
-    wf, bf = lin.weight.float().requires_grad_(), lin.bias.float()
-    sw, sb = small.weight.float().requires_grad_(), small.bias.float().requires_grad_()
+    wf, bf = lin.weight.detach().float().requires_grad_(), lin.bias.detach().float()
+    sw = small.weight.detach().float().requires_grad_()
+    sb = small.bias.detach().float().requires_grad_()
     tot = 0
     for r in range(world):
         yr = torch.nn.functional.gelu(torch.nn.functional.linear(xr[r], wf, bf), approximate="tanh")
@@ -126,6 +136,12 @@ def test_zero3_and_ulysses_two_gpus():
     for p in procs:
         p.start()
     out = q.get(timeout=300)
+    if "error" in out:
+        for p in procs:
+            p.join(timeout=30)
+            if p.is_alive():
+                p.kill()
+        pytest.fail(out["error"])
     for p in procs:
         p.join(timeout=120)
         assert p.exitcode == 0
