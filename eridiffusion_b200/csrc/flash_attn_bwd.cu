@@ -29,6 +29,10 @@ struct FaBwdParams {
   float scale, scale_log2;
   const float* lse2;     // [B, H, Lp]
   const float* delta;    // [B, H, Lp]
+  const bf16* q;         // [B, Lq, H, DH] (read directly by the dQ kernel's operand staging)
+  const bf16* dout;      // [B, Lq, H, DH]
+  long long* trace;      // optional timeline buffer (CTA 0 only), see eri_fa_bwd_set_trace
+  int trace_cap;         // entries per recorder
   bf16* dq;              // [B, Lq, H, DH]
   bf16* dk;              // [B, Lk, H, DH]
   bf16* dv;
@@ -40,28 +44,44 @@ constexpr int T = 128;  // tile edge (queries and keys)
 __global__ void fa_bwd_prep_kernel(const bf16* __restrict__ o, const bf16* __restrict__ dout,
                                    const float* __restrict__ lse, float* __restrict__ lse2,
                                    float* __restrict__ delta, int B, int H, int Lq, int Lp, int DH) {
-  const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
-  const int total = B * H * Lp;
-  if (warp >= total) return;
-  const int l = warp % Lp, h = (warp / Lp) % H, b = warp / (Lp * H);
-  if (l >= Lq) {
-    if (lane == 0) {
-      lse2[warp] = INFINITY;
-      delta[warp] = 0.f;
-    }
-    return;
-  }
-  const size_t base = (((size_t)b * Lq + l) * H + h) * DH;
+  // 16 lanes per (b, h, l) row, one 16-byte load of O and of dO per lane per 128 columns
+  const long long gid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const long long rowid = gid >> 4;
+  const int sub = threadIdx.x & 15;
+  const long long total = (long long)B * H * Lp;
+  if (rowid >= total) return;
+  const int l = (int)(rowid % Lp), h = (int)((rowid / Lp) % H), b = (int)(rowid / ((long long)Lp * H));
   float acc = 0.f;
-  for (int d = lane * 2; d < DH; d += 64) {
-    float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(o + base + d));
-    float2 g = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(dout + base + d));
-    acc += a.x * g.x + a.y * g.y;
+  if (l < Lq) {
+    const size_t base = (((size_t)b * Lq + l) * H + h) * DH;
+    for (int d = sub * 8; d < DH; d += 128) {
+      float a[8], g[8];
+      unpack8(*reinterpret_cast<const bf16x8*>(o + base + d), a);
+      unpack8(*reinterpret_cast<const bf16x8*>(dout + base + d), g);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc = fmaf(a[j], g[j], acc);
+    }
   }
-  acc = warp_sum(acc);
-  if (lane == 0) {
-    delta[warp] = acc;
-    lse2[warp] = lse[((size_t)b * H + h) * Lq + l] * 1.4426950408889634f;
+#pragma unroll
+  for (int off = 8; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
+  if (sub == 0) {
+    if (l < Lq) {
+      delta[rowid] = acc;
+      lse2[rowid] = lse[((size_t)b * H + h) * Lq + l] * 1.4426950408889634f;
+    } else {
+      lse2[rowid] = INFINITY;
+      delta[rowid] = 0.f;
+    }
+  }
+}
+
+// Timeline recorder for performance work: when a trace buffer is set, the MMA-issuing thread and
+// lane 0 of the first softmax warp of CTA (0,0,0) store (clock64 << 8 | event code) at each
+// pipeline hand-off. `rec` selects the recorder's half of the buffer.
+__device__ __forceinline__ void trace_ev(const FaBwdParams& p, int rec, int& n, int code) {
+  if (p.trace && n < p.trace_cap && (blockIdx.x | blockIdx.y | blockIdx.z) == 0) {
+    p.trace[rec * p.trace_cap + n] = (clock64() << 8) | (long long)code;
+    ++n;
   }
 }
 
@@ -71,7 +91,7 @@ __device__ __forceinline__ void named_bar_sync(int id, int nthreads) {
 
 // ------------------------------------------------------------------------------------- dK, dV
 template <int DH, int POLY>
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(576, 1)
 fa_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                    const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmDO,
                    const FaBwdParams p) {
@@ -93,8 +113,10 @@ fa_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   uint64_t* kv_full = bars + 0;
   uint64_t* qdo_full = bars + 1;   // [2]
   uint64_t* qdo_empty = bars + 3;  // [2]
-  uint64_t* sp_full = bars + 5;    // [2] one per 64-query half
-  uint64_t* pds_ready = bars + 7;  // [2]
+  uint64_t* s_full = bars + 5;
+  uint64_t* dp_full = bars + 6;
+  uint64_t* p_ready = bars + 7;    // 16 softmax warps wrote P^T
+  uint64_t* ds_ready = bars + 8;   // 16 softmax warps wrote dS^T
   uint64_t* acc_done = bars + 9;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 10);
 
@@ -108,10 +130,10 @@ fa_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       mbar_init(&qdo_full[s], 1);
       mbar_init(&qdo_empty[s], 1);
     }
-    for (int s = 0; s < 2; ++s) {
-      mbar_init(&sp_full[s], 1);
-      mbar_init(&pds_ready[s], 4);
-    }
+    mbar_init(s_full, 1);
+    mbar_init(dp_full, 1);
+    mbar_init(p_ready, 16);
+    mbar_init(ds_ready, 16);
     mbar_init(acc_done, 1);
     mbar_fence_init();
   }
@@ -148,143 +170,189 @@ fa_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     }
   } else if (warp == 1) {
     if (elect_one()) {
-      // Software pipeline over 64-query halves: while the softmax warps turn one half of
-      // S^T / dP^T into P^T / dS^T, the tensor pipe runs the other half's products, and the
-      // next tile's first half is issued before this tile's second half is consumed.
-      const uint32_t idesc_s = umma_idesc_bf16(T, 64, 0, 0);
+      // Phase pipeline, every MMA 128 x 128 x 16:
+      //   S_i | dP_i | dV_i | S_{i+1} | dK_i | dP_{i+1} | dV_{i+1} | S_{i+2} | dK_{i+1} | ...
+      // The softmax warps turn S_i into P_i while dP_i runs, and P_i, dP_i into dS_i while
+      // dV_i and S_{i+1} run, so the tensor pipe never waits for them in steady state.
+      const uint32_t idesc_s = umma_idesc_bf16(T, T, 0, 0);
       const uint32_t idesc_g = umma_idesc_bf16(T, DH, 0, 1);
       const uint32_t aK = smem_u32(sK), aV = smem_u32(sV);
       const uint32_t aQ0 = smem_u32(sQ), aDO0 = smem_u32(sDO);
-      auto issue_sdp = [&](int st, int hf) {  // S^T and dP^T for queries [64 hf, 64 hf + 64)
-        const uint32_t aQ = aQ0 + st * TILE_BYTES + hf * 8192, aDO = aDO0 + st * TILE_BYTES + hf * 8192;
+      auto issue_s = [&](int st) {
+        const uint32_t aQ = aQ0 + st * TILE_BYTES;
 #pragma unroll
         for (int c = 0; c < CHUNKS; ++c) {
           const uint64_t da = umma_desc_kmajor(aK + c * CHUNK_BYTES, 128);
           const uint64_t db = umma_desc_kmajor(aQ + c * CHUNK_BYTES, 128);
 #pragma unroll
           for (int kk = 0; kk < 4; ++kk)
-            umma_bf16(tmem_base + S_COL + hf * 64, da + kk * 2, db + kk * 2, idesc_s, (c | kk) != 0);
+            umma_bf16(tmem_base + S_COL, da + kk * 2, db + kk * 2, idesc_s, (c | kk) != 0);
         }
+        umma_commit(s_full);
+      };
+      auto issue_dp = [&](int st) {
+        const uint32_t aDO = aDO0 + st * TILE_BYTES;
 #pragma unroll
         for (int c = 0; c < CHUNKS; ++c) {
           const uint64_t da = umma_desc_kmajor(aV + c * CHUNK_BYTES, 128);
           const uint64_t db = umma_desc_kmajor(aDO + c * CHUNK_BYTES, 128);
 #pragma unroll
           for (int kk = 0; kk < 4; ++kk)
-            umma_bf16(tmem_base + DP_COL + hf * 64, da + kk * 2, db + kk * 2, idesc_s, (c | kk) != 0);
+            umma_bf16(tmem_base + DP_COL, da + kk * 2, db + kk * 2, idesc_s, (c | kk) != 0);
         }
-        umma_commit(&sp_full[hf]);
+        umma_commit(dp_full);
       };
-      auto issue_dvdk = [&](int st, int hf, bool first) {
-        const uint32_t aQ = aQ0 + st * TILE_BYTES, aDO = aDO0 + st * TILE_BYTES;
+      // A operand from TMEM: the packed bf16 of query chunk kk/2 sits in that chunk's first columns
+      auto issue_acc = [&](uint32_t acc_col, uint32_t a_col, uint32_t b_smem, bool first) {
 #pragma unroll
-        for (int kk = 0; kk < 4; ++kk) {
-          const uint64_t dbo = umma_desc_mn128(aDO + (hf * 4 + kk) * 2048, CHUNK_BYTES);
-          umma_bf16_ts(tmem_base + DV_COL, tmem_base + S_COL + hf * 64 + kk * 8, dbo, idesc_g,
-                       !first || kk != 0);
-        }
-#pragma unroll
-        for (int kk = 0; kk < 4; ++kk) {
-          const uint64_t dbq = umma_desc_mn128(aQ + (hf * 4 + kk) * 2048, CHUNK_BYTES);
-          umma_bf16_ts(tmem_base + DK_COL, tmem_base + DP_COL + hf * 64 + kk * 8, dbq, idesc_g,
-                       !first || kk != 0);
+        for (int kk = 0; kk < T / 16; ++kk) {
+          const uint64_t db = umma_desc_mn128(b_smem + kk * 2048, CHUNK_BYTES);
+          umma_bf16_ts(tmem_base + acc_col, tmem_base + a_col + (kk >> 1) * 32 + (kk & 1) * 8, db,
+                       idesc_g, !first || kk != 0);
         }
       };
+      int tn = 0;
+      trace_ev(p, 0, tn, 0);
       bool ok = mbar_wait(kv_full, 0);
       if (!ok) atomicExch(p.err, 22);
       if (ok && !mbar_wait(&qdo_full[0], 0)) { atomicExch(p.err, 23); ok = false; }
+      trace_ev(p, 0, tn, 1);
       if (ok) {
         tc_fence_after();
-        issue_sdp(0, 0);
-        issue_sdp(0, 1);
+        issue_s(0);
+        issue_dp(0);
       }
       for (int i = 0; i < nq && ok; ++i) {
         const int s = i & 1;
         const uint32_t par = (uint32_t)(i & 1);
         const bool more = i + 1 < nq;
-        if (!mbar_wait(&pds_ready[0], par)) { atomicExch(p.err, 24); ok = false; break; }
+        if (!mbar_wait(p_ready, par)) { atomicExch(p.err, 24); ok = false; break; }
+        trace_ev(p, 0, tn, 2);
         tc_fence_after();
-        issue_dvdk(s, 0, i == 0);
+        issue_acc(DV_COL, S_COL, aDO0 + s * TILE_BYTES, i == 0);
+        trace_ev(p, 0, tn, 3);
         if (more) {
           if (!mbar_wait(&qdo_full[s ^ 1], (uint32_t)(((i + 1) >> 1) & 1))) {
             atomicExch(p.err, 23);
             ok = false;
             break;
           }
+          trace_ev(p, 0, tn, 4);
           tc_fence_after();
-          issue_sdp(s ^ 1, 0);
+          issue_s(s ^ 1);
+          trace_ev(p, 0, tn, 5);
         }
-        if (!mbar_wait(&pds_ready[1], par)) { atomicExch(p.err, 27); ok = false; break; }
+        if (!mbar_wait(ds_ready, par)) { atomicExch(p.err, 27); ok = false; break; }
+        trace_ev(p, 0, tn, 6);
         tc_fence_after();
-        issue_dvdk(s, 1, false);
+        issue_acc(DK_COL, DP_COL, aQ0 + s * TILE_BYTES, i == 0);
         umma_commit(&qdo_empty[s]);
-        if (more) issue_sdp(s ^ 1, 1);
+        trace_ev(p, 0, tn, 7);
+        if (more) issue_dp(s ^ 1);
+        trace_ev(p, 0, tn, 8);
       }
       if (ok) umma_commit(acc_done);
     }
   } else {
+    // Sixteen softmax warps: warp (qd, c) owns TMEM lanes [32 qd, 32 qd + 32) (keys) and the
+    // 32-query chunk c of every tile. Phase 1 (after S^T): P^T = exp2(S^T c - lse2), written back
+    // over the chunk's first 16 columns as packed bf16 and kept in registers as fp32. Phase 2
+    // (after dP^T): dS^T = P^T * (dP^T - delta), written the same way over dP^T.
     const int qd = warp & 3;
-    const int tid = threadIdx.x - 64;  // 0..127
+    const int ew = warp - 2;
+    const int c = ew >> 2;
+    const int sub = c;                                // epilogue column chunk
+    const int tid = threadIdx.x - 64;                 // 0..511
     const uint32_t lane_addr = tmem_base + ((uint32_t)(qd * 32) << 16);
     const size_t stat_base = ((size_t)b * p.H + h) * p.Lp;
+    const f32x2 sc2 = f2_pack(p.scale_log2, p.scale_log2);
     bool ok = true;
+    int tn = 0;
+    const int rec = (ew == 0 && lane == 0) ? 1 : -1;
+    // Row statistics of the query tile: -lse2 (so one packed fma gives s * c - lse2) and delta,
+    // staged through shared memory one tile ahead: the global load for tile i + 1 is issued at
+    // the top of tile i and stored at its end, so its latency never sits in the loop.
+    const float* stat_src = tid < T ? p.lse2 + stat_base + tid : p.delta + stat_base + tid - T;
+    float* stat_dst = tid < T ? s_lse + tid : s_delta + tid - T;
+    const float stat_sign = tid < T ? -1.f : 1.f;
+    if (tid < 2 * T) stat_dst[0] = stat_sign * stat_src[0];
     for (int i = 0; i < nq; ++i) {
       const int s = i & 1;
-      s_lse[s * T + tid] = -p.lse2[stat_base + i * T + tid];
-      s_delta[s * T + tid] = p.delta[stat_base + i * T + tid];
-      named_bar_sync(1, 128);
-      // s_lse holds -lse2 so that one packed fma gives s * c - lse2 for two queries
-      const float4* ls4 = reinterpret_cast<const float4*>(s_lse + s * T);
-      const float4* dl4 = reinterpret_cast<const float4*>(s_delta + s * T);
-      const f32x2 sc2 = f2_pack(p.scale_log2, p.scale_log2);
-#pragma unroll 1
-      for (int hf = 0; hf < 2 && ok; ++hf) {
-        if (!mbar_wait(&sp_full[hf], (uint32_t)(i & 1))) {
-          if (lane == 0) atomicExch(p.err, 25);
-          ok = false;
-          break;
-        }
-        tc_fence_after();
-#pragma unroll 1
-        for (int cc = 0; cc < 2; ++cc) {
-          const int c = hf * 2 + cc;  // 32-query chunk
-          uint32_t r[32], g[32];
-          tmem_ld32(lane_addr + S_COL + c * 32, r);
-          tmem_ld32(lane_addr + DP_COL + c * 32, g);
-          tmem_ld_wait();
-          uint32_t pk[16], dk_[16];
+      float stat_next = 0.f;
+      if (tid < 2 * T && i + 1 < nq) stat_next = stat_sign * stat_src[(size_t)(i + 1) * T];
+      named_bar_sync(1, 512);
+      const float4* ls4 = reinterpret_cast<const float4*>(s_lse + s * T) + c * 8;
+      const float4* dl4 = reinterpret_cast<const float4*>(s_delta + s * T) + c * 8;
+      if (rec > 0) trace_ev(p, rec, tn, 10);
+      if (!mbar_wait(s_full, (uint32_t)(i & 1))) {
+        if (lane == 0) atomicExch(p.err, 25);
+        ok = false;
+        break;
+      }
+      if (rec > 0) trace_ev(p, rec, tn, 11);
+      tc_fence_after();
+      f32x2 pr[16];
+      {
+        uint32_t r[32];
+        tmem_ld32(lane_addr + S_COL + c * 32, r);
+        tmem_ld_wait();
+        uint32_t pk[16];
 #pragma unroll
-          for (int x4 = 0; x4 < 8; ++x4) {
-            const float4 nl = ls4[c * 8 + x4];
-            const float4 dl = dl4[c * 8 + x4];
+        for (int x4 = 0; x4 < 8; ++x4) {
+          const float4 nl = ls4[x4];
 #pragma unroll
-            for (int hh = 0; hh < 2; ++hh) {
-              const int x = 2 * x4 + hh;
-              const f32x2 nl2 = hh ? f2_pack(nl.z, nl.w) : f2_pack(nl.x, nl.y);
-              const f32x2 dl2 = hh ? f2_pack(dl.z, dl.w) : f2_pack(dl.x, dl.y);
-              f32x2 v = f2_fma(f2_pack_bits(r[2 * x], r[2 * x + 1]), sc2, nl2);
-              if (x < 16 - POLY) {
-                float lo, hi;
-                f2_unpack(v, lo, hi);
-                v = f2_pack(ex2_mufu(lo), ex2_mufu(hi));
-              } else {
-                v = ex2_poly2(v);
-              }
-              const f32x2 d = f2_mul(v, f2_sub(f2_pack_bits(g[2 * x], g[2 * x + 1]), dl2));
-              pk[x] = f2_to_bf162(v);
-              dk_[x] = f2_to_bf162(d);
+          for (int hh = 0; hh < 2; ++hh) {
+            const int x = 2 * x4 + hh;
+            const f32x2 nl2 = hh ? f2_pack(nl.z, nl.w) : f2_pack(nl.x, nl.y);
+            f32x2 v = f2_fma(f2_pack_bits(r[2 * x], r[2 * x + 1]), sc2, nl2);
+            if (x < 16 - POLY) {
+              float lo, hi;
+              f2_unpack(v, lo, hi);
+              v = f2_pack(ex2_mufu(lo), ex2_mufu(hi));
+            } else {
+              v = ex2_poly2(v);
             }
+            pr[x] = v;
+            pk[x] = f2_to_bf162(v);
           }
-          // packed bf16 P^T / dS^T of this half start at the half's own first column
-          tmem_st16(lane_addr + S_COL + hf * 64 + cc * 16, pk);
-          tmem_st16(lane_addr + DP_COL + hf * 64 + cc * 16, dk_);
         }
+        tmem_st16(lane_addr + S_COL + c * 32, pk);
         tmem_st_wait();
         tc_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive(&pds_ready[hf]);
+        if (lane == 0) mbar_arrive(p_ready);
       }
-      if (!ok) break;
+      if (rec > 0) trace_ev(p, rec, tn, 13);
+      if (!mbar_wait(dp_full, (uint32_t)(i & 1))) {
+        if (lane == 0) atomicExch(p.err, 28);
+        ok = false;
+        break;
+      }
+      if (rec > 0) trace_ev(p, rec, tn, 14);
+      tc_fence_after();
+      {
+        uint32_t g[32];
+        tmem_ld32(lane_addr + DP_COL + c * 32, g);
+        tmem_ld_wait();
+        uint32_t dk_[16];
+#pragma unroll
+        for (int x4 = 0; x4 < 8; ++x4) {
+          const float4 dl = dl4[x4];
+#pragma unroll
+          for (int hh = 0; hh < 2; ++hh) {
+            const int x = 2 * x4 + hh;
+            const f32x2 dl2 = hh ? f2_pack(dl.z, dl.w) : f2_pack(dl.x, dl.y);
+            dk_[x] = f2_to_bf162(f2_mul(pr[x], f2_sub(f2_pack_bits(g[2 * x], g[2 * x + 1]), dl2)));
+          }
+        }
+        tmem_st16(lane_addr + DP_COL + c * 32, dk_);
+        tmem_st_wait();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(ds_ready);
+        if (rec > 0) trace_ev(p, rec, tn, 17);
+      }
+      if (tid < 2 * T && i + 1 < nq) stat_dst[(s ^ 1) * T] = stat_next;
     }
     if (ok && !mbar_wait(acc_done, 0)) {
       if (lane == 0) atomicExch(p.err, 26);
@@ -295,7 +363,7 @@ fa_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       const int kv = k0 + qd * 32 + lane;
       const size_t obase = (((size_t)b * p.Lk + kv) * p.H + h) * DH;
 #pragma unroll 1
-      for (int c = 0; c < DH / 32; ++c) {
+      for (int c = sub; c < DH / 32; c += 4) {
         uint32_t rv[32], rk[32];
         tmem_ld32(lane_addr + DV_COL + c * 32, rv);
         tmem_ld32(lane_addr + DK_COL + c * 32, rk);
@@ -327,46 +395,59 @@ fa_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
 
 // ------------------------------------------------------------------------------------- dQ
 template <int DH, int POLY>
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(576, 1)
 fa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                  const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmDO,
                  const FaBwdParams p) {
   constexpr int CHUNKS = DH / 64;
   constexpr int CHUNK_BYTES = T * 128;
   constexpr int TILE_BYTES = CHUNK_BYTES * CHUNKS;
-  constexpr uint32_t S_COL = 0, DP_COL = 128, DQ_COL = 256;
+  // TMEM: S, dP and the dQ accumulator (fp32, 128 columns each), Q as a packed-bf16 A operand
+  // (64 columns, staged once) and dS as a packed-bf16 A operand (64 columns). dS has its own
+  // columns so that the next dP does not have to wait for dQ to consume dS out of the dP region.
+  constexpr uint32_t S_COL = 0, DP_COL = 128, DQ_COL = 256, QA_COL = 384, DS_COL = 448;
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~uintptr_t(1023));
-  uint8_t* sQ = smem;
-  uint8_t* sDO = sQ + TILE_BYTES;
-  uint8_t* sK = sDO + TILE_BYTES;      // 2 stages
-  uint8_t* sV = sK + 2 * TILE_BYTES;   // 2 stages
-  uint64_t* bars = reinterpret_cast<uint64_t*>(sV + 2 * TILE_BYTES);
-  uint64_t* qdo_full = bars + 0;
-  uint64_t* kv_full = bars + 1;   // [2]
-  uint64_t* kv_empty = bars + 3;  // [2]
-  uint64_t* sp_full = bars + 5;   // [2] one per 64-key half
-  uint64_t* ds_ready = bars + 7;  // [2]
-  uint64_t* acc_done = bars + 9;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 10);
+  // Three K/V stages: a 64 KB tile pair takes ~1500 cycles to arrive, about one tile period, so
+  // the load of tile j + 2 has to start while tile j is still being consumed.
+  constexpr int NST = 3;
+  uint8_t* sK = smem;                    // NST stages
+  uint8_t* sV = sK + NST * TILE_BYTES;   // NST stages
+  uint8_t* sDO = sV + NST * TILE_BYTES;  // this CTA's dO tile (A operand of dP, loaded once)
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sDO + TILE_BYTES);
+  uint64_t* qa_ready = bars + 0;  // Q / dO staged in TMEM by the 16 softmax warps
+  uint64_t* kv_full = bars + 1;   // [NST]
+  uint64_t* kv_empty = bars + 4;  // [NST]
+  uint64_t* s_full = bars + 7;
+  uint64_t* dp_full = bars + 8;
+  uint64_t* s_read = bars + 9;     // 16 softmax warps hold S in registers
+  uint64_t* ds_ready = bars + 10;  // 16 softmax warps wrote dS
+  uint64_t* acc_done = bars + 11;
+  uint64_t* do_full = bars + 12;
+  uint64_t* dp_read = bars + 13;   // 16 softmax warps hold dP in registers
+  uint64_t* dq_done = bars + 14;   // dQ_j finished reading dS_j
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 15);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int q0 = blockIdx.x * T, h = blockIdx.y, b = blockIdx.z;
   const int nkv = (p.Lk + T - 1) / T;
 
   if (threadIdx.x == 0) {
-    mbar_init(qdo_full, 1);
-    for (int s = 0; s < 2; ++s) {
+    mbar_init(qa_ready, 16);
+    for (int s = 0; s < NST; ++s) {
       mbar_init(&kv_full[s], 1);
       mbar_init(&kv_empty[s], 1);
     }
-    for (int s = 0; s < 2; ++s) {
-      mbar_init(&sp_full[s], 1);
-      mbar_init(&ds_ready[s], 4);
-    }
+    mbar_init(s_full, 1);
+    mbar_init(dp_full, 1);
+    mbar_init(s_read, 16);
+    mbar_init(ds_ready, 16);
     mbar_init(acc_done, 1);
+    mbar_init(do_full, 1);
+    mbar_init(dp_read, 16);
+    mbar_init(dq_done, 1);
     mbar_fence_init();
   }
   if (warp == 1) {
@@ -380,15 +461,13 @@ fa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
 
   if (warp == 0) {
     if (elect_one()) {
-      mbar_expect_tx(qdo_full, 2 * TILE_BYTES);
+      mbar_expect_tx(do_full, TILE_BYTES);
 #pragma unroll
-      for (int c = 0; c < CHUNKS; ++c) {
-        tma_load_3d(sQ + c * CHUNK_BYTES, &tmQ, qdo_full, h * DH + c * 64, q0, b);
-        tma_load_3d(sDO + c * CHUNK_BYTES, &tmDO, qdo_full, h * DH + c * 64, q0, b);
-      }
+      for (int c = 0; c < CHUNKS; ++c)
+        tma_load_3d(sDO + c * CHUNK_BYTES, &tmDO, do_full, h * DH + c * 64, q0, b);
       for (int j = 0; j < nkv; ++j) {
-        const int s = j & 1;
-        if (!mbar_wait(&kv_empty[s], (uint32_t)(((j >> 1) & 1) ^ 1))) { atomicExch(p.err, 31); break; }
+        const int s = j % NST;
+        if (!mbar_wait(&kv_empty[s], (uint32_t)(((j / NST) & 1) ^ 1))) { atomicExch(p.err, 31); break; }
         mbar_expect_tx(&kv_full[s], 2 * TILE_BYTES);
 #pragma unroll
         for (int c = 0; c < CHUNKS; ++c) {
@@ -401,74 +480,100 @@ fa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     }
   } else if (warp == 1) {
     if (elect_one()) {
-      // Same half-tile software pipeline as the dK/dV kernel, split over 64-key halves.
-      const uint32_t idesc_s = umma_idesc_bf16(T, 64, 0, 0);
+      // Phase pipeline, every MMA 128 x 128 x 16:
+      //   S_0 | dP_0 | S_1 | dP_1 | dQ_0 | S_2 | dP_2 | dQ_1 | ...
+      // S_{j+1} is issued once the softmax warps hold S_j in registers, dP_{j+1} once they hold
+      // dP_j, dQ_j once dS_j is written; nothing the tensor pipe runs next depends on the softmax
+      // work of the tile before it, so that work hides under a full tile of MMAs.
+      const uint32_t idesc_s = umma_idesc_bf16(T, T, 0, 0);
       const uint32_t idesc_g = umma_idesc_bf16(T, DH, 0, 1);
-      const uint32_t aQ = smem_u32(sQ), aDO = smem_u32(sDO);
       const uint32_t aK0 = smem_u32(sK), aV0 = smem_u32(sV);
-      auto issue_sdp = [&](int st, int hf) {  // S and dP for keys [64 hf, 64 hf + 64)
-        const uint32_t aK = aK0 + st * TILE_BYTES + hf * 8192, aV = aV0 + st * TILE_BYTES + hf * 8192;
+      auto issue_s = [&](int st) {
+        const uint32_t aK = aK0 + st * TILE_BYTES;
 #pragma unroll
         for (int c = 0; c < CHUNKS; ++c) {
-          const uint64_t da = umma_desc_kmajor(aQ + c * CHUNK_BYTES, 128);
           const uint64_t db = umma_desc_kmajor(aK + c * CHUNK_BYTES, 128);
 #pragma unroll
           for (int kk = 0; kk < 4; ++kk)
-            umma_bf16(tmem_base + S_COL + hf * 64, da + kk * 2, db + kk * 2, idesc_s, (c | kk) != 0);
+            umma_bf16_ts(tmem_base + S_COL, tmem_base + QA_COL + (c * 4 + kk) * 8, db + kk * 2,
+                         idesc_s, (c | kk) != 0);
         }
+        umma_commit(s_full);
+      };
+      const uint32_t aDO = smem_u32(sDO);
+      auto issue_dp = [&](int st) {
+        const uint32_t aV = aV0 + st * TILE_BYTES;
 #pragma unroll
         for (int c = 0; c < CHUNKS; ++c) {
           const uint64_t da = umma_desc_kmajor(aDO + c * CHUNK_BYTES, 128);
           const uint64_t db = umma_desc_kmajor(aV + c * CHUNK_BYTES, 128);
 #pragma unroll
           for (int kk = 0; kk < 4; ++kk)
-            umma_bf16(tmem_base + DP_COL + hf * 64, da + kk * 2, db + kk * 2, idesc_s, (c | kk) != 0);
+            umma_bf16(tmem_base + DP_COL, da + kk * 2, db + kk * 2, idesc_s, (c | kk) != 0);
         }
-        umma_commit(&sp_full[hf]);
+        umma_commit(dp_full);
       };
-      auto issue_dq = [&](int st, int hf, bool first) {
+      auto issue_dq = [&](int st, bool first) {
         const uint32_t aK = aK0 + st * TILE_BYTES;
 #pragma unroll
-        for (int kk = 0; kk < 4; ++kk) {
-          const uint64_t dbk = umma_desc_mn128(aK + (hf * 4 + kk) * 2048, CHUNK_BYTES);
-          umma_bf16_ts(tmem_base + DQ_COL, tmem_base + DP_COL + hf * 64 + kk * 8, dbk, idesc_g,
+        for (int kk = 0; kk < T / 16; ++kk) {
+          const uint64_t dbk = umma_desc_mn128(aK + kk * 2048, CHUNK_BYTES);
+          umma_bf16_ts(tmem_base + DQ_COL, tmem_base + DS_COL + kk * 8, dbk, idesc_g,
                        !first || kk != 0);
         }
+        umma_commit(dq_done);
       };
-      bool ok = mbar_wait(qdo_full, 0);
+      int tn = 0;
+      trace_ev(p, 0, tn, 0);
+      bool ok = mbar_wait(qa_ready, 0);
       if (!ok) atomicExch(p.err, 32);
+      trace_ev(p, 0, tn, 1);
+      if (ok && !mbar_wait(do_full, 0)) { atomicExch(p.err, 32); ok = false; }
       if (ok && !mbar_wait(&kv_full[0], 0)) { atomicExch(p.err, 33); ok = false; }
       if (ok) {
         tc_fence_after();
-        issue_sdp(0, 0);
-        issue_sdp(0, 1);
+        issue_s(0);
+        issue_dp(0);
       }
       for (int j = 0; j < nkv && ok; ++j) {
-        const int s = j & 1;
+        const int s = j % NST, sn = (j + 1) % NST;
         const uint32_t par = (uint32_t)(j & 1);
         const bool more = j + 1 < nkv;
-        if (!mbar_wait(&ds_ready[0], par)) { atomicExch(p.err, 34); ok = false; break; }
-        tc_fence_after();
-        issue_dq(s, 0, j == 0);
         if (more) {
-          if (!mbar_wait(&kv_full[s ^ 1], (uint32_t)(((j + 1) >> 1) & 1))) {
+          if (!mbar_wait(&kv_full[sn], (uint32_t)(((j + 1) / NST) & 1))) {
             atomicExch(p.err, 33);
             ok = false;
             break;
           }
+          trace_ev(p, 0, tn, 2);
+          if (!mbar_wait(s_read, par)) { atomicExch(p.err, 38); ok = false; break; }
+          trace_ev(p, 0, tn, 3);
           tc_fence_after();
-          issue_sdp(s ^ 1, 0);
+          issue_s(sn);
+          trace_ev(p, 0, tn, 4);
+          if (!mbar_wait(dp_read, par)) { atomicExch(p.err, 40); ok = false; break; }
+          tc_fence_after();
+          issue_dp(sn);
+          trace_ev(p, 0, tn, 7);
         }
-        if (!mbar_wait(&ds_ready[1], par)) { atomicExch(p.err, 37); ok = false; break; }
+        if (!mbar_wait(ds_ready, par)) { atomicExch(p.err, 34); ok = false; break; }
+        trace_ev(p, 0, tn, 5);
         tc_fence_after();
-        issue_dq(s, 1, false);
+        issue_dq(s, j == 0);
         umma_commit(&kv_empty[s]);
-        if (more) issue_sdp(s ^ 1, 1);
+        trace_ev(p, 0, tn, 6);
       }
       if (ok) umma_commit(acc_done);
     }
   } else {
+    // Sixteen softmax warps: warp (qd, c) owns TMEM lanes [32 qd, 32 qd + 32) (queries) and the
+    // 32-key chunk c of every tile. Phase 1 (after S): P = exp2(S c - lse2) into registers.
+    // Phase 2 (after dP): dS = P * (dP - delta), written over the chunk's first 16 dP columns as
+    // packed bf16 (the A operand of dQ += dS K).
     const int qd = warp & 3;
+    const int ew = warp - 2;
+    const int c = ew >> 2;
+    const int sub = c;
     const int row = q0 + qd * 32 + lane;
     const uint32_t lane_addr = tmem_base + ((uint32_t)(qd * 32) << 16);
     const size_t stat = ((size_t)b * p.H + h) * p.Lp + row;  // row < Lp always
@@ -477,65 +582,111 @@ fa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     const f32x2 sc2 = f2_pack(p.scale_log2, p.scale_log2);
     const f32x2 nl2 = f2_pack(-lse2, -lse2);
     const f32x2 dl2 = f2_pack(delta, delta);
-    for (int j = 0; j < nkv && ok; ++j) {
-      const int kv_left = p.Lk - j * T;
-#pragma unroll 1
-      for (int hf = 0; hf < 2; ++hf) {
-        if (!mbar_wait(&sp_full[hf], (uint32_t)(j & 1))) {
-          if (lane == 0) atomicExch(p.err, 35);
+    {
+      // Stage Q as a constant A operand: warp groups 0 and 1 copy one half of the row block
+      // each, every thread its own query row (= TMEM lane), straight from global memory.
+      const bf16* src = p.q + (((size_t)b * p.Lq + row) * p.H + h) * DH + (sub & 1) * (DH / 2);
+      const uint32_t dst = lane_addr + QA_COL + (sub & 1) * (DH / 4);
+#pragma unroll
+      for (int w = 0; w < (sub < 2 ? DH / 64 : 0); ++w) {
+        uint32_t v[16];
+        if (row < p.Lq) {
+          const uint4* s4 = reinterpret_cast<const uint4*>(src + w * 32);
+#pragma unroll
+          for (int t = 0; t < 4; ++t) {
+            const uint4 u = s4[t];
+            v[4 * t] = u.x; v[4 * t + 1] = u.y; v[4 * t + 2] = u.z; v[4 * t + 3] = u.w;
+          }
+        } else {
+#pragma unroll
+          for (int t = 0; t < 16; ++t) v[t] = 0u;
+        }
+        tmem_st16(dst + w * 16, v);
+      }
+      tmem_st_wait();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(qa_ready);
+    }
+    int tn = 0;
+    const int rec = (ew == 0 && lane == 0) ? 1 : -1;
+    for (int j = 0; j < nkv; ++j) {
+      const int kv_left = p.Lk - j * T - c * 32;  // valid keys in this warp's chunk
+      if (rec > 0) trace_ev(p, rec, tn, 10);
+      if (!mbar_wait(s_full, (uint32_t)(j & 1))) {
+        if (lane == 0) atomicExch(p.err, 35);
+        ok = false;
+        break;
+      }
+      if (rec > 0) trace_ev(p, rec, tn, 11);
+      tc_fence_after();
+      f32x2 pr[16];
+      {
+        uint32_t r[32];
+        tmem_ld32(lane_addr + S_COL + c * 32, r);
+        tmem_ld_wait();
+        if (rec > 0) trace_ev(p, rec, tn, 12);
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(s_read);  // S is in registers: the next S may overwrite it
+        if (kv_left >= 32) {
+#pragma unroll
+          for (int x = 0; x < 16; ++x) {
+            f32x2 v = f2_fma(f2_pack_bits(r[2 * x], r[2 * x + 1]), sc2, nl2);
+            if (x < 16 - POLY) {
+              float lo, hi;
+              f2_unpack(v, lo, hi);
+              v = f2_pack(ex2_mufu(lo), ex2_mufu(hi));
+            } else {
+              v = ex2_poly2(v);
+            }
+            pr[x] = v;
+          }
+        } else {
+#pragma unroll
+          for (int x = 0; x < 16; ++x) {
+            float p0 = exp2f(fmaf(__uint_as_float(r[2 * x]), p.scale_log2, -lse2));
+            float p1 = exp2f(fmaf(__uint_as_float(r[2 * x + 1]), p.scale_log2, -lse2));
+            if (2 * x >= kv_left) p0 = 0.f;
+            if (2 * x + 1 >= kv_left) p1 = 0.f;
+            pr[x] = f2_pack(p0, p1);
+          }
+        }
+      }
+      if (rec > 0) trace_ev(p, rec, tn, 13);
+      if (!mbar_wait(dp_full, (uint32_t)(j & 1))) {
+        if (lane == 0) atomicExch(p.err, 39);
+        ok = false;
+        break;
+      }
+      if (rec > 0) trace_ev(p, rec, tn, 14);
+      tc_fence_after();
+      {
+        uint32_t g[32];
+        tmem_ld32(lane_addr + DP_COL + c * 32, g);
+        tmem_ld_wait();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(dp_read);  // dP is in registers: the next dP may overwrite it
+        if (rec > 0) trace_ev(p, rec, tn, 15);
+        uint32_t dk_[16];
+#pragma unroll
+        for (int x = 0; x < 16; ++x)
+          dk_[x] = f2_to_bf162(f2_mul(pr[x], f2_sub(f2_pack_bits(g[2 * x], g[2 * x + 1]), dl2)));
+        // dS_{j-1} must have been consumed by dQ_{j-1} before its columns are overwritten
+        if (j > 0 && !mbar_wait(dq_done, (uint32_t)((j - 1) & 1))) {
+          if (lane == 0) atomicExch(p.err, 41);
           ok = false;
           break;
         }
         tc_fence_after();
-        if (kv_left >= T) {
-#pragma unroll 1
-          for (int cc = 0; cc < 2; ++cc) {
-            const int c = hf * 2 + cc;
-            uint32_t r[32], g[32];
-            tmem_ld32(lane_addr + S_COL + c * 32, r);
-            tmem_ld32(lane_addr + DP_COL + c * 32, g);
-            tmem_ld_wait();
-            uint32_t dk_[16];
-#pragma unroll
-            for (int x = 0; x < 16; ++x) {
-              f32x2 v = f2_fma(f2_pack_bits(r[2 * x], r[2 * x + 1]), sc2, nl2);
-              if (x < 16 - POLY) {
-                float lo, hi;
-                f2_unpack(v, lo, hi);
-                v = f2_pack(ex2_mufu(lo), ex2_mufu(hi));
-              } else {
-                v = ex2_poly2(v);
-              }
-              dk_[x] = f2_to_bf162(f2_mul(v, f2_sub(f2_pack_bits(g[2 * x], g[2 * x + 1]), dl2)));
-            }
-            tmem_st16(lane_addr + DP_COL + hf * 64 + cc * 16, dk_);
-          }
-        } else {
-#pragma unroll 1
-          for (int cc = 0; cc < 2; ++cc) {
-            const int c = hf * 2 + cc;
-            uint32_t r[32], g[32];
-            tmem_ld32(lane_addr + S_COL + c * 32, r);
-            tmem_ld32(lane_addr + DP_COL + c * 32, g);
-            tmem_ld_wait();
-            uint32_t dk_[16];
-#pragma unroll
-            for (int x = 0; x < 16; ++x) {
-              float p0 = exp2f(fmaf(__uint_as_float(r[2 * x]), p.scale_log2, -lse2));
-              float p1 = exp2f(fmaf(__uint_as_float(r[2 * x + 1]), p.scale_log2, -lse2));
-              if (c * 32 + 2 * x >= kv_left) p0 = 0.f;
-              if (c * 32 + 2 * x + 1 >= kv_left) p1 = 0.f;
-              float d0 = p0 * (__uint_as_float(g[2 * x]) - delta);
-              float d1 = p1 * (__uint_as_float(g[2 * x + 1]) - delta);
-              dk_[x] = pack_bf162(d0, d1);
-            }
-            tmem_st16(lane_addr + DP_COL + hf * 64 + cc * 16, dk_);
-          }
-        }
+        tmem_st16(lane_addr + DS_COL + c * 16, dk_);
+        if (rec > 0) trace_ev(p, rec, tn, 16);
         tmem_st_wait();
+        if (rec > 0) trace_ev(p, rec, tn, 17);
         tc_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive(&ds_ready[hf]);
+        if (lane == 0) mbar_arrive(ds_ready);
       }
     }
     if (ok && !mbar_wait(acc_done, 0)) {
@@ -546,7 +697,7 @@ fa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       tc_fence_after();
       const size_t obase = (((size_t)b * p.Lq + row) * p.H + h) * DH;
 #pragma unroll 1
-      for (int c = 0; c < DH / 32; ++c) {
+      for (int c = sub; c < DH / 32; c += 4) {
         uint32_t r[32];
         tmem_ld32(lane_addr + DQ_COL + c * 32, r);
         tmem_ld_wait();
@@ -572,6 +723,9 @@ fa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
 }
 
 int* g_fab_err = nullptr;
+long long* g_fab_trace = nullptr;
+int g_fab_trace_cap = 0;
+int g_fab_trace_kernel = 0;  // 0: dQ kernel, 1: dK/dV kernel
 
 int make_map(CUtensorMap* m, const void* ptr, int B, int L, int H, int DH) {
   uint64_t dims[3] = {(uint64_t)H * DH, (uint64_t)L, (uint64_t)B};
@@ -584,19 +738,22 @@ template <int DH, int POLY>
 int launch_bwd_v(const CUtensorMap& q, const CUtensorMap& k, const CUtensorMap& v,
                  const CUtensorMap& d, const FaBwdParams& p, cudaStream_t st) {
   constexpr int SMEM = 6 * 128 * 128 * (DH / 64) + 2048 + 1024 + 128;
+  constexpr int SMEM_DQ = 7 * 128 * 128 * (DH / 64) + 1024 + 256;  // 3 K/V stages + dO + barriers
   static bool configured = false;
   if (!configured) {
     if (cudaFuncSetAttribute(fa_bwd_dkdv_kernel<DH, POLY>,
                              cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess)
       return -5;
     if (cudaFuncSetAttribute(fa_bwd_dq_kernel<DH, POLY>,
-                             cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess)
+                             cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_DQ) != cudaSuccess)
       return -5;
     configured = true;
   }
   dim3 g1((p.Lk + T - 1) / T, p.H, p.B), g2((p.Lq + T - 1) / T, p.H, p.B);
-  fa_bwd_dkdv_kernel<DH, POLY><<<g1, 192, SMEM, st>>>(q, k, v, d, p);
-  fa_bwd_dq_kernel<DH, POLY><<<g2, 192, SMEM, st>>>(q, k, v, d, p);
+  FaBwdParams p1 = p, p2 = p;
+  if (g_fab_trace_kernel == 0) p1.trace = nullptr; else p2.trace = nullptr;
+  fa_bwd_dkdv_kernel<DH, POLY><<<g1, 576, SMEM, st>>>(q, k, v, d, p1);
+  fa_bwd_dq_kernel<DH, POLY><<<g2, 576, SMEM_DQ, st>>>(q, k, v, d, p2);
   return (int)cudaGetLastError();
 }
 
@@ -606,8 +763,8 @@ int bwd_poly_pairs() {
   static int v = -1;
   if (v < 0) {
     const char* e = getenv("ERI_B200_FA_BWD_POLY");
-    v = e ? atoi(e) : 8;
-    if (v != 0 && v != 4 && v != 8) v = 8;
+    v = e ? atoi(e) : 4;
+    if (v != 0 && v != 4 && v != 8) v = 4;
   }
   return v;
 }
@@ -633,6 +790,17 @@ int eri_fa_bwd_check_error() {
   return h;
 }
 
+// Timeline tracing for performance work: `buf` holds 2 * cap int64 entries (first half: the
+// MMA-issuing thread, second half: lane 0 of the first softmax warp, both of CTA (0,0,0) of the
+// dQ kernel (which_kernel = 0) or the dK/dV kernel (1)), each (clock64 << 8) | event code. Pass
+// nullptr to switch tracing off.
+int eri_fa_bwd_set_trace(long long* buf, int cap, int which_kernel) {
+  g_fab_trace = buf;
+  g_fab_trace_cap = buf ? cap : 0;
+  g_fab_trace_kernel = which_kernel;
+  return 0;
+}
+
 // All tensors contiguous bf16 [B, L, H, DH]; lse [B, H, Lq] fp32 from the forward.
 // Scratch supplied by the caller: lse2 and delta, each [B, H, Lp] fp32 with Lp = ceil(Lq/128)*128.
 int eri_flash_attn_bwd(const void* dout, const void* q, const void* k, const void* v,
@@ -650,7 +818,7 @@ int eri_flash_attn_bwd(const void* dout, const void* q, const void* k, const voi
   {
     const long long warps = (long long)B * H * Lp;
     const int block = 256;
-    const long long grid = (warps * 32 + block - 1) / block;
+    const long long grid = (warps * 16 + block - 1) / block;
     fa_bwd_prep_kernel<<<(unsigned)grid, block, 0, st>>>((const bf16*)out, (const bf16*)dout, lse,
                                                          lse2, delta, B, H, Lq, Lp, DH);
   }
@@ -661,7 +829,8 @@ int eri_flash_attn_bwd(const void* dout, const void* q, const void* k, const voi
   FaBwdParams p;
   p.B = B; p.H = H; p.Lq = Lq; p.Lk = Lk; p.Lp = Lp;
   p.scale = scale; p.scale_log2 = scale * 1.4426950408889634f;
-  p.lse2 = lse2; p.delta = delta;
+  p.lse2 = lse2; p.delta = delta; p.q = (const bf16*)q; p.dout = (const bf16*)dout;
+  p.trace = g_fab_trace; p.trace_cap = g_fab_trace_cap;
   p.dq = (bf16*)dq; p.dk = (bf16*)dk; p.dv = (bf16*)dv; p.err = g_fab_err;
   return DH == 128 ? launch_bwd<128>(tq, tk, tv, td, p, st) : launch_bwd<64>(tq, tk, tv, td, p, st);
 }
@@ -778,7 +947,7 @@ int eri_flash_attn_bwd_noalloc(const void* dout, const void* q, const void* k, c
   cudaStream_t st = (cudaStream_t)stream;
   {
     const int block = 256;
-    const long long grid = (rows * 32 + block - 1) / block;
+    const long long grid = (rows * 16 + block - 1) / block;
     fa_bwd_prep_kernel<<<(unsigned)grid, block, 0, st>>>((const bf16*)out, (const bf16*)dout, lse,
                                                          lse2, delta, B, H, Lq, Lp, DH);
   }
@@ -789,7 +958,8 @@ int eri_flash_attn_bwd_noalloc(const void* dout, const void* q, const void* k, c
   FaBwdParams p;
   p.B = B; p.H = H; p.Lq = Lq; p.Lk = Lk; p.Lp = Lp;
   p.scale = scale; p.scale_log2 = scale * 1.4426950408889634f;
-  p.lse2 = lse2; p.delta = delta;
+  p.lse2 = lse2; p.delta = delta; p.q = (const bf16*)q; p.dout = (const bf16*)dout;
+  p.trace = g_fab_trace; p.trace_cap = g_fab_trace_cap;
   p.dq = (bf16*)dq; p.dk = (bf16*)dk; p.dv = (bf16*)dv; p.err = g_fa_noalloc_status_addr[dev];
   return DH == 128 ? launch_bwd<128>(tq, tk, tv, td, p, st) : launch_bwd<64>(tq, tk, tv, td, p, st);
 }

@@ -37,10 +37,24 @@ __device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t by
       : "memory");
 }
 
+// eight bf16 -> four packed fp32 pairs and back
+__device__ __forceinline__ void unpack8_f2(const bf16x8& r, f32x2 (&p)[4]) {
+  const uint4 u = r.u;
+  p[0] = f2_pack_bits(u.x << 16, u.x & 0xffff0000u);
+  p[1] = f2_pack_bits(u.y << 16, u.y & 0xffff0000u);
+  p[2] = f2_pack_bits(u.z << 16, u.z & 0xffff0000u);
+  p[3] = f2_pack_bits(u.w << 16, u.w & 0xffff0000u);
+}
+__device__ __forceinline__ bf16x8 pack8_f2(const f32x2 (&p)[4]) {
+  bf16x8 o;
+  o.u = make_uint4(f2_to_bf162(p[0]), f2_to_bf162(p[1]), f2_to_bf162(p[2]), f2_to_bf162(p[3]));
+  return o;
+}
+
 constexpr int kBarBytes = 1024;  // room for 32 warps x 2 stages of mbarriers
 
 template <int VPL, bool BWD>
-__global__ void __launch_bounds__(BWD ? 256 : 512, 1) norm_rows_kernel(const NormArgs a) {
+__global__ void __launch_bounds__(BWD ? 256 : 384, 1) norm_rows_kernel(const NormArgs a) {
   extern __shared__ __align__(128) uint8_t smem[];
   constexpr int NT = BWD ? 2 : 1;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
@@ -78,13 +92,16 @@ __global__ void __launch_bounds__(BWD ? 256 : 512, 1) norm_rows_kernel(const Nor
       break;
     }
     const bf16x8* sx = reinterpret_cast<const bf16x8*>(ring + (size_t)st * NT * row_bytes);
-    bf16x8 rx[VPL], rg[BWD ? VPL : 1];
+    // fp32 math runs on packed pairs (one fma / add per two elements): the row is unpacked once
+    // into registers, so every later pass is pure FMA-pipe work.
+    f32x2 xs[VPL][4];
+    f32x2 gs[BWD ? VPL : 1][4];
 #pragma unroll
     for (int i = 0; i < VPL; ++i) {
       const int v = lane + 32 * i;
       if (v < nvec) {
-        rx[i] = sx[v];
-        if (BWD) rg[i] = sx[nvec + v];
+        unpack8_f2(sx[v], xs[i]);
+        if (BWD) unpack8_f2(sx[nvec + v], gs[i]);
       }
     }
     __syncwarp();
@@ -96,126 +113,120 @@ __global__ void __launch_bounds__(BWD ? 256 : 512, 1) norm_rows_kernel(const Nor
     const bf16x8* sc =
         a.scale ? reinterpret_cast<const bf16x8*>(a.scale + (size_t)b * a.mod_stride) : nullptr;
     bf16x8* orow = reinterpret_cast<bf16x8*>(a.out + (size_t)row * D);
+    const f32x2 zero2 = f2_pack(0.f, 0.f);
 
     if (!BWD) {
       const bf16x8* sh =
           a.shift ? reinterpret_cast<const bf16x8*>(a.shift + (size_t)b * a.mod_stride) : nullptr;
-      float s = 0.f;
+      f32x2 acc = zero2;
 #pragma unroll
       for (int i = 0; i < VPL; ++i)
         if (lane + 32 * i < nvec) {
-          float f[8];
-          unpack8(rx[i], f);
 #pragma unroll
-          for (int j = 0; j < 8; ++j) s += a.rms ? f[j] * f[j] : f[j];
+          for (int j = 0; j < 4; ++j) acc = a.rms ? f2_fma(xs[i][j], xs[i][j], acc) : f2_add(acc, xs[i][j]);
         }
-      s = warp_sum(s);
+      float lo, hi;
+      f2_unpack(acc, lo, hi);
+      const float s = warp_sum(lo + hi);
       float mean = 0.f, rstd;
       if (a.rms) {
         rstd = rsqrtf(s * inv_d + a.eps);
       } else {
         mean = s * inv_d;
-        float q = 0.f;
+        const f32x2 m2 = f2_pack(mean, mean);
+        f32x2 q = zero2;
 #pragma unroll
         for (int i = 0; i < VPL; ++i)
           if (lane + 32 * i < nvec) {
-            float f[8];
-            unpack8(rx[i], f);
 #pragma unroll
-            for (int j = 0; j < 8; ++j) {
-              const float d = f[j] - mean;
-              q += d * d;
+            for (int j = 0; j < 4; ++j) {
+              const f32x2 d = f2_sub(xs[i][j], m2);
+              q = f2_fma(d, d, q);
             }
           }
-        rstd = rsqrtf(warp_sum(q) * inv_d + a.eps);
+        f2_unpack(q, lo, hi);
+        rstd = rsqrtf(warp_sum(lo + hi) * inv_d + a.eps);
       }
       if (lane == 0) {
         if (a.mean) a.mean[row] = mean;
         if (a.rstd) a.rstd[row] = rstd;
       }
+      const f32x2 a2 = f2_pack(rstd, rstd), b2 = f2_pack(-mean * rstd, -mean * rstd);
 #pragma unroll
       for (int i = 0; i < VPL; ++i) {
         const int v = lane + 32 * i;
         if (v < nvec) {
-          float o[8], t[8];
-          unpack8(rx[i], o);
+          f32x2 o[4], t[4];
 #pragma unroll
-          for (int j = 0; j < 8; ++j) o[j] = (o[j] - mean) * rstd;
+          for (int j = 0; j < 4; ++j) o[j] = f2_fma(xs[i][j], a2, b2);
           if (wv) {
-            unpack8(wv[v], t);
+            unpack8_f2(wv[v], t);
 #pragma unroll
-            for (int j = 0; j < 8; ++j) o[j] *= t[j];
+            for (int j = 0; j < 4; ++j) o[j] = f2_mul(o[j], t[j]);
           }
           if (bv) {
-            unpack8(bv[v], t);
+            unpack8_f2(bv[v], t);
 #pragma unroll
-            for (int j = 0; j < 8; ++j) o[j] += t[j];
+            for (int j = 0; j < 4; ++j) o[j] = f2_add(o[j], t[j]);
           }
           if (sc) {
-            unpack8(sc[v], t);
+            unpack8_f2(sc[v], t);
 #pragma unroll
-            for (int j = 0; j < 8; ++j) o[j] = fmaf(o[j], t[j], o[j]);
+            for (int j = 0; j < 4; ++j) o[j] = f2_fma(o[j], t[j], o[j]);
           }
           if (sh) {
-            unpack8(sh[v], t);
+            unpack8_f2(sh[v], t);
 #pragma unroll
-            for (int j = 0; j < 8; ++j) o[j] += t[j];
+            for (int j = 0; j < 4; ++j) o[j] = f2_add(o[j], t[j]);
           }
-          orow[v] = pack8(o);
+          orow[v] = pack8_f2(o);
         }
       }
     } else {
       const float mean = a.rms ? 0.f : a.mean[row];
       const float rstd = a.rstd[row];
-      // g = dy * (1 + scale) * weight, kept packed in rg (bf16 would lose bits: keep fp32 sums
-      // from the exact products and recompute the products in the output pass)
-      float s1 = 0.f, s2 = 0.f;
+      const f32x2 a2 = f2_pack(rstd, rstd), b2 = f2_pack(-mean * rstd, -mean * rstd);
+      // first pass: xs <- xhat, gs <- g = dy * (1 + scale) * weight, and the two row sums
+      f32x2 s1 = zero2, s2 = zero2;
 #pragma unroll
       for (int i = 0; i < VPL; ++i) {
         const int v = lane + 32 * i;
         if (v < nvec) {
-          float xx[8], g[8], t[8];
-          unpack8(rx[i], xx);
-          unpack8(rg[i], g);
-          if (sc) {
-            unpack8(sc[v], t);
+          f32x2 t[4];
 #pragma unroll
-            for (int j = 0; j < 8; ++j) g[j] = fmaf(g[j], t[j], g[j]);
+          for (int j = 0; j < 4; ++j) xs[i][j] = f2_fma(xs[i][j], a2, b2);
+          if (sc) {
+            unpack8_f2(sc[v], t);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) gs[i][j] = f2_fma(gs[i][j], t[j], gs[i][j]);
           }
           if (wv) {
-            unpack8(wv[v], t);
+            unpack8_f2(wv[v], t);
 #pragma unroll
-            for (int j = 0; j < 8; ++j) g[j] *= t[j];
+            for (int j = 0; j < 4; ++j) gs[i][j] = f2_mul(gs[i][j], t[j]);
           }
 #pragma unroll
-          for (int j = 0; j < 8; ++j) {
-            s1 += g[j];
-            s2 = fmaf(g[j], (xx[j] - mean) * rstd, s2);
+          for (int j = 0; j < 4; ++j) {
+            s1 = f2_add(s1, gs[i][j]);
+            s2 = f2_fma(gs[i][j], xs[i][j], s2);
           }
         }
       }
-      const float c1 = a.rms ? 0.f : warp_sum(s1) * inv_d;
-      const float c2 = warp_sum(s2) * inv_d;
+      float lo, hi;
+      f2_unpack(s1, lo, hi);
+      const float c1 = a.rms ? 0.f : warp_sum(lo + hi) * inv_d;
+      f2_unpack(s2, lo, hi);
+      const float c2 = warp_sum(lo + hi) * inv_d;
+      // dx = rstd * (g - c1 - xhat * c2)
+      const f32x2 k0 = f2_pack(-c1 * rstd, -c1 * rstd), k2 = f2_pack(-c2 * rstd, -c2 * rstd);
 #pragma unroll
       for (int i = 0; i < VPL; ++i) {
         const int v = lane + 32 * i;
         if (v < nvec) {
-          float xx[8], g[8], t[8], o[8];
-          unpack8(rx[i], xx);
-          unpack8(rg[i], g);
-          if (sc) {
-            unpack8(sc[v], t);
+          f32x2 o[4];
 #pragma unroll
-            for (int j = 0; j < 8; ++j) g[j] = fmaf(g[j], t[j], g[j]);
-          }
-          if (wv) {
-            unpack8(wv[v], t);
-#pragma unroll
-            for (int j = 0; j < 8; ++j) g[j] *= t[j];
-          }
-#pragma unroll
-          for (int j = 0; j < 8; ++j) o[j] = rstd * (g[j] - c1 - (xx[j] - mean) * rstd * c2);
-          orow[v] = pack8(o);
+          for (int j = 0; j < 4; ++j) o[j] = f2_fma(xs[i][j], k2, f2_fma(gs[i][j], a2, k0));
+          orow[v] = pack8_f2(o);
         }
       }
     }
@@ -231,7 +242,7 @@ int launch_rows(const NormArgs& a, cudaStream_t st) {
   const int D = a.D;
   const int per_warp = 2 * NT * D * 2;
   int warps = (200 * 1024 - kBarBytes) / per_warp;
-  if (warps > (BWD ? 8 : 16)) warps = BWD ? 8 : 16;
+  if (warps > (BWD ? 8 : 12)) warps = BWD ? 8 : 12;
   if (warps < 1) return -100;
   const int smem = kBarBytes + warps * per_warp;
   const int vpl = ((D >> 3) + 31) / 32;

@@ -90,10 +90,23 @@ class BasicTransformerBlock(nn.Module):
         return self.ff_out(h, residual=x)
 
 
+class GroupNormAct(nn.GroupNorm):
+    """``nn.GroupNorm`` parameters (same state-dict keys) with the channels-last GroupNorm(+SiLU)
+    kernel as the forward; the result keeps the input's NCHW shape in channels-last format, which
+    is what the cuDNN convolutions that follow want."""
+
+    def __init__(self, groups, ch, eps, silu, dtype=None, device=None):
+        super().__init__(groups, ch, eps=eps, dtype=dtype, device=device)
+        self.silu = silu
+
+    def forward(self, x):
+        return F.group_norm_silu(x, self.weight, self.bias, self.num_groups, self.eps, self.silu)
+
+
 class Transformer2D(nn.Module):
     def __init__(self, ch, depth, cfg: SDXLConfig, dtype, device):
         super().__init__()
-        self.norm = nn.GroupNorm(cfg.groups, ch, eps=1e-6, dtype=dtype, device=device)
+        self.norm = GroupNormAct(cfg.groups, ch, 1e-6, False, dtype=dtype, device=device)
         self.proj_in = Linear(ch, ch, dtype=dtype, device=device)
         self.blocks = nn.ModuleList(BasicTransformerBlock(ch, cfg.context_dim, cfg.head_dim, dtype, device)
                                     for _ in range(depth))
@@ -112,17 +125,17 @@ class Transformer2D(nn.Module):
 class ResBlock(nn.Module):
     def __init__(self, cin, cout, temb, cfg, dtype, device):
         super().__init__()
-        self.norm1 = nn.GroupNorm(cfg.groups, cin, eps=1e-5, dtype=dtype, device=device)
+        self.norm1 = GroupNormAct(cfg.groups, cin, 1e-5, True, dtype=dtype, device=device)
         self.conv1 = nn.Conv2d(cin, cout, 3, padding=1, dtype=dtype, device=device)
         self.temb = nn.Linear(temb, cout, dtype=dtype, device=device)
-        self.norm2 = nn.GroupNorm(cfg.groups, cout, eps=1e-5, dtype=dtype, device=device)
+        self.norm2 = GroupNormAct(cfg.groups, cout, 1e-5, True, dtype=dtype, device=device)
         self.conv2 = nn.Conv2d(cout, cout, 3, padding=1, dtype=dtype, device=device)
         self.skip = nn.Conv2d(cin, cout, 1, dtype=dtype, device=device) if cin != cout else None
 
     def forward(self, x, emb):
-        h = self.conv1(TF.silu(self.norm1(x)))
+        h = self.conv1(self.norm1(x))                                       # GroupNorm + SiLU fused
         h = h + self.temb(TF.silu(emb))[:, :, None, None]
-        h = self.conv2(TF.silu(self.norm2(h)))
+        h = self.conv2(self.norm2(h))
         return (x if self.skip is None else self.skip(x)) + h
 
 
@@ -170,7 +183,7 @@ class SDXLUNet(nn.Module):
             if lvl > 0:
                 self.up.append(nn.Conv2d(c, c, 3, padding=1, **kw))
                 self.up_kinds.append("up")
-        self.norm_out = nn.GroupNorm(cfg.groups, ch[0], eps=1e-5, **kw)
+        self.norm_out = GroupNormAct(cfg.groups, ch[0], 1e-5, True, **kw)
         self.conv_out = nn.Conv2d(ch[0], cfg.out_channels, 3, padding=1, **kw)
 
     def conditioning(self, t, pooled, time_ids):
@@ -204,7 +217,7 @@ class SDXLUNet(nn.Module):
             else:
                 h = m[0](torch.cat([h, hs.pop()], dim=1), emb)
                 h = m[1](h, ctx) if not isinstance(m[1], nn.Identity) else h
-        return self.conv_out(TF.silu(self.norm_out(h)))
+        return self.conv_out(self.norm_out(h))
 
     def lora_targets(self):
         return [r"\.attn[12]\.(to_qkv|to_q|to_kv|to_out)$", r"\.ff_(in|out)$"]

@@ -82,6 +82,15 @@ _SIGNATURES = {
     "eri_adamw32_step": [_P, _P, _P, _P, _P, _L, _I, _F, _F, _F, _F, _F, _I, _F, _F, _U32, _I, _P],
     "eri_ema_update": [_P, _P, _L, _F, _P],
     "eri_scale_bf16": [_P, _L, _P, _F, _F, _P],
+    "eri_gn_stats_fwd": [_P, _P, _I, _I, _I, _P],
+    "eri_gn_apply_fwd": [_P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P],
+    "eri_gn_stats_bwd": [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P],
+    "eri_gn_apply_bwd": [_P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P],
+    "eri_row_l2norm": [_P, _P, _L, _I, _P],
+    "eri_topk_desc": [_P, _P, _I, _I, _I, _P],
+    "eri_build_inverse": [_P, _P, _I, _I, _I, _P],
+    "eri_gather_rows": [_P, _P, _P, _I, _I, _I, _I, _P],
+    "eri_reinject_rows": [_P, _P, _P, _P, _I, _I, _I, _I, _P],
     "eri_gemm_init": [],
     "eri_gemm_check_error": [],
     "eri_gemm_bf16": [C.POINTER(GemmArgs), _P],

@@ -725,3 +725,171 @@ def sumsq(flat, out=None):
     else:
         out.add_(flat.float().pow(2).sum())
     return out
+
+
+# ---------------------------------------------------------------------------- GroupNorm (+SiLU)
+class _GroupNormSilu(torch.autograd.Function):
+    """x [N, HW, C] (channels-last rows). Two bandwidth-bound passes each way (csrc/groupnorm.cu);
+    the channel->group reductions between them run on the [N, C] statistics."""
+
+    @staticmethod
+    def forward(ctx, x, weight, bias, groups, eps, silu_flag):
+        Nn, HW, C = x.shape
+        x = _c(x)
+        lib = N.require()
+        stats = torch.zeros(Nn, C, 2, dtype=torch.float32, device=x.device)
+        N.check(lib.eri_gn_stats_fwd(x.data_ptr(), stats.data_ptr(), Nn, HW, C, N.stream_ptr()), "gn_stats_fwd")
+        m = HW * (C // groups)
+        gs = stats.view(Nn, groups, C // groups, 2).sum(2)
+        mean = gs[..., 0] / m
+        var = (gs[..., 1] / m - mean * mean).clamp_min_(0.0)
+        rstd = torch.rsqrt(var + eps)
+        mean, rstd = mean.contiguous(), rstd.contiguous()
+        y = torch.empty_like(x)
+        N.check(lib.eri_gn_apply_fwd(x.data_ptr(), weight.data_ptr(), N.ptr(bias), mean.data_ptr(),
+                                     rstd.data_ptr(), y.data_ptr(), Nn, HW, C, groups, int(silu_flag),
+                                     N.stream_ptr()), "gn_apply_fwd")
+        ctx.save_for_backward(x, weight, bias, mean, rstd)
+        ctx.meta = (groups, silu_flag)
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, weight, bias, mean, rstd = ctx.saved_tensors
+        groups, silu_flag = ctx.meta
+        Nn, HW, C = x.shape
+        dy = _c(dy)
+        lib = N.require()
+        stats = torch.zeros(Nn, C, 2, dtype=torch.float32, device=x.device)
+        N.check(lib.eri_gn_stats_bwd(x.data_ptr(), dy.data_ptr(), weight.data_ptr(), N.ptr(bias),
+                                     mean.data_ptr(), rstd.data_ptr(), stats.data_ptr(), Nn, HW, C, groups,
+                                     int(silu_flag), N.stream_ptr()), "gn_stats_bwd")
+        m = HW * (C // groups)
+        wf = weight.float()
+        ws = (stats * wf[None, :, None]).view(Nn, groups, C // groups, 2).sum(2) / m
+        s1, s2 = ws[..., 0].contiguous(), ws[..., 1].contiguous()
+        dx = torch.empty_like(x)
+        N.check(lib.eri_gn_apply_bwd(x.data_ptr(), dy.data_ptr(), weight.data_ptr(), N.ptr(bias),
+                                     mean.data_ptr(), rstd.data_ptr(), s1.data_ptr(), s2.data_ptr(),
+                                     dx.data_ptr(), Nn, HW, C, groups, int(silu_flag), N.stream_ptr()),
+                "gn_apply_bwd")
+        dw = stats[..., 1].sum(0).to(weight.dtype) if ctx.needs_input_grad[1] else None
+        db = stats[..., 0].sum(0).to(weight.dtype) if (bias is not None and ctx.needs_input_grad[2]) else None
+        return dx, dw, db, None, None, None
+
+
+def group_norm_silu(x, weight, bias=None, groups=32, eps=1e-5, silu=True):
+    """GroupNorm followed by an optional SiLU on a channels-last activation. ``x`` is either
+    [N, HW, C] or an [N, C, H, W] tensor in ``torch.channels_last`` memory format (returned in the
+    same logical shape and format)."""
+    nchw = x.dim() == 4
+    if nchw:
+        Nn, C, H, W = x.shape
+        rows = x.permute(0, 2, 3, 1)
+        if not rows.is_contiguous():
+            rows = rows.contiguous()
+        rows = rows.view(Nn, H * W, C)
+    else:
+        rows = x
+    C = rows.shape[-1]
+    if _native_ok(rows, weight, bias) and C % 8 == 0 and C % groups == 0 and C <= 8192:
+        y = _GroupNormSilu.apply(rows, weight, bias, groups, eps, silu)
+    else:
+        y = R.group_norm_silu(rows, weight, bias, groups, eps, silu)
+    if nchw:
+        return y.view(Nn, H, W, C).permute(0, 3, 1, 2)
+    return y
+
+
+# ---------------------------------------------------------------------------- token routing
+def token_scores(x):
+    """L2 norm of every token row of x [B, L, D] -> fp32 [B, L]."""
+    if _native_ok(x) and x.shape[-1] % 8 == 0:
+        x = _c(x)
+        out = torch.empty(x.shape[:-1], dtype=torch.float32, device=x.device)
+        N.check(N.require().eri_row_l2norm(x.data_ptr(), out.data_ptr(), out.numel(), x.shape[-1],
+                                           N.stream_ptr()), "row_l2norm")
+        return out
+    return x.float().norm(dim=-1)
+
+
+def topk_indices(scores, k):
+    """Indices [B, k] (int64) of the k largest non-negative scores per row, descending, ties by
+    lower index; selection runs on the device (no host sort)."""
+    B, L = scores.shape
+    if scores.is_cuda and _BACKEND == "fused" and L <= 16384 and scores.dtype == torch.float32:
+        idx = torch.empty(B, k, dtype=torch.int32, device=scores.device)
+        N.check(N.require().eri_topk_desc(_c(scores).data_ptr(), idx.data_ptr(), B, L, k, N.stream_ptr()), "topk")
+        return idx.long()
+    return scores.topk(k, dim=1).indices
+
+
+class _GatherRows(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, idx32):
+        B, L, D = x.shape
+        k = idx32.shape[1]
+        x = _c(x)
+        out = torch.empty(B, k, D, dtype=x.dtype, device=x.device)
+        N.check(N.require().eri_gather_rows(x.data_ptr(), idx32.data_ptr(), out.data_ptr(), B, L, k, D,
+                                            N.stream_ptr()), "gather_rows")
+        ctx.save_for_backward(idx32)
+        ctx.L = L
+        return out
+
+    @staticmethod
+    def backward(ctx, dy):
+        (idx32,) = ctx.saved_tensors
+        B, k, D = dy.shape
+        L = ctx.L
+        dy = _c(dy)
+        lib = N.require()
+        inv = torch.full((B, L), -1, dtype=torch.int32, device=dy.device)
+        N.check(lib.eri_build_inverse(idx32.data_ptr(), inv.data_ptr(), B, L, k, N.stream_ptr()), "build_inverse")
+        dx = torch.empty(B, L, D, dtype=dy.dtype, device=dy.device)
+        N.check(lib.eri_reinject_rows(None, dy.data_ptr(), inv.data_ptr(), dx.data_ptr(), B, L, k, D,
+                                      N.stream_ptr()), "scatter_rows")
+        return dx, None
+
+
+class _ReinjectRows(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, full, routed, idx32):
+        B, L, D = full.shape
+        k = idx32.shape[1]
+        full, routed = _c(full), _c(routed)
+        lib = N.require()
+        inv = torch.full((B, L), -1, dtype=torch.int32, device=full.device)
+        N.check(lib.eri_build_inverse(idx32.data_ptr(), inv.data_ptr(), B, L, k, N.stream_ptr()), "build_inverse")
+        out = torch.empty_like(full)
+        N.check(lib.eri_reinject_rows(full.data_ptr(), routed.data_ptr(), inv.data_ptr(), out.data_ptr(),
+                                      B, L, k, D, N.stream_ptr()), "reinject_rows")
+        ctx.save_for_backward(idx32, inv)
+        return out
+
+    @staticmethod
+    def backward(ctx, dy):
+        idx32, inv = ctx.saved_tensors
+        B, L, D = dy.shape
+        k = idx32.shape[1]
+        dy = _c(dy)
+        lib = N.require()
+        d_routed = torch.empty(B, k, D, dtype=dy.dtype, device=dy.device)
+        N.check(lib.eri_gather_rows(dy.data_ptr(), idx32.data_ptr(), d_routed.data_ptr(), B, L, k, D,
+                                    N.stream_ptr()), "gather_rows")
+        d_full = dy * (inv < 0).unsqueeze(-1).to(dy.dtype)
+        return d_full, d_routed, None
+
+
+def gather_rows(x, idx):
+    """x [B, L, D], idx [B, k] -> [B, k, D]."""
+    if _native_ok(x) and x.shape[-1] % 8 == 0:
+        return _GatherRows.apply(x, idx.to(torch.int32).contiguous())
+    return torch.gather(x, 1, idx.long().unsqueeze(-1).expand(-1, -1, x.shape[-1]))
+
+
+def reinject_rows(full, routed, idx):
+    """Copy of ``full`` [B, L, D] whose rows ``idx`` [B, k] are replaced by ``routed`` [B, k, D]."""
+    if _native_ok(full, routed) and full.shape[-1] % 8 == 0:
+        return _ReinjectRows.apply(full, routed, idx.to(torch.int32).contiguous())
+    return full.scatter(1, idx.long().unsqueeze(-1).expand(-1, -1, full.shape[-1]), routed)

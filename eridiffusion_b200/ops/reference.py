@@ -177,3 +177,13 @@ def mse(pred, target, weight=None):
     if weight is not None:
         d = d * weight.float().view(-1, *([1] * (d.dim() - 1)))
     return d.mean()
+
+
+def group_norm_silu(x, weight, bias=None, groups=32, eps=1e-5, silu=True):
+    """x [N, HW, C] channels-last rows -> GroupNorm over (HW, C/groups) (+ SiLU), fp32 math."""
+    Nn, HW, C = x.shape
+    xf = _f32(x).transpose(1, 2)                                   # [N, C, HW]
+    y = torch.nn.functional.group_norm(xf, groups, _f32(weight), None if bias is None else _f32(bias), eps)
+    if silu:
+        y = torch.nn.functional.silu(y)
+    return y.transpose(1, 2).to(x.dtype)

@@ -16,6 +16,8 @@ from __future__ import annotations
 import torch
 import torch.utils.checkpoint as ckpt
 
+from ..ops import functional as F
+
 
 class _OffloadStore:
     """Pinned-host parking lot for block inputs (one buffer per slot, reused every step)."""
@@ -124,8 +126,8 @@ def tread_select(x, k=None, k_frac=0.5, mask_type="topk_norm", gen=None):
     B, L, _ = x.shape
     k = k or max(1, int(L * k_frac))
     if mask_type in ("topk_norm", "attn_topk"):
-        score = x.float().pow(2).sum(-1)
-        idx = score.topk(k, dim=1).indices
+        # scoring and selection stay on the device (row-norm kernel + in-kernel bitonic top-k)
+        idx = F.topk_indices(F.token_scores(x), k)
     elif mask_type == "random":
         idx = torch.rand(B, L, device=x.device, generator=gen).topk(k, dim=1).indices
     elif mask_type == "uniform":
@@ -136,14 +138,14 @@ def tread_select(x, k=None, k_frac=0.5, mask_type="topk_norm", gen=None):
 
 
 def tread_gather(x, idx):
-    return x.gather(1, idx.unsqueeze(-1).expand(-1, -1, x.shape[-1]))
+    return F.gather_rows(x, idx)
 
 
 def tread_reinject(full, routed, idx, mode="scatter"):
     """Put the routed tokens back at their positions; the other positions keep the value they had
     when routing started (``scatter``) or are zeroed (``zero``)."""
     base = full if mode == "scatter" else torch.zeros_like(full)
-    return base.scatter(1, idx.unsqueeze(-1).expand(-1, -1, full.shape[-1]), routed)
+    return F.reinject_rows(base, routed, idx)
 
 
 class TreadRouter:
