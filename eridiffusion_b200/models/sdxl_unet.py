@@ -195,22 +195,39 @@ class SDXLUNet(nn.Module):
         ids = ids.view(time_ids.shape[0], -1).to(dt)
         return temb + self.add_embed(torch.cat([pooled.to(dt), ids], dim=-1))
 
-    def forward(self, x, t, ctx, pooled, time_ids):
-        """x [B, 4, H, W]; t [B] timesteps (0..999); ctx [B, 77, 2048]; pooled [B, 1280];
-        time_ids [B, 6] = (orig_h, orig_w, crop_y, crop_x, tgt_h, tgt_w)."""
-        emb = self.conditioning(t, pooled, time_ids)
+    def encode(self, x, emb, ctx, adapter_features=None):
+        """conv_in + down path + middle: returns (mid, skips). ``adapter_features`` (T2I-Adapter):
+        one tensor per resolution level, added to the last feature of that level."""
         h = self.conv_in(x.contiguous(memory_format=torch.channels_last))
         hs = [h]
+        level, in_level = 0, 0
+        per_level = self.cfg.layers_per_block
         for kind, m in zip(self.down_kinds, self.down):
             if kind == "down":
                 h = m(h)
+                level, in_level = level + 1, 0
             else:
                 h = m[0](h, emb)
                 h = m[1](h, ctx) if not isinstance(m[1], nn.Identity) else h
+                in_level += 1
+                if adapter_features is not None and in_level == per_level and level < len(adapter_features):
+                    h = h + adapter_features[level].to(h.dtype)
             hs.append(h)
         h = self.mid[0](h, emb)
         h = self.mid[1](h, ctx)
         h = self.mid[2](h, emb)
+        return h, hs
+
+    def forward(self, x, t, ctx, pooled, time_ids, control=None, adapter_features=None):
+        """x [B, 4, H, W]; t [B] timesteps (0..999); ctx [B, 77, 2048]; pooled [B, 1280];
+        time_ids [B, 6] = (orig_h, orig_w, crop_y, crop_x, tgt_h, tgt_w). ``control`` =
+        (skip residuals, mid residual) from a ControlNet; ``adapter_features`` from a T2I-Adapter."""
+        emb = self.conditioning(t, pooled, time_ids)
+        h, hs = self.encode(x, emb, ctx, adapter_features)
+        if control is not None:
+            down_res, mid_res = control
+            hs = [a + r.to(a.dtype) for a, r in zip(hs, down_res)]
+            h = h + mid_res.to(h.dtype)
         for kind, m in zip(self.up_kinds, self.up):
             if kind == "up":
                 h = m(TF.interpolate(h, scale_factor=2.0, mode="nearest"))
