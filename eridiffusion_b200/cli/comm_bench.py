@@ -61,6 +61,13 @@ def main():
 
     t_f = timed(fused)
     st = fdp.status()
+    fdp.enable_phase_timing()
+    dist.barrier()
+    torch.cuda.synchronize()
+    fused()
+    torch.cuda.synchronize()
+    phases = fdp.phase_times_us()
+    fdp.stamps = None
     # NCCL + separate kernels: reduce-scatter, norm all-reduce, optimizer on shard, all-gather
     p2 = [torch.nn.Parameter(torch.randn(n, device=dev).bfloat16() * 0.02)]
     arena2 = ParamArena(p2, shard_multiple=world)
@@ -84,7 +91,8 @@ def main():
                           "world": world, "params": n, "fused_ms": round(t_f, 4), "nccl_path_ms": round(t_n, 4),
                           "nvlink_bytes_per_direction": nbytes, "roofline_ms": round(roof_ms, 4),
                           "fraction_of_roofline": round(roof_ms / t_f, 3) if world > 1 else None,
-                          "link_gbs_used": LINK_GBS, "status": st}))
+                          "link_gbs_used": LINK_GBS, "status": st,
+                          "phases_us_rank0": {k: round(v, 1) for k, v in phases.items()}}))
     dist.barrier()
     dist.destroy_process_group()
 

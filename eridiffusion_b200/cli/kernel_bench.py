@@ -1,6 +1,6 @@
 """Per-kernel timing against the library equivalents and the measured roofline.
 
-    python -m eridiffusion_b200.cli.kernel_bench [--what gemm,attn,elementwise,optim] [--small]
+    python -m eridiffusion_b200.cli.kernel_bench [--what gemm,skinny,attn,elementwise,optim] [--small]
 
 Timing: CUDA events on the launching stream, >= 3 warm-up launches, L2 flushed between timed
 launches by writing a 256 MB buffer, median of the timed launches. Roofline denominators come from
@@ -76,6 +76,20 @@ def bench_gemm(small):
         print(f"{M:6d} {N:6d} {K:6d} | {t_ours*1e6:9.1f} {fl_/t_ours/1e12:7.1f} {fl_/t_ours/fl:6.2f} | "
               f"{t_lib*1e6:9.1f} {fl_/t_lib/1e12:7.1f} | {t_lora*1e6:9.1f} | B[K,N]: {t_mn*1e6:9.1f}   ({tag})")
     assert F.gemm_error_check() == 0
+
+
+def bench_skinny(small):
+    """LoRA down-projection shapes: [M, K] x [16, K]^T; bandwidth-bound on reading the activation."""
+    bw, fl, tag = peaks()
+    for M, K in ([(4608, 3072), (4608, 15360), (4608, 21504), (512, 3072)] if not small else [(1024, 2048)]):
+        a = torch.randn(M, K, device="cuda").bfloat16()
+        b = torch.randn(16, K, device="cuda").bfloat16()
+        t = timeit(lambda: F.skinny_gemm(a, b, alpha=0.5))
+        t0 = timeit(lambda: F.gemm_native(a, b, alpha=0.5))
+        t1 = timeit(lambda: torch.matmul(a, b.t()))
+        nb = a.numel() * 2
+        print(f"skinny [{M}x{K}]x[16x{K}]^T: split-K {t*1e6:.1f} us {nb/t/1e9:.0f} GB/s {nb/t/bw:.2f} {tag} | "
+              f"128-row tiles only {t0*1e6:.1f} us | cuBLAS {t1*1e6:.1f} us")
 
 
 def bench_elementwise(small):
@@ -156,7 +170,8 @@ def main():
     ap.add_argument("--small", action="store_true")
     a = ap.parse_args()
     for w in a.what.split(","):
-        {"gemm": bench_gemm, "elementwise": bench_elementwise, "optim": bench_optim, "attn": bench_attn}[w](a.small)
+        {"gemm": bench_gemm, "skinny": bench_skinny, "elementwise": bench_elementwise, "optim": bench_optim,
+         "attn": bench_attn}[w](a.small)
 
 
 if __name__ == "__main__":

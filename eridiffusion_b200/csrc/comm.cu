@@ -111,9 +111,14 @@ struct FusedDpArgs {
   uint32_t seed;
   int stochastic;
   float* grad_norm_out;   // optional: global gradient norm of this step
+  unsigned long long* stamps;  // optional: %globaltimer at the six phase boundaries (thread 0)
 };
 
-__global__ void __launch_bounds__(256)
+__device__ __forceinline__ void stamp(const FusedDpArgs& a, int i) {
+  if (a.stamps && blockIdx.x == 0 && threadIdx.x == 0) a.stamps[i] = globaltimer_ns();
+}
+
+__global__ void __launch_bounds__(256, 4)
 fused_dp_step_kernel(CommCtx c, FusedDpArgs a) {
   cg::grid_group grid = cg::this_grid();
   __shared__ float red[32];
@@ -125,7 +130,9 @@ fused_dp_step_kernel(CommCtx c, FusedDpArgs a) {
   const float inv_world = 1.f / (float)c.world;
 
   // phase 0: every rank's backward has finished writing its gradient arena
+  stamp(a, 0);
   cross_barrier(c, 0, grid);
+  stamp(a, 1);
 
   // phase 1: reduce-scatter (pull) into fp32 scratch + local sum of squares
   float ss = 0.f;
@@ -134,13 +141,28 @@ fused_dp_step_kernel(CommCtx c, FusedDpArgs a) {
     float acc[8];
 #pragma unroll
     for (int j = 0; j < 8; ++j) acc[j] = 0.f;
-    for (int i = 0; i < c.world; ++i) {
-      const int p = (c.rank + i) % c.world;  // start at self, stagger peers
-      const bf16* g = reinterpret_cast<const bf16*>(a.grads.ptr[p]) + shard_off + e;
-      float f[8];
-      unpack8(*reinterpret_cast<const bf16x8*>(g), f);
+    // issue every peer's 16-byte load before the first add, so that one NVLink round trip is
+    // paid per block instead of one per peer
+    for (int i0 = 0; i0 < c.world; i0 += 8) {
+      bf16x8 raw[8];
 #pragma unroll
-      for (int j = 0; j < 8; ++j) acc[j] += f[j];
+      for (int i = 0; i < 8; ++i) {
+        if (i0 + i < c.world) {
+          int p = c.rank + i0 + i;           // start at self, stagger peers
+          if (p >= c.world) p -= c.world;
+          raw[i] = *reinterpret_cast<const bf16x8*>(reinterpret_cast<const bf16*>(a.grads.ptr[p]) +
+                                                   shard_off + e);
+        }
+      }
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        if (i0 + i < c.world) {
+          float f[8];
+          unpack8(raw[i], f);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) acc[j] += f[j];
+        }
+      }
     }
     float4 o0, o1;
     o0.x = acc[0] * inv_world; o0.y = acc[1] * inv_world; o0.z = acc[2] * inv_world; o0.w = acc[3] * inv_world;
@@ -160,6 +182,7 @@ fused_dp_step_kernel(CommCtx c, FusedDpArgs a) {
     if (threadIdx.x == 0) atomicAdd(a.sumsq_local, t);
   }
   grid.sync();
+  stamp(a, 2);
 
   // phase 2: publish this shard's squared norm to every peer, then wait for all of them
   if (blockIdx.x == 0 && threadIdx.x < c.world) {
@@ -168,6 +191,7 @@ fused_dp_step_kernel(CommCtx c, FusedDpArgs a) {
     asm volatile("st.relaxed.sys.global.f32 [%0], %1;" ::"l"(slot), "f"(mine) : "memory");
   }
   cross_barrier(c, 1, grid);
+  stamp(a, 3);
   float total = 0.f;
   {
     const float* slots = reinterpret_cast<const float*>(a.sumsq_slots.ptr[c.rank]);
@@ -239,7 +263,9 @@ fused_dp_step_kernel(CommCtx c, FusedDpArgs a) {
     }
   }
   // phase 4: all ranks have pushed their shards (and finished reading every gradient arena)
+  stamp(a, 4);
   cross_barrier(c, 2, grid);
+  stamp(a, 5);
   if (blockIdx.x == 0 && threadIdx.x == 0) *a.sumsq_local = 0.f;
 }
 
@@ -334,7 +360,7 @@ int coop_grid(const void* fn, int& cache) {
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per, fn, 256, 0);
   if (per < 1) per = 1;
-  if (per > 2) per = 2;
+  if (per > 4) per = 4;
   cache = sms * per;
   return cache;
 }
@@ -395,6 +421,7 @@ struct EriFusedDpArgs {
   int step;
   unsigned int seed;
   int stochastic;
+  void* stamps;  // optional uint64[6]: device timer at the phase boundaries
 };
 
 int eri_fused_dp_step(const EriCommCtx* h, const EriFusedDpArgs* g, void* stream) {
@@ -416,6 +443,7 @@ int eri_fused_dp_step(const EriCommCtx* h, const EriFusedDpArgs* g, void* stream
   a.bc2 = 1.f - powf(g->beta2, (float)g->step);
   a.seed = g->seed * 2654435761u + g->step; a.stochastic = g->stochastic;
   a.grad_norm_out = (float*)g->grad_norm_out;
+  a.stamps = (unsigned long long*)g->stamps;
   const int grid = coop_grid((const void*)fused_dp_step_kernel, g_coop_blocks_fused);
   void* args[] = {&c, &a};
   return (int)cudaLaunchCooperativeKernel((const void*)fused_dp_step_kernel, dim3(grid), dim3(256),

@@ -401,6 +401,22 @@ def gemm_native(a, b, *, out=None, alpha=1.0, bias=None, lora_h=None, lora_b=Non
     return out
 
 
+def skinny_gemm(a, b, alpha=1.0):
+    """alpha * a[M, K] @ b[N, K]^T for N in {16, 32, 64} (LoRA rank): split-K tcgen05 kernel that
+    keeps every SM busy on a bandwidth-bound problem; other shapes use the general GEMM."""
+    M, K = a.shape
+    Nn = b.shape[0]
+    lib = N.require()
+    if hasattr(lib, "eri_gemm_skinny") and a.stride(1) == 1 and b.stride(1) == 1 and M >= 128:
+        out = torch.empty(M, Nn, dtype=torch.bfloat16, device=a.device)
+        code = lib.eri_gemm_skinny(a.data_ptr(), a.stride(0), b.data_ptr(), b.stride(0), out.data_ptr(),
+                                   Nn, M, Nn, K, float(alpha), N.stream_ptr())
+        if code != -100:
+            N.check(code, "gemm_skinny")
+            return out
+    return gemm_native(a, b, alpha=alpha)
+
+
 def gemm_supported(M, Nn, K) -> bool:
     return M >= 128 and Nn >= 16 and K >= 8 and K % 8 == 0 and Nn % 8 == 0
 
@@ -424,7 +440,7 @@ def kernel_error_check() -> dict:
     family's bounded waits ran out, and cleared by the read). Empty dict = clean."""
     lib = N.require()
     out = {}
-    for name in ("gemm", "gemm2", "fa", "fa_bwd", "norm"):
+    for name in ("gemm", "gemm2", "gemm_skinny", "fa", "fa_bwd", "norm"):
         fn = getattr(lib, f"eri_{name}_check_error", None)
         if fn is not None:
             v = fn()
@@ -471,7 +487,7 @@ class _FusedLinear(torch.autograd.Function):
             gate_v, _ = _mod_view(gate, Nn)
         if native:
             if r and lora_fused:
-                h = gemm_native(x2, lora_a, alpha=lora_scale)
+                h = skinny_gemm(x2, lora_a, alpha=lora_scale)
             elif r:
                 h = (x2 @ lora_a.t()) * lora_scale
             need_pre = act is not None and any(ctx.needs_input_grad[:5])
@@ -544,7 +560,7 @@ class _FusedLinear(torch.autograd.Function):
         if r:
             # Ts = s * dY B  [M, r]
             if native and r in (16, 32, 64):
-                ts = gemm_native(dy2, lora_b.t().contiguous(), alpha=s)
+                ts = skinny_gemm(dy2, lora_b.t().contiguous(), alpha=s)
             else:
                 ts = (dy2 @ lora_b) * s
         if need[0]:

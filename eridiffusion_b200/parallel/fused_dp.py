@@ -51,6 +51,7 @@ class FusedDataParallel:
         self.reduced = torch.empty(self.shard_elems, dtype=torch.float32, device=dev)
         self.sumsq_local = torch.zeros(1, dtype=torch.float32, device=dev)
         self.grad_norm = torch.zeros(1, dtype=torch.float32, device=dev)
+        self.stamps = None     # set by enable_phase_timing()
         assert optimizer.m_q.numel() == self.shard_elems, "optimizer state must cover this rank's shard"
         torch.cuda.synchronize()
         pg.barrier()
@@ -70,12 +71,23 @@ class FusedDataParallel:
         a.lr, (a.beta1, a.beta2), a.eps, a.weight_decay = lr, o.betas, o.eps, o.weight_decay
         a.max_grad_norm = max_grad_norm
         a.step, a.seed, a.stochastic = step, o.seed, int(o.stochastic_rounding)
+        a.stamps = self.stamps.data_ptr() if self.stamps is not None else None
         o.step_count = step
         c = self.comm.ctx()
         N.check(self.comm.lib.eri_fused_dp_step(C.byref(c), C.byref(a), N.stream_ptr()), "fused_dp_step")
 
     def status(self) -> int:
         return self.comm.status()
+
+    def enable_phase_timing(self):
+        """Record the device timer at the kernel's phase boundaries (thread 0 of CTA 0)."""
+        self.stamps = torch.zeros(8, dtype=torch.int64, device=self.arena.data.device)
+
+    def phase_times_us(self) -> dict:
+        """Durations of the last step's phases on this rank, in microseconds."""
+        t = self.stamps.cpu().tolist()
+        names = ["entry_barrier", "reduce_scatter", "norm_exchange", "adamw_and_push", "exit_barrier"]
+        return {n: (t[i + 1] - t[i]) / 1e3 for i, n in enumerate(names)}
 
     def bytes_over_nvlink_per_direction(self) -> int:
         return int(2 * (self.world - 1) / self.world * self.arena.numel * 2)

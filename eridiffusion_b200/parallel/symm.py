@@ -32,7 +32,7 @@ class FusedDpArgs(C.Structure):
                 ("shard_elems", C.c_longlong), ("lr", C.c_float), ("beta1", C.c_float),
                 ("beta2", C.c_float), ("eps", C.c_float), ("weight_decay", C.c_float),
                 ("max_grad_norm", C.c_float), ("step", C.c_int), ("seed", C.c_uint),
-                ("stochastic", C.c_int)]
+                ("stochastic", C.c_int), ("stamps", C.c_void_p)]
 
 
 class CollArgs(C.Structure):
