@@ -370,3 +370,29 @@ def merge_adapters(model: nn.Module):
                 mod.weight.add_(mod.adapter.delta_weight(mod).to(mod.weight.dtype))
             mod.adapter = None
             mod.drop_transpose()
+
+
+def load_adapters_into(model: nn.Module, path, alpha: float | None = None, strict: bool = True):
+    """Attach LoRA adapters to ``model`` from a checkpoint file in any supported key layout: the
+    rank is read from the first down-projection tensor, ``alpha`` from the file when it carries
+    one (kohya layout), else it defaults to the rank. Returns the adapter dict."""
+    from ..io import safetensors as st
+    sd = st.load_file(path)
+    down = next((v for k, v in sd.items() if k.endswith(("lora.A", "lora_A.weight", "lora_down.weight"))), None)
+    if down is None:
+        raise KeyError(f"{path}: no LoRA down-projection tensor found")
+    rank = int(down.shape[0])
+    if alpha is None:
+        a = next((v for k, v in sd.items() if k.endswith(".alpha")), None)
+        alpha = float(a) if a is not None else float(rank)
+    dtype = next(model.parameters()).dtype
+    adapters = inject_adapters(model, AdapterConfig(rank=rank, alpha=alpha, dtype=dtype))
+    # only the adapted sites present in the file are kept (a checkpoint may cover a subset)
+    present = {p for p in adapters
+               if any(p in k or p.replace(".", "_") in k for k in sd)}
+    for p in list(adapters):
+        if p not in present:
+            dict(model.named_modules())[p].adapter = None
+            del adapters[p]
+    load_adapter_state_dict(adapters, sd, strict=strict)
+    return adapters

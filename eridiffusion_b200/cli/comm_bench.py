@@ -1,27 +1,42 @@
 """Multi-GPU timing of the fused communication paths against their rooflines and against NCCL.
 
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 \
-        -m eridiffusion_b200.cli.comm_bench [--params 56000000]
+        -m eridiffusion_b200.cli.comm_bench [--what fused_dp,zero3,ulysses] [--params 56000000]
 
 Times are CUDA-event device times, max over ranks, median of the timed launches after warm-up.
-Roofline of the fused data-parallel step: bytes that must cross NVLink per direction,
-``2 * (W-1)/W * arena_bytes``, over the measured 770 GB/s per direction (900 nominal).
+Rooflines (the slower of the two bounds is the target, as for any fused compute + collective):
+
+* fused data-parallel step: bytes that must cross NVLink per direction, ``2 * (W-1)/W *
+  arena_bytes``, over the measured 770 GB/s per direction (900 nominal);
+* ZeRO-3 gather-in-GEMM (Qwen-Image shapes, weight rows sharded): max(GEMM FLOPs / measured cuBLAS
+  peak, (W-1)/W * weight bytes / 770 GB/s);
+* Ulysses QKV projection with scatter epilogue and out-projection with gathered A operand (LTX
+  shapes, 19008 tokens over W ranks): max(GEMM FLOPs / peak, (W-1)/W * activation bytes / 770 GB/s).
 """
 from __future__ import annotations
 
 import argparse
 import json
 import statistics
+from pathlib import Path
 
 import torch
 import torch.distributed as dist
 
+from ..models.layers import Linear
 from ..ops import functional as F
 from ..optim import AdamW8bit, ParamArena
 from ..parallel.dist import GradSync, ProcessGroup, init_from_env
 from ..parallel.fused_dp import FusedDataParallel
 
 LINK_GBS = 770.0
+
+
+def gemm_peak():
+    p = Path(__file__).resolve().parents[2] / "MEASURED_PEAKS.json"
+    if p.exists():
+        return json.loads(p.read_text())["bf16_tflops"] * 1e12, "measured"
+    return 1.59e15, "fallback"
 
 
 def timed(fn, iters=10, warm=3):
@@ -40,13 +55,7 @@ def timed(fn, iters=10, warm=3):
     return t.item()
 
 
-def main():
-    ap = argparse.ArgumentParser()
-    ap.add_argument("--params", type=int, default=56_000_000)
-    a = ap.parse_args()
-    rank, world, local = init_from_env()
-    dev = torch.device("cuda", local)
-    pg = ProcessGroup()
+def bench_fused_dp(a, pg, rank, world, dev):
     n = a.params // (256 * world) * (256 * world)
     p = [torch.nn.Parameter(torch.randn(n, device=dev).bfloat16() * 0.02)]
     arena = ParamArena(p, shard_multiple=world)
@@ -86,14 +95,122 @@ def main():
     if rank == 0:
         nbytes = fdp.bytes_over_nvlink_per_direction()
         roof_ms = nbytes / (LINK_GBS * 1e9) * 1e3
-        hbm_ms = 0.0
         print(json.dumps({"what": "fused_dp_step (reduce-scatter + clip + adamw8bit + all-gather)",
                           "world": world, "params": n, "fused_ms": round(t_f, 4), "nccl_path_ms": round(t_n, 4),
                           "nvlink_bytes_per_direction": nbytes, "roofline_ms": round(roof_ms, 4),
                           "fraction_of_roofline": round(roof_ms / t_f, 3) if world > 1 else None,
                           "link_gbs_used": LINK_GBS, "status": st,
                           "phases_us_rank0": {k: round(v, 1) for k, v in phases.items()}}))
-    dist.barrier()
+
+
+def bench_zero3(a, pg, rank, world, dev):
+    """Forward of a row-sharded Linear (Qwen-Image MLP up-projection 3072 -> 12288, QKV
+    3072 -> 9216 and MLP down-projection 12288 -> 3072 at 4096 + 512 tokens): the weight gather
+    runs inside the GEMM launch."""
+    from ..parallel.zero3 import Zero3Context, Zero3Linear
+    peak, tag = gemm_peak()
+    z3 = Zero3Context(pg, heap_bytes=512 << 20, max_weight_elems=48 << 20, n_copy=a.n_copy)
+    M = 4608
+    for n_out, k_in in ((12288, 3072), (9216, 3072), (3072, 12288)):
+        torch.manual_seed(0)
+        lin = Linear(k_in, n_out, bias=False, device=dev)
+        zl = Zero3Linear(lin, z3)
+        shard = z3.arena_alloc(zl.weight.numel(), torch.bfloat16, dev).view_as(zl.weight)
+        shard.copy_(zl.weight.data)
+        zl.weight.data = shard
+        z3.barrier()
+        x = torch.randn(1, M, k_in, device=dev).bfloat16()
+        full = torch.empty(n_out, k_in, device=dev, dtype=torch.bfloat16)
+
+        def fused():
+            with torch.no_grad():
+                zl(x)
+
+        def nccl():
+            with torch.no_grad():
+                dist.all_gather_into_tensor(full, zl.weight.data)
+                F.linear(x, full)
+
+        t_f, t_n = timed(fused), timed(nccl)
+        flops = 2.0 * M * n_out * k_in
+        link_bytes = (world - 1) / world * n_out * k_in * 2
+        roof = max(flops / peak, link_bytes / (LINK_GBS * 1e9)) * 1e3
+        if rank == 0:
+            print(json.dumps({"what": f"zero3 gather-in-GEMM forward [{M}x{k_in}] x [{n_out}x{k_in}]^T", "world": world,
+                              "fused_ms": round(t_f, 4), "nccl_allgather_then_gemm_ms": round(t_n, 4),
+                              "gemm_bound_ms": round(flops / peak * 1e3, 4),
+                              "nvlink_bound_ms": round(link_bytes / (LINK_GBS * 1e9) * 1e3, 4),
+                              "roofline_ms": round(roof, 4), "fraction_of_roofline": round(roof / t_f, 3),
+                              "gemm_peak": tag, "status": z3.comm.status(), "gemm_err": F.gemm_error_check()}))
+
+
+def bench_ulysses(a, pg, rank, world, dev):
+    """LTX-shaped attention projections under sequence parallelism: hidden 4096, 32 heads, 19008
+    tokens over W ranks. QKV projection with the head scatter in its epilogue, and out-projection
+    whose A operand is gathered from the peers inside the launch."""
+    from ..parallel.ulysses import UlyssesContext, ulysses_out_proj, ulysses_qkv
+    peak, tag = gemm_peak()
+    D, H = 4096, 32
+    Ll = (19008 // world) // 128 * 128
+    u = UlyssesContext(pg, batch=1, l_local=Ll, hidden=D, heads=H, n_copy=a.n_copy)
+    torch.manual_seed(0)
+    qkv = Linear(D, 3 * D, bias=False, device=dev)
+    out = Linear(D, D, bias=False, device=dev)
+    x = torch.randn(1, Ll, D, device=dev).bfloat16()
+    attn = torch.randn(1, u.Lt, H // world, D // H, device=dev).bfloat16()
+    send = torch.empty(world, Ll, 3 * D // world, device=dev, dtype=torch.bfloat16)
+    recv = torch.empty_like(send)
+
+    def fused_qkv():
+        with torch.no_grad():
+            ulysses_qkv(x, qkv, u)
+
+    def nccl_qkv():
+        with torch.no_grad():
+            y = F.linear(x, qkv.weight)
+            send.copy_(y.view(Ll, world, 3 * D // world).transpose(0, 1))
+            dist.all_to_all_single(recv.view(-1), send.view(-1))
+
+    def fused_out():
+        with torch.no_grad():
+            ulysses_out_proj(attn, out, u)
+
+    send2 = torch.empty(world, Ll, D // world, device=dev, dtype=torch.bfloat16)
+    recv2 = torch.empty_like(send2)
+
+    def nccl_out():
+        with torch.no_grad():
+            send2.copy_(attn.view(world, Ll, D // world))
+            dist.all_to_all_single(recv2.view(-1), send2.view(-1))
+            F.linear(recv2.transpose(0, 1).reshape(1, Ll, D), out.weight)
+
+    for name, f_f, f_n, n_out, act_cols in (("qkv projection + head scatter", fused_qkv, nccl_qkv, 3 * D, 3 * D),
+                                             ("head gather + out projection", fused_out, nccl_out, D, D)):
+        t_f, t_n = timed(f_f), timed(f_n)
+        flops = 2.0 * Ll * n_out * D
+        link_bytes = (world - 1) / world * Ll * act_cols * 2
+        roof = max(flops / peak, link_bytes / (LINK_GBS * 1e9)) * 1e3
+        if rank == 0:
+            print(json.dumps({"what": f"ulysses {name}, {Ll} local tokens, hidden {D}", "world": world,
+                              "fused_ms": round(t_f, 4), "gemm_plus_nccl_all_to_all_ms": round(t_n, 4),
+                              "gemm_bound_ms": round(flops / peak * 1e3, 4),
+                              "nvlink_bound_ms": round(link_bytes / (LINK_GBS * 1e9) * 1e3, 4),
+                              "roofline_ms": round(roof, 4), "fraction_of_roofline": round(roof / t_f, 3),
+                              "gemm_peak": tag, "status": u.comm.status(), "gemm_err": F.gemm_error_check()}))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--params", type=int, default=56_000_000)
+    ap.add_argument("--what", default="fused_dp")
+    ap.add_argument("--n-copy", type=int, default=16, help="copy CTAs of the gather-fused GEMM launches")
+    a = ap.parse_args()
+    rank, world, local = init_from_env()
+    dev = torch.device("cuda", local)
+    pg = ProcessGroup()
+    for w in a.what.split(","):
+        {"fused_dp": bench_fused_dp, "zero3": bench_zero3, "ulysses": bench_ulysses}[w](a, pg, rank, world, dev)
+        dist.barrier()
     dist.destroy_process_group()
 
 

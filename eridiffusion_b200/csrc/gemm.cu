@@ -74,7 +74,9 @@ struct GemmParams {
   unsigned int* flags;        // per-slab counters (zeroed before the launch)
   const unsigned int* flag_target;
   int b_flag_rows;            // rows of B per slab (0: B is not gathered)
-  int a_flag_cols;            // K columns of A per slab (0: A is not gathered)
+  int a_flag_cols;            // K columns per counter of a K-gathered operand (0: none)
+  int a_flag_rows;            // >0: counters also split by row group of the A operand:
+  int a_row_groups;           //     index = (k / a_flag_cols) * a_row_groups + m0 / a_flag_rows
   int rot_n, rot_k;           // rotation of tile order / K order towards the local slab
   // peer scatter epilogue
   int scatter_world;          // 0: off
@@ -137,24 +139,139 @@ __device__ __forceinline__ bool wait_slab(const GemmParams& p, int f) {
   return false;
 }
 
-__device__ void copy_role(const GemmParams& p) {
-  for (int j = blockIdx.x; j < p.n_jobs; j += p.n_copy) {
-    const GatherJob job = p.jobs[j];
-    const int vec_per_row = job.row_bytes >> 4;
-    const long long total = (long long)job.rows * vec_per_row;
-    for (long long i = threadIdx.x; i < total; i += blockDim.x) {
-      const long long r = i / vec_per_row;
-      const int c = (int)(i - r * vec_per_row);
-      const uint4 v = *reinterpret_cast<const uint4*>(reinterpret_cast<const char*>(job.src) +
-                                                      r * job.src_stride + (size_t)c * 16);
-      *reinterpret_cast<uint4*>(reinterpret_cast<char*>(job.dst) + r * job.dst_stride +
-                                (size_t)c * 16) = v;
+// Copy CTA: moves its jobs through a ring of shared-memory stages with bulk asynchronous copies
+// (peer or local global memory -> shared -> local landing buffer). Warp 0 issues the loads, one
+// row segment per lane, each stage completing on its own mbarrier; warp 1 issues the stores and
+// hands the stage back once the store has read it. With 32 KB stages the ring keeps up to
+// ring_stages * 32 KB of NVLink reads in flight per CTA (a 16-byte load per thread kept 3 KB in
+// flight and ran at ~1 GB/s per CTA). No multicast: every copy is a plain cp.async.bulk.
+constexpr int kCopyStageBytes = 32 * 1024;
+
+__device__ __forceinline__ void bulk_g2s_plain(uint32_t dst_smem, const void* src, uint32_t bytes,
+                                               uint32_t bar_smem) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::
+          "r"(dst_smem), "l"(src), "r"(bytes), "r"(bar_smem)
+      : "memory");
+}
+__device__ __forceinline__ void bulk_s2g_plain(void* dst, uint32_t src_smem, uint32_t bytes) {
+  asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(dst),
+               "r"(src_smem), "r"(bytes)
+               : "memory");
+}
+
+// A job is cut into chunks of whole rows (or, for a contiguous slab, of 32 KB pieces of one long
+// row); chunk c of a job covers rows [c * rpc, ...) or bytes [c * 32 KB, ...).
+struct CopyChunking {
+  bool flat;        // rows are back to back in both source and destination
+  long long total;  // flat: bytes of the job
+  int rpc;          // strided: rows per chunk
+  int nchunks;
+};
+__device__ __forceinline__ CopyChunking chunking(const GatherJob& job) {
+  CopyChunking k;
+  k.flat = job.src_stride == job.row_bytes && job.dst_stride == job.row_bytes;
+  k.total = (long long)job.rows * job.row_bytes;
+  if (k.flat) {
+    k.rpc = 0;
+    k.nchunks = (int)((k.total + kCopyStageBytes - 1) / kCopyStageBytes);
+  } else {
+    k.rpc = kCopyStageBytes / job.row_bytes;   // row_bytes <= 32 KB is checked on the host
+    k.nchunks = (job.rows + k.rpc - 1) / k.rpc;
+  }
+  return k;
+}
+
+__device__ void copy_role(const GemmParams& p, uint8_t* smem, int ring_stages) {
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + (size_t)ring_stages * kCopyStageBytes);
+  uint64_t* empty = full + ring_stages;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < ring_stages; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
     }
-    __syncthreads();
-    if (threadIdx.x == 0) {
-      __threadfence();
-      fence_proxy_async_all();
-      atomicAdd(p.flags + job.flag, 1u);
+    mbar_fence_init();
+  }
+  __syncthreads();
+  if (warp == 0) {
+    int it = 0;
+    bool ok = true;
+    for (int j = blockIdx.x; j < p.n_jobs && ok; j += p.n_copy) {
+      const GatherJob job = p.jobs[j];
+      if (job.src_stride != job.row_bytes && job.row_bytes > kCopyStageBytes) {
+        if (lane == 0) atomicExch(p.err, 63);   // a strided row must fit one ring stage
+        break;
+      }
+      const CopyChunking k = chunking(job);
+      for (int c = 0; c < k.nchunks && ok; ++c, ++it) {
+        const int s = it % ring_stages;
+        if (!mbar_wait(&empty[s], (uint32_t)(((it / ring_stages) & 1) ^ 1))) {
+          if (lane == 0) atomicExch(p.err, 61);
+          ok = false;
+          break;
+        }
+        const uint32_t dst = smem_u32(smem + (size_t)s * kCopyStageBytes);
+        const uint32_t bar = smem_u32(&full[s]);
+        if (k.flat) {
+          const long long off = (long long)c * kCopyStageBytes;
+          const uint32_t bytes = (uint32_t)min((long long)kCopyStageBytes, k.total - off);
+          if (lane == 0) {
+            mbar_expect_tx(&full[s], bytes);
+            bulk_g2s_plain(dst, reinterpret_cast<const char*>(job.src) + off, bytes, bar);
+          }
+        } else {
+          const int r0 = c * k.rpc, nr = min(k.rpc, job.rows - r0);
+          if (lane == 0) mbar_expect_tx(&full[s], (uint32_t)nr * (uint32_t)job.row_bytes);
+          __syncwarp();
+          for (int r = lane; r < nr; r += 32)
+            bulk_g2s_plain(dst + (uint32_t)r * (uint32_t)job.row_bytes,
+                           reinterpret_cast<const char*>(job.src) + (long long)(r0 + r) * job.src_stride,
+                           (uint32_t)job.row_bytes, bar);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    int it = 0;
+    bool ok = true;
+    for (int j = blockIdx.x; j < p.n_jobs && ok; j += p.n_copy) {
+      const GatherJob job = p.jobs[j];
+      if (job.src_stride != job.row_bytes && job.row_bytes > kCopyStageBytes) {
+        if (lane == 0) atomicExch(p.err, 63);   // a strided row must fit one ring stage
+        break;
+      }
+      const CopyChunking k = chunking(job);
+      for (int c = 0; c < k.nchunks && ok; ++c, ++it) {
+        const int s = it % ring_stages;
+        if (!mbar_wait(&full[s], (uint32_t)((it / ring_stages) & 1))) {
+          if (lane == 0) atomicExch(p.err, 62);
+          ok = false;
+          break;
+        }
+        const uint32_t src = smem_u32(smem + (size_t)s * kCopyStageBytes);
+        if (k.flat) {
+          const long long off = (long long)c * kCopyStageBytes;
+          const uint32_t bytes = (uint32_t)min((long long)kCopyStageBytes, k.total - off);
+          if (lane == 0) bulk_s2g_plain(reinterpret_cast<char*>(job.dst) + off, src, bytes);
+        } else {
+          const int r0 = c * k.rpc, nr = min(k.rpc, job.rows - r0);
+          for (int r = lane; r < nr; r += 32)
+            bulk_s2g_plain(reinterpret_cast<char*>(job.dst) + (long long)(r0 + r) * job.dst_stride,
+                           src + (uint32_t)r * (uint32_t)job.row_bytes, (uint32_t)job.row_bytes);
+        }
+        tma_store_commit();
+        tma_store_wait_read<0>();      // the stage has been read: the loader may refill it
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&empty[s]);
+      }
+      // the whole job has landed in local memory before its counter moves
+      tma_store_wait<0>();
+      __syncwarp();
+      if (lane == 0 && ok) {
+        __threadfence();
+        fence_proxy_async_all();
+        atomicAdd(p.flags + job.flag, 1u);
+      }
     }
   }
 }
@@ -170,16 +287,17 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   constexpr int TMEM_COLS = tmem_cols_for(BN);
   constexpr int CH = BN >= 32 ? 32 : 16;  // accumulator columns per TMEM load
 
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~uintptr_t(1023));
   if ((int)blockIdx.x < p.n_copy) {
-    copy_role(p);
+    // the copy ring reuses the operand stages' shared memory; its barriers sit where the GEMM's do
+    constexpr int RING = (STAGES * STAGE_BYTES) / kCopyStageBytes;
+    copy_role(p, smem, RING < 6 ? RING : 6);
     return;
   }
   const int worker = blockIdx.x - p.n_copy;
   const int nworkers = gridDim.x - p.n_copy;
-
-  extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
-                                             ~uintptr_t(1023));
   uint64_t* full = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
   uint64_t* empty = full + STAGES;
   uint64_t* acc_full = empty + STAGES;
@@ -250,7 +368,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             int kk = k + p.rot_k;
             if (kk >= p.num_k) kk -= p.num_k;
             if (p.a_flag_cols) {
-              const int f = (kk * BK) / p.a_flag_cols;
+              int f = (kk * BK) / p.a_flag_cols;
+              if (p.a_flag_rows) f = f * p.a_row_groups + m0 / p.a_flag_rows;
               if (f != a_ready) {
                 if (!wait_slab(p, f)) {
                   atomicExch(p.err, 6);
@@ -505,6 +624,7 @@ struct EriGemmArgs {
   void* flags;
   const void* flag_target;
   int b_flag_rows, a_flag_cols, rot_n_rows, rot_k_cols;
+  int a_flag_rows;   // 0, or a multiple of 128: row-group split of the K-range counters
   // peer scatter
   int scatter_world, scatter_rank, scatter_part_cols, scatter_group_cols, scatter_local_rows;
   void* scatter_out[kMaxPeers];
@@ -580,6 +700,9 @@ int eri_gemm_bf16(const EriGemmArgs* g, void* stream) {
   p.n_copy = g->n_copy; p.n_jobs = g->n_jobs; p.jobs = (const GatherJob*)g->jobs;
   p.flags = (unsigned int*)g->flags; p.flag_target = (const unsigned int*)g->flag_target;
   p.b_flag_rows = g->b_flag_rows; p.a_flag_cols = g->a_flag_cols;
+  p.a_flag_rows = g->a_flag_rows;
+  p.a_row_groups = g->a_flag_rows > 0 ? (g->M + g->a_flag_rows - 1) / g->a_flag_rows : 0;
+  if (p.a_flag_rows % BM) return -19;
   p.rot_n = g->rot_n_rows / bn;
   p.rot_k = g->rot_k_cols / BK;
   if (p.n_copy < 0 || p.n_copy > g_num_sms / 2) return -19;

@@ -41,7 +41,7 @@ class GemmArgs(C.Structure):
         ("n_copy", C.c_int), ("n_jobs", C.c_int),
         ("jobs", C.c_void_p), ("flags", C.c_void_p), ("flag_target", C.c_void_p),
         ("b_flag_rows", C.c_int), ("a_flag_cols", C.c_int), ("rot_n_rows", C.c_int),
-        ("rot_k_cols", C.c_int),
+        ("rot_k_cols", C.c_int), ("a_flag_rows", C.c_int),
         ("scatter_world", C.c_int), ("scatter_rank", C.c_int), ("scatter_part_cols", C.c_int),
         ("scatter_group_cols", C.c_int), ("scatter_local_rows", C.c_int),
         ("scatter_out", C.c_void_p * 16), ("rowsq", C.c_void_p), ("rowsq_parts", C.c_int),

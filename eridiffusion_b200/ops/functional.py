@@ -383,6 +383,7 @@ def gemm_native(a, b, *, out=None, alpha=1.0, bias=None, lora_h=None, lora_b=Non
         g.jobs, g.flags, g.flag_target = gather["jobs"], gather["flags"], gather["flag_target"]
         g.b_flag_rows, g.a_flag_cols = gather.get("b_flag_rows", 0), gather.get("a_flag_cols", 0)
         g.rot_n_rows, g.rot_k_cols = gather.get("rot_n_rows", 0), gather.get("rot_k_cols", 0)
+        g.a_flag_rows = gather.get("a_flag_rows", 0)
     if scatter is not None:
         g.scatter_world, g.scatter_rank = scatter["world"], scatter["rank"]
         g.scatter_part_cols, g.scatter_group_cols = scatter["part_cols"], scatter["group_cols"]

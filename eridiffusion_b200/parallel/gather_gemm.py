@@ -35,9 +35,13 @@ class GatherPlan:
         self.flags = torch.zeros(n_flags, dtype=torch.int32, device=self.device)
         self._targets_dev = None
         self.kw = {}
+        self.remote_bytes = 0
 
-    def _add(self, src, dst, rows, row_bytes, src_stride, dst_stride, flag):
+    def _add(self, src, dst, rows, row_bytes, src_stride, dst_stride, flag, remote=True):
         assert row_bytes % 16 == 0 and src % 16 == 0 and dst % 16 == 0
+        assert src_stride == row_bytes or row_bytes <= 32 * 1024, "a strided row must fit one copy stage"
+        if remote:
+            self.remote_bytes += rows * row_bytes
         j = N.GatherJob()
         j.src, j.dst, j.rows, j.row_bytes = src, dst, rows, row_bytes
         j.src_stride, j.dst_stride, j.flag = src_stride, dst_stride, flag
@@ -46,12 +50,16 @@ class GatherPlan:
 
     @classmethod
     def rows(cls, rank, world, shard_ptrs, landing: torch.Tensor, along_k=False, n_copy=16,
-             rows_per_job=64):
-        """landing [N, K]; shard_ptrs[p] -> peer p's [N/W, K] contiguous shard."""
+             rows_per_job=64, flag_rows=256):
+        """landing [N, K]; shard_ptrs[p] -> peer p's [N/W, K] contiguous shard. One counter per
+        ``flag_rows`` landing rows, so a tile (or K range) starts as soon as its own rows are
+        there instead of waiting for a peer's whole slab."""
         Nn, K = landing.shape
         assert Nn % world == 0
         per = Nn // world
-        pl = cls(rank, world, n_copy, landing.device)
+        if per % flag_rows or flag_rows % rows_per_job:
+            flag_rows = per
+        pl = cls(rank, world, n_copy, landing.device, n_flags=Nn // flag_rows)
         rb = K * landing.element_size()
         # interleave peers so that every slab makes progress; own slab first
         order = [(rank + i) % world for i in range(world)]
@@ -60,12 +68,12 @@ class GatherPlan:
             nr = min(rows_per_job, per - r0)
             for p in order:
                 pl._add(shard_ptrs[p] + r0 * rb, landing.data_ptr() + (p * per + r0) * landing.stride(0) * landing.element_size(),
-                        nr, rb, rb, landing.stride(0) * landing.element_size(), p)
+                        nr, rb, rb, landing.stride(0) * landing.element_size(), (p * per + r0) // flag_rows, remote=p != rank)
             r0 += nr
         if along_k:
-            pl.kw = dict(a_flag_cols=per, rot_k_cols=rank * per)
+            pl.kw = dict(a_flag_cols=flag_rows, rot_k_cols=rank * per)
         else:
-            pl.kw = dict(b_flag_rows=per, rot_n_rows=rank * per)
+            pl.kw = dict(b_flag_rows=flag_rows, rot_n_rows=rank * per)
         return pl._finish()
 
     @classmethod
@@ -76,7 +84,8 @@ class GatherPlan:
         L, WC = landing.shape
         Cc = WC // world
         es = landing.element_size()
-        pl = cls(rank, world, n_copy, landing.device)
+        groups = (L + rows_per_job - 1) // rows_per_job
+        pl = cls(rank, world, n_copy, landing.device, n_flags=world * groups)
         order = [(rank + i) % world for i in range(world)]
         r0 = 0
         while r0 < L:
@@ -84,9 +93,10 @@ class GatherPlan:
             for p in order:
                 pl._add(src_ptrs[p] + (src_row_offset + r0) * src_stride_bytes,
                         landing.data_ptr() + (r0 * landing.stride(0) + p * Cc) * es,
-                        nr, Cc * es, src_stride_bytes, landing.stride(0) * es, p)
+                        nr, Cc * es, src_stride_bytes, landing.stride(0) * es, p * groups + r0 // rows_per_job, remote=p != rank)
             r0 += nr
-        pl.kw = dict(a_flag_cols=Cc, rot_k_cols=rank * Cc)
+        # one counter per (column block, 128-row group): a tile waits for its own rows only
+        pl.kw = dict(a_flag_cols=Cc, rot_k_cols=rank * Cc, a_flag_rows=rows_per_job)
         return pl._finish()
 
     def _finish(self):
@@ -104,4 +114,4 @@ class GatherPlan:
                     flags=self.flags.data_ptr(), flag_target=self._targets_dev.data_ptr(), **self.kw)
 
     def bytes_from_peers(self):
-        return sum(j.rows * j.row_bytes for j in self.jobs if (j.flag % self.world) != self.rank)
+        return self.remote_bytes

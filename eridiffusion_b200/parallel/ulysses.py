@@ -63,7 +63,10 @@ class UlyssesContext:
         pl = self._plans.get(k)
         if pl is None:
             W, G = self.world, self.G
-            pl = GatherPlan(self.rank, W, self.n_copy, landing.device, n_flags=parts * W)
+            # counters per 128-row group need the jobs' rows to line up with the GEMM's M tiles
+            fine = self.B == 1 or self.Ll % 128 == 0
+            groups = (self.B * self.Ll + 127) // 128 if fine else 1
+            pl = GatherPlan(self.rank, W, self.n_copy, landing.device, n_flags=parts * W * groups)
             es = 2
             src_stride = parts * G * es
             order = [(self.rank + i) % W for i in range(W)]
@@ -74,9 +77,11 @@ class UlyssesContext:
                         for part in range(parts):
                             src = src_sym.peer_ptrs[p] + ((b * self.Lt + self.rank * self.Ll + r0) * parts * G + part * G) * es
                             dst = landing.data_ptr() + ((b * self.Ll + r0) * landing.stride(0) + part * W * G + p * G) * es
-                            pl._add(src, dst, nr, G * es, src_stride, landing.stride(0) * es, part * W + p)
-            # K blocks are ordered [part][peer]: one counter per (part, peer) = k // G
-            pl.kw = dict(a_flag_cols=G, rot_k_cols=self.rank * G)
+                            pl._add(src, dst, nr, G * es, src_stride, landing.stride(0) * es,
+                                    (part * W + p) * groups + ((b * self.Ll + r0) // 128 if fine else 0),
+                                    remote=p != self.rank)
+            # K blocks are ordered [part][peer]; one counter per (part, peer, 128-row group)
+            pl.kw = dict(a_flag_cols=G, rot_k_cols=self.rank * G, a_flag_rows=128 if fine else 0)
             pl._finish()
             self._plans[k] = pl
         return pl

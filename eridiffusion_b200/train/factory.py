@@ -15,8 +15,10 @@ from .trainer import Trainer, TrainerConfig, default_forward, ltx_forward
 
 _KIND_TO_MODEL = {"flux": "flux", "chroma": "chroma", "qwen_image": "qwen_image", "sdxl": "sdxl",
                   "sd3": "sd35", "sd35": "sd35", "ltx": "ltx_video", "wan22": "wan22", "klein": "klein",
-                  "zimage": "zimage", "tiny_mmdit": "tiny_mmdit"}
-_UNIMPLEMENTED = {"hunyuan", "lumina", "hidream_i1", "omnigen2"}
+                  "zimage": "zimage", "tiny_mmdit": "tiny_mmdit", "krea": "krea", "hunyuan": "hunyuan",
+                  "lumina": "lumina", "hidream_i1": "hidream", "hidream": "hidream", "omnigen2": "omnigen2",
+                  "qwen_edit_image": "qwen_edit_image"}
+_UNIMPLEMENTED = set()
 
 
 def build_job(cfg: TrainCfg, device=None):
