@@ -130,8 +130,10 @@ def forward_with_swap(blocks, x, step, cfg: BlockSwapConfig | None = None):
 
 
 # ------------------------------------------------------------------------- quantised base weights
-NF4_LEVELS = torch.tensor([-1.0, -0.6961928, -0.5250730, -0.3949175, -0.2844414, -0.1847734, -0.0910500, 0.0,
-                           0.0795803, 0.1609302, 0.2461123, 0.3379152, 0.4407098, 0.5626170, 0.7229568, 1.0])
+NF4_LEVELS = torch.tensor([-1.0, -0.6961928009986877, -0.5250730514526367, -0.39491748809814453,
+                           -0.28444138169288635, -0.18477343022823334, -0.09105003625154495, 0.0,
+                           0.07958029955625534, 0.16093020141124725, 0.24611230194568634, 0.33791524171829224,
+                           0.44070982933044434, 0.5626170039176941, 0.7229568362236023, 1.0])
 
 
 @dataclass
@@ -169,7 +171,32 @@ def quantize(w: torch.Tensor, kind="int8", block=64) -> QuantizedTensor:
     return QuantizedTensor(kind, packed, s.squeeze(1), shape, block)
 
 
-def dequantize(q: QuantizedTensor, dtype=torch.bfloat16):
+def _dequantize_native(q: QuantizedTensor, out=None):
+    """CUDA path: one kernel expands the codes into a bf16 operand (csrc/dequant.cu)."""
+    from ..ops import _native as N
+    lib = N.require()
+    n = 1
+    for s in q.shape:
+        n *= s
+    if out is None:
+        out = torch.empty(q.shape, dtype=torch.bfloat16, device=q.data.device)
+    scale = q.scale.float().contiguous()
+    if q.kind == "int8":
+        cols = q.shape[-1]
+        N.check(lib.eri_dequant_int8(q.data.data_ptr(), scale.data_ptr(), out.data_ptr(), n // cols, cols,
+                                     N.stream_ptr()), "dequant_int8")
+    else:
+        N.check(lib.eri_dequant_4bit(q.data.data_ptr(), scale.data_ptr(), out.data_ptr(), n, q.block,
+                                     1 if q.kind == "nf4" else 0, N.stream_ptr()), "dequant_4bit")
+    return out
+
+
+def dequantize(q: QuantizedTensor, dtype=torch.bfloat16, out=None):
+    if q.data.is_cuda and dtype == torch.bfloat16 and q.data.is_contiguous():
+        from ..ops import functional as F
+        ok = (q.shape[-1] % 16 == 0) if q.kind == "int8" else (q.block % 32 == 0)
+        if ok and F.get_backend() == "fused":
+            return _dequantize_native(q, out)
     if q.kind == "int8":
         return (q.data.float() * q.scale.unsqueeze(-1)).to(dtype).view(q.shape)
     lo, hi = (q.data & 0xF).long(), (q.data >> 4).long()

@@ -91,6 +91,8 @@ _SIGNATURES = {
     "eri_build_inverse": [_P, _P, _I, _I, _I, _P],
     "eri_gather_rows": [_P, _P, _P, _I, _I, _I, _I, _P],
     "eri_reinject_rows": [_P, _P, _P, _P, _I, _I, _I, _I, _P],
+    "eri_dequant_int8": [_P, _P, _P, _L, _I, _P],
+    "eri_dequant_4bit": [_P, _P, _P, _L, _I, _I, _P],
     "eri_gemm_skinny": [_P, _L, _P, _L, _P, _I, _I, _I, _I, _F, _P],
     "eri_gemm_skinny_check_error": [],
     "eri_gemm_init": [],

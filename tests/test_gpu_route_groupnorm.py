@@ -80,3 +80,25 @@ def test_token_route_topk_gather_reinject(B, L, D, k):
 def test_topk_ties_prefer_lower_index():
     s = torch.tensor([[1.0, 3.0, 3.0, 0.5, 3.0, 2.0]], device="cuda")
     assert F.topk_indices(s, 4).tolist() == [[1, 2, 4, 5]]
+
+
+@pytest.mark.parametrize("kind", ["int8", "int4", "nf4"])
+def test_dequant_kernels_match_the_torch_statement(kind):
+    """Quantised base weights: the CUDA expansion equals the elementwise PyTorch de-quantisation
+    bit for bit, and a quantised linear runs through the fused GEMM."""
+    from eridiffusion_b200 import memory as M
+    from eridiffusion_b200.models.layers import Linear
+    w = rnd(384, 512, seed=4, scale=0.05)
+    q = M.quantize(w, kind, block=64)
+    F.set_backend("eager")
+    ref = M.dequantize(q)
+    F.set_backend("fused")
+    got = M.dequantize(q)
+    assert got.dtype == torch.bfloat16 and torch.equal(got, ref)
+    lin = Linear(512, 384, device="cuda")
+    lin.weight.requires_grad_(False)
+    ql = M.QuantizedLinear(lin, kind)
+    x = rnd(2, 200, 512, seed=6)
+    y = ql(x)
+    yr = x.float() @ M.dequantize(ql.q).float().t() + lin.bias.float()
+    close(y, yr, 2e-2)
