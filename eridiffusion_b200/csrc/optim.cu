@@ -65,7 +65,7 @@ __global__ void adamw8bit_kernel(bf16* __restrict__ param, const bf16* __restric
                                  int8_t* __restrict__ mq, uint8_t* __restrict__ vq,
                                  float* __restrict__ m_absmax, float* __restrict__ v_absmax,
                                  const float* __restrict__ grad_sumsq, long long nblocks,
-                                 long long n, AdamArgs a) {
+                                 long long n, AdamArgs a, const float* __restrict__ lr_scale) {
   const int lane = threadIdx.x & 31;
   const long long warps = ((long long)gridDim.x * blockDim.x) >> 5;
   float gs = a.grad_scale;
@@ -81,6 +81,13 @@ __global__ void adamw8bit_kernel(bf16* __restrict__ param, const bf16* __restric
        blk += warps) {
     const long long e0 = blk * kBlock + lane * 8;
     const bool live = e0 < n;  // n is padded to a multiple of 8 by the arena
+    // optional per-block learning-rate multiplier (per-layer rates, layer rotation): a block
+    // whose multiplier is zero is frozen, parameters and moments untouched
+    float lr = a.lr;
+    if (lr_scale) {
+      lr *= lr_scale[blk];
+      if (lr == 0.f) continue;
+    }
     float p[8], g[8], m[8], v[8];
     if (live) {
       unpack8(*reinterpret_cast<const bf16x8*>(param + e0), p);
@@ -108,7 +115,7 @@ __global__ void adamw8bit_kernel(bf16* __restrict__ param, const bf16* __restric
       mmax = fmaxf(mmax, fabsf(m[j]));
       vmax = fmaxf(vmax, v[j]);
       float upd = (m[j] / a.bc1) / (sqrtf(v[j] / a.bc2) + a.eps);
-      p[j] = p[j] * (1.f - a.lr * a.weight_decay) - a.lr * upd;
+      p[j] = p[j] * (1.f - lr * a.weight_decay) - lr * upd;
     }
     mmax = warp_max(mmax);
     vmax = warp_max(vmax);
@@ -207,7 +214,27 @@ int eri_adamw8bit_step(void* param, const void* grad, void* mq, void* vq, float*
   long long nblocks = (n + kBlock - 1) / kBlock;
   adamw8bit_kernel<<<grid_for(nblocks * 32, 256), 256, 0, (cudaStream_t)stream>>>(
       (bf16*)param, (const bf16*)grad, (int8_t*)mq, (uint8_t*)vq, m_absmax, v_absmax, grad_sumsq,
-      nblocks, n, a);
+      nblocks, n, a, nullptr);
+  return (int)cudaGetLastError();
+}
+
+// Same step with a per-block learning-rate multiplier lr_scale[n / 256] (fp32, may be null).
+int eri_adamw8bit_step_scaled(void* param, const void* grad, void* mq, void* vq, float* m_absmax,
+                              float* v_absmax, const float* grad_sumsq, long long n, float lr, float beta1,
+                              float beta2, float eps, float weight_decay, int step, float max_grad_norm,
+                              float grad_scale, unsigned int seed, int stochastic, const float* lr_scale,
+                              void* stream) {
+  if (step < 1) return -1;
+  AdamArgs a;
+  a.lr = lr; a.beta1 = beta1; a.beta2 = beta2; a.eps = eps; a.weight_decay = weight_decay;
+  a.bc1 = 1.f - powf(beta1, (float)step);
+  a.bc2 = 1.f - powf(beta2, (float)step);
+  a.max_grad_norm = max_grad_norm; a.grad_scale = grad_scale; a.seed = seed * 2654435761u + step;
+  a.stochastic = stochastic;
+  long long nblocks = (n + kBlock - 1) / kBlock;
+  adamw8bit_kernel<<<grid_for(nblocks * 32, 256), 256, 0, (cudaStream_t)stream>>>(
+      (bf16*)param, (const bf16*)grad, (int8_t*)mq, (uint8_t*)vq, m_absmax, v_absmax, grad_sumsq,
+      nblocks, n, a, lr_scale);
   return (int)cudaGetLastError();
 }
 

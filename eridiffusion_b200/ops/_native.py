@@ -79,6 +79,7 @@ _SIGNATURES = {
     "eri_post_clamp_u8": [_P, _P, _L, _P],
     "eri_poison_fill": [_P, _L, _U32, _P],
     "eri_adamw8bit_step": [_P, _P, _P, _P, _P, _P, _P, _L, _F, _F, _F, _F, _F, _I, _F, _F, _U32, _I, _P],
+    "eri_adamw8bit_step_scaled": [_P, _P, _P, _P, _P, _P, _P, _L, _F, _F, _F, _F, _F, _I, _F, _F, _U32, _I, _P, _P],
     "eri_adamw32_step": [_P, _P, _P, _P, _P, _L, _I, _F, _F, _F, _F, _F, _I, _F, _F, _U32, _I, _P],
     "eri_ema_update": [_P, _P, _L, _F, _P],
     "eri_scale_bf16": [_P, _L, _P, _F, _F, _P],

@@ -77,6 +77,7 @@ class AdamW8bit:
         self.m_absmax = torch.zeros(n // BLOCK, dtype=torch.float32, device=dev)
         self.v_absmax = torch.zeros(n // BLOCK, dtype=torch.float32, device=dev)
         self.param_groups = [{"lr": lr}]       # so LR schedulers can drive it
+        self.lr_scale = None                   # optional fp32 [n / 256] per-block LR multiplier
 
     def _slices(self):
         if self.shard is None:
@@ -97,12 +98,12 @@ class AdamW8bit:
         b1, b2 = self.betas
         if data.is_cuda and data.dtype == torch.bfloat16 and F.get_backend() == "fused":
             lib = N.require()
-            N.check(lib.eri_adamw8bit_step(
+            N.check(lib.eri_adamw8bit_step_scaled(
                 data.data_ptr(), grad.data_ptr(), self.m_q.data_ptr(), self.v_q.data_ptr(),
                 self.m_absmax.data_ptr(), self.v_absmax.data_ptr(), N.ptr(grad_sumsq),
                 data.numel(), lr, b1, b2, self.eps, self.weight_decay, self.step_count,
                 max_grad_norm, grad_scale, self.seed, 1 if self.stochastic_rounding else 0,
-                N.stream_ptr()), "adamw8bit_step")
+                N.ptr(self.lr_scale), N.stream_ptr()), "adamw8bit_step")
             return
         self._step_reference(data, grad, lr, grad_sumsq, max_grad_norm, grad_scale)
 
@@ -113,14 +114,19 @@ class AdamW8bit:
             norm = float(grad_sumsq) ** 0.5 * grad_scale
             gs *= min(1.0, max_grad_norm / (norm + 1e-6))
         g = grad.float() * gs
-        m = dequantize_m(self.m_q, self.m_absmax)
-        v = dequantize_v(self.v_q, self.v_absmax)
-        m = b1 * m + (1 - b1) * g
-        v = b2 * v + (1 - b2) * g * g
+        m0 = dequantize_m(self.m_q, self.m_absmax)
+        v0 = dequantize_v(self.v_q, self.v_absmax)
+        m = b1 * m0 + (1 - b1) * g
+        v = b2 * v0 + (1 - b2) * g * g
         bc1 = 1 - b1 ** self.step_count
         bc2 = 1 - b2 ** self.step_count
         upd = (m / bc1) / ((v / bc2).sqrt() + self.eps)
-        p = data.float() * (1 - lr * self.weight_decay) - lr * upd
+        lr_e = lr
+        if self.lr_scale is not None:          # per-block multiplier; zero freezes the block
+            lr_e = lr * self.lr_scale.to(data.device).repeat_interleave(BLOCK)[: data.numel()]
+            frozen = lr_e == 0
+            m, v = torch.where(frozen, m0, m), torch.where(frozen, v0, v)
+        p = data.float() * (1 - lr_e * self.weight_decay) - lr_e * upd
         data.copy_(p.to(data.dtype))
         mq, ma = quantize_m(m)
         vq, va = quantize_v(v)

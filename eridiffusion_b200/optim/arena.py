@@ -74,3 +74,29 @@ class ParamArena:
 
     def named_slices(self, names):
         return {n: (o, p.numel(), tuple(p.shape)) for n, p, o in zip(names, self.params, self.offsets)}
+
+
+def block_lr_scale(arena: ParamArena, names, rules: dict | None = None, frozen=None, block: int = 256,
+                   shard=None):
+    """Per-block learning-rate multipliers for an arena-based optimizer (fp32 [numel / block]).
+
+    ``rules``: ``{substring: multiplier}`` — a parameter takes the multiplier of the first rule its
+    name contains (the reference's ``lr_if_contains``, crates/training/src/chroma/train.rs:98).
+    ``frozen``: a predicate ``name -> bool``; frozen parameters get multiplier 0 (their values and
+    optimizer moments stay untouched). ``shard = (rank, world)`` returns this rank's slice."""
+    scale = torch.ones(arena.numel // block, dtype=torch.float32)
+    for name, p, off in zip(names, arena.params, arena.offsets):
+        mult = 1.0
+        for sub, m in (rules or {}).items():
+            if sub in name:
+                mult = float(m)
+                break
+        if frozen is not None and frozen(name):
+            mult = 0.0
+        n_blocks = (p.numel() + block - 1) // block
+        scale[off // block: off // block + n_blocks] = mult
+    if shard is not None:
+        rank, world = shard
+        per = scale.numel() // world
+        scale = scale[rank * per:(rank + 1) * per]
+    return scale.to(arena.data.device)

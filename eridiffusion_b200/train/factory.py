@@ -72,7 +72,8 @@ def build_job(cfg: TrainCfg, device=None):
         max_grad_norm=cfg.max_grad_norm, ema_decay=cfg.ema_decay, seed=cfg.seed,
         out_dir=cfg.training_folder, ckpt_every=cfg.ckpt_every, keep_last=cfg.save.max_step_saves_to_keep,
         activation_checkpointing=cfg.gradient_checkpointing and not cuda, stochastic_rounding=cuda,
-        patch=1 if cfg.model.kind in ("sdxl", "ltx", "wan22") else 2)
+        patch=1 if cfg.model.kind in ("sdxl", "ltx", "wan22") else 2,
+        lr_if_contains=dict(cfg.network.lr_if_contains or {}) if cfg.train_mode == "lora" else {})
     fwd = default_forward
     if cfg.model.kind == "ltx":
         fwd = ltx_forward

@@ -58,6 +58,9 @@ class TrainerConfig:
     out_dir: str | None = None
     ckpt_every: int = 0
     keep_last: int = 0
+    lr_if_contains: dict = field(default_factory=dict)   # {name substring: LR multiplier}
+    rotate_window: int = 0                  # >0: train only this many consecutive blocks at a time
+    rotate_period: int = 100                # optimizer steps between window moves
     log_csv: str | None = None
     nan_policy: str = "skip"                # skip | raise
     lr_backoff: float = 0.5
@@ -95,6 +98,21 @@ class Trainer:
         self.optimizer = create_optimizer(cfg.optimizer, self.arena, **kw)
         if grad_sync is not None:
             grad_sync.attach(self.arena, self.optimizer)
+        # per-layer learning rates and block rotation act through the 8-bit optimizer's per-block
+        # multiplier (single-process and ZeRO-1 sharded optimizers; the fused DP kernel has none)
+        self.rotator = None
+        if (cfg.lr_if_contains or cfg.rotate_window) and hasattr(self.optimizer, "lr_scale") and not (
+                grad_sync is not None and grad_sync.fused_optimizer):
+            from ..optim.arena import block_lr_scale
+            self._lr_shard = shard
+            if cfg.rotate_window:
+                from .rotation import LayerRotator
+                n_double = len(getattr(model, "double_blocks", []))
+                self.rotator = LayerRotator(self.param_names, cfg.rotate_window, cfg.rotate_period, n_double)
+                self.rotator.apply(self.optimizer, self.arena, 0, cfg.lr_if_contains, shard)
+            else:
+                self.optimizer.lr_scale = block_lr_scale(self.arena, self.param_names, cfg.lr_if_contains,
+                                                         shard=shard)
         self.schedule = LRSchedule(cfg.lr, cfg.lr_schedule, cfg.warmup_steps, cfg.total_steps)
         self.scaler = GradScaler(enabled=False)
         self.ema = EMA(self.arena, cfg.ema_decay) if cfg.ema_decay else None
@@ -140,6 +158,8 @@ class Trainer:
     def _optimizer_step(self):
         cfg = self.cfg
         lr = self.schedule.apply(self.optimizer, self.step)
+        if self.rotator is not None:
+            self.rotator.apply(self.optimizer, self.arena, self.step, cfg.lr_if_contains, self._lr_shard)
         if self.grad_sync is not None and self.grad_sync.fused_optimizer:
             # reduce-scatter + clip + 8-bit AdamW + all-gather in the communication kernel
             self.grad_sync.reduce_and_step(lr=lr, max_grad_norm=cfg.max_grad_norm, step=self.step + 1)

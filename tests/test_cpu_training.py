@@ -101,3 +101,31 @@ def test_grad_accumulation_matches_big_batch():
         tr1.train_step(hb)
     tr2.train_step({**b, "noise": noise})
     assert torch.allclose(tr1.arena.data, tr2.arena.data, atol=2e-5)
+
+
+def test_per_layer_lr_and_block_rotation_freeze_the_right_adapters():
+    """``lr_if_contains`` scales a layer's update, rotation trains one block window at a time and
+    leaves the other blocks' parameters and optimizer moments untouched."""
+    import torch
+    from eridiffusion_b200.adapters import AdapterConfig
+    from eridiffusion_b200.data import synthetic_batch
+    from eridiffusion_b200.models import build_model
+    from eridiffusion_b200.train.trainer import Trainer, TrainerConfig
+    torch.manual_seed(0)
+    m = build_model("tiny_mmdit")
+    cfg = TrainerConfig(mode="lora", adapter=AdapterConfig(rank=4, alpha=4, dtype=torch.float32),
+                        lr=1e-2, stochastic_rounding=False, rotate_window=1, rotate_period=1,
+                        lr_if_contains={"single_blocks": 0.5})
+    tr = Trainer(m, cfg)
+    names = tr.param_names
+    snap = lambda: {n: p.detach().clone() for n, p in zip(names, tr.arena.params)}
+    before = snap()
+    tr.train_step(synthetic_batch("tiny_mmdit", 1, "cpu", torch.float32, 0))
+    after = snap()
+    changed = {n for n in names if not torch.equal(before[n], after[n])}
+    assert changed and all("double_blocks.0." in n for n in changed), sorted(changed)[:4]
+    before = after
+    tr.train_step(synthetic_batch("tiny_mmdit", 1, "cpu", torch.float32, 1))
+    after = snap()
+    changed = {n for n in names if not torch.equal(before[n], after[n])}
+    assert changed and all("double_blocks.1." in n for n in changed), sorted(changed)[:4]
