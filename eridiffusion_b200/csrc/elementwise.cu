@@ -860,3 +860,29 @@ int eri_poison_fill(void* p, long long nbytes, unsigned int pattern, void* strea
 }
 
 }  // extern "C"
+
+// ---------------------------------------------------------------------------------------------
+// Batched transpose of many small bf16 matrices in one launch (the LoRA A / B matrices of every
+// adapted linear: backward needs B^T and A^T). grid = (chunks of the largest matrix, matrices).
+namespace {
+struct TransposeJob {
+  const bf16* src;
+  bf16* dst;
+  int rows, cols;
+};
+__global__ void batched_transpose_kernel(const TransposeJob* __restrict__ jobs) {
+  const TransposeJob j = jobs[blockIdx.y];
+  const long long n = (long long)j.rows * j.cols;
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;   // index into dst [cols, rows]
+  if (i >= n) return;
+  const int c = (int)(i / j.rows), r = (int)(i - (long long)c * j.rows);
+  j.dst[i] = j.src[(long long)r * j.cols + c];
+}
+}  // namespace
+
+extern "C" int eri_batched_transpose(const void* jobs, int n_jobs, int max_elems, void* stream) {
+  if (n_jobs < 1) return 0;
+  dim3 grid((max_elems + 255) / 256, n_jobs);
+  batched_transpose_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>((const TransposeJob*)jobs);
+  return (int)cudaGetLastError();
+}

@@ -462,6 +462,64 @@ def _mm(a, b_nk, **kw):
     return y
 
 
+_ACCUM_INTO_GRAD = os.environ.get("ERI_B200_ACCUM_INTO_GRAD", "1") == "1"
+_LORA_T = {}        # data_ptr of an adapter matrix -> (epoch, transposed copy)
+_LORA_T_EPOCH = 0
+_LORA_T_PLAN = None
+
+
+class _TransposeJob(__import__("ctypes").Structure):
+    _fields_ = [("src", __import__("ctypes").c_void_p), ("dst", __import__("ctypes").c_void_p),
+                ("rows", __import__("ctypes").c_int), ("cols", __import__("ctypes").c_int)]
+
+
+def prepare_lora_transposes(matrices):
+    """Transpose every adapter matrix of a model in ONE launch and publish the copies for this
+    step's backward (which needs B^T for ``dY B`` and A^T as the rank-r K-step operand). Without
+    this each adapted linear transposes its two small matrices itself: two extra launches per
+    site per step. Call once per step after the optimizer update, before backward."""
+    global _LORA_T_EPOCH, _LORA_T_PLAN
+    import ctypes as C
+    mats = [m for m in matrices if m.is_cuda and m.dtype == torch.bfloat16 and m.dim() == 2 and m.is_contiguous()]
+    if not mats or _BACKEND != "fused":
+        return 0
+    key = tuple(m.data_ptr() for m in mats)
+    if _LORA_T_PLAN is None or _LORA_T_PLAN[0] != key:
+        total = sum(m.numel() for m in mats)
+        buf = torch.empty(total, dtype=torch.bfloat16, device=mats[0].device)
+        jobs = (_TransposeJob * len(mats))()
+        outs, off = [], 0
+        for i, m in enumerate(mats):
+            o = buf[off:off + m.numel()].view(m.shape[1], m.shape[0])
+            jobs[i].src, jobs[i].dst, jobs[i].rows, jobs[i].cols = m.data_ptr(), o.data_ptr(), m.shape[0], m.shape[1]
+            outs.append(o)
+            off += m.numel()
+        dev_jobs = torch.frombuffer(bytearray(bytes(jobs)), dtype=torch.uint8).to(mats[0].device)
+        _LORA_T_PLAN = (key, buf, outs, dev_jobs, max(m.numel() for m in mats))
+    _, buf, outs, dev_jobs, max_elems = _LORA_T_PLAN
+    lib = N.require()
+    lib.eri_batched_transpose.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_void_p]
+    lib.eri_batched_transpose.restype = C.c_int
+    N.check(lib.eri_batched_transpose(dev_jobs.data_ptr(), len(mats), max_elems, N.stream_ptr()), "batched_transpose")
+    _LORA_T_EPOCH += 1
+    for m, o in zip(mats, outs):
+        _LORA_T[m.data_ptr()] = (_LORA_T_EPOCH, o)
+    return len(mats)
+
+
+def invalidate_lora_transposes():
+    """The adapter matrices changed (optimizer step): published transposes are stale."""
+    global _LORA_T_EPOCH
+    _LORA_T_EPOCH += 1
+
+
+def _lora_transposed(m):
+    hit = _LORA_T.get(m.data_ptr())
+    if hit is not None and hit[0] == _LORA_T_EPOCH and hit[1].shape == (m.shape[1], m.shape[0]):
+        return hit[1]
+    return m.t().contiguous()
+
+
 class _FusedLinear(torch.autograd.Function):
     """y = [residual + gate *] act(x W^T + b + s (x A^T) B^T), M = B*L rows.
 
@@ -561,7 +619,7 @@ class _FusedLinear(torch.autograd.Function):
         if r:
             # Ts = s * dY B  [M, r]
             if native and r in (16, 32, 64):
-                ts = skinny_gemm(dy2, lora_b.t().contiguous(), alpha=s)
+                ts = skinny_gemm(dy2, _lora_transposed(lora_b), alpha=s)
             else:
                 ts = (dy2 @ lora_b) * s
         if need[0]:
@@ -572,7 +630,7 @@ class _FusedLinear(torch.autograd.Function):
                 if mn and K < 64:
                     b_op, mn = w.t().contiguous(), False
                 if r in (16, 32, 64):
-                    dx = gemm_native(dy2, b_op, b_mn=mn, lora_h=ts, lora_b=lora_a.t().contiguous())
+                    dx = gemm_native(dy2, b_op, b_mn=mn, lora_h=ts, lora_b=_lora_transposed(lora_a))
                 else:
                     dx = gemm_native(dy2, b_op, b_mn=mn)
                     if r:
@@ -586,10 +644,19 @@ class _FusedLinear(torch.autograd.Function):
             dw = dy2.t() @ x2
         if has_bias and need[2]:
             dbias = dy2.sum(0)
+        # Adapter gradients accumulate straight into the parameters' (arena) gradient views with
+        # the GEMM's beta = 1, instead of returning a tensor that autograd adds with one more
+        # launch per parameter.
         if r and need[3]:
-            da = ts.t() @ x2
+            if _ACCUM_INTO_GRAD and lora_a.grad is not None and lora_a.grad.dtype == x2.dtype:
+                lora_a.grad.addmm_(ts.t(), x2)
+            else:
+                da = ts.t() @ x2
         if r and need[4]:
-            db = dy2.t() @ h
+            if _ACCUM_INTO_GRAD and lora_b.grad is not None and lora_b.grad.dtype == h.dtype:
+                lora_b.grad.addmm_(dy2.t(), h)
+            else:
+                db = dy2.t() @ h
         return dx, dw, dbias, da, db, None, None, d_res, dgate, None
 
 

@@ -121,6 +121,9 @@ class Trainer:
         else:
             pred = {"eps": "epsilon", "v": "v", "sample": "sample"}[cfg.objective]
             self.objective = DDPM(prediction=pred, min_snr_gamma=cfg.min_snr_gamma)
+        self._lora_mats = [m for ad in (self.adapters or {}).values() if getattr(ad, "kind", "") == "lora"
+                           for m in (ad.lora_A, ad.lora_B)]
+        self._lora_t_stale = True
         self.step = 0
         self.micro = 0
         self.nan_skips = 0
@@ -149,6 +152,10 @@ class Trainer:
                                  eps=batch.get("noise"), patch=cfg.patch)
         pred = self.forward_fn(self.model, xt, self.objective.model_time(t), batch, cfg)
         loss = loss_fn(cfg.loss, pred, target, self.objective.loss_weight(t))
+        if self._lora_mats and self._lora_t_stale:
+            # one launch transposes every adapter matrix for this step's backward
+            F.prepare_lora_transposes(self._lora_mats)
+            self._lora_t_stale = False
         (loss / cfg.grad_accum).backward()
         self.micro += 1
         if self.micro % cfg.grad_accum == 0:
@@ -183,6 +190,9 @@ class Trainer:
             if self.grad_sync is not None:
                 self.grad_sync.gather_params()
         self.arena.zero_grad()
+        if self._lora_mats:
+            F.invalidate_lora_transposes()
+            self._lora_t_stale = True
         if self.ema is not None:
             self.ema.update()
         self.step += 1
