@@ -8,10 +8,11 @@
 //   warp 1     tcgen05.mma issue:  S = Q K^T  (smem x smem -> TMEM, fp32)
 //                                  O += P V   (P read from TMEM as packed bf16, V from smem as an
 //                                              MN-major operand, accumulator O in TMEM)
-//   warps 2-5  softmax: one thread per query row reads S from TMEM, keeps the running max / sum in
-//              registers, writes P back over S in TMEM as packed bf16, rescales O in TMEM only when
-//              the running max moved by more than 2^8 (lazy rescale), and writes O / l and the
-//              log-sum-exp at the end.
+//   warps 2-9  softmax: two threads per query row (warps w and w + 4 share 32 rows and take 64 of
+//              the tile's 128 keys each) read S from TMEM, keep the running max / partial sum in
+//              registers, write P back over S in TMEM as packed bf16, rescale their half of O in
+//              TMEM only when the running max moved by more than 2^8 (lazy rescale), and write
+//              O / l and the log-sum-exp at the end.
 // The reference reaches attention through an external flame-core SDPA or a chunked online-softmax
 // composition of bmm + elementwise ops (crates/training/src/sdxl/runtime.rs:2814-3025,
 // crates/training/src/flux/runtime.rs:707-745); the softmax recurrence is the same.
@@ -37,7 +38,7 @@ constexpr int BQ = 128, BKV = 128;
 constexpr float kRescaleThreshold = 8.0f;  // log2 units
 
 template <int DH, int POLY>
-__global__ void __launch_bounds__(192, 2)
+__global__ void __launch_bounds__(320, 2)
 fa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
               const __grid_constant__ CUtensorMap tmV, const FaParams p) {
   constexpr int CHUNKS = DH / 64;
@@ -62,6 +63,7 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
   uint64_t* p_full = bars + 6;
   uint64_t* o_done = bars + 7;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 8);
+  float* xchg = reinterpret_cast<float*>(bars + 16);  // [4][128] row max / row sum exchange
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int q0 = blockIdx.x * BQ, h = blockIdx.y, b = blockIdx.z;
@@ -74,7 +76,7 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
     mbar_init(v_full, 1);
     mbar_init(v_empty, 1);
     mbar_init(s_full, 1);
-    mbar_init(p_full, 4);
+    mbar_init(p_full, 8);
     mbar_init(o_done, 1);
     mbar_fence_init();
     tma_prefetch_desc(&tmQ);
@@ -137,55 +139,69 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
 #pragma unroll
         for (int kk = 0; kk < BKV / 16; ++kk) {
           const uint64_t dv = umma_desc_mn128(aV + kk * 2048, CHUNK_BYTES);
-          umma_bf16_ts(tmem_base + O_COL, tmem_base + S_COL + kk * 8, dv, idesc_o, (j | kk) != 0);
+          umma_bf16_ts(tmem_base + O_COL, tmem_base + S_COL + (kk >> 2) * 64 + (kk & 3) * 8, dv, idesc_o,
+                       (j | kk) != 0);
         }
         umma_commit(o_done);
         umma_commit(v_empty);
       }
     }
   } else {
+    // Eight softmax warps: warps w and w + 4 own the same 32 query rows (TMEM lanes) and split
+    // the 128 key columns of every tile in halves, so each scheduler has two softmax warps of this
+    // CTA to interleave (four with the second resident CTA). The row maximum and, at the end, the
+    // row sum are exchanged through shared memory.
     const int qd = warp & 3;
-    const int row = q0 + qd * 32 + lane;
+    const int half = (warp - 2) >> 2;
+    const int r_in = qd * 32 + lane;
+    const int row = q0 + r_in;
     const uint32_t lane_addr = tmem_base + ((uint32_t)(qd * 32) << 16);
-    float m_used = -INFINITY, l = 0.f;
+    const uint32_t s_col = S_COL + half * 64;        // this warp's 64 score columns
+    float* s_mx = xchg;                               // [2][128]
+    float* s_l = xchg + 256;                          // [2][128]
+    float m_used = -INFINITY, l = 0.f;                // l: partial row sum over this warp's columns
     bool ok = true;
     for (int j = 0; j < nkv; ++j) {
       const uint32_t par = (uint32_t)(j & 1);
-      if (!mbar_wait(s_full, par)) {
+      if (ok && !mbar_wait(s_full, par)) {
         if (lane == 0) atomicExch(p.err, 17);
         ok = false;
-        break;
+      }
+      if (!ok) {
+        // a warp that gave up still meets its partners at the block barrier and on p_full, so that
+        // no other warp is left waiting without a limit
+        asm volatile("bar.sync 1, 256;" ::: "memory");
+        if (lane == 0) mbar_arrive(p_full);
+        continue;
       }
       tc_fence_after();
-      const int kv_left = p.Lk - j * BKV;  // valid key columns in this tile
-      const bool full_tile = kv_left >= BKV;
+      const int kv_left = p.Lk - j * BKV - half * 64;  // valid key columns in this warp's half
+      const bool full_half = kv_left >= 64;
       float mx = -INFINITY;
-      if (full_tile) {
-#pragma unroll 1
-        for (int c = 0; c < 2; ++c) {
-          uint32_t r[32], r2[32];
-          tmem_ld32(lane_addr + S_COL + c * 64, r);
-          tmem_ld32(lane_addr + S_COL + c * 64 + 32, r2);
-          tmem_ld_wait();
+      if (full_half) {
+        uint32_t r[32], r2[32];
+        tmem_ld32(lane_addr + s_col, r);
+        tmem_ld32(lane_addr + s_col + 32, r2);
+        tmem_ld_wait();
 #pragma unroll
-          for (int i = 0; i < 32; i += 2) {
-            mx = fmax3(mx, __uint_as_float(r[i]), __uint_as_float(r[i + 1]));
-            mx = fmax3(mx, __uint_as_float(r2[i]), __uint_as_float(r2[i + 1]));
-          }
+        for (int i = 0; i < 32; i += 2) {
+          mx = fmax3(mx, __uint_as_float(r[i]), __uint_as_float(r[i + 1]));
+          mx = fmax3(mx, __uint_as_float(r2[i]), __uint_as_float(r2[i + 1]));
         }
       } else {
 #pragma unroll 1
-        for (int c = 0; c < 4; ++c) {
+        for (int c = 0; c < 2; ++c) {
           uint32_t r[32];
-          tmem_ld32(lane_addr + S_COL + c * 32, r);
+          tmem_ld32(lane_addr + s_col + c * 32, r);
           tmem_ld_wait();
 #pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            float s = __uint_as_float(r[i]);
-            if (c * 32 + i < kv_left) mx = fmaxf(mx, s);
-          }
+          for (int i = 0; i < 32; ++i)
+            if (c * 32 + i < kv_left) mx = fmaxf(mx, __uint_as_float(r[i]));
         }
       }
+      s_mx[half * 128 + r_in] = mx;
+      asm volatile("bar.sync 1, 256;" ::: "memory");
+      mx = fmaxf(mx, s_mx[(half ^ 1) * 128 + r_in]);
       const float m_new = mx * p.scale_log2;
       if (j == 0) {
         m_used = m_new;
@@ -193,12 +209,14 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
         const bool need = (m_new - m_used) > kRescaleThreshold;
         if (__any_sync(0xffffffffu, need)) {
           // s_full of this tile was committed after PV of the previous tile, so O is complete.
+          // Both warps of a row pair take the same decision; each rescales its half of O.
           const float m_t = need ? m_new : m_used;
           const float alpha = exp2f(m_used - m_t);
 #pragma unroll 1
-          for (int c = 0; c < DH / 32; ++c) {
+          for (int c = 0; c < DH / 64; ++c) {
             uint32_t r[32];
-            tmem_ld32(lane_addr + O_COL + c * 32, r);
+            const uint32_t oc = O_COL + half * (DH / 2) + c * 32;
+            tmem_ld32(lane_addr + oc, r);
             tmem_ld_wait();
             uint32_t a0[16], a1[16];
 #pragma unroll
@@ -206,16 +224,18 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
               a0[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
               a1[i] = __float_as_uint(__uint_as_float(r[16 + i]) * alpha);
             }
-            tmem_st16(lane_addr + O_COL + c * 32, a0);
-            tmem_st16(lane_addr + O_COL + c * 32 + 16, a1);
+            tmem_st16(lane_addr + oc, a0);
+            tmem_st16(lane_addr + oc + 16, a1);
           }
           tmem_st_wait();
           l *= alpha;
           m_used = m_t;
         }
       }
+      // s_mx needs no second barrier: the next tile's s_full cannot complete before all eight warps
+      // have arrived on p_full, i.e. after both warps of a pair have read the other's maximum
       float lsum = 0.f;
-      if (full_tile) {
+      if (full_half) {
         // Hot path: packed fp32 pairs (one fma / add per two scores), 2^x split between the
         // special-function unit and a polynomial on the FMA pipe (POLY of every 16 pairs), the
         // row sum taken from the unrounded fp32 values.
@@ -223,9 +243,9 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
         const f32x2 nm2 = f2_pack(-m_used, -m_used);
         f32x2 acc2 = f2_pack(0.f, 0.f);
 #pragma unroll 1
-        for (int c = 0; c < 4; ++c) {
+        for (int c = 0; c < 2; ++c) {
           uint32_t r[32];
-          tmem_ld32(lane_addr + S_COL + c * 32, r);
+          tmem_ld32(lane_addr + s_col + c * 32, r);
           tmem_ld_wait();
           uint32_t pk[16];
 #pragma unroll
@@ -241,16 +261,17 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
             acc2 = f2_add(acc2, v);
             pk[i] = f2_to_bf162(v);
           }
-          tmem_st16(lane_addr + S_COL + c * 16, pk);
+          // packed P of this half starts at the half's own first column
+          tmem_st16(lane_addr + s_col + c * 16, pk);
         }
         float a_lo, a_hi;
         f2_unpack(acc2, a_lo, a_hi);
         lsum = a_lo + a_hi;
       } else {
 #pragma unroll 1
-        for (int c = 0; c < 4; ++c) {
+        for (int c = 0; c < 2; ++c) {
           uint32_t r[32];
-          tmem_ld32(lane_addr + S_COL + c * 32, r);
+          tmem_ld32(lane_addr + s_col + c * 32, r);
           tmem_ld_wait();
           uint32_t pk[16];
 #pragma unroll
@@ -262,7 +283,7 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
             lsum += p0 + p1;
             pk[i] = pack_bf162(p0, p1);
           }
-          tmem_st16(lane_addr + S_COL + c * 16, pk);
+          tmem_st16(lane_addr + s_col + c * 16, pk);
         }
       }
       l += lsum;
@@ -277,14 +298,19 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
         ok = false;
       }
     }
+    // total row sum = the two halves' partial sums (exchanged even after an error so that the
+    // barrier is always reached by all eight warps)
+    s_l[half * 128 + r_in] = l;
+    asm volatile("bar.sync 1, 256;" ::: "memory");
+    l += s_l[(half ^ 1) * 128 + r_in];
     if (ok) {
       tc_fence_after();
       const float inv_l = 1.f / l;
-      bf16* orow = p.out + (((size_t)b * p.Lq + row) * p.H + h) * DH;
+      bf16* orow = p.out + (((size_t)b * p.Lq + row) * p.H + h) * DH + half * (DH / 2);
 #pragma unroll 1
-      for (int c = 0; c < DH / 32; ++c) {
+      for (int c = 0; c < DH / 64; ++c) {
         uint32_t r[32];
-        tmem_ld32(lane_addr + O_COL + c * 32, r);
+        tmem_ld32(lane_addr + O_COL + half * (DH / 2) + c * 32, r);
         tmem_ld_wait();
         if (row < p.Lq) {
 #pragma unroll
@@ -296,7 +322,7 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
           }
         }
       }
-      if (p.lse && row < p.Lq)
+      if (half == 0 && p.lse && row < p.Lq)
         p.lse[((size_t)b * p.H + h) * p.Lq + row] = (m_used + log2f(l)) * 0.6931471805599453f;
     }
   }
@@ -314,7 +340,7 @@ int* g_fa_err = nullptr;
 template <int DH, int POLY>
 int launch_fwd(const CUtensorMap& q, const CUtensorMap& k, const CUtensorMap& v, const FaParams& p,
                cudaStream_t st) {
-  constexpr int SMEM = 3 * 128 * 128 * (DH / 64) + 1024 + 128;
+  constexpr int SMEM = 3 * 128 * 128 * (DH / 64) + 1024 + 128 + 2048;
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(fa_fwd_kernel<DH, POLY>,
@@ -323,7 +349,7 @@ int launch_fwd(const CUtensorMap& q, const CUtensorMap& k, const CUtensorMap& v,
     configured = true;
   }
   dim3 grid((p.Lq + BQ - 1) / BQ, p.H, p.B);
-  fa_fwd_kernel<DH, POLY><<<grid, 192, SMEM, st>>>(q, k, v, p);
+  fa_fwd_kernel<DH, POLY><<<grid, 320, SMEM, st>>>(q, k, v, p);
   return (int)cudaGetLastError();
 }
 
@@ -333,8 +359,8 @@ int poly_pairs() {
   static int v = -1;
   if (v < 0) {
     const char* e = getenv("ERI_B200_FA_POLY");
-    v = e ? atoi(e) : 8;
-    if (v != 0 && v != 4 && v != 8) v = 8;
+    v = e ? atoi(e) : 4;
+    if (v != 0 && v != 4 && v != 8) v = 4;
   }
   return v;
 }
