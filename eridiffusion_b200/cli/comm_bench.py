@@ -40,13 +40,23 @@ def gemm_peak():
 
 
 def timed(fn, iters=10, warm=3):
-    for _ in range(warm):
+    for i in range(warm):
         fn()
+        if i == 0:
+            # a bounded wait that ran out on any rank ends the benchmark on all ranks, instead of
+            # repeating the same wait in every following launch
+            bad = torch.tensor([1.0 if F.kernel_error_check() else 0.0], device="cuda")
+            dist.all_reduce(bad, dist.ReduceOp.MAX)
+            if bad.item():
+                raise SystemExit("a kernel reported an error in the first launch; stopping")
     ts = []
     for _ in range(iters):
         dist.barrier()
         torch.cuda.synchronize()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        # a short device-side sleep lets the host queue the launches before the start event fires, so
+        # the interval is device time and not the host's launch path (as inside a busy training step)
+        torch.cuda._sleep(1_000_000)
         e0.record(); fn(); e1.record()
         torch.cuda.synchronize()
         ts.append(e0.elapsed_time(e1))

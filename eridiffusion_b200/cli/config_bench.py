@@ -85,10 +85,9 @@ def main(argv=None):
         Ll = L // world
         gs = GradSync("allreduce") if world > 1 else None
         cfg = TrainerConfig(mode="lora", adapter=AdapterConfig(rank=16, alpha=16, dtype=dt), objective="flow",
-                            optimizer="adamw8bit", lr=1e-4, patch=1, seed=0, guidance=None)
+                            optimizer="adamw8bit", lr=1e-4, patch=1, seed=0, guidance=None,
+                            seq_parallel=world)   # the ranks work on ONE sample: same timestep stream
         tr = Trainer(model, cfg, grad_sync=gs, forward_fn=ltx_forward)
-        # the ranks of a sequence-parallel group work on ONE sample: they must draw the same timestep
-        tr._gen = torch.Generator(device=dev).manual_seed(1234)
         if world > 1:
             from ..parallel.ulysses import UlyssesContext
             if L % world or model.cfg.num_heads % world:
@@ -112,6 +111,13 @@ def main(argv=None):
 
     for i in range(a.warmup):
         tr.train_step(batch(i))
+        if i == 0:
+            # a bounded wait that ran out in any kernel of any rank ends the run here, on all ranks
+            bad = torch.tensor([1.0 if F.kernel_error_check() else 0.0], device=dev)
+            if world > 1:
+                dist.all_reduce(bad, dist.ReduceOp.MAX)
+            if bad.item():
+                raise SystemExit(f"rank {rank}: a kernel reported an error in the first step; stopping")
     barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()

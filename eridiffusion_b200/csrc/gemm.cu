@@ -134,7 +134,11 @@ __device__ __forceinline__ bool wait_slab(const GemmParams& p, int f) {
   const uint64_t t0 = globaltimer_ns();
   for (uint32_t i = 0; i < (1u << 28); ++i) {
     if (ld_acquire_gpu(p.flags + f) >= want) return true;
-    if ((i & 63u) == 63u && globaltimer_ns() - t0 > ERI_WAIT_LIMIT_NS) return false;
+    if ((i & 63u) == 63u) {
+      if (globaltimer_ns() - t0 > ERI_WAIT_LIMIT_NS) return false;
+      // another role or CTA of this launch already gave up: do not stack a second full wait on it
+      if (*reinterpret_cast<volatile int*>(p.err) != 0) return false;
+    }
   }
   return false;
 }

@@ -42,7 +42,18 @@ def build_job(cfg: TrainCfg, device=None):
 
     par = cfg.parallel
     grad_sync = None
-    if world > 1:
+    seq_par = par.ulysses if world > 1 else 1
+    if seq_par > 1:
+        # one sequence-parallel group spanning the job: every rank holds a token slice of the same
+        # sample, the two all-to-alls run inside the QKV / output projections
+        if seq_par != world:
+            raise ValueError(f"parallel.ulysses ({seq_par}) must equal the number of ranks ({world})")
+        if not hasattr(model, "set_sequence_parallel"):
+            raise ValueError(f"model kind '{cfg.model.kind}' has no sequence-parallel attention path")
+        if model.cfg.num_heads % world:
+            raise ValueError("the head count must divide by parallel.ulysses")
+        grad_sync = GradSync("allreduce")
+    elif world > 1:
         if par.zero_stage == 3:
             from ..parallel.zero3 import Zero3Context, Zero3Sync, shard_model
             z3 = Zero3Context()
@@ -69,7 +80,7 @@ def build_job(cfg: TrainCfg, device=None):
         guidance=1.0 if cfg.bypass_guidance_embedding and cfg.guidance is None else (cfg.guidance or 3.5),
         optimizer=cfg.optimizer, lr=cfg.lr, weight_decay=cfg.weight_decay, lr_schedule=cfg.lr_schedule,
         warmup_steps=cfg.warmup_steps, total_steps=cfg.steps, grad_accum=cfg.grad_accum_steps,
-        max_grad_norm=cfg.max_grad_norm, ema_decay=cfg.ema_decay, seed=cfg.seed,
+        max_grad_norm=cfg.max_grad_norm, ema_decay=cfg.ema_decay, seed=cfg.seed, seq_parallel=seq_par,
         out_dir=cfg.training_folder, ckpt_every=cfg.ckpt_every, keep_last=cfg.save.max_step_saves_to_keep,
         activation_checkpointing=cfg.gradient_checkpointing and not cuda, stochastic_rounding=cuda,
         patch=1 if cfg.model.kind in ("sdxl", "ltx", "wan22") else 2,
@@ -87,8 +98,9 @@ def build_job(cfg: TrainCfg, device=None):
         loader = CachedEmbeddingLoader(ds.manifest, kind="sdxl" if cfg.model.kind == "sdxl" else "flux",
                                        batch_size=cfg.batch_size, root_dir=ds.manifest_root,
                                        index_path=ds.manifest_index, shuffle=ds.manifest_shuffle,
-                                       repeat=ds.manifest_repeat, seed=cfg.seed, device=dev, rank=rank,
-                                       world=world, validate=ds.manifest_validate)
+                                       repeat=ds.manifest_repeat, seed=cfg.seed, device=dev,
+                                       rank=0 if seq_par > 1 else rank, world=1 if seq_par > 1 else world,
+                                       validate=ds.manifest_validate)
         batches = iter(loader)
     else:
         res = (ds.resolution[0] if ds and ds.resolution else 1024)
@@ -97,7 +109,31 @@ def build_job(cfg: TrainCfg, device=None):
             i = 0
             while True:
                 yield synthetic_batch(model_id if model_id != "ltx_video" else "ltx", cfg.batch_size, dev, dtype,
-                                      seed=cfg.seed + i * world + rank, height=res, width=res)
+                                      seed=cfg.seed + (i if seq_par > 1 else i * world + rank), height=res,
+                                      width=res)
                 i += 1
         batches = gen()
+    if seq_par > 1:
+        batches = _sequence_parallel_batches(batches, model, rank, world)
     return trainer, batches, {"rank": rank, "world": world, "device": str(dev), "model": model_id}
+
+
+def _sequence_parallel_batches(batches, model, rank, world):
+    """Every rank of the group receives the same sample and keeps its contiguous token slice of the
+    token-major latents ``[B, C, L, 1]``; the attention context is created from the first batch."""
+    from ..parallel.dist import ProcessGroup
+    from ..parallel.ulysses import UlyssesContext
+    attached = False
+    for b in batches:
+        lat = b["latents"]
+        L = lat.shape[2]
+        if L % world:
+            raise ValueError(f"token count {L} must divide by the sequence-parallel size {world}")
+        Ll = L // world
+        if not attached:
+            model.set_sequence_parallel(UlyssesContext(ProcessGroup(), batch=lat.shape[0], l_local=Ll,
+                                                       hidden=model.cfg.hidden, heads=model.cfg.num_heads))
+            attached = True
+        b = dict(b)
+        b["latents"] = lat[:, :, rank * Ll:(rank + 1) * Ll].contiguous()
+        yield b

@@ -61,6 +61,7 @@ class TrainerConfig:
     lr_if_contains: dict = field(default_factory=dict)   # {name substring: LR multiplier}
     rotate_window: int = 0                  # >0: train only this many consecutive blocks at a time
     rotate_period: int = 100                # optimizer steps between window moves
+    seq_parallel: int = 1                   # ranks that share ONE sample (Ulysses); they draw the same timestep
     log_csv: str | None = None
     nan_policy: str = "skip"                # skip | raise
     lr_backoff: float = 0.5
@@ -135,7 +136,10 @@ class Trainer:
     def _generator(self, device):
         if self._gen is None or self._gen.device != torch.device(device):
             rank = self.grad_sync.rank if self.grad_sync is not None else 0
-            self._gen = torch.Generator(device=device).manual_seed(self.cfg.seed * 1000003 + rank)
+            # the ranks of a sequence-parallel group hold token slices of one sample: same timestep
+            # stream for the group (the noise below stays per rank, as every rank owns other tokens)
+            group = rank // max(1, self.cfg.seq_parallel)
+            self._gen = torch.Generator(device=device).manual_seed(self.cfg.seed * 1000003 + group)
         return self._gen
 
     def train_step(self, batch: dict):
