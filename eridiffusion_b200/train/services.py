@@ -286,6 +286,94 @@ class TrainingVerifier:
             return "dead_gradients"
         return "healthy"
 
+    def verify_training_step(self, loss, step, grad_norm=None, grad_range=(1e-8, 1e3), loss_range=(0.0, 100.0)):
+        """One report per step in the shape of the reference's ``verify_training_step``
+        (src/training_verifier.rs:326-400): gradient, parameter, loss-trend and memory checks, and
+        an overall health of ``healthy`` / ``warning`` (at most two soft issues) / ``failed``.
+        ``grad_norm``: the step's global gradient norm when the gradients themselves were already
+        cleared by the optimizer step (``Trainer.grad_norm()``); otherwise the arena's are read."""
+        if not hasattr(self, "analyzer"):
+            self.analyzer, self.memory, self.log = TrainingAnalyzer(loss_range), MemoryMonitor(), []
+        issues = []
+        if grad_norm is not None:
+            n = float(grad_norm)
+            g = {"finite": n == n and abs(n) != float("inf"), "nonzero_frac": 1.0 if n != 0 else 0.0, "norm": n}
+        else:
+            g = self.gradients()
+        if g["nonzero_frac"] == 0:
+            issues.append("No gradients detected")
+        if not g["finite"]:
+            issues.append("Non-finite gradients")
+        elif g["nonzero_frac"] and not (grad_range[0] <= g["norm"] <= grad_range[1]):
+            issues.append(f"Gradient magnitude out of range: {g['norm']:.2e}")
+        moved = self.parameters_changed()
+        if step > 0 and moved == 0:
+            issues.append("Parameters not updating")
+        ls = self.analyzer.analyze_loss(float(loss))
+        if not ls["is_finite"]:
+            issues.append("Loss is not finite")
+        elif not ls["in_expected_range"]:
+            issues.append(f"Loss out of range: {float(loss)}")
+        ms = self.memory.check_memory()
+        if not ms["within_bounds"]:
+            issues.append(f"Memory usage too high: {ms['current_usage_gb']:.1f}GB")
+        if not ms["stable"]:
+            issues.append("Memory usage unstable")
+        hard = any("not updating" in i or "No gradients" in i for i in issues)
+        health = "healthy" if not issues else ("warning" if len(issues) <= 2 and not hard else "failed")
+        rep = {"step": step, "health": health, "issues": issues, "gradients": g, "param_max_delta": moved,
+               "loss": ls, "memory": ms}
+        self.log.append(rep)
+        return rep
+
+
+class TrainingAnalyzer:
+    """Loss bookkeeping: finiteness, range, and the trend of the last five values against the five
+    before them (2 % band), as ``TrainingAnalyzer::analyze_loss`` (src/training_verifier.rs:225-262)."""
+
+    def __init__(self, loss_range=(0.0, 100.0)):
+        self.loss_history, self.loss_range = [], loss_range
+
+    def analyze_loss(self, loss):
+        self.loss_history.append(loss)
+        finite = loss == loss and abs(loss) != float("inf")
+        h = self.loss_history
+        trend = "warming_up"
+        if len(h) >= 10:
+            recent, older = sum(h[-5:]) / 5.0, sum(h[-10:-5]) / 5.0
+            trend = "decreasing" if recent < older * 0.98 else "increasing" if recent > older * 1.02 else "stable"
+        return {"is_finite": finite, "in_expected_range": finite and self.loss_range[0] < loss < self.loss_range[1],
+                "trend": trend, "current_loss": loss}
+
+
+class MemoryMonitor:
+    """Device memory in use per step, its peak, whether it stays under ``limit_frac`` of the device
+    and whether the five-step average moved by less than ``drift_gb`` (the reference's
+    ``MemoryMonitor`` reports a constant, src/training_verifier.rs:266-305; this one reads the
+    allocator)."""
+
+    def __init__(self, limit_frac=0.95, drift_gb=0.5, reader=None):
+        self.peak_usage, self.usage_history = 0.0, []
+        self.limit_frac, self.drift_gb, self._reader = limit_frac, drift_gb, reader
+
+    def _read(self):
+        if self._reader is not None:
+            return self._reader()
+        if torch.cuda.is_available():
+            free, total = torch.cuda.mem_get_info()
+            return torch.cuda.memory_allocated() / 2 ** 30, total / 2 ** 30
+        return 0.0, float("inf")
+
+    def check_memory(self):
+        cur, total = self._read()
+        self.usage_history.append(cur)
+        self.peak_usage = max(self.peak_usage, cur)
+        h, stable = self.usage_history, True
+        if len(h) >= 10:
+            stable = abs(sum(h[-5:]) / 5.0 - sum(h[-10:-5]) / 5.0) < self.drift_gb
+        return {"current_usage_gb": cur, "peak_usage_gb": self.peak_usage,
+                "within_bounds": cur < self.limit_frac * total, "stable": stable}
+
 
 # ------------------------------------------------------------------------- run driver
 def run_training(trainer, batches, steps, callbacks=(), log_every=10, world=1, batch_size=1, nan_guard=None,

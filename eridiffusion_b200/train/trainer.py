@@ -131,6 +131,10 @@ class Trainer:
         self._gen = None
         self._sumsq = None
         self._csv = None
+        # per-phase device times (noise / forward / backward / optimizer), read with
+        # ``trainer.phases.summary()``; off unless ERI_B200_PHASE_TIMING=1
+        from ..utils.trace import PhaseTimer
+        self.phases = PhaseTimer(enabled=os.environ.get("ERI_B200_PHASE_TIMING") == "1")
 
     # ------------------------------------------------------------------ one micro-step
     def _generator(self, device):
@@ -149,21 +153,26 @@ class Trainer:
         x0 = batch["latents"]
         B = x0.shape[0]
         dev = x0.device
-        t = self.objective.sample_t(B, self._generator(dev), dev)
-        coef = self.objective.coefficients(t)
-        rank = self.grad_sync.rank if self.grad_sync is not None else 0
-        xt, target = F.noise_mix(x0, coef, seed=cfg.seed + 7919 * rank, offset=self.micro << 24,
-                                 eps=batch.get("noise"), patch=cfg.patch)
-        pred = self.forward_fn(self.model, xt, self.objective.model_time(t), batch, cfg)
-        loss = loss_fn(cfg.loss, pred, target, self.objective.loss_weight(t))
-        if self._lora_mats and self._lora_t_stale:
-            # one launch transposes every adapter matrix for this step's backward
-            F.prepare_lora_transposes(self._lora_mats)
-            self._lora_t_stale = False
-        (loss / cfg.grad_accum).backward()
+        ph = self.phases
+        with ph.phase("noise"):
+            t = self.objective.sample_t(B, self._generator(dev), dev)
+            coef = self.objective.coefficients(t)
+            rank = self.grad_sync.rank if self.grad_sync is not None else 0
+            xt, target = F.noise_mix(x0, coef, seed=cfg.seed + 7919 * rank, offset=self.micro << 24,
+                                     eps=batch.get("noise"), patch=cfg.patch)
+        with ph.phase("forward"):
+            pred = self.forward_fn(self.model, xt, self.objective.model_time(t), batch, cfg)
+            loss = loss_fn(cfg.loss, pred, target, self.objective.loss_weight(t))
+        with ph.phase("backward"):
+            if self._lora_mats and self._lora_t_stale:
+                # one launch transposes every adapter matrix for this step's backward
+                F.prepare_lora_transposes(self._lora_mats)
+                self._lora_t_stale = False
+            (loss / cfg.grad_accum).backward()
         self.micro += 1
         if self.micro % cfg.grad_accum == 0:
-            self._optimizer_step()
+            with ph.phase("optimizer"):
+                self._optimizer_step()
         return loss.detach()
 
     def _optimizer_step(self):
