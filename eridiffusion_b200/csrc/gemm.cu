@@ -280,7 +280,11 @@ __device__ void copy_role(const GemmParams& p, uint8_t* smem, int ring_stages) {
   }
 }
 
-template <int BN, int STAGES>
+// STAGED: the epilogue writes each accumulator row to shared memory first and sends it with ONE
+// bulk asynchronous copy per row (BN * 2 bytes) instead of one 16-byte store per 8 columns. Used by
+// the peer scatter, where a row's destination is another GPU: NVLink then carries 512-byte writes
+// and the epilogue warps do not wait for remote stores before they release the accumulator.
+template <int BN, int STAGES, bool STAGED>
 __global__ void __launch_bounds__(192, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                  const __grid_constant__ CUtensorMap tmA2, const __grid_constant__ CUtensorMap tmB2,
@@ -307,6 +311,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   uint64_t* acc_full = empty + STAGES;
   uint64_t* acc_empty = acc_full + 2;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+  // staged epilogue: one padded row per epilogue thread (the 16-byte pad spreads the rows over banks)
+  constexpr int STG_PITCH = BN * 2 + 16;
+  uint8_t* stg = smem + STAGES * STAGE_BYTES + 256;
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -494,6 +501,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       }
       const bf16* gate = p.gate ? p.gate + (size_t)(row_ok ? row / p.rows_per_batch : 0) * p.gate_stride
                                 : nullptr;
+      uint8_t* stg_row = stg + (size_t)(q * 32 + lane) * STG_PITCH;
+      if constexpr (STAGED) {
+        // this thread's previous row copy must have read its staging row before it is rewritten
+        if (it > 0) tma_store_wait_read<0>();
+      }
       float sq = 0.f;
 #pragma unroll 1
       for (int c = 0; c < BN / CH; ++c) {
@@ -548,10 +560,23 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 #pragma unroll
                 for (int j = 0; j < 8; ++j) sq += v[j] * v[j];
               }
-              *reinterpret_cast<bf16x8*>(dst + (col - dcol_off)) = pack8(v);
+              if constexpr (STAGED)
+                *reinterpret_cast<bf16x8*>(stg_row + (size_t)(col - n0) * 2) = pack8(v);
+              else
+                *reinterpret_cast<bf16x8*>(dst + (col - dcol_off)) = pack8(v);
             }
           }
         }
+      }
+      if constexpr (STAGED) {
+        // the row was written by this thread alone: order it before the async proxy reads it, then
+        // one bulk copy carries the whole row to its (possibly remote) destination
+        fence_proxy_async_all();
+        if (row_ok) {
+          const int ncols = min(BN, p.N - n0);
+          bulk_s2g_plain(dst + (n0 - dcol_off), smem_u32(stg_row), (uint32_t)ncols * 2u);
+        }
+        tma_store_commit();
       }
       if (p.rowsq && row_ok) {
         const int part = n0 / p.scatter_part_cols;
@@ -561,6 +586,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       __syncwarp();
       if (lane == 0) mbar_arrive(&acc_empty[buf]);
     }
+    if constexpr (STAGED) tma_store_wait<0>();   // every row copy of this thread has completed
   }
 
   tc_fence_before();
@@ -571,13 +597,13 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   }
 }
 
-template <int BN, int STAGES>
+template <int BN, int STAGES, bool STAGED = false>
 int launch(const CUtensorMap& a, const CUtensorMap& b, const CUtensorMap& a2, const CUtensorMap& b2,
            const GemmParams& p, int max_ctas, cudaStream_t stream) {
-  constexpr int SMEM = STAGES * (BM * BK * 2 + BN * BK * 2) + 1024 + 256;
+  constexpr int SMEM = STAGES * (BM * BK * 2 + BN * BK * 2) + 1024 + 256 + (STAGED ? BM * (BN * 2 + 16) : 0);
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_bf16_kernel<BN, STAGES>,
+    cudaError_t e = cudaFuncSetAttribute(gemm_bf16_kernel<BN, STAGES, STAGED>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
     if (e != cudaSuccess) return (int)e;
     configured = true;
@@ -588,10 +614,10 @@ int launch(const CUtensorMap& a, const CUtensorMap& b, const CUtensorMap& a2, co
   if (p.n_copy > 0) {
     // the compute CTAs spin on counters that the copy CTAs bump: all must be resident
     void* args[] = {(void*)&a, (void*)&b, (void*)&a2, (void*)&b2, (void*)&p};
-    return (int)cudaLaunchCooperativeKernel((const void*)gemm_bf16_kernel<BN, STAGES>, dim3(grid),
+    return (int)cudaLaunchCooperativeKernel((const void*)gemm_bf16_kernel<BN, STAGES, STAGED>, dim3(grid),
                                             dim3(192), args, SMEM, stream);
   }
-  gemm_bf16_kernel<BN, STAGES><<<grid, 192, SMEM, stream>>>(a, b, a2, b2, p);
+  gemm_bf16_kernel<BN, STAGES, STAGED><<<grid, 192, SMEM, stream>>>(a, b, a2, b2, p);
   return (int)cudaGetLastError();
 }
 
@@ -750,6 +776,12 @@ int eri_gemm_bf16(const EriGemmArgs* g, void* stream) {
     tb2 = tb;
   }
   cudaStream_t st = (cudaStream_t)stream;
+  if (p.scatter_world && (g->ldc * 2) % 16 == 0) {
+    // rows leave through bulk copies (16-byte aligned destinations: ldc and every column offset
+    // are multiples of 8 elements); one operand stage less pays for the staging rows
+    if (bn == 256) return launch<256, 3, true>(ta, tb, ta2, tb2, p, g_num_sms, st);
+    if (bn == 128) return launch<128, 5, true>(ta, tb, ta2, tb2, p, g_num_sms, st);
+  }
   switch (bn) {
     case 256: return launch<256, 4>(ta, tb, ta2, tb2, p, g_num_sms, st);
     case 128: return launch<128, 6>(ta, tb, ta2, tb2, p, g_num_sms, st);
