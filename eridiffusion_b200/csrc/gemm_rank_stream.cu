@@ -1,0 +1,144 @@
+// out[M, N] = alpha * a[M, K] b[N, K]^T for N = 16 / 32 / 64 (a LoRA rank) as a streaming kernel.
+//
+// The problem is bound by reading a once (M * K * 2 bytes; 2 * N FLOP per byte), so the kernel is
+// built around loads in flight, not around the tensor cores: no shared-memory operand staging, no
+// tensor-memory allocation, no barriers in the main loop. One CTA of eight warps owns 16 rows of a;
+// the warps split K among themselves (contiguous ranges, so each warp walks whole DRAM pages) and
+// every thread keeps several 16-byte loads of a in flight. The products run on mma.sync m16n8k16:
+// the instruction sums over 16 k-slots, and which column sits in which slot is free as long as a and
+// b agree, so a thread's 16-byte load (8 consecutive columns of one row) feeds two instructions
+// directly from registers: slots {2t, 2t+1, 2t+8, 2t+9} take columns {8t..8t+3} for the first and
+// {8t+4..8t+7} for the second. b is loaded the same way (row n = lane / 4 of each 8-row group) and
+// stays in L1 / L2 (N * K * 2 bytes for the whole grid). The eight partial 16 x N tiles are summed
+// through shared memory at the end.
+//
+// The reference computes the LoRA down-projection as a separate library GEMM per adapter site
+// (crates/training/src/flux/lora.rs:47-63).
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <cstdint>
+
+typedef __nv_bfloat16 bf16;
+
+namespace {
+
+__device__ __forceinline__ uint4 ld_stream16(const void* p) {
+  uint4 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0, %1, %2, %3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p));
+  return v;
+}
+__device__ __forceinline__ uint4 ld_cached16(const void* p) {
+  uint4 v;
+  asm volatile("ld.global.nc.v4.u32 {%0, %1, %2, %3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p));
+  return v;
+}
+__device__ __forceinline__ void mma16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2,
+                                         uint32_t a3, uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, "
+      "{%8, %9}, {%0, %1, %2, %3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+constexpr int kWarps = 8;
+
+// NT: 8-column tiles of the output (N = 8 * NT); U: 32-column steps whose loads are issued together.
+template <int NT, int U>
+__global__ void __launch_bounds__(kWarps * 32)
+rank_stream_kernel(const bf16* __restrict__ a, long long lda, const bf16* __restrict__ b,
+                   long long ldb, bf16* __restrict__ out, int ldc, int M, int K, float alpha) {
+  constexpr int N = NT * 8;
+  __shared__ float red[kWarps][16][N + 1];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+  const int m0 = blockIdx.x * 16;
+  // rows past the end read the last row (valid memory) and are never stored
+  const int r0 = min(m0 + g, M - 1), r1 = min(m0 + g + 8, M - 1);
+  const int nsteps = K >> 5;
+  const int s_begin = (int)((long long)warp * nsteps / kWarps);
+  const int s_end = (int)((long long)(warp + 1) * nsteps / kWarps);
+  const uint4* pa0 = reinterpret_cast<const uint4*>(a + (size_t)r0 * lda) + t;
+  const uint4* pa1 = reinterpret_cast<const uint4*>(a + (size_t)r1 * lda) + t;
+  const uint4* pb = reinterpret_cast<const uint4*>(b + (size_t)g * ldb) + t;
+  const size_t b_tile = (size_t)ldb;   // uint4 units between 8-row groups of b: 8 rows * ldb * 2 B / 16 B
+
+  float acc[NT][4];
+#pragma unroll
+  for (int j = 0; j < NT; ++j)
+#pragma unroll
+    for (int i = 0; i < 4; ++i) acc[j][i] = 0.f;
+
+  for (int s = s_begin; s < s_end; s += U) {
+    uint4 va0[U], va1[U], vb[U][NT];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int ss = min(s + u, s_end - 1);       // the tail repeats a step; its product is dropped
+      va0[u] = ld_stream16(pa0 + 4 * ss);
+      va1[u] = ld_stream16(pa1 + 4 * ss);
+#pragma unroll
+      for (int j = 0; j < NT; ++j) vb[u][j] = ld_cached16(pb + j * b_tile + 4 * ss);
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      if (s + u < s_end) {
+#pragma unroll
+        for (int j = 0; j < NT; ++j) {
+          mma16816(acc[j], va0[u].x, va1[u].x, va0[u].y, va1[u].y, vb[u][j].x, vb[u][j].y);
+          mma16816(acc[j], va0[u].z, va1[u].z, va0[u].w, va1[u].w, vb[u][j].z, vb[u][j].w);
+        }
+      }
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < NT; ++j) {
+    red[warp][g][j * 8 + 2 * t] = acc[j][0];
+    red[warp][g][j * 8 + 2 * t + 1] = acc[j][1];
+    red[warp][g + 8][j * 8 + 2 * t] = acc[j][2];
+    red[warp][g + 8][j * 8 + 2 * t + 1] = acc[j][3];
+  }
+  __syncthreads();
+  // 16 x N outputs, two adjacent columns per thread
+  for (int i = threadIdx.x; i < 16 * N / 2; i += kWarps * 32) {
+    const int row = i / (N / 2), col = (i % (N / 2)) * 2;
+    float v0 = 0.f, v1 = 0.f;
+#pragma unroll
+    for (int w = 0; w < kWarps; ++w) {
+      v0 += red[w][row][col];
+      v1 += red[w][row][col + 1];
+    }
+    if (m0 + row < M)
+      *reinterpret_cast<__nv_bfloat162*>(out + (size_t)(m0 + row) * ldc + col) =
+          __floats2bfloat162_rn(v0 * alpha, v1 * alpha);
+  }
+}
+
+}  // namespace
+
+extern "C" {
+
+// a [M, K] (row stride lda elements), b [N, K] (row stride ldb), out [M, N] (row stride ldc), bf16.
+// Returns -100 when the shape is outside this kernel's range (the caller uses another kernel).
+int eri_gemm_rank_stream(const void* a, long long lda, const void* b, long long ldb, void* out,
+                         int ldc, int M, int N, int K, float alpha, void* stream) {
+  if (!(N == 16 || N == 32 || N == 64) || M < 1 || K < 256 || K % 32 || lda % 8 || ldb % 8 || ldc % 2)
+    return -100;
+  if ((((uintptr_t)a | (uintptr_t)b) & 15) || ((uintptr_t)out & 3)) return -100;
+  cudaStream_t st = (cudaStream_t)stream;
+  const bf16* pa = (const bf16*)a;
+  const bf16* pb = (const bf16*)b;
+  bf16* po = (bf16*)out;
+  const int grid = (M + 15) / 16;
+  if (N == 16)
+    rank_stream_kernel<2, 4><<<grid, kWarps * 32, 0, st>>>(pa, lda, pb, ldb, po, ldc, M, K, alpha);
+  else if (N == 32)
+    rank_stream_kernel<4, 2><<<grid, kWarps * 32, 0, st>>>(pa, lda, pb, ldb, po, ldc, M, K, alpha);
+  else
+    rank_stream_kernel<8, 1><<<grid, kWarps * 32, 0, st>>>(pa, lda, pb, ldb, po, ldc, M, K, alpha);
+  return (int)cudaGetLastError();
+}
+
+}  // extern "C"

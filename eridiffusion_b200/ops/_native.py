@@ -96,6 +96,7 @@ _SIGNATURES = {
     "eri_dequant_4bit": [_P, _P, _P, _L, _I, _I, _P],
     "eri_gemm_skinny": [_P, _L, _P, _L, _P, _I, _I, _I, _I, _F, _P],
     "eri_gemm_skinny_check_error": [],
+    "eri_gemm_rank_stream": [_P, _L, _P, _L, _P, _I, _I, _I, _I, _F, _P],
     "eri_gemm_init": [],
     "eri_gemm_check_error": [],
     "eri_gemm_bf16": [C.POINTER(GemmArgs), _P],

@@ -17,6 +17,7 @@ _BACKEND = os.environ.get("ERI_B200_BACKEND", "fused")  # "fused" | "eager"
 _GEMM_NATIVE = os.environ.get("ERI_B200_GEMM", "native")  # "native" | "library"
 _ATTN_NATIVE = os.environ.get("ERI_B200_ATTN", "native")  # "native" | "library"
 _GEMM_PAIR = os.environ.get("ERI_B200_GEMM2", "1") == "1"  # two-CTA tiles for large problems
+_RANK_STREAM = os.environ.get("ERI_B200_RANK_STREAM", "1") == "1"  # streaming kernel for [M,K] x [r,K]^T
 
 
 def set_backend(name: str) -> None:
@@ -408,6 +409,14 @@ def skinny_gemm(a, b, alpha=1.0):
     M, K = a.shape
     Nn = b.shape[0]
     lib = N.require()
+    if _RANK_STREAM and hasattr(lib, "eri_gemm_rank_stream") and a.stride(1) == 1 and b.stride(1) == 1:
+        # streaming kernel: bound by reading a once, no operand staging
+        out = torch.empty(M, Nn, dtype=torch.bfloat16, device=a.device)
+        code = lib.eri_gemm_rank_stream(a.data_ptr(), a.stride(0), b.data_ptr(), b.stride(0), out.data_ptr(),
+                                        Nn, M, Nn, K, float(alpha), N.stream_ptr())
+        if code != -100:
+            N.check(code, "gemm_rank_stream")
+            return out
     if hasattr(lib, "eri_gemm_skinny") and a.stride(1) == 1 and b.stride(1) == 1 and M >= 128:
         out = torch.empty(M, Nn, dtype=torch.bfloat16, device=a.device)
         code = lib.eri_gemm_skinny(a.data_ptr(), a.stride(0), b.data_ptr(), b.stride(0), out.data_ptr(),

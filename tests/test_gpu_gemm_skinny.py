@@ -12,6 +12,12 @@ from eridiffusion_b200.ops import functional as F  # noqa: E402
 pytestmark = pytest.mark.gpu
 
 
+@pytest.fixture(autouse=True)
+def _split_k_kernel_only(monkeypatch):
+    """These cases cover the split-K tcgen05 kernel; the streaming kernel has its own file."""
+    monkeypatch.setattr(F, "_RANK_STREAM", False)
+
+
 @pytest.mark.parametrize("M,N,K", [(4608, 16, 3072), (4096, 16, 21504), (512, 16, 3072), (300, 32, 1000),
                                    (128, 64, 512), (5000, 64, 12288), (4608, 16, 15360)])
 def test_skinny_gemm_matches_fp32(M, N, K):
