@@ -1,7 +1,7 @@
 """Small single-kernel workloads for profiler captures (inputs larger than L2, a few hundred MB on
 the device, a handful of launches), one per hot kernel:
 
-    python -m eridiffusion_b200.cli.profile_target gemm|gemm_lora|attn_fwd|attn_bwd|norm|qknorm|adamw|gemv
+    python -m eridiffusion_b200.cli.profile_target gemm|gemm_lora|rank_stream|attn_fwd|attn_bwd|norm|qknorm|adamw|gemv
 
 Meant to be run as ``ncu --set full --clock-control none -k regex:<kernel> -s 2 -c 1 ... python -m
 eridiffusion_b200.cli.profile_target <what>`` after the same command line exited 0 without ncu.
@@ -30,6 +30,14 @@ def main():
             F.gemm_native(a, b, out=out, lora_h=h if what == "gemm_lora" else None,
                           lora_b=lb if what == "gemm_lora" else None)
         assert F.gemm_error_check() == 0
+    elif what == "rank_stream":
+        # LoRA down-projection [M, K] x [16, K]^T; eight different activations so that every launch
+        # reads from DRAM (226 MB in total, larger than L2)
+        xs = [r(4608, 3072) for _ in range(8)]
+        la = r(16, 3072)
+        for x in xs:
+            F.skinny_gemm(x, la, alpha=0.5)
+        assert F.kernel_error_check() == {}
     elif what in ("attn_fwd", "attn_bwd"):
         B, L, H, D = 1, 4608, 24, 128
         q, k, v = r(B, L, H, D), r(B, L, H, D), r(B, L, H, D)

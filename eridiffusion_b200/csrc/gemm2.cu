@@ -16,6 +16,8 @@
 // scatter stay in the single-CTA kernel.
 #include "ptx.cuh"
 #include "tma_host.h"
+#include "gather_copy.cuh"
+#include "gemm_args.h"
 
 using namespace eri;
 typedef __nv_bfloat16 bf16;
@@ -37,6 +39,15 @@ struct Gemm2Params {
   bf16* out2;
   bf16* pre_out;
   int* err;
+  // gather mode (see gather_copy.cuh): the first n_copy CTAs (whole clusters) run copy jobs
+  int n_copy, n_jobs;
+  const GatherJob* jobs;
+  unsigned int* flags;
+  const unsigned int* flag_target;
+  int b_flag_rows;            // rows of B per landing counter (0: B is not gathered)
+  int a_flag_cols;            // K columns per counter of a K-gathered A operand (0: none)
+  int a_flag_rows, a_row_groups;
+  int rot_n, rot_k;           // rotation of the tile order / K order towards the local slab
 };
 
 constexpr int BM = 128;       // rows per CTA (256 per pair)
@@ -107,7 +118,8 @@ __device__ __forceinline__ void umma2_commit_addr(uint32_t bar_cluster_addr) {
       : "memory");
 }
 
-__device__ __forceinline__ void tile_coords(int t, int num_m, int num_n, int& m_blk, int& n_blk) {
+__device__ __forceinline__ void tile_coords(int t, int num_m, int num_n, int rot_n, int& m_blk,
+                                            int& n_blk) {
   const int group_sz = kGroupN * num_m;
   const int g = t / group_sz;
   const int first_n = g * kGroupN;
@@ -115,6 +127,10 @@ __device__ __forceinline__ void tile_coords(int t, int num_m, int num_n, int& m_
   const int r = t - g * group_sz;
   n_blk = first_n + r % gw;
   m_blk = r / gw;
+  if (rot_n) {
+    n_blk += rot_n;
+    if (n_blk >= num_n) n_blk -= num_n;
+  }
 }
 __device__ __forceinline__ float apply_act(float v, int act) {
   return act == 1 ? gelu_tanh_f(v) : act == 2 ? silu_f(v) : v;
@@ -130,6 +146,14 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~uintptr_t(1023));
+  if ((int)blockIdx.x < p.n_copy) {
+    // copy clusters (n_copy is even): both CTAs move slabs and leave; they take no part in the
+    // cluster barriers or the tensor-memory allocation of the compute clusters. The copy ring reuses
+    // the operand stages' shared memory; its barriers sit where the GEMM's do.
+    constexpr int RING = (STAGES * STAGE_BYTES) / kCopyStageBytes;
+    copy_role(p, smem, RING < 6 ? RING : 6, (int)blockIdx.x);
+    return;
+  }
   uint64_t* full = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
   uint64_t* empty = full + STAGES;
   uint64_t* acc_full = empty + STAGES;
@@ -165,7 +189,8 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
   const int num_n = (p.N + BN - 1) / BN;
   const int tiles = num_m * num_n;
   const int k_iters = p.num_k + (p.lora_r > 0 ? 1 : 0);
-  const int cluster_id = blockIdx.x >> 1, num_clusters = gridDim.x >> 1;
+  const int cluster_id = ((int)blockIdx.x - p.n_copy) >> 1;
+  const int num_clusters = ((int)gridDim.x - p.n_copy) >> 1;
 
   if (warp == 0) {
     if (elect_one()) {
@@ -174,9 +199,21 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
       bool ok = true;
       for (int t = cluster_id; t < tiles && ok; t += num_clusters) {
         int m_blk, n_blk;
-        tile_coords(t, num_m, num_n, m_blk, n_blk);
+        tile_coords(t, num_m, num_n, p.rot_n, m_blk, n_blk);
         const int m0 = m_blk * 2 * BM + (int)rank * BM;
         const int n0 = n_blk * BN + (int)rank * BNH;
+        if (p.b_flag_rows) {
+          // every slab that the B rows staged by THIS CTA touch must have landed
+          const int f0 = n0 / p.b_flag_rows, f1 = (min(n0 + BNH, p.N) - 1) / p.b_flag_rows;
+          for (int f = f0; f <= f1 && ok; ++f)
+            if (!wait_slab(p, f)) {
+              atomicExch(p.err, 45);
+              ok = false;
+            }
+          if (!ok) break;
+          fence_proxy_async_all();
+        }
+        int a_ready = -1;
         for (int k = 0; k < k_iters; ++k) {
           if (!mbar_wait(&empty[stage], phase ^ 1)) {
             atomicExch(p.err, 41);
@@ -187,13 +224,28 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
           uint8_t* sB = sA + A_BYTES;
           const uint32_t bar = map_to_cta(smem_u32(&full[stage]), 0);
           if (k < p.num_k) {
+            int kk = k + p.rot_k;
+            if (kk >= p.num_k) kk -= p.num_k;
+            if (p.a_flag_cols) {
+              int f = (kk * BK) / p.a_flag_cols;
+              if (p.a_flag_rows) f = f * p.a_row_groups + min(m0, p.M - 1) / p.a_flag_rows;
+              if (f != a_ready) {
+                if (!wait_slab(p, f)) {
+                  atomicExch(p.err, 46);
+                  ok = false;
+                  break;
+                }
+                fence_proxy_async_all();
+                a_ready = f;
+              }
+            }
             if (leader) mbar_expect_tx(&full[stage], 2 * STAGE_BYTES);
-            tma_load_2d_pair(sA, &tmA, bar, k * BK, m0);
+            tma_load_2d_pair(sA, &tmA, bar, kk * BK, m0);
             if (!p.b_mn) {
-              tma_load_2d_pair(sB, &tmB, bar, k * BK, n0);
+              tma_load_2d_pair(sB, &tmB, bar, kk * BK, n0);
             } else {
-              tma_load_2d_pair(sB, &tmB, bar, n0, k * BK);
-              tma_load_2d_pair(sB + BK * 128, &tmB, bar, n0 + 64, k * BK);
+              tma_load_2d_pair(sB, &tmB, bar, n0, kk * BK);
+              tma_load_2d_pair(sB + BK * 128, &tmB, bar, n0 + 64, kk * BK);
             }
           } else {
             if (leader) mbar_expect_tx(&full[stage], 2 * (BM + BNH) * p.lora_r * 2);
@@ -272,7 +324,7 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     int it = 0;
     for (int t = cluster_id; t < tiles; t += num_clusters, ++it) {
       int m_blk, n_blk;
-      tile_coords(t, num_m, num_n, m_blk, n_blk);
+      tile_coords(t, num_m, num_n, p.rot_n, m_blk, n_blk);
       const int m0 = m_blk * 2 * BM + (int)rank * BM, n0 = n_blk * BN;
       const int buf = it & 1;
       const uint32_t use = (uint32_t)(it >> 1);
@@ -365,23 +417,7 @@ int* g2_err = nullptr;
 
 extern "C" {
 
-struct EriGemmArgs2 {   // same leading layout as EriGemmArgs in gemm.cu (fields used here only)
-  const void* a; const void* b; const void* lora_h; const void* lora_b;
-  const void* bias; const void* residual; const void* gate; const void* pre_in;
-  void* out; void* out2; void* pre_out;
-  long long lda, ldb, ld_h, ld_lb;
-  int M, N, K, lora_r;
-  int act, n_split;
-  int ldc, ldc2, ld_pre, ldr;
-  int rows_per_batch, gate_stride;
-  int force_bn;
-  float alpha;
-  int b_mn;
-  int n_copy, n_jobs;
-  const void* jobs; void* flags; const void* flag_target;
-  int b_flag_rows, a_flag_cols, rot_n_rows, rot_k_cols;
-  int scatter_world;
-};
+typedef EriGemmArgs EriGemmArgs2;
 
 int eri_gemm2_check_error() {
   if (!g2_err) return 0;
@@ -393,7 +429,12 @@ int eri_gemm2_check_error() {
 
 // Returns -30 when the problem does not fit this kernel (caller falls back to eri_gemm_bf16).
 int eri_gemm2_bf16(const EriGemmArgs2* g, void* stream) {
-  if (g->n_copy || g->scatter_world) return -30;
+  if (g->scatter_world || g->rowsq) return -30;
+  if (g->n_copy) {
+    // gather mode: whole copy clusters, rotations in whole pair tiles / K blocks
+    if (g->n_copy % 2 || g->n_copy < 0 || g->n_copy > 64) return -30;
+    if (g->rot_n_rows % BN || g->rot_k_cols % BK || g->a_flag_cols % BK || g->a_flag_rows % BM) return -30;
+  }
   if (g->M < 256 || g->N < 256 || g->K < 64) return -30;
   if (g->K % 8 || g->N % 8 || g->lda % 8 || g->ldb % 8 || g->ldc % 8) return -30;
   if (g->lora_r && g->lora_r != 16 && g->lora_r != 32 && g->lora_r != 64) return -30;
@@ -416,6 +457,11 @@ int eri_gemm2_bf16(const EriGemmArgs2* g, void* stream) {
   p.gate = (const bf16*)g->gate; p.pre_in = (const bf16*)g->pre_in;
   p.out = (bf16*)g->out; p.out2 = (bf16*)g->out2; p.pre_out = (bf16*)g->pre_out;
   p.err = g2_err;
+  p.n_copy = g->n_copy; p.n_jobs = g->n_jobs; p.jobs = (const GatherJob*)g->jobs;
+  p.flags = (unsigned int*)g->flags; p.flag_target = (const unsigned int*)g->flag_target;
+  p.b_flag_rows = g->b_flag_rows; p.a_flag_cols = g->a_flag_cols; p.a_flag_rows = g->a_flag_rows;
+  p.a_row_groups = g->a_flag_rows > 0 ? (g->M + g->a_flag_rows - 1) / g->a_flag_rows : 0;
+  p.rot_n = g->rot_n_rows / BN; p.rot_k = g->rot_k_cols / BK;
 
   CUtensorMap ta, tb, ta2, tb2;
   {
@@ -457,6 +503,39 @@ int eri_gemm2_bf16(const EriGemmArgs2* g, void* stream) {
     configured = true;
   }
   const int tiles = ((g->M + 2 * BM - 1) / (2 * BM)) * ((g->N + BN - 1) / BN);
+  if (p.n_copy > 0) {
+    // The compute clusters spin on counters that the copy clusters bump, so every CTA of the grid
+    // must be resident: the grid is sized by the cluster occupancy query and launched cooperatively.
+    static int coop_clusters = -1;
+    if (coop_clusters < 0) {
+      cudaLaunchConfig_t cfg = {};
+      cfg.gridDim = dim3(g2_num_sms / 2 * 2);
+      cfg.blockDim = dim3(192);
+      cfg.dynamicSmemBytes = SMEM;
+      cudaLaunchAttribute at[1];
+      at[0].id = cudaLaunchAttributeClusterDimension;
+      at[0].val.clusterDim.x = 2; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 1;
+      cfg.attrs = at;
+      cfg.numAttrs = 1;
+      int n = 0;
+      if (cudaOccupancyMaxActiveClusters(&n, gemm2_bf16_kernel, &cfg) != cudaSuccess) {
+        cudaGetLastError();
+        n = 0;
+      }
+      coop_clusters = n;
+    }
+    const int room = coop_clusters - p.n_copy / 2;
+    if (room < 8) return -30;
+    const int clusters = tiles < room ? tiles : room;
+    void* args[] = {(void*)&ta, (void*)&tb, (void*)&ta2, (void*)&tb2, (void*)&p};
+    cudaError_t e = cudaLaunchCooperativeKernel((const void*)gemm2_bf16_kernel, dim3(p.n_copy + clusters * 2),
+                                                dim3(192), args, SMEM, (cudaStream_t)stream);
+    if (e != cudaSuccess) {
+      cudaGetLastError();
+      return -30;   // the caller falls back to the one-CTA kernel
+    }
+    return 0;
+  }
   const int max_clusters = g2_num_sms / 2;
   const int clusters = tiles < max_clusters ? tiles : max_clusters;
   gemm2_bf16_kernel<<<clusters * 2, 192, SMEM, (cudaStream_t)stream>>>(ta, tb, ta2, tb2, p);

@@ -1,0 +1,43 @@
+// Argument block of the GEMM entry points (eri_gemm_bf16, eri_gemm2_bf16); mirrored field by field
+// by ``GemmArgs`` in ops/_native.py.
+#pragma once
+
+constexpr int kMaxPeers = 16;
+
+extern "C" {
+
+struct EriGemmArgs {
+  const void* a;        // [M, K] bf16, row stride lda
+  const void* b;        // [N, K] bf16 (or [K, N] when b_mn), row stride ldb
+  const void* lora_h;   // [M, r] bf16 (row stride ld_h) or null
+  const void* lora_b;   // [N, r] bf16 (row stride ld_lb) or null
+  const void* bias;
+  const void* residual;
+  const void* gate;
+  const void* pre_in;
+  void* out;
+  void* out2;
+  void* pre_out;
+  long long lda, ldb, ld_h, ld_lb;
+  int M, N, K, lora_r;
+  int act, n_split;
+  int ldc, ldc2, ld_pre, ldr;
+  int rows_per_batch, gate_stride;
+  int force_bn;
+  float alpha;
+  int b_mn;
+  // gather mode (all zero / null when unused)
+  int n_copy, n_jobs;
+  const void* jobs;
+  void* flags;
+  const void* flag_target;
+  int b_flag_rows, a_flag_cols, rot_n_rows, rot_k_cols;
+  int a_flag_rows;   // 0, or a multiple of 128: row-group split of the K-range counters
+  // peer scatter
+  int scatter_world, scatter_rank, scatter_part_cols, scatter_group_cols, scatter_local_rows;
+  void* scatter_out[kMaxPeers];
+  void* rowsq;
+  int rowsq_parts;
+};
+
+}  // extern "C"

@@ -17,6 +17,7 @@ _BACKEND = os.environ.get("ERI_B200_BACKEND", "fused")  # "fused" | "eager"
 _GEMM_NATIVE = os.environ.get("ERI_B200_GEMM", "native")  # "native" | "library"
 _ATTN_NATIVE = os.environ.get("ERI_B200_ATTN", "native")  # "native" | "library"
 _GEMM_PAIR = os.environ.get("ERI_B200_GEMM2", "1") == "1"  # two-CTA tiles for large problems
+_GATHER_PAIR = os.environ.get("ERI_B200_GATHER_PAIR", "1") == "1"  # gather-fused GEMMs on the two-CTA kernel
 _RANK_STREAM = os.environ.get("ERI_B200_RANK_STREAM", "1") == "1"  # streaming kernel for [M,K] x [r,K]^T
 
 
@@ -393,8 +394,11 @@ def gemm_native(a, b, *, out=None, alpha=1.0, bias=None, lora_h=None, lora_b=Non
             g.scatter_out[i] = ptr_
         if scatter.get("rowsq") is not None:
             g.rowsq, g.rowsq_parts = scatter["rowsq"].data_ptr(), scatter["rowsq"].shape[0]
-    if _GEMM_PAIR and gather is None and scatter is None and force_bn in (0, 256) and M >= 256 and Nn >= 256:
-        code = lib.eri_gemm2_bf16(g, N.stream_ptr())       # two-CTA 256x256 tiles
+    if _GEMM_PAIR and (gather is None or _GATHER_PAIR) and scatter is None and force_bn in (0, 256) \
+            and M >= 256 and Nn >= 256:
+        # two-CTA 256x256 tiles; in gather mode with whole copy clusters in front (answers -30 when
+        # the gather plan does not line up with pair tiles, and the one-CTA kernel takes over)
+        code = lib.eri_gemm2_bf16(g, N.stream_ptr())
         if code != -30:
             N.check(code, "gemm2_bf16")
             return out
