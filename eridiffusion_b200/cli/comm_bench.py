@@ -24,6 +24,7 @@ import torch
 import torch.distributed as dist
 
 from ..models.layers import Linear
+from ..ops import _native as N_
 from ..ops import functional as F
 from ..optim import AdamW8bit, ParamArena
 from ..parallel.dist import GradSync, ProcessGroup, init_from_env
@@ -151,7 +152,8 @@ def bench_zero3(a, pg, rank, world, dev):
                               "gemm_bound_ms": round(flops / peak * 1e3, 4),
                               "nvlink_bound_ms": round(link_bytes / (LINK_GBS * 1e9) * 1e3, 4),
                               "roofline_ms": round(roof, 4), "fraction_of_roofline": round(roof / t_f, 3),
-                              "gemm_peak": tag, "status": z3.comm.status(), "gemm_err": F.gemm_error_check()}))
+                              "gemm_peak": tag, "status": z3.comm.status(), "gemm_err": F.gemm_error_check(),
+                              "two_cta_gather_launches": N_.require().eri_gemm2_gather_count()}))
 
 
 def bench_ulysses(a, pg, rank, world, dev):
@@ -206,7 +208,8 @@ def bench_ulysses(a, pg, rank, world, dev):
                               "gemm_bound_ms": round(flops / peak * 1e3, 4),
                               "nvlink_bound_ms": round(link_bytes / (LINK_GBS * 1e9) * 1e3, 4),
                               "roofline_ms": round(roof, 4), "fraction_of_roofline": round(roof / t_f, 3),
-                              "gemm_peak": tag, "status": u.comm.status(), "gemm_err": F.gemm_error_check()}))
+                              "gemm_peak": tag, "status": u.comm.status(), "gemm_err": F.gemm_error_check(),
+                              "two_cta_gather_launches": N_.require().eri_gemm2_gather_count()}))
 
 
 def main():

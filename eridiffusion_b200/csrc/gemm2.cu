@@ -412,12 +412,15 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
 
 int g2_num_sms = 0;
 int* g2_err = nullptr;
+long long g2_gather_launches = 0;   // gather-mode launches that ran on this kernel (host counter)
 
 }  // namespace
 
 extern "C" {
 
 typedef EriGemmArgs EriGemmArgs2;
+
+int eri_gemm2_gather_count() { return (int)g2_gather_launches; }
 
 int eri_gemm2_check_error() {
   if (!g2_err) return 0;
@@ -534,6 +537,7 @@ int eri_gemm2_bf16(const EriGemmArgs2* g, void* stream) {
       cudaGetLastError();
       return -30;   // the caller falls back to the one-CTA kernel
     }
+    ++g2_gather_launches;
     return 0;
   }
   const int max_clusters = g2_num_sms / 2;

@@ -102,6 +102,7 @@ _SIGNATURES = {
     "eri_gemm_bf16": [C.POINTER(GemmArgs), _P],
     "eri_gemm2_bf16": [C.POINTER(GemmArgs), _P],
     "eri_gemm2_check_error": [],
+    "eri_gemm2_gather_count": [],
     "eri_gemv_bf16": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P],
 }
 
