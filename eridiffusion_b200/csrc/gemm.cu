@@ -68,6 +68,7 @@ struct GemmParams {
   int a_flag_rows;            // >0: counters also split by row group of the A operand:
   int a_row_groups;           //     index = (k / a_flag_cols) * a_row_groups + m0 / a_flag_rows
   int rot_n, rot_k;           // rotation of tile order / K order towards the local slab
+  int pdl;                    // launched as a programmatic dependent of the kernel that writes lora_h
   // peer scatter epilogue
   int scatter_world;          // 0: off
   int scatter_rank;
@@ -179,6 +180,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
+      bool dep_done = false;
       for (int t = worker; t < tiles && ok; t += nworkers) {
         int m_blk, n_blk;
         tile_coords(t, num_m, num_n, p.rot_n, m_blk, n_blk);
@@ -229,6 +231,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                 tma_load_2d(sB + c * (BK * 128), &tmB, &full[stage], n0 + c * 64, kk * BK);
             }
           } else {
+            // lora_h may still be in production by the previous kernel (dependent launch)
+            if (!dep_done) {
+              griddep_wait();
+              dep_done = true;
+            }
             mbar_expect_tx(&full[stage], (BM + BN) * p.lora_r * 2);
             tma_load_2d(sA, &tmA2, &full[stage], 0, m0);
             tma_load_2d(sB, &tmB2, &full[stage], 0, n0);
@@ -445,6 +452,19 @@ int launch(const CUtensorMap& a, const CUtensorMap& b, const CUtensorMap& a2, co
     return (int)cudaLaunchCooperativeKernel((const void*)gemm_bf16_kernel<BN, STAGES, STAGED>, dim3(grid),
                                             dim3(192), args, SMEM, stream);
   }
+  if (p.pdl && p.lora_r) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3(192);
+    cfg.dynamicSmemBytes = SMEM;
+    cfg.stream = stream;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = at;
+    cfg.numAttrs = 1;
+    return (int)cudaLaunchKernelEx(&cfg, gemm_bf16_kernel<BN, STAGES, STAGED>, a, b, a2, b2, p);
+  }
   gemm_bf16_kernel<BN, STAGES, STAGED><<<grid, 192, SMEM, stream>>>(a, b, a2, b2, p);
   return (int)cudaGetLastError();
 }
@@ -536,6 +556,7 @@ int eri_gemm_bf16(const EriGemmArgs* g, void* stream) {
   p.scatter_local_rows = g->scatter_local_rows > 0 ? g->scatter_local_rows : g->M;
   for (int i = 0; i < kMaxPeers; ++i) p.scatter_out[i] = (bf16*)g->scatter_out[i];
   p.rowsq = (float*)g->rowsq; p.rowsq_parts = g->rowsq_parts;
+  p.pdl = g->pdl;
   if (p.rowsq && p.scatter_part_cols <= 0) return -17;
 
   CUtensorMap ta, tb, ta2, tb2;

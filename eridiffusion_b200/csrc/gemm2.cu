@@ -197,6 +197,7 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
+      bool dep_done = false;
       for (int t = cluster_id; t < tiles && ok; t += num_clusters) {
         int m_blk, n_blk;
         tile_coords(t, num_m, num_n, p.rot_n, m_blk, n_blk);
@@ -248,6 +249,11 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
               tma_load_2d_pair(sB + BK * 128, &tmB, bar, n0 + 64, kk * BK);
             }
           } else {
+            // lora_h may still be in production by the previous kernel (dependent launch)
+            if (!dep_done) {
+              griddep_wait();
+              dep_done = true;
+            }
             if (leader) mbar_expect_tx(&full[stage], 2 * (BM + BNH) * p.lora_r * 2);
             tma_load_2d_pair(sA, &tmA2, bar, 0, m0);
             tma_load_2d_pair(sB, &tmB2, bar, 0, n0);
@@ -542,6 +548,19 @@ int eri_gemm2_bf16(const EriGemmArgs2* g, void* stream) {
   }
   const int max_clusters = g2_num_sms / 2;
   const int clusters = tiles < max_clusters ? tiles : max_clusters;
+  if (g->pdl && g->lora_r) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(clusters * 2);
+    cfg.blockDim = dim3(192);
+    cfg.dynamicSmemBytes = SMEM;
+    cfg.stream = (cudaStream_t)stream;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = at;
+    cfg.numAttrs = 1;
+    return (int)cudaLaunchKernelEx(&cfg, gemm2_bf16_kernel, ta, tb, ta2, tb2, p);
+  }
   gemm2_bf16_kernel<<<clusters * 2, 192, SMEM, (cudaStream_t)stream>>>(ta, tb, ta2, tb2, p);
   return (int)cudaGetLastError();
 }

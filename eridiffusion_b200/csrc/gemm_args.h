@@ -38,6 +38,11 @@ struct EriGemmArgs {
   void* scatter_out[kMaxPeers];
   void* rowsq;
   int rowsq_parts;
+  // 1: launch as a programmatic dependent of the previous kernel on the stream. The caller promises
+  // that this previous kernel is the one that writes lora_h and nothing else this GEMM reads; the
+  // GEMM then starts its main K loop while that kernel still runs and waits for it
+  // (griddepcontrol.wait) only before it loads lora_h for the rank-r step.
+  int pdl;
 };
 
 }  // extern "C"

@@ -54,6 +54,9 @@ rank_stream_kernel(const bf16* __restrict__ a, long long lda, const bf16* __rest
                    long long ldb, bf16* __restrict__ out, int ldc, int M, int K, float alpha) {
   constexpr int N = NT * 8;
   __shared__ float red[kWarps][16][N + 1];
+  // the GEMM that consumes this kernel's output may be scheduled now; it waits for this kernel's
+  // completion only before it reads the output (programmatic dependent launch)
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
   const int m0 = blockIdx.x * 16;
   // rows past the end read the last row (valid memory) and are never stored

@@ -52,6 +52,17 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
+// Programmatic dependent launch: a kernel launched with the programmatic-stream-serialization
+// attribute may start while the previous kernel on the stream still runs; griddep_wait() blocks
+// until that kernel has completed and its writes are visible (a no-op without the attribute).
+// griddep_launch_dependents() in the earlier kernel lets the next one be scheduled right away.
+__device__ __forceinline__ void griddep_wait() {
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+__device__ __forceinline__ void griddep_launch_dependents() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
 __device__ __forceinline__ uint64_t globaltimer_ns() {
   uint64_t t;
   asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));

@@ -45,6 +45,7 @@ class GemmArgs(C.Structure):
         ("scatter_world", C.c_int), ("scatter_rank", C.c_int), ("scatter_part_cols", C.c_int),
         ("scatter_group_cols", C.c_int), ("scatter_local_rows", C.c_int),
         ("scatter_out", C.c_void_p * 16), ("rowsq", C.c_void_p), ("rowsq_parts", C.c_int),
+        ("pdl", C.c_int),
     ]
 
 

@@ -19,6 +19,15 @@ _ATTN_NATIVE = os.environ.get("ERI_B200_ATTN", "native")  # "native" | "library"
 _GEMM_PAIR = os.environ.get("ERI_B200_GEMM2", "1") == "1"  # two-CTA tiles for large problems
 _GATHER_PAIR = os.environ.get("ERI_B200_GATHER_PAIR", "1") == "1"  # gather-fused GEMMs on the two-CTA kernel
 _RANK_STREAM = os.environ.get("ERI_B200_RANK_STREAM", "1") == "1"  # streaming kernel for [M,K] x [r,K]^T
+# Launch the LoRA-fused GEMM as a programmatic dependent of the down-projection kernel that precedes
+# it on the stream: its main K loop overlaps that kernel and only the rank-r step waits for it.
+_PDL = os.environ.get("ERI_B200_PDL", "0") == "1"
+
+
+def _pdl_ok() -> bool:
+    # the overlap is only sound when the down-projection is the launch right before the GEMM;
+    # deterministic mode makes torch.empty launch a fill kernel in between
+    return _PDL and not torch.are_deterministic_algorithms_enabled()
 
 
 def set_backend(name: str) -> None:
@@ -339,7 +348,7 @@ _ACT_CODE = {None: 0, "gelu": 1, "silu": 2, "gelu_bwd": 3, "silu_bwd": 4}
 
 def gemm_native(a, b, *, out=None, alpha=1.0, bias=None, lora_h=None, lora_b=None, act=None,
                 pre_out=None, pre_in=None, residual=None, gate=None, rows_per_batch=0,
-                n_split=0, out2=None, force_bn=0, b_mn=False, gather=None, scatter=None):
+                n_split=0, out2=None, force_bn=0, b_mn=False, gather=None, scatter=None, pdl=False):
     """out[M,N] = epilogue(a[M,K] @ op(b) (+ lora_h[M,r] @ lora_b[N,r]^T)) on the tcgen05 kernel.
 
     ``b`` is [N, K] (``op`` = transpose) or, with ``b_mn=True``, [K, N] used as is. ``a``/``b``/
@@ -380,6 +389,7 @@ def gemm_native(a, b, *, out=None, alpha=1.0, bias=None, lora_h=None, lora_b=Non
         g.out2, g.ldc2 = out2.data_ptr(), out2.stride(0)
     g.force_bn = force_bn
     g.b_mn = 1 if b_mn else 0
+    g.pdl = 1 if (pdl and lora_h is not None and gather is None) else 0
     if gather is not None:
         g.n_copy, g.n_jobs = gather["n_copy"], gather["n_jobs"]
         g.jobs, g.flags, g.flag_target = gather["jobs"], gather["flags"], gather["flag_target"]
@@ -558,13 +568,13 @@ class _FusedLinear(torch.autograd.Function):
         if gate is not None:
             gate_v, _ = _mod_view(gate, Nn)
         if native:
-            if r and lora_fused:
-                h = skinny_gemm(x2, lora_a, alpha=lora_scale)
-            elif r:
-                h = (x2 @ lora_a.t()) * lora_scale
             need_pre = act is not None and any(ctx.needs_input_grad[:5])
             if need_pre:
                 pre = torch.empty(M, Nn, dtype=x.dtype, device=x.device)
+            if r and lora_fused:
+                h = skinny_gemm(x2, lora_a, alpha=lora_scale)     # the launch right before the GEMM
+            elif r:
+                h = (x2 @ lora_a.t()) * lora_scale
             if r and not lora_fused:
                 y = gemm_native(x2, w, bias=bias)
                 y = y + h @ lora_b.t()
@@ -577,7 +587,7 @@ class _FusedLinear(torch.autograd.Function):
             else:
                 y = gemm_native(x2, w, bias=bias, lora_h=h, lora_b=lora_b if r else None,
                                 act=act, pre_out=pre, residual=res2, gate=gate_v,
-                                rows_per_batch=L)
+                                rows_per_batch=L, pdl=_pdl_ok())
         else:
             y = torch.nn.functional.linear(x2, w, bias)
             if r:
@@ -629,10 +639,13 @@ class _FusedLinear(torch.autograd.Function):
         r = 0 if lora_a is None else lora_a.shape[0]
         native = lib is not None and _GEMM_NATIVE == "native" and gemm_supported(M, K, Nn)
         ts = None
+        la_t = None
         if r:
             # Ts = s * dY B  [M, r]
             if native and r in (16, 32, 64):
-                ts = skinny_gemm(dy2, _lora_transposed(lora_b), alpha=s)
+                # both transposes are looked up first: nothing may launch between Ts and the dX GEMM
+                lb_t, la_t = _lora_transposed(lora_b), _lora_transposed(lora_a)
+                ts = skinny_gemm(dy2, lb_t, alpha=s)
             else:
                 ts = (dy2 @ lora_b) * s
         if need[0]:
@@ -640,10 +653,12 @@ class _FusedLinear(torch.autograd.Function):
                 # dX = dY W: with a cached transpose W^T is a K-major operand, otherwise W itself
                 # is read as the MN-major operand (no copy).
                 b_op, mn = (wt, False) if wt is not None else (w, True)
-                if mn and K < 64:
-                    b_op, mn = w.t().contiguous(), False
+                copied = mn and K < 64
+                if copied:
+                    b_op, mn = w.t().contiguous(), False       # a launch between Ts and the GEMM
                 if r in (16, 32, 64):
-                    dx = gemm_native(dy2, b_op, b_mn=mn, lora_h=ts, lora_b=_lora_transposed(lora_a))
+                    dx = gemm_native(dy2, b_op, b_mn=mn, lora_h=ts, lora_b=la_t,
+                                     pdl=_pdl_ok() and not copied)
                 else:
                     dx = gemm_native(dy2, b_op, b_mn=mn)
                     if r:
