@@ -75,25 +75,38 @@ rank_stream_kernel(const bf16* __restrict__ a, long long lda, const bf16* __rest
 #pragma unroll
     for (int i = 0; i < 4; ++i) acc[j][i] = 0.f;
 
-  for (int s = s_begin; s < s_end; s += U) {
-    uint4 va0[U], va1[U], vb[U][NT];
+  // Software pipeline over batches of U steps: the loads of a for batch i + 1 are issued before the
+  // products of batch i, so every thread keeps 2 * U * 32 bytes of a in flight across the loop; b
+  // comes from L1 / L2 right before its use.
+  uint4 cur0[U], cur1[U], nxt0[U], nxt1[U];
+  auto load_a = [&](uint4 (&v0)[U], uint4 (&v1)[U], int s) {
 #pragma unroll
     for (int u = 0; u < U; ++u) {
       const int ss = min(s + u, s_end - 1);       // the tail repeats a step; its product is dropped
-      va0[u] = ld_stream16(pa0 + 4 * ss);
-      va1[u] = ld_stream16(pa1 + 4 * ss);
-#pragma unroll
-      for (int j = 0; j < NT; ++j) vb[u][j] = ld_cached16(pb + j * b_tile + 4 * ss);
+      v0[u] = ld_stream16(pa0 + 4 * ss);
+      v1[u] = ld_stream16(pa1 + 4 * ss);
     }
+  };
+  if (s_begin < s_end) load_a(cur0, cur1, s_begin);
+  for (int s = s_begin; s < s_end; s += U) {
+    if (s + U < s_end) load_a(nxt0, nxt1, s + U);
 #pragma unroll
     for (int u = 0; u < U; ++u) {
       if (s + u < s_end) {
+        uint4 vb[NT];
+#pragma unroll
+        for (int j = 0; j < NT; ++j) vb[j] = ld_cached16(pb + j * b_tile + 4 * (s + u));
 #pragma unroll
         for (int j = 0; j < NT; ++j) {
-          mma16816(acc[j], va0[u].x, va1[u].x, va0[u].y, va1[u].y, vb[u][j].x, vb[u][j].y);
-          mma16816(acc[j], va0[u].z, va1[u].z, va0[u].w, va1[u].w, vb[u][j].z, vb[u][j].w);
+          mma16816(acc[j], cur0[u].x, cur1[u].x, cur0[u].y, cur1[u].y, vb[j].x, vb[j].y);
+          mma16816(acc[j], cur0[u].z, cur1[u].z, cur0[u].w, cur1[u].w, vb[j].z, vb[j].w);
         }
       }
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      cur0[u] = nxt0[u];
+      cur1[u] = nxt1[u];
     }
   }
 #pragma unroll
@@ -138,9 +151,9 @@ int eri_gemm_rank_stream(const void* a, long long lda, const void* b, long long 
   if (N == 16)
     rank_stream_kernel<2, 4><<<grid, kWarps * 32, 0, st>>>(pa, lda, pb, ldb, po, ldc, M, K, alpha);
   else if (N == 32)
-    rank_stream_kernel<4, 2><<<grid, kWarps * 32, 0, st>>>(pa, lda, pb, ldb, po, ldc, M, K, alpha);
+    rank_stream_kernel<4, 4><<<grid, kWarps * 32, 0, st>>>(pa, lda, pb, ldb, po, ldc, M, K, alpha);
   else
-    rank_stream_kernel<8, 1><<<grid, kWarps * 32, 0, st>>>(pa, lda, pb, ldb, po, ldc, M, K, alpha);
+    rank_stream_kernel<8, 2><<<grid, kWarps * 32, 0, st>>>(pa, lda, pb, ldb, po, ldc, M, K, alpha);
   return (int)cudaGetLastError();
 }
 

@@ -21,7 +21,7 @@ _GATHER_PAIR = os.environ.get("ERI_B200_GATHER_PAIR", "1") == "1"  # gather-fuse
 _RANK_STREAM = os.environ.get("ERI_B200_RANK_STREAM", "1") == "1"  # streaming kernel for [M,K] x [r,K]^T
 # Launch the LoRA-fused GEMM as a programmatic dependent of the down-projection kernel that precedes
 # it on the stream: its main K loop overlaps that kernel and only the rank-r step waits for it.
-_PDL = os.environ.get("ERI_B200_PDL", "0") == "1"
+_PDL = os.environ.get("ERI_B200_PDL", "1") == "1"
 
 
 def _pdl_ok() -> bool:
