@@ -140,7 +140,11 @@ __device__ void copy_role(const P& p, uint8_t* smem, int ring_stages, int cta) {
       }
     }
   } else if (warp == 1) {
-    int it = 0;
+    // Up to kStoreDepth stores stay in flight: a stage goes back to the loader once the store that
+    // reads it is no longer among the kStoreDepth - 1 youngest groups (one store at a time capped a
+    // CTA at one 32 KB chunk per store latency, ~20 GB/s).
+    constexpr int kStoreDepth = 3;
+    int it = 0, released = 0;
     bool ok = true;
     for (int j = cta; j < p.n_jobs && ok; j += p.n_copy) {
       const GatherJob job = p.jobs[j];
@@ -168,13 +172,16 @@ __device__ void copy_role(const P& p, uint8_t* smem, int ring_stages, int cta) {
                            src + (uint32_t)r * (uint32_t)job.row_bytes, (uint32_t)job.row_bytes);
         }
         tma_store_commit();
-        tma_store_wait_read<0>();      // the stage has been read: the loader may refill it
+        tma_store_wait_read<kStoreDepth - 1>();   // all but the youngest groups have read their stage
         __syncwarp();
-        if (lane == 0) mbar_arrive(&empty[s]);
+        for (; released <= it - (kStoreDepth - 1); ++released)
+          if (lane == 0) mbar_arrive(&empty[released % ring_stages]);
       }
       // the whole job has landed in local memory before its counter moves
       tma_store_wait<0>();
       __syncwarp();
+      for (; released < it; ++released)
+        if (lane == 0) mbar_arrive(&empty[released % ring_stages]);
       if (lane == 0 && ok) {
         __threadfence();
         fence_proxy_async_all();

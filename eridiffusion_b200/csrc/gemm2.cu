@@ -48,6 +48,9 @@ struct Gemm2Params {
   int a_flag_cols;            // K columns per counter of a K-gathered A operand (0: none)
   int a_flag_rows, a_row_groups;
   int rot_n, rot_k;           // rotation of the tile order / K order towards the local slab
+  // 1: B rows [loc_lo, loc_hi) are read from this rank's own shard (tensor map tmBL, row - loc_lo);
+  // 2: K range [loc_lo, loc_hi) of an MN-major B likewise. Those slabs have no copy jobs.
+  int loc_mode, loc_lo, loc_hi;
 };
 
 constexpr int BM = 128;       // rows per CTA (256 per pair)
@@ -142,7 +145,7 @@ __device__ __forceinline__ float apply_act_grad(float pre, int act) {
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(192, 1)
 gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                   const __grid_constant__ CUtensorMap tmA2, const __grid_constant__ CUtensorMap tmB2,
-                  const __grid_constant__ Gemm2Params p) {
+                  const __grid_constant__ CUtensorMap tmBL, const __grid_constant__ Gemm2Params p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~uintptr_t(1023));
@@ -203,7 +206,8 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
         tile_coords(t, num_m, num_n, p.rot_n, m_blk, n_blk);
         const int m0 = m_blk * 2 * BM + (int)rank * BM;
         const int n0 = n_blk * BN + (int)rank * BNH;
-        if (p.b_flag_rows) {
+        const bool b_rows_local = p.loc_mode == 1 && n0 >= p.loc_lo && n0 + BNH <= p.loc_hi;
+        if (p.b_flag_rows && !b_rows_local) {
           // every slab that the B rows staged by THIS CTA touch must have landed
           const int f0 = n0 / p.b_flag_rows, f1 = (min(n0 + BNH, p.N) - 1) / p.b_flag_rows;
           for (int f = f0; f <= f1 && ok; ++f)
@@ -227,7 +231,8 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
           if (k < p.num_k) {
             int kk = k + p.rot_k;
             if (kk >= p.num_k) kk -= p.num_k;
-            if (p.a_flag_cols) {
+            const bool k_local = p.loc_mode == 2 && kk * BK >= p.loc_lo && kk * BK + BK <= p.loc_hi;
+            if (p.a_flag_cols && !k_local) {
               int f = (kk * BK) / p.a_flag_cols;
               if (p.a_flag_rows) f = f * p.a_row_groups + min(m0, p.M - 1) / p.a_flag_rows;
               if (f != a_ready) {
@@ -243,10 +248,13 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
             if (leader) mbar_expect_tx(&full[stage], 2 * STAGE_BYTES);
             tma_load_2d_pair(sA, &tmA, bar, kk * BK, m0);
             if (!p.b_mn) {
-              tma_load_2d_pair(sB, &tmB, bar, kk * BK, n0);
+              if (b_rows_local) tma_load_2d_pair(sB, &tmBL, bar, kk * BK, n0 - p.loc_lo);
+              else tma_load_2d_pair(sB, &tmB, bar, kk * BK, n0);
             } else {
-              tma_load_2d_pair(sB, &tmB, bar, n0, kk * BK);
-              tma_load_2d_pair(sB + BK * 128, &tmB, bar, n0 + 64, kk * BK);
+              const CUtensorMap* tb = k_local ? &tmBL : &tmB;
+              const int ky = k_local ? kk * BK - p.loc_lo : kk * BK;
+              tma_load_2d_pair(sB, tb, bar, n0, ky);
+              tma_load_2d_pair(sB + BK * 128, tb, bar, n0 + 64, ky);
             }
           } else {
             // lora_h may still be in production by the previous kernel (dependent launch)
@@ -471,6 +479,15 @@ int eri_gemm2_bf16(const EriGemmArgs2* g, void* stream) {
   p.b_flag_rows = g->b_flag_rows; p.a_flag_cols = g->a_flag_cols; p.a_flag_rows = g->a_flag_rows;
   p.a_row_groups = g->a_flag_rows > 0 ? (g->M + g->a_flag_rows - 1) / g->a_flag_rows : 0;
   p.rot_n = g->rot_n_rows / BN; p.rot_k = g->rot_k_cols / BK;
+  const bool use_local = g->n_copy && g->b_local && g->jobs_nl && g->flag_target_nl &&
+                         !(((uintptr_t)g->b_local) & 15) && g->ldb_local % 8 == 0 &&
+                         ((g->loc_mode == 1 && !g->b_mn && g->loc_lo % BNH == 0 && g->loc_hi % BNH == 0) ||
+                          (g->loc_mode == 2 && g->b_mn && g->loc_lo % BK == 0 && g->loc_hi % BK == 0));
+  if (use_local) {
+    p.loc_mode = g->loc_mode; p.loc_lo = g->loc_lo; p.loc_hi = g->loc_hi;
+    p.n_jobs = g->n_jobs_nl; p.jobs = (const GatherJob*)g->jobs_nl;
+    p.flag_target = (const unsigned int*)g->flag_target_nl;
+  }
 
   CUtensorMap ta, tb, ta2, tb2;
   {
@@ -502,6 +519,20 @@ int eri_gemm2_bf16(const EriGemmArgs2* g, void* stream) {
   } else {
     ta2 = ta;
     tb2 = tb;
+  }
+  CUtensorMap tbl = tb;
+  if (use_local) {
+    const uint64_t rows = (uint64_t)(g->loc_hi - g->loc_lo);
+    uint64_t s[1] = {(uint64_t)g->ldb_local * 2};
+    if (g->loc_mode == 1) {
+      uint64_t d[2] = {(uint64_t)g->K, rows};
+      uint32_t bx[2] = {BK, BNH};
+      if (make_tensor_map(&tbl, g->b_local, 2, d, s, bx, 128)) return -33;
+    } else {
+      uint64_t d[2] = {(uint64_t)g->N, rows};
+      uint32_t bx[2] = {64, BK};
+      if (make_tensor_map(&tbl, g->b_local, 2, d, s, bx, 128)) return -33;
+    }
   }
   constexpr int SMEM = STAGES * STAGE_BYTES + 1024 + 256;
   static bool configured = false;
@@ -536,7 +567,7 @@ int eri_gemm2_bf16(const EriGemmArgs2* g, void* stream) {
     const int room = coop_clusters - p.n_copy / 2;
     if (room < 8) return -30;
     const int clusters = tiles < room ? tiles : room;
-    void* args[] = {(void*)&ta, (void*)&tb, (void*)&ta2, (void*)&tb2, (void*)&p};
+    void* args[] = {(void*)&ta, (void*)&tb, (void*)&ta2, (void*)&tb2, (void*)&tbl, (void*)&p};
     cudaError_t e = cudaLaunchCooperativeKernel((const void*)gemm2_bf16_kernel, dim3(p.n_copy + clusters * 2),
                                                 dim3(192), args, SMEM, (cudaStream_t)stream);
     if (e != cudaSuccess) {
@@ -559,9 +590,9 @@ int eri_gemm2_bf16(const EriGemmArgs2* g, void* stream) {
     at[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = at;
     cfg.numAttrs = 1;
-    return (int)cudaLaunchKernelEx(&cfg, gemm2_bf16_kernel, ta, tb, ta2, tb2, p);
+    return (int)cudaLaunchKernelEx(&cfg, gemm2_bf16_kernel, ta, tb, ta2, tb2, tbl, p);
   }
-  gemm2_bf16_kernel<<<clusters * 2, 192, SMEM, (cudaStream_t)stream>>>(ta, tb, ta2, tb2, p);
+  gemm2_bf16_kernel<<<clusters * 2, 192, SMEM, (cudaStream_t)stream>>>(ta, tb, ta2, tb2, tbl, p);
   return (int)cudaGetLastError();
 }
 

@@ -43,6 +43,15 @@ struct EriGemmArgs {
   // GEMM then starts its main K loop while that kernel still runs and waits for it
   // (griddepcontrol.wait) only before it loads lora_h for the rank-r step.
   int pdl;
+  // Gather mode, optional: this rank's own slab of the gathered B operand is read in place through
+  // a second tensor map instead of being copied into the landing buffer (two-CTA kernel only; the
+  // *_nl job list and targets leave the local slab's jobs out).
+  const void* b_local;        // this rank's shard: rows [loc_lo, loc_hi) of B (loc_mode 1), or of the
+  long long ldb_local;        // K dimension of an MN-major B (loc_mode 2); row stride in elements
+  int loc_mode, loc_lo, loc_hi;
+  int n_jobs_nl;
+  const void* jobs_nl;
+  const void* flag_target_nl;
 };
 
 }  // extern "C"

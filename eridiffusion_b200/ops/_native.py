@@ -46,6 +46,9 @@ class GemmArgs(C.Structure):
         ("scatter_group_cols", C.c_int), ("scatter_local_rows", C.c_int),
         ("scatter_out", C.c_void_p * 16), ("rowsq", C.c_void_p), ("rowsq_parts", C.c_int),
         ("pdl", C.c_int),
+        ("b_local", C.c_void_p), ("ldb_local", C.c_longlong),
+        ("loc_mode", C.c_int), ("loc_lo", C.c_int), ("loc_hi", C.c_int), ("n_jobs_nl", C.c_int),
+        ("jobs_nl", C.c_void_p), ("flag_target_nl", C.c_void_p),
     ]
 
 

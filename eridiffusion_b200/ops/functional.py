@@ -18,6 +18,7 @@ _GEMM_NATIVE = os.environ.get("ERI_B200_GEMM", "native")  # "native" | "library"
 _ATTN_NATIVE = os.environ.get("ERI_B200_ATTN", "native")  # "native" | "library"
 _GEMM_PAIR = os.environ.get("ERI_B200_GEMM2", "1") == "1"  # two-CTA tiles for large problems
 _GATHER_PAIR = os.environ.get("ERI_B200_GATHER_PAIR", "1") == "1"  # gather-fused GEMMs on the two-CTA kernel
+_GATHER_LOCAL = os.environ.get("ERI_B200_GATHER_LOCAL", "1") == "1"  # own slab read in place, not copied
 _RANK_STREAM = os.environ.get("ERI_B200_RANK_STREAM", "1") == "1"  # streaming kernel for [M,K] x [r,K]^T
 # Launch the LoRA-fused GEMM as a programmatic dependent of the down-projection kernel that precedes
 # it on the stream: its main K loop overlaps that kernel and only the rank-r step waits for it.
@@ -396,6 +397,11 @@ def gemm_native(a, b, *, out=None, alpha=1.0, bias=None, lora_h=None, lora_b=Non
         g.b_flag_rows, g.a_flag_cols = gather.get("b_flag_rows", 0), gather.get("a_flag_cols", 0)
         g.rot_n_rows, g.rot_k_cols = gather.get("rot_n_rows", 0), gather.get("rot_k_cols", 0)
         g.a_flag_rows = gather.get("a_flag_rows", 0)
+        loc = gather.get("local") if _GATHER_LOCAL else None
+        if loc is not None:
+            g.b_local, g.ldb_local = loc["ptr"], loc["ld"]
+            g.loc_mode, g.loc_lo, g.loc_hi = loc["mode"], loc["lo"], loc["hi"]
+            g.n_jobs_nl, g.jobs_nl, g.flag_target_nl = loc["n_jobs"], loc["jobs"], loc["flag_target"]
     if scatter is not None:
         g.scatter_world, g.scatter_rank = scatter["world"], scatter["rank"]
         g.scatter_part_cols, g.scatter_group_cols = scatter["part_cols"], scatter["group_cols"]

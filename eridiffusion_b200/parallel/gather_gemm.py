@@ -29,8 +29,11 @@ class GatherPlan:
         self.rank, self.world, self.n_copy = rank, world, n_copy
         self.device = device or torch.device("cuda", torch.cuda.current_device())
         self.jobs = []
+        self.jobs_nl = []                 # the same jobs without this rank's own slab
         n_flags = n_flags or world
         self.targets = [0] * n_flags
+        self.targets_nl = [0] * n_flags
+        self.local = None                 # dict(ptr, ld, mode, lo, hi): own slab readable in place
         self._dev_jobs = None
         self.flags = torch.zeros(n_flags, dtype=torch.int32, device=self.device)
         self._targets_dev = None
@@ -47,6 +50,9 @@ class GatherPlan:
         j.src_stride, j.dst_stride, j.flag = src_stride, dst_stride, flag
         self.jobs.append(j)
         self.targets[flag] += 1
+        if remote:
+            self.jobs_nl.append(j)
+            self.targets_nl[flag] += 1
 
     @classmethod
     def rows(cls, rank, world, shard_ptrs, landing: torch.Tensor, along_k=False, n_copy=16,
@@ -74,6 +80,8 @@ class GatherPlan:
             pl.kw = dict(a_flag_cols=flag_rows, rot_k_cols=rank * per)
         else:
             pl.kw = dict(b_flag_rows=flag_rows, rot_n_rows=rank * per)
+        # the own shard can feed the GEMM in place (second tensor map) when the kernel supports it
+        pl.local = dict(ptr=shard_ptrs[rank], ld=K, mode=2 if along_k else 1, lo=rank * per, hi=(rank + 1) * per)
         return pl._finish()
 
     @classmethod
@@ -104,14 +112,24 @@ class GatherPlan:
         raw = bytes(arr)
         self._dev_jobs = torch.frombuffer(bytearray(raw), dtype=torch.uint8).to(self.device)
         self._targets_dev = torch.tensor(self.targets, dtype=torch.int32, device=self.device)
+        if self.local is not None and self.jobs_nl:
+            arr = (N.GatherJob * len(self.jobs_nl))(*self.jobs_nl)
+            self._dev_jobs_nl = torch.frombuffer(bytearray(bytes(arr)), dtype=torch.uint8).to(self.device)
+            self._targets_nl_dev = torch.tensor(self.targets_nl, dtype=torch.int32, device=self.device)
+        else:
+            self.local = None
         return self
 
     def launch_args(self):
         """Zero the slab counters (stream-ordered) and return the ``gather=`` dict for
         ``ops.functional.gemm_native``."""
         self.flags.zero_()
-        return dict(n_copy=self.n_copy, n_jobs=len(self.jobs), jobs=self._dev_jobs.data_ptr(),
-                    flags=self.flags.data_ptr(), flag_target=self._targets_dev.data_ptr(), **self.kw)
+        d = dict(n_copy=self.n_copy, n_jobs=len(self.jobs), jobs=self._dev_jobs.data_ptr(),
+                 flags=self.flags.data_ptr(), flag_target=self._targets_dev.data_ptr(), **self.kw)
+        if self.local is not None:
+            d["local"] = dict(self.local, n_jobs=len(self.jobs_nl), jobs=self._dev_jobs_nl.data_ptr(),
+                              flag_target=self._targets_nl_dev.data_ptr())
+        return d
 
     def bytes_from_peers(self):
         return self.remote_bytes

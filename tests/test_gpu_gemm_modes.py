@@ -38,7 +38,10 @@ def test_gather_rows_forward(rank):
     out = F.gemm_native(x, landing, gather=plan.launch_args())
     assert F.gemm_error_check() == 0
     w = torch.cat(shards, 0)
-    assert torch.equal(landing, w)
+    per = N // W
+    for p in range(W):                       # the own slab may be read in place and never land
+        if p != rank:
+            assert torch.equal(landing[p * per:(p + 1) * per], shards[p])
     close(out, x.float() @ w.float().t(), 0.05)
 
 
