@@ -49,7 +49,8 @@ struct Gemm2Params {
   int a_flag_rows, a_row_groups;
   int rot_n, rot_k;           // rotation of the tile order / K order towards the local slab
   // 1: B rows [loc_lo, loc_hi) are read from this rank's own shard (tensor map tmBL, row - loc_lo);
-  // 2: K range [loc_lo, loc_hi) of an MN-major B likewise. Those slabs have no copy jobs.
+  // 2: K range [loc_lo, loc_hi) of an MN-major B likewise; 3: K range [loc_lo, loc_hi) of the A
+  // operand (tmBL then maps A[:, loc_lo:loc_hi] in its home buffer). Those slabs have no copy jobs.
   int loc_mode, loc_lo, loc_hi;
 };
 
@@ -231,7 +232,7 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
           if (k < p.num_k) {
             int kk = k + p.rot_k;
             if (kk >= p.num_k) kk -= p.num_k;
-            const bool k_local = p.loc_mode == 2 && kk * BK >= p.loc_lo && kk * BK + BK <= p.loc_hi;
+            const bool k_local = p.loc_mode >= 2 && kk * BK >= p.loc_lo && kk * BK + BK <= p.loc_hi;
             if (p.a_flag_cols && !k_local) {
               int f = (kk * BK) / p.a_flag_cols;
               if (p.a_flag_rows) f = f * p.a_row_groups + min(m0, p.M - 1) / p.a_flag_rows;
@@ -246,13 +247,15 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
               }
             }
             if (leader) mbar_expect_tx(&full[stage], 2 * STAGE_BYTES);
-            tma_load_2d_pair(sA, &tmA, bar, kk * BK, m0);
+            if (p.loc_mode == 3 && k_local) tma_load_2d_pair(sA, &tmBL, bar, kk * BK - p.loc_lo, m0);
+            else tma_load_2d_pair(sA, &tmA, bar, kk * BK, m0);
             if (!p.b_mn) {
               if (b_rows_local) tma_load_2d_pair(sB, &tmBL, bar, kk * BK, n0 - p.loc_lo);
               else tma_load_2d_pair(sB, &tmB, bar, kk * BK, n0);
             } else {
-              const CUtensorMap* tb = k_local ? &tmBL : &tmB;
-              const int ky = k_local ? kk * BK - p.loc_lo : kk * BK;
+              const bool bl = k_local && p.loc_mode == 2;
+              const CUtensorMap* tb = bl ? &tmBL : &tmB;
+              const int ky = bl ? kk * BK - p.loc_lo : kk * BK;
               tma_load_2d_pair(sB, tb, bar, n0, ky);
               tma_load_2d_pair(sB + BK * 128, tb, bar, n0 + 64, ky);
             }
@@ -482,7 +485,8 @@ int eri_gemm2_bf16(const EriGemmArgs2* g, void* stream) {
   const bool use_local = g->n_copy && g->b_local && g->jobs_nl && g->flag_target_nl &&
                          !(((uintptr_t)g->b_local) & 15) && g->ldb_local % 8 == 0 &&
                          ((g->loc_mode == 1 && !g->b_mn && g->loc_lo % BNH == 0 && g->loc_hi % BNH == 0) ||
-                          (g->loc_mode == 2 && g->b_mn && g->loc_lo % BK == 0 && g->loc_hi % BK == 0));
+                          (g->loc_mode == 2 && g->b_mn && g->loc_lo % BK == 0 && g->loc_hi % BK == 0) ||
+                          (g->loc_mode == 3 && g->loc_lo % BK == 0 && g->loc_hi % BK == 0));
   if (use_local) {
     p.loc_mode = g->loc_mode; p.loc_lo = g->loc_lo; p.loc_hi = g->loc_hi;
     p.n_jobs = g->n_jobs_nl; p.jobs = (const GatherJob*)g->jobs_nl;
@@ -528,9 +532,13 @@ int eri_gemm2_bf16(const EriGemmArgs2* g, void* stream) {
       uint64_t d[2] = {(uint64_t)g->K, rows};
       uint32_t bx[2] = {BK, BNH};
       if (make_tensor_map(&tbl, g->b_local, 2, d, s, bx, 128)) return -33;
-    } else {
+    } else if (g->loc_mode == 2) {
       uint64_t d[2] = {(uint64_t)g->N, rows};
       uint32_t bx[2] = {64, BK};
+      if (make_tensor_map(&tbl, g->b_local, 2, d, s, bx, 128)) return -33;
+    } else {
+      uint64_t d[2] = {rows, (uint64_t)g->M};      // A[:, loc_lo:loc_hi] in its home buffer
+      uint32_t bx[2] = {BK, BM};
       if (make_tensor_map(&tbl, g->b_local, 2, d, s, bx, 128)) return -33;
     }
   }

@@ -105,6 +105,9 @@ class GatherPlan:
             r0 += nr
         # one counter per (column block, 128-row group): a tile waits for its own rows only
         pl.kw = dict(a_flag_cols=Cc, rot_k_cols=rank * Cc, a_flag_rows=rows_per_job)
+        # this rank's own column block can be read where it lives (mode 3: K range of the A operand)
+        pl.local = dict(ptr=src_ptrs[rank] + src_row_offset * src_stride_bytes, ld=src_stride_bytes // es,
+                        mode=3, lo=rank * Cc, hi=(rank + 1) * Cc)
         return pl._finish()
 
     def _finish(self):

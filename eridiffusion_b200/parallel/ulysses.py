@@ -82,6 +82,10 @@ class UlyssesContext:
                                     remote=p != self.rank)
             # K blocks are ordered [part][peer]; one counter per (part, peer, 128-row group)
             pl.kw = dict(a_flag_cols=G, rot_k_cols=self.rank * G, a_flag_rows=128 if fine else 0)
+            if parts == 1 and self.B == 1:
+                # this rank's own column block is read from its home buffer, not copied
+                pl.local = dict(ptr=src_sym.peer_ptrs[self.rank] + self.rank * self.Ll * G * es, ld=G, mode=3,
+                                lo=self.rank * G, hi=(self.rank + 1) * G)
             pl._finish()
             self._plans[k] = pl
         return pl
@@ -160,13 +164,18 @@ class _UlyssesOutProj(torch.autograd.Function):
         if gate is not None:
             gate_v, _ = F._mod_view(gate, D)
         h = None
+        ga = pl.launch_args()
+        # A is kept for the weight / adapter gradients (and read again by the second GEMM of the
+        # LoRA path), so it must land completely; only when nothing reads it afterwards may the
+        # kernel take this rank's own column block from where it lives instead of copying it
+        if la is not None or any(ctx.needs_input_grad[i] for i in (1, 3, 4)):
+            ga.pop("local", None)
         if la is not None:
-            h = F.gemm_native(A, la, alpha=ls, gather=pl.launch_args())              # lands A
+            h = F.gemm_native(A, la, alpha=ls, gather=ga)                            # lands A
             y = F.gemm_native(A, w, bias=bias, lora_h=h, lora_b=lb, residual=res2, gate=gate_v,
                               rows_per_batch=Ll)
         else:
-            y = F.gemm_native(A, w, bias=bias, residual=res2, gate=gate_v, rows_per_batch=Ll,
-                              gather=pl.launch_args())
+            y = F.gemm_native(A, w, bias=bias, residual=res2, gate=gate_v, rows_per_batch=Ll, gather=ga)
         u.nvlink_bytes += B * Ll * D * 2 * (W - 1) // W
         ctx.save_for_backward(A, w, gate_v, la, lb, h)
         ctx.u, ctx.has_res, ctx.has_bias, ctx.ls = u, residual is not None, bias is not None, ls

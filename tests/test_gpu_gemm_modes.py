@@ -68,7 +68,9 @@ def test_gather_cols_reverse_all_to_all():
     out = F.gemm_native(landing, wo, gather=plan.launch_args())
     assert F.gemm_error_check() == 0
     a = torch.cat([s[rank * L:(rank + 1) * L] for s in srcs], 1)
-    assert torch.equal(landing, a)
+    for p in range(W):                       # the own column block may be read in place and never land
+        if p != rank:
+            assert torch.equal(landing[:, p * Cc:(p + 1) * Cc], a[:, p * Cc:(p + 1) * Cc])
     close(out, a.float() @ wo.float().t(), 0.05)
 
 
