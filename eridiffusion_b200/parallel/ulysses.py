@@ -151,7 +151,7 @@ class _UlyssesOutProj(torch.autograd.Function):
     A[:, p-block] taken from peer p."""
 
     @staticmethod
-    def forward(ctx, attn, w, bias, la, lb, ls, u, residual, gate):
+    def forward(ctx, attn, w, bias, la, lb, ls, u, residual, gate, keep_a=True):
         B, Ll, D = u.B, u.Ll, u.D
         W = u.world
         u.barrier()
@@ -168,7 +168,7 @@ class _UlyssesOutProj(torch.autograd.Function):
         # A is kept for the weight / adapter gradients (and read again by the second GEMM of the
         # LoRA path), so it must land completely; only when nothing reads it afterwards may the
         # kernel take this rank's own column block from where it lives instead of copying it
-        if la is not None or any(ctx.needs_input_grad[i] for i in (1, 3, 4)):
+        if la is not None or (keep_a and any(ctx.needs_input_grad[i] for i in (1, 3, 4))):
             ga.pop("local", None)
         if la is not None:
             h = F.gemm_native(A, la, alpha=ls, gather=ga)                            # lands A
@@ -201,7 +201,7 @@ class _UlyssesOutProj(torch.autograd.Function):
         db = dy2.sum(0) if (ctx.has_bias and ctx.needs_input_grad[2]) else None
         da = ts.t() @ A if (la is not None and ctx.needs_input_grad[3]) else None
         db_ = dy2.t() @ h if (la is not None and ctx.needs_input_grad[4]) else None
-        return d_attn, dw, db, da, db_, None, None, d_res, None
+        return d_attn, dw, db, da, db_, None, None, d_res, None, None
 
 
 def _lora_of(linear):
@@ -220,7 +220,9 @@ def ulysses_qkv(x, linear, u: UlyssesContext, want_rowsq=False):
 
 def ulysses_out_proj(attn, linear, u: UlyssesContext, residual=None, gate=None):
     la, lb, ls = _lora_of(linear)
-    return _UlyssesOutProj.apply(attn, linear.weight, linear.bias, la, lb, ls, u, residual, gate)
+    # grad mode is read here: inside an autograd Function's forward it is always off
+    return _UlyssesOutProj.apply(attn, linear.weight, linear.bias, la, lb, ls, u, residual, gate,
+                                 torch.is_grad_enabled())
 
 
 class _DistRowNorm(torch.autograd.Function):
