@@ -35,12 +35,16 @@ class _SingleStream(torch.autograd.Function):
         dev, dt = xm.device, xm.dtype
         lib = N.require()
         xm2 = xm.contiguous().view(M, D)
-        h1 = F.gemm_native(xm2, a1, alpha=s1) if a1 is not None else None
+        x2 = x.contiguous().view(M, D)
+        gate_v, _ = F._mod_view(gate, D)
         qkv = torch.empty(M, 3 * D, dtype=dt, device=dev)
         cat = torch.empty(M, D + Fm, dtype=dt, device=dev)
         pre = torch.empty(M, Fm, dtype=dt, device=dev)
+        # each rank-r product is the launch right before the GEMM that consumes it, so that GEMM can
+        # start while it still runs (programmatic dependent launch)
+        h1 = F.skinny_gemm(xm2, a1, alpha=s1) if a1 is not None else None
         F.gemm_native(xm2, w1, bias=b1, lora_h=h1, lora_b=bb1, out=qkv, n_split=3 * D,
-                      out2=cat[:, D:], act="gelu", pre_out=pre)
+                      out2=cat[:, D:], act="gelu", pre_out=pre, pdl=F._pdl_ok())
         q = torch.empty(B, L, heads, Dh, dtype=dt, device=dev)
         k, v = torch.empty_like(q), torch.empty_like(q)
         N.check(lib.eri_qknorm_rope_fwd(qkv.data_ptr(), N.ptr(qs), N.ptr(ks), N.ptr(cos), N.ptr(sin),
@@ -48,10 +52,9 @@ class _SingleStream(torch.autograd.Function):
                                         1e-6, 3 * D, D, N.stream_ptr()), "qknorm_rope_fwd")
         o, lse = FA.fwd(q, k, v)
         cat[:, :D].copy_(o.view(M, D))
-        h2 = F.gemm_native(cat, a2, alpha=s2) if a2 is not None else None
-        gate_v, _ = F._mod_view(gate, D)
-        y = F.gemm_native(cat, w2, bias=b2, lora_h=h2, lora_b=bb2, residual=x.contiguous().view(M, D),
-                          gate=gate_v, rows_per_batch=L)
+        h2 = F.skinny_gemm(cat, a2, alpha=s2) if a2 is not None else None
+        y = F.gemm_native(cat, w2, bias=b2, lora_h=h2, lora_b=bb2, residual=x2,
+                          gate=gate_v, rows_per_batch=L, pdl=F._pdl_ok())
         ctx.save_for_backward(xm2, qkv, pre, cat, q, k, v, o, lse, h1, h2, gate_v, w1, w2, a1, bb1, a2,
                               bb2, qs, ks, cos, sin)
         ctx.meta = (B, L, D, Fm, heads, Dh, s1, s2)
@@ -70,11 +73,14 @@ class _SingleStream(torch.autograd.Function):
         g = torch.empty_like(dy2)
         N.check(lib.eri_gate_residual(None, dy2.data_ptr(), gate_v.data_ptr(), g.data_ptr(), M, D, L,
                                       gate_v.stride(0), N.stream_ptr()), "gate_bwd")
-        ts2 = F.gemm_native(g, _t(bb2), alpha=s2) if a2 is not None else None
+        lt = F._lora_transposed
+        bb2_t, a2_t = (lt(bb2), lt(a2)) if a2 is not None else (None, None)
+        bb1_t, a1_t = (lt(bb1), lt(a1)) if a1 is not None else (None, None)
         d_attn = torch.empty(M, D, dtype=dt, device=dev)
         d_h = torch.empty(M, 3 * D + Fm, dtype=dt, device=dev)
-        F.gemm_native(g, w2, b_mn=True, lora_h=ts2, lora_b=_t(a2) if a2 is not None else None,
-                      out=d_attn, n_split=D, out2=d_h[:, 3 * D:], act="gelu_bwd", pre_in=pre)
+        ts2 = F.skinny_gemm(g, bb2_t, alpha=s2) if a2 is not None else None
+        F.gemm_native(g, w2, b_mn=True, lora_h=ts2, lora_b=a2_t,
+                      out=d_attn, n_split=D, out2=d_h[:, 3 * D:], act="gelu_bwd", pre_in=pre, pdl=F._pdl_ok())
         da2 = (ts2.t() @ cat) if (a2 is not None and need[10]) else None
         db2 = (g.t() @ h2) if (a2 is not None and need[11]) else None
         dq, dk, dv = FA.bwd(d_attn.view(B, L, heads, Dh), q, k, v, o, lse)
@@ -85,11 +91,10 @@ class _SingleStream(torch.autograd.Function):
                                         N.ptr(qs), N.ptr(ks), N.ptr(cos), N.ptr(sin), d_h.data_ptr(),
                                         N.ptr(dqs), N.ptr(dks), B, L, heads, Dh, L, 0, 1e-6, 3 * D, D,
                                         3 * D + Fm, N.stream_ptr()), "qknorm_rope_bwd")
-        ts1 = F.gemm_native(d_h, _t(bb1), alpha=s1) if a1 is not None else None
+        ts1 = F.skinny_gemm(d_h, bb1_t, alpha=s1) if a1 is not None else None
         dxm = None
         if need[0]:
-            dxm = F.gemm_native(d_h, w1, b_mn=True, lora_h=ts1,
-                                lora_b=_t(a1) if a1 is not None else None).view(B, L, D)
+            dxm = F.gemm_native(d_h, w1, b_mn=True, lora_h=ts1, lora_b=a1_t, pdl=F._pdl_ok()).view(B, L, D)
         da1 = (ts1.t() @ xm2) if (a1 is not None and need[7]) else None
         db1 = (d_h.t() @ h1) if (a1 is not None and need[8]) else None
         dw1 = (d_h.t() @ xm2) if need[3] else None
