@@ -164,7 +164,7 @@ def bench_ulysses(a, pg, rank, world, dev):
     peak, tag = gemm_peak()
     D, H = 4096, 32
     Ll = (19008 // world) // 128 * 128
-    u = UlyssesContext(pg, batch=1, l_local=Ll, hidden=D, heads=H, n_copy=a.n_copy)
+    u = UlyssesContext(pg, batch=1, l_local=Ll, hidden=D, heads=H, n_copy=a.n_copy, attn_slots=2)
     torch.manual_seed(0)
     qkv = Linear(D, 3 * D, bias=False, device=dev)
     out = Linear(D, D, bias=False, device=dev)
@@ -183,7 +183,16 @@ def bench_ulysses(a, pg, rank, world, dev):
             send.copy_(y.view(Ll, world, 3 * D // world).transpose(0, 1))
             dist.all_to_all_single(recv.view(-1), send.view(-1))
 
+    # as in the model: the attention kernel writes its output into the layer's symmetric slot
+    attn_slot = u.attn_buffer(1, H // world)
+    attn_slot.copy_(attn)
+
     def fused_out():
+        with torch.no_grad():
+            ulysses_out_proj(attn_slot, out, u)
+
+    def fused_out_publish():
+        # attention output in ordinary memory: published with a barrier and a copy first
         with torch.no_grad():
             ulysses_out_proj(attn, out, u)
 
@@ -199,6 +208,7 @@ def bench_ulysses(a, pg, rank, world, dev):
     for name, f_f, f_n, n_out, act_cols in (("qkv projection + head scatter", fused_qkv, nccl_qkv, 3 * D, 3 * D),
                                              ("head gather + out projection", fused_out, nccl_out, D, D)):
         t_f, t_n = timed(f_f), timed(f_n)
+        extra = {"fused_with_publish_copy_ms": round(timed(fused_out_publish), 4)} if f_f is fused_out else {}
         flops = 2.0 * Ll * n_out * D
         link_bytes = (world - 1) / world * Ll * act_cols * 2
         roof = max(flops / peak, link_bytes / (LINK_GBS * 1e9)) * 1e3
@@ -209,7 +219,7 @@ def bench_ulysses(a, pg, rank, world, dev):
                               "nvlink_bound_ms": round(link_bytes / (LINK_GBS * 1e9) * 1e3, 4),
                               "roofline_ms": round(roof, 4), "fraction_of_roofline": round(roof / t_f, 3),
                               "gemm_peak": tag, "status": u.comm.status(), "gemm_err": F.gemm_error_check(),
-                              "two_cta_gather_launches": N_.require().eri_gemm2_gather_count()}))
+                              "two_cta_gather_launches": N_.require().eri_gemm2_gather_count(), **extra}))
 
 
 def main():

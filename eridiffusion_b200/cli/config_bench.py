@@ -93,7 +93,7 @@ def main(argv=None):
             if L % world or model.cfg.num_heads % world:
                 raise SystemExit("token count and head count must divide by the world size")
             model.set_sequence_parallel(UlyssesContext(pg, batch=a.batch, l_local=Ll, hidden=model.cfg.hidden,
-                                                       heads=model.cfg.num_heads))
+                                                       heads=model.cfg.num_heads, attn_slots=depth))
 
         def batch(i):
             # every rank sees the same clip and text (seeded by step only) and keeps its token slice

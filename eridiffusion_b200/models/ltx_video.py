@@ -119,7 +119,10 @@ class LTXBlock(nn.Module):
         q, k = _rope_full(q, c, s), _rope_full(k, c, s)
         hl = self.heads // W
         sh = (B, u.Lt, hl, G // hl)
-        return F.attention(q.view(sh), k.view(sh), recv[:, :, 2].contiguous().view(sh)).view(B, u.Lt, G)
+        # with one slot per layer the attention output is written where the peers' out-projection
+        # launches fetch it
+        out = u.attn_buffer(getattr(self, "layer_idx", 0), hl)
+        return F.attention(q.view(sh), k.view(sh), recv[:, :, 2].contiguous().view(sh), out=out).view(B, u.Lt, G)
 
     def forward(self, x, ctx, temb6, cos, sin, u=None):
         B, L, D = x.shape
@@ -157,6 +160,8 @@ class LTXVideo(nn.Module):
         self.caption_in = Linear(cfg.caption_dim, D, dtype=dtype, device=device)
         self.caption_out = Linear(D, cfg.context_dim, dtype=dtype, device=device)
         self.blocks = nn.ModuleList(LTXBlock(cfg, dtype, device) for _ in range(cfg.depth))
+        for i, blk in enumerate(self.blocks):
+            blk.layer_idx = i            # selects the block's attention-output slot under Ulysses
         self.scale_shift_table = nn.Parameter(torch.randn(2, D, device=device).mul_(D ** -0.5).to(dtype))
         self.proj_out = Linear(D, cfg.in_channels, dtype=dtype, device=device)
         self.ulysses = None

@@ -47,14 +47,18 @@ def supported(q, k, v) -> bool:
             and k.shape[1] >= 128 and L >= 128 and k.shape[2] == H and v.shape == k.shape)
 
 
-def fwd(q, k, v, scale=None):
-    """Returns (out [B, Lq, H, Dh] bf16, lse [B, H, Lq] fp32)."""
+def fwd(q, k, v, scale=None, out=None):
+    """Returns (out [B, Lq, H, Dh] bf16, lse [B, H, Lq] fp32). ``out``: optional contiguous
+    destination of q's shape (e.g. a buffer that peers can read)."""
     lib = N.require()
     _bind(lib)
     B, Lq, H, D = q.shape
     Lk = k.shape[1]
     scale = scale if scale is not None else 1.0 / math.sqrt(D)
-    out = torch.empty_like(q)
+    if out is None:
+        out = torch.empty_like(q)
+    elif out.shape != q.shape or out.dtype != q.dtype or not out.is_contiguous():
+        raise ValueError("flash attention: out must be contiguous with q's shape and dtype")
     lse = torch.empty(B, H, Lq, dtype=torch.float32, device=q.device)
     N.check(lib.eri_flash_attn_fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(),
                                    lse.data_ptr(), B, H, Lq, Lk, D, scale, N.stream_ptr()),
@@ -91,8 +95,8 @@ def check_error() -> int:
 
 class _FlashAttention(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, q, k, v, scale):
-        out, lse = fwd(q, k, v, scale)
+    def forward(ctx, q, k, v, scale, out_buf=None):
+        out, lse = fwd(q, k, v, scale, out_buf)
         ctx.save_for_backward(q, k, v, out, lse)
         ctx.scale = scale
         return out
@@ -103,15 +107,15 @@ class _FlashAttention(torch.autograd.Function):
         do = do.contiguous()
         if has_backward():
             dq, dk, dv = bwd(do, q, k, v, out, lse, ctx.scale)
-            return dq, dk, dv, None
+            return dq, dk, dv, None, None
         # Library recompute path, used only while the native backward is absent from the build.
         from . import reference as R
         with torch.enable_grad():
             qq, kk, vv = (t.detach().requires_grad_() for t in (q, k, v))
             o = R.attention(qq, kk, vv, ctx.scale)
         dq, dk, dv = torch.autograd.grad(o, (qq, kk, vv), do)
-        return dq, dk, dv, None
+        return dq, dk, dv, None, None
 
 
-def flash_attention(q, k, v, scale=None):
-    return _FlashAttention.apply(q, k, v, scale)
+def flash_attention(q, k, v, scale=None, out=None):
+    return _FlashAttention.apply(q, k, v, scale, out)

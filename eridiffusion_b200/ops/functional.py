@@ -757,12 +757,13 @@ def small_linear(x, w, bias=None, silu_in=False):
 
 
 # ---------------------------------------------------------------------------- attention
-def attention(q, k, v, scale=None, mask=None):
-    """Non-causal attention over token-major [B, L, H, Dh] tensors."""
+def attention(q, k, v, scale=None, mask=None, out=None):
+    """Non-causal attention over token-major [B, L, H, Dh] tensors. ``out``: optional destination
+    buffer for the native kernel (ignored by the library path, which returns its own tensor)."""
     if _ATTN_NATIVE == "native" and mask is None and _native_ok(q, k, v):
         from . import flash_attn as FA
         if FA.supported(q, k, v):
-            return FA.flash_attention(q, k, v, scale)
+            return FA.flash_attention(q, k, v, scale, out)
     return R.attention(q, k, v, scale, mask)
 
 

@@ -32,7 +32,7 @@ from .symm import Communicator, SymmetricHeap
 
 class UlyssesContext:
     def __init__(self, pg: ProcessGroup | None, batch: int, l_local: int, hidden: int, heads: int,
-                 n_copy: int = 8, wait_ms: float = 2000.0):
+                 n_copy: int = 8, wait_ms: float = 2000.0, attn_slots: int = 1):
         self.pg = pg or ProcessGroup()
         self.rank, self.world = self.pg.rank, self.pg.world_size
         W = self.world
@@ -41,12 +41,18 @@ class UlyssesContext:
         self.G = hidden // W                       # columns of one rank's head group
         self.Lt = W * l_local
         nb = batch * self.Lt * 3 * self.G * 2
-        self.heap = SymmetricHeap(4 * nb + (4 << 20), group=self.pg.group)
+        self.heap = SymmetricHeap(4 * nb + max(0, attn_slots - 1) * (nb // 3 + 4096) + (4 << 20),
+                                  group=self.pg.group)
         self.comm = Communicator(self.heap, wait_ms)
         self.n_copy = n_copy
         # receive buffers (symmetric): qkv forward, attention output, and their gradients
         self.recv_qkv = self.heap.tensor((batch * self.Lt, 3 * self.G), torch.bfloat16)
-        self.attn_out = self.heap.tensor((batch * self.Lt, self.G), torch.bfloat16)
+        # Attention outputs that peers read. One slot per layer lets the attention kernel write its
+        # output where the peers fetch it (no publish copy) while autograd keeps it for backward.
+        self.attn_outs = [self.heap.tensor((batch * self.Lt, self.G), torch.bfloat16)
+                          for _ in range(max(1, attn_slots))]
+        self.attn_out = self.attn_outs[0]
+        self._slot_of = {t.local.data_ptr(): t for t in self.attn_outs}
         self.d_recv_qkv = self.heap.tensor((batch * self.Lt, 3 * self.G), torch.bfloat16)
         self.d_attn_out = self.heap.tensor((batch * self.Lt, self.G), torch.bfloat16)
         self._plans = {}
@@ -55,6 +61,13 @@ class UlyssesContext:
     def barrier(self):
         if self.world > 1:
             self.comm.collective("barrier", self.recv_qkv, count=0)
+
+    def attn_buffer(self, slot: int, heads_local: int):
+        """[B, W*L_local, H/W, Dh] view of attention-output slot ``slot`` (None when the context
+        has fewer slots): pass it as ``out=`` to the attention call of layer ``slot``."""
+        if slot >= len(self.attn_outs) or (len(self.attn_outs) == 1 and slot > 0):
+            return None
+        return self.attn_outs[slot].local.view(self.B, self.Lt, heads_local, self.G // heads_local)
 
     def cols_plan(self, key, src_sym, parts, landing):
         """landing [B*Ll, parts*W*G]: for each part, column block p comes from peer p's rows of
@@ -154,11 +167,16 @@ class _UlyssesOutProj(torch.autograd.Function):
     def forward(ctx, attn, w, bias, la, lb, ls, u, residual, gate, keep_a=True):
         B, Ll, D = u.B, u.Ll, u.D
         W = u.world
-        u.barrier()
-        u.attn_out.local.copy_(attn.reshape(B * u.Lt, u.G))
-        u.barrier()
+        sym = u._slot_of.get(attn.data_ptr()) if len(u.attn_outs) > 1 else None
+        if sym is None:
+            sym = u.attn_out
+            u.barrier()           # peers are done reading the previous contents
+            sym.local.copy_(attn.reshape(B * u.Lt, u.G))
+        # with a slot per layer the attention kernel wrote straight into ``sym``; peers finished
+        # reading this slot's previous contents (last step) many barriers ago
+        u.barrier()               # every rank has published
         A = torch.empty(B * Ll, D, dtype=attn.dtype, device=attn.device)
-        pl = u.cols_plan("attn", u.attn_out, 1, A)
+        pl = u.cols_plan(("attn", sym.local.data_ptr()), sym, 1, A)
         res2 = None if residual is None else residual.contiguous().view(B * Ll, D)
         gate_v = None
         if gate is not None:

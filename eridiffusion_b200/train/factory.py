@@ -132,7 +132,8 @@ def _sequence_parallel_batches(batches, model, rank, world):
         Ll = L // world
         if not attached:
             model.set_sequence_parallel(UlyssesContext(ProcessGroup(), batch=lat.shape[0], l_local=Ll,
-                                                       hidden=model.cfg.hidden, heads=model.cfg.num_heads))
+                                                       hidden=model.cfg.hidden, heads=model.cfg.num_heads,
+                                                       attn_slots=len(model.blocks)))
             attached = True
         b = dict(b)
         b["latents"] = lat[:, :, rank * Ll:(rank + 1) * Ll].contiguous()
