@@ -57,3 +57,22 @@ def test_flash_bwd(B, H, Lq, Lk, D):
     for a, b, n in ((dq, qf.grad, "dq"), (dk, kf.grad, "dk"), (dv, vf.grad, "dv")):
         err = (a.float() - b).abs().max().item()
         assert err < 0.02 * b.abs().max().item() + 2e-2, (n, err, b.abs().max().item())
+
+
+def test_flash_attention_into_caller_buffer():
+    """``out=``: the forward writes into the caller's buffer (a peer-readable slot under sequence
+    parallelism), autograd keeps that buffer for the backward, gradients match the default path."""
+    from eridiffusion_b200.ops import functional as F
+    q, k, v = (mk(1, 384, 2, 128, s).requires_grad_() for s in (11, 12, 13))
+    go = mk(1, 384, 2, 128, 14)
+    ref = F.attention(q, k, v)
+    gref = torch.autograd.grad(ref, (q, k, v), go)
+    buf = torch.full_like(q, float("nan")).detach()
+    out = F.attention(q, k, v, out=buf)
+    assert out.data_ptr() == buf.data_ptr() and torch.equal(out, ref)
+    got = torch.autograd.grad(out, (q, k, v), go)
+    for a, b in zip(gref, got):
+        assert torch.equal(a, b)
+    with pytest.raises(ValueError):
+        F.attention(q, k, v, out=buf[:, :128])
+    assert FA.check_error() == 0
