@@ -17,15 +17,16 @@
 // straight into the owning rank's buffer over NVLink (Ulysses all-to-all folded into the QKV
 // projection).
 //
-// LoRA: Y = X W^T + (s X A^T) B^T is one launch of this kernel for the rank-r product
-// H = s X A^T followed by the main launch, which appends one extra K step whose operands are
+// LoRA: Y = X W^T + (s X A^T) B^T is one launch for the rank-r product H = s X A^T (the streaming
+// kernel of gemm_rank_stream.cu) followed by the main launch, which appends one extra K step whose operands are
 // H[M,r] and B[N,r]; the low-rank update lands in the same TMEM accumulator before the epilogue,
 // so no [M,N] delta tensor is ever written. (Reference: two library GEMMs, a scale and an add per
 // site, crates/training/src/flux/lora.rs:47-63, crates/training/src/flux/runtime.rs:555-600.)
 //
 // Gather mode (ZeRO-3 parameter all-gather / Ulysses reverse all-to-all fused with the GEMM):
 // the first `n_copy` CTAs of the same launch do not compute; they pull slabs of an operand from
-// peer GPUs (plain 16-byte peer loads) into a local landing buffer and bump a per-slab counter.
+// peer GPUs (bulk asynchronous copies through a shared-memory ring, gather_copy.cuh) into a local
+// landing buffer and bump a per-slab counter.
 // The TMA producer of every compute CTA waits (bounded) on the counter of the slab it is about to
 // load, and tile / K order start at this rank's own slab, so the math on slabs that have landed
 // overlaps the transfer of the rest. The launch is cooperative, which guarantees the copy CTAs are

@@ -21,10 +21,6 @@ from . import flash_attn as FA
 from . import functional as F
 
 
-def _t(x):
-    return x.t().contiguous()
-
-
 class _SingleStream(torch.autograd.Function):
     @staticmethod
     def forward(ctx, xm, x, gate, w1, b1, w2, b2, a1, bb1, s1, a2, bb2, s2, qs, ks, cos, sin, heads):

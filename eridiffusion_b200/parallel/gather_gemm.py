@@ -3,7 +3,7 @@
 ``GatherPlan`` describes how an operand is assembled in a local landing buffer from slabs that
 live on peer GPUs: a device array of copy jobs (source pointer, destination pointer, rows, row
 bytes, strides, slab id) plus one counter per slab. The GEMM launch (``csrc/gemm.cu``) reserves
-its first ``n_copy`` CTAs to execute the jobs with plain 16-byte peer loads; compute CTAs wait on
+its first ``n_copy`` CTAs to execute the jobs with bulk copies through shared memory; compute CTAs wait on
 the counter of the slab they are about to read and start with this rank's own slab, so the tensor
 cores work on data that has landed while the remaining slabs are still crossing NVLink.
 
