@@ -1,7 +1,8 @@
 """Small single-kernel workloads for profiler captures (inputs larger than L2, a few hundred MB on
 the device, a handful of launches), one per hot kernel:
 
-    python -m eridiffusion_b200.cli.profile_target gemm|gemm_lora|rank_stream|attn_fwd|attn_bwd|norm|qknorm|adamw|gemv
+    python -m eridiffusion_b200.cli.profile_target gemm|gemm_lora|rank_stream|attn_fwd|attn_bwd|norm|qknorm|adamw|gemv|
+        elementwise|groupnorm|token_route|dequant
 
 Meant to be run as ``ncu --set full --clock-control none -k regex:<kernel> -s 2 -c 1 ... python -m
 eridiffusion_b200.cli.profile_target <what>`` after the same command line exited 0 without ncu.
@@ -76,6 +77,42 @@ def main():
         x, w, b = r(1, 3072), r(18432, 3072), r(18432)
         for _ in range(iters):
             F.small_linear(x, w, b, silu_in=True)
+    elif what == "elementwise":
+        # gate + residual, GELU forward / backward, GEGLU, weighted MSE, noise mix: 4 x 4608 x 3072
+        # activations (113 MB each, larger than L2 together)
+        x, y = r(4, 4608, 3072), r(4, 4608, 3072)
+        gate = r(4, 3072)
+        wide = r(4, 4608, 6144)
+        lat = r(4, 16, 128, 128)
+        coef = torch.tensor([[0.5] * 4, [0.5] * 4, [1.0] * 4, [-1.0] * 4], device=dev)   # rows a, s, ca, cb
+        for _ in range(iters):
+            F.gate_residual(x, y, gate)
+            xg = x.detach().requires_grad_()
+            F.gelu_tanh(xg).backward(y)
+            F.glu(wide, "gelu")
+            F.mse_loss(x, y)
+            F.noise_mix(lat, coef, seed=1, patch=2)
+    elif what == "groupnorm":
+        x = r(2, 128, 128, 320).permute(0, 3, 1, 2)                # channels-last view of [2, 320, 128, 128]
+        w, b = r(320), r(320)
+        x.requires_grad_()
+        for _ in range(iters):
+            yv = F.group_norm_silu(x, w, b, 32)
+            yv.backward(torch.ones_like(yv))
+            x.grad = None
+    elif what == "token_route":
+        x = r(4, 4608, 3072)
+        for _ in range(iters):
+            sc = F.token_scores(x)
+            idx = F.topk_indices(sc, 2304)
+            F.gather_rows(x, idx)
+    elif what == "dequant":
+        from ..memory import dequantize, quantize
+        w = r(12288, 3072)
+        qs = [quantize(w, kind) for kind in ("int8", "int4", "nf4")]
+        for _ in range(iters):
+            for q in qs:
+                dequantize(q)
     else:
         raise SystemExit(f"unknown target {what}")
     torch.cuda.synchronize()
