@@ -1,0 +1,55 @@
+"""Host-side planning of the gather-fused GEMM: job lists, landing counters and the in-place local
+slab, built on CPU tensors with made-up peer addresses (nothing is launched)."""
+import torch
+
+from eridiffusion_b200.parallel.gather_gemm import GatherPlan
+
+
+def _ptrs(world, stride):
+    return [0x10000000 + p * stride for p in range(world)]
+
+
+def test_rows_plan_counters_and_local_slab():
+    W, rank, Nn, K = 4, 2, 2048, 512
+    landing = torch.empty(Nn, K, dtype=torch.bfloat16)
+    per = Nn // W
+    pl = GatherPlan.rows(rank, W, _ptrs(W, per * K * 2), landing, n_copy=8, rows_per_job=64, flag_rows=256)
+    assert len(pl.flags) == Nn // 256 and pl.kw == dict(b_flag_rows=256, rot_n_rows=rank * per)
+    # every 256-row counter expects its four 64-row jobs; without the local slab its counters expect none
+    assert pl.targets == [4] * 8
+    own = [f for f in range(8) if rank * per <= f * 256 < (rank + 1) * per]
+    assert [pl.targets_nl[f] for f in own] == [0, 0] and sum(pl.targets_nl) == 4 * 6
+    assert len(pl.jobs) == W * per // 64 and len(pl.jobs_nl) == (W - 1) * per // 64
+    assert pl.bytes_from_peers() == (W - 1) * per * K * 2
+    assert pl.local == dict(ptr=_ptrs(W, per * K * 2)[rank], ld=K, mode=1, lo=rank * per, hi=(rank + 1) * per)
+    # the own slab's jobs come first in the full list (tiles start there), peers are interleaved after it
+    first = pl.jobs[0]
+    assert first.src == pl.local["ptr"] and first.flag == rank * per // 256
+    dst0 = landing.data_ptr() + rank * per * K * 2
+    assert first.dst == dst0 and first.rows == 64 and first.row_bytes == K * 2
+    args = pl.launch_args()
+    assert args["n_jobs"] == len(pl.jobs) and args["local"]["n_jobs"] == len(pl.jobs_nl) and args["local"]["mode"] == 1
+
+
+def test_rows_plan_along_k_and_coarse_flags():
+    W, rank, Nn, K = 8, 5, 9216, 256
+    landing = torch.empty(Nn, K, dtype=torch.bfloat16)
+    per = Nn // W                                  # 1152 rows: not a multiple of 256 -> one counter per slab
+    pl = GatherPlan.rows(rank, W, _ptrs(W, per * K * 2), landing, along_k=True, n_copy=16)
+    assert len(pl.flags) == W and pl.kw == dict(a_flag_cols=per, rot_k_cols=rank * per)
+    assert pl.targets == [per // 64] * W
+    assert pl.targets_nl[rank] == 0 and pl.local["mode"] == 2
+
+
+def test_cols_plan_row_groups_and_local_block():
+    W, rank, L, Cc = 4, 1, 384, 128
+    landing = torch.empty(L, W * Cc, dtype=torch.bfloat16)
+    src = _ptrs(W, W * L * Cc * 2)
+    pl = GatherPlan.cols(rank, W, src, rank * L, Cc * 2, landing, n_copy=4, rows_per_job=128)
+    groups = L // 128
+    assert len(pl.flags) == W * groups and pl.targets == [1] * (W * groups)
+    assert pl.kw == dict(a_flag_cols=Cc, rot_k_cols=rank * Cc, a_flag_rows=128)
+    assert [pl.targets_nl[rank * groups + g] for g in range(groups)] == [0] * groups
+    assert pl.local["mode"] == 3 and pl.local["ptr"] == src[rank] + rank * L * Cc * 2 and pl.local["ld"] == Cc
+    j = pl.jobs_nl[0]
+    assert j.row_bytes == Cc * 2 and j.src_stride == Cc * 2 and j.dst_stride == W * Cc * 2
