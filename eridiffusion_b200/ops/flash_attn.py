@@ -96,6 +96,8 @@ def check_error() -> int:
 class _FlashAttention(torch.autograd.Function):
     @staticmethod
     def forward(ctx, q, k, v, scale, out_buf=None):
+        if out_buf is not None:
+            ctx.mark_dirty(out_buf)          # an input that is written in place and returned
         out, lse = fwd(q, k, v, scale, out_buf)
         ctx.save_for_backward(q, k, v, out, lse)
         ctx.scale = scale

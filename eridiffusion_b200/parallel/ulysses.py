@@ -65,8 +65,8 @@ class UlyssesContext:
     def attn_buffer(self, slot: int, heads_local: int):
         """[B, W*L_local, H/W, Dh] view of attention-output slot ``slot`` (None when the context
         has fewer slots): pass it as ``out=`` to the attention call of layer ``slot``."""
-        if slot >= len(self.attn_outs) or (len(self.attn_outs) == 1 and slot > 0):
-            return None
+        if len(self.attn_outs) < 2 or slot >= len(self.attn_outs):
+            return None                  # a single slot is the staging buffer of the publish copy
         return self.attn_outs[slot].local.view(self.B, self.Lt, heads_local, self.G // heads_local)
 
     def cols_plan(self, key, src_sym, parts, landing):
