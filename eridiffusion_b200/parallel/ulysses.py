@@ -67,7 +67,15 @@ class UlyssesContext:
         has fewer slots): pass it as ``out=`` to the attention call of layer ``slot``."""
         if len(self.attn_outs) < 2 or slot >= len(self.attn_outs):
             return None                  # a single slot is the staging buffer of the publish copy
-        return self.attn_outs[slot].local.view(self.B, self.Lt, heads_local, self.G // heads_local)
+        # Not a view of the heap tensor: views share one version counter, and autograd would see
+        # layer i's saved output "modified" when layer i+1 writes its own slot. ``set_`` gives a
+        # tensor over the same memory with a version counter of its own; a fresh one per call, so
+        # that no autograd history of an earlier step hangs on it.
+        base = self.attn_outs[slot].local
+        t = torch.empty(0, dtype=base.dtype, device=base.device)
+        t.set_(base.untyped_storage(), base.storage_offset(),
+               (self.B, self.Lt, heads_local, self.G // heads_local))
+        return t
 
     def cols_plan(self, key, src_sym, parts, landing):
         """landing [B*Ll, parts*W*G]: for each part, column block p comes from peer p's rows of
