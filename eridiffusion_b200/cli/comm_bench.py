@@ -152,7 +152,7 @@ def bench_zero3(a, pg, rank, world, dev):
                               "gemm_bound_ms": round(flops / peak * 1e3, 4),
                               "nvlink_bound_ms": round(link_bytes / (LINK_GBS * 1e9) * 1e3, 4),
                               "roofline_ms": round(roof, 4), "fraction_of_roofline": round(roof / t_f, 3),
-                              "gemm_peak": tag, "status": z3.comm.status(), "gemm_err": F.gemm_error_check(),
+                              "n_copy": a.n_copy, "gemm_peak": tag, "status": z3.comm.status(), "gemm_err": F.gemm_error_check(),
                               "two_cta_gather_launches": N_.require().eri_gemm2_gather_count()}))
 
 
@@ -218,7 +218,7 @@ def bench_ulysses(a, pg, rank, world, dev):
                               "gemm_bound_ms": round(flops / peak * 1e3, 4),
                               "nvlink_bound_ms": round(link_bytes / (LINK_GBS * 1e9) * 1e3, 4),
                               "roofline_ms": round(roof, 4), "fraction_of_roofline": round(roof / t_f, 3),
-                              "gemm_peak": tag, "status": u.comm.status(), "gemm_err": F.gemm_error_check(),
+                              "n_copy": a.n_copy, "gemm_peak": tag, "status": u.comm.status(), "gemm_err": F.gemm_error_check(),
                               "two_cta_gather_launches": N_.require().eri_gemm2_gather_count(), **extra}))
 
 
@@ -226,14 +226,19 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--params", type=int, default=56_000_000)
     ap.add_argument("--what", default="fused_dp")
-    ap.add_argument("--n-copy", type=int, default=16, help="copy CTAs of the gather-fused GEMM launches")
+    ap.add_argument("--n-copy", default="16", help="copy CTAs of the gather-fused GEMM launches; a comma-separated "
+                    "list repeats the zero3 / ulysses measurements for every value")
     a = ap.parse_args()
     rank, world, local = init_from_env()
     dev = torch.device("cuda", local)
     pg = ProcessGroup()
+    sweep = [int(v) for v in str(a.n_copy).split(",")]
     for w in a.what.split(","):
-        {"fused_dp": bench_fused_dp, "zero3": bench_zero3, "ulysses": bench_ulysses}[w](a, pg, rank, world, dev)
-        dist.barrier()
+        for nc in (sweep if w != "fused_dp" else sweep[:1]):
+            a.n_copy = nc
+            {"fused_dp": bench_fused_dp, "zero3": bench_zero3, "ulysses": bench_ulysses}[w](a, pg, rank, world, dev)
+            dist.barrier()
+            torch.cuda.empty_cache()
     dist.destroy_process_group()
 
 
