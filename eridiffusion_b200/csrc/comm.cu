@@ -370,6 +370,35 @@ int coop_grid(const void* fn, int& cache) {
 extern "C" {
 
 int eri_symm_malloc(long long bytes, void** out) { return (int)cudaMalloc(out, (size_t)bytes); }
+
+// Copy-engine leg of a gather: one asynchronous device-to-device copy from a peer's (IPC-mapped)
+// buffer into local memory, then ``n_flags`` 32-bit stream memory writes of ``value`` starting at
+// ``flags`` (one per landing counter the copied slab covers). Both are stream operations executed by
+// the copy engine / front end, not kernels, so a GEMM that is already running and waits (bounded)
+// on those counters cannot starve them of SMs. Returns 0 on success.
+int eri_peer_copy_flags(void* dst, const void* src, long long bytes, void* flags, int n_flags,
+                        unsigned int value, void* stream) {
+  typedef int (*WriteValue32Fn)(void* /*CUstream*/, unsigned long long /*CUdeviceptr*/, unsigned int,
+                                unsigned int);
+  static WriteValue32Fn write32 = nullptr;
+  static bool looked = false;
+  if (!looked) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuStreamWriteValue32", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      write32 = reinterpret_cast<WriteValue32Fn>(p);
+    looked = true;
+  }
+  if (!write32) return -1;
+  cudaError_t e = cudaMemcpyAsync(dst, src, (size_t)bytes, cudaMemcpyDeviceToDevice, (cudaStream_t)stream);
+  if (e != cudaSuccess) return (int)e;
+  for (int i = 0; i < n_flags; ++i) {
+    const int r = write32(stream, (unsigned long long)(uintptr_t)flags + 4ull * i, value, 0u);
+    if (r != 0) return 1000 + r;
+  }
+  return 0;
+}
 int eri_symm_free(void* p) { return (int)cudaFree(p); }
 int eri_ipc_get_handle(void* p, void* handle64) {
   cudaIpcMemHandle_t h;

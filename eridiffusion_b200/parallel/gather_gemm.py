@@ -34,6 +34,7 @@ class GatherPlan:
         self.targets = [0] * n_flags
         self.targets_nl = [0] * n_flags
         self.local = None                 # dict(ptr, ld, mode, lo, hi): own slab readable in place
+        self.slabs = None                 # [(src, dst, bytes, first counter, counters)] per peer, own first
         self._dev_jobs = None
         self.flags = torch.zeros(n_flags, dtype=torch.int32, device=self.device)
         self._targets_dev = None
@@ -80,6 +81,11 @@ class GatherPlan:
             pl.kw = dict(a_flag_cols=flag_rows, rot_k_cols=rank * per)
         else:
             pl.kw = dict(b_flag_rows=flag_rows, rot_n_rows=rank * per)
+        # whole slabs in the same order, for the copy-engine variant of the gather
+        sb = per * rb
+        pl.slabs = [(shard_ptrs[p], landing.data_ptr() + p * per * landing.stride(0) * landing.element_size(), sb,
+                     p * per // flag_rows, per // flag_rows) for p in order] \
+            if landing.stride(0) == K else None
         # the own shard can feed the GEMM in place (second tensor map) when the kernel supports it
         pl.local = dict(ptr=shard_ptrs[rank], ld=K, mode=2 if along_k else 1, lo=rank * per, hi=(rank + 1) * per)
         return pl._finish()
@@ -133,6 +139,32 @@ class GatherPlan:
             d["local"] = dict(self.local, n_jobs=len(self.jobs_nl), jobs=self._dev_jobs_nl.data_ptr(),
                               flag_target=self._targets_nl_dev.data_ptr())
         return d
+
+    def launch_args_engine(self, side_stream):
+        """Copy-engine variant: every slab is one asynchronous device-to-device copy on
+        ``side_stream`` followed by stream memory writes that set the slab's counters to their
+        targets; the GEMM launch then has no copy CTAs (``n_copy`` 0) and only waits on the counters.
+        Peer reads by the copy engines run at link rate, where copy CTAs pulling with bulk copies
+        saturate near 200 GB/s per GPU however many CTAs pull."""
+        if self.slabs is None:
+            return self.launch_args()
+        lib = N.require()
+        if not hasattr(lib.eri_peer_copy_flags, "_bound"):
+            lib.eri_peer_copy_flags.argtypes = [C.c_void_p, C.c_void_p, C.c_longlong, C.c_void_p, C.c_int,
+                                                C.c_uint, C.c_void_p]
+            lib.eri_peer_copy_flags.restype = C.c_int
+            lib.eri_peer_copy_flags._bound = True
+        self.flags.zero_()
+        ev = torch.cuda.Event()
+        ev.record()                       # counters are zero and the landing buffer's last reader is done
+        side_stream.wait_event(ev)
+        for src, dst, nbytes, f0, nfl in self.slabs:
+            code = lib.eri_peer_copy_flags(dst, src, nbytes, self.flags.data_ptr() + 4 * f0, nfl,
+                                           self.targets[f0], side_stream.cuda_stream)
+            if code:
+                raise RuntimeError(f"copy-engine gather failed with code {code}")
+        return dict(n_copy=0, n_jobs=0, jobs=0, flags=self.flags.data_ptr(),
+                    flag_target=self._targets_dev.data_ptr(), **self.kw)
 
     def bytes_from_peers(self):
         return self.remote_bytes

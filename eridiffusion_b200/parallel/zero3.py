@@ -20,6 +20,8 @@ crates/training/src/streaming.rs:12-17): materialise -> run -> release per block
 """
 from __future__ import annotations
 
+import os
+
 import torch
 import torch.distributed as dist
 import torch.nn as nn
@@ -43,6 +45,10 @@ class Zero3Context:
         self.landing = [torch.empty(max_weight_elems, dtype=torch.bfloat16, device=dev) for _ in range(2)]
         self.stage = self.heap.tensor((max_weight_elems,), torch.bfloat16)
         self.n_copy = n_copy
+        # "sm": copy CTAs inside the GEMM launch pull the slabs; "ce": the copy engines do, on a side
+        # stream, and the GEMM only waits on the landing counters (ERI_B200_ZERO3_GATHER overrides)
+        self.gather_engine = os.environ.get("ERI_B200_ZERO3_GATHER", "sm")
+        self.copy_stream = torch.cuda.Stream(device=dev) if self.gather_engine == "ce" else None
         self._flip = 0
         self._plans = {}
         self.gathered_bytes = 0
@@ -72,6 +78,11 @@ class Zero3Context:
         self.gathered_bytes += pl.bytes_from_peers()
         return pl, landing
 
+    def gather_args(self, pl):
+        if self.copy_stream is not None:
+            return pl.launch_args_engine(self.copy_stream)
+        return pl.launch_args()
+
     def barrier(self):
         """Cross-GPU barrier on the current stream (a kernel; no host synchronisation)."""
         if self.world > 1:
@@ -93,7 +104,7 @@ class _Zero3LinearFn(torch.autograd.Function):
         if gate is not None:
             gate_v, _ = F._mod_view(gate, n_out)
         y = F.gemm_native(x2, landing, bias=bias, act=act, pre_out=pre, residual=res2, gate=gate_v,
-                          rows_per_batch=L, gather=pl.launch_args())
+                          rows_per_batch=L, gather=z3.gather_args(pl))
         ctx.save_for_backward(x2, shard, pre, gate_v)
         ctx.meta = (shp, n_out, L, act, residual is not None, bias is not None)
         ctx.z3 = z3
@@ -118,7 +129,7 @@ class _Zero3LinearFn(torch.autograd.Function):
         dx = None
         if ctx.needs_input_grad[0]:
             pl, landing = z3.plan(shard, n_out, K, along_k=True)
-            dx = F.gemm_native(dy2, landing, b_mn=True, gather=pl.launch_args()).view(shp)
+            dx = F.gemm_native(dy2, landing, b_mn=True, gather=z3.gather_args(pl)).view(shp)
         dshard = None
         if ctx.needs_input_grad[1]:
             per = n_out // z3.world
