@@ -43,6 +43,14 @@ __global__ void dequant_int8_kernel(const int8_t* __restrict__ q, const float* _
 template <bool NF4>
 __global__ void dequant_4bit_kernel(const uint8_t* __restrict__ q, const float* __restrict__ scale,
                                     bf16* __restrict__ out, long long nbytes, int block) {
+  // The 16-entry code table is read with a different index in every lane: from constant memory
+  // that serialises per distinct address (116 us for a 12288 x 3072 weight against 25 us for int4),
+  // from shared memory the 16 entries sit in 16 banks.
+  __shared__ float s_nf4[16];
+  if (NF4) {
+    if (threadIdx.x < 16) s_nf4[threadIdx.x] = c_nf4[threadIdx.x];
+    __syncthreads();
+  }
   const long long vec = (long long)blockIdx.x * blockDim.x + threadIdx.x;   // 16 bytes = 32 codes
   if (vec * 16 >= nbytes) return;
   const uint4 raw = *reinterpret_cast<const uint4*>(q + vec * 16);
@@ -57,8 +65,8 @@ __global__ void dequant_4bit_kernel(const uint8_t* __restrict__ q, const float* 
     for (int j = 0; j < 4; ++j) {
       const uint8_t byte = b[g * 4 + j];
       const int c0 = byte & 0xF, c1 = byte >> 4;   // low nibble is the even element
-      v[2 * j] = (NF4 ? c_nf4[c0] : ((float)c0 - 8.f) / 7.f) * s;
-      v[2 * j + 1] = (NF4 ? c_nf4[c1] : ((float)c1 - 8.f) / 7.f) * s;
+      v[2 * j] = (NF4 ? s_nf4[c0] : ((float)c0 - 8.f) / 7.f) * s;
+      v[2 * j + 1] = (NF4 ? s_nf4[c1] : ((float)c1 - 8.f) / 7.f) * s;
     }
     o[g] = pack8(v);
   }
