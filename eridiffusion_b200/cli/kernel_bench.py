@@ -139,6 +139,20 @@ def bench_optim(small):
     print(f"sumsq: {t*1e6:.1f} us  {opt.arena.numel*2/t/1e9:.0f} GB/s")
 
 
+def bench_dequant(small):
+    """Quantised base weight -> bf16 GEMM operand (codes read + bf16 written)."""
+    from ..memory import dequantize, quantize
+    bw, fl, tag = peaks()
+    rows, cols = (12288, 3072) if not small else (2048, 1024)
+    w = torch.randn(rows, cols, device="cuda").bfloat16()
+    for kind, code_bytes in (("int8", 1.0), ("int4", 0.5), ("nf4", 0.5)):
+        q = quantize(w, kind)
+        out = torch.empty_like(w)
+        t = timeit(lambda: dequantize(q, out=out))
+        nb = rows * cols * (code_bytes + 2)
+        print(f"dequant {kind} [{rows}x{cols}]: {t*1e6:.1f} us  {nb/t/1e9:.0f} GB/s  {nb/t/bw:.2f} {tag}")
+
+
 def bench_attn(small):
     bw, fl, tag = peaks()
     for (B, L, H, D) in ([(1, 4608, 24, 128)] if not small else [(1, 1024, 8, 128)]):
@@ -171,7 +185,7 @@ def main():
     a = ap.parse_args()
     for w in a.what.split(","):
         {"gemm": bench_gemm, "skinny": bench_skinny, "elementwise": bench_elementwise, "optim": bench_optim,
-         "attn": bench_attn}[w](a.small)
+         "attn": bench_attn, "dequant": bench_dequant}[w](a.small)
 
 
 if __name__ == "__main__":
