@@ -51,6 +51,7 @@ def main(argv=None):
     ap.add_argument("--cfg-scale", type=float, default=1.0)
     ap.add_argument("--height", type=int, default=1024); ap.add_argument("--width", type=int, default=1024)
     ap.add_argument("--seed", type=int, default=0); ap.add_argument("--sampler", default="euler")
+    ap.add_argument("--frames", type=int, default=9, help="latent frames (video families)")
     ap.add_argument("--device", default="cuda:0" if torch.cuda.is_available() else "cpu")
     ap.add_argument("--override", action="append", default=[], help="model config override key=value")
     a = ap.parse_args(argv)
@@ -100,8 +101,17 @@ def main(argv=None):
             lat = S.generate_flow(model, txt, pooled, a.height, a.width, a.steps, a.guidance, seed=a.seed,
                                   channels=ch, dtype=dt, cfg_scale=a.cfg_scale)
             vae_kind = "vae_flux"
+        elif a.family in ("ltx_video", "wan22"):
+            # video families: token-major flow model, Euler over the token-count dependent sigma grid
+            from ..sampling.pipelines import generate_video_flow
+            ctx_dim = getattr(model.cfg, "caption_dim", getattr(model.cfg, "context_dim", 4096))
+            txt, _ = _embeds(a, dev, dt, ctx_dim, 0, 256)
+            ch = getattr(model.cfg, "in_channels", 128)
+            lat = generate_video_flow(model, txt, a.frames, a.height // 32, a.width // 32, ch, a.steps, a.seed,
+                                      dtype=dt, cfg_scale=1.0)
+            a.vae = None                                   # video latents are written as they are
         else:
-            raise SystemExit(f"family {a.family!r} has no image sampler here (video families: use the training CLI's sampler hooks)")
+            raise SystemExit(f"family {a.family!r} has no sampler")
         if a.vae:
             vae = build_model(vae_kind, device=dev, dtype=dt).eval()
             from ..io.weights import load_model_weights
