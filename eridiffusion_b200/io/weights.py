@@ -41,6 +41,27 @@ def load_model_weights(model, path, kind="flux", strict=True, device=None):
     files = sorted(path.glob("*.safetensors")) if path.is_dir() else [path]
     own = dict(model.named_parameters())
     used, seen = set(), set()
+    if kind == "sdxl":
+        # single-file checkpoints in the original layout: remap (and fuse q/k/v) instead of renaming
+        from .sdxl_keys import remap_sdxl_state_dict
+        raw = {}
+        for f in files:
+            with st.SafeFile(f) as sf:
+                ks = [k for k in sf.keys() if k.startswith("model.diffusion_model.")]
+                raw.update({k: sf.get(k, device=device or "cpu") for k in ks})
+        if raw:
+            sd = remap_sdxl_state_dict(raw, strict=strict)
+            with torch.no_grad():
+                for k, t in sd.items():
+                    if k in own:
+                        if tuple(t.shape) != tuple(own[k].shape):
+                            raise ValueError(f"{k}: shape {tuple(t.shape)} != parameter {tuple(own[k].shape)}")
+                        own[k].copy_(t.to(own[k].dtype))
+                        used.add(k)
+            if strict and (set(own) - used or set(sd) - used):
+                raise KeyError(f"strict weight load: missing={sorted(set(own) - used)[:5]} "
+                               f"unused={sorted(set(sd) - used)[:5]}")
+            return used
     for f in files:
         with st.SafeFile(f) as sf:
             st.assert_not_text_encoder(sf.keys())
