@@ -12,7 +12,7 @@ import sys
 
 from ..config import load_config
 from ..train.factory import build_job
-from ..train.services import CSVLogger, StepWatchdog, run_training
+from ..train.services import CSVLogger, SampleCallback, StepWatchdog, run_training
 
 
 def main(argv=None):
@@ -32,6 +32,8 @@ def main(argv=None):
         if r and info["rank"] == 0:
             print(f"resumed from step {r[0]} (seed {r[1]})")
     cbs = [CSVLogger(a.csv)] if a.csv and info["rank"] == 0 else []
+    if cfg.sample.sample_every and cfg.training_folder and info["rank"] == 0:
+        cbs.append(SampleCallback(cfg.sample, info["model"], cfg.training_folder, rank=info["rank"]))
     wd = StepWatchdog()
     run_training(trainer, batches, cfg.steps, callbacks=cbs, log_every=a.log_every or cfg.performance_log_every,
                  world=info["world"], batch_size=cfg.batch_size, watchdog=wd,

@@ -196,7 +196,11 @@ def loss_fn(kind, pred, target, weight=None, mask=None, huber_delta=1.0):
         a = d.abs()
         e = torch.where(a <= huber_delta, 0.5 * d.pow(2), huber_delta * (a - 0.5 * huber_delta))
     else:
-        raise ValueError(kind)
+        # named objects (lpips / perceptual / mae / flow_matching / v): whole-tensor reductions
+        from .losses import create_loss
+        if weight is not None or mask is not None:
+            raise ValueError(f"loss {kind!r} takes no per-sample weight or mask")
+        return create_loss(kind)(pred, target)
     if weight is not None:
         e = e * weight.float().view(-1, *([1] * (e.dim() - 1)))
     if mask is not None:

@@ -18,6 +18,7 @@ import os
 import signal
 import threading
 import time
+from pathlib import Path
 from collections import deque
 from dataclasses import dataclass, field
 
@@ -93,6 +94,71 @@ class TensorBoardCallback(Callback):
                     self.writer.add_scalar(k, v, step)
                 else:
                     self.history.append((step, k, v))
+
+
+class SampleCallback(Callback):
+    """Validation sampling during training: every ``sample_every`` optimizer steps the model is
+    put in eval mode, the unified inference pipeline draws one sample per prompt embedding with the
+    configured sampler settings, and the latents (PNG files when a VAE is attached) are written to
+    ``out_dir/samples`` (``sample.sample_every`` of the YAML; crates/training/src/trainer.rs:379-382).
+    ``embeddings``: list of (txt [1, T, D], pooled [1, P] or None), e.g. from the embedding cache;
+    with none given, seeded random embeddings of the right shape stand in so that the hook still
+    exercises the sampler."""
+
+    def __init__(self, sample_cfg, family: str, out_dir, embeddings=None, vae=None, rank: int = 0, frames: int = 1):
+        self.cfg, self.family, self.out = sample_cfg, family, Path(out_dir) / "samples"
+        self.embeddings, self.vae, self.rank, self.frames = embeddings, vae, rank, frames
+        self.written = []
+
+    def _model_type(self):
+        from ..sampling.pipelines import ModelType
+        for mt in ModelType:
+            if mt.family == self.family:
+                return mt
+        return ModelType.FLUX_DEV               # MMDiT-style call signature
+
+    def _embeds(self, model, n):
+        if self.embeddings:
+            return self.embeddings
+        c = model.cfg
+        dim = getattr(c, "context_dim", getattr(c, "caption_dim", 4096))
+        vec = getattr(c, "vec_dim", getattr(c, "pooled_dim", 0))
+        p = next(model.parameters())
+        out = []
+        for i in range(max(1, n)):
+            g = torch.Generator().manual_seed(1000 + i)
+            out.append((torch.randn(1, 64, dim, generator=g).to(p.device, p.dtype),
+                        torch.randn(1, vec, generator=g).to(p.device, p.dtype) if vec else None))
+        return out
+
+    def on_step_end(self, trainer, step, logs):
+        every = self.cfg.sample_every
+        if not every or step % every or self.rank != 0:
+            return
+        from ..io import safetensors as st
+        from ..sampling import save_png
+        from ..sampling.pipelines import UnifiedInferencePipeline
+        model = trainer.model
+        was_training = model.training
+        model.eval()
+        try:
+            pipe = UnifiedInferencePipeline(model, self._model_type(), vae=self.vae)
+            self.out.mkdir(parents=True, exist_ok=True)
+            for i, (txt, pooled) in enumerate(self._embeds(model, len(self.cfg.prompts))):
+                seed = self.cfg.seed + (i if self.cfg.walk_seed else 0)
+                lat = pipe.generate(txt=txt, pooled=pooled, width=self.cfg.width, height=self.cfg.height,
+                                    steps=self.cfg.sample_steps, guidance_scale=self.cfg.guidance_scale, seed=seed,
+                                    frames=self.frames)
+                stem = self.out / f"step{step:07d}_{i}"
+                if self.vae is not None and lat.dim() == 4:
+                    save_png(pipe.decode(lat)[0], str(stem) + ".png")
+                    self.written.append(str(stem) + ".png")
+                else:
+                    st.save_file({"latent": lat.float().cpu()}, str(stem) + ".safetensors",
+                                 metadata={"step": str(step), "seed": str(seed)})
+                    self.written.append(str(stem) + ".safetensors")
+        finally:
+            model.train(was_training)
 
 
 # ------------------------------------------------------------------------- metrics

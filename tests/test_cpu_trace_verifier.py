@@ -72,3 +72,22 @@ def test_verify_training_step_and_trainer_phases(monkeypatch):
     assert rep["health"] == "failed" and "No gradients detected" in rep["issues"] and "Loss is not finite" in rep["issues"]
     s = tr.phases.summary()
     assert list(s) == ["noise", "forward", "backward", "optimizer"] and s["forward"]["calls"] == 3
+
+
+def test_sample_callback_writes_latents(tmp_path):
+    from eridiffusion_b200.config import SampleCfg
+    from eridiffusion_b200.io import safetensors as st
+    from eridiffusion_b200.train.services import SampleCallback, run_training
+    torch.manual_seed(0)
+    m = build_model("tiny_mmdit", device="cpu", dtype=torch.float32)
+    cfg = TrainerConfig(mode="lora", adapter=AdapterConfig(rank=4, alpha=4, dtype=torch.float32), optimizer="adamw",
+                        lr=1e-3, seed=1, total_steps=4)
+    tr = Trainer(m, cfg)
+    cb = SampleCallback(SampleCfg(sample_every=2, width=64, height=64, sample_steps=2, prompts=["a", "b"], walk_seed=True),
+                        "tiny_mmdit", tmp_path)
+    batches = (synthetic_batch("tiny_mmdit", 1, "cpu", torch.float32, i) for i in range(100))
+    run_training(tr, batches, 4, callbacks=[cb], log_every=1, print_fn=lambda *_: None)
+    assert len(cb.written) == 4 and m.training                       # steps 2 and 4, two prompts each
+    f = tmp_path / "samples" / "step0000002_1.safetensors"
+    assert f.exists() and st.load_file(f)["latent"].shape == (1, 16, 8, 8)
+    assert st.read_metadata(f)["seed"] == "43"
