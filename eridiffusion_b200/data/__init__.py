@@ -47,7 +47,7 @@ def xorshift_permutation(n: int, seed: int) -> list[int]:
 
 
 # ------------------------------------------------------------------------- cache files
-_KEY_ORDER = ("data", "latent", "text_embed")
+_KEY_ORDER = ("data", "latent", "text_embed", "text_hidden")
 
 
 def load_cached_tensor(path, dtype=torch.bfloat16):
