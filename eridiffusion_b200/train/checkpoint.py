@@ -20,6 +20,7 @@ import json
 import os
 import re
 import shutil
+import struct
 import time
 from pathlib import Path
 
@@ -116,12 +117,31 @@ def find_latest(root, pattern=r"(?:step_|checkpoint-)(\d+)$"):
     return found[-1][1] if found else None
 
 
-def load_latest_training_checkpoint(trainer, root):
-    """Restore parameters (+EMA, + optimizer state when its world size matches). Returns
-    ``(step, seed)`` or ``None`` when there is nothing to resume from."""
-    d = find_latest(root)
-    if d is None:
-        return None
+def find_checkpoints(root, pattern=r"(?:step_|checkpoint-)(\d+)$"):
+    """Checkpoint directories under ``root``, newest first."""
+    root = Path(root)
+    if not root.is_dir():
+        return []
+    found = sorted(((int(m.group(1)), p) for p in root.iterdir()
+                    if (m := re.match(pattern, p.name)) and p.is_dir()), reverse=True)
+    return [p for _, p in found]
+
+
+def load_latest_training_checkpoint(trainer, root, on_skip=None):
+    """Restore parameters (+EMA, + optimizer state when its world size matches) from the newest
+    checkpoint that loads. A checkpoint that is truncated, unreadable or inconsistent (a crash
+    during the write, a damaged shard) is skipped and the one before it is tried; ``on_skip(path,
+    error)`` is told. Returns ``(step, seed)`` or ``None`` when there is nothing to resume from."""
+    for d in find_checkpoints(root):
+        try:
+            return _load_checkpoint_dir(trainer, d)
+        except (OSError, ValueError, KeyError, RuntimeError, json.JSONDecodeError, struct.error) as e:
+            if on_skip is not None:
+                on_skip(d, e)
+    return None
+
+
+def _load_checkpoint_dir(trainer, d):
     rank, world = _rank_world(trainer)
     dev = trainer.arena.data.device
     if trainer.adapters is not None:

@@ -302,6 +302,36 @@ def retry(fn, attempts=3, base_delay=0.5, exceptions=(Exception,), sleep=time.sl
             sleep(base_delay * (2 ** i))
 
 
+class ResilientBatches:
+    """Iterator wrapper for the data path: a batch whose production raises (an unreadable file, a
+    decode error) is skipped and counted instead of ending the run; ``max_consecutive`` failures in
+    a row re-raise the last error, since then the source itself is broken. ``StopIteration`` passes
+    through."""
+
+    def __init__(self, batches, max_consecutive: int = 8, on_error=None, exceptions=(Exception,)):
+        self._it = iter(batches)
+        self.max_consecutive, self.on_error, self.exceptions = max_consecutive, on_error, exceptions
+        self.skipped = 0
+
+    def __iter__(self):
+        return self
+
+    def __next__(self):
+        bad = 0
+        while True:
+            try:
+                return next(self._it)
+            except StopIteration:
+                raise
+            except self.exceptions as e:
+                bad += 1
+                self.skipped += 1
+                if self.on_error is not None:
+                    self.on_error(e)
+                if bad >= self.max_consecutive:
+                    raise
+
+
 class GracefulInterrupt:
     """SIGINT / SIGTERM set a flag; the loop checkpoints and leaves at the next step boundary."""
 
@@ -443,10 +473,13 @@ class MemoryMonitor:
 
 # ------------------------------------------------------------------------- run driver
 def run_training(trainer, batches, steps, callbacks=(), log_every=10, world=1, batch_size=1, nan_guard=None,
-                 watchdog=None, print_fn=print):
+                 watchdog=None, print_fn=print, heartbeat=None):
     """Drive ``trainer`` for ``steps`` optimizer steps over the iterator ``batches``.
     Prints the reference's per-step line (loss, grad_norm, sec/it, alloc_MB, samples/s) every
-    ``log_every`` steps; reading the loss is the only host synchronisation."""
+    ``log_every`` steps; reading the loss is the only host synchronisation. ``heartbeat``
+    (``parallel.health.Heartbeat``) is checked between steps: when a peer is gone this rank writes
+    its checkpoint and leaves with ``RankFailure`` before it launches anything that would wait
+    for the missing rank."""
     cbs = list(callbacks)
     guard = nan_guard or NanGuard()
     for cb in cbs:
@@ -455,6 +488,13 @@ def run_training(trainer, batches, steps, callbacks=(), log_every=10, world=1, b
     t_last = time.time()
     with GracefulInterrupt() as intr:
         while trainer.step < steps:
+            if heartbeat is not None:
+                try:
+                    heartbeat.check()
+                except Exception:
+                    if getattr(trainer.cfg, "out_dir", None):
+                        trainer.save_checkpoint()
+                    raise
             if watchdog:
                 watchdog.begin()
             step_before = trainer.step

@@ -1,0 +1,159 @@
+"""Failures injected on the host: a damaged checkpoint, a data source that raises, a peer that stops
+beating or leaves. Nothing here touches a GPU."""
+import multiprocessing as mp
+import time
+
+import pytest
+import torch
+
+from eridiffusion_b200.adapters import AdapterConfig
+from eridiffusion_b200.data import synthetic_batch
+from eridiffusion_b200.models import build_model
+from eridiffusion_b200.parallel.health import Heartbeat, RankFailure
+from eridiffusion_b200.train.services import ResilientBatches
+from eridiffusion_b200.train.trainer import Trainer, TrainerConfig
+
+
+def _trainer(out):
+    torch.manual_seed(0)
+    m = build_model("tiny_mmdit", device="cpu", dtype=torch.float32)
+    cfg = TrainerConfig(mode="lora", adapter=AdapterConfig(rank=4, alpha=4, dtype=torch.float32), optimizer="adamw",
+                        lr=1e-2, seed=3, out_dir=str(out))
+    return Trainer(m, cfg)
+
+
+def test_damaged_checkpoint_falls_back_to_the_previous_one(tmp_path):
+    tr = _trainer(tmp_path)
+    for i in range(2):
+        tr.train_step(synthetic_batch("tiny_mmdit", 1, "cpu", torch.float32, i))
+    tr.save_checkpoint()
+    good = {n: p.detach().clone() for n, p in tr.model.named_parameters() if p.requires_grad}
+    tr.train_step(synthetic_batch("tiny_mmdit", 1, "cpu", torch.float32, 2))
+    tr.save_checkpoint()
+    newest = sorted(tmp_path.glob("step_*"))[-1]
+    f = newest / "lora.safetensors"
+    f.write_bytes(f.read_bytes()[: f.stat().st_size // 2])                 # a crash in the middle of the write
+    tr2 = _trainer(tmp_path)
+    skipped = []
+    from eridiffusion_b200.train.checkpoint import load_latest_training_checkpoint
+    r = load_latest_training_checkpoint(tr2, tmp_path, on_skip=lambda p, e: skipped.append(p.name))
+    assert r is not None and r[0] == 2 and skipped == [newest.name]
+    for n, p in tr2.model.named_parameters():
+        if p.requires_grad:
+            assert torch.equal(p, good[n].bfloat16().float()), n       # adapters are stored as bf16
+    (sorted(tmp_path.glob("step_*"))[0] / "meta.json").write_text("{ not json")
+    assert load_latest_training_checkpoint(_trainer(tmp_path), tmp_path) is None   # nothing loadable left
+
+
+class _Flaky:
+    def __init__(self, fail_at, n=8):
+        self.i, self.fail_at, self.n = 0, set(fail_at), n
+
+    def __iter__(self):
+        return self
+
+    def __next__(self):
+        self.i += 1
+        if self.i > self.n:
+            raise StopIteration
+        if self.i in self.fail_at:
+            raise OSError(f"cannot read sample {self.i}")
+        return self.i
+
+
+def test_data_source_errors_are_skipped_until_they_persist():
+    seen = []
+    rb = ResilientBatches(_Flaky({2, 5}), on_error=lambda e: seen.append(str(e)))
+    assert list(rb) == [1, 3, 4, 6, 7, 8] and rb.skipped == 2 and len(seen) == 2
+    with pytest.raises(OSError):
+        list(ResilientBatches(_Flaky({2, 3, 4}), max_consecutive=3))
+
+
+class _Store(dict):
+    def set(self, k, v):
+        self[k] = v
+
+    def get(self, k):
+        return self[k]
+
+
+def test_heartbeat_logic_with_a_fake_clock():
+    now = [0.0]
+    s = _Store()
+    a = Heartbeat(s, 0, 3, timeout_s=5.0, clock=lambda: now[0], start=False)
+    b = Heartbeat(s, 1, 3, timeout_s=5.0, clock=lambda: now[0], start=False)
+    assert a.status() == {0: "alive", 1: "alive", 2: "unknown"}
+    now[0] = 4.0
+    b.beat()
+    a.check()                                             # rank 2 has not joined yet, still within the grace time
+    now[0] = 6.0
+    with pytest.raises(RankFailure) as e:
+        a.check()
+    assert e.value.dead == [2] and e.value.left == []
+    c = Heartbeat(s, 2, 3, timeout_s=5.0, clock=lambda: now[0], start=False)
+    a.check()                                             # it joined: all alive
+    now[0] = 12.0
+    c.beat()
+    with pytest.raises(RankFailure) as e:                 # rank 1 stopped beating at t = 4
+        a.check()
+    assert e.value.dead == [1]
+    b.leave()
+    with pytest.raises(RankFailure) as e:
+        a.check()
+    assert e.value.dead == [] and e.value.left == [1]
+
+
+def _rank(rank, port, q):
+    import datetime
+    import torch.distributed as dist
+    store = dist.TCPStore("127.0.0.1", port, 2, is_master=(rank == 0), timeout=datetime.timedelta(seconds=30),
+                          wait_for_workers=False)
+    hb = Heartbeat(store, rank, 2, interval_s=0.1, timeout_s=1.0)
+    if rank == 1:
+        time.sleep(0.5)                                   # two healthy "steps", then the process dies
+        import os
+        os._exit(0)
+    t0 = time.time()
+    try:
+        while time.time() - t0 < 20:
+            hb.check()                                    # between steps, before the next launch
+            time.sleep(0.1)
+        q.put(("no failure seen", None))
+    except RankFailure as e:
+        q.put(("failure", (e.dead, round(time.time() - t0, 1))))
+    hb.close()
+
+
+def test_peer_death_is_noticed_on_the_host():
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = 29000 + (int(time.time() * 1000) % 500)
+    ps = [ctx.Process(target=_rank, args=(r, port, q)) for r in range(2)]
+    for p in ps:
+        p.start()
+    kind, info = q.get(timeout=60)
+    for p in ps:
+        p.join(timeout=30)
+    assert kind == "failure" and info[0] == [1] and info[1] < 10
+
+
+def test_run_training_leaves_with_a_checkpoint_when_a_peer_is_gone(tmp_path):
+    from eridiffusion_b200.train.services import run_training
+    now = [0.0]
+    s = _Store()
+    me = Heartbeat(s, 0, 2, timeout_s=5.0, clock=lambda: now[0], start=False)
+    peer = Heartbeat(s, 1, 2, timeout_s=5.0, clock=lambda: now[0], start=False)
+    tr = _trainer(tmp_path)
+
+    def batches():
+        i = 0
+        while True:
+            if i == 2:
+                peer.leave()                              # the peer exits cleanly between steps
+            yield synthetic_batch("tiny_mmdit", 1, "cpu", torch.float32, i)
+            i += 1
+
+    with pytest.raises(RankFailure) as e:
+        run_training(tr, batches(), 10, log_every=100, print_fn=lambda *_: None, heartbeat=me)
+    assert e.value.left == [1] and tr.step == 3
+    assert sorted(p.name for p in tmp_path.glob("step_*")) == ["step_000003"]
