@@ -173,9 +173,38 @@ def _load_checkpoint_dir(trainer, d):
             trainer.optimizer.load_state_dict(sdict)
         except (KeyError, RuntimeError):
             pass  # different optimizer kind: moments restart, as in the reference's Flux path
+    elif saved_world != world and hasattr(trainer.optimizer, "m_q"):
+        # the job restarts on another number of ranks: rebuild this rank's slice of the 8-bit state
+        files = [d / f"optimizer.rank{r}.safetensors" for r in range(saved_world)]
+        if saved_world == 1 and not files[0].exists():
+            files = [d / "optimizer.safetensors"]
+        if all(f.exists() for f in files):
+            part = reshard_8bit_state(files, rank, world, trainer.optimizer.m_q.numel())
+            md = st.read_metadata(files[0])
+            part["step"] = int(md.get("step", step))
+            part["lr"] = trainer.optimizer.param_groups[0]["lr"]
+            trainer.optimizer.load_state_dict(part)
     trainer.step = step
     trainer.micro = step * trainer.cfg.grad_accum
     return step, seed
+
+
+def reshard_8bit_state(files, new_rank: int, new_world: int, shard_numel: int, block: int = 256):
+    """Block-wise 8-bit optimizer state saved by ``len(files)`` ranks -> the slice that rank
+    ``new_rank`` of ``new_world`` owns. Shards are contiguous ranges of the flat parameter arena
+    and start on block boundaries in every layout, so the codes and the per-block maxima are
+    concatenated and cut again without de-quantising (lossless); a longer new layout is padded with
+    zero codes (value 0)."""
+    parts = [st.load_file(f) for f in files]
+    out = {}
+    for key, per_elem in (("m_q", 1), ("v_q", 1), ("m_absmax", block), ("v_absmax", block)):
+        full = torch.cat([p[f"optimizer.{key}"].reshape(-1).cpu() for p in parts])
+        n = shard_numel // per_elem
+        lo, hi = new_rank * n, (new_rank + 1) * n
+        if hi > full.numel():
+            full = torch.cat([full, torch.zeros(hi - full.numel(), dtype=full.dtype)])
+        out[key] = full[lo:hi].clone()
+    return out
 
 
 def export_lora(trainer, path, layout="kohya"):

@@ -157,3 +157,32 @@ def test_run_training_leaves_with_a_checkpoint_when_a_peer_is_gone(tmp_path):
         run_training(tr, batches(), 10, log_every=100, print_fn=lambda *_: None, heartbeat=me)
     assert e.value.left == [1] and tr.step == 3
     assert sorted(p.name for p in tmp_path.glob("step_*")) == ["step_000003"]
+
+
+def test_8bit_optimizer_state_resharding(tmp_path):
+    from eridiffusion_b200.io import safetensors as st
+    from eridiffusion_b200.train.checkpoint import reshard_8bit_state
+    g = torch.Generator().manual_seed(0)
+    nblk = 12                                            # 12 blocks of 256 saved by 2 ranks
+    full = {"m_q": torch.randint(-127, 127, (nblk * 256,), generator=g, dtype=torch.int8),
+            "v_q": torch.randint(0, 255, (nblk * 256,), generator=g, dtype=torch.uint8),
+            "m_absmax": torch.rand(nblk, generator=g), "v_absmax": torch.rand(nblk, generator=g)}
+    files = []
+    for r in range(2):
+        sl, bl = slice(r * 6 * 256, (r + 1) * 6 * 256), slice(r * 6, (r + 1) * 6)
+        f = tmp_path / f"optimizer.rank{r}.safetensors"
+        st.save_file({"optimizer.m_q": full["m_q"][sl], "optimizer.v_q": full["v_q"][sl],
+                      "optimizer.m_absmax": full["m_absmax"][bl], "optimizer.v_absmax": full["v_absmax"][bl]}, f)
+        files.append(f)
+    one = reshard_8bit_state(files, 0, 1, nblk * 256)
+    assert all(torch.equal(one[k], full[k]) for k in full)
+    # 3 ranks: 4 blocks each
+    for r in range(3):
+        p = reshard_8bit_state(files, r, 3, 4 * 256)
+        assert torch.equal(p["m_q"], full["m_q"][r * 1024:(r + 1) * 1024])
+        assert torch.equal(p["v_absmax"], full["v_absmax"][r * 4:(r + 1) * 4])
+    # 8 ranks need 16 blocks (2 per rank): the tail is zero padding
+    last = reshard_8bit_state(files, 7, 8, 2 * 256)
+    assert last["m_q"].abs().sum() == 0 and last["v_absmax"].sum() == 0 and last["m_q"].numel() == 512
+    p5 = reshard_8bit_state(files, 5, 8, 2 * 256)
+    assert torch.equal(p5["v_q"], full["v_q"][10 * 256:12 * 256])
