@@ -60,6 +60,32 @@ def load_cached_tensor(path, dtype=torch.bfloat16):
     return t.to(dtype)
 
 
+def load_cached_tensors(paths, dtype=torch.bfloat16, prefetcher=None):
+    """``load_cached_tensor`` for many files at once. With a native ``Prefetcher`` every payload is
+    queued first, so the reads of a batch overlap on the worker threads."""
+    if prefetcher is None:
+        return [load_cached_tensor(p, dtype) for p in paths]
+    pending = []
+    for p in paths:
+        f = st.SafeFile(p)
+        keys = f.keys()
+        key = next((k for k in _KEY_ORDER if k in keys), keys[0])
+        pending.append((f, key, prefetcher.submit_tensor(f, key)))
+    out = []
+    for f, key, ticket in pending:
+        try:
+            raw = prefetcher.wait(ticket)
+            dt, shape = f.info(key)
+            t = raw.view(dt).view(shape).clone() if raw.numel() else torch.empty(shape, dtype=dt)
+        finally:
+            prefetcher.release(ticket)
+            f.close()
+        if t.dim() >= 3 and t.shape[0] == 1:
+            t = t.squeeze(0)
+        out.append(t.to(dtype))
+    return out
+
+
 def save_cached_tensor(path, t, key="data"):
     st.save_file({key: t}, path)
 
@@ -164,6 +190,14 @@ class CachedEmbeddingLoader:
         self._q = queue.Queue(maxsize=max(1, prefetch))
         self._stop = threading.Event()
         self._stream = torch.cuda.Stream() if self.device.type == "cuda" else None
+        # native read-ahead threads for the per-sample files (csrc/host/prefetch.cpp) when built
+        self._pf = None
+        if os.environ.get("ERI_B200_NATIVE_PREFETCH", "1") == "1":
+            try:
+                from ..io.native_host import Prefetcher
+                self._pf = Prefetcher(threads=4, max_inflight=max(8, 4 * batch_size))
+            except Exception:
+                self._pf = None
         self._thread = threading.Thread(target=self._worker, daemon=True)
         self._thread.start()
 
@@ -180,10 +214,11 @@ class CachedEmbeddingLoader:
         es = [self.entries[i] for i in idxs]
         pin = self.device.type == "cuda"
         out = {"captions": [e.caption for e in es], "metadata": [e.metadata for e in es]}
-        lat = torch.stack([load_cached_tensor(e.paths["latents_path"]) for e in es])
+        many = lambda col: load_cached_tensors([e.paths[col] for e in es], prefetcher=self._pf)
+        lat = torch.stack(many("latents_path"))
         out["latents"] = lat
         if self.kind == "flux":
-            txts = [load_cached_tensor(e.paths["t5_path"]) for e in es]
+            txts = many("t5_path")
             T = max(t.shape[0] for t in txts)
             txt = torch.zeros(len(es), T, txts[0].shape[-1], dtype=torch.bfloat16)
             mask = torch.zeros(len(es), 1, 1, T, dtype=torch.bool)
@@ -191,11 +226,11 @@ class CachedEmbeddingLoader:
                 txt[i, : t.shape[0]] = t
                 mask[i, ..., : t.shape[0]] = True
             out["txt"], out["txt_mask"] = txt, mask
-            out["pooled"] = torch.stack([load_cached_tensor(e.paths["clip_path"]).reshape(-1) for e in es])
+            out["pooled"] = torch.stack([t.reshape(-1) for t in many("clip_path")])
         else:
-            out["clip_l"] = torch.stack([load_cached_tensor(e.paths["clip_l_path"]) for e in es])
-            out["clip_g"] = torch.stack([load_cached_tensor(e.paths["clip_g_path"]) for e in es])
-            out["pooled"] = torch.stack([load_cached_tensor(e.paths["pooled_path"]).reshape(-1) for e in es])
+            out["clip_l"] = torch.stack(many("clip_l_path"))
+            out["clip_g"] = torch.stack(many("clip_g_path"))
+            out["pooled"] = torch.stack([t.reshape(-1) for t in many("pooled_path")])
             h, w = lat.shape[-2] * 8, lat.shape[-1] * 8
             ids = [[e.metadata.get("orig_h", h), e.metadata.get("orig_w", w), e.metadata.get("crop_y", 0),
                     e.metadata.get("crop_x", 0), e.metadata.get("tgt_h", h), e.metadata.get("tgt_w", w)] for e in es]
@@ -255,6 +290,10 @@ class CachedEmbeddingLoader:
 
     def close(self):
         self._stop.set()
+        if self._pf is not None:
+            self._thread.join(timeout=5)
+            self._pf.close()
+            self._pf = None
 
 
 # ------------------------------------------------------------------------- synthetic batches

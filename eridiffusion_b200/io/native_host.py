@@ -32,6 +32,13 @@ def lib():
         h.eri_sha256_file.restype, h.eri_sha256_file.argtypes = I, [C.c_char_p, C.c_char_p]
         h.eri_sha256_bytes.restype, h.eri_sha256_bytes.argtypes = I, [C.c_char_p, L, C.c_char_p]
         h.eri_xorshift_permutation.argtypes = [L, C.c_ulonglong, C.POINTER(L)]
+        if hasattr(h, "eri_prefetch_create"):
+            h.eri_prefetch_create.restype, h.eri_prefetch_create.argtypes = P, [I, I]
+            h.eri_prefetch_submit.restype, h.eri_prefetch_submit.argtypes = L, [P, C.c_char_p, L, L]
+            h.eri_prefetch_wait.restype, h.eri_prefetch_wait.argtypes = I, [P, L, C.POINTER(P), C.POINTER(L)]
+            h.eri_prefetch_release.restype, h.eri_prefetch_release.argtypes = I, [P, L]
+            h.eri_prefetch_bytes_read.restype, h.eri_prefetch_bytes_read.argtypes = L, [P]
+            h.eri_prefetch_destroy.argtypes = [P]
         _lib = h
     return _lib
 
@@ -90,6 +97,59 @@ class NativeSafeFile:
         if self.h:
             lib().eri_st_close(self.h)
             self.h = None
+
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *a):
+        self.close()
+
+
+class Prefetcher:
+    """Read-ahead of file byte ranges on native worker threads into pinned buffers
+    (``csrc/host/prefetch.cpp``). ``submit`` returns a ticket at once (it blocks only while
+    ``max_inflight`` tickets are outstanding), ``wait`` returns the bytes as a uint8 tensor that
+    aliases the pinned buffer, ``release`` hands the buffer back to the pool."""
+
+    _ERR = {-1: "unknown ticket", -2: "cannot open the file", -3: "short read", -4: "out of memory"}
+
+    def __init__(self, threads: int = 4, max_inflight: int = 16):
+        h = lib()
+        if h is None or not hasattr(h, "eri_prefetch_create"):
+            raise RuntimeError("native host library without the prefetcher; run python -m eridiffusion_b200.csrc.build")
+        self._h, self._p = h, h.eri_prefetch_create(threads, max_inflight)
+
+    def submit(self, path, offset: int, nbytes: int) -> int:
+        t = self._h.eri_prefetch_submit(self._p, str(path).encode(), int(offset), int(nbytes))
+        if t < 0:
+            raise ValueError(f"prefetch submit rejected ({path}, {offset}, {nbytes})")
+        return t
+
+    def submit_tensor(self, safe_file, name: str) -> int:
+        """Queue the payload of tensor ``name`` of an ``io.safetensors.SafeFile``."""
+        b, e = safe_file.header[name]["data_offsets"]
+        return self.submit(safe_file.path, safe_file._base + b, e - b)
+
+    def wait(self, ticket: int):
+        ptr, n = C.c_void_p(), C.c_longlong()
+        code = self._h.eri_prefetch_wait(self._p, ticket, C.byref(ptr), C.byref(n))
+        if code != 0:
+            raise OSError(f"prefetch ticket {ticket}: {self._ERR.get(code, code)}")
+        if n.value == 0:
+            return torch.empty(0, dtype=torch.uint8)
+        buf = (C.c_ubyte * n.value).from_address(ptr.value)
+        return torch.frombuffer(buf, dtype=torch.uint8)
+
+    def release(self, ticket: int) -> None:
+        self._h.eri_prefetch_release(self._p, ticket)
+
+    def bytes_read(self) -> int:
+        return self._h.eri_prefetch_bytes_read(self._p)
+
+    def close(self):
+        if self._p:
+            self._h.eri_prefetch_destroy(self._p)
+            self._p = None
 
     def __enter__(self):
         return self
