@@ -65,6 +65,12 @@ def load_cached_tensors(paths, dtype=torch.bfloat16, prefetcher=None):
     queued first, so the reads of a batch overlap on the worker threads."""
     if prefetcher is None:
         return [load_cached_tensor(p, dtype) for p in paths]
+    win = getattr(prefetcher, "max_inflight", 1)
+    if len(paths) > win:                      # never queue more than the prefetcher holds at once
+        out = []
+        for i in range(0, len(paths), win):
+            out += load_cached_tensors(paths[i:i + win], dtype, prefetcher)
+        return out
     pending = []
     for p in paths:
         f = st.SafeFile(p)

@@ -117,6 +117,7 @@ class Prefetcher:
         h = lib()
         if h is None or not hasattr(h, "eri_prefetch_create"):
             raise RuntimeError("native host library without the prefetcher; run python -m eridiffusion_b200.csrc.build")
+        self.max_inflight = max(1, int(max_inflight))
         self._h, self._p = h, h.eri_prefetch_create(threads, max_inflight)
 
     def submit(self, path, offset: int, nbytes: int) -> int:
