@@ -27,7 +27,8 @@ from pathlib import Path
 import yaml
 
 MODEL_KINDS = ("flux", "sdxl", "sd3", "sd35", "qwen_image", "wan22", "ltx", "hunyuan", "lumina",
-               "hidream_i1", "omnigen2", "chroma", "klein", "zimage", "tiny_mmdit")
+               "hidream_i1", "hidream", "omnigen2", "chroma", "klein", "zimage", "krea", "qwen_edit_image",
+               "tiny_mmdit")
 
 
 class ConfigError(ValueError):
@@ -200,6 +201,14 @@ def _take(cls, d: dict, where: str, rename: dict | None = None):
     unknown = set(d) - names
     if unknown:
         raise ConfigError(f"unknown keys in {where}: {sorted(unknown)}")
+    # YAML 1.1 reads ``1e-05`` (no dot) as a string: numeric fields take such strings as numbers
+    for f in fields(cls):
+        v = d.get(f.name)
+        if isinstance(v, str) and str(f.type) in ("float", "int"):
+            try:
+                d[f.name] = float(v) if str(f.type) == "float" else int(v)
+            except ValueError:
+                raise ConfigError(f"{where}.{f.name}: {v!r} is not a number") from None
     return cls(**d)
 
 
@@ -345,6 +354,19 @@ ENV_VARS = {
     "ERI_B200_NO_BUILD": "1: never try to build the native library on import",
     "ERI_B200_FROZEN_TRANSPOSE": "1: keep transposed copies of frozen weights for input-gradient GEMMs",
     "ERI_B200_WAIT_MS": "bound of in-kernel cross-GPU waits, milliseconds",
+    "ERI_B200_GEMM2": "1 | 0: two-CTA (cta_group::2) GEMM tiles for large problems",
+    "ERI_B200_GATHER_PAIR": "1 | 0: gather-fused GEMMs on the two-CTA kernel",
+    "ERI_B200_GATHER_LOCAL": "1 | 0: read this rank's own slab in place instead of copying it",
+    "ERI_B200_ZERO3_GATHER": "sm | ce: copy CTAs inside the GEMM launch, or copy engines on a side stream",
+    "ERI_B200_RANK_STREAM": "1 | 0: streaming kernel for LoRA down-projections",
+    "ERI_B200_SKINNY_MIN_K": "smallest K that uses the split-K tcgen05 kernel when the streaming kernel declines",
+    "ERI_B200_PDL": "1 | 0: launch the LoRA-fused GEMM as a programmatic dependent of the down-projection",
+    "ERI_B200_ACCUM_INTO_GRAD": "1 | 0: accumulate adapter gradients into the arena inside the GEMM call",
+    "ERI_B200_FA_POLY / ERI_B200_FA_BWD_POLY": "0 | 4 | 8: exponentials per 16 pairs evaluated as a polynomial",
+    "ERI_B200_NVTX": "1: NVTX ranges per block and phase",
+    "ERI_B200_PHASE_TIMING": "1: device-timed noise / forward / backward / optimizer phases in the trainer",
+    "ERI_B200_NATIVE_PREFETCH": "1 | 0: native read-ahead threads in the cached-embedding loader",
+    "ERI_B200_PLUGINS": "colon-separated plug-in modules loaded at start-up",
     "TRAIN_LOG_CSV": "per-step CSV path (step,loss,grad_norm,sec_per_it,alloc_mb,ckpt_path)",
     "CKPT_EVERY": "checkpoint interval override",
     "EXPECT_STEP_SEC": "fail the run when a step is slower than this many seconds",
