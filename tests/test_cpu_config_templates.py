@@ -30,3 +30,9 @@ def test_numeric_strings_and_bad_values():
     with pytest.raises(C.ConfigError):
         C.load_config({"model_kind": "flux", "lr": "fast"})
     assert "ERI_B200_PDL" in C.ENV_VARS and "ERI_B200_ZERO3_GATHER" in C.ENV_VARS
+
+
+def test_nested_template_loads():
+    cfg = C.load_config(Path(C.__file__).parent / "templates" / "flux_lora_nested.yaml")
+    assert cfg.model.kind == "flux" and cfg.network.linear == 16 and cfg.parallel.fused_comm == "on"
+    assert cfg.sample.sample_every == 250 and cfg.network.lr_if_contains == {"single_blocks": 0.5}
