@@ -131,6 +131,37 @@ def attention_fp32(q, k, v, scale=None, mask=None):
     return torch.einsum("bhlm,bmhd->blhd", p, v.float())
 
 
+def attention_chunked(q, k, v, scale=None, q_chunk=1024, kv_chunk=1024):
+    """Blockwise attention with an online softmax: queries in chunks of ``q_chunk``, keys / values
+    in chunks of ``kv_chunk``, a running row maximum ``m``, row sum ``l`` and accumulator that is
+    rescaled when the maximum moves. Peak memory is one [B, H, q_chunk, kv_chunk] score block
+    instead of [B, H, Lq, Lk]. This is the reference's single-GPU long-sequence mechanism
+    (``sdpa_chunked_bf16``, crates/training/src/sdxl/runtime.rs:2814-3025; running ``(m, l, acc)``
+    at :2958-2997) and the recurrence the tcgen05 flash kernels implement; here it serves the
+    eager path when the score matrix would not fit, and as an oracle for the kernels' recurrence.
+    Differentiable through autograd. Token-major [B, L, H, Dh] in and out."""
+    B, Lq, H, D = q.shape
+    Lk = k.shape[1]
+    scale = scale if scale is not None else 1.0 / math.sqrt(D)
+    qh, kh, vh = (t.transpose(1, 2).float() for t in (q, k, v))          # [B, H, L, D]
+    outs = []
+    for q0 in range(0, Lq, q_chunk):
+        qc = qh[:, :, q0:q0 + q_chunk] * scale
+        m = torch.full(qc.shape[:-1], float("-inf"), device=q.device)
+        l = torch.zeros_like(m)
+        acc = torch.zeros(*qc.shape[:-1], vh.shape[-1], device=q.device)
+        for k0 in range(0, Lk, kv_chunk):
+            s = qc @ kh[:, :, k0:k0 + kv_chunk].transpose(-1, -2)
+            m_new = torch.maximum(m, s.amax(-1))
+            alpha = torch.exp(m - m_new)                                  # exp(-inf) = 0 on the first chunk
+            p = torch.exp(s - m_new.unsqueeze(-1))
+            l = l * alpha + p.sum(-1)
+            acc = acc * alpha.unsqueeze(-1) + p @ vh[:, :, k0:k0 + kv_chunk]
+            m = m_new
+        outs.append(acc / l.unsqueeze(-1))
+    return torch.cat(outs, dim=2).transpose(1, 2).to(q.dtype).contiguous()
+
+
 def linear(x, w, bias=None, lora=None, act=None, residual=None, gate=None):
     """y = act(x W^T + bias + s * (x A^T) B^T); then residual + gate[:, None] * y.
 

@@ -15,6 +15,8 @@ from collections import OrderedDict
 
 import torch
 
+builtins_range = range          # the module defines its own ``range`` context manager below
+
 _NVTX = os.environ.get("ERI_B200_NVTX") == "1"
 
 
@@ -106,3 +108,22 @@ class PhaseTimer:
     def format(self):
         s = self.summary()
         return "  ".join(f"{k} {v['ms'] / max(1, v['calls']):.2f} ms ({100 * v['share']:.0f}%)" for k, v in s.items())
+
+
+def profile_steps(step_fn, n_steps: int, out_path, warmup: int = 1, with_stack: bool = False):
+    """Run ``step_fn()`` ``warmup + n_steps`` times under ``torch.profiler`` (CPU activity, plus CUDA
+    when a GPU is present), write a Chrome trace to ``out_path`` and return the per-kernel / per-op
+    table as text. A diagnostic: timings taken under the profiler are not benchmark numbers."""
+    from torch.profiler import ProfilerActivity, profile
+    acts = [ProfilerActivity.CPU] + ([ProfilerActivity.CUDA] if torch.cuda.is_available() else [])
+    for _ in builtins_range(warmup):
+        step_fn()
+    with profile(activities=acts, with_stack=with_stack) as prof:
+        for i in builtins_range(n_steps):
+            with range(f"step {i}"):
+                step_fn()
+        if torch.cuda.is_available():
+            torch.cuda.synchronize()
+    prof.export_chrome_trace(str(out_path))
+    key = "cuda_time_total" if torch.cuda.is_available() else "cpu_time_total"
+    return prof.key_averages().table(sort_by=key, row_limit=30)
