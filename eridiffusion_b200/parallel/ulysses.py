@@ -32,7 +32,7 @@ from .symm import Communicator, SymmetricHeap
 
 class UlyssesContext:
     def __init__(self, pg: ProcessGroup | None, batch: int, l_local: int, hidden: int, heads: int,
-                 n_copy: int = 8, wait_ms: float = 2000.0, attn_slots: int = 1):
+                 n_copy: int = 16, wait_ms: float = 2000.0, attn_slots: int = 1):
         self.pg = pg or ProcessGroup()
         self.rank, self.world = self.pg.rank, self.pg.world_size
         W = self.world
