@@ -21,7 +21,7 @@ import torch.nn as nn
 
 from ..ops import functional as F
 from .layers import Linear, MLPEmbedder, Modulation, RMSNormScale, rope_table, timestep_embedding
-from .mmdit import DoubleStreamBlock, LastLayer, MMDiTConfig
+from .mmdit import DoubleStreamBlock, LastLayer, MMDiTConfig, SelfAttentionProj
 from .registry import register_model
 
 
@@ -34,9 +34,72 @@ def sincos_2d(dim, h, w, device=None):
     return torch.cat([one(dim // 2, yy), one(dim // 2, xx)], dim=1).float()
 
 
+class SD35JointBlock(nn.Module):
+    """Joint block with the two SD3.5 variations of the plain two-stream block
+    (src/models/mmdit_blocks.rs:2393-2394):
+
+    * ``context_pre_only`` (the last block): the text stream only feeds the joint attention. It has
+      a 2-way modulation and a q/k/v projection, no output projection and no MLP, and leaves the
+      block unchanged.
+    * ``x_self_attn`` (the "dual attention" blocks of SD3.5-medium): a second, image-only
+      self-attention. The image modulation is 9-way; the second attention reads the same
+      normalised input with its own shift / scale and is added with its own gate.
+    """
+
+    def __init__(self, cfg: MMDiTConfig, dtype, device, context_pre_only=False, x_self_attn=False):
+        super().__init__()
+        D, H = cfg.hidden, cfg.num_heads
+        mlp = int(D * cfg.mlp_ratio)
+        self.heads, self.context_pre_only, self.x_self_attn = H, context_pre_only, x_self_attn
+        self.img_mod = Modulation(D, 9 if x_self_attn else 6, dtype=dtype, device=device)
+        self.txt_mod = Modulation(D, 2 if context_pre_only else 6, dtype=dtype, device=device)
+        self.img_attn = SelfAttentionProj(D, H, cfg.qkv_bias, dtype, device)
+        self.txt_attn = SelfAttentionProj(D, H, cfg.qkv_bias, dtype, device)
+        if context_pre_only:
+            self.txt_attn.proj = None
+        self.img_attn2 = SelfAttentionProj(D, H, cfg.qkv_bias, dtype, device) if x_self_attn else None
+        self.img_mlp_0 = Linear(D, mlp, dtype=dtype, device=device)
+        self.img_mlp_2 = Linear(mlp, D, dtype=dtype, device=device)
+        if not context_pre_only:
+            self.txt_mlp_0 = Linear(D, mlp, dtype=dtype, device=device)
+            self.txt_mlp_2 = Linear(mlp, D, dtype=dtype, device=device)
+
+    def forward(self, img, txt, vec, cos=None, sin=None):
+        im = self.img_mod(vec)
+        i_sh1, i_sc1, i_g1, i_sh2, i_sc2, i_g2 = im[:6]
+        tm = self.txt_mod(vec)
+        t_sh1, t_sc1 = tm[0], tm[1]
+        Lt = txt.shape[1]
+        img_qkv = self.img_attn.qkv(F.norm_modulate(img, i_sc1, i_sh1))
+        txt_qkv = self.txt_attn.qkv(F.norm_modulate(txt, t_sc1, t_sh1))
+        q, k, v = F.qknorm_rope_joint(
+            [(txt_qkv, self.txt_attn.q_norm.scale, self.txt_attn.k_norm.scale),
+             (img_qkv, self.img_attn.q_norm.scale, self.img_attn.k_norm.scale)],
+            cos, sin, self.heads)
+        attn = F.attention(q, k, v).flatten(2)
+        txt_a, img_a = attn[:, :Lt], attn[:, Lt:]
+        x = self.img_attn.proj(img_a, residual=img, gate=i_g1)
+        if self.x_self_attn:
+            i_sh3, i_sc3, i_g3 = im[6:9]
+            qkv2 = self.img_attn2.qkv(F.norm_modulate(img, i_sc3, i_sh3))
+            q2, k2, v2 = F.qknorm_rope_joint(
+                [(qkv2, self.img_attn2.q_norm.scale, self.img_attn2.k_norm.scale)], None, None, self.heads)
+            x = self.img_attn2.proj(F.attention(q2, k2, v2).flatten(2), residual=x, gate=i_g3)
+        img = self.img_mlp_2(self.img_mlp_0(F.norm_modulate(x, i_sc2, i_sh2), act="gelu"),
+                             residual=x, gate=i_g2)
+        if self.context_pre_only:
+            return img, txt
+        t_g1, t_sh2, t_sc2, t_g2 = tm[2:6]
+        txt = self.txt_attn.proj(txt_a, residual=txt, gate=t_g1)
+        txt = self.txt_mlp_2(self.txt_mlp_0(F.norm_modulate(txt, t_sc2, t_sh2), act="gelu"),
+                             residual=txt, gate=t_g2)
+        return img, txt
+
+
 class SD35MMDiT(nn.Module):
     def __init__(self, hidden=2432, num_heads=38, depth=38, in_channels=64, context_dim=4096,
-                 pooled_dim=2048, mlp_ratio=4.0, dtype=torch.bfloat16, device=None):
+                 pooled_dim=2048, mlp_ratio=4.0, dtype=torch.bfloat16, device=None,
+                 context_pre_only_last=False, x_self_attn_layers=()):
         super().__init__()
         self.cfg = MMDiTConfig(in_channels=in_channels, hidden=hidden, num_heads=num_heads,
                                depth_double=depth, depth_single=0, mlp_ratio=mlp_ratio,
@@ -47,7 +110,14 @@ class SD35MMDiT(nn.Module):
         self.context_embedder = Linear(context_dim, D, dtype=dtype, device=device)
         self.t_embedder = MLPEmbedder(256, D, dtype=dtype, device=device)
         self.y_embedder = MLPEmbedder(pooled_dim, D, dtype=dtype, device=device)
-        self.joint_blocks = nn.ModuleList(DoubleStreamBlock(self.cfg, dtype, device) for _ in range(depth))
+        dual = set(x_self_attn_layers)
+
+        def block(i):
+            pre_only = context_pre_only_last and i == depth - 1
+            if pre_only or i in dual:
+                return SD35JointBlock(self.cfg, dtype, device, context_pre_only=pre_only, x_self_attn=i in dual)
+            return DoubleStreamBlock(self.cfg, dtype, device)
+        self.joint_blocks = nn.ModuleList(block(i) for i in range(depth))
         self.final_layer = LastLayer(D, in_channels, dtype, device)
         self._pos = {}
 
@@ -71,12 +141,22 @@ class SD35MMDiT(nn.Module):
         return self.final_layer(x, vec)
 
     def lora_targets(self):
-        return [r"joint_blocks\.\d+\.(img|txt)_attn\.(qkv|proj)$", r"joint_blocks\.\d+\.(img|txt)_mlp_[02]$"]
+        return [r"joint_blocks\.\d+\.(img|txt)_attn2?\.(qkv|proj)$", r"joint_blocks\.\d+\.(img|txt)_mlp_[02]$"]
 
 
 @register_model("sd35")
 def build_sd35(dtype=torch.bfloat16, device=None, **kw):
     return SD35MMDiT(dtype=dtype, device=device, **kw)
+
+
+@register_model("sd35_medium")
+def build_sd35_medium(dtype=torch.bfloat16, device=None, **kw):
+    """SD3.5-medium layout: 24 blocks, hidden 1536 (24 x 64), image-only second attention in blocks
+    0-12, text stream dropped after the last block's attention."""
+    base = dict(hidden=1536, num_heads=24, depth=24, context_pre_only_last=True,
+                x_self_attn_layers=tuple(range(13)))
+    base.update(kw)
+    return SD35MMDiT(dtype=dtype, device=device, **base)
 
 
 # ------------------------------------------------------------------------------ Klein

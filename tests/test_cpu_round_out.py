@@ -1,0 +1,172 @@
+"""Accumulation service, parameter registry, SD3.5 block variants and projections (CPU)."""
+import json
+import types
+
+import pytest
+import torch
+
+from eridiffusion_b200.io.param_registry import ParamRegistry, assert_vram_below, vram_used_gb
+from eridiffusion_b200.train.accumulation import (AccumulationConfig, CheckpointSelection, DynamicAccumulator,
+                                                  GradientAccumulator, ReductionMode, SyncMode,
+                                                  create_accumulation_schedule, effective_batch_size,
+                                                  estimate_memory_requirement)
+
+
+# ----------------------------------------------------------------------------- accumulation
+def test_accumulator_mean_sum_weighted():
+    g1, g2 = torch.tensor([1.0, 2.0]), torch.tensor([3.0, 6.0])
+    for red, want in ((ReductionMode.MEAN, [2.0, 4.0]), (ReductionMode.SUM, [4.0, 8.0]),
+                      (ReductionMode.WEIGHTED_MEAN, [1.0, 2.0])):
+        acc = GradientAccumulator(AccumulationConfig(steps=2, reduction=red, weight=0.5))
+        acc.accumulate("w", g1); acc.step()
+        assert not acc.should_sync()
+        acc.accumulate("w", g2); acc.step()
+        assert acc.should_sync()
+        assert acc.memory_usage() == 8
+        out = acc.get_gradients()
+        assert torch.allclose(out["w"], torch.tensor(want))
+        assert acc.current_step == 0 and acc.memory_usage() == 0
+    # the accumulator owns its buffer: the caller's gradient is not modified
+    assert torch.equal(g1, torch.tensor([1.0, 2.0]))
+
+
+def test_accumulator_sync_modes_count_reductions():
+    calls = []
+
+    def reduce_fn(t):
+        calls.append(t.clone())
+        t.mul_(2.0)                      # stands for a SUM over two identical ranks
+
+    for mode, n_sync in ((SyncMode.IMMEDIATE, 4), (SyncMode.DEFERRED, 1), (SyncMode.ADAPTIVE, 1)):
+        calls.clear()
+        acc = GradientAccumulator(AccumulationConfig(steps=4, sync_mode=mode), reduce_fn)
+        for i in range(4):
+            acc.accumulate("w", torch.full((3,), float(i)))
+            acc.step()
+        out = acc.get_gradients()["w"]
+        assert acc.syncs == n_sync == len(calls)
+        assert torch.allclose(out, torch.full((3,), 2.0 * (0 + 1 + 2 + 3) / 4))
+
+
+def test_accumulator_stats_and_apply():
+    p = torch.nn.Parameter(torch.zeros(2, 2, dtype=torch.bfloat16))
+    acc = GradientAccumulator(AccumulationConfig(steps=1, dtype="float32"))
+    acc.accumulate("p", torch.ones(2, 2), scale=0.5)
+    acc.accumulate("bad", torch.tensor([float("nan")]))
+    st = acc.stats()
+    assert st.num_tensors == 2 and st.num_nonfinite == 1 and abs(st.total_norm - 1.0) < 1e-6
+    acc.apply_to({"p": p})
+    assert p.grad.dtype == torch.bfloat16 and torch.allclose(p.grad.float(), torch.full((2, 2), 0.5))
+    with pytest.raises(ValueError):
+        AccumulationConfig(dtype="int8")
+
+
+def test_dynamic_accumulator_and_helpers():
+    dyn = DynamicAccumulator(AccumulationConfig(steps=2), memory_threshold=1000)
+    assert dyn.adjust_steps(2000, 0.1) == 4
+    assert dyn.adjust_steps(2000, 0.1) == 8
+    assert dyn.adjust_steps(700, 0.1) == 8
+    assert dyn.adjust_steps(100, 0.1) == 4
+    for _ in range(10):
+        dyn.adjust_steps(700, 2.0)
+    assert dyn.get_optimal_config().sync_mode == SyncMode.DEFERRED
+    dyn2 = DynamicAccumulator(AccumulationConfig(steps=64), memory_threshold=1000)
+    assert dyn2.adjust_steps(5000, 0.1) == 64                 # capped
+    assert effective_batch_size(4, 8) == 32 and effective_batch_size(4, 8, 8) == 256
+    assert estimate_memory_requirement(10, 2, 3, 2) == 3 * 20 + 10 * 4 * 2 * 3 * 2
+    assert create_accumulation_schedule(6, 4, 5) == [1, 2, 3, 4, 5, 5]
+    sel = CheckpointSelection(True, segment_size=2)
+    sel.select_every([f"b{i}" for i in range(6)])
+    assert sel.should_checkpoint("b0") and not sel.should_checkpoint("b1")
+    assert abs(sel.estimate_memory_savings(6) - 0.5 * 0.33) < 1e-6
+    assert CheckpointSelection(False).estimate_memory_savings(6) == 0.0
+
+
+# ----------------------------------------------------------------------------- registry
+def test_param_registry():
+    reg = ParamRegistry()
+    a = reg.insert("a", torch.zeros(2, 3))
+    b = reg.insert("b", torch.zeros(4, dtype=torch.bfloat16))
+    assert a != b and reg.id_of("a") == a and reg.name_of(b) == "b" and len(reg) == 2
+    reg.set_requires_grad([b])
+    assert reg.get("b").requires_grad and not reg.get("a").requires_grad
+    reg.assign(a, torch.ones(5))
+    assert reg.get_by_id(a).shape == (5,)
+    s = json.loads(reg.emit_json_summary())
+    assert s["count"] == 2 and s["bytes"] == 20 + 8 and s["trainable"] == 1
+    assert reg.remove("a") and not reg.remove("a") and reg.get_by_id(a) is None
+    with pytest.raises(KeyError):
+        reg.assign(a, torch.zeros(1))
+    lin = torch.nn.Linear(3, 2)
+    assert {n for n, _, _ in ParamRegistry.from_module(lin, "m.")} == {"m.weight", "m.bias"}
+
+
+def test_vram_guard_with_fake_nvml():
+    fake = types.SimpleNamespace(
+        nvmlInit=lambda: None, nvmlDeviceGetHandleByIndex=lambda i: i,
+        nvmlDeviceGetMemoryInfo=lambda h: types.SimpleNamespace(used=3 * 2 ** 30))
+    assert vram_used_gb(nvml=fake) == 3.0
+    assert assert_vram_below(4.0, nvml=fake) == 3.0
+    with pytest.raises(MemoryError):
+        assert_vram_below(2.0, nvml=fake)
+
+
+# ----------------------------------------------------------------------------- SD3.5
+def _sd35(**kw):
+    from eridiffusion_b200.models.sd35_klein import SD35MMDiT
+    torch.manual_seed(0)
+    m = SD35MMDiT(hidden=64, num_heads=2, depth=3, in_channels=8, context_dim=16, pooled_dim=12,
+                  dtype=torch.float32, **kw)
+    for p in m.parameters():
+        torch.nn.init.normal_(p, std=0.05)
+    return m
+
+
+def test_sd35_context_pre_only_and_dual_attention():
+    from eridiffusion_b200.models.sd35_klein import SD35JointBlock
+    m = _sd35(context_pre_only_last=True, x_self_attn_layers=(0, 1))
+    blocks = m.joint_blocks
+    assert isinstance(blocks[0], SD35JointBlock) and blocks[0].x_self_attn and not blocks[0].context_pre_only
+    assert blocks[2].context_pre_only and not hasattr(blocks[2], "txt_mlp_0") and blocks[2].txt_attn.proj is None
+    assert blocks[0].img_mod.lin.weight.shape[0] == 9 * 64 and blocks[2].txt_mod.lin.weight.shape[0] == 2 * 64
+    img, txt = torch.randn(2, 16, 8), torch.randn(2, 5, 16)
+    t, y = torch.rand(2), torch.randn(2, 12)
+    out = m(img, txt, t, y, grid_hw=(4, 4))
+    assert out.shape == (2, 16, 8) and torch.isfinite(out).all()
+    out.square().mean().backward()
+    assert blocks[0].img_attn2.qkv.weight.grad.abs().sum() > 0
+    assert blocks[2].txt_attn.qkv.weight.grad.abs().sum() > 0
+    # the last block's text stream is a pure input: its result must not depend on text modulation gates
+    x, c = torch.randn(2, 16, 64), torch.randn(2, 5, 64)
+    vec = torch.randn(2, 64)
+    _, c_out = blocks[2](x, c, vec)
+    assert torch.equal(c_out, c)
+    # zero gate on the second attention reproduces the plain joint block's image update
+    plain = _sd35(context_pre_only_last=False)
+    assert not any(isinstance(b, SD35JointBlock) for b in plain.joint_blocks)
+    assert any("attn2" in n for n, _ in m.named_parameters())
+
+
+def test_sd35_projections_match_fp32_statement():
+    from eridiffusion_b200.models.sd35_projections import (Latent1x1Conv, TextLinearPad, VelocityHead,
+                                                           trainable_projections)
+    lat = Latent1x1Conv(32, dtype=torch.float32, seed=1)
+    x = torch.randn(2, 16, 3, 5)
+    want = torch.einsum("bchw,oc->bohw", x, lat.proj.weight) + lat.proj.bias[None, :, None, None]
+    assert torch.allclose(lat(x), want, atol=1e-5)
+    assert abs(float(lat.proj.weight.detach().std()) - 0.25) < 0.05 and float(lat.proj.bias.detach().abs().sum()) == 0
+    with pytest.raises(ValueError):
+        lat(torch.randn(2, 4, 3, 5))
+    tp = TextLinearPad(8, dtype=torch.float32, seed=2, in_dim=12, tokens=7)
+    short, long = torch.randn(1, 3, 12), torch.randn(1, 9, 12)
+    o = tp(short)
+    assert o.shape == (1, 7, 8)
+    assert torch.allclose(o[:, :3], short @ tp.proj.weight.T + tp.proj.bias, atol=1e-5)
+    assert torch.allclose(o[:, 3:], tp.proj.bias.expand(1, 4, 8), atol=1e-6)
+    assert torch.allclose(tp(long), long[:, :7] @ tp.proj.weight.T + tp.proj.bias, atol=1e-5)
+    vh = VelocityHead(32, dtype=torch.float32, seed=3)
+    h = torch.randn(2, 32, 3, 5)
+    assert torch.allclose(vh(h), torch.einsum("bchw,oc->bohw", h, vh.proj.weight), atol=1e-5)
+    d = trainable_projections(32, dtype=torch.float32)
+    assert set(d) == {"latent_in", "text_in", "velocity_out"}
+    assert d["velocity_out"](d["latent_in"](x)).shape == x.shape
