@@ -170,3 +170,23 @@ def test_sd35_projections_match_fp32_statement():
     d = trainable_projections(32, dtype=torch.float32)
     assert set(d) == {"latent_in", "text_in", "velocity_out"}
     assert d["velocity_out"](d["latent_in"](x)).shape == x.shape
+
+
+# ----------------------------------------------------------------------------- slices
+def test_narrow_copy_and_backward_add_cpu_path():
+    from eridiffusion_b200.ops.narrow import narrow_backward_add, narrow_copy, narrow_copy_raw
+    x = torch.randn(3, 10, 4)
+    assert torch.equal(narrow_copy_raw(x, -2, 2, 5), x[:, 2:7])
+    xr = x.clone().requires_grad_()
+    narrow_copy(xr, 1, 2, 5).sum().backward()
+    want = torch.zeros_like(x); want[:, 2:7] = 1
+    assert torch.equal(xr.grad, want)
+    gin = torch.ones(3, 10, 4)
+    narrow_backward_add(torch.full((3, 2, 4), 2.0), gin, 1, 8)
+    assert gin[:, 8:].eq(3).all() and gin[:, :8].eq(1).all()
+    with pytest.raises(IndexError):
+        narrow_copy_raw(x, 1, 8, 5)
+    with pytest.raises(ValueError):
+        narrow_backward_add(torch.zeros(3, 2, 5), gin, 1, 0)
+    with pytest.raises(ValueError):
+        narrow_backward_add(torch.zeros(3, 2, 4), torch.zeros(1, 10, 4).expand(3, 10, 4), 1, 0)
