@@ -125,6 +125,12 @@ class LTXBlock(nn.Module):
         return F.attention(q.view(sh), k.view(sh), recv[:, :, 2].contiguous().view(sh), out=out).view(B, u.Lt, G)
 
     def forward(self, x, ctx, temb6, cos, sin, u=None):
+        x, ff_mod = self.forward_attn(x, ctx, temb6, cos, sin, u)
+        return self.forward_ff(x, ff_mod)
+
+    def forward_attn(self, x, ctx, temb6, cos, sin, u=None):
+        """Self-attention and text cross-attention; returns the stream and the feed-forward's
+        (shift, scale, gate), so that a caller can put work between the two halves of the block."""
         B, L, D = x.shape
         mod = self.scale_shift_table.unsqueeze(0) + temb6                    # [B, 6, D]
         sh_a, sc_a, g_a, sh_m, sc_m, g_m = (mod[:, i] for i in range(6))
@@ -145,6 +151,10 @@ class LTXBlock(nn.Module):
         ca = F.attention(q.view(B, L, self.heads, hd), k.view(B, -1, self.heads, hd),
                          v.contiguous().view(B, -1, self.heads, hd)).view(B, L, D)
         x = self.attn2_out(ca, residual=x)
+        return x, (sh_m, sc_m, g_m)
+
+    def forward_ff(self, x, ff_mod):
+        sh_m, sc_m, g_m = ff_mod
         h = F.norm_modulate(x, sc_m, sh_m, rms=True)
         return self.ff_out(self.ff_in(h, act="gelu"), residual=x, gate=g_m)
 

@@ -190,3 +190,57 @@ def test_narrow_copy_and_backward_add_cpu_path():
         narrow_backward_add(torch.zeros(3, 2, 5), gin, 1, 0)
     with pytest.raises(ValueError):
         narrow_backward_add(torch.zeros(3, 2, 4), torch.zeros(1, 10, 4).expand(3, 10, 4), 1, 0)
+
+
+# ----------------------------------------------------------------------------- LTX audio + video
+def _ltx_av():
+    from eridiffusion_b200.models import build_model
+    torch.manual_seed(0)
+    m = build_model("ltx_av", dtype=torch.float32, hidden=48, num_heads=2, depth=2, in_channels=8,
+                    context_dim=24, caption_dim=12, audio=dict(audio_in_channels=6, audio_heads=2,
+                                                               audio_head_dim=8, audio_context_dim=16))
+    for p in m.parameters():
+        torch.nn.init.normal_(p, std=0.08)
+    return m
+
+
+def test_ltx_audio_video_streams_exchange_information():
+    m = _ltx_av()
+    B, grid, La = 2, (2, 2, 3), 7
+    xv, xa = torch.randn(B, 12, 8), torch.randn(B, La, 6)
+    ctx, t = torch.randn(B, 5, 12), torch.tensor([0.2, 0.8])
+    pv, pa = m(xv, xa, ctx, t, grid)
+    assert pv.shape == xv.shape and pa.shape == xa.shape
+    assert torch.isfinite(pv).all() and torch.isfinite(pa).all()
+    # the audio stream changes the video prediction and the other way round
+    pv2, pa2 = m(xv, xa + 1.0, ctx, t, grid)
+    assert (pv2 - pv).abs().max() > 1e-6
+    pv3, pa3 = m(xv + 1.0, xa, ctx, t, grid)
+    assert (pa3 - pa).abs().max() > 1e-6
+    (pv.square().mean() + pa.square().mean()).backward()
+    assert all(p.grad is not None for n, p in m.named_parameters() if "a2v" in n or "v2a" in n)
+    # closing the cross-modal gates (per-layer row 4 and the gate embedder) decouples the streams
+    # and the video prediction equals the video-only path
+    with torch.no_grad():
+        for blk in m.blocks:
+            blk.video_ca_table[4].zero_(); blk.audio_ca_table[4].zero_()
+        for io in (m.video_io, m.audio_io):
+            io.ca_gate.weight.zero_()
+            if io.ca_gate.bias is not None:
+                io.ca_gate.bias.zero_()
+    pv4, pa4 = m(xv, xa, ctx, t, grid)
+    pv5, _ = m(xv, xa * 3.0, ctx, t, grid)
+    assert torch.allclose(pv4, pv5, atol=1e-6)
+    assert torch.allclose(pv4, m.forward_video_only(xv, ctx, t, grid), atol=1e-5)
+    import re
+    pats = [re.compile(p) for p in m.lora_targets()]
+    hit = [n for n, _ in m.named_modules() if any(p.search(n) for p in pats)]
+    assert len(hit) == 2 * (7 * 2 + 3 * 2)
+
+
+def test_rope_1d_table_aligns_instants():
+    from eridiffusion_b200.models.ltx_av import rope_1d_table
+    c1, s1 = rope_1d_table(torch.tensor([0.0, 1.0, 2.0]), 16)
+    c2, s2 = rope_1d_table(torch.tensor([1.0]), 16)
+    assert c1.shape == (3, 8) and torch.allclose(c1[1], c2[0]) and torch.allclose(s1[1], s2[0])
+    assert torch.allclose(c1 ** 2 + s1 ** 2, torch.ones_like(c1), atol=1e-6)
