@@ -200,7 +200,8 @@ def _request_model():
         from pydantic import create_model
         _REQ_MODEL = create_model("Txt2Img", prompt=(str, ...), negative_prompt=(str, ""), width=(int, 1024),
                                   height=(int, 1024), steps=(int, 20), guidance_scale=(float, 3.5),
-                                  seed=(int, 0), priority=(int, 0), sync=(bool, False))
+                                  seed=(int, 0), priority=(int, 0), sync=(bool, False), strength=(float, 0.8),
+                                  image=(str | None, None), mask=(str | None, None))
     return _REQ_MODEL
 
 
@@ -218,7 +219,17 @@ def create_app(engine: InferenceEngine):
         except Exception as e:
             raise HTTPException(422, str(e))
         sync = d.pop("sync", False)
-        rid = engine.submit(GenerationRequest(mode=mode, **d))
+        # images arrive as base64 PNG text (``image``, ``mask``) and are kept as bytes
+        import base64
+        try:
+            img, msk = (base64.b64decode(v) if v else None for v in (d.pop("image", None), d.pop("mask", None)))
+        except Exception as e:
+            raise HTTPException(422, f"image / mask must be base64: {e}")
+        if mode != "txt2img" and img is None:
+            raise HTTPException(422, f"{mode} needs an `image`")
+        if mode == "inpaint" and msk is None:
+            raise HTTPException(422, "inpaint needs a `mask`")
+        rid = engine.submit(GenerationRequest(mode=mode, init_image=img, mask=msk, **d))
         if sync:
             st, out = engine.wait(rid)
             if st != "done":

@@ -350,7 +350,7 @@ def test_http_routes():
     assert c.get("/health").json()["status"] == "ok"
     r = c.post("/v1/txt2img", json={"prompt": "x", "sync": True})
     assert r.status_code == 200 and r.content == b"\x89PNG"
-    rid = c.post("/v1/img2img", json={"prompt": "y"}).json()["id"]
+    rid = c.post("/v1/img2img", json={"prompt": "y", "image": "eA=="}).json()["id"]
     assert c.get(f"/v1/status/{rid}").status_code == 200
     assert c.get("/v1/status/nope").status_code == 404
     assert "eridiffusion_requests_total" in c.get("/metrics").text
