@@ -28,7 +28,7 @@ import yaml
 
 MODEL_KINDS = ("flux", "sdxl", "sd3", "sd35", "qwen_image", "wan22", "ltx", "hunyuan", "lumina",
                "hidream_i1", "hidream", "omnigen2", "chroma", "klein", "zimage", "krea", "qwen_edit_image",
-               "tiny_mmdit")
+               "tiny_mmdit", "sd15")
 
 
 class ConfigError(ValueError):

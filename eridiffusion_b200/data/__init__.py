@@ -318,6 +318,8 @@ def synthetic_batch(kind="flux", batch=1, device="cpu", dtype=torch.bfloat16, se
     if kind == "sdxl":
         return {"latents": mk(batch, 4, height // 8, width // 8), "txt": mk(batch, 77, 2048), "pooled": mk(batch, 1280),
                 "time_ids": torch.tensor([[height, width, 0, 0, height, width]] * batch, dtype=torch.float32, device=device)}
+    if kind == "sd15":
+        return {"latents": mk(batch, 4, height // 8, width // 8), "txt": mk(batch, 77, 768)}
     if kind in ("sd3", "sd35"):
         return {"latents": mk(batch, 16, height // 8, width // 8), "txt": mk(batch, text_tokens or 333, 4096),
                 "pooled": mk(batch, 2048)}

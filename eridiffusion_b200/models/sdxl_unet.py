@@ -34,7 +34,16 @@ class SDXLConfig:
     context_dim: int = 2048
     groups: int = 32
     addition_time_embed_dim: int = 256
-    pooled_dim: int = 1280
+    pooled_dim: int = 1280                  # 0: no additional (pooled text + size ids) embedding
+    num_heads: int | None = None            # set: a fixed head count per level instead of a fixed head size
+    mid_transformer_depth: int | None = None   # default: the last level's depth
+
+
+# Stable Diffusion 1.5: four levels, one transformer block per attention level (none at the deepest),
+# 8 heads at every width, CLIP-L context (768), no pooled / size conditioning
+# (crates/training/src/pipelines/sd15_pipeline.rs:12-275; src/models/unet_2d.rs).
+SD15_CONFIG = dict(block_channels=(320, 640, 1280, 1280), transformer_depth=(1, 1, 1, 0), context_dim=768,
+                   num_heads=8, pooled_dim=0, mid_transformer_depth=1)
 
 
 class LayerNormAffine(nn.Module):
@@ -108,7 +117,8 @@ class Transformer2D(nn.Module):
         super().__init__()
         self.norm = GroupNormAct(cfg.groups, ch, 1e-6, False, dtype=dtype, device=device)
         self.proj_in = Linear(ch, ch, dtype=dtype, device=device)
-        self.blocks = nn.ModuleList(BasicTransformerBlock(ch, cfg.context_dim, cfg.head_dim, dtype, device)
+        head_dim = ch // cfg.num_heads if cfg.num_heads else cfg.head_dim
+        self.blocks = nn.ModuleList(BasicTransformerBlock(ch, cfg.context_dim, head_dim, dtype, device)
                                     for _ in range(depth))
         self.proj_out = Linear(ch, ch, dtype=dtype, device=device)
 
@@ -148,7 +158,8 @@ class SDXLUNet(nn.Module):
         kw = dict(dtype=dtype, device=device)
         self.time_embed = nn.Sequential(nn.Linear(ch[0], te, **kw), nn.SiLU(), nn.Linear(te, te, **kw))
         add_in = cfg.pooled_dim + 6 * cfg.addition_time_embed_dim
-        self.add_embed = nn.Sequential(nn.Linear(add_in, te, **kw), nn.SiLU(), nn.Linear(te, te, **kw))
+        self.add_embed = nn.Sequential(nn.Linear(add_in, te, **kw), nn.SiLU(), nn.Linear(te, te, **kw)) \
+            if cfg.pooled_dim else None
         self.conv_in = nn.Conv2d(cfg.in_channels, ch[0], 3, padding=1, **kw)
         self.down = nn.ModuleList()
         self.down_kinds = []
@@ -166,8 +177,9 @@ class SDXLUNet(nn.Module):
                 self.down.append(nn.Conv2d(c, c, 3, stride=2, padding=1, **kw))
                 self.down_kinds.append("down")
                 skips.append(c)
+        mid_depth = cfg.transformer_depth[-1] if cfg.mid_transformer_depth is None else cfg.mid_transformer_depth
         self.mid = nn.ModuleList([ResBlock(cin, cin, te, cfg, dtype, device),
-                                  Transformer2D(cin, cfg.transformer_depth[-1], cfg, dtype, device),
+                                  Transformer2D(cin, mid_depth, cfg, dtype, device),
                                   ResBlock(cin, cin, te, cfg, dtype, device)])
         self.up = nn.ModuleList()
         self.up_kinds = []
@@ -191,6 +203,8 @@ class SDXLUNet(nn.Module):
         cfg = self.cfg
         dt = self.conv_in.weight.dtype
         temb = self.time_embed(timestep_embedding(t, cfg.block_channels[0], time_factor=1.0).to(dt))
+        if self.add_embed is None:
+            return temb
         ids = timestep_embedding(time_ids.flatten(), cfg.addition_time_embed_dim, time_factor=1.0)
         ids = ids.view(time_ids.shape[0], -1).to(dt)
         return temb + self.add_embed(torch.cat([pooled.to(dt), ids], dim=-1))
@@ -218,7 +232,7 @@ class SDXLUNet(nn.Module):
         h = self.mid[2](h, emb)
         return h, hs
 
-    def forward(self, x, t, ctx, pooled, time_ids, control=None, adapter_features=None):
+    def forward(self, x, t, ctx, pooled=None, time_ids=None, control=None, adapter_features=None):
         """x [B, 4, H, W]; t [B] timesteps (0..999); ctx [B, 77, 2048]; pooled [B, 1280];
         time_ids [B, 6] = (orig_h, orig_w, crop_y, crop_x, tgt_h, tgt_w). ``control`` =
         (skip residuals, mid residual) from a ControlNet; ``adapter_features`` from a T2I-Adapter."""
@@ -249,11 +263,17 @@ def sdxl_forward(model, xt, t, batch, cfg):
     B, L, C = xt.shape
     hh = batch["latents"].shape[-2]
     x = xt.view(B, hh, L // hh, C).permute(0, 3, 1, 2)
-    out = model(x, t, batch["txt"], batch["pooled"], batch["time_ids"])
+    out = model(x, t, batch["txt"], batch.get("pooled"), batch.get("time_ids"))
     return out.permute(0, 2, 3, 1).reshape(B, L, C)
 
 
 @register_model("sdxl")
 def build_sdxl(dtype=torch.bfloat16, device=None, **overrides):
     cfg = SDXLConfig(**{**SDXLConfig().__dict__, **overrides})
+    return SDXLUNet(cfg, dtype=dtype, device=device)
+
+
+@register_model("sd15")
+def build_sd15(dtype=torch.bfloat16, device=None, **overrides):
+    cfg = SDXLConfig(**{**SDXLConfig().__dict__, **SD15_CONFIG, **overrides})
     return SDXLUNet(cfg, dtype=dtype, device=device)

@@ -17,7 +17,7 @@ _KIND_TO_MODEL = {"flux": "flux", "chroma": "chroma", "qwen_image": "qwen_image"
                   "sd3": "sd35", "sd35": "sd35", "ltx": "ltx_video", "wan22": "wan22", "klein": "klein",
                   "zimage": "zimage", "tiny_mmdit": "tiny_mmdit", "krea": "krea", "hunyuan": "hunyuan",
                   "lumina": "lumina", "hidream_i1": "hidream", "hidream": "hidream", "omnigen2": "omnigen2",
-                  "qwen_edit_image": "qwen_edit_image"}
+                  "qwen_edit_image": "qwen_edit_image", "sd15": "sd15"}
 _UNIMPLEMENTED = set()
 
 
@@ -66,8 +66,8 @@ def build_job(cfg: TrainCfg, device=None):
             grad_sync = GradSync(mode)
 
     objective = {"flowmatch": "flow", "flow": "flow", "ddpm": "eps", "eps": "eps", "v": "v"}.get(
-        cfg.noise_scheduler, "flow" if cfg.model.kind != "sdxl" else "eps")
-    if cfg.model.kind == "sdxl":
+        cfg.noise_scheduler, "flow" if cfg.model.kind not in ("sdxl", "sd15") else "eps")
+    if cfg.model.kind in ("sdxl", "sd15"):
         objective = "eps" if objective == "flow" else objective
     acfg = None
     if cfg.train_mode == "lora":
@@ -83,12 +83,12 @@ def build_job(cfg: TrainCfg, device=None):
         max_grad_norm=cfg.max_grad_norm, ema_decay=cfg.ema_decay, seed=cfg.seed, seq_parallel=seq_par,
         out_dir=cfg.training_folder, ckpt_every=cfg.ckpt_every, keep_last=cfg.save.max_step_saves_to_keep,
         activation_checkpointing=cfg.gradient_checkpointing and not cuda, stochastic_rounding=cuda,
-        patch=1 if cfg.model.kind in ("sdxl", "ltx", "wan22") else 2,
+        patch=1 if cfg.model.kind in ("sdxl", "sd15", "ltx", "wan22") else 2,
         lr_if_contains=dict(cfg.network.lr_if_contains or {}) if cfg.train_mode == "lora" else {})
     fwd = default_forward
     if cfg.model.kind == "ltx":
         fwd = ltx_forward
-    elif cfg.model.kind == "sdxl":
+    elif cfg.model.kind in ("sdxl", "sd15"):
         from ..models.sdxl_unet import sdxl_forward
         fwd = sdxl_forward
     trainer = Trainer(model, tcfg, grad_sync=grad_sync, forward_fn=fwd)
