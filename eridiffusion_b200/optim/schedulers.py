@@ -204,6 +204,11 @@ class EMA:
             p.copy_(b)
         self._backup = None
 
+    def applied(self):
+        """``with ema.applied(): ...`` runs the body on the averaged weights and restores the live
+        ones afterwards, also when the body raises (crates/common/ema/src/ema.rs: ``EMAContext``)."""
+        return EMAContext(self)
+
     def state_dict(self, names=None, dtype=torch.float32):
         names = names or [str(i) for i in range(len(self.params))]
         return {f"ema.{n}": self.shadow_of(i).to(dtype).contiguous() for i, n in enumerate(names)}
@@ -213,3 +218,18 @@ class EMA:
         with torch.no_grad():
             for i, n in enumerate(names):
                 self.shadow_of(i).copy_(sd[f"ema.{n}"].float())
+
+
+class EMAContext:
+    """Swap-in / swap-out guard around evaluation or sampling with the averaged weights."""
+
+    def __init__(self, ema: EMA):
+        self.ema = ema
+
+    def __enter__(self):
+        self.ema.swap_in()
+        return self.ema
+
+    def __exit__(self, *exc):
+        self.ema.swap_out()
+        return False
