@@ -1,6 +1,6 @@
 """Per-kernel timing against the library equivalents and the measured roofline.
 
-    python -m eridiffusion_b200.cli.kernel_bench [--what gemm,skinny,attn,elementwise,optim] [--small]
+    python -m eridiffusion_b200.cli.kernel_bench [--what gemm,skinny,attn,elementwise,optim,dequant,narrow] [--small]
 
 Timing: CUDA events on the launching stream, >= 3 warm-up launches, L2 flushed between timed
 launches by writing a 256 MB buffer, median of the timed launches. Roofline denominators come from
@@ -153,6 +153,28 @@ def bench_dequant(small):
         print(f"dequant {kind} [{rows}x{cols}]: {t*1e6:.1f} us  {nb/t/1e9:.0f} GB/s  {nb/t/bw:.2f} {tag}")
 
 
+def bench_narrow(small):
+    """Slice gather and slice-gradient accumulation against the PyTorch statements
+    (``narrow().contiguous()``, ``narrow().add_()``). Bytes: slice read + slice written for the copy;
+    slice read twice + written once for the accumulation."""
+    from ..ops.narrow import narrow_backward_add, narrow_copy_raw
+    bw, fl, tag = peaks()
+    B, L, D = (4, 4608, 21504) if not small else (2, 1024, 4096)
+    x = torch.randn(B, L, D, device="cuda").bfloat16()
+    for dim, start, length in ((2, 3 * 3072, 4 * 3072), (1, 512, L - 512)):
+        nb = x.numel() // x.shape[dim] * length * 2
+        t = timeit(lambda: narrow_copy_raw(x, dim, start, length))
+        t_lib = timeit(lambda: x.narrow(dim, start, length).contiguous())
+        print(f"narrow copy [{B}x{L}x{D}] dim {dim} len {length}: {t*1e6:.1f} us {2*nb/t/1e9:.0f} GB/s "
+              f"{2*nb/t/bw:.2f} {tag}   torch {t_lib*1e6:.1f} us")
+        g = torch.randn_like(x.narrow(dim, start, length).contiguous())
+        gi = torch.zeros_like(x)
+        t = timeit(lambda: narrow_backward_add(g, gi, dim, start))
+        t_lib = timeit(lambda: gi.narrow(dim, start, length).add_(g))
+        print(f"narrow grad add same slice: {t*1e6:.1f} us {3*nb/t/1e9:.0f} GB/s {3*nb/t/bw:.2f} {tag}   "
+              f"torch {t_lib*1e6:.1f} us")
+
+
 def bench_attn(small):
     bw, fl, tag = peaks()
     for (B, L, H, D) in ([(1, 4608, 24, 128)] if not small else [(1, 1024, 8, 128)]):
@@ -185,7 +207,7 @@ def main():
     a = ap.parse_args()
     for w in a.what.split(","):
         {"gemm": bench_gemm, "skinny": bench_skinny, "elementwise": bench_elementwise, "optim": bench_optim,
-         "attn": bench_attn, "dequant": bench_dequant}[w](a.small)
+         "attn": bench_attn, "dequant": bench_dequant, "narrow": bench_narrow}[w](a.small)
 
 
 if __name__ == "__main__":
