@@ -129,23 +129,22 @@ int eri_narrow_copy(const void* src, void* dst, long long outer, long long dim_l
     const long long total_bytes = outer * len * inner * elem;
     if (total_bytes == 0) return 0;
     cudaStream_t st = (cudaStream_t)stream;
-    const long long inner_b = inner * elem;
-    if (inner_b % 16 == 0 && aligned16(src) && aligned16(dst)) {
-        const long long w = inner_b / 16, total = outer * len * w;
-        narrow_rows_kernel<uint4><<<grid_for(total, 256), 256, 0, st>>>(
-            (const uint4*)src, (uint4*)dst, outer, dim_len, w, start, len);
-    } else if (elem % 4 == 0) {
-        const long long w = inner_b / 4, total = outer * len * w;
-        narrow_rows_kernel<uint32_t><<<grid_for(total, 256), 256, 0, st>>>(
-            (const uint32_t*)src, (uint32_t*)dst, outer, dim_len, w, start, len);
-    } else if (elem % 2 == 0) {
-        const long long w = inner_b / 2, total = outer * len * w;
-        narrow_rows_kernel<uint16_t><<<grid_for(total, 256), 256, 0, st>>>(
-            (const uint16_t*)src, (uint16_t*)dst, outer, dim_len, w, start, len);
-    } else {
-        const long long total = outer * len * inner_b;
-        narrow_rows_kernel<uint8_t><<<grid_for(total, 256), 256, 0, st>>>(
-            (const uint8_t*)src, (uint8_t*)dst, outer, dim_len, inner_b, start, len);
+    // A row of the source is dim_len * inner * elem bytes, of which the bytes [off_b, off_b + run_b)
+    // are kept. The widest word that divides all three (and the base addresses) moves the data, so
+    // a slice of the LAST dimension (inner = 1) is vectorised like any other.
+    const long long row_b = dim_len * inner * elem, off_b = start * inner * elem, run_b = len * inner * elem;
+    int v = 16;
+    while (v > 1 && (row_b % v || off_b % v || run_b % v || (reinterpret_cast<uintptr_t>(src) % v) ||
+                     (reinterpret_cast<uintptr_t>(dst) % v)))
+        v >>= 1;
+    const long long total = outer * (run_b / v);
+    const int g = grid_for(total, 256);
+    switch (v) {
+        case 16: narrow_rows_kernel<uint4><<<g, 256, 0, st>>>((const uint4*)src, (uint4*)dst, outer, row_b / v, 1, off_b / v, run_b / v); break;
+        case 8: narrow_rows_kernel<uint2><<<g, 256, 0, st>>>((const uint2*)src, (uint2*)dst, outer, row_b / v, 1, off_b / v, run_b / v); break;
+        case 4: narrow_rows_kernel<uint32_t><<<g, 256, 0, st>>>((const uint32_t*)src, (uint32_t*)dst, outer, row_b / v, 1, off_b / v, run_b / v); break;
+        case 2: narrow_rows_kernel<uint16_t><<<g, 256, 0, st>>>((const uint16_t*)src, (uint16_t*)dst, outer, row_b / v, 1, off_b / v, run_b / v); break;
+        default: narrow_rows_kernel<uint8_t><<<g, 256, 0, st>>>((const uint8_t*)src, (uint8_t*)dst, outer, row_b, 1, off_b, run_b); break;
     }
     return (int)cudaGetLastError();
 }
@@ -159,7 +158,9 @@ int eri_narrow_backward_add(const void* grad_out, void* grad_in, long long outer
     if (total == 0) return 0;
     cudaStream_t st = (cudaStream_t)stream;
     const int per = dtype == 0 ? 4 : 8;
-    const bool vec = inner % per == 0 && aligned16(grad_out) && aligned16(grad_in);
+    // in elements: row length, offset and length of the kept run; 16-byte words when all three divide
+    const long long row_e = dim_len * inner, off_e = start * inner, run_e = len * inner;
+    const bool vec = row_e % per == 0 && off_e % per == 0 && run_e % per == 0 && aligned16(grad_out) && aligned16(grad_in);
     StridedView v{};
     v.rank = 3;
     v.shape[0] = outer; v.shape[1] = len; v.shape[2] = inner;
@@ -167,13 +168,13 @@ int eri_narrow_backward_add(const void* grad_out, void* grad_in, long long outer
     v.offset = start * inner;
     const int g = grid_for(vec ? total / per : total, 256);
     if (dtype == 0) {
-        if (vec) narrow_add_rows_kernel<float, 4><<<g, 256, 0, st>>>((const float*)grad_out, (float*)grad_in, outer, dim_len, inner, start, len);
+        if (vec) narrow_add_rows_kernel<float, 4><<<g, 256, 0, st>>>((const float*)grad_out, (float*)grad_in, outer, row_e / 4, 4, off_e / 4, run_e / 4);
         else narrow_add_strided_kernel<float><<<g, 256, 0, st>>>((const float*)grad_out, (float*)grad_in, v, total);
     } else if (dtype == 1) {
-        if (vec) narrow_add_rows_kernel<__nv_bfloat16, 8><<<g, 256, 0, st>>>((const __nv_bfloat16*)grad_out, (__nv_bfloat16*)grad_in, outer, dim_len, inner, start, len);
+        if (vec) narrow_add_rows_kernel<__nv_bfloat16, 8><<<g, 256, 0, st>>>((const __nv_bfloat16*)grad_out, (__nv_bfloat16*)grad_in, outer, row_e / 8, 8, off_e / 8, run_e / 8);
         else narrow_add_strided_kernel<__nv_bfloat16><<<g, 256, 0, st>>>((const __nv_bfloat16*)grad_out, (__nv_bfloat16*)grad_in, v, total);
     } else {
-        if (vec) narrow_add_rows_kernel<__half, 8><<<g, 256, 0, st>>>((const __half*)grad_out, (__half*)grad_in, outer, dim_len, inner, start, len);
+        if (vec) narrow_add_rows_kernel<__half, 8><<<g, 256, 0, st>>>((const __half*)grad_out, (__half*)grad_in, outer, row_e / 8, 8, off_e / 8, run_e / 8);
         else narrow_add_strided_kernel<__half><<<g, 256, 0, st>>>((const __half*)grad_out, (__half*)grad_in, v, total);
     }
     return (int)cudaGetLastError();
