@@ -340,8 +340,15 @@ def load_config(path_or_dict) -> TrainCfg:
         cfg = _from_ai_toolkit(doc)
     elif "model_kind" in doc:
         cfg = _from_flat(doc)
+    elif isinstance(doc.get("job"), dict) and isinstance(doc.get("model"), dict) and "architecture" in doc["model"]:
+        from .universal import UniversalConfig, UniversalConfigError
+        try:
+            return UniversalConfig.from_dict(doc).to_train_cfg()
+        except UniversalConfigError as e:
+            raise ConfigError(str(e)) from e
     else:
-        raise ConfigError("neither an ai-toolkit style document (config.process) nor a flat model_kind document")
+        raise ConfigError("not an ai-toolkit style document (config.process), a flat model_kind document or a "
+                          "universal job document (job + model.architecture)")
     apply_env(cfg)
     return cfg.validate()
 
