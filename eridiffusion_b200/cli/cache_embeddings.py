@@ -50,10 +50,8 @@ def load_image(path: Path, size: int) -> torch.Tensor:
 
 
 def _tokenize(tok_dir, text, max_len):
-    from transformers import AutoTokenizer
-    tok = AutoTokenizer.from_pretrained(tok_dir)
-    enc = tok(text, padding="max_length", truncation=True, max_length=max_len, return_tensors="pt")
-    return enc["input_ids"], enc["attention_mask"].bool()
+    from ..data.tokenizers import HfTokenizer
+    return HfTokenizer(tok_dir, max_len)(text)
 
 
 def main(argv=None):
