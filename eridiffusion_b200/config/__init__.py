@@ -124,6 +124,7 @@ class ParallelCfg:
     dp: int = 1
     zero_stage: int = 0                 # 0 (DDP) | 1/2 (sharded optimizer + grads) | 3 (sharded params)
     ulysses: int = 1
+    context: int = 1                    # ring-attention context parallelism degree (token slices per sample)
     fused_comm: str = "on"              # on | nccl
 
 

@@ -97,6 +97,12 @@ class LTXBlock(nn.Module):
         k = F.norm_modulate(k.contiguous(), weight=self.attn1_knorm, rms=True)
         q, k = _rope_full(q, cos, sin), _rope_full(k, cos, sin)
         sh = (B, L, self.heads, D // self.heads)
+        cp = getattr(self, "context_parallel", None)
+        if cp is not None:
+            # tokens are sharded over the group; keys / values travel around the ring
+            from ..parallel.ring_attention import ring_attention
+            return ring_attention(q.view(sh).contiguous(), k.view(sh).contiguous(), v.contiguous().view(sh),
+                                  group=cp.group).view(B, L, D)
         return F.attention(q.view(sh), k.view(sh), v.contiguous().view(sh)).view(B, L, D)
 
     def _self_attention_ulysses(self, h, cos, sin, u, eps=1e-6):
@@ -180,6 +186,18 @@ class LTXVideo(nn.Module):
     def set_sequence_parallel(self, u):
         self.ulysses = u
 
+    def set_context_parallel(self, group=None, enabled=True):
+        """Ring-attention context parallelism: every rank of ``group`` (default: all ranks) feeds
+        its contiguous token slice; only the self-attention communicates (key / value slices around
+        the ring), every other layer is per token. Unlike Ulysses the degree is not bounded by the
+        head count. Mutually exclusive with ``set_sequence_parallel``."""
+        from types import SimpleNamespace
+        import torch.distributed as dist
+        cp = SimpleNamespace(group=group, world=dist.get_world_size(group), rank=dist.get_rank(group)) if enabled else None
+        self.context = cp
+        for blk in self.blocks:
+            blk.context_parallel = cp
+
     def rope(self, frames, h, w, device):
         key = (frames, h, w, str(device))
         if key not in self._rope:
@@ -194,7 +212,15 @@ class LTXVideo(nn.Module):
         dt = self.patchify_proj.weight.dtype
         u = self.ulysses
         cos, sin = self.rope(*grid_fhw, x.device)
-        if u is None and cos.shape[0] != x.shape[1]:
+        cp = getattr(self, "context", None)
+        if cp is not None:
+            if u is not None:
+                raise ValueError("context parallelism and Ulysses sequence parallelism are mutually exclusive")
+            Ll = x.shape[1]
+            if Ll * cp.world != cos.shape[0]:
+                raise ValueError("local token count times the group size does not match the grid")
+            cos, sin = cos[cp.rank * Ll:(cp.rank + 1) * Ll], sin[cp.rank * Ll:(cp.rank + 1) * Ll]
+        elif u is None and cos.shape[0] != x.shape[1]:
             raise ValueError("token count does not match the grid")
         temb = self.time_embed(timestep_embedding(t, cfg.time_embed_dim).to(dt))       # [B, D]
         temb6 = self.adaln_single(temb, silu_in=True).view(-1, 6, cfg.hidden)

@@ -113,7 +113,7 @@ class _RingAttention(torch.autograd.Function):
             if reqs is not None:
                 _wait(reqs)
                 kv = land
-        out_t = out.to(q.dtype)
+        out_t = out.to(q.dtype).contiguous()
         ctx.save_for_backward(q, k, v, out_t, lse)
         ctx.scale, ctx.group = scale, group
         return out_t

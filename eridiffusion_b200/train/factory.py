@@ -43,7 +43,20 @@ def build_job(cfg: TrainCfg, device=None):
     par = cfg.parallel
     grad_sync = None
     seq_par = par.ulysses if world > 1 else 1
-    if seq_par > 1:
+    ctx_par = par.context if world > 1 else 1
+    if ctx_par > 1:
+        # ring attention: every rank holds a token slice of the same sample; only self-attention
+        # communicates, so the degree is not tied to the head count
+        if seq_par > 1:
+            raise ValueError("parallel.context and parallel.ulysses are mutually exclusive")
+        if ctx_par != world:
+            raise ValueError(f"parallel.context ({ctx_par}) must equal the number of ranks ({world})")
+        if not hasattr(model, "set_context_parallel"):
+            raise ValueError(f"model kind '{cfg.model.kind}' has no context-parallel attention path")
+        model.set_context_parallel()
+        grad_sync = GradSync("allreduce")
+        seq_par = ctx_par                    # same batch / timestep handling as a sequence-parallel group
+    elif seq_par > 1:
         # one sequence-parallel group spanning the job: every rank holds a token slice of the same
         # sample, the two all-to-alls run inside the QKV / output projections
         if seq_par != world:
@@ -113,9 +126,22 @@ def build_job(cfg: TrainCfg, device=None):
                                       width=res)
                 i += 1
         batches = gen()
-    if seq_par > 1:
+    if ctx_par > 1:
+        batches = _token_slices(batches, rank, world)
+    elif seq_par > 1:
         batches = _sequence_parallel_batches(batches, model, rank, world)
     return trainer, batches, {"rank": rank, "world": world, "device": str(dev), "model": model_id}
+
+
+def _token_slices(batches, rank, world):
+    """Every rank keeps its contiguous token slice of the token-major latents ``[B, C, L, 1]``."""
+    for b in batches:
+        lat = b["latents"]
+        L = lat.shape[2]
+        if L % world:
+            raise ValueError(f"token count {L} must divide by the context-parallel size {world}")
+        Ll = L // world
+        yield {**b, "latents": lat[:, :, rank * Ll:(rank + 1) * Ll].contiguous()}
 
 
 def _sequence_parallel_batches(batches, model, rank, world):

@@ -75,3 +75,59 @@ def test_merge_is_associative_and_matches_softmax():
         assert torch.allclose(dk_s, kk.grad[:, a:a + 4], atol=1e-5)
         assert torch.allclose(dv_s, vv.grad[:, a:a + 4], atol=1e-5)
     assert torch.allclose(dq, qq.grad, atol=1e-5)
+
+
+def _ltx(seed=0):
+    from eridiffusion_b200.models import build_model
+    torch.manual_seed(seed)
+    m = build_model("ltx_video", dtype=torch.float32, hidden=48, num_heads=2, depth=2, in_channels=8,
+                    context_dim=24, caption_dim=12)
+    for p in m.parameters():
+        torch.nn.init.normal_(p, std=0.08)
+    return m
+
+
+def _ltx_inputs():
+    g = torch.Generator().manual_seed(4)
+    return (torch.randn(1, 24, 8, generator=g), torch.randn(1, 5, 12, generator=g), torch.tensor([0.4]),
+            torch.randn(1, 24, 8, generator=g))
+
+
+def _ltx_worker(rank, world, port, q_out):
+    os.environ.update(WORLD_SIZE=str(world), RANK=str(rank), MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    import datetime
+    import torch.distributed as dist
+    from eridiffusion_b200.parallel.ring_attention import shard_sequence
+    torch.set_num_threads(1)
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=120))
+    m = _ltx()
+    m.set_context_parallel()
+    x, ctx, t, go = _ltx_inputs()
+    out = m(shard_sequence(x), ctx, t, (2, 3, 4))
+    out.backward(shard_sequence(go))
+    grads = torch.cat([p.grad.flatten() for p in m.parameters()])
+    dist.all_reduce(grads)                                  # per-token work is split: gradients add up
+    q_out.put((rank, out.detach(), grads if rank == 0 else None))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_ltx_context_parallel_matches_single_process():
+    world = 2
+    ctx_mp = mp.get_context("spawn")
+    qu = ctx_mp.Queue()
+    port = _free_port()
+    procs = [ctx_mp.Process(target=_ltx_worker, args=(r, world, port, qu)) for r in range(world)]
+    for p in procs:
+        p.start()
+    got = sorted((qu.get(timeout=180) for _ in range(world)), key=lambda t: t[0])
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    m = _ltx()
+    x, ctx, t, go = _ltx_inputs()
+    ref = m(x, ctx, t, (2, 3, 4))
+    ref.backward(go)
+    assert torch.allclose(torch.cat([g[1] for g in got], dim=1), ref.detach(), atol=1e-5)
+    ref_g = torch.cat([p.grad.flatten() for p in m.parameters()])
+    assert torch.allclose(got[0][2], ref_g, atol=1e-4, rtol=1e-3), (got[0][2] - ref_g).abs().max()
