@@ -21,8 +21,9 @@ share of ``dQ`` and the complete ``dK`` / ``dV`` of that slice. Otherwise the sa
 in fp32 PyTorch (CPU ranks under gloo, odd shapes).
 
 The transfer of step ``s + 1``'s slice is posted (``batch_isend_irecv``) before step ``s``'s
-product is launched, so on NCCL it overlaps the kernels. In the backward the slice's gradient
-accumulator travels with it and is home again after ``P`` hops. Non-causal attention has equal work
+product is launched, so on NCCL it overlaps the kernels. In the backward the keys / values are
+forwarded the same way (in their own dtype) and the slice's fp32 gradient accumulator follows after
+the step's products; it is home again after ``P`` hops. Non-causal attention has equal work
 per slice, so no zig-zag reordering is needed.
 """
 from __future__ import annotations
@@ -126,19 +127,26 @@ class _RingAttention(torch.autograd.Function):
         rank = dist.get_rank(group)
         do = do.contiguous()
         dq = torch.zeros_like(q, dtype=torch.float32)
-        # [k, v, dk, dv] of the slice currently held; fp32 so that P partial sums add exactly once
-        pack = torch.stack((k.float(), v.float(), torch.zeros_like(k, dtype=torch.float32),
-                            torch.zeros_like(v, dtype=torch.float32)))
+        # keys / values travel in their own dtype and are forwarded BEFORE this step's products (the
+        # next rank needs them one step later), so that transfer overlaps the kernels; the fp32
+        # gradient accumulator of the slice follows after the products and is home after P hops
+        kv = torch.stack((k, v))
+        dkv = torch.zeros_like(kv, dtype=torch.float32)
         for s in range(world):
-            ks, vs = pack[0].to(q.dtype), pack[1].to(q.dtype)
-            dq_s, dk_s, dv_s = block_backward(do, q, ks, vs, out, lse, scale)
+            kv_reqs = kv_land = None
+            if s + 1 < world:
+                kv_reqs, kv_land = _rotate(kv, group, rank, world)
+            dq_s, dk_s, dv_s = block_backward(do, q, kv[0], kv[1], out, lse, scale)
             dq += dq_s
-            pack[2] += dk_s
-            pack[3] += dv_s
-            reqs, land = _rotate(pack, group, rank, world)             # after P hops the slice is home
+            dkv[0] += dk_s
+            dkv[1] += dv_s
+            reqs, land = _rotate(dkv, group, rank, world)
             _wait(reqs)
-            pack = land
-        return dq.to(q.dtype), pack[2].to(k.dtype), pack[3].to(v.dtype), None, None
+            dkv = land
+            if kv_reqs is not None:
+                _wait(kv_reqs)
+                kv = kv_land
+        return dq.to(q.dtype), dkv[0].to(k.dtype), dkv[1].to(v.dtype), None, None
 
 
 def ring_attention(q, k, v, scale=None, group=None):
