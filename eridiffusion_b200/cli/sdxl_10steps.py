@@ -8,6 +8,10 @@ in milliseconds and the ``avg step time`` line the reference prints.
 ``MODE=lora|full`` (default lora), ``LORA_RANK``, ``LR``. ``SDXL_MMAP_PATH`` points at a UNet
 safetensors file to load; without it the weights are random. ``BLOCK_INDEX`` restricts the trainable
 adapters to one transformer block (the reference trains a single block per run).
+``SDXL_TIMING=1`` prints the device-timed phase breakdown at the end, ``SDXL_LOAD_TRACE=1`` the GiB/s
+of the weight load, ``BACKWARD_DEBUG=1`` runs the first step under autograd anomaly detection and
+prints per-parameter gradient statistics; ``ATTN_Q_CHUNK ATTN_KV_CHUNK ATTN_REUSE ATTN_MAX_WS_MB
+ATTN_MIN_FREE_MB`` act on the library attention path (``utils/env_flags.py``).
 """
 from __future__ import annotations
 
@@ -47,12 +51,18 @@ def main():
     path = os.environ.get("SDXL_MMAP_PATH")
     if path:
         from ..io.weights import load_model_weights
-        load_model_weights(model, path, "sdxl")
+        from ..utils.env_flags import load_trace
+        with load_trace("sdxl unet", lambda: os.path.getsize(path) if os.path.isfile(path) else sum(
+                os.path.getsize(os.path.join(path, f)) for f in os.listdir(path))):
+            load_model_weights(model, path, "sdxl")
     mode = os.environ.get("MODE", "lora")
     acfg = AdapterConfig(rank=_env("LORA_RANK", 16), alpha=float(_env("LORA_RANK", 16)), dtype=dt) if mode == "lora" else None
     cfg = TrainerConfig(mode=mode, adapter=acfg, objective="eps", lr=_env("LR", 1e-4, float), seed=seed, patch=1,
                         stochastic_rounding=dev.type == "cuda")
     tr = Trainer(model, cfg, forward_fn=sdxl_forward)
+    from ..utils.env_flags import backward_debug, flag
+    if flag("SDXL_TIMING"):
+        tr.phases.enabled = True
     blk = os.environ.get("BLOCK_INDEX")
     if blk is not None and mode == "lora":
         keep = f"blocks.{int(blk)}."
@@ -68,7 +78,11 @@ def main():
         if dev.type == "cuda":
             torch.cuda.synchronize()
         t0 = time.perf_counter()
-        loss = tr.train_step(b)
+        if i == 0:
+            with backward_debug([(n, p) for n, p in model.named_parameters() if p.requires_grad]):
+                loss = tr.train_step(b)
+        else:
+            loss = tr.train_step(b)
         if dev.type == "cuda":
             torch.cuda.synchronize()
         ms = (time.perf_counter() - t0) * 1e3
@@ -76,6 +90,9 @@ def main():
         print(f"step {i + 1}/{steps} loss {float(loss):.5f} {ms:.1f} ms")
     warm = times[1:] or times
     print(f"avg step time: {sum(warm) / len(warm):.1f} ms ({len(warm)} steps after warm-up)")
+    if flag("SDXL_TIMING"):
+        for name, v in tr.phases.summary().items():
+            print(f"  phase {name:<10s} {v['ms'] / max(1, v['calls']):9.3f} ms/call  {100 * v['share']:5.1f} %")
     return 0
 
 

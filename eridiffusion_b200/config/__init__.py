@@ -375,6 +375,11 @@ ENV_VARS = {
     "ERI_B200_PHASE_TIMING": "1: device-timed noise / forward / backward / optimizer phases in the trainer",
     "ERI_B200_NATIVE_PREFETCH": "1 | 0: native read-ahead threads in the cached-embedding loader",
     "ERI_B200_PLUGINS": "colon-separated plug-in modules loaded at start-up",
+    "ATTN_Q_CHUNK / ATTN_KV_CHUNK / ATTN_REUSE / ATTN_MAX_WS_MB / ATTN_MIN_FREE_MB":
+        "block sizes, shared workspace and caps of the library (blockwise) attention path",
+    "SDXL_TIMING / SDXL_LOAD_TRACE / BACKWARD_DEBUG": "1: phase breakdown, load GiB/s, anomaly mode + gradient report",
+    "ERID_PINNED_CHECKPOINT_CACHE_MB": "pinned staging cache for checkpoint writes, MiB",
+    "AI_TOOLKIT_<SECTION>__<KEY>": "override of a universal-schema document (config/universal.py)",
     "TRAIN_LOG_CSV": "per-step CSV path (step,loss,grad_norm,sec_per_it,alloc_mb,ckpt_path)",
     "CKPT_EVERY": "checkpoint interval override",
     "EXPECT_STEP_SEC": "fail the run when a step is slower than this many seconds",

@@ -757,6 +757,10 @@ def small_linear(x, w, bias=None, silu_in=False):
 
 
 # ---------------------------------------------------------------------------- attention
+# read once at import: the ATTN_* switches of the library attention path (utils/env_flags.py)
+_ATTN_ENV_POLICY = any(os.environ.get(k) for k in ("ATTN_Q_CHUNK", "ATTN_KV_CHUNK", "ATTN_MAX_WS_MB", "ATTN_MIN_FREE_MB"))
+
+
 def attention(q, k, v, scale=None, mask=None, out=None):
     """Non-causal attention over token-major [B, L, H, Dh] tensors. ``out``: optional destination
     buffer for the native kernel (ignored by the library path, which returns its own tensor)."""
@@ -764,6 +768,11 @@ def attention(q, k, v, scale=None, mask=None, out=None):
         from . import flash_attn as FA
         if FA.supported(q, k, v):
             return FA.flash_attention(q, k, v, scale, out)
+    if mask is None and _ATTN_ENV_POLICY:
+        from ..utils.env_flags import library_attention
+        o = library_attention(q, k, v, scale)
+        if o is not None:
+            return o
     return R.attention(q, k, v, scale, mask)
 
 
