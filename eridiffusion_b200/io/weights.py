@@ -21,9 +21,31 @@ _FLUX_RENAMES = [
 ]
 
 
+# SD3 / SD3.5 original layout (``joint_blocks.N.{x_block, context_block}.{attn, attn2, mlp,
+# adaLN_modulation}``; crates/models/src/sd35/keymap.rs:3-348, src/loaders/mmdit_weights.rs) -> the
+# two-stream block's names. The adaLN chunk order (shift, scale, gate of attention; shift, scale, gate of
+# the MLP; then the second attention's three) is the same on both sides, so tensors copy as they are.
+_SD35_RENAMES = [
+    (r"^model\.diffusion_model\.", ""),
+    (r"\.x_block\.adaLN_modulation\.1\.", ".img_mod.lin."), (r"\.context_block\.adaLN_modulation\.1\.", ".txt_mod.lin."),
+    (r"\.x_block\.attn2\.", ".img_attn2."), (r"\.x_block\.attn\.", ".img_attn."), (r"\.context_block\.attn\.", ".txt_attn."),
+    (r"\.ln_q\.weight$", ".q_norm.scale"), (r"\.ln_k\.weight$", ".k_norm.scale"),
+    (r"\.x_block\.mlp\.fc1\.", ".img_mlp_0."), (r"\.x_block\.mlp\.fc2\.", ".img_mlp_2."),
+    (r"\.context_block\.mlp\.fc1\.", ".txt_mlp_0."), (r"\.context_block\.mlp\.fc2\.", ".txt_mlp_2."),
+    (r"^x_embedder\.proj\.", "x_embedder."),
+    (r"^(t_embedder|y_embedder)\.mlp\.0\.", r"\1.in_layer."), (r"^(t_embedder|y_embedder)\.mlp\.2\.", r"\1.out_layer."),
+    (r"^final_layer\.adaLN_modulation\.1\.", "final_layer.adaLN.lin."),
+]
+# tensors of a checkpoint that the model computes instead of storing
+_COMPUTED_KEYS = {"sd35": {"pos_embed"}, "sd3": {"pos_embed"}}
+
+
 def canonical_key(key: str, kind: str) -> str:
     if kind in ("flux", "chroma"):
         for pat, rep in _FLUX_RENAMES:
+            key = re.sub(pat, rep, key)
+    elif kind in ("sd3", "sd35"):
+        for pat, rep in _SD35_RENAMES:
             key = re.sub(pat, rep, key)
     return key
 
@@ -67,10 +89,14 @@ def load_model_weights(model, path, kind="flux", strict=True, device=None):
             st.assert_not_text_encoder(sf.keys())
             for k in sf.keys():
                 ck = canonical_key(k, kind)
+                if ck in _COMPUTED_KEYS.get(kind, ()):
+                    continue
                 seen.add(ck)
                 if ck in own:
                     p = own[ck]
                     t = sf.get(k, device=device or p.device, dtype=p.dtype)
+                    if t.dim() == 4 and p.dim() == 2 and t.shape[0] == p.shape[0] and t.numel() == p.numel():
+                        t = t.reshape(p.shape)      # patch-embedding convolution [D, C, p, p] -> linear [D, C*p*p]
                     if tuple(t.shape) != tuple(p.shape):
                         raise ValueError(f"{k}: shape {tuple(t.shape)} != parameter {tuple(p.shape)}")
                     with torch.no_grad():

@@ -146,6 +146,9 @@ class SD35MMDiT(nn.Module):
 
 @register_model("sd35")
 def build_sd35(dtype=torch.bfloat16, device=None, **kw):
+    """SD3.5-large layout; as in the released weights the last block's text stream stops after its
+    attention (adaLN width 2 x hidden there: crates/models/src/sd35/keymap.rs ``ADA_DIM_LAST_CONTEXT``)."""
+    kw.setdefault("context_pre_only_last", True)
     return SD35MMDiT(dtype=dtype, device=device, **kw)
 
 

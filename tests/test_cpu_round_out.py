@@ -244,3 +244,46 @@ def test_rope_1d_table_aligns_instants():
     c2, s2 = rope_1d_table(torch.tensor([1.0]), 16)
     assert c1.shape == (3, 8) and torch.allclose(c1[1], c2[0]) and torch.allclose(s1[1], s2[0])
     assert torch.allclose(c1 ** 2 + s1 ** 2, torch.ones_like(c1), atol=1e-6)
+
+
+# ----------------------------------------------------------------------------- SD3.5 checkpoint keys
+def test_sd35_original_layout_loads(tmp_path):
+    from eridiffusion_b200.io import safetensors as st
+    from eridiffusion_b200.io.weights import canonical_key, load_model_weights
+    from eridiffusion_b200.models import build_model
+    kw = dict(hidden=64, num_heads=2, depth=2, in_channels=64, context_dim=16, pooled_dim=12, dtype=torch.float32,
+              x_self_attn_layers=(0,))
+    torch.manual_seed(0)
+    src = build_model("sd35", **kw)
+    for p in src.parameters():
+        torch.nn.init.normal_(p, std=0.1)
+    assert src.joint_blocks[1].context_pre_only            # released layout: last block's text stream is pre-only
+    back = {"img_mod.lin": "x_block.adaLN_modulation.1", "txt_mod.lin": "context_block.adaLN_modulation.1",
+            "img_attn2.": "x_block.attn2.", "img_attn.": "x_block.attn.", "txt_attn.": "context_block.attn.",
+            "img_mlp_0": "x_block.mlp.fc1", "img_mlp_2": "x_block.mlp.fc2", "txt_mlp_0": "context_block.mlp.fc1",
+            "txt_mlp_2": "context_block.mlp.fc2", "q_norm.scale": "ln_q.weight", "k_norm.scale": "ln_k.weight",
+            "in_layer": "mlp.0", "out_layer": "mlp.2", "final_layer.adaLN.lin": "final_layer.adaLN_modulation.1"}
+    sd = {}
+    for n, p in src.named_parameters():
+        k = n
+        for a, b in back.items():
+            k = k.replace(a, b)
+        if k.startswith("x_embedder."):
+            k = k.replace("x_embedder.", "x_embedder.proj.")
+        t = p.detach().clone()
+        if k == "x_embedder.proj.weight":
+            t = t.view(64, 16, 2, 2)
+        sd["model.diffusion_model." + k] = t
+    sd["model.diffusion_model.pos_embed"] = torch.zeros(1, 36864 // 64, 64)
+    key = canonical_key("model.diffusion_model.joint_blocks.3.x_block.attn.ln_q.weight", "sd35")
+    assert key == "joint_blocks.3.img_attn.q_norm.scale"
+    f = tmp_path / "sd35.safetensors"
+    st.save_file(sd, f)
+    dst = build_model("sd35", **kw)
+    used = load_model_weights(dst, f, "sd35", strict=True)
+    assert len(used) == len(list(dst.named_parameters()))
+    for (n, a), (_, b) in zip(src.named_parameters(), dst.named_parameters()):
+        assert torch.equal(a, b), n
+    img, txt = torch.randn(1, 16, 64), torch.randn(1, 5, 16)
+    t, y = torch.rand(1), torch.randn(1, 12)
+    assert torch.equal(src(img, txt, t, y, grid_hw=(4, 4)), dst(img, txt, t, y, grid_hw=(4, 4)))
