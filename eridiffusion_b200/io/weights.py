@@ -36,6 +36,21 @@ _SD35_RENAMES = [
     (r"^(t_embedder|y_embedder)\.mlp\.0\.", r"\1.in_layer."), (r"^(t_embedder|y_embedder)\.mlp\.2\.", r"\1.out_layer."),
     (r"^final_layer\.adaLN_modulation\.1\.", "final_layer.adaLN.lin."),
 ]
+# Flux-2 Klein checkpoints (src/models/klein_model.rs:348-529, 600-640): per-stream names under
+# ``{img,txt}_attn`` / ``{img,txt}_mlp``, model-level modulation linears, no bias tensors anywhere.
+_KLEIN_RENAMES = [
+    (r"^model\.diffusion_model\.", ""),
+    (r"\.(img|txt)_attn\.norm\.query_norm\.scale$", r".\1.q_norm.scale"),
+    (r"\.(img|txt)_attn\.norm\.key_norm\.scale$", r".\1.k_norm.scale"),
+    (r"\.(img|txt)_attn\.(qkv|proj)\.", r".\1.\2."),
+    (r"\.(img|txt)_mlp\.0\.", r".\1.mlp_in."), (r"\.(img|txt)_mlp\.2\.", r".\1.mlp_out."),
+    (r"^(single_blocks\.\d+)\.norm\.query_norm\.scale$", r"\1.q_norm.scale"),
+    (r"^(single_blocks\.\d+)\.norm\.key_norm\.scale$", r"\1.k_norm.scale"),
+    (r"^double_stream_modulation_(img|txt)\.", r"double_mod_\1."), (r"^single_stream_modulation\.", "single_mod."),
+    (r"^final_layer\.adaLN_modulation\.1\.", "final_layer.adaLN.lin."),
+]
+# parameters a family's checkpoints never carry: zero-filled instead of reported missing
+_ZERO_IF_MISSING = {"klein": re.compile(r"\.bias$")}
 # tensors of a checkpoint that the model computes instead of storing
 _COMPUTED_KEYS = {"sd35": {"pos_embed"}, "sd3": {"pos_embed"}}
 
@@ -46,6 +61,9 @@ def canonical_key(key: str, kind: str) -> str:
             key = re.sub(pat, rep, key)
     elif kind in ("sd3", "sd35"):
         for pat, rep in _SD35_RENAMES:
+            key = re.sub(pat, rep, key)
+    elif kind == "klein":
+        for pat, rep in _KLEIN_RENAMES:
             key = re.sub(pat, rep, key)
     return key
 
@@ -102,6 +120,13 @@ def load_model_weights(model, path, kind="flux", strict=True, device=None):
                     with torch.no_grad():
                         p.copy_(t)
                     used.add(ck)
+    zero = _ZERO_IF_MISSING.get(kind)
+    if zero is not None:
+        with torch.no_grad():
+            for k in set(own) - used:
+                if zero.search(k):
+                    own[k].zero_()
+                    used.add(k)
     if strict:
         missing, unused = set(own) - used, seen - used
         if missing or unused:

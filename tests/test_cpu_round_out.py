@@ -287,3 +287,43 @@ def test_sd35_original_layout_loads(tmp_path):
     img, txt = torch.randn(1, 16, 64), torch.randn(1, 5, 16)
     t, y = torch.rand(1), torch.randn(1, 12)
     assert torch.equal(src(img, txt, t, y, grid_hw=(4, 4)), dst(img, txt, t, y, grid_hw=(4, 4)))
+
+
+def test_klein_checkpoint_layout_loads(tmp_path):
+    from eridiffusion_b200.io import safetensors as st
+    from eridiffusion_b200.io.weights import load_model_weights
+    from eridiffusion_b200.models import build_model
+    kw = dict(dtype=torch.float32, in_channels=8, dim=64, num_heads=2, depth_double=1, depth_single=2, context_dim=16,
+              axes_dim=(8, 8, 8, 8))
+    torch.manual_seed(0)
+    src = build_model("klein", **kw)
+    for n, p in src.named_parameters():
+        torch.nn.init.zeros_(p) if n.endswith(".bias") else torch.nn.init.normal_(p, std=0.1)
+    back = [(".img.q_norm.scale", ".img_attn.norm.query_norm.scale"), (".img.k_norm.scale", ".img_attn.norm.key_norm.scale"),
+            (".txt.q_norm.scale", ".txt_attn.norm.query_norm.scale"), (".txt.k_norm.scale", ".txt_attn.norm.key_norm.scale"),
+            (".img.qkv.", ".img_attn.qkv."), (".img.proj.", ".img_attn.proj."), (".txt.qkv.", ".txt_attn.qkv."),
+            (".txt.proj.", ".txt_attn.proj."), (".img.mlp_in.", ".img_mlp.0."), (".img.mlp_out.", ".img_mlp.2."),
+            (".txt.mlp_in.", ".txt_mlp.0."), (".txt.mlp_out.", ".txt_mlp.2."),
+            ("double_mod_img.", "double_stream_modulation_img."), ("double_mod_txt.", "double_stream_modulation_txt."),
+            ("single_mod.", "single_stream_modulation."), ("final_layer.adaLN.lin.", "final_layer.adaLN_modulation.1.")]
+    sd = {}
+    for n, p in src.named_parameters():
+        if n.endswith(".bias"):
+            continue                                           # the released files have no bias tensors
+        k = n
+        for a, b in back:
+            k = k.replace(a, b)
+        if k.startswith("single_blocks.") and k.endswith(("q_norm.scale", "k_norm.scale")):
+            k = k.replace("q_norm.scale", "norm.query_norm.scale").replace("k_norm.scale", "norm.key_norm.scale")
+        sd[k] = p.detach().clone()
+    assert "double_blocks.0.img_attn.norm.query_norm.scale" in sd and "single_blocks.1.norm.key_norm.scale" in sd
+    f = tmp_path / "klein.safetensors"
+    st.save_file(sd, f)
+    dst = build_model("klein", **kw)
+    load_model_weights(dst, f, "klein", strict=True)
+    for (n, a), (_, b) in zip(src.named_parameters(), dst.named_parameters()):
+        assert torch.equal(a, b), n
+    sd["extra.weight"] = torch.zeros(1)
+    st.save_file(sd, f)
+    with pytest.raises(KeyError, match="unused"):
+        load_model_weights(build_model("klein", **kw), f, "klein", strict=True)
