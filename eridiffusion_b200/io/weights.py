@@ -102,6 +102,25 @@ def load_model_weights(model, path, kind="flux", strict=True, device=None):
                 raise KeyError(f"strict weight load: missing={sorted(set(own) - used)[:5]} "
                                f"unused={sorted(set(sd) - used)[:5]}")
             return used
+    if kind in ("ltx", "ltx_video"):
+        # diffusers layout with separate q / k / v projections: fused while loading
+        from .ltx_keys import remap_ltx_state_dict
+        raw = {}
+        for f in files:
+            with st.SafeFile(f) as sf:
+                raw.update({k: sf.get(k, device=device or "cpu") for k in sf.keys()})
+        sd = remap_ltx_state_dict(raw, strict=strict)
+        with torch.no_grad():
+            for k, t in sd.items():
+                if k in own:
+                    if tuple(t.shape) != tuple(own[k].shape):
+                        raise ValueError(f"{k}: shape {tuple(t.shape)} != parameter {tuple(own[k].shape)}")
+                    own[k].copy_(t.to(own[k].dtype))
+                    used.add(k)
+        if strict and (set(own) - used or set(sd) - used):
+            raise KeyError(f"strict weight load: missing={sorted(set(own) - used)[:5]} "
+                           f"unused={sorted(set(sd) - used)[:5]}")
+        return used
     for f in files:
         with st.SafeFile(f) as sf:
             st.assert_not_text_encoder(sf.keys())

@@ -327,3 +327,35 @@ def test_klein_checkpoint_layout_loads(tmp_path):
     st.save_file(sd, f)
     with pytest.raises(KeyError, match="unused"):
         load_model_weights(build_model("klein", **kw), f, "klein", strict=True)
+
+
+def test_ltx_diffusers_layout_round_trip(tmp_path):
+    from eridiffusion_b200.io import safetensors as st
+    from eridiffusion_b200.io.ltx_keys import export_ltx_state_dict, remap_ltx_state_dict
+    from eridiffusion_b200.io.weights import load_model_weights
+    from eridiffusion_b200.models import build_model
+    kw = dict(dtype=torch.float32, hidden=48, num_heads=2, depth=2, in_channels=8, context_dim=24, caption_dim=12)
+    torch.manual_seed(0)
+    src = build_model("ltx_video", **kw)
+    for p in src.parameters():
+        torch.nn.init.normal_(p, std=0.1)
+    ext = export_ltx_state_dict({n: p.detach().clone() for n, p in src.named_parameters()})
+    assert "transformer_blocks.1.attn1.to_k.weight" in ext and ext["transformer_blocks.1.attn1.to_k.weight"].shape == (48, 48)
+    assert "transformer_blocks.0.attn2.to_v.bias" in ext and "transformer_blocks.0.ff.net.0.proj.weight" in ext
+    assert "time_embed.linear.weight" in ext and "caption_projection.linear_2.bias" in ext and "proj_in.weight" in ext
+    assert not any(k.startswith("blocks.") for k in ext)
+    # tensors a released file has and this model does not store
+    ext["transformer_blocks.0.norm1.weight"] = torch.ones(48)
+    ext["audio_proj_in.weight"] = torch.zeros(4, 4)
+    ext["transformer_blocks.0.audio_attn1.to_q.weight"] = torch.zeros(4, 4)
+    back = remap_ltx_state_dict(ext)
+    assert set(back) == {n for n, _ in src.named_parameters()}
+    f = tmp_path / "ltx.safetensors"
+    st.save_file({"transformer." + k: v for k, v in ext.items()}, f)
+    dst = build_model("ltx_video", **kw)
+    load_model_weights(dst, f, "ltx", strict=True)
+    for (n, a), (_, b) in zip(src.named_parameters(), dst.named_parameters()):
+        assert torch.equal(a, b), n
+    del ext["transformer_blocks.1.attn1.to_v.weight"]
+    with pytest.raises(KeyError, match="expected"):
+        remap_ltx_state_dict(ext)
