@@ -1,6 +1,6 @@
 """Per-kernel timing against the library equivalents and the measured roofline.
 
-    python -m eridiffusion_b200.cli.kernel_bench [--what gemm,skinny,attn,elementwise,optim,dequant,narrow] [--small]
+    python -m eridiffusion_b200.cli.kernel_bench [--what gemm,skinny,attn,elementwise,optim,dequant,narrow,wgrad] [--small]
 
 Timing: CUDA events on the launching stream, >= 3 warm-up launches, L2 flushed between timed
 launches by writing a 256 MB buffer, median of the timed launches. Roofline denominators come from
@@ -90,6 +90,41 @@ def bench_skinny(small):
         nb = a.numel() * 2
         print(f"skinny [{M}x{K}]x[16x{K}]^T: split-K {t*1e6:.1f} us {nb/t/1e9:.0f} GB/s {nb/t/bw:.2f} {tag} | "
               f"128-row tiles only {t0*1e6:.1f} us | cuBLAS {t1*1e6:.1f} us")
+
+
+def bench_wgrad(small):
+    """Weight-gradient products: dW = dY^T X on the two-CTA kernel (both operands token-major) and the
+    skinny token reductions of the LoRA gradients, against torch (cuBLAS)."""
+    bw, fl, tag = peaks()
+    T = 4608 if not small else 1024
+    for Nn, K in ([(9216, 3072), (3072, 3072), (12288, 3072), (3072, 12288)] if not small else [(1024, 512)]):
+        dy = torch.randn(T, Nn, device="cuda").bfloat16()
+        x = torch.randn(T, K, device="cuda").bfloat16()
+        g = torch.zeros(Nn, K, device="cuda", dtype=torch.bfloat16)
+        t = timeit(lambda: F.wgrad(dy, x, accum=g))
+        t_lib = timeit(lambda: g.addmm_(dy.t(), x))
+        fl_ = 2.0 * T * Nn * K
+        print(f"wgrad dW[{Nn}x{K}] += dY[{T}x{Nn}]^T X: ours {t*1e6:.1f} us {fl_/t/1e12:.0f} TF/s {fl_/t/fl:.2f} {tag} | "
+              f"cuBLAS addmm {t_lib*1e6:.1f} us {fl_/t_lib/1e12:.0f} TF/s")
+    lib = F.N.require()
+    for Mg in ([3072, 9216, 12288, 15360, 21504] if not small else [2048]):
+        a = torch.randn(T, Mg, device="cuda").bfloat16()
+        b = torch.randn(T, 16, device="cuda").bfloat16()
+        g = torch.zeros(Mg, 16, device="cuda", dtype=torch.bfloat16)
+        gt = torch.zeros(16, Mg, device="cuda", dtype=torch.bfloat16)
+        nb = a.numel() * 2
+        row = []
+        for target in (0, 148, 296, 1184):
+            lib.eri_gemm_tokred_set_target(target)
+            t = timeit(lambda: F.lora_wgrad(a, b, out=g, accumulate=True))
+            t2 = timeit(lambda: F.lora_wgrad(a, b, out=gt, transpose_out=True, accumulate=True))
+            row.append(f"target {target}: {t*1e6:.1f} / {t2*1e6:.1f} us ({nb/t/bw:.2f})")
+        lib.eri_gemm_tokred_set_target(0)
+        t_lib = timeit(lambda: g.addmm_(a.t(), b))
+        t_lib2 = timeit(lambda: gt.addmm_(b.t(), a))
+        print(f"token reduction [{T}x{Mg}]^T x [{T}x16] (plain / transposed out): " + "; ".join(row) +
+              f" | cuBLAS addmm {t_lib*1e6:.1f} / {t_lib2*1e6:.1f} us   ({tag})")
+    assert F.kernel_error_check() == {}
 
 
 def bench_elementwise(small):
@@ -207,7 +242,7 @@ def main():
     a = ap.parse_args()
     for w in a.what.split(","):
         {"gemm": bench_gemm, "skinny": bench_skinny, "elementwise": bench_elementwise, "optim": bench_optim,
-         "attn": bench_attn, "dequant": bench_dequant, "narrow": bench_narrow}[w](a.small)
+         "attn": bench_attn, "dequant": bench_dequant, "narrow": bench_narrow, "wgrad": bench_wgrad}[w](a.small)
 
 
 if __name__ == "__main__":

@@ -13,6 +13,13 @@
 //              registers, write P back over S in TMEM as packed bf16, rescale their half of O in
 //              TMEM only when the running max moved by more than 2^8 (lazy rescale), and write
 //              O / l and the log-sum-exp at the end.
+// Key masks (MASK variant): an additive per-(batch, key) bias in log2 units, 0 for a visible key
+// and -1e30 for a masked or padded one, is added to the scaled scores before the running maximum
+// is taken; a masked probability is then exactly zero and a fully masked tile is wiped by the next
+// rescale. This is the text-padding mask of cached-embedding batches ([B, 1, 1, T],
+// crates/training/src/flux/data_loader.rs:254-264, masked attention path of
+// crates/training/src/flux/runtime.rs:943-961) and the 77-key cross-attention of the SDXL blocks
+// (crates/training/src/sdxl/runtime.rs:146-246), whose single key tile is mostly padding.
 // The reference reaches attention through an external flame-core SDPA or a chunked online-softmax
 // composition of bmm + elementwise ops (crates/training/src/sdxl/runtime.rs:2814-3025,
 // crates/training/src/flux/runtime.rs:707-745); the softmax recurrence is the same.
@@ -32,12 +39,14 @@ struct FaParams {
   bf16* out;         // [B, Lq, H, DH]
   float* lse;        // [B, H, Lq] natural-log log-sum-exp (may be null)
   int* err;
+  const float* kbias;  // MASK variant: [B, Lkb] additive key bias in log2 units (-1e30 = masked)
+  int Lkb;             // row length of kbias: ceil(Lk / 128) * 128
 };
 
 constexpr int BQ = 128, BKV = 128;
 constexpr float kRescaleThreshold = 8.0f;  // log2 units
 
-template <int DH, int POLY>
+template <int DH, int POLY, bool MASK>
 __global__ void __launch_bounds__(320, 2)
 fa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
               const __grid_constant__ CUtensorMap tmV, const FaParams p) {
@@ -176,9 +185,27 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
       }
       tc_fence_after();
       const int kv_left = p.Lk - j * BKV - half * 64;  // valid key columns in this warp's half
-      const bool full_half = kv_left >= 64;
+      const bool full_half = !MASK && kv_left >= 64;
+      // MASK: this half's 64 bias values (every lane reads the same addresses: one transaction each)
+      const float4* kb4 = MASK ? reinterpret_cast<const float4*>(p.kbias + (size_t)b * p.Lkb + j * BKV + half * 64)
+                               : nullptr;
       float mx = -INFINITY;
-      if (full_half) {
+      if constexpr (MASK) {
+#pragma unroll 1
+        for (int c = 0; c < 2; ++c) {
+          uint32_t r[32];
+          tmem_ld32(lane_addr + s_col + c * 32, r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i4 = 0; i4 < 8; ++i4) {
+            const float4 kb = __ldg(kb4 + c * 8 + i4);
+            mx = fmaxf(mx, fmaf(__uint_as_float(r[4 * i4]), p.scale_log2, kb.x));
+            mx = fmaxf(mx, fmaf(__uint_as_float(r[4 * i4 + 1]), p.scale_log2, kb.y));
+            mx = fmaxf(mx, fmaf(__uint_as_float(r[4 * i4 + 2]), p.scale_log2, kb.z));
+            mx = fmaxf(mx, fmaf(__uint_as_float(r[4 * i4 + 3]), p.scale_log2, kb.w));
+          }
+        }
+      } else if (full_half) {
         uint32_t r[32], r2[32];
         tmem_ld32(lane_addr + s_col, r);
         tmem_ld32(lane_addr + s_col + 32, r2);
@@ -202,7 +229,7 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
       s_mx[half * 128 + r_in] = mx;
       asm volatile("bar.sync 1, 256;" ::: "memory");
       mx = fmaxf(mx, s_mx[(half ^ 1) * 128 + r_in]);
-      const float m_new = mx * p.scale_log2;
+      const float m_new = MASK ? mx : mx * p.scale_log2;   // MASK: the bias went in before the maximum
       if (j == 0) {
         m_used = m_new;
       } else {
@@ -267,6 +294,27 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
         float a_lo, a_hi;
         f2_unpack(acc2, a_lo, a_hi);
         lsum = a_lo + a_hi;
+      } else if constexpr (MASK) {
+#pragma unroll 1
+        for (int c = 0; c < 2; ++c) {
+          uint32_t r[32];
+          tmem_ld32(lane_addr + s_col + c * 32, r);
+          tmem_ld_wait();
+          uint32_t pk[16];
+#pragma unroll
+          for (int i4 = 0; i4 < 8; ++i4) {
+            const float4 kb = __ldg(kb4 + c * 8 + i4);
+            // a masked score is about -1e30: its 2^x is exactly zero whatever the running maximum
+            const float p0 = ex2_mufu(fmaf(__uint_as_float(r[4 * i4]), p.scale_log2, kb.x) - m_used);
+            const float p1 = ex2_mufu(fmaf(__uint_as_float(r[4 * i4 + 1]), p.scale_log2, kb.y) - m_used);
+            const float p2 = ex2_mufu(fmaf(__uint_as_float(r[4 * i4 + 2]), p.scale_log2, kb.z) - m_used);
+            const float p3 = ex2_mufu(fmaf(__uint_as_float(r[4 * i4 + 3]), p.scale_log2, kb.w) - m_used);
+            lsum += (p0 + p1) + (p2 + p3);
+            pk[2 * i4] = pack_bf162(p0, p1);
+            pk[2 * i4 + 1] = pack_bf162(p2, p3);
+          }
+          tmem_st16(lane_addr + s_col + c * 16, pk);
+        }
       } else {
 #pragma unroll 1
         for (int c = 0; c < 2; ++c) {
@@ -335,21 +383,21 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
   }
 }
 
-int* g_fa_err = nullptr;
+int* g_fa_err[64] = {nullptr};   // one error word per device
 
-template <int DH, int POLY>
+template <int DH, int POLY, bool MASK>
 int launch_fwd(const CUtensorMap& q, const CUtensorMap& k, const CUtensorMap& v, const FaParams& p,
-               cudaStream_t st) {
+               int dev, cudaStream_t st) {
   constexpr int SMEM = 3 * 128 * 128 * (DH / 64) + 1024 + 128 + 2048;
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(fa_fwd_kernel<DH, POLY>,
+  static bool configured[64] = {};
+  if (!configured[dev]) {
+    cudaError_t e = cudaFuncSetAttribute(fa_fwd_kernel<DH, POLY, MASK>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
     if (e != cudaSuccess) return (int)e;
-    configured = true;
+    configured[dev] = true;
   }
   dim3 grid((p.Lq + BQ - 1) / BQ, p.H, p.B);
-  fa_fwd_kernel<DH, POLY><<<grid, 320, SMEM, st>>>(q, k, v, p);
+  fa_fwd_kernel<DH, POLY, MASK><<<grid, 320, SMEM, st>>>(q, k, v, p);
   return (int)cudaGetLastError();
 }
 
@@ -372,26 +420,17 @@ int make_qkv_map(CUtensorMap* m, const void* ptr, int B, int L, int H, int DH) {
   return make_tensor_map(m, ptr, 3, dims, strides, box, 128);
 }
 
-}  // namespace
-
-extern "C" {
-
-int eri_fa_check_error() {
-  if (!g_fa_err) return 0;
-  int h = 0;
-  cudaMemcpy(&h, g_fa_err, sizeof(int), cudaMemcpyDeviceToHost);
-  if (h) cudaMemset(g_fa_err, 0, sizeof(int));
-  return h;
-}
-
-// q [B, Lq, H, DH], k/v [B, Lk, H, DH], out [B, Lq, H, DH] (all contiguous bf16), lse [B, H, Lq].
-int eri_flash_attn_fwd(const void* q, const void* k, const void* v, void* out, float* lse, int B,
-                       int H, int Lq, int Lk, int DH, float scale, void* stream) {
+int fwd_entry(const void* q, const void* k, const void* v, void* out, float* lse, const float* kbias,
+              int B, int H, int Lq, int Lk, int DH, float scale, void* stream) {
   if (DH != 64 && DH != 128) return -1;
-  if (Lq < 128 || Lk < 128) return -2;
-  if (!g_fa_err) {
-    if (cudaMalloc(&g_fa_err, sizeof(int)) != cudaSuccess) return -3;
-    cudaMemset(g_fa_err, 0, sizeof(int));
+  // Fewer than 128 keys (one mostly empty tile) need the key bias to blank the padding; queries are
+  // tiled by 128 rows and a short last tile is simply not written back.
+  if (Lq < 1 || Lk < 1 || (Lk < 128 && !kbias)) return -2;
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return -3;
+  if (!g_fa_err[dev]) {
+    if (cudaMalloc(&g_fa_err[dev], sizeof(int)) != cudaSuccess) return -3;
+    cudaMemset(g_fa_err[dev], 0, sizeof(int));
   }
   CUtensorMap tq, tk, tv;
   if (make_qkv_map(&tq, q, B, Lq, H, DH) || make_qkv_map(&tk, k, B, Lk, H, DH) ||
@@ -400,17 +439,52 @@ int eri_flash_attn_fwd(const void* q, const void* k, const void* v, void* out, f
   FaParams p;
   p.B = B; p.H = H; p.Lq = Lq; p.Lk = Lk;
   p.scale_log2 = scale * 1.4426950408889634f;
-  p.out = (bf16*)out; p.lse = lse; p.err = g_fa_err;
+  p.out = (bf16*)out; p.lse = lse; p.err = g_fa_err[dev];
+  p.kbias = kbias; p.Lkb = (Lk + BKV - 1) / BKV * BKV;
   cudaStream_t st = (cudaStream_t)stream;
+  if (kbias) {
+    if (((uintptr_t)kbias) & 15) return -6;
+    return DH == 128 ? launch_fwd<128, 0, true>(tq, tk, tv, p, dev, st)
+                     : launch_fwd<64, 0, true>(tq, tk, tv, p, dev, st);
+  }
   const int poly = poly_pairs();
   if (DH == 128) {
-    if (poly == 0) return launch_fwd<128, 0>(tq, tk, tv, p, st);
-    if (poly == 8) return launch_fwd<128, 8>(tq, tk, tv, p, st);
-    return launch_fwd<128, 4>(tq, tk, tv, p, st);
+    if (poly == 0) return launch_fwd<128, 0, false>(tq, tk, tv, p, dev, st);
+    if (poly == 8) return launch_fwd<128, 8, false>(tq, tk, tv, p, dev, st);
+    return launch_fwd<128, 4, false>(tq, tk, tv, p, dev, st);
   }
-  if (poly == 0) return launch_fwd<64, 0>(tq, tk, tv, p, st);
-  if (poly == 8) return launch_fwd<64, 8>(tq, tk, tv, p, st);
-  return launch_fwd<64, 4>(tq, tk, tv, p, st);
+  if (poly == 0) return launch_fwd<64, 0, false>(tq, tk, tv, p, dev, st);
+  if (poly == 8) return launch_fwd<64, 8, false>(tq, tk, tv, p, dev, st);
+  return launch_fwd<64, 4, false>(tq, tk, tv, p, dev, st);
+}
+
+}  // namespace
+
+extern "C" {
+
+int eri_fa_check_error() {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64 || !g_fa_err[dev]) return 0;
+  int h = 0;
+  cudaMemcpy(&h, g_fa_err[dev], sizeof(int), cudaMemcpyDeviceToHost);
+  if (h) cudaMemset(g_fa_err[dev], 0, sizeof(int));
+  return h;
+}
+
+// q [B, Lq, H, DH], k/v [B, Lk, H, DH], out [B, Lq, H, DH] (all contiguous bf16), lse [B, H, Lq].
+int eri_flash_attn_fwd(const void* q, const void* k, const void* v, void* out, float* lse, int B,
+                       int H, int Lq, int Lk, int DH, float scale, void* stream) {
+  return fwd_entry(q, k, v, out, lse, nullptr, B, H, Lq, Lk, DH, scale, stream);
+}
+
+// The same with an additive key bias: kbias [B, ceil(Lk/128)*128] fp32 in log2 units (the caller
+// multiplies a natural-log bias by log2(e)); -1e30 marks a masked key and every column at or beyond
+// Lk. Any Lk >= 1 is accepted.
+int eri_flash_attn_fwd_masked(const void* q, const void* k, const void* v, void* out, float* lse,
+                              const float* kbias, int B, int H, int Lq, int Lk, int DH, float scale,
+                              void* stream) {
+  if (!kbias) return -6;
+  return fwd_entry(q, k, v, out, lse, kbias, B, H, Lq, Lk, DH, scale, stream);
 }
 
 }  // extern "C"

@@ -37,6 +37,8 @@ struct FaBwdParams {
   bf16* dk;              // [B, Lk, H, DH]
   bf16* dv;
   int* err;
+  const float* kbias;    // MASK variants: [B, Lkb] additive key bias in log2 units (-1e30 = masked)
+  int Lkb;               // ceil(Lk / 128) * 128
 };
 
 constexpr int T = 128;  // tile edge (queries and keys)
@@ -90,7 +92,7 @@ __device__ __forceinline__ void named_bar_sync(int id, int nthreads) {
 }
 
 // ------------------------------------------------------------------------------------- dK, dV
-template <int DH, int POLY>
+template <int DH, int POLY, bool MASK>
 __global__ void __launch_bounds__(576, 1)
 fa_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                    const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmDO,
@@ -266,6 +268,10 @@ fa_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     const uint32_t lane_addr = tmem_base + ((uint32_t)(qd * 32) << 16);
     const size_t stat_base = ((size_t)b * p.H + h) * p.Lp;
     const f32x2 sc2 = f2_pack(p.scale_log2, p.scale_log2);
+    // MASK: this thread's key (its TMEM lane) carries one bias value for every query of the tile
+    float kb = 0.f;
+    if constexpr (MASK) kb = p.kbias[(size_t)b * p.Lkb + k0 + qd * 32 + lane];
+    const f32x2 kb2 = f2_pack(kb, kb);
     bool ok = true;
     int tn = 0;
     const int rec = (ew == 0 && lane == 0) ? 1 : -1;
@@ -305,6 +311,7 @@ fa_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
             const int x = 2 * x4 + hh;
             const f32x2 nl2 = hh ? f2_pack(nl.z, nl.w) : f2_pack(nl.x, nl.y);
             f32x2 v = f2_fma(f2_pack_bits(r[2 * x], r[2 * x + 1]), sc2, nl2);
+            if constexpr (MASK) v = f2_add(v, kb2);
             if (x < 16 - POLY) {
               float lo, hi;
               f2_unpack(v, lo, hi);
@@ -394,7 +401,7 @@ fa_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
 }
 
 // ------------------------------------------------------------------------------------- dQ
-template <int DH, int POLY>
+template <int DH, int POLY, bool MASK>
 __global__ void __launch_bounds__(576, 1)
 fa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                  const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmDO,
@@ -629,7 +636,20 @@ fa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(s_read);  // S is in registers: the next S may overwrite it
-        if (kv_left >= 32) {
+        if constexpr (MASK) {
+          // the 32 keys of this warp's chunk: every lane reads the same bias values
+          const float4* kb4 = reinterpret_cast<const float4*>(p.kbias + (size_t)b * p.Lkb + j * T + c * 32);
+#pragma unroll
+          for (int x4 = 0; x4 < 8; ++x4) {
+            const float4 kb = __ldg(kb4 + x4);
+            const float p0 = ex2_mufu(fmaf(__uint_as_float(r[4 * x4]), p.scale_log2, kb.x) - lse2);
+            const float p1 = ex2_mufu(fmaf(__uint_as_float(r[4 * x4 + 1]), p.scale_log2, kb.y) - lse2);
+            const float p2 = ex2_mufu(fmaf(__uint_as_float(r[4 * x4 + 2]), p.scale_log2, kb.z) - lse2);
+            const float p3 = ex2_mufu(fmaf(__uint_as_float(r[4 * x4 + 3]), p.scale_log2, kb.w) - lse2);
+            pr[2 * x4] = f2_pack(p0, p1);
+            pr[2 * x4 + 1] = f2_pack(p2, p3);
+          }
+        } else if (kv_left >= 32) {
 #pragma unroll
           for (int x = 0; x < 16; ++x) {
             f32x2 v = f2_fma(f2_pack_bits(r[2 * x], r[2 * x + 1]), sc2, nl2);
@@ -722,7 +742,7 @@ fa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   }
 }
 
-int* g_fab_err = nullptr;
+int* g_fab_err[64] = {nullptr};   // one error word per device
 long long* g_fab_trace = nullptr;
 int g_fab_trace_cap = 0;
 int g_fab_trace_kernel = 0;  // 0: dQ kernel, 1: dK/dV kernel
@@ -734,26 +754,30 @@ int make_map(CUtensorMap* m, const void* ptr, int B, int L, int H, int DH) {
   return make_tensor_map(m, ptr, 3, dims, strides, box, 128);
 }
 
-template <int DH, int POLY>
+template <int DH, int POLY, bool MASK>
 int launch_bwd_v(const CUtensorMap& q, const CUtensorMap& k, const CUtensorMap& v,
                  const CUtensorMap& d, const FaBwdParams& p, cudaStream_t st) {
   constexpr int SMEM = 6 * 128 * 128 * (DH / 64) + 2048 + 1024 + 128;
   constexpr int SMEM_DQ = 7 * 128 * 128 * (DH / 64) + 1024 + 256;  // 3 K/V stages + dO + barriers
-  static bool configured = false;
-  if (!configured) {
-    if (cudaFuncSetAttribute(fa_bwd_dkdv_kernel<DH, POLY>,
+  // The shared-memory limit is an attribute of the (kernel, device) pair: one flag per device, so
+  // that a process driving several GPUs raises it on each of them.
+  static bool configured[64] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return -5;
+  if (!configured[dev]) {
+    if (cudaFuncSetAttribute(fa_bwd_dkdv_kernel<DH, POLY, MASK>,
                              cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess)
       return -5;
-    if (cudaFuncSetAttribute(fa_bwd_dq_kernel<DH, POLY>,
+    if (cudaFuncSetAttribute(fa_bwd_dq_kernel<DH, POLY, MASK>,
                              cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_DQ) != cudaSuccess)
       return -5;
-    configured = true;
+    configured[dev] = true;
   }
   dim3 g1((p.Lk + T - 1) / T, p.H, p.B), g2((p.Lq + T - 1) / T, p.H, p.B);
   FaBwdParams p1 = p, p2 = p;
   if (g_fab_trace_kernel == 0) p1.trace = nullptr; else p2.trace = nullptr;
-  fa_bwd_dkdv_kernel<DH, POLY><<<g1, 576, SMEM, st>>>(q, k, v, d, p1);
-  fa_bwd_dq_kernel<DH, POLY><<<g2, 576, SMEM_DQ, st>>>(q, k, v, d, p2);
+  fa_bwd_dkdv_kernel<DH, POLY, MASK><<<g1, 576, SMEM, st>>>(q, k, v, d, p1);
+  fa_bwd_dq_kernel<DH, POLY, MASK><<<g2, 576, SMEM_DQ, st>>>(q, k, v, d, p2);
   return (int)cudaGetLastError();
 }
 
@@ -772,10 +796,49 @@ int bwd_poly_pairs() {
 template <int DH>
 int launch_bwd(const CUtensorMap& q, const CUtensorMap& k, const CUtensorMap& v,
                const CUtensorMap& d, const FaBwdParams& p, cudaStream_t st) {
+  if (p.kbias) return launch_bwd_v<DH, 0, true>(q, k, v, d, p, st);
   const int poly = bwd_poly_pairs();
-  if (poly == 0) return launch_bwd_v<DH, 0>(q, k, v, d, p, st);
-  if (poly == 8) return launch_bwd_v<DH, 8>(q, k, v, d, p, st);
-  return launch_bwd_v<DH, 4>(q, k, v, d, p, st);
+  if (poly == 0) return launch_bwd_v<DH, 0, false>(q, k, v, d, p, st);
+  if (poly == 8) return launch_bwd_v<DH, 8, false>(q, k, v, d, p, st);
+  return launch_bwd_v<DH, 4, false>(q, k, v, d, p, st);
+}
+
+void launch_prep(const void* out, const void* dout, const float* lse, float* lse2, float* delta, int B,
+                 int H, int Lq, int Lp, int DH, cudaStream_t st) {
+  const long long rows = (long long)B * H * Lp;
+  const int block = 256;
+  const long long grid = (rows * 16 + block - 1) / block;
+  fa_bwd_prep_kernel<<<(unsigned)grid, block, 0, st>>>((const bf16*)out, (const bf16*)dout, lse, lse2,
+                                                       delta, B, H, Lq, Lp, DH);
+}
+
+int bwd_entry(const void* dout, const void* q, const void* k, const void* v, const void* out,
+              const float* lse, float* lse2, float* delta, void* dq, void* dk, void* dv,
+              const float* kbias, int B, int H, int Lq, int Lk, int DH, float scale, void* stream) {
+  if (DH != 64 && DH != 128) return -1;
+  if (Lq < 1 || Lk < 1 || (Lk < 128 && !kbias)) return -2;
+  if (kbias && (((uintptr_t)kbias) & 15)) return -6;
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return -3;
+  if (!g_fab_err[dev]) {
+    if (cudaMalloc(&g_fab_err[dev], sizeof(int)) != cudaSuccess) return -3;
+    cudaMemset(g_fab_err[dev], 0, sizeof(int));
+  }
+  cudaStream_t st = (cudaStream_t)stream;
+  const int Lp = (Lq + T - 1) / T * T;
+  CUtensorMap tq, tk, tv, td;
+  if (make_map(&tq, q, B, Lq, H, DH) || make_map(&tk, k, B, Lk, H, DH) ||
+      make_map(&tv, v, B, Lk, H, DH) || make_map(&td, dout, B, Lq, H, DH))
+    return -4;
+  launch_prep(out, dout, lse, lse2, delta, B, H, Lq, Lp, DH, st);
+  FaBwdParams p;
+  p.B = B; p.H = H; p.Lq = Lq; p.Lk = Lk; p.Lp = Lp;
+  p.scale = scale; p.scale_log2 = scale * 1.4426950408889634f;
+  p.lse2 = lse2; p.delta = delta; p.q = (const bf16*)q; p.dout = (const bf16*)dout;
+  p.trace = g_fab_trace; p.trace_cap = g_fab_trace_cap;
+  p.dq = (bf16*)dq; p.dk = (bf16*)dk; p.dv = (bf16*)dv; p.err = g_fab_err[dev];
+  p.kbias = kbias; p.Lkb = (Lk + T - 1) / T * T;
+  return DH == 128 ? launch_bwd<128>(tq, tk, tv, td, p, st) : launch_bwd<64>(tq, tk, tv, td, p, st);
 }
 
 }  // namespace
@@ -783,10 +846,11 @@ int launch_bwd(const CUtensorMap& q, const CUtensorMap& k, const CUtensorMap& v,
 extern "C" {
 
 int eri_fa_bwd_check_error() {
-  if (!g_fab_err) return 0;
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64 || !g_fab_err[dev]) return 0;
   int h = 0;
-  cudaMemcpy(&h, g_fab_err, sizeof(int), cudaMemcpyDeviceToHost);
-  if (h) cudaMemset(g_fab_err, 0, sizeof(int));
+  cudaMemcpy(&h, g_fab_err[dev], sizeof(int), cudaMemcpyDeviceToHost);
+  if (h) cudaMemset(g_fab_err[dev], 0, sizeof(int));
   return h;
 }
 
@@ -807,32 +871,19 @@ int eri_flash_attn_bwd(const void* dout, const void* q, const void* k, const voi
                        const void* out, const float* lse, float* lse2, float* delta, void* dq,
                        void* dk, void* dv, int B, int H, int Lq, int Lk, int DH, float scale,
                        void* stream) {
-  if (DH != 64 && DH != 128) return -1;
-  if (Lq < 128 || Lk < 128) return -2;
-  if (!g_fab_err) {
-    if (cudaMalloc(&g_fab_err, sizeof(int)) != cudaSuccess) return -3;
-    cudaMemset(g_fab_err, 0, sizeof(int));
-  }
-  cudaStream_t st = (cudaStream_t)stream;
-  const int Lp = (Lq + T - 1) / T * T;
-  {
-    const long long warps = (long long)B * H * Lp;
-    const int block = 256;
-    const long long grid = (warps * 16 + block - 1) / block;
-    fa_bwd_prep_kernel<<<(unsigned)grid, block, 0, st>>>((const bf16*)out, (const bf16*)dout, lse,
-                                                         lse2, delta, B, H, Lq, Lp, DH);
-  }
-  CUtensorMap tq, tk, tv, td;
-  if (make_map(&tq, q, B, Lq, H, DH) || make_map(&tk, k, B, Lk, H, DH) ||
-      make_map(&tv, v, B, Lk, H, DH) || make_map(&td, dout, B, Lq, H, DH))
-    return -4;
-  FaBwdParams p;
-  p.B = B; p.H = H; p.Lq = Lq; p.Lk = Lk; p.Lp = Lp;
-  p.scale = scale; p.scale_log2 = scale * 1.4426950408889634f;
-  p.lse2 = lse2; p.delta = delta; p.q = (const bf16*)q; p.dout = (const bf16*)dout;
-  p.trace = g_fab_trace; p.trace_cap = g_fab_trace_cap;
-  p.dq = (bf16*)dq; p.dk = (bf16*)dk; p.dv = (bf16*)dv; p.err = g_fab_err;
-  return DH == 128 ? launch_bwd<128>(tq, tk, tv, td, p, st) : launch_bwd<64>(tq, tk, tv, td, p, st);
+  return bwd_entry(dout, q, k, v, out, lse, lse2, delta, dq, dk, dv, nullptr, B, H, Lq, Lk, DH, scale,
+                   stream);
+}
+
+// The same with the additive key bias of eri_flash_attn_fwd_masked (the forward's lse already
+// contains it). Gradients of masked keys come out as zeros.
+int eri_flash_attn_bwd_masked(const void* dout, const void* q, const void* k, const void* v,
+                              const void* out, const float* lse, float* lse2, float* delta, void* dq,
+                              void* dk, void* dv, const float* kbias, int B, int H, int Lq, int Lk,
+                              int DH, float scale, void* stream) {
+  if (!kbias) return -6;
+  return bwd_entry(dout, q, k, v, out, lse, lse2, delta, dq, dk, dv, kbias, B, H, Lq, Lk, DH, scale,
+                   stream);
 }
 
 }  // extern "C"
@@ -945,22 +996,20 @@ int eri_flash_attn_bwd_noalloc(const void* dout, const void* q, const void* k, c
   float* lse2 = g_fa_noalloc_scratch_addr[dev];
   float* delta = lse2 + ERI_FA_NOALLOC_MAX_ROWS;
   cudaStream_t st = (cudaStream_t)stream;
-  {
-    const int block = 256;
-    const long long grid = (rows * 16 + block - 1) / block;
-    fa_bwd_prep_kernel<<<(unsigned)grid, block, 0, st>>>((const bf16*)out, (const bf16*)dout, lse,
-                                                         lse2, delta, B, H, Lq, Lp, DH);
-  }
+  // every check that can fail comes before the first launch, so that a rejected call leaves the
+  // shared scratch untouched
   CUtensorMap tq, tk, tv, td;
   if (encode_map_uncached(&tq, q, B, Lq, H, DH) || encode_map_uncached(&tk, k, B, Lk, H, DH) ||
       encode_map_uncached(&tv, v, B, Lk, H, DH) || encode_map_uncached(&td, dout, B, Lq, H, DH))
     return -4;
+  launch_prep(out, dout, lse, lse2, delta, B, H, Lq, Lp, DH, st);
   FaBwdParams p;
   p.B = B; p.H = H; p.Lq = Lq; p.Lk = Lk; p.Lp = Lp;
   p.scale = scale; p.scale_log2 = scale * 1.4426950408889634f;
   p.lse2 = lse2; p.delta = delta; p.q = (const bf16*)q; p.dout = (const bf16*)dout;
   p.trace = g_fab_trace; p.trace_cap = g_fab_trace_cap;
   p.dq = (bf16*)dq; p.dk = (bf16*)dk; p.dv = (bf16*)dv; p.err = g_fa_noalloc_status_addr[dev];
+  p.kbias = nullptr; p.Lkb = 0;
   return DH == 128 ? launch_bwd<128>(tq, tk, tv, td, p, st) : launch_bwd<64>(tq, tk, tv, td, p, st);
 }
 

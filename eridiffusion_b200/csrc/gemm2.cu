@@ -12,8 +12,17 @@
 // No multicast of any kind is used: every CTA issues its own loads.
 //
 // Same fused epilogue family and LoRA K step as gemm.cu (bias, GELU/SiLU + saved pre-activation,
-// activation backward, gate + residual, column split, MN-major B); operand gathers and the peer
-// scatter stay in the single-CTA kernel.
+// activation backward, gate + residual, column split, MN-major B, operand gathers, peer scatter
+// through staged rows), plus:
+//   * MN-major A ([K, M] row-major): with an MN-major B this is the weight-gradient product
+//     dW[N_out, K_in] = dY[T, N_out]^T X[T, K_in] read straight from the token-major activations;
+//     the `residual` epilogue input (same buffer as `out`) gives the beta = 1 accumulation into an
+//     existing gradient.
+//   * gated-linear-unit epilogue (GEGLU / SwiGLU, the reference's fused feed-forward kernel,
+//     crates/training/src/sdxl/runtime.rs:249-321): the pair's two CTAs stage the B rows of the
+//     FIRST and of the SECOND half of an up-projection [2*hidden, K], so one 256-column accumulator
+//     holds 128 value columns next to their 128 gate columns and the epilogue writes
+//     out[M, hidden] = a * act(b) (or act(a) * b) and, for backward, the raw halves.
 #include "ptx.cuh"
 #include "tma_host.h"
 #include "gather_copy.cuh"
@@ -29,7 +38,8 @@ struct Gemm2Params {
   int lora_r, act, n_split;
   int ldc, ldc2, ld_pre, ldr;
   int rows_per_batch, gate_stride;
-  int b_mn;
+  int b_mn, a_mn;
+  int glu, glu_hidden;        // glu: 0 off, 1 a*gelu(b), 2 a*silu(b), 3 gelu(a)*b, 4 silu(a)*b
   float alpha;
   const bf16* bias;
   const bf16* residual;
@@ -52,14 +62,19 @@ struct Gemm2Params {
   // 2: K range [loc_lo, loc_hi) of an MN-major B likewise; 3: K range [loc_lo, loc_hi) of the A
   // operand (tmBL then maps A[:, loc_lo:loc_hi] in its home buffer). Those slabs have no copy jobs.
   int loc_mode, loc_lo, loc_hi;
+  // peer scatter epilogue (as in gemm.cu): all columns of a pair tile belong to one (part, rank) group
+  int scatter_world, scatter_rank, scatter_part_cols, scatter_group_cols, scatter_local_rows;
+  bf16* scatter_out[kMaxPeers];
+  float* rowsq;
+  int rowsq_parts;
 };
 
 constexpr int BM = 128;       // rows per CTA (256 per pair)
 constexpr int BN = 256;       // columns per pair tile
 constexpr int BNH = 128;      // B rows staged per CTA
 constexpr int BK = 64;
-constexpr int STAGES = 6;
 constexpr int A_BYTES = BM * BK * 2, B_BYTES = BNH * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
+constexpr int STG_PITCH = BN * 2 + 16;   // staged epilogue: one padded accumulator row per thread
 constexpr int kGroupN = 8;
 
 __device__ __forceinline__ uint32_t cluster_ctarank() {
@@ -143,6 +158,9 @@ __device__ __forceinline__ float apply_act_grad(float pre, int act) {
   return act == 3 ? gelu_tanh_grad_f(pre) : silu_grad_f(pre);
 }
 
+// STAGED: the epilogue writes each accumulator row to shared memory and sends it with one bulk
+// asynchronous copy (the peer scatter, whose destination rows live on other GPUs).
+template <int STAGES, bool STAGED>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(192, 1)
 gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                   const __grid_constant__ CUtensorMap tmA2, const __grid_constant__ CUtensorMap tmB2,
@@ -163,6 +181,7 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
   uint64_t* acc_full = empty + STAGES;
   uint64_t* acc_empty = acc_full + 2;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+  uint8_t* stg = smem + STAGES * STAGE_BYTES + 256;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t rank = cluster_ctarank();
@@ -190,7 +209,8 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
   const uint32_t tmem_base = *tmem_slot;
 
   const int num_m = (p.M + 2 * BM - 1) / (2 * BM);
-  const int num_n = (p.N + BN - 1) / BN;
+  // GLU: a tile is 128 output columns (value rows from the first half of B, gate rows from the second)
+  const int num_n = p.glu ? (p.glu_hidden + BNH - 1) / BNH : (p.N + BN - 1) / BN;
   const int tiles = num_m * num_n;
   const int k_iters = p.num_k + (p.lora_r > 0 ? 1 : 0);
   const int cluster_id = ((int)blockIdx.x - p.n_copy) >> 1;
@@ -206,7 +226,7 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
         int m_blk, n_blk;
         tile_coords(t, num_m, num_n, p.rot_n, m_blk, n_blk);
         const int m0 = m_blk * 2 * BM + (int)rank * BM;
-        const int n0 = n_blk * BN + (int)rank * BNH;
+        const int n0 = p.glu ? n_blk * BNH + (int)rank * p.glu_hidden : n_blk * BN + (int)rank * BNH;
         const bool b_rows_local = p.loc_mode == 1 && n0 >= p.loc_lo && n0 + BNH <= p.loc_hi;
         if (p.b_flag_rows && !b_rows_local) {
           // every slab that the B rows staged by THIS CTA touch must have landed
@@ -247,8 +267,14 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
               }
             }
             if (leader) mbar_expect_tx(&full[stage], 2 * STAGE_BYTES);
-            if (p.loc_mode == 3 && k_local) tma_load_2d_pair(sA, &tmBL, bar, kk * BK - p.loc_lo, m0);
-            else tma_load_2d_pair(sA, &tmA, bar, kk * BK, m0);
+            if (p.a_mn) {
+              tma_load_2d_pair(sA, &tmA, bar, m0, kk * BK);
+              tma_load_2d_pair(sA + BK * 128, &tmA, bar, m0 + 64, kk * BK);
+            } else if (p.loc_mode == 3 && k_local) {
+              tma_load_2d_pair(sA, &tmBL, bar, kk * BK - p.loc_lo, m0);
+            } else {
+              tma_load_2d_pair(sA, &tmA, bar, kk * BK, m0);
+            }
             if (!p.b_mn) {
               if (b_rows_local) tma_load_2d_pair(sB, &tmBL, bar, kk * BK, n0 - p.loc_lo);
               else tma_load_2d_pair(sB, &tmB, bar, kk * BK, n0);
@@ -282,7 +308,7 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
       uint32_t phase = 0;
       bool ok = true;
       int it = 0;
-      const uint32_t idesc = umma_idesc_bf16(256, BN, 0, p.b_mn);
+      const uint32_t idesc = umma_idesc_bf16(256, BN, p.a_mn, p.b_mn);
       const uint32_t idesc_lora = umma_idesc_bf16(256, BN, 0, 0);
       for (int t = cluster_id; t < tiles && ok; t += num_clusters, ++it) {
         const int buf = it & 1;
@@ -304,7 +330,15 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
           const uint32_t sB = sA + A_BYTES;
           if (k < p.num_k) {
             const uint64_t da = umma_desc_kmajor(sA, 128);
-            if (!p.b_mn) {
+            if (p.a_mn) {
+              // both operands token-major (weight gradient): 16 K rows are 2048 bytes apart
+#pragma unroll
+              for (int kk = 0; kk < BK / 16; ++kk)
+                umma2_bf16(d_tmem, umma_desc_mn128(sA + kk * 2048, BK * 128),
+                           p.b_mn ? umma_desc_mn128(sB + kk * 2048, BK * 128)
+                                  : umma_desc_kmajor(sB, 128) + kk * 2,
+                           idesc, (k | kk) != 0);
+            } else if (!p.b_mn) {
               const uint64_t db = umma_desc_kmajor(sB, 128);
 #pragma unroll
               for (int kk = 0; kk < BK / 16; ++kk)
@@ -342,7 +376,7 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     for (int t = cluster_id; t < tiles; t += num_clusters, ++it) {
       int m_blk, n_blk;
       tile_coords(t, num_m, num_n, p.rot_n, m_blk, n_blk);
-      const int m0 = m_blk * 2 * BM + (int)rank * BM, n0 = n_blk * BN;
+      const int m0 = m_blk * 2 * BM + (int)rank * BM, n0 = p.glu ? n_blk * BNH : n_blk * BN;
       const int buf = it & 1;
       const uint32_t use = (uint32_t)(it >> 1);
       if (!mbar_wait(&acc_full[buf], use & 1)) {
@@ -352,19 +386,97 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
       tc_fence_after();
       const int row = m0 + q * 32 + lane;
       const bool row_ok = row < p.M;
+      const uint32_t acc_addr = tmem_base + ((uint32_t)(q * 32) << 16) + buf * BN;
+      if (p.glu) {
+        // columns [0,128) of the accumulator: first half of the up-projection, [128,256): second half
+        bf16* dst = p.out + (size_t)row * p.ldc;
+        const bool act_first = p.glu >= 3;
+        const int amode = (p.glu == 1 || p.glu == 3) ? 1 : 2;
+#pragma unroll 1
+        for (int c = 0; c < BNH / 32; ++c) {
+          const int col0 = n0 + c * 32;
+          if (col0 >= p.glu_hidden) break;
+          uint32_t ra[32], rb[32];
+          tmem_ld32(acc_addr + c * 32, ra);
+          tmem_ld32(acc_addr + BNH + c * 32, rb);
+          tmem_ld_wait();
+          if (row_ok) {
+#pragma unroll
+            for (int g = 0; g < 4; ++g) {
+              const int col = col0 + g * 8;
+              if (col < p.glu_hidden) {
+                float va[8], vb[8];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                  va[j] = __uint_as_float(ra[g * 8 + j]) * p.alpha;
+                  vb[j] = __uint_as_float(rb[g * 8 + j]) * p.alpha;
+                }
+                if (p.bias) {
+                  float b0[8], b1[8];
+                  unpack8(*reinterpret_cast<const bf16x8*>(p.bias + col), b0);
+                  unpack8(*reinterpret_cast<const bf16x8*>(p.bias + p.glu_hidden + col), b1);
+#pragma unroll
+                  for (int j = 0; j < 8; ++j) {
+                    va[j] += b0[j];
+                    vb[j] += b1[j];
+                  }
+                }
+                if (p.pre_out) {
+                  // the halves are kept as bf16 (what the unfused path would have stored); the
+                  // product below uses the same rounded values so that backward sees its inputs
+                  bf16* pr = p.pre_out + (size_t)row * p.ld_pre;
+                  const bf16x8 pa = pack8(va), pb = pack8(vb);
+                  *reinterpret_cast<bf16x8*>(pr + col) = pa;
+                  *reinterpret_cast<bf16x8*>(pr + p.glu_hidden + col) = pb;
+                  unpack8(pa, va);
+                  unpack8(pb, vb);
+                }
+                float v[8];
+#pragma unroll
+                for (int j = 0; j < 8; ++j)
+                  v[j] = act_first ? apply_act(va[j], amode) * vb[j] : va[j] * apply_act(vb[j], amode);
+                *reinterpret_cast<bf16x8*>(dst + col) = pack8(v);
+              }
+            }
+          }
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&acc_empty[buf]), 0));
+        continue;
+      }
       const bool second = p.n_split >= 0 && n0 >= p.n_split;
       const int act = second || p.n_split < 0 ? p.act : 0;
       const int coff = second ? p.n_split : 0;
       bf16* dst = second && p.out2 ? p.out2 + (size_t)row * p.ldc2 : p.out + (size_t)row * p.ldc;
-      const int dcol_off = second && p.out2 ? coff : 0;
+      int dcol_off = second && p.out2 ? coff : 0;
+      if (p.scatter_world) {
+        // all columns of a tile belong to one (part, rank) group
+        const int part = n0 / p.scatter_part_cols;
+        const int within = n0 - part * p.scatter_part_cols;
+        const int dest = within / p.scatter_group_cols;
+        const int bidx = row_ok ? row / p.scatter_local_rows : 0;
+        const int lrow = row - bidx * p.scatter_local_rows;
+        const size_t drow = (size_t)bidx * p.scatter_world * p.scatter_local_rows +
+                            (size_t)p.scatter_rank * p.scatter_local_rows + lrow;
+        dst = p.scatter_out[dest] + drow * p.ldc;
+        // destination column = part * group_cols + (col % group_cols)
+        dcol_off = n0 - (part * p.scatter_group_cols + (within - dest * p.scatter_group_cols));
+      }
       const bf16* gate = p.gate ? p.gate + (size_t)(row_ok ? row / p.rows_per_batch : 0) * p.gate_stride
                                 : nullptr;
+      uint8_t* stg_row = stg + (size_t)(q * 32 + lane) * STG_PITCH;
+      if constexpr (STAGED) {
+        // this thread's previous row copy must have read its staging row before it is rewritten
+        if (it > 0) tma_store_wait_read<0>();
+      }
+      float sq = 0.f;
 #pragma unroll 1
       for (int c = 0; c < BN / 32; ++c) {
         const int col0 = n0 + c * 32;
         if (col0 >= p.N) break;
         uint32_t r[32];
-        tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + buf * BN + c * 32, r);
+        tmem_ld32(acc_addr + c * 32, r);
         tmem_ld_wait();
         if (row_ok) {
 #pragma unroll
@@ -407,15 +519,37 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
 #pragma unroll
                 for (int j = 0; j < 8; ++j) v[j] += rs[j];
               }
-              *reinterpret_cast<bf16x8*>(dst + (col - dcol_off)) = pack8(v);
+              if (p.rowsq) {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) sq += v[j] * v[j];
+              }
+              if constexpr (STAGED)
+                *reinterpret_cast<bf16x8*>(stg_row + (size_t)(col - n0) * 2) = pack8(v);
+              else
+                *reinterpret_cast<bf16x8*>(dst + (col - dcol_off)) = pack8(v);
             }
           }
         }
+      }
+      if constexpr (STAGED) {
+        // the row was written by this thread alone: order it before the async proxy reads it, then
+        // one bulk copy carries the whole row to its (possibly remote) destination
+        fence_proxy_async_all();
+        if (row_ok) {
+          const int ncols = min(BN, p.N - n0);
+          bulk_s2g_plain(dst + (n0 - dcol_off), smem_u32(stg_row), (uint32_t)ncols * 2u);
+        }
+        tma_store_commit();
+      }
+      if (p.rowsq && row_ok) {
+        const int part = n0 / p.scatter_part_cols;
+        if (part < p.rowsq_parts) atomicAdd(p.rowsq + (size_t)part * p.M + row, sq);
       }
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&acc_empty[buf]), 0));
     }
+    if constexpr (STAGED) tma_store_wait<0>();   // every row copy of this thread has completed
   }
 
   tc_fence_before();
@@ -430,6 +564,74 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
 int g2_num_sms = 0;
 int* g2_err = nullptr;
 long long g2_gather_launches = 0;   // gather-mode launches that ran on this kernel (host counter)
+
+template <int STAGES, bool STAGED>
+int launch2(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& ta2, const CUtensorMap& tb2,
+            const CUtensorMap& tbl, Gemm2Params& p, int tiles, int pdl, cudaStream_t st) {
+  constexpr int SMEM = STAGES * STAGE_BYTES + 1024 + 256 + (STAGED ? BM * STG_PITCH : 0);
+  auto kern = gemm2_bf16_kernel<STAGES, STAGED>;
+  int dev = 0;
+  cudaGetDevice(&dev);
+  static bool configured[64] = {};
+  if (dev < 0 || dev >= 64) return -36;
+  if (!configured[dev]) {
+    // the attribute belongs to the (function, device) pair
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess)
+      return -36;
+    configured[dev] = true;
+  }
+  if (p.n_copy > 0) {
+    // The compute clusters spin on counters that the copy clusters bump, so every CTA of the grid
+    // must be resident: the grid is sized by the cluster occupancy query and launched cooperatively.
+    static int coop_clusters = -1;
+    if (coop_clusters < 0) {
+      cudaLaunchConfig_t cfg = {};
+      cfg.gridDim = dim3(g2_num_sms / 2 * 2);
+      cfg.blockDim = dim3(192);
+      cfg.dynamicSmemBytes = SMEM;
+      cudaLaunchAttribute at[1];
+      at[0].id = cudaLaunchAttributeClusterDimension;
+      at[0].val.clusterDim.x = 2; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 1;
+      cfg.attrs = at;
+      cfg.numAttrs = 1;
+      int n = 0;
+      if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) != cudaSuccess) {
+        cudaGetLastError();
+        n = 0;
+      }
+      coop_clusters = n;
+    }
+    const int room = coop_clusters - p.n_copy / 2;
+    if (room < 8) return -30;
+    const int clusters = tiles < room ? tiles : room;
+    void* args[] = {(void*)&ta, (void*)&tb, (void*)&ta2, (void*)&tb2, (void*)&tbl, (void*)&p};
+    cudaError_t e = cudaLaunchCooperativeKernel((const void*)kern, dim3(p.n_copy + clusters * 2),
+                                                dim3(192), args, SMEM, st);
+    if (e != cudaSuccess) {
+      cudaGetLastError();
+      return -30;   // the caller falls back to the one-CTA kernel
+    }
+    ++g2_gather_launches;
+    return 0;
+  }
+  const int max_clusters = g2_num_sms / 2;
+  const int clusters = tiles < max_clusters ? tiles : max_clusters;
+  if (pdl) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(clusters * 2);
+    cfg.blockDim = dim3(192);
+    cfg.dynamicSmemBytes = SMEM;
+    cfg.stream = st;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = at;
+    cfg.numAttrs = 1;
+    return (int)cudaLaunchKernelEx(&cfg, kern, ta, tb, ta2, tb2, tbl, p);
+  }
+  kern<<<clusters * 2, 192, SMEM, st>>>(ta, tb, ta2, tb2, tbl, p);
+  return (int)cudaGetLastError();
+}
 
 }  // namespace
 
@@ -449,14 +651,31 @@ int eri_gemm2_check_error() {
 
 // Returns -30 when the problem does not fit this kernel (caller falls back to eri_gemm_bf16).
 int eri_gemm2_bf16(const EriGemmArgs2* g, void* stream) {
-  if (g->scatter_world || g->rowsq) return -30;
+  const bool scatter = g->scatter_world != 0;
+  if (g->rowsq && !scatter) return -30;
+  if (scatter) {
+    // a pair tile must sit inside one (part, rank) column group; rows leave through 16-byte aligned
+    // bulk copies
+    if (g->scatter_group_cols % BN || g->scatter_part_cols % BN || (g->ldc * 2) % 16 || g->n_copy ||
+        g->glu || g->a_mn)
+      return -30;
+  }
   if (g->n_copy) {
     // gather mode: whole copy clusters, rotations in whole pair tiles / K blocks
     if (g->n_copy % 2 || g->n_copy < 0 || g->n_copy > 64) return -30;
     if (g->rot_n_rows % BN || g->rot_k_cols % BK || g->a_flag_cols % BK || g->a_flag_rows % BM) return -30;
+    if (g->a_mn || g->glu) return -30;
   }
+  if (g->glu) {
+    // N counts the rows of the up-projection weight (both halves); the output has N / 2 columns
+    if (g->glu < 1 || g->glu > 4 || g->N % 2 || (g->N / 2) % 8 || g->N / 2 < BNH || g->b_mn || g->a_mn ||
+        g->n_split > 0 || g->act || g->residual || g->gate || g->out2)
+      return -30;
+  }
+  if (g->a_mn && (g->lora_r || g->M % 8)) return -30;
   if (g->M < 256 || g->N < 256 || g->K < 64) return -30;
-  if (g->K % 8 || g->N % 8 || g->lda % 8 || g->ldb % 8 || g->ldc % 8) return -30;
+  // a dimension that is contiguous in memory must keep rows 16-byte aligned
+  if ((!(g->a_mn && g->b_mn) && g->K % 8) || g->N % 8 || g->lda % 8 || g->ldb % 8 || g->ldc % 8) return -30;
   if (g->lora_r && g->lora_r != 16 && g->lora_r != 32 && g->lora_r != 64) return -30;
   if (g->n_split > 0 && g->n_split % BN) return -30;
   if (!g2_err) {
@@ -472,7 +691,8 @@ int eri_gemm2_bf16(const EriGemmArgs2* g, void* stream) {
   p.lora_r = g->lora_r; p.act = g->act; p.n_split = g->n_split > 0 ? g->n_split : -1;
   p.ldc = g->ldc; p.ldc2 = g->ldc2; p.ld_pre = g->ld_pre; p.ldr = g->ldr;
   p.rows_per_batch = g->rows_per_batch > 0 ? g->rows_per_batch : g->M;
-  p.gate_stride = g->gate_stride; p.alpha = g->alpha; p.b_mn = g->b_mn;
+  p.gate_stride = g->gate_stride; p.alpha = g->alpha; p.b_mn = g->b_mn; p.a_mn = g->a_mn ? 1 : 0;
+  p.glu = g->glu; p.glu_hidden = g->glu ? g->N / 2 : 0;
   p.bias = (const bf16*)g->bias; p.residual = (const bf16*)g->residual;
   p.gate = (const bf16*)g->gate; p.pre_in = (const bf16*)g->pre_in;
   p.out = (bf16*)g->out; p.out2 = (bf16*)g->out2; p.pre_out = (bf16*)g->pre_out;
@@ -482,6 +702,13 @@ int eri_gemm2_bf16(const EriGemmArgs2* g, void* stream) {
   p.b_flag_rows = g->b_flag_rows; p.a_flag_cols = g->a_flag_cols; p.a_flag_rows = g->a_flag_rows;
   p.a_row_groups = g->a_flag_rows > 0 ? (g->M + g->a_flag_rows - 1) / g->a_flag_rows : 0;
   p.rot_n = g->rot_n_rows / BN; p.rot_k = g->rot_k_cols / BK;
+  if (scatter) {
+    p.scatter_world = g->scatter_world; p.scatter_rank = g->scatter_rank;
+    p.scatter_part_cols = g->scatter_part_cols; p.scatter_group_cols = g->scatter_group_cols;
+    p.scatter_local_rows = g->scatter_local_rows > 0 ? g->scatter_local_rows : g->M;
+    for (int i = 0; i < kMaxPeers; ++i) p.scatter_out[i] = (bf16*)g->scatter_out[i];
+    p.rowsq = (float*)g->rowsq; p.rowsq_parts = g->rowsq_parts;
+  }
   const bool use_local = g->n_copy && g->b_local && g->jobs_nl && g->flag_target_nl &&
                          !(((uintptr_t)g->b_local) & 15) && g->ldb_local % 8 == 0 &&
                          ((g->loc_mode == 1 && !g->b_mn && g->loc_lo % BNH == 0 && g->loc_hi % BNH == 0) ||
@@ -494,10 +721,15 @@ int eri_gemm2_bf16(const EriGemmArgs2* g, void* stream) {
   }
 
   CUtensorMap ta, tb, ta2, tb2;
-  {
+  if (!g->a_mn) {
     uint64_t d[2] = {(uint64_t)g->K, (uint64_t)g->M};
     uint64_t s[1] = {(uint64_t)g->lda * 2};
     uint32_t bx[2] = {BK, BM};
+    if (make_tensor_map(&ta, g->a, 2, d, s, bx, 128)) return -32;
+  } else {
+    uint64_t d[2] = {(uint64_t)g->M, (uint64_t)g->K};     // A given as [K, M]
+    uint64_t s[1] = {(uint64_t)g->lda * 2};
+    uint32_t bx[2] = {64, BK};
     if (make_tensor_map(&ta, g->a, 2, d, s, bx, 128)) return -32;
   }
   if (!g->b_mn) {
@@ -542,66 +774,12 @@ int eri_gemm2_bf16(const EriGemmArgs2* g, void* stream) {
       if (make_tensor_map(&tbl, g->b_local, 2, d, s, bx, 128)) return -33;
     }
   }
-  constexpr int SMEM = STAGES * STAGE_BYTES + 1024 + 256;
-  static bool configured = false;
-  if (!configured) {
-    if (cudaFuncSetAttribute(gemm2_bf16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) !=
-        cudaSuccess)
-      return -36;
-    configured = true;
-  }
-  const int tiles = ((g->M + 2 * BM - 1) / (2 * BM)) * ((g->N + BN - 1) / BN);
-  if (p.n_copy > 0) {
-    // The compute clusters spin on counters that the copy clusters bump, so every CTA of the grid
-    // must be resident: the grid is sized by the cluster occupancy query and launched cooperatively.
-    static int coop_clusters = -1;
-    if (coop_clusters < 0) {
-      cudaLaunchConfig_t cfg = {};
-      cfg.gridDim = dim3(g2_num_sms / 2 * 2);
-      cfg.blockDim = dim3(192);
-      cfg.dynamicSmemBytes = SMEM;
-      cudaLaunchAttribute at[1];
-      at[0].id = cudaLaunchAttributeClusterDimension;
-      at[0].val.clusterDim.x = 2; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 1;
-      cfg.attrs = at;
-      cfg.numAttrs = 1;
-      int n = 0;
-      if (cudaOccupancyMaxActiveClusters(&n, gemm2_bf16_kernel, &cfg) != cudaSuccess) {
-        cudaGetLastError();
-        n = 0;
-      }
-      coop_clusters = n;
-    }
-    const int room = coop_clusters - p.n_copy / 2;
-    if (room < 8) return -30;
-    const int clusters = tiles < room ? tiles : room;
-    void* args[] = {(void*)&ta, (void*)&tb, (void*)&ta2, (void*)&tb2, (void*)&tbl, (void*)&p};
-    cudaError_t e = cudaLaunchCooperativeKernel((const void*)gemm2_bf16_kernel, dim3(p.n_copy + clusters * 2),
-                                                dim3(192), args, SMEM, (cudaStream_t)stream);
-    if (e != cudaSuccess) {
-      cudaGetLastError();
-      return -30;   // the caller falls back to the one-CTA kernel
-    }
-    ++g2_gather_launches;
-    return 0;
-  }
-  const int max_clusters = g2_num_sms / 2;
-  const int clusters = tiles < max_clusters ? tiles : max_clusters;
-  if (g->pdl && g->lora_r) {
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(clusters * 2);
-    cfg.blockDim = dim3(192);
-    cfg.dynamicSmemBytes = SMEM;
-    cfg.stream = (cudaStream_t)stream;
-    cudaLaunchAttribute at[1];
-    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    at[0].val.programmaticStreamSerializationAllowed = 1;
-    cfg.attrs = at;
-    cfg.numAttrs = 1;
-    return (int)cudaLaunchKernelEx(&cfg, gemm2_bf16_kernel, ta, tb, ta2, tb2, tbl, p);
-  }
-  gemm2_bf16_kernel<<<clusters * 2, 192, SMEM, (cudaStream_t)stream>>>(ta, tb, ta2, tb2, tbl, p);
-  return (int)cudaGetLastError();
+  const int n_tiles = g->glu ? (g->N / 2 + BNH - 1) / BNH : (g->N + BN - 1) / BN;
+  const int tiles = ((g->M + 2 * BM - 1) / (2 * BM)) * n_tiles;
+  cudaStream_t st = (cudaStream_t)stream;
+  // four operand stages leave room for the 128 staged accumulator rows of the peer scatter
+  if (scatter) return launch2<4, true>(ta, tb, ta2, tb2, tbl, p, tiles, 0, st);
+  return launch2<6, false>(ta, tb, ta2, tb2, tbl, p, tiles, g->pdl && g->lora_r, st);
 }
 
 }  // extern "C"

@@ -52,6 +52,13 @@ struct EriGemmArgs {
   int n_jobs_nl;
   const void* jobs_nl;
   const void* flag_target_nl;
+  // 1: A is given as [K, M] row-major (MN-major operand; row stride lda). Together with b_mn this is
+  // the weight-gradient product dW = dY^T X over token-major activations (two-CTA kernel only).
+  int a_mn;
+  // Gated linear unit on an up-projection b = [2 * hidden, K]: out[M, hidden] = a * act(g) with a, g
+  // the two halves of the projection; pre_out (optional, [M, 2 * hidden]) keeps the halves.
+  // 1: a * gelu(g), 2: a * silu(g), 3: gelu(a) * g, 4: silu(a) * g (two-CTA kernel only).
+  int glu;
 };
 
 }  // extern "C"

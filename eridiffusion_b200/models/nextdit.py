@@ -74,7 +74,7 @@ class NextDiTBlock(nn.Module):
         a = self.attn_norm2(self.out(F.attention(q, k, v).flatten(2)))
         x = F.gate_residual(x, a, g_a)
         h = self.ffn_norm1(x, sc_m)
-        m = self.ffn_norm2(self.w2(F.glu(self.w13(h), "silu", act_first=True)))
+        m = self.ffn_norm2(self.w2(F.linear_glu(h, self.w13, "silu", act_first=True)))
         return F.gate_residual(x, m, g_m)
 
 

@@ -205,8 +205,8 @@ class KleinDouble(nn.Module):
         a = F.attention(q, k, v).flatten(2)
         img = self.img.proj(a[:, Lt:], residual=img, gate=i_g1)
         txt = self.txt.proj(a[:, :Lt], residual=txt, gate=t_g1)
-        img = self.img.mlp_out(F.glu(self.img.mlp_in(F.norm_modulate(img, i_sc2, i_sh2)), "silu"), residual=img, gate=i_g2)
-        txt = self.txt.mlp_out(F.glu(self.txt.mlp_in(F.norm_modulate(txt, t_sc2, t_sh2)), "silu"), residual=txt, gate=t_g2)
+        img = self.img.mlp_out(F.linear_glu(F.norm_modulate(img, i_sc2, i_sh2), self.img.mlp_in, "silu"), residual=img, gate=i_g2)
+        txt = self.txt.mlp_out(F.linear_glu(F.norm_modulate(txt, t_sc2, t_sh2), self.txt.mlp_in, "silu"), residual=txt, gate=t_g2)
         return img, txt
 
 

@@ -95,7 +95,7 @@ class BasicTransformerBlock(nn.Module):
     def forward(self, x, ctx):
         x = self.attn1(self.norm1(x), residual=x)
         x = self.attn2(self.norm2(x), ctx, residual=x)
-        h = F.glu(self.ff_in(self.norm3(x)), "gelu", act_first=False)       # value * gelu(gate)
+        h = F.linear_glu(self.norm3(x), self.ff_in, "gelu", act_first=False)       # value * gelu(gate)
         return self.ff_out(h, residual=x)
 
 

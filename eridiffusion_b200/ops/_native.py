@@ -49,6 +49,7 @@ class GemmArgs(C.Structure):
         ("b_local", C.c_void_p), ("ldb_local", C.c_longlong),
         ("loc_mode", C.c_int), ("loc_lo", C.c_int), ("loc_hi", C.c_int), ("n_jobs_nl", C.c_int),
         ("jobs_nl", C.c_void_p), ("flag_target_nl", C.c_void_p),
+        ("a_mn", C.c_int), ("glu", C.c_int),
     ]
 
 
@@ -101,6 +102,9 @@ _SIGNATURES = {
     "eri_gemm_skinny": [_P, _L, _P, _L, _P, _I, _I, _I, _I, _F, _P],
     "eri_gemm_skinny_check_error": [],
     "eri_gemm_rank_stream": [_P, _L, _P, _L, _P, _I, _I, _I, _I, _F, _P],
+    "eri_gemm_tokred": [_P, _L, _P, _L, _P, _I, _I, _I, _I, _F, _I, _I, _P],
+    "eri_gemm_tokred_check_error": [],
+    "eri_gemm_tokred_set_target": [_I],
     "eri_gemm_init": [],
     "eri_gemm_check_error": [],
     "eri_gemm_bf16": [C.POINTER(GemmArgs), _P],

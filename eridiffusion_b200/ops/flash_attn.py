@@ -2,6 +2,11 @@
 
 Tensors are token-major ``[B, L, H, Dh]`` bf16. The forward returns the output and the
 log-sum-exp per (batch, head, query); the backward kernels recompute the probabilities from it.
+
+Key masks: a mask that depends on (batch, key) only — the text-padding mask ``[B, 1, 1, T]`` of
+cached-embedding batches, boolean or additive — becomes a per-key bias row that the kernels add to
+the scaled scores (``key_bias``). Fewer than 128 keys (SDXL cross-attention over 77 text tokens) run
+as one key tile whose padding is blanked by the same bias.
 """
 from __future__ import annotations
 
@@ -15,14 +20,20 @@ _P, _I, _F = N.C.c_void_p, N.C.c_int, N.C.c_float
 N._SIGNATURES.update({
     "eri_flash_attn_fwd": [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _P],
     "eri_flash_attn_bwd": [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _P],
+    "eri_flash_attn_fwd_masked": [_P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _P],
+    "eri_flash_attn_bwd_masked": [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _P],
     "eri_fa_check_error": [],
     "eri_fa_bwd_check_error": [],
 })
 
+_LOG2E = 1.4426950408889634
+_PAD_BIAS = {}
+_MASKED = -1.0e30      # bias of a masked key: its probability is exactly zero, and the value stays finite
+
 
 def _bind(lib):
-    for name in ("eri_flash_attn_fwd", "eri_flash_attn_bwd", "eri_fa_check_error",
-                 "eri_fa_bwd_check_error"):
+    for name in ("eri_flash_attn_fwd", "eri_flash_attn_bwd", "eri_flash_attn_fwd_masked",
+                 "eri_flash_attn_bwd_masked", "eri_fa_check_error", "eri_fa_bwd_check_error"):
         if hasattr(lib, name):
             fn = getattr(lib, name)
             fn.argtypes = N._SIGNATURES[name]
@@ -40,16 +51,53 @@ def has_backward() -> bool:
 
 
 def supported(q, k, v) -> bool:
+    """Shapes the kernels take: head size 64 / 128, at least one key, at least 16 query rows
+    (shorter query sets are conditioning-vector sized and stay on the library)."""
     if not has_forward():
         return False
     B, L, H, D = q.shape
     return (D in (64, 128) and q.is_contiguous() and k.is_contiguous() and v.is_contiguous()
-            and k.shape[1] >= 128 and L >= 128 and k.shape[2] == H and v.shape == k.shape)
+            and k.shape[1] >= 1 and L >= 16 and k.shape[2] == H and v.shape == k.shape and k.shape[0] == B)
 
 
-def fwd(q, k, v, scale=None, out=None):
+def mask_is_key_only(mask, B, Lk) -> bool:
+    """True for masks that depend on (batch, key) only: [B|1, Lk] or [B|1, 1, 1, Lk]."""
+    if mask is None:
+        return False
+    shp = tuple(mask.shape)
+    if len(shp) == 2:
+        return shp[1] == Lk and shp[0] in (1, B)
+    return len(shp) == 4 and shp[1] == 1 and shp[2] == 1 and shp[3] == Lk and shp[0] in (1, B)
+
+
+def key_bias(mask, B, Lk, device):
+    """[B, ceil(Lk/128)*128] fp32 additive key bias in log2 units for the masked kernels. ``mask``:
+    None (only the padding beyond Lk is blanked), boolean (True = visible) or additive (natural-log
+    units; -inf allowed), of a shape accepted by ``mask_is_key_only``."""
+    Lkb = (Lk + 127) // 128 * 128
+    if mask is None:
+        # constant per (B, Lk, device): built once (70 cross-attention calls per SDXL step share it)
+        key = (B, Lk, str(device))
+        kb = _PAD_BIAS.get(key)
+        if kb is None:
+            kb = torch.full((B, Lkb), _MASKED, dtype=torch.float32, device=device)
+            kb[:, :Lk] = 0.0
+            _PAD_BIAS[key] = kb
+        return kb
+    kb = torch.full((B, Lkb), _MASKED, dtype=torch.float32, device=device)
+    m = mask.reshape(mask.shape[0], Lk).to(device)
+    if m.dtype == torch.bool:
+        row = torch.where(m, 0.0, _MASKED).float()
+    else:
+        row = (m.float() * _LOG2E).clamp_min(_MASKED)
+    kb[:, :Lk] = row.expand(B, Lk)
+    return kb
+
+
+def fwd(q, k, v, scale=None, out=None, kbias=None):
     """Returns (out [B, Lq, H, Dh] bf16, lse [B, H, Lq] fp32). ``out``: optional contiguous
-    destination of q's shape (e.g. a buffer that peers can read)."""
+    destination of q's shape (e.g. a buffer that peers can read). ``kbias``: key bias from
+    ``key_bias`` (required when there are fewer than 128 keys)."""
     lib = N.require()
     _bind(lib)
     B, Lq, H, D = q.shape
@@ -60,14 +108,21 @@ def fwd(q, k, v, scale=None, out=None):
     elif out.shape != q.shape or out.dtype != q.dtype or not out.is_contiguous():
         raise ValueError("flash attention: out must be contiguous with q's shape and dtype")
     lse = torch.empty(B, H, Lq, dtype=torch.float32, device=q.device)
+    if kbias is None and Lk < 128:
+        kbias = key_bias(None, B, Lk, q.device)
+    if kbias is not None:
+        N.check(lib.eri_flash_attn_fwd_masked(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(),
+                                              lse.data_ptr(), kbias.data_ptr(), B, H, Lq, Lk, D, scale,
+                                              N.stream_ptr()), "flash_attn_fwd_masked")
+        return out, lse
     N.check(lib.eri_flash_attn_fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(),
                                    lse.data_ptr(), B, H, Lq, Lk, D, scale, N.stream_ptr()),
             "flash_attn_fwd")
     return out, lse
 
 
-def bwd(do, q, k, v, out, lse, scale=None):
-    """Returns (dq, dk, dv)."""
+def bwd(do, q, k, v, out, lse, scale=None, kbias=None):
+    """Returns (dq, dk, dv). ``kbias``: the key bias the forward ran with."""
     lib = N.require()
     _bind(lib)
     B, Lq, H, D = q.shape
@@ -77,6 +132,15 @@ def bwd(do, q, k, v, out, lse, scale=None):
     dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
     lse2 = torch.empty(B, H, Lp, dtype=torch.float32, device=q.device)
     delta = torch.empty_like(lse2)
+    if kbias is None and Lk < 128:
+        kbias = key_bias(None, B, Lk, q.device)
+    if kbias is not None:
+        N.check(lib.eri_flash_attn_bwd_masked(do.data_ptr(), q.data_ptr(), k.data_ptr(), v.data_ptr(),
+                                              out.data_ptr(), lse.data_ptr(), lse2.data_ptr(),
+                                              delta.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(),
+                                              kbias.data_ptr(), B, H, Lq, Lk, D, scale, N.stream_ptr()),
+                "flash_attn_bwd_masked")
+        return dq, dk, dv
     N.check(lib.eri_flash_attn_bwd(do.data_ptr(), q.data_ptr(), k.data_ptr(), v.data_ptr(),
                                    out.data_ptr(), lse.data_ptr(), lse2.data_ptr(),
                                    delta.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(),
@@ -95,29 +159,35 @@ def check_error() -> int:
 
 class _FlashAttention(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, q, k, v, scale, out_buf=None):
+    def forward(ctx, q, k, v, scale, out_buf=None, kbias=None):
         if out_buf is not None:
             ctx.mark_dirty(out_buf)          # an input that is written in place and returned
-        out, lse = fwd(q, k, v, scale, out_buf)
-        ctx.save_for_backward(q, k, v, out, lse)
+        if kbias is None and k.shape[1] < 128:
+            kbias = key_bias(None, k.shape[0], k.shape[1], q.device)
+        out, lse = fwd(q, k, v, scale, out_buf, kbias)
+        ctx.save_for_backward(q, k, v, out, lse, kbias)
         ctx.scale = scale
         return out
 
     @staticmethod
     def backward(ctx, do):
-        q, k, v, out, lse = ctx.saved_tensors
+        q, k, v, out, lse, kbias = ctx.saved_tensors
         do = do.contiguous()
         if has_backward():
-            dq, dk, dv = bwd(do, q, k, v, out, lse, ctx.scale)
-            return dq, dk, dv, None, None
+            dq, dk, dv = bwd(do, q, k, v, out, lse, ctx.scale, kbias)
+            return dq, dk, dv, None, None, None
+        if kbias is not None:
+            raise RuntimeError("masked flash attention needs the native backward kernels")
         # Library recompute path, used only while the native backward is absent from the build.
         from . import reference as R
         with torch.enable_grad():
             qq, kk, vv = (t.detach().requires_grad_() for t in (q, k, v))
             o = R.attention(qq, kk, vv, ctx.scale)
         dq, dk, dv = torch.autograd.grad(o, (qq, kk, vv), do)
-        return dq, dk, dv, None, None
+        return dq, dk, dv, None, None, None
 
 
-def flash_attention(q, k, v, scale=None, out=None):
-    return _FlashAttention.apply(q, k, v, scale, out)
+def flash_attention(q, k, v, scale=None, out=None, mask=None):
+    """``mask``: None or a key-only mask (see ``mask_is_key_only``); the bias row is built here."""
+    kbias = None if mask is None else key_bias(mask, q.shape[0], k.shape[1], q.device)
+    return _FlashAttention.apply(q, k, v, scale, out, kbias)

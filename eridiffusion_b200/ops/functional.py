@@ -19,6 +19,8 @@ _ATTN_NATIVE = os.environ.get("ERI_B200_ATTN", "native")  # "native" | "library"
 _GEMM_PAIR = os.environ.get("ERI_B200_GEMM2", "1") == "1"  # two-CTA tiles for large problems
 _GATHER_PAIR = os.environ.get("ERI_B200_GATHER_PAIR", "1") == "1"  # gather-fused GEMMs on the two-CTA kernel
 _GATHER_LOCAL = os.environ.get("ERI_B200_GATHER_LOCAL", "1") == "1"  # own slab read in place, not copied
+_SCATTER_PAIR = os.environ.get("ERI_B200_SCATTER_PAIR", "1") == "1"  # peer-scatter epilogue on the two-CTA kernel
+_WGRAD_NATIVE = os.environ.get("ERI_B200_WGRAD", "native") == "native"  # weight gradients on tcgen05 (else torch.mm)
 _RANK_STREAM = os.environ.get("ERI_B200_RANK_STREAM", "1") == "1"  # streaming kernel for [M,K] x [r,K]^T
 # Launch the LoRA-fused GEMM as a programmatic dependent of the down-projection kernel that precedes
 # it on the stream: its main K loop overlaps that kernel and only the rank-r step waits for it.
@@ -349,21 +351,27 @@ _ACT_CODE = {None: 0, "gelu": 1, "silu": 2, "gelu_bwd": 3, "silu_bwd": 4}
 
 def gemm_native(a, b, *, out=None, alpha=1.0, bias=None, lora_h=None, lora_b=None, act=None,
                 pre_out=None, pre_in=None, residual=None, gate=None, rows_per_batch=0,
-                n_split=0, out2=None, force_bn=0, b_mn=False, gather=None, scatter=None, pdl=False):
+                n_split=0, out2=None, force_bn=0, b_mn=False, gather=None, scatter=None, pdl=False,
+                a_mn=False, glu=0):
     """out[M,N] = epilogue(a[M,K] @ op(b) (+ lora_h[M,r] @ lora_b[N,r]^T)) on the tcgen05 kernel.
 
     ``b`` is [N, K] (``op`` = transpose) or, with ``b_mn=True``, [K, N] used as is. ``a``/``b``/
     ``out`` may be row-strided views (last dim contiguous). ``gather``: dict built by
     ``parallel.gather_gemm`` (copy jobs + slab counters, fuses an operand gather into the launch).
     ``scatter``: dict(world, rank, part_cols, group_cols, local_rows, ptrs) routing column groups
-    to peer buffers (``out`` is then only used for its row stride). Returns ``out``.
+    to peer buffers (``out`` is then only used for its row stride). ``a_mn=True``: ``a`` is [K, M]
+    used as is (with ``b_mn`` this is the weight-gradient product over token-major activations).
+    ``glu`` 1-4: ``b`` is an up-projection [2*hidden, K] and the output is the gated product of its
+    halves, [M, hidden] (1 a*gelu(g), 2 a*silu(g), 3 gelu(a)*g, 4 silu(a)*g); ``pre_out``
+    [M, 2*hidden] keeps the halves for backward. Returns ``out``.
     """
     lib = N.require()
-    M, K = a.shape
+    K, M = a.shape if a_mn else a.shape[::-1]
     Nn = b.shape[1] if b_mn else b.shape[0]
     assert (b.shape[0] if b_mn else b.shape[1]) == K and a.stride(1) == 1 and b.stride(1) == 1
     if out is None:
-        out = torch.empty(M, Nn if not n_split else n_split, dtype=torch.bfloat16, device=a.device)
+        cols = Nn // 2 if glu else (Nn if not n_split else n_split)
+        out = torch.empty(M, cols, dtype=torch.bfloat16, device=a.device)
     g = N.GemmArgs()
     g.a, g.b = a.data_ptr(), b.data_ptr()
     g.lda, g.ldb = a.stride(0), b.stride(0)
@@ -390,6 +398,8 @@ def gemm_native(a, b, *, out=None, alpha=1.0, bias=None, lora_h=None, lora_b=Non
         g.out2, g.ldc2 = out2.data_ptr(), out2.stride(0)
     g.force_bn = force_bn
     g.b_mn = 1 if b_mn else 0
+    g.a_mn = 1 if a_mn else 0
+    g.glu = int(glu)
     g.pdl = 1 if (pdl and lora_h is not None and gather is None) else 0
     if gather is not None:
         g.n_copy, g.n_jobs = gather["n_copy"], gather["n_jobs"]
@@ -410,14 +420,16 @@ def gemm_native(a, b, *, out=None, alpha=1.0, bias=None, lora_h=None, lora_b=Non
             g.scatter_out[i] = ptr_
         if scatter.get("rowsq") is not None:
             g.rowsq, g.rowsq_parts = scatter["rowsq"].data_ptr(), scatter["rowsq"].shape[0]
-    if _GEMM_PAIR and (gather is None or _GATHER_PAIR) and scatter is None and force_bn in (0, 256) \
-            and M >= 256 and Nn >= 256:
+    if (_GEMM_PAIR or a_mn or glu) and (gather is None or _GATHER_PAIR) and (scatter is None or _SCATTER_PAIR) \
+            and force_bn in (0, 256) and M >= 256 and Nn >= 256:
         # two-CTA 256x256 tiles; in gather mode with whole copy clusters in front (answers -30 when
         # the gather plan does not line up with pair tiles, and the one-CTA kernel takes over)
         code = lib.eri_gemm2_bf16(g, N.stream_ptr())
         if code != -30:
             N.check(code, "gemm2_bf16")
             return out
+    if a_mn or glu:
+        raise ValueError(f"gemm_native: a_mn / glu need the two-CTA kernel's shape range (M={M}, N={Nn}, K={K})")
     code = lib.eri_gemm_bf16(g, N.stream_ptr())
     N.check(code, "gemm_bf16")
     return out
@@ -470,7 +482,7 @@ def kernel_error_check() -> dict:
     family's bounded waits ran out, and cleared by the read). Empty dict = clean."""
     lib = N.require()
     out = {}
-    for name in ("gemm", "gemm2", "gemm_skinny", "fa", "fa_bwd", "norm"):
+    for name in ("gemm", "gemm2", "gemm_skinny", "gemm_tokred", "fa", "fa_bwd", "norm"):
         fn = getattr(lib, f"eri_{name}_check_error", None)
         if fn is not None:
             v = fn()
@@ -489,6 +501,57 @@ def _mm(a, b_nk, **kw):
     if kw.get("alpha", 1.0) != 1.0:
         y = y * kw["alpha"]
     return y
+
+
+def _wgrad_ok(*ts) -> bool:
+    return _WGRAD_NATIVE and _BACKEND == "fused" and _GEMM_NATIVE == "native" and all(
+        t.is_cuda and t.dtype == torch.bfloat16 and t.dim() == 2 and t.stride(1) == 1
+        and t.stride(0) % 8 == 0 and t.data_ptr() % 16 == 0 for t in ts)
+
+
+def wgrad(dy2, x2, accum=None, out=None):
+    """Weight gradient dW[N_out, K_in] = dy2[T, N_out]^T @ x2[T, K_in] on the two-CTA tcgen05 kernel:
+    both activations are read token-major as MN-major operands, so no transposed copy is made.
+    ``accum``: an existing bf16 gradient of that shape; the product is added into it (beta = 1 in the
+    GEMM epilogue) and ``accum`` is returned. ``out``: destination for the plain product. Shapes
+    outside the kernel's range use ``torch``."""
+    T, Nn = dy2.shape
+    K = x2.shape[1]
+    dst = accum if accum is not None else out
+    if _wgrad_ok(dy2, x2) and Nn >= 256 and K >= 256 and T >= 64 and Nn % 8 == 0 and K % 8 == 0 \
+            and (dst is None or _wgrad_ok(dst)):
+        return gemm_native(dy2, x2, a_mn=True, b_mn=True, out=dst, residual=accum)
+    if accum is not None:
+        return accum.addmm_(dy2.t(), x2)
+    if out is not None:
+        return torch.mm(dy2.t(), x2, out=out)
+    return dy2.t() @ x2
+
+
+def lora_wgrad(a_tok, b_tok, out=None, transpose_out=False, accumulate=False):
+    """Skinny token reduction ``a_tok[T, Mg]^T @ b_tok[T, r]`` (r = adapter rank) for the LoRA
+    gradients: dB[N_out, r] = dY^T H, and with ``transpose_out`` dA[r, K_in] = (X^T Ts)^T. Split over
+    the tokens across CTAs on tcgen05; ``accumulate`` adds into ``out``."""
+    T, Mg = a_tok.shape
+    r = b_tok.shape[1]
+    shape = (r, Mg) if transpose_out else (Mg, r)
+    lib = N.lib() if a_tok.is_cuda else None
+    if lib is not None and hasattr(lib, "eri_gemm_tokred") and _wgrad_ok(a_tok) and r in (16, 32, 64) \
+            and b_tok.is_cuda and b_tok.dtype == torch.bfloat16 and b_tok.stride(1) == 1 and b_tok.stride(0) % 8 == 0 \
+            and b_tok.data_ptr() % 16 == 0 and T >= 64 and Mg >= 128 and Mg % 8 == 0 \
+            and (out is None or (out.dtype == torch.bfloat16 and out.stride(1) == 1 and tuple(out.shape) == shape)):
+        if out is None:
+            out, accumulate = torch.empty(shape, dtype=torch.bfloat16, device=a_tok.device), False
+        code = lib.eri_gemm_tokred(a_tok.data_ptr(), a_tok.stride(0), b_tok.data_ptr(), b_tok.stride(0),
+                                   out.data_ptr(), out.stride(0), T, Mg, r, 1.0, 1 if transpose_out else 0,
+                                   1 if accumulate else 0, N.stream_ptr())
+        if code != -100:
+            N.check(code, "gemm_tokred")
+            return out
+    prod = b_tok.t() @ a_tok if transpose_out else a_tok.t() @ b_tok
+    if out is None:
+        return prod
+    return out.add_(prod) if accumulate else out.copy_(prod)
 
 
 _ACCUM_INTO_GRAD = os.environ.get("ERI_B200_ACCUM_INTO_GRAD", "1") == "1"
@@ -547,6 +610,68 @@ def _lora_transposed(m):
     if hit is not None and hit[0] == _LORA_T_EPOCH and hit[1].shape == (m.shape[1], m.shape[0]):
         return hit[1]
     return m.t().contiguous()
+
+
+def _linear_grads(dy2, x2, w, lora_a, lora_b, h, s, wt, need, shp, has_bias, lib):
+    """Gradients of y = x W^T + b + s (x A^T) B^T given dy2 = dL/dy [M, N]: (dx, dw, dbias, da, db).
+    ``need``: five flags in that order. Adapter and weight gradients accumulate straight into the
+    parameters' gradient views when those exist (the returned entry is then None)."""
+    M, K = x2.shape
+    Nn = dy2.shape[1]
+    dx = dw = dbias = da = db = None
+    r = 0 if lora_a is None else lora_a.shape[0]
+    native = lib is not None and _GEMM_NATIVE == "native" and gemm_supported(M, K, Nn)
+    ts = None
+    la_t = None
+    if r:
+        # Ts = s * dY B  [M, r]
+        if native and r in (16, 32, 64):
+            # both transposes are looked up first: nothing may launch between Ts and the dX GEMM
+            lb_t, la_t = _lora_transposed(lora_b), _lora_transposed(lora_a)
+            ts = skinny_gemm(dy2, lb_t, alpha=s)
+        else:
+            ts = (dy2 @ lora_b) * s
+    if need[0]:
+        if native:
+            # dX = dY W: with a cached transpose W^T is a K-major operand, otherwise W itself
+            # is read as the MN-major operand (no copy).
+            b_op, mn = (wt, False) if wt is not None else (w, True)
+            copied = mn and K < 64
+            if copied:
+                b_op, mn = w.t().contiguous(), False       # a launch between Ts and the GEMM
+            if r in (16, 32, 64):
+                dx = gemm_native(dy2, b_op, b_mn=mn, lora_h=ts, lora_b=la_t,
+                                 pdl=_pdl_ok() and not copied)
+            else:
+                dx = gemm_native(dy2, b_op, b_mn=mn)
+                if r:
+                    dx = dx + ts @ lora_a
+        else:
+            dx = dy2 @ w
+            if r:
+                dx = dx + ts @ lora_a
+        dx = dx.view(shp)
+    if need[1]:
+        if _ACCUM_INTO_GRAD and w.grad is not None and w.grad.dtype == x2.dtype and w.grad.is_contiguous():
+            wgrad(dy2, x2, accum=w.grad)       # beta = 1 into the (arena) gradient view
+        else:
+            dw = wgrad(dy2, x2)
+    if has_bias and need[2]:
+        dbias = dy2.sum(0)
+    # Adapter gradients accumulate straight into the parameters' (arena) gradient views with
+    # the GEMM's beta = 1, instead of returning a tensor that autograd adds with one more
+    # launch per parameter.
+    if r and need[3]:
+        if _ACCUM_INTO_GRAD and lora_a.grad is not None and lora_a.grad.dtype == x2.dtype:
+            lora_wgrad(x2, ts, out=lora_a.grad, transpose_out=True, accumulate=True)
+        else:
+            da = lora_wgrad(x2, ts, transpose_out=True)
+    if r and need[4]:
+        if _ACCUM_INTO_GRAD and lora_b.grad is not None and lora_b.grad.dtype == h.dtype:
+            lora_wgrad(dy2, h, out=lora_b.grad, accumulate=True)
+        else:
+            db = lora_wgrad(dy2, h)
+    return dx, dw, dbias, da, db
 
 
 class _FusedLinear(torch.autograd.Function):
@@ -641,56 +766,7 @@ class _FusedLinear(torch.autograd.Function):
                     a = torch.nn.functional.gelu(pf, approximate="tanh") if act == "gelu" \
                         else torch.nn.functional.silu(pf)
                 dy2 = torch.autograd.grad(a, pf, dy2.float())[0].to(dy2.dtype)
-        dx = dw = dbias = da = db = None
-        r = 0 if lora_a is None else lora_a.shape[0]
-        native = lib is not None and _GEMM_NATIVE == "native" and gemm_supported(M, K, Nn)
-        ts = None
-        la_t = None
-        if r:
-            # Ts = s * dY B  [M, r]
-            if native and r in (16, 32, 64):
-                # both transposes are looked up first: nothing may launch between Ts and the dX GEMM
-                lb_t, la_t = _lora_transposed(lora_b), _lora_transposed(lora_a)
-                ts = skinny_gemm(dy2, lb_t, alpha=s)
-            else:
-                ts = (dy2 @ lora_b) * s
-        if need[0]:
-            if native:
-                # dX = dY W: with a cached transpose W^T is a K-major operand, otherwise W itself
-                # is read as the MN-major operand (no copy).
-                b_op, mn = (wt, False) if wt is not None else (w, True)
-                copied = mn and K < 64
-                if copied:
-                    b_op, mn = w.t().contiguous(), False       # a launch between Ts and the GEMM
-                if r in (16, 32, 64):
-                    dx = gemm_native(dy2, b_op, b_mn=mn, lora_h=ts, lora_b=la_t,
-                                     pdl=_pdl_ok() and not copied)
-                else:
-                    dx = gemm_native(dy2, b_op, b_mn=mn)
-                    if r:
-                        dx = dx + ts @ lora_a
-            else:
-                dx = dy2 @ w
-                if r:
-                    dx = dx + ts @ lora_a
-            dx = dx.view(shp)
-        if need[1]:
-            dw = dy2.t() @ x2
-        if has_bias and need[2]:
-            dbias = dy2.sum(0)
-        # Adapter gradients accumulate straight into the parameters' (arena) gradient views with
-        # the GEMM's beta = 1, instead of returning a tensor that autograd adds with one more
-        # launch per parameter.
-        if r and need[3]:
-            if _ACCUM_INTO_GRAD and lora_a.grad is not None and lora_a.grad.dtype == x2.dtype:
-                lora_a.grad.addmm_(ts.t(), x2)
-            else:
-                da = ts.t() @ x2
-        if r and need[4]:
-            if _ACCUM_INTO_GRAD and lora_b.grad is not None and lora_b.grad.dtype == h.dtype:
-                lora_b.grad.addmm_(dy2.t(), h)
-            else:
-                db = dy2.t() @ h
+        dx, dw, dbias, da, db = _linear_grads(dy2, x2, w, lora_a, lora_b, h, s, wt, need, shp, has_bias, lib)
         return dx, dw, dbias, da, db, None, None, d_res, dgate, None
 
 
@@ -708,6 +784,66 @@ def linear(x, w, bias=None, lora=None, act=None, residual=None, gate=None, wt=No
     if gate is not None or residual is not None:
         y = R.gate_residual(residual, y, gate)
     return y
+
+
+_GLU_FUSED = os.environ.get("ERI_B200_GLU_FUSED", "1") == "1"
+_GLU_CODE = {("gelu", False): 1, ("silu", False): 2, ("gelu", True): 3, ("silu", True): 4}
+
+
+class _FusedLinearGlu(torch.autograd.Function):
+    """out[M, hidden] = glu(x W^T + b + s (x A^T) B^T) with W an up-projection [2*hidden, K]: the
+    gate is applied in the GEMM epilogue (each CTA pair holds the value columns next to their gate
+    columns), so the [M, 2*hidden] projection is written once for backward and never re-read in
+    forward. The reference fuses the same pair in its feed-forward kernel
+    (crates/training/src/sdxl/runtime.rs:249-321, host side :698-799)."""
+
+    @staticmethod
+    def forward(ctx, x, w, bias, lora_a, lora_b, lora_scale, code, wt):
+        shp = x.shape
+        K = shp[-1]
+        x2 = _c(x).view(-1, K)
+        M, N2 = x2.shape[0], w.shape[0]
+        r = 0 if lora_a is None else lora_a.shape[0]
+        need_pre = any(ctx.needs_input_grad[:5])
+        pre = torch.empty(M, N2, dtype=x.dtype, device=x.device) if need_pre else None
+        h = skinny_gemm(x2, lora_a, alpha=lora_scale) if r else None
+        out = gemm_native(x2, w, bias=bias, lora_h=h, lora_b=lora_b if r else None, glu=code,
+                          pre_out=pre, pdl=_pdl_ok())
+        ctx.save_for_backward(x2, w, lora_a, lora_b, h, pre, wt)
+        ctx.meta = (shp, N2, lora_scale, code, bias is not None)
+        return out.view(*shp[:-1], N2 // 2)
+
+    @staticmethod
+    def backward(ctx, dout):
+        x2, w, lora_a, lora_b, h, pre, wt = ctx.saved_tensors
+        shp, N2, s, code, has_bias = ctx.meta
+        M = x2.shape[0]
+        lib = N.require()
+        d2 = _c(dout).view(M, N2 // 2)
+        dh = torch.empty(M, N2, dtype=x2.dtype, device=x2.device)
+        N.check(lib.eri_glu_bwd(d2.data_ptr(), pre.data_ptr(), dh.data_ptr(), M, N2 // 2,
+                                0 if code in (1, 3) else 1, 1 if code >= 3 else 0, N.stream_ptr()), "glu_bwd")
+        dx, dw, dbias, da, db = _linear_grads(dh, x2, w, lora_a, lora_b, h, s, wt, ctx.needs_input_grad,
+                                              shp, has_bias, lib)
+        return dx, dw, dbias, da, db, None, None, None
+
+
+def linear_glu(x, lin, mode="gelu", act_first=True):
+    """``glu(lin(x), mode, act_first)`` for an up-projection module ``lin`` ([2*hidden, K] weight).
+    One GEMM launch with the gate in its epilogue when the shape fits the two-CTA kernel and the
+    adapter (if any) is a plain LoRA; otherwise the projection and the gate run as separate ops."""
+    ad = getattr(lin, "adapter", None)
+    w, b = lin.weight, lin.bias
+    rows = x.numel() // x.shape[-1]
+    plain_lora = ad is not None and getattr(ad, "kind", "") == "lora" and ad.rank in (16, 32, 64) \
+        and not (ad.dropout > 0 and ad.training)
+    if _GLU_FUSED and _GEMM_NATIVE == "native" and _native_ok(x, w, b) and (ad is None or plain_lora) \
+            and type(lin).__name__ == "Linear" and rows >= 256 and w.shape[0] >= 256 and w.shape[0] % 16 == 0 \
+            and x.shape[-1] % 8 == 0 and x.shape[-1] >= 64:
+        wt = lin.frozen_transpose() if torch.is_grad_enabled() else None
+        a, bb, s = (ad.lora_A, ad.lora_B, float(ad.scale)) if ad is not None else (None, None, 1.0)
+        return _FusedLinearGlu.apply(x, w, b, a, bb, s, _GLU_CODE[(mode, bool(act_first))], wt)
+    return glu(lin(x), mode, act_first)
 
 
 class _SmallLinear(torch.autograd.Function):
@@ -764,10 +900,11 @@ _ATTN_ENV_POLICY = any(os.environ.get(k) for k in ("ATTN_Q_CHUNK", "ATTN_KV_CHUN
 def attention(q, k, v, scale=None, mask=None, out=None):
     """Non-causal attention over token-major [B, L, H, Dh] tensors. ``out``: optional destination
     buffer for the native kernel (ignored by the library path, which returns its own tensor)."""
-    if _ATTN_NATIVE == "native" and mask is None and _native_ok(q, k, v):
+    if _ATTN_NATIVE == "native" and _native_ok(q, k, v):
         from . import flash_attn as FA
-        if FA.supported(q, k, v):
-            return FA.flash_attention(q, k, v, scale, out)
+        # key-only masks (text padding, [B, 1, 1, T]) ride on the native kernel as a per-key bias
+        if FA.supported(q, k, v) and (mask is None or FA.mask_is_key_only(mask, q.shape[0], k.shape[1])):
+            return FA.flash_attention(q, k, v, scale, out, mask)
     if mask is None and _ATTN_ENV_POLICY:
         from ..utils.env_flags import library_attention
         o = library_attention(q, k, v, scale)

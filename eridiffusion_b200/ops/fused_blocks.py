@@ -77,8 +77,8 @@ class _SingleStream(torch.autograd.Function):
         ts2 = F.skinny_gemm(g, bb2_t, alpha=s2) if a2 is not None else None
         F.gemm_native(g, w2, b_mn=True, lora_h=ts2, lora_b=a2_t,
                       out=d_attn, n_split=D, out2=d_h[:, 3 * D:], act="gelu_bwd", pre_in=pre, pdl=F._pdl_ok())
-        da2 = (ts2.t() @ cat) if (a2 is not None and need[10]) else None
-        db2 = (g.t() @ h2) if (a2 is not None and need[11]) else None
+        da2 = F.lora_wgrad(cat, ts2, transpose_out=True) if (a2 is not None and need[10]) else None
+        db2 = F.lora_wgrad(g, h2) if (a2 is not None and need[11]) else None
         dq, dk, dv = FA.bwd(d_attn.view(B, L, heads, Dh), q, k, v, o, lse)
         f32 = dict(dtype=torch.float32, device=dev)
         dqs = torch.zeros(Dh, **f32) if (qs is not None and need[13]) else None
@@ -91,10 +91,10 @@ class _SingleStream(torch.autograd.Function):
         dxm = None
         if need[0]:
             dxm = F.gemm_native(d_h, w1, b_mn=True, lora_h=ts1, lora_b=a1_t, pdl=F._pdl_ok()).view(B, L, D)
-        da1 = (ts1.t() @ xm2) if (a1 is not None and need[7]) else None
-        db1 = (d_h.t() @ h1) if (a1 is not None and need[8]) else None
-        dw1 = (d_h.t() @ xm2) if need[3] else None
-        dw2 = (g.t() @ cat) if need[5] else None
+        da1 = F.lora_wgrad(xm2, ts1, transpose_out=True) if (a1 is not None and need[7]) else None
+        db1 = F.lora_wgrad(d_h, h1) if (a1 is not None and need[8]) else None
+        dw1 = F.wgrad(d_h, xm2) if need[3] else None
+        dw2 = F.wgrad(g, cat) if need[5] else None
         dgate = None
         if need[2]:
             raise NotImplementedError("trainable modulation uses the unfused single-stream path")

@@ -64,8 +64,18 @@ class GatherPlan:
         Nn, K = landing.shape
         assert Nn % world == 0
         per = Nn // world
-        if per % flag_rows or flag_rows % rows_per_job:
-            flag_rows = per
+        # A slab that is not a multiple of 256 rows (9216 / 8 = 1152, 3072 / 8 = 384) keeps counters
+        # INSIDE the slab at the largest granule that divides it; one counter per whole slab would
+        # hold every tile of a slab back until its last byte has landed.
+        for cand in (flag_rows, 128, 64):
+            if per % cand == 0 and cand % rows_per_job == 0:
+                flag_rows = cand
+                break
+        else:
+            if per % rows_per_job == 0 and per >= rows_per_job:
+                flag_rows = rows_per_job
+            else:
+                flag_rows = per
         pl = cls(rank, world, n_copy, landing.device, n_flags=Nn // flag_rows)
         rb = K * landing.element_size()
         # interleave peers so that every slab makes progress; own slab first
@@ -77,10 +87,13 @@ class GatherPlan:
                 pl._add(shard_ptrs[p] + r0 * rb, landing.data_ptr() + (p * per + r0) * landing.stride(0) * landing.element_size(),
                         nr, rb, rb, landing.stride(0) * landing.element_size(), (p * per + r0) // flag_rows, remote=p != rank)
             r0 += nr
+        # The rotation only says where the tile / K order starts (at this rank's own slab); it is
+        # rounded down to whole 256-column pair tiles / 64-wide K blocks so that the two-CTA kernel
+        # accepts the plan on every rank, whatever the slab size.
         if along_k:
-            pl.kw = dict(a_flag_cols=flag_rows, rot_k_cols=rank * per)
+            pl.kw = dict(a_flag_cols=flag_rows, rot_k_cols=(rank * per) // 64 * 64)
         else:
-            pl.kw = dict(b_flag_rows=flag_rows, rot_n_rows=rank * per)
+            pl.kw = dict(b_flag_rows=flag_rows, rot_n_rows=(rank * per) // 256 * 256)
         # whole slabs in the same order, for the copy-engine variant of the gather
         sb = per * rb
         pl.slabs = [(shard_ptrs[p], landing.data_ptr() + p * per * landing.stride(0) * landing.element_size(), sb,

@@ -134,7 +134,7 @@ class _Zero3LinearFn(torch.autograd.Function):
         if ctx.needs_input_grad[1]:
             per = n_out // z3.world
             stage = z3.stage.local[: n_out * K].view(n_out, K)
-            torch.mm(dy2.t(), x2, out=stage)
+            F.wgrad(dy2, x2, out=stage)
             if z3.world > 1:
                 dshard = torch.empty(per, K, dtype=dy2.dtype, device=dy2.device)
                 z3.comm.collective("reduce_scatter", z3.stage, dst=dshard, count=per * K, avg=True)

@@ -31,14 +31,35 @@ def test_rows_plan_counters_and_local_slab():
     assert args["n_jobs"] == len(pl.jobs) and args["local"]["n_jobs"] == len(pl.jobs_nl) and args["local"]["mode"] == 1
 
 
-def test_rows_plan_along_k_and_coarse_flags():
+def test_rows_plan_along_k_keeps_counters_inside_an_unaligned_slab():
     W, rank, Nn, K = 8, 5, 9216, 256
     landing = torch.empty(Nn, K, dtype=torch.bfloat16)
-    per = Nn // W                                  # 1152 rows: not a multiple of 256 -> one counter per slab
+    per = Nn // W                                  # 1152 rows: not a multiple of 256 -> 128-row counters
     pl = GatherPlan.rows(rank, W, _ptrs(W, per * K * 2), landing, along_k=True, n_copy=16)
-    assert len(pl.flags) == W and pl.kw == dict(a_flag_cols=per, rot_k_cols=rank * per)
-    assert pl.targets == [per // 64] * W
-    assert pl.targets_nl[rank] == 0 and pl.local["mode"] == 2
+    assert len(pl.flags) == Nn // 128 and pl.kw == dict(a_flag_cols=128, rot_k_cols=rank * per)
+    assert pl.targets == [2] * (Nn // 128)         # two 64-row jobs per counter
+    own = range(rank * per // 128, (rank + 1) * per // 128)
+    assert all(pl.targets_nl[f] == 0 for f in own) and pl.local["mode"] == 2
+
+
+def test_rows_plan_rotation_is_a_whole_pair_tile_on_every_rank():
+    # the two shapes whose slabs are not multiples of 256 rows at 8 ranks
+    for Nn in (9216, 3072):
+        W, K = 8, 128
+        per = Nn // W
+        landing = torch.empty(Nn, K, dtype=torch.bfloat16)
+        for rank in range(W):
+            pl = GatherPlan.rows(rank, W, _ptrs(W, per * K * 2), landing, n_copy=16)
+            assert pl.kw["b_flag_rows"] == 128 and pl.kw["rot_n_rows"] % 256 == 0
+            assert pl.kw["rot_n_rows"] <= rank * per < pl.kw["rot_n_rows"] + 256
+            assert pl.local["lo"] % 128 == 0 and pl.local["hi"] % 128 == 0
+            # every counter is bumped by exactly the jobs that cover its rows
+            rows_per_flag = [0] * len(pl.flags)
+            for j in pl.jobs:
+                rows_per_flag[j.flag] += j.rows
+            assert rows_per_flag == [128] * (Nn // 128)
+            pk = GatherPlan.rows(rank, W, _ptrs(W, per * K * 2), landing, along_k=True, n_copy=16)
+            assert pk.kw["rot_k_cols"] % 64 == 0 and pk.kw["a_flag_cols"] % 64 == 0
 
 
 def test_cols_plan_row_groups_and_local_block():

@@ -76,3 +76,85 @@ def test_flash_attention_into_caller_buffer():
     with pytest.raises(ValueError):
         F.attention(q, k, v, out=buf[:, :128])
     assert FA.check_error() == 0
+
+
+def _ref_masked(q, k, v, bias):
+    """fp32 softmax(QK^T / sqrt(D) + bias[b, key]) V with autograd, bias [B, Lk] additive."""
+    D = q.shape[-1]
+    s = torch.einsum("blhd,bmhd->bhlm", q, k) / math.sqrt(D) + bias[:, None, None, :]
+    return torch.einsum("bhlm,bmhd->blhd", torch.softmax(s, -1), v)
+
+
+@pytest.mark.parametrize("B,H,Lq,Lk,D", [(2, 2, 256, 384, 128), (2, 3, 200, 333, 64), (1, 2, 640, 640, 128)])
+@pytest.mark.parametrize("kind", ["bool", "additive"])
+def test_flash_key_padding_mask_fwd_bwd(B, H, Lq, Lk, D, kind):
+    """Text-padding style key masks ([B, 1, 1, Lk]): per-sample valid prefixes in the middle of a joint
+    sequence, forward and all three gradients against fp32; masked keys get zero gradient."""
+    from eridiffusion_b200.ops import functional as F
+    q, k, v = (mk(B, L, H, D, s).requires_grad_() for L, s in ((Lq, 1), (Lk, 2), (Lk, 3)))
+    do = mk(B, Lq, H, D, 4)
+    # keys [lo_b, 96) are padding (a whole first tile stays partly visible; for the last sample a
+    # 128-key tile is masked completely when Lk allows it)
+    visible = torch.ones(B, Lk, dtype=torch.bool, device="cuda")
+    for b in range(B):
+        visible[b, 17 + 31 * b:96] = False
+    if Lk >= 384:
+        visible[B - 1, 128:256] = False
+    if kind == "bool":
+        mask = visible[:, None, None, :]
+    else:
+        mask = torch.where(visible, 0.0, float("-inf"))[:, None, None, :]
+        mask = mask + 0.25 * torch.randn(B, 1, 1, Lk, device="cuda") * visible[:, None, None, :]
+    out = F.attention(q, k, v, mask=mask)
+    gq, gk, gv = torch.autograd.grad(out, (q, k, v), do)
+    assert FA.check_error() == 0
+    bias = torch.where(visible, 0.0, -1e30) if kind == "bool" else mask.reshape(B, Lk).clamp_min(-1e30)
+    qf, kf, vf = (t.detach().float().requires_grad_() for t in (q, k, v))
+    ref = _ref_masked(qf, kf, vf, bias.float())
+    ref.backward(do.float())
+    assert (out.float() - ref).abs().max().item() < 2e-2
+    for a, b_, n in ((gq, qf.grad, "dq"), (gk, kf.grad, "dk"), (gv, vf.grad, "dv")):
+        err = (a.float() - b_).abs().max().item()
+        assert err < 0.02 * b_.abs().max().item() + 2e-2, (n, err)
+    hidden = ~visible
+    assert gk.float()[hidden].abs().max().item() == 0.0 and gv.float()[hidden].abs().max().item() == 0.0
+
+
+@pytest.mark.parametrize("B,H,Lq,Lk,D", [(2, 10, 1024, 77, 64), (1, 20, 256, 77, 64), (1, 2, 200, 1, 128),
+                                         (1, 4, 130, 127, 128)])
+def test_flash_short_keys_cross_attention(B, H, Lq, Lk, D):
+    """Fewer than 128 keys (SDXL cross-attention over 77 text tokens) stay on the native kernels."""
+    from eridiffusion_b200.ops import functional as F
+    q, k, v = (mk(B, L, H, D, s).requires_grad_() for L, s in ((Lq, 1), (Lk, 2), (Lk, 3)))
+    do = mk(B, Lq, H, D, 4)
+    c0 = F.N.launch_count()
+    out = F.attention(q, k, v)
+    assert F.N.launch_count() > c0, "short-key attention left the native path"
+    gq, gk, gv = torch.autograd.grad(out, (q, k, v), do)
+    assert FA.check_error() == 0
+    qf, kf, vf = (t.detach().float().requires_grad_() for t in (q, k, v))
+    ref = R.attention_fp32(qf, kf, vf)
+    ref.backward(do.float())
+    assert (out.float() - ref).abs().max().item() < 2e-2
+    for a, b_, n in ((gq, qf.grad, "dq"), (gk, kf.grad, "dk"), (gv, vf.grad, "dv")):
+        err = (a.float() - b_).abs().max().item()
+        assert err < 0.02 * b_.abs().max().item() + 2e-2, (n, err)
+
+
+def test_flash_headline_shape_against_fp32():
+    """The benchmark's attention call (B1, 4608 tokens, 24 heads of 128): 36 key tiles per query tile,
+    forward and backward against fp32, head by head to bound the reference's memory."""
+    B, L, H, D = 1, 4608, 24, 128
+    q, k, v, do = (mk(B, L, H, D, s) for s in (1, 2, 3, 4))
+    out, lse = FA.fwd(q, k, v)
+    dq, dk, dv = FA.bwd(do, q, k, v, out, lse)
+    assert FA.check_error() == 0
+    worst = {}
+    for h in range(0, H, 5):
+        qf, kf, vf = (t[:, :, h:h + 1].float().requires_grad_() for t in (q, k, v))
+        ref = R.attention_fp32(qf, kf, vf)
+        ref.backward(do[:, :, h:h + 1].float())
+        for name, got, want in (("out", out, ref.detach()), ("dq", dq, qf.grad), ("dk", dk, kf.grad), ("dv", dv, vf.grad)):
+            rel = (got[:, :, h:h + 1].float() - want).abs().max().item() / want.abs().max().item()
+            worst[name] = max(worst.get(name, 0.0), rel)
+    assert worst["out"] < 1.5e-2 and worst["dq"] < 2.5e-2 and worst["dk"] < 2.5e-2 and worst["dv"] < 2.5e-2, worst

@@ -91,3 +91,59 @@ def test_scatter_epilogue_routes_head_groups():
         got = dests[d].view(B, W, Ll, 3, group)
         close(got[:, rank], y[:, :, :, d], 0.05)
         assert got[:, 1 - rank].abs().max().item() == 0.0
+
+
+@pytest.mark.parametrize("N,K", [(9216, 256), (3072, 512)])
+def test_gather_rows_unaligned_slabs_stay_on_the_pair_kernel(N, K):
+    """Eight ranks with slabs of 1152 / 384 rows (not multiples of the 256-column pair tile): every
+    emulated rank must run on the two-CTA kernel, forward and input-gradient direction."""
+    W, M = 8, 512
+    lib = F.N.require()
+    x = rnd(M, K)
+    dy = rnd(M, N, seed=3)
+    shards = [rnd(N // W, K, seed=10 + p, scale=K ** -0.5) for p in range(W)]
+    w = torch.cat(shards, 0)
+    ref_y = x.float() @ w.float().t()
+    ref_dx = dy.float() @ w.float()
+    for rank in range(W):
+        landing = torch.full((N, K), float("nan"), device=DEV, dtype=torch.bfloat16)
+        plan = GatherPlan.rows(rank, W, [s.data_ptr() for s in shards], landing, n_copy=4)
+        c0 = lib.eri_gemm2_gather_count()
+        out = F.gemm_native(x, landing, gather=plan.launch_args())
+        assert lib.eri_gemm2_gather_count() == c0 + 1, f"rank {rank} fell back to the one-CTA kernel"
+        assert F.gemm_error_check() == 0
+        close(out, ref_y, 0.05)
+        landing.fill_(float("nan"))
+        plan = GatherPlan.rows(rank, W, [s.data_ptr() for s in shards], landing, along_k=True, n_copy=4)
+        c0 = lib.eri_gemm2_gather_count()
+        dx = F.gemm_native(dy, landing, b_mn=True, gather=plan.launch_args())
+        assert lib.eri_gemm2_gather_count() == c0 + 1, f"rank {rank} (dX) fell back to the one-CTA kernel"
+        assert F.gemm_error_check() == 0
+        close(dx, ref_dx, 0.05 * (N / 1024) ** 0.5)
+
+
+@pytest.mark.parametrize("pair", [True, False])
+def test_scatter_epilogue_pair_tiles_and_row_squares(pair, monkeypatch):
+    """Head groups of 512 columns (whole 256-column pair tiles): the scatter epilogue of the two-CTA
+    kernel against the one-CTA kernel and the fp32 statement, with the QK-norm row sums."""
+    monkeypatch.setattr(F, "_SCATTER_PAIR", pair)
+    W, rank, B, Ll, H, Dh, K = 2, 1, 1, 384, 8, 128, 320
+    part = H * Dh                  # 1024 columns per q / k / v part
+    group = part // W              # 512 columns per rank
+    x = rnd(B * Ll, K)
+    wqkv = rnd(3 * part, K, seed=1, scale=K ** -0.5)
+    bias = rnd(3 * part, seed=2)
+    dests = [torch.zeros(B * W * Ll, 3 * group, device=DEV, dtype=torch.bfloat16) for _ in range(W)]
+    rowsq = torch.zeros(2, B * Ll, device=DEV, dtype=torch.float32)
+    F.gemm_native(x, wqkv, bias=bias, out=dests[0],
+                  scatter=dict(world=W, rank=rank, part_cols=part, group_cols=group, local_rows=Ll,
+                               ptrs=[d.data_ptr() for d in dests], rowsq=rowsq))
+    assert F.gemm_error_check() == 0
+    yf = x.float() @ wqkv.float().t() + bias.float()
+    y = yf.view(B, Ll, 3, W, group)
+    for d in range(W):
+        got = dests[d].view(B, W, Ll, 3, group)
+        close(got[:, rank], y[:, :, :, d], 0.05)
+        assert got[:, 1 - rank].abs().max().item() == 0.0
+    want_sq = yf.view(B * Ll, 3, part)[:, :2].pow(2).sum(-1).t()
+    assert torch.allclose(rowsq, want_sq, rtol=2e-2, atol=1e-2)

@@ -53,7 +53,10 @@ def _run_noalloc(lib, do, q, k, v, out, lse):
 def test_noalloc_backward_matches_regular_entry_point_twice():
     from eridiffusion_b200.ops import flash_attn as FA
     lib = _lib()
-    for call, (B, H, Lq, Lk, D) in enumerate([(1, 2, 384, 256, 128), (2, 3, 256, 320, 64)]):
+    # The third call has a query length that is not a multiple of 128 and follows larger calls: its
+    # padded rows of the shared scratch still hold the earlier calls' values unless the kernel
+    # rewrites them, which is the one place where leftovers could leak into a result.
+    for call, (B, H, Lq, Lk, D) in enumerate([(1, 2, 384, 256, 128), (2, 3, 256, 320, 64), (1, 2, 200, 256, 128)]):
         q, k, v = _mk(B, Lq, H, D, 10 + call), _mk(B, Lk, H, D, 20 + call), _mk(B, Lk, H, D, 30 + call)
         do = _mk(B, Lq, H, D, 40 + call)
         out, lse = FA.fwd(q, k, v)
@@ -62,8 +65,8 @@ def test_noalloc_backward_matches_regular_entry_point_twice():
         torch.cuda.synchronize()
         assert lib.eri_flash_attn_bwd_noalloc_status() == 0
         for a, b in zip(got, ref):
-            # same kernels, same inputs: the results agree to the tolerance of the numerics tests
-            assert (a.float() - b.float()).abs().max().item() <= 2e-2 * max(1.0, b.float().abs().max().item())
+            # the same kernels on the same inputs, only the scratch lives elsewhere: bit-equal
+            assert torch.equal(a, b), (call, (a.float() - b.float()).abs().max().item())
 
 
 def test_noalloc_rejects_oversized_problem():
