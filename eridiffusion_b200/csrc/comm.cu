@@ -203,11 +203,16 @@ fused_dp_step_kernel(CommCtx c, FusedDpArgs a) {
   }
   if (blockIdx.x == 0 && threadIdx.x == 0 && a.grad_norm_out) *a.grad_norm_out = sqrtf(total);
   const bool finite = isfinite(total);
+  // A bounded wait of this launch (or of an earlier one that the host has not read yet) ran out:
+  // the reduced gradient may be partial. The word was written before the grid-wide sync that ends
+  // cross_barrier, so every thread of the grid reads the same value and the whole grid skips the
+  // update: parameters and optimizer state stay as they were and nothing is pushed to the peers.
+  const bool comm_ok = *reinterpret_cast<volatile int*>(c.err) == 0;
   float gs = 1.f;
   if (a.max_grad_norm > 0.f) gs = fminf(1.f, a.max_grad_norm / (sqrtf(total) + 1e-6f));
 
   // phase 3: 8-bit AdamW on the shard, push new parameters to every rank
-  if (finite) {
+  if (finite && comm_ok) {
     for (long long blk = gwarp; blk < nblocks; blk += warps) {
       const long long e = blk * kBlock + lane * 8;
       float p[8], g[8], m[8], v[8];

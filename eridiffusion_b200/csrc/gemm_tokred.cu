@@ -13,9 +13,11 @@
 // (no transposed copy exists anywhere): the A tile is two 64-column slabs of 64 token rows, the B
 // tile one slab whose columns beyond r are zero-filled by the TMA unit (box wider than the tensor),
 // so the instruction always runs with N = 64. The token dimension is split across CTAs
-// (grid = Mg / 128 tiles x splits); partial sums meet in an fp32 workspace through global
-// reductions and the last CTA of a tile converts, optionally adds the existing gradient (beta = 1),
-// writes bf16 and clears the workspace for the next call. One launch per gradient.
+// (grid = Mg / 128 tiles x splits); every CTA stores its partial tile into its own slot of an fp32
+// workspace (plain coalesced stores, no atomics) and the last CTA of a tile (an arrival counter)
+// adds the slots in split order, optionally adds the existing gradient (beta = 1) and writes bf16.
+// The summation order is fixed, so the result is bit-reproducible run to run. One launch per
+// gradient.
 //
 // The workspace is one buffer per device shared by all calls: calls whose GPU work may overlap
 // (different streams) must not use this entry point concurrently.
@@ -41,7 +43,7 @@ struct TokredParams {
   int accumulate;      // 1: out += result
   float alpha;
   bf16* out;
-  float* ws;           // [m_tiles * 128, 64] fp32 partial sums (zero between calls)
+  float* ws;           // [m_tiles][splits][r][128] fp32 partial tiles (every slot is rewritten per call)
   int* counters;       // [m_tiles] arrivals (zero between calls)
   int* err;
 };
@@ -136,11 +138,14 @@ gemm_tokred_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
 #pragma unroll
       for (int j = 0; j < BN; ++j) acc[j] = 0.f;
     }
-    float* wrow = p.ws + ((size_t)m_tile * BM + r_in) * BN;
+    // slot of (tile, split): [r][128] floats, lanes along the row index -> coalesced
+    const size_t slot_elems = (size_t)p.r * BM;
+    float* tile_ws = p.ws + (size_t)m_tile * p.splits * slot_elems;
     if (p.splits > 1) {
+      float* mine = tile_ws + (size_t)split * slot_elems + r_in;
 #pragma unroll
       for (int j = 0; j < BN; ++j)
-        if (j < p.r) atomicAdd(wrow + j, acc[j]);
+        if (j < p.r) __stcg(mine + (size_t)j * BM, acc[j]);
       __threadfence();
       asm volatile("bar.sync 1, 128;" ::: "memory");
       if (threadIdx.x == 64) *s_last = (atomicAdd(p.counters + m_tile, 1) == p.splits - 1) ? 1 : 0;
@@ -150,11 +155,13 @@ gemm_tokred_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
       if (p.splits > 1) {
         __threadfence();
 #pragma unroll
-        for (int j = 0; j < BN; ++j)
-          if (j < p.r) {
-            acc[j] = __ldcg(wrow + j);
-            wrow[j] = 0.f;
-          }
+        for (int j = 0; j < BN; ++j) acc[j] = 0.f;
+        for (int sp = 0; sp < p.splits; ++sp) {
+          const float* src = tile_ws + (size_t)sp * slot_elems + r_in;
+#pragma unroll
+          for (int j = 0; j < BN; ++j)
+            if (j < p.r) acc[j] += __ldcg(src + (size_t)j * BM);
+        }
         if (threadIdx.x == 64) p.counters[m_tile] = 0;
       }
       if (row < p.Mg) {
@@ -200,7 +207,7 @@ struct TokredState {
   float* ws = nullptr;
   int* counters = nullptr;
   int* err = nullptr;
-  long long ws_rows = 0;
+  long long ws_elems = 0;
   int n_counters = 0;
   bool configured = false;
   int sms = 0;
@@ -252,9 +259,9 @@ int eri_gemm_tokred(const void* a, long long lda, const void* b, long long ldb, 
   }
   const int m_tiles = (Mg + BM - 1) / BM;
   const int ksteps = (T + BK - 1) / BK;
-  // Two CTAs are resident per SM; aim at two rounds of them so that the uneven last round is short,
-  // with at least four K steps per CTA to pay for its prologue and reduction.
-  const int target = g_tokred_target > 0 ? g_tokred_target : 4 * s.sms;
+  // About one CTA per SM measured best (every extra split adds a partial tile to store and re-read);
+  // at least four K steps per CTA pay for its prologue.
+  const int target = g_tokred_target > 0 ? g_tokred_target : s.sms;
   int splits = (target + m_tiles / 2) / m_tiles;
   if (splits > ksteps / 4) splits = ksteps / 4;
   if (splits < 1) splits = 1;
@@ -263,18 +270,17 @@ int eri_gemm_tokred(const void* a, long long lda, const void* b, long long ldb, 
     if (cudaMalloc(&s.err, sizeof(int)) != cudaSuccess) return -3;
     cudaMemsetAsync(s.err, 0, sizeof(int), st);
   }
-  const long long rows = (long long)m_tiles * BM;
-  if (rows > s.ws_rows || m_tiles > s.n_counters) {
-    // grow the workspace (rare: first call and larger Mg); the old buffers are released only
+  const long long need = splits > 1 ? (long long)m_tiles * splits * r * BM : 0;
+  if (need > s.ws_elems || m_tiles > s.n_counters) {
+    // grow the workspace (rare: first call and larger problems); the old buffers are released only
     // after the stream has drained, since earlier launches may still use them
     cudaStreamSynchronize(st);
     if (s.ws) cudaFree(s.ws);
     if (s.counters) cudaFree(s.counters);
-    s.ws_rows = rows > 32768 ? rows : 32768;
-    s.n_counters = (int)(s.ws_rows / BM);
-    if (cudaMalloc(&s.ws, (size_t)s.ws_rows * BN * sizeof(float)) != cudaSuccess) return -3;
+    s.ws_elems = need > (8ll << 20) ? need : (8ll << 20);
+    s.n_counters = m_tiles > 4096 ? m_tiles : 4096;
+    if (cudaMalloc(&s.ws, (size_t)s.ws_elems * sizeof(float)) != cudaSuccess) return -3;
     if (cudaMalloc(&s.counters, (size_t)s.n_counters * sizeof(int)) != cudaSuccess) return -3;
-    cudaMemsetAsync(s.ws, 0, (size_t)s.ws_rows * BN * sizeof(float), st);
     cudaMemsetAsync(s.counters, 0, (size_t)s.n_counters * sizeof(int), st);
   }
   CUtensorMap ta, tb;

@@ -51,15 +51,66 @@ _KLEIN_RENAMES = [
 ]
 # parameters a family's checkpoints never carry: zero-filled instead of reported missing
 _ZERO_IF_MISSING = {"klein": re.compile(r"\.bias$")}
-# tensors of a checkpoint that the model computes instead of storing
-_COMPUTED_KEYS = {"sd35": {"pos_embed"}, "sd3": {"pos_embed"}}
+# tensors of a checkpoint that the model computes instead of storing (none at present: the SD3
+# ``pos_embed`` table is loaded into the model's buffer when the model keeps one)
+_COMPUTED_KEYS = {}
+
+
+def sd3_final_rows_to_model(t, out_channels, patch=2):
+    """SD3 files order the rows of ``final_layer.linear`` (and its bias) as (patch row, patch column,
+    channel) — their unpatchify reshapes a token to [p, p, C] (src/models/mmdit_blocks.rs:2280-2288).
+    This package packs and unpacks a token as (channel, patch row, patch column) everywhere, so the
+    rows are permuted once on load."""
+    pp = patch * patch
+    c = out_channels // pp
+    return t.reshape(pp, c, *t.shape[1:]).transpose(0, 1).reshape(t.shape).contiguous()
+
+
+def sd3_final_rows_to_file(t, out_channels, patch=2):
+    """Inverse of ``sd3_final_rows_to_model`` (for exports in the original layout)."""
+    pp = patch * patch
+    c = out_channels // pp
+    return t.reshape(c, pp, *t.shape[1:]).transpose(0, 1).reshape(t.shape).contiguous()
+
+
+def export_sd3_original(model) -> dict:
+    """State dict of an SD3 / SD3.5 model under the ORIGINAL checkpoint names and conventions
+    (``joint_blocks.N.x_block...``, patch-embedding convolution, (p, p, c) final rows, ``pos_embed``
+    as [1, N, D]); the inverse of ``load_model_weights(..., kind="sd35")``."""
+    inv = [
+        (r"\.img_mod\.lin\.", ".x_block.adaLN_modulation.1."), (r"\.txt_mod\.lin\.", ".context_block.adaLN_modulation.1."),
+        (r"\.img_attn2\.", ".x_block.attn2."), (r"\.img_attn\.", ".x_block.attn."), (r"\.txt_attn\.", ".context_block.attn."),
+        (r"\.q_norm\.scale$", ".ln_q.weight"), (r"\.k_norm\.scale$", ".ln_k.weight"),
+        (r"\.img_mlp_0\.", ".x_block.mlp.fc1."), (r"\.img_mlp_2\.", ".x_block.mlp.fc2."),
+        (r"\.txt_mlp_0\.", ".context_block.mlp.fc1."), (r"\.txt_mlp_2\.", ".context_block.mlp.fc2."),
+        (r"^x_embedder\.", "x_embedder.proj."),
+        (r"^(t_embedder|y_embedder)\.in_layer\.", r"\1.mlp.0."), (r"^(t_embedder|y_embedder)\.out_layer\.", r"\1.mlp.2."),
+        (r"^final_layer\.adaLN\.lin\.", "final_layer.adaLN_modulation.1."),
+    ]
+    out = {}
+    oc = model.final_layer.linear.weight.shape[0]
+    items = list(model.named_parameters()) + [(k, b) for k, b in model.named_buffers() if k == "pos_embed"]
+    for k, t in items:
+        t = t.detach()
+        if k.startswith("final_layer.linear."):
+            t = sd3_final_rows_to_file(t, oc)
+        elif k == "x_embedder.weight":
+            c = t.shape[1] // 4
+            t = t.reshape(t.shape[0], c, 2, 2)
+        elif k == "pos_embed":
+            t = t.unsqueeze(0)
+        fk = k
+        for pat, rep in inv:
+            fk = re.sub(pat, rep, fk)
+        out[fk] = t.contiguous()
+    return out
 
 
 def canonical_key(key: str, kind: str) -> str:
     if kind in ("flux", "chroma"):
         for pat, rep in _FLUX_RENAMES:
             key = re.sub(pat, rep, key)
-    elif kind in ("sd3", "sd35"):
+    elif kind in ("sd3", "sd35", "sd35_medium"):
         for pat, rep in _SD35_RENAMES:
             key = re.sub(pat, rep, key)
     elif kind == "klein":
@@ -80,6 +131,9 @@ def load_model_weights(model, path, kind="flux", strict=True, device=None):
     path = Path(path)
     files = sorted(path.glob("*.safetensors")) if path.is_dir() else [path]
     own = dict(model.named_parameters())
+    sd3 = kind in ("sd3", "sd35", "sd35_medium")
+    if sd3 and isinstance(getattr(model, "pos_embed", None), torch.Tensor):
+        own["pos_embed"] = model.pos_embed          # position table buffer: loaded, not recomputed
     used, seen = set(), set()
     if kind == "sdxl":
         # single-file checkpoints in the original layout: remap (and fuse q/k/v) instead of renaming
@@ -128,12 +182,18 @@ def load_model_weights(model, path, kind="flux", strict=True, device=None):
                 ck = canonical_key(k, kind)
                 if ck in _COMPUTED_KEYS.get(kind, ()):
                     continue
+                if sd3 and ck == "pos_embed" and ck not in own:
+                    continue                        # a model without a table computes positions itself
                 seen.add(ck)
                 if ck in own:
                     p = own[ck]
                     t = sf.get(k, device=device or p.device, dtype=p.dtype)
                     if t.dim() == 4 and p.dim() == 2 and t.shape[0] == p.shape[0] and t.numel() == p.numel():
                         t = t.reshape(p.shape)      # patch-embedding convolution [D, C, p, p] -> linear [D, C*p*p]
+                    if sd3 and ck == "pos_embed" and t.dim() == 3:
+                        t = t.reshape(t.shape[1], t.shape[2])
+                    if sd3 and ck.startswith("final_layer.linear."):
+                        t = sd3_final_rows_to_model(t, t.shape[0])
                     if tuple(t.shape) != tuple(p.shape):
                         raise ValueError(f"{k}: shape {tuple(t.shape)} != parameter {tuple(p.shape)}")
                     with torch.no_grad():

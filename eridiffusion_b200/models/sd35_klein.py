@@ -25,13 +25,18 @@ from .mmdit import DoubleStreamBlock, LastLayer, MMDiTConfig, SelfAttentionProj
 from .registry import register_model
 
 
-def sincos_2d(dim, h, w, device=None):
+def sincos_2d(dim, h, w, device=None, top=0, left=0):
+    """SD3 position table for an h x w patch grid whose first patch sits at (top, left) of the full
+    grid: per token ``[emb(column) | emb(row)]`` with ``emb(p) = [sin(p f), cos(p f)]``,
+    ``f_i = 10000^(-i / (dim / 4))`` — the column half comes FIRST, as in the released ``pos_embed``
+    tables and in ``RoPE2D::embed`` (src/models/mmdit_blocks.rs:2107-2136)."""
     def one(d, pos):
         om = 1.0 / (10000 ** (torch.arange(d // 2, dtype=torch.float64, device=device) / (d / 2)))
         out = pos.double().reshape(-1)[:, None] * om[None]
         return torch.cat([torch.sin(out), torch.cos(out)], dim=1)
-    yy, xx = torch.meshgrid(torch.arange(h, device=device), torch.arange(w, device=device), indexing="ij")
-    return torch.cat([one(dim // 2, yy), one(dim // 2, xx)], dim=1).float()
+    yy, xx = torch.meshgrid(torch.arange(top, top + h, device=device),
+                            torch.arange(left, left + w, device=device), indexing="ij")
+    return torch.cat([one(dim // 2, xx), one(dim // 2, yy)], dim=1).float()
 
 
 class SD35JointBlock(nn.Module):
@@ -99,7 +104,7 @@ class SD35JointBlock(nn.Module):
 class SD35MMDiT(nn.Module):
     def __init__(self, hidden=2432, num_heads=38, depth=38, in_channels=64, context_dim=4096,
                  pooled_dim=2048, mlp_ratio=4.0, dtype=torch.bfloat16, device=None,
-                 context_pre_only_last=False, x_self_attn_layers=()):
+                 context_pre_only_last=False, x_self_attn_layers=(), pos_embed_max_size=None):
         super().__init__()
         self.cfg = MMDiTConfig(in_channels=in_channels, hidden=hidden, num_heads=num_heads,
                                depth_double=depth, depth_single=0, mlp_ratio=mlp_ratio,
@@ -120,8 +125,24 @@ class SD35MMDiT(nn.Module):
         self.joint_blocks = nn.ModuleList(block(i) for i in range(depth))
         self.final_layer = LastLayer(D, in_channels, dtype, device)
         self._pos = {}
+        # Released checkpoints carry a ``pos_embed`` table over the largest patch grid (192 x 192 for
+        # SD3.5-large, 384 x 384 for medium); a smaller image uses the CENTRE crop of it. With a
+        # table size the model keeps the table as a buffer (filled with the closed form, replaced by
+        # the file's tensor on load); without one positions start at 0 for every grid.
+        self.pos_embed_max_size = pos_embed_max_size
+        if pos_embed_max_size:
+            m = int(pos_embed_max_size)
+            self.register_buffer("pos_embed", sincos_2d(D, m, m, device).to(dtype), persistent=True)
 
-    def pos_embed(self, h, w, device, dtype):
+    def pos_table(self, h, w, device, dtype):
+        """[h*w, hidden] position rows for an h x w patch grid."""
+        m = self.pos_embed_max_size
+        if m:
+            if h > m or w > m:
+                raise ValueError(f"patch grid {h}x{w} exceeds the position table ({m}x{m})")
+            top, left = (m - h) // 2, (m - w) // 2
+            tab = self.pos_embed.view(m, m, -1)[top:top + h, left:left + w]
+            return tab.reshape(h * w, -1).to(device=device, dtype=dtype)
         key = (h, w, str(device))
         if key not in self._pos:
             self._pos[key] = sincos_2d(self.cfg.hidden, h, w, device).to(dtype)
@@ -134,7 +155,7 @@ class SD35MMDiT(nn.Module):
             grid_hw = (s, Li // s)
         dt = self.x_embedder.weight.dtype
         vec = self.t_embedder(timestep_embedding(t, 256).to(dt)) + self.y_embedder(y.to(dt))
-        x = self.x_embedder(img) + self.pos_embed(grid_hw[0], grid_hw[1], img.device, dt)
+        x = self.x_embedder(img) + self.pos_table(grid_hw[0], grid_hw[1], img.device, dt)
         c = self.context_embedder(txt)
         for blk in self.joint_blocks:
             x, c = blk(x, c, vec, None, None)
@@ -149,6 +170,8 @@ def build_sd35(dtype=torch.bfloat16, device=None, **kw):
     """SD3.5-large layout; as in the released weights the last block's text stream stops after its
     attention (adaLN width 2 x hidden there: crates/models/src/sd35/keymap.rs ``ADA_DIM_LAST_CONTEXT``)."""
     kw.setdefault("context_pre_only_last", True)
+    if kw.get("hidden", 2432) == 2432:
+        kw.setdefault("pos_embed_max_size", 192)
     return SD35MMDiT(dtype=dtype, device=device, **kw)
 
 
@@ -159,6 +182,8 @@ def build_sd35_medium(dtype=torch.bfloat16, device=None, **kw):
     base = dict(hidden=1536, num_heads=24, depth=24, context_pre_only_last=True,
                 x_self_attn_layers=tuple(range(13)))
     base.update(kw)
+    if base["hidden"] == 1536:
+        base.setdefault("pos_embed_max_size", 384)
     return SD35MMDiT(dtype=dtype, device=device, **base)
 
 

@@ -35,6 +35,56 @@ def _rank_world(trainer):
     return (gs.rank, gs.world_size) if gs is not None else (0, 1)
 
 
+def _dist_group(trainer):
+    """(dist module, group) when this trainer runs among several ranks of an initialised process
+    group, else (None, None)."""
+    gs = trainer.grad_sync
+    if gs is None or gs.world_size <= 1:
+        return None, None
+    import torch.distributed as dist
+    if not dist.is_available() or not dist.is_initialized():
+        return None, None
+    return dist, getattr(getattr(gs, "pg", None), "group", None)
+
+
+def _host_barrier(trainer):
+    """All ranks have finished their part of the checkpoint (their optimizer shard is on disk)."""
+    dist, group = _dist_group(trainer)
+    if dist is not None:
+        dist.barrier(group=group)
+
+
+def _gather_objects(trainer, value):
+    """Every rank's ``value``, in rank order (a one-element list in a single-process run)."""
+    dist, group = _dist_group(trainer)
+    if dist is None:
+        return [value]
+    out = [None] * dist.get_world_size(group)
+    dist.all_gather_object(out, value, group=group)
+    return out
+
+
+def _generator_state(trainer):
+    """The timestep generator's state as a list of bytes-as-ints (JSON-friendly), or None."""
+    gen = getattr(trainer, "_gen", None)
+    if gen is None:
+        return None
+    return {"device": str(gen.device), "state": gen.get_state().cpu().tolist()}
+
+
+def _restore_generator(trainer, saved):
+    """Continue the timestep stream where the saved run stopped: without this every resume replays
+    the draws of step 0 (early timesteps oversampled under frequent preemption, and a resumed run
+    is not reproducible against an uninterrupted one)."""
+    if not saved:
+        return
+    try:
+        gen = trainer._generator(torch.device(saved["device"]))
+        gen.set_state(torch.tensor(saved["state"], dtype=torch.uint8))
+    except (RuntimeError, KeyError, TypeError, ValueError):
+        trainer._gen = None          # a state from another device type: fall back to reseeding
+
+
 def _optimizer_tensors(opt):
     sd = opt.state_dict() if hasattr(opt, "state_dict") else {}
     tensors, scalars = {}, {}
@@ -71,9 +121,16 @@ def save_training_checkpoint(trainer, root):
         if tensors:
             st.save_file(tensors, d / f"optimizer.rank{rank}.safetensors",
                          {"step": step, "rank": rank, "world_size": world, **{k: json.dumps(v) for k, v in scalars.items()}})
+        # the timestep generator differs per rank (per sequence-parallel group): one small file each
+        (d / f"rng.rank{rank}.json").write_text(json.dumps({"step": step, "timestep_generator": _generator_state(trainer)}))
+        # meta.json marks the directory complete and older directories are deleted only after EVERY
+        # rank's shard is on disk: a crash before this point leaves no directory that looks whole
+        # and never removes the last good one
+        _host_barrier(trainer)
         if rank == 0:
             (d / "meta.json").write_text(json.dumps(meta, indent=1))
             _cleanup(root, r"step_(\d+)$", cfg.keep_last)
+        _host_barrier(trainer)
         return d
     d = root / f"checkpoint-{step:06d}"
     d.mkdir(parents=True, exist_ok=True)
@@ -84,6 +141,8 @@ def save_training_checkpoint(trainer, root):
     name = "optimizer.safetensors" if world == 1 else f"optimizer.rank{rank}.safetensors"
     if tensors:
         st.save_file(tensors, d / name, {"step": step, "rank": rank, "world_size": world})
+    (d / f"rng.rank{rank}.json").write_text(json.dumps({"step": step, "timestep_generator": _generator_state(trainer)}))
+    _host_barrier(trainer)                  # every shard is written before the directory is marked complete
     if rank == 0:
         (d / "metadata.json").write_text(json.dumps(
             {"step": step, "seed": cfg.seed, "time": time.time(), "world_size": world,
@@ -96,6 +155,7 @@ def save_training_checkpoint(trainer, root):
             latest.symlink_to(d.name)
         except OSError:
             pass
+    _host_barrier(trainer)
     return d
 
 
@@ -127,23 +187,48 @@ def find_checkpoints(root, pattern=r"(?:step_|checkpoint-)(\d+)$"):
     return [p for _, p in found]
 
 
+class _OptimizerStateMismatch(ValueError):
+    """The ranks disagree on whether the optimizer state of a checkpoint could be restored."""
+
+
 def load_latest_training_checkpoint(trainer, root, on_skip=None):
     """Restore parameters (+EMA, + optimizer state when its world size matches) from the newest
-    checkpoint that loads. A checkpoint that is truncated, unreadable or inconsistent (a crash
-    during the write, a damaged shard) is skipped and the one before it is tried; ``on_skip(path,
-    error)`` is told. Returns ``(step, seed)`` or ``None`` when there is nothing to resume from."""
-    for d in find_checkpoints(root):
+    checkpoint that loads ON EVERY RANK. A checkpoint that is truncated, unreadable or inconsistent
+    (a crash during the write, a damaged shard of one rank) is skipped by all ranks together and the
+    one before it is tried; ``on_skip(path, error)`` is told. All ranks walk rank 0's list of
+    directories and exchange their result after each attempt, so they always return the same
+    ``(step, seed)`` — or ``None`` when there is nothing to resume from."""
+    cands = [str(p) for p in find_checkpoints(root)]
+    cands = _gather_objects(trainer, cands)[0]            # one list for everybody: rank 0's
+    for d in map(Path, cands):
+        err, res = None, None
         try:
-            return _load_checkpoint_dir(trainer, d)
+            res = _load_checkpoint_dir(trainer, d)
         except (OSError, ValueError, KeyError, RuntimeError, json.JSONDecodeError, struct.error) as e:
-            if on_skip is not None:
-                on_skip(d, e)
+            err = e
+        states = _gather_objects(trainer, None if err is not None else (res[0], res[1], res[2]))
+        if all(s is not None for s in states):
+            if len({s[2] for s in states}) > 1:
+                # some ranks restored their moments and some could not: training would continue out
+                # of step, so the directory counts as damaged for everyone
+                err = _OptimizerStateMismatch(f"optimizer state restored on ranks "
+                                              f"{[i for i, s in enumerate(states) if s[2]]} only")
+            elif len({(s[0], s[1]) for s in states}) > 1:
+                err = ValueError(f"ranks disagree on (step, seed): {sorted({(s[0], s[1]) for s in states})}")
+            else:
+                return res[0], res[1]
+        if err is None:
+            bad = [i for i, s in enumerate(states) if s is None]
+            err = ValueError(f"checkpoint did not load on ranks {bad}")
+        if on_skip is not None:
+            on_skip(d, err)
     return None
 
 
 def _load_checkpoint_dir(trainer, d):
     rank, world = _rank_world(trainer)
     dev = trainer.arena.data.device
+    opt_restored = False
     if trainer.adapters is not None:
         meta = json.loads((d / "meta.json").read_text())
         sd = st.load_file(d / meta["lora_file"], device=dev)
@@ -171,8 +256,11 @@ def _load_checkpoint_dir(trainer, d):
         sdict["lr"] = trainer.optimizer.param_groups[0]["lr"]
         try:
             trainer.optimizer.load_state_dict(sdict)
+            opt_restored = True
         except (KeyError, RuntimeError):
-            pass  # different optimizer kind: moments restart, as in the reference's Flux path
+            # different optimizer kind: moments restart, as in the reference's Flux path. The caller
+            # compares this flag across ranks, so a restart on one rank alone is not accepted.
+            opt_restored = False
     elif saved_world != world and hasattr(trainer.optimizer, "m_q"):
         # the job restarts on another number of ranks: rebuild this rank's slice of the 8-bit state
         files = [d / f"optimizer.rank{r}.safetensors" for r in range(saved_world)]
@@ -184,9 +272,15 @@ def _load_checkpoint_dir(trainer, d):
             part["step"] = int(md.get("step", step))
             part["lr"] = trainer.optimizer.param_groups[0]["lr"]
             trainer.optimizer.load_state_dict(part)
+            opt_restored = True
     trainer.step = step
     trainer.micro = step * trainer.cfg.grad_accum
-    return step, seed
+    rng = d / f"rng.rank{rank}.json"
+    if saved_world == world and rng.exists():
+        _restore_generator(trainer, json.loads(rng.read_text()).get("timestep_generator"))
+    else:
+        trainer._gen = None
+    return step, seed, opt_restored
 
 
 def reshard_8bit_state(files, new_rank: int, new_world: int, shard_numel: int, block: int = 256):

@@ -216,10 +216,42 @@ class Trainer:
         """Last global gradient norm (device tensor) when clipping or NaN checks are on."""
         return None if self._sumsq is None else self._sumsq.sqrt()
 
+    # ------------------------------------------------------------------ device health
+    def status_sources(self):
+        """Objects whose ``status()`` returns (and clears) a device status word set by a bounded
+        peer wait that ran out: the fused data-parallel communicator, and the ZeRO-3 / sequence-
+        parallel communicators when the job wired them (``extra_status_sources``)."""
+        src = []
+        fused = getattr(self.grad_sync, "_fused", None) if self.grad_sync is not None else None
+        if fused is not None:
+            src.append(("fused data-parallel step", fused))
+        for name, obj in getattr(self, "extra_status_sources", []):
+            src.append((name, obj))
+        return src
+
+    def check_device_status(self):
+        """Read every device status word (this synchronises; call it where the loss is read anyway:
+        log and checkpoint boundaries). A kernel whose bounded wait ran out has skipped its work
+        (the fused optimizer step leaves parameters and moments untouched), so the step that set the
+        word did not happen: raise instead of training on or saving from that state."""
+        from ..utils.errors import CommTimeoutError, KernelError
+        rank = self.grad_sync.rank if self.grad_sync is not None else 0
+        for name, obj in self.status_sources():
+            st = int(obj.status())
+            if st:
+                raise CommTimeoutError(st, rank=rank)
+        if torch.cuda.is_available() and F.N.lib() is not None:
+            words = F.kernel_error_check()
+            if words:
+                fam, code = next(iter(words.items()))
+                raise KernelError(f"device error word of the {fam} kernels (all: {words})", code)
+
     # ------------------------------------------------------------------ logging
     def log_row(self, loss, sec_per_it, ckpt_path=""):
         """Append ``step,loss,grad_norm,sec_per_it,alloc_mb,ckpt_path`` (the reference's
-        TRAIN_LOG_CSV columns, crates/training/src/run.rs:181-188)."""
+        TRAIN_LOG_CSV columns, crates/training/src/run.rs:181-188). The device status words are
+        read first: a logged step is a step that really ran."""
+        self.check_device_status()
         path = self.cfg.log_csv or os.environ.get("TRAIN_LOG_CSV")
         if not path:
             return
@@ -239,6 +271,7 @@ class Trainer:
         ``{root}/checkpoint-{step:06}/model.safetensors`` with ``model.`` key prefix plus
         ``optimizer.safetensors`` and ``metadata.json`` (src/trainers/checkpoint_saver.rs:63-118)."""
         from .checkpoint import save_training_checkpoint
+        self.check_device_status()          # never write a checkpoint from a state a failed step left
         return save_training_checkpoint(self, root or self.cfg.out_dir)
 
     def load_latest_checkpoint(self, root=None):

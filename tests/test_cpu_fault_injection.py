@@ -186,3 +186,97 @@ def test_8bit_optimizer_state_resharding(tmp_path):
     assert last["m_q"].abs().sum() == 0 and last["v_absmax"].sum() == 0 and last["m_q"].numel() == 512
     p5 = reshard_8bit_state(files, 5, 8, 2 * 256)
     assert torch.equal(p5["v_q"], full["v_q"][10 * 256:12 * 256])
+
+
+def test_resumed_run_draws_the_same_timesteps_as_an_uninterrupted_one(tmp_path):
+    """The timestep generator's state travels with the checkpoint: a run resumed at step k continues
+    the stream instead of replaying the draws of step 0."""
+    drawn = {}
+
+    def spy(tr, tag):
+        orig = tr.objective.sample_t
+
+        def wrapped(n, gen=None, device="cpu"):
+            t = orig(n, gen, device)
+            drawn.setdefault(tag, []).append(t.clone())
+            return t
+        tr.objective.sample_t = wrapped
+
+    full = _trainer(tmp_path / "a")
+    spy(full, "full")
+    for i in range(5):
+        full.train_step(synthetic_batch("tiny_mmdit", 1, "cpu", torch.float32, i))
+    first = _trainer(tmp_path / "b")
+    spy(first, "first")
+    for i in range(3):
+        first.train_step(synthetic_batch("tiny_mmdit", 1, "cpu", torch.float32, i))
+    first.save_checkpoint()
+    resumed = _trainer(tmp_path / "b")
+    assert resumed.load_latest_checkpoint() == (3, 3)
+    spy(resumed, "resumed")
+    for i in range(3, 5):
+        resumed.train_step(synthetic_batch("tiny_mmdit", 1, "cpu", torch.float32, i))
+    got = drawn["first"] + drawn["resumed"]
+    assert len(got) == 5 and all(torch.equal(a, b) for a, b in zip(got, drawn["full"]))
+    assert not torch.equal(drawn["resumed"][0], drawn["full"][0])      # not a replay from the start
+
+
+def _ckpt_worker(rank, world, port, root, q):
+    import os
+    os.environ.update(WORLD_SIZE=str(world), RANK=str(rank), LOCAL_RANK=str(rank),
+                      MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    import torch
+    import torch.distributed as dist
+    from pathlib import Path
+    from eridiffusion_b200.parallel.dist import GradSync, init_from_env
+    from eridiffusion_b200.train.checkpoint import load_latest_training_checkpoint
+    torch.set_num_threads(2)
+    init_from_env("gloo", timeout_s=120)
+    root = Path(root)
+
+    def mk():
+        torch.manual_seed(0)
+        m = build_model("tiny_mmdit", device="cpu", dtype=torch.float32)
+        cfg = TrainerConfig(mode="lora", adapter=AdapterConfig(rank=4, alpha=4, dtype=torch.float32),
+                            optimizer="adamw8bit", lr=1e-2, seed=3, out_dir=str(root), stochastic_rounding=False)
+        return Trainer(m, cfg, grad_sync=GradSync("zero1"))
+
+    tr = mk()
+    for i in range(2):
+        tr.train_step(synthetic_batch("tiny_mmdit", 1, "cpu", torch.float32, 10 * i + rank))
+    tr.save_checkpoint()
+    tr.train_step(synthetic_batch("tiny_mmdit", 1, "cpu", torch.float32, 20 + rank))
+    tr.save_checkpoint()
+    dist.barrier()
+    newest = sorted(root.glob("step_*"))[-1]
+    # every rank wrote its shard before meta.json appeared
+    assert all((newest / f"optimizer.rank{r}.safetensors").exists() for r in range(world))
+    if rank == 1:
+        f = newest / "optimizer.rank1.safetensors"                    # damage ONE rank's shard only
+        f.write_bytes(f.read_bytes()[: f.stat().st_size // 2])
+    dist.barrier()
+    tr2 = mk()
+    skipped = []
+    res = load_latest_training_checkpoint(tr2, root, on_skip=lambda p, e: skipped.append(p.name))
+    q.put((rank, res, skipped, tr2.step))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_one_damaged_shard_makes_every_rank_fall_back_together(tmp_path):
+    """Two gloo ranks with sharded 8-bit optimizer state: a truncated shard of rank 1 must send BOTH
+    ranks to the previous checkpoint, so that they resume at the same step."""
+    import socket
+    s = socket.socket(); s.bind(("127.0.0.1", 0)); port = s.getsockname()[1]; s.close()
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_ckpt_worker, args=(r, 2, port, str(tmp_path), q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    out = sorted(q.get(timeout=240) for _ in range(2))
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    (r0, res0, skip0, step0), (r1, res1, skip1, step1) = out
+    assert res0 == res1 == (2, 3) and step0 == step1 == 2
+    assert skip0 == skip1 == ["step_000003"]

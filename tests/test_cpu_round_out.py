@@ -247,46 +247,91 @@ def test_rope_1d_table_aligns_instants():
 
 
 # ----------------------------------------------------------------------------- SD3.5 checkpoint keys
+def _sd3_reference_pos(hidden, max_size, gh, gw):
+    """fp32 restatement of RoPE2D::embed (src/models/mmdit_blocks.rs:2107-2136): centre crop of the
+    largest grid, integer positions, [sin | cos] per axis, the column axis FIRST."""
+    axis = hidden // 2
+    half = axis // 2
+    inv = torch.tensor([1.0 / 10000.0 ** (i / half) for i in range(half)], dtype=torch.float32)
+    top, left = (max_size - gh) // 2, (max_size - gw) // 2
+    hp = torch.arange(top, top + gh, dtype=torch.float32)
+    wp = torch.arange(left, left + gw, dtype=torch.float32)
+    ha, wa = hp[:, None] * inv[None], wp[:, None] * inv[None]
+    he = torch.cat([ha.sin(), ha.cos()], 1).view(gh, 1, axis).expand(gh, gw, axis)
+    we = torch.cat([wa.sin(), wa.cos()], 1).view(1, gw, axis).expand(gh, gw, axis)
+    return torch.cat([we, he], 2).reshape(gh * gw, hidden)
+
+
+def _sd3_reference_unpatchify(tok, gh, gw, C, p=2):
+    """fp32 restatement of the reference unpatchify (src/models/mmdit_blocks.rs:2280-2288): a token
+    holds its patch as [p, p, C]."""
+    B = tok.shape[0]
+    return tok.reshape(B, gh, gw, p, p, C).permute(0, 5, 1, 3, 2, 4).reshape(B, C, gh * p, gw * p)
+
+
 def test_sd35_original_layout_loads(tmp_path):
+    """A checkpoint in the ORIGINAL SD3 conventions — (p, p, c) rows of the final projection, a real
+    ``pos_embed`` table over the largest grid, convolution-shaped patch embedding — loads into the
+    model so that the model computes the ORIGINAL function: the position rows equal the reference's
+    centre-cropped embed and the predicted image equals the reference's unpatchify of the file-order
+    projection."""
     from eridiffusion_b200.io import safetensors as st
-    from eridiffusion_b200.io.weights import canonical_key, load_model_weights
+    from eridiffusion_b200.io.weights import canonical_key, export_sd3_original, load_model_weights
     from eridiffusion_b200.models import build_model
+    from eridiffusion_b200.ops import reference as R
+    M = 10                                                   # largest patch grid of this toy table
     kw = dict(hidden=64, num_heads=2, depth=2, in_channels=64, context_dim=16, pooled_dim=12, dtype=torch.float32,
-              x_self_attn_layers=(0,))
+              x_self_attn_layers=(0,), pos_embed_max_size=M)
     torch.manual_seed(0)
     src = build_model("sd35", **kw)
     for p in src.parameters():
         torch.nn.init.normal_(p, std=0.1)
     assert src.joint_blocks[1].context_pre_only            # released layout: last block's text stream is pre-only
-    back = {"img_mod.lin": "x_block.adaLN_modulation.1", "txt_mod.lin": "context_block.adaLN_modulation.1",
-            "img_attn2.": "x_block.attn2.", "img_attn.": "x_block.attn.", "txt_attn.": "context_block.attn.",
-            "img_mlp_0": "x_block.mlp.fc1", "img_mlp_2": "x_block.mlp.fc2", "txt_mlp_0": "context_block.mlp.fc1",
-            "txt_mlp_2": "context_block.mlp.fc2", "q_norm.scale": "ln_q.weight", "k_norm.scale": "ln_k.weight",
-            "in_layer": "mlp.0", "out_layer": "mlp.2", "final_layer.adaLN.lin": "final_layer.adaLN_modulation.1"}
-    sd = {}
-    for n, p in src.named_parameters():
-        k = n
-        for a, b in back.items():
-            k = k.replace(a, b)
-        if k.startswith("x_embedder."):
-            k = k.replace("x_embedder.", "x_embedder.proj.")
-        t = p.detach().clone()
-        if k == "x_embedder.proj.weight":
-            t = t.view(64, 16, 2, 2)
-        sd["model.diffusion_model." + k] = t
-    sd["model.diffusion_model.pos_embed"] = torch.zeros(1, 36864 // 64, 64)
+    # the closed-form table is the reference's embed for every crop
+    for gh, gw in ((4, 4), (3, 6), (10, 10)):
+        assert torch.allclose(src.pos_table(gh, gw, "cpu", torch.float32), _sd3_reference_pos(64, M, gh, gw), atol=1e-5)
+    # a checkpoint in the original layout, with a table that is NOT the closed form
+    sd = {"model.diffusion_model." + k: v for k, v in export_sd3_original(src).items()}
+    table = torch.randn(1, M * M, 64)
+    sd["model.diffusion_model.pos_embed"] = table
+    assert sd["model.diffusion_model.x_embedder.proj.weight"].shape == (64, 16, 2, 2)
+    assert "model.diffusion_model.joint_blocks.0.x_block.attn2.qkv.weight" in sd
     key = canonical_key("model.diffusion_model.joint_blocks.3.x_block.attn.ln_q.weight", "sd35")
     assert key == "joint_blocks.3.img_attn.q_norm.scale"
     f = tmp_path / "sd35.safetensors"
     st.save_file(sd, f)
     dst = build_model("sd35", **kw)
     used = load_model_weights(dst, f, "sd35", strict=True)
-    assert len(used) == len(list(dst.named_parameters()))
+    assert len(used) == len(list(dst.named_parameters())) + 1          # + the position table
     for (n, a), (_, b) in zip(src.named_parameters(), dst.named_parameters()):
         assert torch.equal(a, b), n
-    img, txt = torch.randn(1, 16, 64), torch.randn(1, 5, 16)
-    t, y = torch.rand(1), torch.randn(1, 12)
-    assert torch.equal(src(img, txt, t, y, grid_hw=(4, 4)), dst(img, txt, t, y, grid_hw=(4, 4)))
+    # the file's table is used, centre-cropped
+    gh, gw = 4, 6
+    top, left = (M - gh) // 2, (M - gw) // 2
+    want = table.view(M, M, 64)[top:top + gh, left:left + gw].reshape(gh * gw, 64)
+    assert torch.equal(dst.pos_table(gh, gw, "cpu", torch.float32), want)
+    # the final projection: file-order rows + the reference's unpatchify == model rows + this package's
+    fw = sd["model.diffusion_model.final_layer.linear.weight"]
+    fb = sd["model.diffusion_model.final_layer.linear.bias"]
+    h = torch.randn(2, gh * gw, 64)
+    ref_img = _sd3_reference_unpatchify(h @ fw.t() + fb, gh, gw, 16)
+    lin = dst.final_layer.linear
+    our_img = R.unpatchify(h @ lin.weight.t() + lin.bias, 16, gh * 2, gw * 2)
+    assert torch.allclose(ref_img, our_img, atol=1e-6)
+    assert not torch.allclose(fw, lin.weight)              # the rows really were permuted
+    # and the patch embedding: the file's convolution over an image == the linear over packed tokens
+    img = torch.randn(2, 16, gh * 2, gw * 2)
+    conv = torch.nn.functional.conv2d(img, sd["model.diffusion_model.x_embedder.proj.weight"],
+                                      sd["model.diffusion_model.x_embedder.proj.bias"], stride=2)
+    tok = R.patchify(img) @ dst.x_embedder.weight.t() + dst.x_embedder.bias
+    assert torch.allclose(conv.flatten(2).transpose(1, 2), tok, atol=1e-5)
+    txt = torch.randn(2, 5, 16)
+    t, y = torch.rand(2), torch.randn(2, 12)
+    # end to end: with the file's table loaded, the model differs from the closed-form one only
+    # through the position rows
+    src.pos_embed.copy_(table[0])
+    assert torch.equal(src(R.patchify(img), txt, t, y, grid_hw=(gh, gw)), dst(R.patchify(img), txt, t, y, grid_hw=(gh, gw)))
+
 
 
 def test_klein_checkpoint_layout_loads(tmp_path):

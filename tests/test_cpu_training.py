@@ -129,3 +129,33 @@ def test_per_layer_lr_and_block_rotation_freeze_the_right_adapters():
     after = snap()
     changed = {n for n in names if not torch.equal(before[n], after[n])}
     assert changed and all("double_blocks.1." in n for n in changed), sorted(changed)[:4]
+
+
+def test_device_status_word_stops_logging_and_checkpointing(tmp_path):
+    """A status word set by a bounded device wait (here: a stand-in source) makes the trainer raise
+    at the next log row and before any checkpoint is written."""
+    import pytest
+    from eridiffusion_b200.utils.errors import CommTimeoutError
+    tr = make_trainer(tmp_path / "run")
+    tr.train_step(batch())
+
+    class Source:
+        def __init__(self):
+            self.word = 0
+
+        def status(self):
+            w, self.word = self.word, 0
+            return w
+
+    src = Source()
+    tr.extra_status_sources = [("stand-in communicator", src)]
+    tr.log_row(1.0, 0.1)                                   # clean word: nothing happens
+    src.word = (1 << 8) | 3                                 # channel 0, peer 3
+    with pytest.raises(CommTimeoutError) as ei:
+        tr.save_checkpoint()
+    assert ei.value.peer == 3 and ei.value.channel == 0
+    assert not (tmp_path / "run").exists() or not any((tmp_path / "run").iterdir())
+    src.word = (2 << 8) | 1
+    with pytest.raises(CommTimeoutError):
+        tr.log_row(1.0, 0.1)
+    assert tr.save_checkpoint() is not None                # the word was cleared by the read

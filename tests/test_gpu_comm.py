@@ -37,6 +37,55 @@ def test_barrier_wait_runs_out_and_reports():
     assert torch.ones(4, device="cuda").sum().item() == 4.0
 
 
+def test_fused_dp_step_skips_the_update_when_a_peer_never_arrives():
+    """Fabricated two-rank context on one GPU whose peer never signals: every barrier of the fused
+    data-parallel kernel runs out (30 ms each), the status word names the silent peer, and the
+    kernel must NOT have touched parameters or optimizer state (nor pushed anything to the peer)."""
+    from eridiffusion_b200.ops import _native as N
+    from eridiffusion_b200.parallel import symm
+    lib = N.require()
+    symm._bind(lib)
+    dev = "cuda"
+    shard = 4096
+    n = 2 * shard
+    g = torch.Generator(device=dev).manual_seed(3)
+    grads = [torch.randn(n, device=dev, generator=g).bfloat16() for _ in range(2)]
+    params = [torch.randn(n, device=dev, generator=g).bfloat16() for _ in range(2)]
+    before = [p.clone() for p in params]
+    slots = [torch.zeros(16, device=dev) for _ in range(2)]
+    mq = torch.randint(-100, 100, (shard,), device=dev, dtype=torch.int8)
+    vq = torch.randint(0, 255, (shard,), device=dev, dtype=torch.uint8)
+    mab, vab = torch.rand(shard // 256, device=dev), torch.rand(shard // 256, device=dev)
+    state_before = [t.clone() for t in (mq, vq, mab, vab)]
+    flags = torch.zeros(symm.FLAG_CHANNELS * symm.MAX_WORLD, dtype=torch.int32, device=dev)
+    peer_flags = torch.zeros_like(flags)          # the peer's flag words: written, never answered
+    err = torch.zeros(1, dtype=torch.int32, device=dev)
+    c = symm.CommCtx()
+    c.flags_local = flags.data_ptr()
+    c.flags_peer[0], c.flags_peer[1] = flags.data_ptr(), peer_flags.data_ptr()
+    c.rank, c.world, c.epoch, c.wait_ns, c.err = 0, 2, 1, 30_000_000, err.data_ptr()
+    a = symm.FusedDpArgs()
+    for i in range(2):
+        a.grads[i], a.params[i], a.sumsq_slots[i] = grads[i].data_ptr(), params[i].data_ptr(), slots[i].data_ptr()
+    reduced = torch.zeros(shard, device=dev)
+    sumsq_local = torch.zeros(1, device=dev)
+    a.reduced, a.sumsq_local = reduced.data_ptr(), sumsq_local.data_ptr()
+    a.mq, a.vq, a.m_absmax, a.v_absmax = mq.data_ptr(), vq.data_ptr(), mab.data_ptr(), vab.data_ptr()
+    a.shard_elems = shard
+    a.lr, a.beta1, a.beta2, a.eps, a.weight_decay, a.max_grad_norm = 1e-2, 0.9, 0.999, 1e-8, 0.01, 1.0
+    a.step, a.seed, a.stochastic = 1, 7, 0
+    rc = lib.eri_fused_dp_step(C.byref(c), C.byref(a), torch.cuda.current_stream().cuda_stream)
+    assert rc == 0
+    torch.cuda.synchronize()
+    code = int(err.item())
+    assert code != 0 and (code & 0xFF) == 1 and (code >> 8) == 1      # first barrier (channel 0 + 1), peer 1
+    for p, b in zip(params, before):
+        assert torch.equal(p, b), "parameters changed although the reduce was incomplete"
+    for t, b in zip((mq, vq, mab, vab), state_before):
+        assert torch.equal(t, b), "optimizer state changed although the reduce was incomplete"
+    assert torch.ones(4, device=dev).sum().item() == 4.0               # the context is still usable
+
+
 def test_fused_dp_world1_matches_plain_optimizer():
     from eridiffusion_b200.ops import functional as F
     from eridiffusion_b200.optim import AdamW8bit, ParamArena
