@@ -25,7 +25,7 @@ class AdapterConfig:
     rank: int = 16
     alpha: float | None = None    # default: rank (scale 1)
     dropout: float = 0.0
-    init: str = "kaiming"         # "kaiming" | "reference" (A ~ N(0, 1/sqrt(r)), flux/lora.rs:22-44)
+    init: str = "kaiming"         # "kaiming" | "reference" (A ~ N(0, 1/sqrt(r)), flux/lora.rs:22-44) | "nonzero" (B small, not zero)
     target: list[str] = field(default_factory=lambda: [r".*"])   # regexes on module paths
     exclude: list[str] = field(default_factory=list)
     rank_pattern: dict[str, int] = field(default_factory=dict)   # regex -> rank override
@@ -49,7 +49,12 @@ class LoRA(nn.Module):
         std = 1.0 / math.sqrt(rank) if init == "reference" else 1.0 / math.sqrt(base.in_features)
         a.normal_(0.0, std, generator=gen)
         self.lora_A = nn.Parameter(a.to(dtype))
-        self.lora_B = nn.Parameter(torch.zeros(base.out_features, rank, dtype=dtype, device=dev))
+        b = torch.zeros(base.out_features, rank, dtype=torch.float32, device=dev)
+        if init == "nonzero":
+            # ``lora_zero_init: false`` (crates/training/src/lora_keys.rs:31, flux_trainer.rs:59): the
+            # up-projection starts small instead of at zero, so the adapter acts from the first step
+            b.normal_(0.0, 0.01, generator=gen)
+        self.lora_B = nn.Parameter(b.to(dtype))
 
     def forward(self, base: Linear, x, act=None, residual=None, gate=None):
         wt = base.frozen_transpose() if torch.is_grad_enabled() else None

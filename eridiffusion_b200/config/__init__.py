@@ -12,8 +12,16 @@ arch, is_flux, is_v3, is_sdxl, quantize, low_vram, vae_path, ...}, sample{sample
 width, height, prompts, neg, seed, walk_seed, guidance_scale, sample_steps}, tread{...}}]} / meta``
 
 Schema 2 — flat ``TrainCfg`` keyed by ``model_kind`` (crates/training/src/model_registry.rs:125-289;
-templates crates/training/config/templates/train_*.yaml): ``model_kind, weights, bf16_params,
-steps, batch_size, grad_accum_steps, lr, seed, ckpt_every, optimizer, mode, flux_manifest*, ...``
+templates crates/training/config/templates/train_*.yaml). EVERY field of that struct is accepted:
+``model_kind`` (``flux sdxl sd3 qwen_image_v1 wan22 hidream_i1 omnigen2 ltx hunyuan lumina``),
+``recipe, weights, bf16_params, steps, batch_size, grad_accum_steps, lr, seed, ckpt_every, optimizer,
+offload_pinned_threshold_mb``, the ``flux_* / sdxl_* / sd35_*`` model, tokenizer and manifest paths,
+``lora_rank, lora_alpha, lora_zero_init, data_root, prefetch, schedule_name, schedule_steps,
+sigma_min, sigma_max, clip_grad_norm``, the nested groups ``paths / data / lora / train / schedule``
+(also under their struct names ``paths_nested`` ...; hydrated into the flat fields with the
+reference's precedence: an explicit flat value wins, model_registry.rs:351-482) and the ``mode``
+struct ``{baseline, tread, srpo}`` of which exactly one must be true (:327-347, :483-492; a plain
+string is accepted too).
 
 Validation follows crates/training/src/eridiffusion_config.rs:203-369 (batch > 0, steps > 0,
 lr in [1e-7, 1e-2], bf16 only, device ``cuda:N``); unknown keys raise instead of being ignored.
@@ -26,9 +34,12 @@ from pathlib import Path
 
 import yaml
 
-MODEL_KINDS = ("flux", "sdxl", "sd3", "sd35", "qwen_image", "wan22", "ltx", "hunyuan", "lumina",
+MODEL_KINDS = ("flux", "sdxl", "sd3", "sd35", "sd35_medium", "qwen_image", "wan22", "ltx", "hunyuan", "lumina",
                "hidream_i1", "hidream", "omnigen2", "chroma", "klein", "zimage", "krea", "qwen_edit_image",
                "tiny_mmdit", "sd15")
+# spellings of the reference's ``ModelKind`` enum that differ from this package's registry names
+MODEL_KIND_ALIASES = {"qwen_image_v1": "qwen_image", "qwenimagev1": "qwen_image", "s_d_x_l": "sdxl", "s_d3": "sd3",
+                      "hi_dream_i1": "hidream_i1"}
 
 
 class ConfigError(ValueError):
@@ -44,6 +55,7 @@ class NetworkCfg:
     conv_alpha: float | None = None
     dropout: float = 0.0
     lr_if_contains: dict = field(default_factory=dict)
+    zero_init: bool = True              # up-projection starts at zero (flat schema: lora_zero_init)
     ramp_double_blocks: bool | None = None
     ramp_target_lr: float | None = None
     ramp_warmup_steps: int | None = None
@@ -76,6 +88,9 @@ class DatasetCfg:
     manifest_shuffle: bool = True
     manifest_repeat: int = 1
     synthetic: bool = False
+    random_init_encoders: bool = False          # smoke runs: cache a folder with randomly initialised encoders
+    encoder_overrides: dict = field(default_factory=dict)   # {encoder kind: constructor overrides}
+    max_text_tokens: int | None = None          # text length when a folder is cached (default 512 / 77)
 
 
 @dataclass
@@ -114,7 +129,11 @@ class ModelCfg:
     text_encoder_path: str | None = None
     text_encoder_2_path: str | None = None
     clip_l_path: str | None = None
+    clip_g_path: str | None = None
     t5_path: str | None = None
+    t5_tokenizer: str | None = None
+    clip_l_tokenizer: str | None = None
+    clip_g_tokenizer: str | None = None
     variant: str | None = None
     overrides: dict = field(default_factory=dict)
 
@@ -159,6 +178,13 @@ class TrainCfg:
     performance_log_every: int = 10
     trigger_word: str | None = None
     offload_pinned_threshold_mb: int | None = None
+    bf16_params: bool = True
+    recipe: list | None = None          # optional stage list for the pipeline orchestrator
+    schedule_name: str = ""             # "" | flow names | "sigma_eps" / "eps_sigma" / "bounded_sigma" (phase-4 eps objective)
+    schedule_steps: int = 0             # > 0: length of the LR schedule when it differs from ``steps``
+    sigma_min: float | None = None
+    sigma_max: float | None = None
+    prefetch: int | None = None         # loader read-ahead depth (batches)
     network: NetworkCfg = field(default_factory=NetworkCfg)
     save: SaveCfg = field(default_factory=SaveCfg)
     datasets: list = field(default_factory=list)
@@ -185,6 +211,12 @@ class TrainCfg:
             raise ConfigError("zero_stage must be 0..3")
         if self.mode not in ("baseline", "tread", "srpo"):
             raise ConfigError(f"unknown mode {self.mode!r}")
+        if self.sigma_min is not None and self.sigma_min <= 0:
+            raise ConfigError("sigma_min must be > 0")
+        if self.sigma_min is not None and self.sigma_max is not None and self.sigma_max < self.sigma_min:
+            raise ConfigError("sigma_max must be >= sigma_min")
+        if self.prefetch is not None and self.prefetch < 0:
+            raise ConfigError("prefetch must be >= 0")
         return self
 
     def to_dict(self):
@@ -292,41 +324,149 @@ def _from_ai_toolkit(doc: dict) -> TrainCfg:
     return out
 
 
-_FLAT_DATASET_KEYS = {"flux_manifest": "manifest", "flux_manifest_root": "manifest_root",
-                      "flux_manifest_index": "manifest_index", "flux_manifest_validate": "manifest_validate",
-                      "flux_manifest_shuffle": "manifest_shuffle", "flux_manifest_repeat": "manifest_repeat",
-                      "sdxl_manifest": "manifest", "sdxl_manifest_root": "manifest_root"}
-_FLAT_MODEL_KEYS = {"weights": "name_or_path", "flux_model_path": "name_or_path", "flux_vae_path": "vae_path",
-                    "flux_t5_path": "t5_path", "flux_clip_path": "clip_l_path", "flux_variant": "variant"}
-_FLAT_IGNORED = {"flux_t5_tokenizer", "flux_clip_tokenizer", "recipe"}
+# flat key -> ModelCfg field, per model family (the reference keeps one set of path fields per family)
+_FLAT_MODEL_KEYS = {
+    "weights": "name_or_path",
+    "flux_model_path": "name_or_path", "flux_vae_path": "vae_path", "flux_t5_path": "t5_path",
+    "flux_clip_path": "clip_l_path", "flux_t5_tokenizer": "t5_tokenizer", "flux_clip_tokenizer": "clip_l_tokenizer",
+    "flux_variant": "variant",
+    "sdxl_unet_path": "name_or_path", "sdxl_vae_path": "vae_path", "sdxl_clip_l_path": "clip_l_path",
+    "sdxl_clip_g_path": "clip_g_path", "sdxl_clip_l_tokenizer": "clip_l_tokenizer",
+    "sdxl_clip_g_tokenizer": "clip_g_tokenizer",
+    "sd35_model_path": "name_or_path", "sd35_vae_path": "vae_path", "sd35_clip_l_path": "clip_l_path",
+    "sd35_clip_g_path": "clip_g_path", "sd35_t5_path": "t5_path", "sd35_clip_l_tokenizer": "clip_l_tokenizer",
+    "sd35_clip_g_tokenizer": "clip_g_tokenizer", "sd35_t5_tokenizer": "t5_tokenizer",
+}
+_MANIFEST_FIELDS = ("", "_root", "_index", "_validate", "_shuffle", "_repeat")
+_MANIFEST_FAMILY = {"sdxl": "sdxl", "sd15": "sdxl", "sd3": "sd35", "sd35": "sd35", "sd35_medium": "sd35"}
+# nested group -> {group key: flat key}; ``data`` is expanded below because of its three manifest sets
+_NESTED = {
+    "paths": {"flux_weights": "flux_model_path", "vae": "flux_vae_path", "t5": "flux_t5_path", "clip": "flux_clip_path",
+              "t5_tokenizer": "flux_t5_tokenizer", "clip_tokenizer": "flux_clip_tokenizer"},
+    "data": {"root": "data_root", "batch_size": "batch_size", "prefetch": "prefetch",
+             **{f"manifest{f}": f"flux_manifest{f}" for f in _MANIFEST_FIELDS},
+             **{f"manifest_sdxl{f}": f"sdxl_manifest{f}" for f in _MANIFEST_FIELDS},
+             **{f"manifest_sd35{f}": f"sd35_manifest{f}" for f in _MANIFEST_FIELDS}},
+    "lora": {"rank": "lora_rank", "alpha": "lora_alpha", "zero_init": "lora_zero_init"},
+    "train": {"steps": "steps", "grad_accum_steps": "grad_accum_steps", "lr": "lr", "ckpt_every": "ckpt_every",
+              "bf16": "bf16_params", "clip_grad_norm": "clip_grad_norm"},
+    "schedule": {"name": "schedule_name", "steps": "schedule_steps", "sigma_min": "sigma_min", "sigma_max": "sigma_max"},
+}
+_SIGMA_EPS_NAMES = ("sigma_eps", "eps_sigma", "bounded_sigma", "phase4_eps")
+
+
+def _hydrate_nested(d: dict) -> dict:
+    """Fold the nested groups into the flat keys with the reference's precedence: a flat key that is
+    present wins; zero / empty group values count as "not given" (model_registry.rs:351-482)."""
+    d = dict(d)
+    for group, mapping in _NESTED.items():
+        for name in (group, f"{group}_nested"):
+            if name not in d:
+                continue
+            g = d.pop(name) or {}
+            if not isinstance(g, dict):
+                raise ConfigError(f"{name} must be a mapping")
+            unknown = set(g) - set(mapping)
+            if unknown:
+                raise ConfigError(f"unknown keys in {name}: {sorted(unknown)}")
+            for k, flat in mapping.items():
+                v = g.get(k)
+                if v is None or v == "" or (isinstance(v, (int, float)) and not isinstance(v, bool) and v == 0):
+                    continue
+                d.setdefault(flat, v)
+            if group == "lora" and "rank" in g:
+                d.setdefault("lora_alpha", float(g["rank"]))       # alpha defaults to the rank
+                d.setdefault("lora_zero_init", True)
+    return d
+
+
+def _mode_name(mode) -> str:
+    """``mode`` is a struct of three booleans in the reference (exactly one true); a plain string names
+    the mode directly."""
+    if mode is None:
+        return "baseline"
+    if isinstance(mode, str):
+        return mode
+    if isinstance(mode, dict):
+        unknown = set(mode) - {"baseline", "tread", "srpo"}
+        if unknown:
+            raise ConfigError(f"unknown keys in mode: {sorted(unknown)}")
+        flags = {"baseline": bool(mode.get("baseline", not (mode.get("tread") or mode.get("srpo")))),
+                 "tread": bool(mode.get("tread", False)), "srpo": bool(mode.get("srpo", False))}
+        on = [k for k, v in flags.items() if v]
+        if len(on) != 1:
+            raise ConfigError("config.mode must set exactly one of baseline|tread|srpo to true")
+        return on[0]
+    raise ConfigError("mode must be a string or a {baseline, tread, srpo} mapping")
 
 
 def _from_flat(doc: dict) -> TrainCfg:
-    d = dict(doc)
+    d = _hydrate_nested(doc)
     kind = str(d.pop("model_kind")).lower()
-    ds, model = {}, {"kind": kind}
-    for k, v in list(d.items()):
-        if k in _FLAT_DATASET_KEYS:
-            ds[_FLAT_DATASET_KEYS[k]] = d.pop(k)
-        elif k in _FLAT_MODEL_KEYS:
-            model[_FLAT_MODEL_KEYS[k]] = d.pop(k)
-        elif k in _FLAT_IGNORED:
-            d.pop(k)
-    d.pop("bf16_params", None)
+    kind = MODEL_KIND_ALIASES.get(kind, kind)
+    model = {"kind": kind}
+    # model / encoder / tokenizer paths: the family's own keys win over the generic ``weights``
+    own_prefix = {"sdxl": "sdxl_", "sd15": "sdxl_", "sd3": "sd35_", "sd35": "sd35_", "sd35_medium": "sd35_"}.get(kind, "flux_")
+    for k in list(d):
+        if k in _FLAT_MODEL_KEYS:
+            v = d.pop(k)
+            if v in (None, ""):
+                continue
+            fld = _FLAT_MODEL_KEYS[k]
+            if k.startswith(own_prefix) or fld not in model:
+                model[fld] = v
+    # manifests: the set that belongs to the model family feeds the dataset; the others are kept in meta
+    fam = _MANIFEST_FAMILY.get(kind, "flux")
+    ds, other = {}, {}
+    for f in ("flux", "sdxl", "sd35"):
+        for suf in _MANIFEST_FIELDS:
+            k = f"{f}_manifest{suf}"
+            if k in d:
+                v = d.pop(k)
+                if v is None:
+                    continue
+                (ds if f == fam else other)["manifest" + suf] = v
+    data_root = d.pop("data_root", None)
+    lora_rank, lora_alpha = d.pop("lora_rank", None), d.pop("lora_alpha", None)
+    lora_zero = d.pop("lora_zero_init", None)
+    clip = d.pop("clip_grad_norm", None)
+    if clip is not None:
+        d.setdefault("max_grad_norm", float(clip))
+    d["mode"] = _mode_name(d.get("mode"))
+    if "schedule_name" in d and d["schedule_name"] is None:
+        d.pop("schedule_name")
     nested = {}
     for k, cls in (("network", NetworkCfg), ("save", SaveCfg), ("sample", SampleCfg), ("tread", TreadCfg),
                    ("parallel", ParallelCfg)):
         if k in d:
             nested[k] = _take(cls, d.pop(k), k)
+    net = nested.get("network") or NetworkCfg()
+    if lora_rank is not None:
+        net.linear = int(lora_rank)
+        net.linear_alpha = float(lora_alpha if lora_alpha is not None else lora_rank)
+    elif lora_alpha is not None:
+        net.linear_alpha = float(lora_alpha)
+    if lora_zero is not None:
+        net.zero_init = bool(lora_zero)
+    nested["network"] = net
     if "model" in d:
         model.update(d.pop("model"))
     if "datasets" in d:
         nested["datasets"] = [_take(DatasetCfg, x, "datasets[]") for x in d.pop("datasets")]
-    elif ds:
+    elif ds or data_root:
+        if data_root and not ds.get("manifest"):
+            ds["folder_path"] = str(data_root)           # a folder of images + captions, cached on the fly
+        elif data_root:
+            ds.setdefault("manifest_root", str(data_root))
         nested["datasets"] = [_take(DatasetCfg, ds, "dataset")]
-    if "optimizer" in d and d["optimizer"] is None:
-        d.pop("optimizer")
+    for k in ("optimizer", "ckpt_every", "offload_pinned_threshold_mb", "recipe", "sigma_min", "sigma_max", "prefetch"):
+        if k in d and d[k] is None:
+            d.pop(k)
     cfg = _take(TrainCfg, {**d, **nested, "model": _take(ModelCfg, model, "model")}, "config")
+    if other:
+        cfg.meta["other_manifests"] = other
+    if cfg.mode == "tread":
+        cfg.tread.enabled = True
     return cfg
 
 
@@ -425,6 +565,17 @@ def assert_precomp_vae_compat(vae: VaeBlock, latent_channels: int, latent_div: i
                           f"{vae.kind} ({vae.latent_channels} ch, /{vae.latent_div})")
 
 
-TEMPLATES = {k: f"model_kind: {k}\nweights: \"/path/to/weights\"\nbf16_params: true\nsteps: 10\n"
-                f"batch_size: 1\ngrad_accum_steps: 1\nlr: 0.0001\noptimizer: adamw\n"
-             for k in ("flux", "sdxl", "sd3", "qwen_image", "wan22", "ltx", "hunyuan", "lumina", "hidream_i1", "omnigen2")}
+_TEMPLATE_TAIL = "bf16_params: true\nsteps: 10\nbatch_size: 1\ngrad_accum_steps: 1\nlr: 0.0001\noptimizer: adamw\n"
+# the ten templates of crates/training/config/templates/, field for field
+TEMPLATES = {k: f"model_kind: {k}\nweights: \"/path/to/weights\"\n" + _TEMPLATE_TAIL
+             for k in ("flux", "qwen_image_v1", "wan22", "ltx", "hunyuan", "lumina", "hidream_i1", "omnigen2")}
+TEMPLATES["sdxl"] = "model_kind: sdxl\n" + _TEMPLATE_TAIL + "".join(
+    f"sdxl_{k}: \"/path/to/{v}\"\n" for k, v in (
+        ("unet_path", "sdxl_unet.safetensors"), ("vae_path", "sdxl_vae.safetensors"), ("clip_l_path", "clip_l.safetensors"),
+        ("clip_g_path", "clip_g.safetensors"), ("clip_l_tokenizer", "clip_l_tokenizer.json"),
+        ("clip_g_tokenizer", "clip_g_tokenizer.json")))
+TEMPLATES["sd3"] = "model_kind: sd3\n" + _TEMPLATE_TAIL + "".join(
+    f"sd35_{k}: \"/path/to/{v}\"\n" for k, v in (
+        ("model_path", "sd35_model.safetensors"), ("vae_path", "sd35_vae.safetensors"), ("clip_l_path", "clip_l.safetensors"),
+        ("clip_g_path", "clip_g.safetensors"), ("t5_path", "t5.safetensors"), ("clip_l_tokenizer", "clip_l_tokenizer.json"),
+        ("clip_g_tokenizer", "clip_g_tokenizer.json"), ("t5_tokenizer", "t5_tokenizer.json")))

@@ -60,6 +60,14 @@ def load_cached_tensor(path, dtype=torch.bfloat16):
     return t.to(dtype)
 
 
+def load_cached_key(path, key, dtype=torch.bfloat16):
+    """One named tensor of a cache file, or ``None`` when the file has no such key."""
+    with st.SafeFile(path) as f:
+        if key not in f.keys():
+            return None
+        return f.get(key).to(dtype)
+
+
 def load_cached_tensors(paths, dtype=torch.bfloat16, prefetcher=None):
     """``load_cached_tensor`` for many files at once. With a native ``Prefetcher`` every payload is
     queued first, so the reads of a batch overlap on the worker threads."""
@@ -232,7 +240,13 @@ class CachedEmbeddingLoader:
                 txt[i, : t.shape[0]] = t
                 mask[i, ..., : t.shape[0]] = True
             out["txt"], out["txt_mask"] = txt, mask
-            out["pooled"] = torch.stack([t.reshape(-1) for t in many("clip_path")])
+            if all(str(e.paths.get("clip_path") or "") not in ("", ".") and Path(e.paths["clip_path"]).is_file() for e in es):
+                out["pooled"] = torch.stack([t.reshape(-1) for t in many("clip_path")])
+            else:
+                # folder caches written by ``data.precache`` keep the pooled vector inside the text file
+                pooled = [load_cached_key(e.paths["t5_path"], "pooled") for e in es]
+                if all(p is not None for p in pooled):
+                    out["pooled"] = torch.stack([p.reshape(-1) for p in pooled])
         else:
             out["clip_l"] = torch.stack(many("clip_l_path"))
             out["clip_g"] = torch.stack(many("clip_g_path"))

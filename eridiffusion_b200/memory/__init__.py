@@ -38,9 +38,10 @@ class BlockSwapManager:
     ``run(i, fn)`` makes block i resident (prefetching the next ones on a copy stream), runs
     ``fn(block)`` and evicts least-recently-used blocks beyond the window."""
 
-    def __init__(self, blocks, cfg: BlockSwapConfig | None = None, device=None):
+    def __init__(self, blocks, cfg: BlockSwapConfig | None = None, device=None, frozen_only=False):
         self.blocks = list(blocks)
         self.cfg = cfg or BlockSwapConfig()
+        self.frozen_only = frozen_only
         self.device = torch.device(device or ("cuda" if torch.cuda.is_available() else "cpu"))
         self.cuda = self.device.type == "cuda"
         self.copy_stream = torch.cuda.Stream() if self.cuda else None
@@ -52,7 +53,7 @@ class BlockSwapManager:
         self.window = max(1, min(self.cfg.max_active_blocks, by_budget, len(self.blocks)))
         for i, b in enumerate(self.blocks):
             self.host[i] = {n: (p.detach().cpu().pin_memory() if self.cuda else p.detach().cpu())
-                            for n, p in b.named_parameters()}
+                            for n, p in self._swappable(b)}
             if self.cuda and i not in self.cfg.persistent:
                 self._drop(i)
             else:
@@ -62,8 +63,13 @@ class BlockSwapManager:
     def _block_bytes(b):
         return sum(p.numel() * p.element_size() for p in b.parameters())
 
+    def _swappable(self, b):
+        """Tensors that move between host and device. With ``frozen_only`` (training with adapters)
+        trainable tensors stay where they are: they live in the optimizer's flat arena."""
+        return [(n, p) for n, p in b.named_parameters() if not (self.frozen_only and p.requires_grad)]
+
     def _drop(self, i):
-        for n, p in self.blocks[i].named_parameters():
+        for n, p in self._swappable(self.blocks[i]):
             p.data = torch.empty(0, dtype=p.dtype, device=self.device)
 
     def _load(self, i, sync=False):
@@ -73,24 +79,27 @@ class BlockSwapManager:
         ev = None
         if self.cuda:
             with torch.cuda.stream(self.copy_stream):
-                for n, p in self.blocks[i].named_parameters():
+                for n, p in self._swappable(self.blocks[i]):
                     src = self.host[i][n]
                     p.data = src.to(self.device, non_blocking=True)
                     self.stats["bytes_h2d"] += src.numel() * src.element_size()
                 ev = torch.cuda.Event()
                 ev.record(self.copy_stream)
         else:
-            for n, p in self.blocks[i].named_parameters():
+            for n, p in self._swappable(self.blocks[i]):
                 p.data = self.host[i][n]
         self.resident[i] = ev
         self.stats["loads"] += 1
 
-    def plan(self, i):
-        """Indices that should be resident while block i runs."""
+    def plan(self, i, direction=1):
+        """Indices that should be resident while block i runs (``direction`` -1: the backward pass
+        walks the stack from the last block to the first)."""
+        if direction < 0:
+            return [j for j in range(i, max(-1, i - 1 - self.cfg.prefetch), -1)]
         return [j for j in range(i, min(len(self.blocks), i + 1 + self.cfg.prefetch))]
 
-    def prefetch_next(self, i):
-        for j in self.plan(i)[1:]:
+    def prefetch_next(self, i, direction=1):
+        for j in self.plan(i, direction)[1:]:
             if len(self.resident) < self.window + len(self.cfg.persistent):
                 self._load(j)
 
@@ -100,14 +109,14 @@ class BlockSwapManager:
             if victim is None:
                 break
             # trainable tensors are written back before eviction
-            if any(p.requires_grad for p in self.blocks[victim].parameters()):
-                for n, p in self.blocks[victim].named_parameters():
+            if any(p.requires_grad for _, p in self._swappable(self.blocks[victim])):
+                for n, p in self._swappable(self.blocks[victim]):
                     self.host[victim][n].copy_(p.detach(), non_blocking=True)
             self.resident.pop(victim)
             self._drop(victim)
             self.stats["evictions"] += 1
 
-    def run(self, i, fn):
+    def run(self, i, fn, direction=1):
         hit = i in self.resident
         self._load(i)
         if hit:
@@ -115,7 +124,7 @@ class BlockSwapManager:
         ev = self.resident[i]
         if ev is not None:
             torch.cuda.current_stream().wait_event(ev)
-        self.prefetch_next(i)
+        self.prefetch_next(i, direction)
         out = fn(self.blocks[i])
         self.release_previous(i)
         return out

@@ -159,6 +159,9 @@ class MMDiT(nn.Module):
                                            for _ in range(cfg.depth_single))
         self.final_layer = LastLayer(D, cfg.out_channels or cfg.in_channels, dtype, device)
         self._rope_cache = {}
+        # train.act_checkpoint.BlockRunner: activation policy, layer streaming and TREAD routing of
+        # the block stacks (None: the blocks are simply called in order)
+        self.runner = None
 
     def rope(self, txt_len, h, w, device):
         key = (txt_len, h, w, str(device))
@@ -188,13 +191,17 @@ class MMDiT(nn.Module):
         if self.txt_norm is not None:
             txt = F.norm_modulate(txt, weight=self.txt_norm.scale, rms=True)
         txt = self.txt_in(txt)
-        for blk in self.double_blocks:
-            img, txt = blk(img, txt, vec, cos, sin)
+        run = self.runner
+        for i, blk in enumerate(self.double_blocks):
+            img, txt = blk(img, txt, vec, cos, sin) if run is None else run.double(i, blk, img, txt, vec, cos, sin)
         if len(self.single_blocks) == 0:
             return self.final_layer(img, vec)
         x = torch.cat((txt, img), dim=1)
-        for blk in self.single_blocks:
-            x = blk(x, vec, cos, sin)
+        if run is None:
+            for blk in self.single_blocks:
+                x = blk(x, vec, cos, sin)
+        else:
+            x = run.single_stack(self.single_blocks, x, vec, cos, sin, Lt, first_index=len(self.double_blocks))
         return self.final_layer(x[:, Lt:], vec)
 
     def lora_targets(self):

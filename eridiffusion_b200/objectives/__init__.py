@@ -15,7 +15,11 @@ Reference behaviour reproduced here:
   (crates/training/src/sd35_trainer_impl.rs:146-169, 234-290);
 * DDPM: 1000 steps, scaled-linear betas 0.00085 -> 0.012, eps / v / x0 targets, zero-terminal-SNR,
   alpha-bar clamped to [1e-8, 0.999] (crates/training/src/pipelines/sdxl_pipeline.rs:52-194);
-* min-SNR-gamma weight ``min(snr, gamma) / snr`` (src/trainers/snr_weighting.rs:23-74).
+* min-SNR-gamma weight ``min(snr, gamma) / snr`` (src/trainers/snr_weighting.rs:23-74);
+* the phase-4 FLUX trainer's additive-noise eps objective ``x_t = x0 + sigma eps``, target ``eps``,
+  ``sigma = sigma_min r^{-t}`` with ``r = max(sigma_max / sigma_min, 1 + 1e-6)``, t uniform in
+  [0, 1), sigma clamped to [1e-3, 1] (crates/training/src/flux_trainer.rs:312-325, 410-414;
+  crates/training/src/policy.rs:90-95).
 """
 from __future__ import annotations
 
@@ -95,6 +99,40 @@ class FlowMatching:
 
     def model_time(self, t):
         return t
+
+
+# ------------------------------------------------------------------------- phase-4 eps objective
+@dataclass
+class SigmaEps:
+    """Additive-noise epsilon prediction of the reference's phase-4 FLUX LoRA trainer: the clean
+    latent is NOT scaled down, ``x_t = x0 + sigma(t) eps`` and the network regresses ``eps`` under a
+    plain MSE. ``sigma(t) = sigma_min * r^{-t}`` (t uniform in [0, 1)) falls from ``sigma_min`` at
+    t = 0 towards ``sigma_min / r`` — the formula is kept exactly as the reference computes it,
+    including that ``sigma_max`` only enters through the ratio — and is then bounded to
+    [``floor``, ``ceil``] = [1e-3, 1]."""
+    sigma_min: float = 0.02
+    sigma_max: float = 1.0
+    floor: float = 1e-3
+    ceil: float = 1.0
+
+    def sample_t(self, n, gen=None, device="cpu"):
+        return sample_uniform(n, gen, device)
+
+    def sigma(self, t):
+        ratio = max(self.sigma_max / self.sigma_min, 1.0 + 1e-6)
+        return (self.sigma_min * torch.exp(-t.float() * math.log(ratio))).clamp(self.floor, self.ceil)
+
+    def coefficients(self, t):
+        """[4, B] rows (a, s, ca, cb): x_t = x0 + sigma eps, target = eps."""
+        sg = self.sigma(t)
+        one, zero = torch.ones_like(sg), torch.zeros_like(sg)
+        return torch.stack([one, sg, one, zero]).float()
+
+    def loss_weight(self, t):
+        return None
+
+    def model_time(self, t):
+        return self.sigma(t)
 
 
 # ------------------------------------------------------------------------- DDPM family

@@ -149,14 +149,35 @@ def tread_reinject(full, routed, idx, mode="scatter"):
 
 
 class TreadRouter:
-    """Applies a ``schedule`` [{out: i, in: j}, ...] to a list of blocks that map x -> x."""
+    """Applies a ``schedule`` [{out: i, in: j}, ...] to a list of blocks that map x -> x.
+
+    ``keep_prefix``: the first tokens of the sequence (the text tokens of a joint [text | image]
+    stream) are never routed out; the selection runs over the remaining tokens only. When a rotary
+    table accompanies the tokens, every sample of the micro-batch routes the SAME positions (scores
+    are averaged over the batch) so that one table slice serves the whole batch."""
 
     def __init__(self, schedule, k=None, k_frac=0.5, mask_type="topk_norm", reinject="scatter"):
         self.schedule = {int(p["out"]): int(p["in"]) for p in schedule}
         self.k, self.k_frac, self.mask_type, self.reinject = k, k_frac, mask_type, reinject
         self.kept_frac = {}
 
-    def run(self, blocks, x, step, rope=None):
+    def _select(self, x, keep_prefix, shared):
+        body = x[:, keep_prefix:]
+        if shared and body.shape[0] > 1 and self.mask_type in ("topk_norm", "attn_topk"):
+            L = body.shape[1]
+            k = self.k or max(1, int(L * self.k_frac))
+            score = body.float().pow(2).sum(-1).mean(0, keepdim=True)
+            idx = score.topk(k, dim=1).indices.sort(dim=1).values.expand(body.shape[0], k)
+        else:
+            idx = tread_select(body, self.k, self.k_frac, self.mask_type)
+            if shared and body.shape[0] > 1:
+                idx = idx[:1].expand(body.shape[0], idx.shape[1])
+        if keep_prefix:
+            pre = torch.arange(keep_prefix, device=x.device).unsqueeze(0).expand(x.shape[0], keep_prefix)
+            idx = torch.cat([pre, idx + keep_prefix], dim=1)
+        return idx.contiguous()
+
+    def run(self, blocks, x, step, rope=None, keep_prefix=0):
         """``step(block, x, cos, sin) -> x``; ``rope`` = (cos, sin) rows follow the routed tokens."""
         active = None          # (resume_layer, idx, saved_full)
         for i, blk in enumerate(blocks):
@@ -164,7 +185,7 @@ class TreadRouter:
                 x = tread_reinject(active[2], x, active[1], self.reinject)
                 active = None
             if active is None and i in self.schedule and self.schedule[i] > i:
-                idx = tread_select(x, self.k, self.k_frac, self.mask_type)
+                idx = self._select(x, keep_prefix, shared=rope is not None)
                 active = (self.schedule[i], idx, x)
                 x = tread_gather(x, idx)
                 self.kept_frac[i] = idx.shape[1] / active[2].shape[1]
@@ -176,4 +197,99 @@ class TreadRouter:
                 x = step(blk, x, *(rope or (None, None)))
         if active is not None:
             x = tread_reinject(active[2], x, active[1], self.reinject)
+        return x
+
+
+# ------------------------------------------------------------------------------ layer streaming
+class _StreamedBlock(torch.autograd.Function):
+    """One block of a streamed stack: forward runs without an autograd graph while the block's
+    frozen weights are resident (``BlockSwapManager`` window), backward makes them resident again,
+    re-runs the block with a graph and back-propagates through it. Streaming therefore implies
+    recomputation; the trainable adapter tensors are ordinary leaves and receive their gradients
+    from the inner backward (src/trainers/flux_layer_streaming.rs:395-771 streams per layer in both
+    directions the same way)."""
+
+    @staticmethod
+    def forward(ctx, mgr, idx, fn, n_args, *rest):
+        # rest = the block's call arguments followed by its trainable tensors. The latter are not
+        # used here; they are inputs so that autograd knows the output depends on them even when no
+        # activation requires a gradient yet (first block behind a frozen input projection).
+        args = rest[:n_args]
+        ctx.mgr, ctx.idx, ctx.fn, ctx.n_args, ctx.n_rest = mgr, idx, fn, n_args, len(rest)
+        ctx.is_tensor = [torch.is_tensor(a) for a in args]
+        ctx.consts = [None if torch.is_tensor(a) else a for a in args]
+        ctx.save_for_backward(*[a for a in args if torch.is_tensor(a)])
+        with torch.no_grad():
+            out = mgr.run(idx, lambda b: fn(b, *args))
+        ctx.tuple_out = isinstance(out, tuple)
+        return out
+
+    @staticmethod
+    def backward(ctx, *douts):
+        it = iter(ctx.saved_tensors)
+        args = []
+        for flag, const, need in zip(ctx.is_tensor, ctx.consts, ctx.needs_input_grad[4:4 + ctx.n_args]):
+            if flag:
+                t = next(it).detach()
+                if need and t.is_floating_point():
+                    t.requires_grad_()
+                args.append(t)
+            else:
+                args.append(const)
+        with torch.enable_grad():
+            out = ctx.mgr.run(ctx.idx, lambda b: ctx.fn(b, *args), direction=-1)
+        outs = out if ctx.tuple_out else (out,)
+        pairs = [(o, g) for o, g in zip(outs, douts) if g is not None and o.requires_grad]
+        # the trainable tensors are leaves: this inner backward adds to their .grad directly
+        torch.autograd.backward([o for o, _ in pairs], [g for _, g in pairs])
+        grads = [a.grad if (torch.is_tensor(a) and a.requires_grad) else None for a in args]
+        return (None, None, None, None, *grads, *([None] * (ctx.n_rest - ctx.n_args)))
+
+
+def _streamed(mgr, idx, blk, *args):
+    params = [p for p in blk.parameters() if p.requires_grad]
+    return _StreamedBlock.apply(mgr, idx, lambda b, *a: b(*a), len(args), *args, *params)
+
+
+class BlockRunner:
+    """How the blocks of an MMDiT-style stack execute during training. A model consults its
+    ``runner`` (when one is attached) instead of calling the blocks directly:
+
+    * ``policy``: activation handling per block — ``none``, ``recompute``, ``cpu_offload`` (block
+      inputs parked in pinned host memory), ``adaptive`` (crates/training/src/gradient_checkpointing.rs:
+      76-140, src/trainers/gpu_gradient_checkpoint.rs:165-188);
+    * ``streamer``: a ``memory.BlockSwapManager`` over ALL blocks (double first, then single): frozen
+      weights live in pinned host memory and a window of blocks is resident (layer streaming with
+      persistent blocks, src/trainers/flux_layer_streaming.rs:65-131);
+    * ``tread``: a ``TreadRouter`` applied to the single-stream stack, text tokens always kept
+      (crates/training/src/tread.rs:140-248).
+    """
+
+    def __init__(self, policy="none", streamer=None, tread=None):
+        self.policy, self.streamer, self.tread = policy, streamer, tread
+
+    def double(self, i, blk, img, txt, vec, cos, sin):
+        if self.streamer is not None and torch.is_grad_enabled():
+            return _streamed(self.streamer, i, blk, img, txt, vec, cos, sin)
+        if self.streamer is not None:
+            return self.streamer.run(i, lambda b: b(img, txt, vec, cos, sin))
+        if self.policy != "none" and torch.is_grad_enabled():
+            return ckpt.checkpoint(blk, img, txt, vec, cos, sin, use_reentrant=False)
+        return blk(img, txt, vec, cos, sin)
+
+    def _single(self, i, blk, x, vec, cos, sin):
+        if self.streamer is not None and torch.is_grad_enabled():
+            return _streamed(self.streamer, i, blk, x, vec, cos, sin)
+        if self.streamer is not None:
+            return self.streamer.run(i, lambda b: b(x, vec, cos, sin))
+        return run_block(blk, x, vec, cos, sin, policy=self.policy, slot=i)
+
+    def single_stack(self, blocks, x, vec, cos, sin, txt_len, first_index=0):
+        index = {id(b): first_index + j for j, b in enumerate(blocks)}
+        step = lambda blk, h, c, s: self._single(index[id(blk)], blk, h, vec, c, s)
+        if self.tread is not None and torch.is_grad_enabled():
+            return self.tread.run(list(blocks), x, step, rope=(cos, sin) if cos is not None else None,
+                                  keep_prefix=txt_len)
+        for blk in blocks:
+            x = step(blk, x, cos, sin)
         return x

@@ -26,7 +26,7 @@ import torch
 from ..adapters import (AdapterConfig, adapter_parameters, adapter_state_dict, inject_adapters,
                         load_adapter_state_dict)
 from ..io import safetensors as st
-from ..objectives import DDPM, FlowMatching, loss_fn
+from ..objectives import DDPM, FlowMatching, SigmaEps, loss_fn
 from ..ops import functional as F
 from ..optim import EMA, GradScaler, LRSchedule, ParamArena, create_optimizer
 
@@ -35,7 +35,9 @@ from ..optim import EMA, GradScaler, LRSchedule, ParamArena, create_optimizer
 class TrainerConfig:
     mode: str = "lora"                      # lora | full
     adapter: AdapterConfig | None = None
-    objective: str = "flow"                 # flow | eps | v | sample
+    objective: str = "flow"                 # flow | eps | v | sample | sigma_eps (x0 + sigma eps, target eps)
+    sigma_min: float = 0.02                 # sigma_eps: sigma = sigma_min * (sigma_max / sigma_min)^(-t)
+    sigma_max: float = 1.0
     timestep_sampler: str = "logit_normal"
     timestep_kw: dict = field(default_factory=dict)
     guidance: float | None = 3.5            # value fed to the guidance embedder (None: 1.0)
@@ -66,6 +68,10 @@ class TrainerConfig:
     nan_policy: str = "skip"                # skip | raise
     lr_backoff: float = 0.5
     activation_checkpointing: bool = False
+    # {"contains", "target_mult", "warmup_steps", "kind"}: the LR multiplier of parameters whose name
+    # contains ``contains`` moves from its base value to ``target_mult`` over ``warmup_steps``
+    # optimizer steps ("linear" or "cosine"; src/trainers/flux_layer_streaming.rs:362-392)
+    lr_ramp: dict | None = None
 
 
 class Trainer:
@@ -102,7 +108,12 @@ class Trainer:
         # per-layer learning rates and block rotation act through the 8-bit optimizer's per-block
         # multiplier (single-process and ZeRO-1 sharded optimizers; the fused DP kernel has none)
         self.rotator = None
-        if (cfg.lr_if_contains or cfg.rotate_window) and hasattr(self.optimizer, "lr_scale") and not (
+        self._ramp_done = cfg.lr_ramp is None
+        if cfg.lr_ramp is not None and (not hasattr(self.optimizer, "lr_scale") or (
+                grad_sync is not None and grad_sync.fused_optimizer)):
+            raise ValueError("lr_ramp needs an optimizer with per-block learning-rate multipliers (adamw8bit, "
+                             "not the fused data-parallel step)")
+        if (cfg.lr_if_contains or cfg.rotate_window or cfg.lr_ramp) and hasattr(self.optimizer, "lr_scale") and not (
                 grad_sync is not None and grad_sync.fused_optimizer):
             from ..optim.arena import block_lr_scale
             self._lr_shard = shard
@@ -112,13 +123,15 @@ class Trainer:
                 self.rotator = LayerRotator(self.param_names, cfg.rotate_window, cfg.rotate_period, n_double)
                 self.rotator.apply(self.optimizer, self.arena, 0, cfg.lr_if_contains, shard)
             else:
-                self.optimizer.lr_scale = block_lr_scale(self.arena, self.param_names, cfg.lr_if_contains,
+                self.optimizer.lr_scale = block_lr_scale(self.arena, self.param_names, self.lr_rules(0),
                                                          shard=shard)
         self.schedule = LRSchedule(cfg.lr, cfg.lr_schedule, cfg.warmup_steps, cfg.total_steps)
         self.scaler = GradScaler(enabled=False)
         self.ema = EMA(self.arena, cfg.ema_decay) if cfg.ema_decay else None
         if cfg.objective == "flow":
             self.objective = FlowMatching(cfg.timestep_sampler, cfg.timestep_kw)
+        elif cfg.objective == "sigma_eps":
+            self.objective = SigmaEps(cfg.sigma_min, cfg.sigma_max)
         else:
             pred = {"eps": "epsilon", "v": "v", "sample": "sample"}[cfg.objective]
             self.objective = DDPM(prediction=pred, min_snr_gamma=cfg.min_snr_gamma)
@@ -135,6 +148,20 @@ class Trainer:
         # ``trainer.phases.summary()``; off unless ERI_B200_PHASE_TIMING=1
         from ..utils.trace import PhaseTimer
         self.phases = PhaseTimer(enabled=os.environ.get("ERI_B200_PHASE_TIMING") == "1")
+
+    def lr_rules(self, step):
+        """``lr_if_contains`` with the ramp applied: during the warm-up the multiplier of the ramped
+        parameters is ``base * (1 - f) + target * f`` with ``f`` the linear or half-cosine progress."""
+        rules = dict(self.cfg.lr_if_contains or {})
+        ramp = self.cfg.lr_ramp
+        if ramp is None:
+            return rules
+        prog = min(1.0, step / max(1, ramp["warmup_steps"]))
+        f = 0.5 * (1.0 - math.cos(prog * math.pi)) if ramp.get("kind") == "cosine" else prog
+        key = ramp["contains"]
+        base = next((float(m) for sub, m in rules.items() if sub in key or key in sub), 1.0)
+        # the ramp rule goes first: block_lr_scale takes the first rule a name contains
+        return {key: base * (1.0 - f) + float(ramp["target_mult"]) * f, **{k: v for k, v in rules.items() if k != key}}
 
     # ------------------------------------------------------------------ one micro-step
     def _generator(self, device):
@@ -180,6 +207,11 @@ class Trainer:
         lr = self.schedule.apply(self.optimizer, self.step)
         if self.rotator is not None:
             self.rotator.apply(self.optimizer, self.arena, self.step, cfg.lr_if_contains, self._lr_shard)
+        elif not self._ramp_done:
+            from ..optim.arena import block_lr_scale
+            self.optimizer.lr_scale = block_lr_scale(self.arena, self.param_names, self.lr_rules(self.step),
+                                                     shard=self._lr_shard)
+            self._ramp_done = self.step >= cfg.lr_ramp["warmup_steps"]
         if self.grad_sync is not None and self.grad_sync.fused_optimizer:
             # reduce-scatter + clip + 8-bit AdamW + all-gather in the communication kernel
             self.grad_sync.reduce_and_step(lr=lr, max_grad_norm=cfg.max_grad_norm, step=self.step + 1)

@@ -59,7 +59,7 @@ def test_config_both_schemas(tmp_path):
         p = tmp_path / f"train_{kind}.yaml"
         p.write_text(text)
         flat = C.load_config(p)
-        assert flat.model.kind == kind and flat.steps == 10 and flat.optimizer == "adamw"
+        assert flat.model.kind == C.MODEL_KIND_ALIASES.get(kind, kind) and flat.steps == 10 and flat.optimizer == "adamw"
     with pytest.raises(C.ConfigError):
         C.load_config({"model_kind": "flux", "lr": 1.0})
     with pytest.raises(C.ConfigError):
