@@ -307,15 +307,23 @@ def adapter_parameters(adapters: dict):
     return ps
 
 
-def adapter_state_dict(adapters: dict, layout: str = "eri"):
+def adapter_state_dict(adapters: dict, layout: str = "eri", model=None, strict: bool = True):
     """Flatten adapter tensors under one of the supported key layouts:
 
+    * ``phase4`` / ``stable`` / ``sdxl`` : the reference's per-site names (``lora.block{NN}.attn.q.
+      lora.A`` ...; see ``adapters.reference_keys``); these need ``model`` to number the blocks and
+      split the fused projections
     * ``eri``   : ``lora.{path}.lora.A`` / ``.lora.B`` (phase-4 layout,
       crates/training/src/flux_trainer.rs:633-666); non-LoRA kinds use ``lora.{path}.{leaf}``
     * ``peft``  : ``{path}.lora_A.weight`` / ``.lora_B.weight`` (src/networks/lora.rs:193-194)
     * ``kohya`` : ``lora_unet_{path_with_underscores}.lora_down.weight`` / ``.lora_up.weight`` /
       ``.alpha`` (src/networks/lora_flame.rs:274-285, src/networks/sd_lora.rs:175-176)
     """
+    if layout in ("phase4", "stable", "sdxl"):
+        from .reference_keys import reference_state_dict
+        if model is None:
+            raise ValueError(f"the {layout} layout needs the model (block numbering, fused projections)")
+        return reference_state_dict(adapters, model, layout, strict=strict)[0]
     sd = {}
     for path in sorted(adapters):
         ad = adapters[path]
@@ -382,7 +390,15 @@ def load_adapters_into(model: nn.Module, path, alpha: float | None = None, stric
     rank is read from the first down-projection tensor, ``alpha`` from the file when it carries
     one (kohya layout), else it defaults to the rank. Returns the adapter dict."""
     from ..io import safetensors as st
+    from .reference_keys import detect_layout, load_reference_lora
     sd = st.load_file(path)
+    ref_layout = detect_layout(sd.keys())
+    if ref_layout is not None:
+        # a file written by the reference (per-site names): sites are stacked into the fused adapters
+        if alpha is None:
+            md = st.read_metadata(path) or {}
+            alpha = float(md["alpha"]) if md.get("alpha") not in (None, "") else None
+        return load_reference_lora(model, sd, ref_layout, alpha=alpha, strict=strict)
     down = next((v for k, v in sd.items() if k.endswith(("lora.A", "lora_A.weight", "lora_down.weight"))), None)
     if down is None:
         raise KeyError(f"{path}: no LoRA down-projection tensor found")

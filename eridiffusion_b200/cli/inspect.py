@@ -28,6 +28,10 @@ _LAYOUTS = (
     ("vae", r"^(first_stage_model\.|encoder\.down|decoder\.up)"),
 )
 _ADAPTER = (
+    # the reference's per-site names come first: "lora.block03.attn.q.lora.A" also ends in ".lora.A"
+    ("lora (reference phase-4 keys: lora.blockNN.attn.q.lora.A)", r"^lora\.block\d+\.(attn|mlp)\.\w+\.lora\.[AB]$"),
+    ("lora (reference stable keys: lora.blocks.NN.attn.q.A)", r"^lora\.blocks\.(\d+|mid)\.(attn|mlp)\.\w+\.[AB]$"),
+    ("lora (reference SDXL keys: blocks.NN.attn1.to_q.A)", r"^blocks\.\d+\.attn[12]\.to_(q|k|v|out\.0)\.[AB]$"),
     ("lora (eri keys)", r"\.lora\.(A|B)$"), ("lora (PEFT keys)", r"\.lora_(A|B)\.weight$"),
     ("lora (kohya keys)", r"\.lora_(down|up)\.weight$"), ("loha", r"\.hada_w[12]_[ab]$"), ("lokr", r"\.lokr_w[12]"),
     ("dora", r"\.(dora_scale|magnitude)$"), ("ia3", r"\.ia3_"),
@@ -58,8 +62,9 @@ def summarise(path) -> dict:
     except ValueError:
         out["model_type_from_path"] = None
     blocks = {}
-    for name in ("double_blocks", "single_blocks", "joint_blocks", "transformer_blocks", "blocks", "layers"):
-        idx = {int(m.group(1)) for k in keys if (m := re.search(rf"(?:^|\.){name}\.(\d+)\.", k))}
+    for name in ("double_blocks", "single_blocks", "joint_blocks", "transformer_blocks", "blocks", "layers", "block"):
+        sep = "" if name == "block" else r"\."          # the phase-4 LoRA names write "block03"
+        idx = {int(m.group(1)) for k in keys if (m := re.search(rf"(?:^|\.){name}{sep}(\d+)\.", k))}
         if idx:
             blocks[name] = max(idx) + 1
     out["blocks"] = blocks
@@ -68,9 +73,9 @@ def summarise(path) -> dict:
         ranks = Counter()
         targets = set()
         for k, (dt, shape) in entries.items():
-            if re.search(r"(lora\.A|lora_A\.weight|lora_down\.weight)$", k) and len(shape) >= 2:
+            if re.search(r"(lora\.A|lora_A\.weight|lora_down\.weight|\.A)$", k) and len(shape) >= 2:
                 ranks[shape[0]] += 1
-                targets.add(re.sub(r"\.(lora\.A|lora_A\.weight|lora_down\.weight)$", "", k).split(".")[-1])
+                targets.add(re.sub(r"\.(lora\.A|lora_A\.weight|lora_down\.weight|A)$", "", k).split(".")[-1])
         out["adapter"] = {"kind": kind, "ranks": dict(ranks), "targets": sorted(targets)}
     out["_entries"] = entries
     return out

@@ -110,9 +110,13 @@ def save_training_checkpoint(trainer, root):
                 "ema_file": None, "world_size": world,
                 "optimizer_files": [f"optimizer.rank{r}.safetensors" for r in range(world)]}
         if rank == 0:
-            sd = adapter_state_dict(trainer.adapters, "eri")
+            layout = getattr(cfg, "lora_layout", "eri") or "eri"
+            sd = adapter_state_dict(trainer.adapters, layout, model=trainer.model)
+            acfg = cfg.adapter
             st.save_file({k: v.to(torch.bfloat16) for k, v in sd.items()}, d / "lora.safetensors",
-                         {"step": step, "seed": cfg.seed, "dtype_policy": "storage=bf16,compute=fp32"})
+                         {"step": step, "seed": cfg.seed, "dtype_policy": "storage=bf16,compute=fp32",
+                          "layout": layout, "rank": acfg.rank if acfg else "",
+                          "alpha": (acfg.alpha if acfg and acfg.alpha else (acfg.rank if acfg else ""))})
             if trainer.ema is not None:
                 st.save_file(trainer.ema.state_dict(trainer.param_names), d / "ema.safetensors",
                              {"step": step, "seed": cfg.seed, "ema_decay": trainer.ema.decay})
@@ -232,7 +236,12 @@ def _load_checkpoint_dir(trainer, d):
     if trainer.adapters is not None:
         meta = json.loads((d / "meta.json").read_text())
         sd = st.load_file(d / meta["lora_file"], device=dev)
-        load_adapter_state_dict(trainer.adapters, sd, strict=True)
+        from ..adapters.reference_keys import detect_layout, fill_adapters_from_reference
+        ref_layout = detect_layout(sd.keys())
+        if ref_layout is not None:
+            fill_adapters_from_reference(trainer.adapters, trainer.model, sd, ref_layout)
+        else:
+            load_adapter_state_dict(trainer.adapters, sd, strict=True)
         if trainer.ema is not None and meta.get("ema_file"):
             trainer.ema.load_state_dict(st.load_file(d / meta["ema_file"], device=dev), trainer.param_names)
         step, seed = int(meta["step"]), int(meta["seed"])
@@ -301,9 +310,10 @@ def reshard_8bit_state(files, new_rank: int, new_world: int, shard_numel: int, b
     return out
 
 
-def export_lora(trainer, path, layout="kohya"):
-    """Single-file export for other tools (kohya / ComfyUI / PEFT key conventions)."""
-    sd = adapter_state_dict(trainer.adapters, layout)
+def export_lora(trainer, path, layout="kohya", strict=True):
+    """Single-file export for other tools: kohya / ComfyUI / PEFT key conventions, or the reference's
+    per-site names (``phase4``: ``lora.block{NN}.attn.q.lora.A`` ..., ``stable``, ``sdxl``)."""
+    sd = adapter_state_dict(trainer.adapters, layout, model=trainer.model, strict=strict)
     acfg = trainer.cfg.adapter
     st.save_file({k: v.to(torch.bfloat16) if v.dim() else v.float() for k, v in sd.items()}, path,
                  {"format": "eridiffusion", "network_type": acfg.kind if acfg else "lora",

@@ -72,6 +72,9 @@ class TrainerConfig:
     # contains ``contains`` moves from its base value to ``target_mult`` over ``warmup_steps``
     # optimizer steps ("linear" or "cosine"; src/trainers/flux_layer_streaming.rs:362-392)
     lr_ramp: dict | None = None
+    # tensor names of lora.safetensors in checkpoints: "eri" (module paths; every adapter kind) or
+    # the reference's per-site names "phase4" / "stable" / "sdxl" (plain LoRA on sites that have one)
+    lora_layout: str = "eri"
 
 
 class Trainer:
