@@ -520,6 +520,22 @@ ENV_VARS = {
     "SDXL_TIMING / SDXL_LOAD_TRACE / BACKWARD_DEBUG": "1: phase breakdown, load GiB/s, anomaly mode + gradient report",
     "ERID_PINNED_CHECKPOINT_CACHE_MB": "pinned staging cache for checkpoint writes, MiB",
     "AI_TOOLKIT_<SECTION>__<KEY>": "override of a universal-schema document (config/universal.py)",
+    "FLUX_FORCE_DENSE_ATTENTION": "1: dense library attention instead of the flash kernels",
+    "STREAMING_SDPA_CHUNK_MAX / ATTN_CHUNK_SIZE / ATTN_MAX_WORKSPACE_MB / ATTN_CHUNK_REUSE":
+        "blockwise library attention: key-block size, workspace cap, shared workspace",
+    "STREAM_ATTENTION_SELFTEST": "1: compare blockwise with dense attention once at start-up",
+    "STREAM_ATTENTION_CAUSAL_TEXT": "refused (no causal text mask)",
+    "ERID_FUSE": "1 fused kernels (default) | 0 unfused PyTorch statements",
+    "STRICT_BF16": "1 | panic: strict-bf16 counters around every training step",
+    "GRADIENT_CHECKPOINT_POLICY": "recompute | cpu_offload | adaptive (+ GRADIENT_CHECKPOINT_MEMORY_THRESHOLD_MB, "
+                                  "GRADIENT_CHECKPOINT_PREFER_RECOMPUTE)",
+    "DISABLE_LAYER_STREAMING": "1: ignore use_layer_streaming",
+    "TREAD_ENABLED / TREAD_MASK_TYPE / TREAD_K / TREAD_K_FRAC / TREAD_SCHEDULE / TREAD_REINJECT_MODE / TREAD_LAMBDA":
+        "override the tread block (schedule as out:in,out:in)",
+    "ERI_B200_WGRAD": "native | library: weight-gradient GEMMs on tcgen05 or torch",
+    "ERI_B200_SCATTER_PAIR": "1 | 0: peer-scatter epilogue on the two-CTA kernel",
+    "ERI_B200_GLU_FUSED": "1 | 0: GEGLU / SwiGLU in the up-projection GEMM epilogue",
+    "ERI_B200_DEBUG_BOUNDS": "1: build and load the bounds-checked debug variant of the kernel library",
     "TRAIN_LOG_CSV": "per-step CSV path (step,loss,grad_norm,sec_per_it,alloc_mb,ckpt_path)",
     "CKPT_EVERY": "checkpoint interval override",
     "EXPECT_STEP_SEC": "fail the run when a step is slower than this many seconds",
@@ -530,6 +546,14 @@ ENV_VARS = {
 def apply_env(cfg: TrainCfg):
     if os.environ.get("CKPT_EVERY"):
         cfg.ckpt_every = int(os.environ["CKPT_EVERY"])
+    # the reference's behaviour switches (attention mode, fusion, checkpoint policy, TREAD_*, ...)
+    from ..utils.env_flags import ReferenceEnvError, apply_reference_env
+    try:
+        applied = apply_reference_env(cfg, print_fn=lambda *_: None)
+    except ReferenceEnvError as e:
+        raise ConfigError(str(e)) from e
+    if applied:
+        cfg.meta["reference_env"] = applied
     return cfg
 
 

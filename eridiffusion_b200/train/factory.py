@@ -61,7 +61,8 @@ def _block_runner(cfg: TrainCfg, model, dev, cuda: bool):
     from .act_checkpoint import BlockRunner, TreadRouter
     policy = "none"
     if cfg.gradient_checkpointing:
-        policy = "cpu_offload" if (cfg.model.low_vram and cuda) else "recompute"
+        # GRADIENT_CHECKPOINT_POLICY (recorded by config.apply_env) wins; low_vram parks block inputs on the host
+        policy = cfg.meta.get("checkpoint_policy") or ("cpu_offload" if (cfg.model.low_vram and cuda) else "recompute")
     streamer = None
     if cfg.use_layer_streaming:
         from ..memory import BlockSwapConfig, BlockSwapManager
@@ -287,6 +288,7 @@ def build_job(cfg: TrainCfg, device=None):
         fwd = sdxl_forward
     trainer = Trainer(model, tcfg, grad_sync=grad_sync, forward_fn=fwd)
     trainer.extra_status_sources = status_sources
+    trainer.strict_bf16 = cfg.meta.get("strict_bf16")       # None | "count" | "panic" (STRICT_BF16)
     # activation policy / layer streaming / token routing are attached after the adapters exist, so
     # that the streamer sees which tensors are trainable
     recompute_blocks = 0

@@ -179,6 +179,18 @@ class Trainer:
     def train_step(self, batch: dict):
         """batch: ``latents`` [B, C, H, W] plus the conditioning tensors the model's forward
         function consumes. Returns the (device) loss tensor of this micro-batch."""
+        mode = getattr(self, "strict_bf16", None)
+        if mode:
+            # STRICT_BF16: count (or refuse) clones, layout-fixing copies and fp32 up-casts of
+            # activations during the step; the totals are in ``self.strict_events``
+            from ..utils.strict import strict_scope
+            with strict_scope(panic=mode == "panic", reset=False) as c:
+                out = self._train_step(batch)
+            self.strict_events = c.snapshot()
+            return out
+        return self._train_step(batch)
+
+    def _train_step(self, batch: dict):
         cfg = self.cfg
         x0 = batch["latents"]
         B = x0.shape[0]

@@ -16,6 +16,28 @@
 
 The native flash-attention kernels never materialise scores, so the ``ATTN_*`` switches only act on
 the library path (masks, unsupported head sizes, CPU).
+
+``apply_reference_env`` maps the switches that gate the reference's attention / fusion behaviour onto
+this package's own switches (or refuses them by name when nothing here corresponds):
+
+* ``FLUX_FORCE_DENSE_ATTENTION`` (crates/training/src/flux/runtime.rs:484-486) -> dense library
+  attention instead of the flash kernels;
+* ``STREAMING_SDPA_CHUNK_MAX`` / ``ATTN_CHUNK_SIZE`` (runtime.rs:210, 488-520; default cap 2048 keys)
+  -> blockwise library attention with that key-block size; ``ATTN_MAX_WORKSPACE_MB`` and
+  ``ATTN_CHUNK_REUSE`` are the reference's spellings of ``ATTN_MAX_WS_MB`` / ``ATTN_REUSE``;
+* ``STREAM_ATTENTION_SELFTEST`` -> blockwise vs dense attention compared once at start-up;
+* ``STREAM_ATTENTION_CAUSAL_TEXT`` -> refused: there is no causal text mask here;
+* ``STREAM_ATTENTION_LOG_ALLOCS`` / ``STREAM_ATTENTION_DEBUG_WRITES`` / ``ATTN_LOG_MS`` -> noted as
+  having no effect (no score workspace is ever allocated on the native path);
+* ``ERID_FUSE`` (crates/core/src/layers/norms.rs:5-12, mlp.rs:45-56): ``0`` selects the unfused
+  PyTorch statements (``ERI_B200_BACKEND=eager``), ``1`` the fused kernels (the default here);
+* ``STRICT_BF16=1`` -> the strict-bf16 counters run around every training step and a violation
+  count is reported with the log row (``=panic`` raises at the first event);
+* ``GRADIENT_CHECKPOINT_POLICY`` = ``recompute | cpu_offload | adaptive``
+  (src/trainers/gpu_gradient_checkpoint.rs:165-188) -> activation policy of the block runner, with
+  ``GRADIENT_CHECKPOINT_MEMORY_THRESHOLD_MB`` / ``GRADIENT_CHECKPOINT_PREFER_RECOMPUTE`` for the
+  adaptive choice;
+* ``DISABLE_LAYER_STREAMING=1`` -> ``use_layer_streaming`` off; ``TREAD_*`` -> the ``tread`` block.
 """
 from __future__ import annotations
 
@@ -162,3 +184,105 @@ def backward_debug(named_params=None, print_fn=print):
 
 def pinned_checkpoint_cache_bytes(default_mb: int = 256) -> int:
     return (_int("ERID_PINNED_CHECKPOINT_CACHE_MB", default_mb)) << 20
+
+
+# ------------------------------------------------------------------------------- reference switches
+_NO_EFFECT = ("STREAM_ATTENTION_LOG_ALLOCS", "STREAM_ATTENTION_DEBUG_WRITES", "ATTN_LOG_MS")
+_REFUSED = {"STREAM_ATTENTION_CAUSAL_TEXT": "causal text masks are not implemented (attention here is non-causal; "
+                                            "key-padding masks are supported)"}
+
+
+class ReferenceEnvError(RuntimeError):
+    """An environment switch of the reference asks for behaviour that does not exist here."""
+
+
+def _truthy(v) -> bool:
+    return str(v).lower() in ("1", "true", "on", "yes")
+
+
+def adaptive_checkpoint_settings():
+    """(memory threshold in bytes, prefer recompute) of ``GRADIENT_CHECKPOINT_POLICY=adaptive``."""
+    mb = max(1, _int("GRADIENT_CHECKPOINT_MEMORY_THRESHOLD_MB", 8192))
+    prefer = _truthy(os.environ.get("GRADIENT_CHECKPOINT_PREFER_RECOMPUTE", "1"))
+    return mb << 20, prefer
+
+
+def apply_reference_env(cfg=None, environ=None, print_fn=print) -> dict:
+    """Apply the reference's behaviour switches found in ``environ`` (default ``os.environ``) to this
+    package's module-level switches and, when given, to a loaded ``TrainCfg``. Returns what was
+    applied as ``{variable: effect}``; raises ``ReferenceEnvError`` for a switch that cannot be
+    honoured."""
+    env = os.environ if environ is None else environ
+    done = {}
+    for name, why in _REFUSED.items():
+        if _truthy(env.get(name, "")):
+            raise ReferenceEnvError(f"{name}: {why}")
+    for name in _NO_EFFECT:
+        if env.get(name):
+            done[name] = "no effect: the native attention allocates no score workspace"
+            print_fn(f"[env] {name} is set but has no effect here ({done[name][11:]})")
+    from ..ops import functional as F
+    if _truthy(env.get("FLUX_FORCE_DENSE_ATTENTION", "")):
+        F.set_attention_impl("library")
+        done["FLUX_FORCE_DENSE_ATTENTION"] = "attention -> dense library path"
+    chunk = env.get("STREAMING_SDPA_CHUNK_MAX") or env.get("ATTN_CHUNK_SIZE")
+    if chunk:
+        n = int(chunk)
+        if n < 16:
+            raise ReferenceEnvError(f"attention chunk size {n} is below 16 keys")
+        os.environ.setdefault("ATTN_KV_CHUNK", str(n))
+        F.set_attention_impl("library")
+        F._ATTN_ENV_POLICY = True
+        done["STREAMING_SDPA_CHUNK_MAX" if env.get("STREAMING_SDPA_CHUNK_MAX") else "ATTN_CHUNK_SIZE"] = \
+            f"blockwise library attention, {n}-key blocks"
+    for ref, ours in (("ATTN_MAX_WORKSPACE_MB", "ATTN_MAX_WS_MB"), ("ATTN_CHUNK_REUSE", "ATTN_REUSE")):
+        if env.get(ref):
+            os.environ.setdefault(ours, env[ref])
+            F._ATTN_ENV_POLICY = True
+            done[ref] = f"-> {ours}"
+    if _truthy(env.get("STREAM_ATTENTION_SELFTEST", "")):
+        from ..ops import reference as R
+        g = torch.Generator().manual_seed(0)
+        q, k, v = (torch.randn(1, 96, 2, 32, generator=g) for _ in range(3))
+        err = (R.attention_chunked(q, k, v, None, 32, 32) - R.attention_fp32(q, k, v)).abs().max().item()
+        if err > 1e-4:
+            raise ReferenceEnvError(f"STREAM_ATTENTION_SELFTEST: blockwise attention differs from dense by {err:.2e}")
+        done["STREAM_ATTENTION_SELFTEST"] = f"passed (max difference {err:.1e})"
+    fuse = env.get("ERID_FUSE")
+    if fuse is not None and fuse != "":
+        F.set_backend("fused" if fuse == "1" else "eager")
+        done["ERID_FUSE"] = f"backend -> {F.get_backend()}"
+    strict = env.get("STRICT_BF16", "")
+    if strict and strict != "0":
+        done["STRICT_BF16"] = "panic" if strict.lower() == "panic" else "count"
+    pol = env.get("GRADIENT_CHECKPOINT_POLICY", "").lower()
+    if pol:
+        policy = {"cpu": "cpu_offload", "cpu_offload": "cpu_offload", "cpu-offload": "cpu_offload",
+                  "adaptive": "adaptive"}.get(pol, "recompute")
+        if pol not in ("cpu", "cpu_offload", "cpu-offload", "adaptive", "recompute"):
+            print_fn(f"[env] unknown GRADIENT_CHECKPOINT_POLICY={pol!r}: using recompute")
+        done["GRADIENT_CHECKPOINT_POLICY"] = policy
+        if cfg is not None:
+            cfg.gradient_checkpointing = True
+            cfg.meta["checkpoint_policy"] = policy
+    if cfg is not None:
+        if _truthy(env.get("DISABLE_LAYER_STREAMING", "")) and cfg.use_layer_streaming:
+            cfg.use_layer_streaming = False
+            done["DISABLE_LAYER_STREAMING"] = "use_layer_streaming -> false"
+        if "STRICT_BF16" in done:
+            cfg.meta["strict_bf16"] = done["STRICT_BF16"]
+        t = cfg.tread
+        if env.get("TREAD_ENABLED") is not None and env.get("TREAD_ENABLED") != "":
+            t.enabled = _truthy(env["TREAD_ENABLED"])
+            done["TREAD_ENABLED"] = str(t.enabled)
+        for var, attr, cast in (("TREAD_MASK_TYPE", "mask_type", str), ("TREAD_K", "k", int), ("TREAD_K_FRAC", "k_frac", float),
+                                ("TREAD_REINJECT_MODE", "reinject", str), ("TREAD_LAMBDA", "route_lambda", float)):
+            if env.get(var):
+                setattr(t, attr, cast(env[var]))
+                done[var] = f"tread.{attr} = {getattr(t, attr)}"
+        if env.get("TREAD_SCHEDULE"):
+            # "out:in,out:in" pairs
+            t.schedule = [{"out": int(a), "in": int(b)} for a, b in
+                          (p.split(":") for p in env["TREAD_SCHEDULE"].split(",") if p)]
+            done["TREAD_SCHEDULE"] = str(t.schedule)
+    return done

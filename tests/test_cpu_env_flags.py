@@ -74,3 +74,51 @@ def test_attention_env_switch_reaches_op_in_fresh_process():
     r = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, env=env, timeout=120)
     assert r.returncode == 0, r.stderr[-400:]
     assert "(64, 16)" in r.stdout
+
+
+def test_reference_behaviour_switches_map_onto_this_package(monkeypatch):
+    """The reference's attention / fusion / checkpoint-policy switches change this package's
+    switches, or are refused by name."""
+    import eridiffusion_b200.config as C
+    from eridiffusion_b200.ops import functional as F
+    from eridiffusion_b200.utils.env_flags import ReferenceEnvError, apply_reference_env
+    monkeypatch.setattr(F, "_ATTN_NATIVE", "native")
+    monkeypatch.setattr(F, "_BACKEND", "fused")
+    monkeypatch.setattr(F, "_ATTN_ENV_POLICY", False)
+    for k in ("ATTN_KV_CHUNK", "ATTN_MAX_WS_MB", "ATTN_REUSE"):
+        monkeypatch.delenv(k, raising=False)
+    notes = []
+    done = apply_reference_env(environ={"FLUX_FORCE_DENSE_ATTENTION": "1", "ERID_FUSE": "0", "ATTN_LOG_MS": "1",
+                                        "STREAM_ATTENTION_SELFTEST": "1"}, print_fn=notes.append)
+    assert F._ATTN_NATIVE == "library" and F.get_backend() == "eager"
+    assert "passed" in done["STREAM_ATTENTION_SELFTEST"] and "no effect" in done["ATTN_LOG_MS"] and notes
+    F.set_backend("fused"); F.set_attention_impl("native")
+    done = apply_reference_env(environ={"STREAMING_SDPA_CHUNK_MAX": "2048", "ATTN_MAX_WORKSPACE_MB": "64",
+                                        "ATTN_CHUNK_REUSE": "1"}, print_fn=notes.append)
+    assert os.environ["ATTN_KV_CHUNK"] == "2048" and os.environ["ATTN_MAX_WS_MB"] == "64" and os.environ["ATTN_REUSE"] == "1"
+    assert F._ATTN_ENV_POLICY and F._ATTN_NATIVE == "library"
+    F.set_attention_impl("native")
+    with pytest.raises(ReferenceEnvError, match="CAUSAL_TEXT"):
+        apply_reference_env(environ={"STREAM_ATTENTION_CAUSAL_TEXT": "1"})
+    # through the configuration loader: checkpoint policy, streaming off, TREAD_* and strict bf16
+    for k, v in {"GRADIENT_CHECKPOINT_POLICY": "cpu", "DISABLE_LAYER_STREAMING": "1", "TREAD_ENABLED": "1",
+                 "TREAD_K_FRAC": "0.25", "TREAD_SCHEDULE": "2:5,7:9", "STRICT_BF16": "1"}.items():
+        monkeypatch.setenv(k, v)
+    cfg = C.load_config({"model_kind": "flux", "use_layer_streaming": True})
+    assert cfg.gradient_checkpointing and cfg.meta["checkpoint_policy"] == "cpu_offload" and not cfg.use_layer_streaming
+    assert cfg.tread.enabled and cfg.tread.k_frac == 0.25 and cfg.tread.schedule == [{"out": 2, "in": 5}, {"out": 7, "in": 9}]
+    assert cfg.meta["strict_bf16"] == "count" and "GRADIENT_CHECKPOINT_POLICY" in cfg.meta["reference_env"]
+    monkeypatch.setenv("STREAM_ATTENTION_CAUSAL_TEXT", "on")
+    with pytest.raises(C.ConfigError, match="CAUSAL_TEXT"):
+        C.load_config({"model_kind": "flux"})
+
+
+def test_strict_bf16_counts_events_of_a_training_step(monkeypatch):
+    import eridiffusion_b200.config as C
+    from eridiffusion_b200.train.factory import build_job
+    monkeypatch.setenv("STRICT_BF16", "1")
+    cfg = C.load_config({"model_kind": "tiny_mmdit", "device": "cpu", "datasets": [{"synthetic": True, "resolution": [256]}]})
+    tr, batches, _ = build_job(cfg, device="cpu")
+    assert tr.strict_bf16 == "count"
+    tr.train_step(next(batches))
+    assert set(tr.strict_events) == {"clone_allocs", "f32_graph_casts", "layout_fixes"}
