@@ -99,6 +99,54 @@ def reference_unavailable():
                        "pyproject.toml found', so it cannot be installed or run offline"}))
 
 
+def dp_parity(trainer, gs, rank, world, dev):
+    """One optimizer step from the SAME state and the same per-rank gradients, once through the fused
+    kernel (reduce-scatter + clip + AdamW8bit + all-gather in one launch over peer memory) and once
+    through NCCL reduce-scatter / all-reduce / all-gather around the plain optimizer kernel; returns
+    the largest absolute parameter difference over all ranks. Runs outside every timed region, with
+    stochastic rounding off (the two kernels seed it differently); the state is restored afterwards."""
+    import torch
+    import torch.distributed as dist
+    from eridiffusion_b200.ops import functional as F
+    opt, arena = trainer.optimizer, trainer.arena
+    state = (arena.data, opt.m_q, opt.v_q, opt.m_absmax, opt.v_absmax)
+    keep = [t.clone() for t in state]
+    sr, step0 = opt.stochastic_rounding, opt.step_count
+    opt.stochastic_rounding = False
+    g = torch.Generator(device=dev).manual_seed(777 + rank)
+    grad = (torch.randn(arena.numel, device=dev, generator=g) * 0.01).bfloat16()
+
+    def restore():
+        for t, k in zip(state, keep):
+            t.copy_(k)
+        opt.step_count = step0
+
+    arena.grad.copy_(grad)
+    torch.cuda.synchronize(); dist.barrier()
+    gs.reduce_and_step(lr=1e-4, max_grad_norm=1.0, step=step0 + 1)
+    torch.cuda.synchronize(); dist.barrier()
+    fused = arena.data.clone()
+    restore()
+    arena.grad.copy_(grad)
+    torch.cuda.synchronize(); dist.barrier()
+    pshard, gshard = arena.shard(rank, world)
+    gs.pg.reduce_scatter_into(gshard, arena.grad, avg=True)
+    ss = F.sumsq(gshard)
+    dist.all_reduce(ss)
+    opt.param_groups[0]["lr"] = 1e-4
+    opt.step(grad_sumsq=ss, max_grad_norm=1.0)
+    gs.pg.all_gather_into(arena.data, pshard)
+    torch.cuda.synchronize(); dist.barrier()
+    err = (fused.float() - arena.data.float()).abs().max()
+    ref = arena.data.float().abs().max()
+    dist.all_reduce(err, dist.ReduceOp.MAX)
+    restore()
+    opt.stochastic_rounding = sr
+    arena.zero_grad()
+    torch.cuda.synchronize(); dist.barrier()
+    return float(err), float(ref)
+
+
 def main():
     args = parse()
     if args.impl == "reference":
@@ -214,6 +262,11 @@ def main():
         dist.all_reduce(t, dist.ReduceOp.MAX)
     ms_max, ms2_max = t.tolist()
     err = F.gemm_error_check() if (cuda and args.impl == "ours") else 0
+    parity = None
+    if world > 1 and cuda and args.impl == "ours" and sync_mode == "fused":
+        parity = dp_parity(trainer, gs, rank, world, dev)
+        st = gs._fused.status()
+        err = err or st
     if rank == 0:
         gb = B * world
         value = gb * args.steps / (ms_max / 1e3)
@@ -229,7 +282,8 @@ def main():
                        "parallelism": f"dp{world}", "grad_sync": sync_mode if world > 1 else "none",
                        "optimizer": "adamw8bit (block-wise 256)", "lora_rank": rank_r,
                        "l2_policy": "working set (>=24 GB of weights per step) far exceeds the 126 MB L2; no explicit flush",
-                       "final_loss": final_loss, "kernel_error_word": err},
+                       "final_loss": final_loss, "kernel_error_word": err,
+                       **({"dp_parity_max_err": parity[0], "dp_parity_param_absmax": parity[1]} if parity else {})},
             "gpu_launches": launches,
         }
         if e2e:

@@ -1,7 +1,7 @@
 """Multi-GPU timing of the fused communication paths against their rooflines and against NCCL.
 
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 \
-        -m eridiffusion_b200.cli.comm_bench [--what fused_dp,zero3,ulysses] [--params 56000000]
+        -m eridiffusion_b200.cli.comm_bench [--what fused_dp,zero3,ulysses,link] [--params 56000000]
 
 Times are CUDA-event device times, max over ranks, median of the timed launches after warm-up.
 Rooflines (the slower of the two bounds is the target, as for any fused compute + collective):
@@ -242,6 +242,66 @@ def bench_ulysses(a, pg, rank, world, dev):
                               "two_cta_gather_launches": N_.require().eri_gemm2_gather_count(), **extra}))
 
 
+def bench_link(a, pg, rank, world, dev):
+    """Peer transfer rate by mechanism and CTA count: every rank moves 64 MiB between its own memory
+    and the next rank's at the same time (all links busy in both directions, as in a gather)."""
+    import ctypes as C
+    from ..parallel.symm import SymmetricHeap
+    lib = N_.require()
+    lib.eri_link_probe.argtypes = [C.c_int, C.c_void_p, C.c_void_p, C.c_longlong, C.c_int, C.c_void_p, C.c_int,
+                                   C.c_void_p, C.c_void_p, C.c_int, C.c_void_p]
+    lib.eri_link_probe.restype = C.c_int
+    nbytes = 64 << 20
+    heap = SymmetricHeap(2 * nbytes + (1 << 20), group=pg.group)
+    src_sym = heap.tensor((nbytes,), torch.uint8)
+    dst_sym = heap.tensor((nbytes,), torch.uint8)
+    src_sym.local.random_(0, 255)
+    local_dst = torch.empty(nbytes, dtype=torch.uint8, device=dev)
+    local_src = torch.empty(nbytes, dtype=torch.uint8, device=dev).random_(0, 255)
+    peer = (rank + 1) % world
+    torch.cuda.synchronize()
+    dist.barrier()
+    flags = torch.zeros(4096, dtype=torch.int32, device=dev)
+    targets = torch.full((4096,), 1 << 30, dtype=torch.int32, device=dev)
+
+    def jobs_for(src_ptr, dst_ptr, n_ctas):
+        # one contiguous slab per job, several jobs per CTA so that the ring stays busy
+        per = 1 << 20
+        arr = (N_.GatherJob * (nbytes // per))()
+        for i in range(nbytes // per):
+            arr[i].src, arr[i].dst, arr[i].rows, arr[i].row_bytes = src_ptr + i * per, dst_ptr + i * per, 1, per
+            arr[i].src_stride = arr[i].dst_stride = per
+            arr[i].flag = i % 4096
+        return torch.frombuffer(bytearray(bytes(arr)), dtype=torch.uint8).to(dev), nbytes // per
+
+    rows = []
+    for mode, name, s_ptr, d_ptr in ((0, "bulk pull (cp.async.bulk peer -> smem -> local)", src_sym.peer_ptrs[peer], local_dst.data_ptr()),
+                                     (1, "load pull (16-byte peer loads)", src_sym.peer_ptrs[peer], local_dst.data_ptr()),
+                                     (2, "store push (16-byte peer stores)", local_src.data_ptr(), dst_sym.peer_ptrs[peer]),
+                                     (3, "bulk push (local -> smem -> cp.async.bulk to peer)", local_src.data_ptr(), dst_sym.peer_ptrs[peer])):
+        for n_ctas in (8, 16, 32, 64, 132):
+            jobs, nj = jobs_for(s_ptr, d_ptr, n_ctas) if mode in (0, 3) else (None, 0)
+            stream = torch.cuda.current_stream().cuda_stream
+
+            def run():
+                code = lib.eri_link_probe(mode, s_ptr, d_ptr, nbytes, n_ctas, jobs.data_ptr() if jobs is not None else None,
+                                          nj, flags.data_ptr(), targets.data_ptr(), 6, stream)
+                if code:
+                    raise RuntimeError(f"link probe mode {mode} failed with code {code}")
+            t = timed(run, iters=5, warm=2)
+            rows.append((name, n_ctas, t))
+            if rank == 0:
+                print(json.dumps({"what": f"link probe, {name}", "world": world, "ctas": n_ctas, "mib": nbytes >> 20,
+                                  "ms": round(t, 4), "gbs_per_gpu_per_direction": round(nbytes / t / 1e6, 1),
+                                  "probe_err": lib.eri_link_probe_check_error()}))
+    # NCCL reference point: all-gather of the same 64 MiB per rank
+    full = torch.empty(world * nbytes, dtype=torch.uint8, device=dev)
+    t = timed(lambda: dist.all_gather_into_tensor(full, local_src), iters=5, warm=2)
+    if rank == 0:
+        print(json.dumps({"what": "NCCL all-gather of 64 MiB per rank", "world": world, "ms": round(t, 4),
+                          "ingress_gbs_per_gpu": round((world - 1) * nbytes / t / 1e6, 1)}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--params", type=int, default=56_000_000)
@@ -254,9 +314,10 @@ def main():
     pg = ProcessGroup()
     sweep = [int(v) for v in str(a.n_copy).split(",")]
     for w in a.what.split(","):
-        for nc in (sweep if w != "fused_dp" else sweep[:1]):
+        for nc in (sweep if w not in ("fused_dp", "link") else sweep[:1]):
             a.n_copy = nc
-            {"fused_dp": bench_fused_dp, "zero3": bench_zero3, "ulysses": bench_ulysses}[w](a, pg, rank, world, dev)
+            {"fused_dp": bench_fused_dp, "zero3": bench_zero3, "ulysses": bench_ulysses, "link": bench_link}[w](
+                a, pg, rank, world, dev)
             dist.barrier()
             torch.cuda.empty_cache()
     dist.destroy_process_group()

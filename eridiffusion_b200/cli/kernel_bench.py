@@ -220,7 +220,15 @@ def bench_attn(small):
         from ..ops import flash_attn as FA
         if FA.supported(q, k, v):
             t = timeit(lambda: FA.flash_attention(q, k, v))
-            print(f"   ours {t*1e6:.1f} us {fl_/t/1e12:.0f} TF/s  {fl_/t/fl:.2f} {tag}")
+            which = "CTA-pair kernel" if (D == 128 and FA.pair_forward_ok(q.device)) else "one-CTA kernel"
+            print(f"   ours ({which}) {t*1e6:.1f} us {fl_/t/1e12:.0f} TF/s  {fl_/t/fl:.2f} {tag}")
+            if which == "CTA-pair kernel":
+                lib = FA.N.require()
+                o1 = torch.empty_like(q)
+                l1 = torch.empty(B, H, L, dtype=torch.float32, device="cuda")
+                t1 = timeit(lambda: lib.eri_flash_attn_fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), o1.data_ptr(),
+                                                           l1.data_ptr(), B, H, L, L, D, D ** -0.5, FA.N.stream_ptr()))
+                print(f"   ours (one-CTA kernel) {t1*1e6:.1f} us {fl_/t1/1e12:.0f} TF/s  {fl_/t1/fl:.2f} {tag}")
         if FA.supported(q, k, v) and FA.has_backward():
             o_, lse_ = FA.fwd(q, k, v)
             go_ = torch.randn_like(o_)

@@ -8,6 +8,12 @@ Two shared objects are produced under ``eridiffusion_b200/lib``:
 * ``liberi_b200_host.so`` — the C++ host runtime (safetensors mmap reader / writer, pinned staging
   pool, manifest loader worker), no CUDA device code.
 
+``ERI_B200_DEBUG_BOUNDS=1`` (or ``build_kernels(debug_bounds=True)``) builds a second library,
+``liberi_b200_kernels_debug.so``, from the same sources with ``-DERI_DEBUG_BOUNDS``: every guarded
+global / peer access range-checks itself against the extent the host passed and records a
+violation instead of performing the access (see ``ptx.cuh``). ``ops/_native.py`` loads that library
+when the variable is set. It is the stand-in for a memory checker on the small test shapes.
+
 The sources are compiled in parallel with one ``nvcc -c`` per file and relinked only when an
 object changed, so a rebuild after touching one kernel takes seconds. Nothing is written outside
 the package directory.
@@ -54,10 +60,11 @@ def _digest(path: Path, extra: str) -> str:
     return h.hexdigest()
 
 
-def _compile_one(src: Path, verbose: bool, ptxas_v: bool) -> tuple[Path, bool, str]:
-    obj = OBJ_DIR / (src.stem + ".o")
-    stamp = OBJ_DIR / (src.stem + ".sha")
-    flags = list(NVCC_FLAGS) + (["-Xptxas", "-v"] if ptxas_v else [])
+def _compile_one(src: Path, verbose: bool, ptxas_v: bool, debug_bounds: bool = False) -> tuple[Path, bool, str]:
+    suffix = ".dbg" if debug_bounds else ""
+    obj = OBJ_DIR / (src.stem + suffix + ".o")
+    stamp = OBJ_DIR / (src.stem + suffix + ".sha")
+    flags = list(NVCC_FLAGS) + (["-Xptxas", "-v"] if ptxas_v else []) + (["-DERI_DEBUG_BOUNDS=1"] if debug_bounds else [])
     dig = _digest(src, " ".join(flags))
     if obj.exists() and stamp.exists() and stamp.read_text() == dig:
         return obj, False, ""
@@ -69,15 +76,15 @@ def _compile_one(src: Path, verbose: bool, ptxas_v: bool) -> tuple[Path, bool, s
     return obj, True, r.stderr if (verbose or ptxas_v) else ""
 
 
-def build_kernels(verbose: bool = False, ptxas_v: bool = False) -> Path:
+def build_kernels(verbose: bool = False, ptxas_v: bool = False, debug_bounds: bool = False) -> Path:
     OBJ_DIR.mkdir(exist_ok=True)
     LIB_DIR.mkdir(exist_ok=True)
     srcs = sorted(CSRC.glob("*.cu"))
-    out = LIB_DIR / "liberi_b200_kernels.so"
+    out = LIB_DIR / ("liberi_b200_kernels_debug.so" if debug_bounds else "liberi_b200_kernels.so")
     changed = False
     objs = []
     with cf.ThreadPoolExecutor(max_workers=min(8, len(srcs) or 1)) as ex:
-        for obj, ch, log in ex.map(lambda s: _compile_one(s, verbose, ptxas_v), srcs):
+        for obj, ch, log in ex.map(lambda s: _compile_one(s, verbose, ptxas_v, debug_bounds), srcs):
             objs.append(obj)
             changed |= ch
             if log:
@@ -114,11 +121,18 @@ def build_host(verbose: bool = False) -> Path:
     return out
 
 
-def build_all(verbose: bool = False, ptxas_v: bool = False) -> list[Path]:
-    return [build_kernels(verbose, ptxas_v), build_host(verbose)]
+def build_all(verbose: bool = False, ptxas_v: bool = False, debug_bounds: bool | None = None) -> list[Path]:
+    """Kernel library, host library and — with ``debug_bounds`` (default: ``ERI_B200_DEBUG_BOUNDS=1``
+    in the environment) — the bounds-checked debug variant of the kernel library."""
+    if debug_bounds is None:
+        debug_bounds = os.environ.get("ERI_B200_DEBUG_BOUNDS") == "1"
+    out = [build_kernels(verbose, ptxas_v), build_host(verbose)]
+    if debug_bounds:
+        out.append(build_kernels(verbose, False, debug_bounds=True))
+    return out
 
 
 if __name__ == "__main__":
     v = "-v" in sys.argv
-    for p in build_all(verbose=v, ptxas_v="--ptxas" in sys.argv):
+    for p in build_all(verbose=v, ptxas_v="--ptxas" in sys.argv, debug_bounds=True if "--debug-bounds" in sys.argv else None):
         print(p)

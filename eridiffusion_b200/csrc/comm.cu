@@ -20,6 +20,7 @@
 #include <cooperative_groups.h>
 
 #include "ptx.cuh"
+#include "optim_codec.cuh"
 
 namespace cg = cooperative_groups;
 using namespace eri;
@@ -63,27 +64,6 @@ __device__ void cross_barrier(const CommCtx& c, int channel, cg::grid_group& gri
   grid.sync();
 }
 
-__device__ __forceinline__ float decode_m(int8_t q, float absmax) {
-  float a = (float)(q < 0 ? -q : q) * (1.f / 127.f);
-  float v = a * a * absmax;
-  return q < 0 ? -v : v;
-}
-__device__ __forceinline__ int8_t encode_m(float m, float inv) {
-  float a = sqrtf(fminf(fabsf(m) * inv, 1.f));
-  int q = __float2int_rn(a * 127.f);
-  return (int8_t)(m < 0.f ? -q : q);
-}
-__device__ __forceinline__ float decode_v(uint8_t q, float absmax) {
-  float a = (float)q * (1.f / 255.f);
-  a = a * a;
-  return a * a * absmax;
-}
-__device__ __forceinline__ uint8_t encode_v(float v, float inv) {
-  float a = sqrtf(sqrtf(fminf(v * inv, 1.f)));
-  int q = __float2int_rn(a * 255.f);
-  if (q == 0 && v > 0.f) q = 1;
-  return (uint8_t)q;
-}
 __device__ __forceinline__ uint32_t hash_u32(uint32_t x) {
   x ^= x >> 16; x *= 0x7feb352dU; x ^= x >> 15; x *= 0x846ca68bU; x ^= x >> 16;
   return x;
@@ -227,6 +207,8 @@ fused_dp_step_kernel(CommCtx c, FusedDpArgs a) {
       const int8_t* mb = reinterpret_cast<const int8_t*>(&mraw);
       const uint8_t* vb = reinterpret_cast<const uint8_t*>(&vraw);
       float mmax = 0.f, vmax = 0.f;
+      float sv[8];                     // sqrt(v): shared by Adam's denominator and the code of v
+      const float inv_bc1 = 1.f / a.bc1, rsqrt_bc2 = rsqrtf(a.bc2), decay = 1.f - a.lr * a.weight_decay;
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
         m[j] = decode_m(mb[j], ma);
@@ -236,12 +218,13 @@ fused_dp_step_kernel(CommCtx c, FusedDpArgs a) {
         v[j] = a.beta2 * v[j] + (1.f - a.beta2) * gj * gj;
         mmax = fmaxf(mmax, fabsf(m[j]));
         vmax = fmaxf(vmax, v[j]);
-        const float upd = (m[j] / a.bc1) / (sqrtf(v[j] / a.bc2) + a.eps);
-        p[j] = p[j] * (1.f - a.lr * a.weight_decay) - a.lr * upd;
+        sv[j] = sqrtf(v[j]);
+        const float upd = __fdividef(m[j] * inv_bc1, sv[j] * rsqrt_bc2 + a.eps);
+        p[j] = p[j] * decay - a.lr * upd;
       }
       mmax = warp_max(mmax);
       vmax = warp_max(vmax);
-      const float im = mmax > 0.f ? 1.f / mmax : 0.f, iv = vmax > 0.f ? 1.f / vmax : 0.f;
+      const float im = mmax > 0.f ? 1.f / mmax : 0.f, siv = vmax > 0.f ? rsqrtf(vmax) : 0.f;
       uint2 mo, vo;
       int8_t* mob = reinterpret_cast<int8_t*>(&mo);
       uint8_t* vob = reinterpret_cast<uint8_t*>(&vo);
@@ -250,7 +233,7 @@ fused_dp_step_kernel(CommCtx c, FusedDpArgs a) {
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
         mob[j] = encode_m(m[j], im);
-        vob[j] = encode_v(v[j], iv);
+        vob[j] = encode_v_from_sqrt(sv[j], siv);
         pb[j] = round_bf16(p[j], a.stochastic != 0,
                            hash_u32(a.seed ^ (uint32_t)(shard_off + e + j) * 0x9E3779B9u));
       }

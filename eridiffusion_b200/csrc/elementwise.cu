@@ -886,3 +886,43 @@ extern "C" int eri_batched_transpose(const void* jobs, int n_jobs, int max_elems
   batched_transpose_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>((const TransposeJob*)jobs);
   return (int)cudaGetLastError();
 }
+
+// ---------------------------------------------------------------------------------------------
+// out[i] (+)= scale * sum_w slots[w][i]: the owner's side of the weight-gradient reduce-scatter that
+// the dW GEMM's row-slab scatter epilogue starts (every rank has pushed its partial slab into slot
+// `rank` of this rank's receive buffer). fp32 sum, bf16 in / out, eight elements per thread.
+namespace {
+__global__ void slot_reduce_kernel(const bf16* __restrict__ slots, bf16* __restrict__ out, int world,
+                                   long long n, float scale, int accumulate) {
+  const long long stride = (long long)gridDim.x * blockDim.x * 8;
+  for (long long i = ((long long)blockIdx.x * blockDim.x + threadIdx.x) * 8; i < n; i += stride) {
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    for (int w = 0; w < world; ++w) {
+      float f[8];
+      unpack8(*reinterpret_cast<const bf16x8*>(slots + (size_t)w * n + i), f);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[j] += f[j];
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[j] *= scale;
+    if (accumulate) {
+      float f[8];
+      unpack8(*reinterpret_cast<const bf16x8*>(out + i), f);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[j] += f[j];
+    }
+    *reinterpret_cast<bf16x8*>(out + i) = pack8(acc);
+  }
+}
+}  // namespace
+
+extern "C" int eri_slot_reduce(const void* slots, void* out, int world, long long n, float scale,
+                               int accumulate, void* stream) {
+  if (n % 8 || world < 1) return -1;
+  const int block = 256;
+  long long blocks = (n / 8 + block - 1) / block;
+  if (blocks > 148 * 8) blocks = 148 * 8;
+  slot_reduce_kernel<<<(unsigned)blocks, block, 0, (cudaStream_t)stream>>>((const bf16*)slots, (bf16*)out, world, n,
+                                                                          scale, accumulate);
+  return (int)cudaGetLastError();
+}

@@ -46,6 +46,8 @@ struct FaParams {
 constexpr int BQ = 128, BKV = 128;
 constexpr float kRescaleThreshold = 8.0f;  // log2 units
 
+ERI_DEBUG_BOUNDS_DEFINE(fa)
+
 template <int DH, int POLY, bool MASK>
 __global__ void __launch_bounds__(320, 2)
 fa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
@@ -366,7 +368,8 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
             float v[8];
 #pragma unroll
             for (int i = 0; i < 8; ++i) v[i] = __uint_as_float(r[g * 8 + i]) * inv_l;
-            *reinterpret_cast<bf16x8*>(orow + c * 32 + g * 8) = pack8(v);
+            if (ERI_DBG_RANGE(p.out, (size_t)p.B * p.Lq * p.H * DH * 2, orow + c * 32 + g * 8, 16, 51))
+              *reinterpret_cast<bf16x8*>(orow + c * 32 + g * 8) = pack8(v);
           }
         }
       }
@@ -488,3 +491,5 @@ int eri_flash_attn_fwd_masked(const void* q, const void* k, const void* v, void*
 }
 
 }  // extern "C"
+
+ERI_DEBUG_BOUNDS_EXPORT(fa)

@@ -79,7 +79,10 @@ struct GemmParams {
   bf16* scatter_out[kMaxPeers];
   float* rowsq;               // optional [rowsq_parts][M]: sum of squares of each output row over
   int rowsq_parts;            // the columns of part 0..rowsq_parts-1 (QK-norm across heads)
+  long long dbg_out_bytes, dbg_out2_bytes, dbg_pre_bytes, dbg_res_bytes;   // debug build only
 };
+
+ERI_DEBUG_BOUNDS_DEFINE(gemm)
 
 constexpr int BM = 128, BK = 64;
 constexpr int kGroupN = 8;
@@ -396,10 +399,15 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 #pragma unroll
                 for (int j = 0; j < 8; ++j) sq += v[j] * v[j];
               }
-              if constexpr (STAGED)
+              if constexpr (STAGED) {
                 *reinterpret_cast<bf16x8*>(stg_row + (size_t)(col - n0) * 2) = pack8(v);
-              else
-                *reinterpret_cast<bf16x8*>(dst + (col - dcol_off)) = pack8(v);
+              } else {
+                const bool to2 = second && p.out2;
+                if (p.scatter_world ||
+                    ERI_DBG_RANGE(to2 ? p.out2 : p.out, to2 ? p.dbg_out2_bytes : p.dbg_out_bytes,
+                                  dst + (col - dcol_off), 16, 81))
+                  *reinterpret_cast<bf16x8*>(dst + (col - dcol_off)) = pack8(v);
+              }
             }
           }
         }
@@ -528,6 +536,7 @@ int eri_gemm_bf16(const EriGemmArgs* g, void* stream) {
     if (g->scatter_group_cols % bn) return -17;
   }
   if (g->b_mn && bn < 64) return -18;
+  if (g->scatter_mode || g->a_mn || g->glu) return -24;   // two-CTA kernel only
   if (g->M < BM) return -15;  // box taller than the tensor: use the small-M path instead
 
   GemmParams p;
@@ -542,6 +551,8 @@ int eri_gemm_bf16(const EriGemmArgs* g, void* stream) {
   p.gate = (const bf16*)g->gate; p.pre_in = (const bf16*)g->pre_in;
   p.out = (bf16*)g->out; p.out2 = (bf16*)g->out2; p.pre_out = (bf16*)g->pre_out;
   p.err = g_err_flag;
+  p.dbg_out_bytes = g->dbg_out_bytes; p.dbg_out2_bytes = g->dbg_out2_bytes;
+  p.dbg_pre_bytes = g->dbg_pre_bytes; p.dbg_res_bytes = g->dbg_res_bytes;
   p.n_copy = g->n_copy; p.n_jobs = g->n_jobs; p.jobs = (const GatherJob*)g->jobs;
   p.flags = (unsigned int*)g->flags; p.flag_target = (const unsigned int*)g->flag_target;
   p.b_flag_rows = g->b_flag_rows; p.a_flag_cols = g->a_flag_cols;
@@ -609,3 +620,5 @@ int eri_gemm_bf16(const EriGemmArgs* g, void* stream) {
 }
 
 }  // extern "C"
+
+ERI_DEBUG_BOUNDS_EXPORT(gemm)

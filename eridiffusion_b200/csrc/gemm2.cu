@@ -64,10 +64,14 @@ struct Gemm2Params {
   int loc_mode, loc_lo, loc_hi;
   // peer scatter epilogue (as in gemm.cu): all columns of a pair tile belong to one (part, rank) group
   int scatter_world, scatter_rank, scatter_part_cols, scatter_group_cols, scatter_local_rows;
+  int scatter_mode;           // 0 column groups, 1 row slabs (see gemm_args.h)
   bf16* scatter_out[kMaxPeers];
   float* rowsq;
   int rowsq_parts;
+  long long dbg_out_bytes, dbg_out2_bytes, dbg_pre_bytes, dbg_res_bytes;   // debug build only
 };
+
+ERI_DEBUG_BOUNDS_DEFINE(gemm2)
 
 constexpr int BM = 128;       // rows per CTA (256 per pair)
 constexpr int BN = 256;       // columns per pair tile
@@ -76,66 +80,6 @@ constexpr int BK = 64;
 constexpr int A_BYTES = BM * BK * 2, B_BYTES = BNH * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
 constexpr int STG_PITCH = BN * 2 + 16;   // staged epilogue: one padded accumulator row per thread
 constexpr int kGroupN = 8;
-
-__device__ __forceinline__ uint32_t cluster_ctarank() {
-  uint32_t r;
-  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
-  return r;
-}
-__device__ __forceinline__ void cluster_sync_all() {
-  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
-  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
-}
-__device__ __forceinline__ uint32_t map_to_cta(uint32_t saddr, uint32_t rank) {
-  uint32_t r;
-  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(saddr), "r"(rank));
-  return r;
-}
-__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
-  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr)
-               : "memory");
-}
-// TMA load whose completion bytes are credited to the barrier at `bar_cluster_addr`
-// (a shared::cluster address, here always the leader CTA's barrier).
-__device__ __forceinline__ void tma_load_2d_pair(void* smem_dst, const void* desc,
-                                                 uint32_t bar_cluster_addr, int32_t x, int32_t y) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes"
-      " [%0], [%1, {%3, %4}], [%2];"
-      ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(desc)), "r"(bar_cluster_addr),
-      "r"(x), "r"(y)
-      : "memory");
-}
-__device__ __forceinline__ void tmem_alloc2(uint32_t* smem_dst, uint32_t ncols) {
-  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
-                   smem_u32(smem_dst)),
-               "r"(ncols)
-               : "memory");
-}
-__device__ __forceinline__ void tmem_relinquish2() {
-  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
-}
-__device__ __forceinline__ void tmem_dealloc2(uint32_t taddr, uint32_t ncols) {
-  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols)
-               : "memory");
-}
-__device__ __forceinline__ void umma2_bf16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b,
-                                           uint32_t idesc, uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}\n"
-      ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
-// Arrive (once all prior UMMAs of this thread are done) on a barrier given by its shared::cluster
-// address: used for the local CTA's barrier and, with the mapped address, for the peer's.
-__device__ __forceinline__ void umma2_commit_addr(uint32_t bar_cluster_addr) {
-  asm volatile(
-      "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
-          bar_cluster_addr)
-      : "memory");
-}
 
 __device__ __forceinline__ void tile_coords(int t, int num_m, int num_n, int rot_n, int& m_blk,
                                             int& n_blk) {
@@ -435,7 +379,8 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
 #pragma unroll
                 for (int j = 0; j < 8; ++j)
                   v[j] = act_first ? apply_act(va[j], amode) * vb[j] : va[j] * apply_act(vb[j], amode);
-                *reinterpret_cast<bf16x8*>(dst + col) = pack8(v);
+                if (ERI_DBG_RANGE(p.out, p.dbg_out_bytes, dst + col, 16, 94))
+                  *reinterpret_cast<bf16x8*>(dst + col) = pack8(v);
               }
             }
           }
@@ -450,7 +395,14 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
       const int coff = second ? p.n_split : 0;
       bf16* dst = second && p.out2 ? p.out2 + (size_t)row * p.ldc2 : p.out + (size_t)row * p.ldc;
       int dcol_off = second && p.out2 ? coff : 0;
-      if (p.scatter_world) {
+      if (p.scatter_world && p.scatter_mode == 1) {
+        // row slabs: this thread's output row belongs to rank row / slab; it lands in this rank's
+        // slot of the owner's receive buffer, same columns
+        const int dest = row_ok ? row / p.scatter_local_rows : 0;
+        const size_t drow = (size_t)p.scatter_rank * p.scatter_local_rows + (row - dest * p.scatter_local_rows);
+        dst = p.scatter_out[dest] + drow * p.ldc;
+        dcol_off = 0;
+      } else if (p.scatter_world) {
         // all columns of a tile belong to one (part, rank) group
         const int part = n0 / p.scatter_part_cols;
         const int within = n0 - part * p.scatter_part_cols;
@@ -493,7 +445,8 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
                 for (int j = 0; j < 8; ++j) v[j] += b[j];
               }
               if (act == 1 || act == 2) {
-                if (p.pre_out)
+                if (p.pre_out && ERI_DBG_RANGE(p.pre_out, p.dbg_pre_bytes,
+                                               p.pre_out + (size_t)row * p.ld_pre + (col - coff), 16, 92))
                   *reinterpret_cast<bf16x8*>(p.pre_out + (size_t)row * p.ld_pre + (col - coff)) =
                       pack8(v);
 #pragma unroll
@@ -512,7 +465,8 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
 #pragma unroll
                 for (int j = 0; j < 8; ++j) v[j] *= gt[j];
               }
-              if (p.residual) {
+              if (p.residual && ERI_DBG_RANGE(p.residual, p.dbg_res_bytes,
+                                              p.residual + (size_t)row * p.ldr + col, 16, 93)) {
                 float rs[8];
                 unpack8(*reinterpret_cast<const bf16x8*>(p.residual + (size_t)row * p.ldr + col),
                         rs);
@@ -523,10 +477,14 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
 #pragma unroll
                 for (int j = 0; j < 8; ++j) sq += v[j] * v[j];
               }
-              if constexpr (STAGED)
+              if constexpr (STAGED) {
                 *reinterpret_cast<bf16x8*>(stg_row + (size_t)(col - n0) * 2) = pack8(v);
-              else
-                *reinterpret_cast<bf16x8*>(dst + (col - dcol_off)) = pack8(v);
+              } else {
+                const bool to2 = second && p.out2;
+                if (ERI_DBG_RANGE(to2 ? p.out2 : p.out, to2 ? p.dbg_out2_bytes : p.dbg_out_bytes,
+                                  dst + (col - dcol_off), 16, 91))
+                  *reinterpret_cast<bf16x8*>(dst + (col - dcol_off)) = pack8(v);
+              }
             }
           }
         }
@@ -541,7 +499,7 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
         }
         tma_store_commit();
       }
-      if (p.rowsq && row_ok) {
+      if (p.rowsq && row_ok && p.scatter_mode == 0) {
         const int part = n0 / p.scatter_part_cols;
         if (part < p.rowsq_parts) atomicAdd(p.rowsq + (size_t)part * p.M + row, sq);
       }
@@ -653,7 +611,12 @@ int eri_gemm2_check_error() {
 int eri_gemm2_bf16(const EriGemmArgs2* g, void* stream) {
   const bool scatter = g->scatter_world != 0;
   if (g->rowsq && !scatter) return -30;
-  if (scatter) {
+  if (scatter && g->scatter_mode == 1) {
+    // row slabs (weight-gradient reduce-scatter): any operand majors, plain epilogue only
+    if ((g->ldc * 2) % 16 || g->n_copy || g->glu || g->rowsq || g->scatter_local_rows <= 0 || g->N % 8 ||
+        g->M != g->scatter_world * g->scatter_local_rows)
+      return -30;
+  } else if (scatter) {
     // a pair tile must sit inside one (part, rank) column group; rows leave through 16-byte aligned
     // bulk copies
     if (g->scatter_group_cols % BN || g->scatter_part_cols % BN || (g->ldc * 2) % 16 || g->n_copy ||
@@ -697,6 +660,8 @@ int eri_gemm2_bf16(const EriGemmArgs2* g, void* stream) {
   p.gate = (const bf16*)g->gate; p.pre_in = (const bf16*)g->pre_in;
   p.out = (bf16*)g->out; p.out2 = (bf16*)g->out2; p.pre_out = (bf16*)g->pre_out;
   p.err = g2_err;
+  p.dbg_out_bytes = g->dbg_out_bytes; p.dbg_out2_bytes = g->dbg_out2_bytes;
+  p.dbg_pre_bytes = g->dbg_pre_bytes; p.dbg_res_bytes = g->dbg_res_bytes;
   p.n_copy = g->n_copy; p.n_jobs = g->n_jobs; p.jobs = (const GatherJob*)g->jobs;
   p.flags = (unsigned int*)g->flags; p.flag_target = (const unsigned int*)g->flag_target;
   p.b_flag_rows = g->b_flag_rows; p.a_flag_cols = g->a_flag_cols; p.a_flag_rows = g->a_flag_rows;
@@ -706,6 +671,7 @@ int eri_gemm2_bf16(const EriGemmArgs2* g, void* stream) {
     p.scatter_world = g->scatter_world; p.scatter_rank = g->scatter_rank;
     p.scatter_part_cols = g->scatter_part_cols; p.scatter_group_cols = g->scatter_group_cols;
     p.scatter_local_rows = g->scatter_local_rows > 0 ? g->scatter_local_rows : g->M;
+    p.scatter_mode = g->scatter_mode;
     for (int i = 0; i < kMaxPeers; ++i) p.scatter_out[i] = (bf16*)g->scatter_out[i];
     p.rowsq = (float*)g->rowsq; p.rowsq_parts = g->rowsq_parts;
   }
@@ -783,3 +749,5 @@ int eri_gemm2_bf16(const EriGemmArgs2* g, void* stream) {
 }
 
 }  // extern "C"
+
+ERI_DEBUG_BOUNDS_EXPORT(gemm2)

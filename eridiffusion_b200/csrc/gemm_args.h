@@ -59,6 +59,14 @@ struct EriGemmArgs {
   // the two halves of the projection; pre_out (optional, [M, 2 * hidden]) keeps the halves.
   // 1: a * gelu(g), 2: a * silu(g), 3: gelu(a) * g, 4: silu(a) * g (two-CTA kernel only).
   int glu;
+  // Byte extents of the destination / auxiliary buffers counted from their pointers (0: unknown).
+  // Only the bounds-checked debug build reads them.
+  long long dbg_out_bytes, dbg_out2_bytes, dbg_pre_bytes, dbg_res_bytes;
+  // Peer scatter by ROW slabs (two-CTA kernel): 0 = column groups (Ulysses head scatter, above);
+  // 1 = output row r goes to rank r / scatter_local_rows, into slot scatter_rank of that rank's
+  // receive buffer [world][scatter_local_rows, N] (the weight-gradient reduce-scatter of ZeRO-3
+  // folded into the dW GEMM: every rank's partial slab lands at its owner as the tiles finish).
+  int scatter_mode;
 };
 
 }  // extern "C"

@@ -43,10 +43,13 @@ struct TokredParams {
   int accumulate;      // 1: out += result
   float alpha;
   bf16* out;
+  long long dbg_out_bytes;   // extent of `out` in bytes (debug build only; 0: unknown)
   float* ws;           // [m_tiles][splits][r][128] fp32 partial tiles (every slot is rewritten per call)
   int* counters;       // [m_tiles] arrivals (zero between calls)
   int* err;
 };
+
+ERI_DEBUG_BOUNDS_DEFINE(tokred)
 
 __global__ void __launch_bounds__(192, 2)
 gemm_tokred_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
@@ -171,6 +174,7 @@ gemm_tokred_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
           for (int j = 0; j < BN; ++j)
             if (j < p.r) {
               bf16* o = p.out + (size_t)j * p.ldc + row;
+              if (!ERI_DBG_RANGE(p.out, p.dbg_out_bytes, o, 2, 71)) continue;
               float v = acc[j] * p.alpha;
               if (p.accumulate) v += __bfloat162float(*o);
               *o = __float2bfloat16(v);
@@ -179,7 +183,7 @@ gemm_tokred_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
           bf16* o = p.out + (size_t)row * p.ldc;
 #pragma unroll
           for (int g = 0; g < BN / 8; ++g)
-            if (g * 8 < p.r) {
+            if (g * 8 < p.r && ERI_DBG_RANGE(p.out, p.dbg_out_bytes, o + g * 8, 16, 72)) {
               float v[8];
 #pragma unroll
               for (int j = 0; j < 8; ++j) v[j] = acc[g * 8 + j] * p.alpha;
@@ -236,11 +240,12 @@ int eri_gemm_tokred_set_target(int ctas) {
 }
 
 // a [T, Mg] (row stride lda elements), b [T, r] (row stride ldb), bf16. out: [Mg, r] or, with
-// transpose_out, [r, Mg]; row stride ldc. accumulate: out += alpha * a^T b.
+// transpose_out, [r, Mg]; row stride ldc. accumulate: out += alpha * a^T b. out_bytes: extent of
+// `out` from its pointer (0: unknown), checked by the bounds-checked debug build only.
 // Returns -100 when the shape is outside this kernel's range (the caller uses another path).
 int eri_gemm_tokred(const void* a, long long lda, const void* b, long long ldb, void* out, int ldc,
                     int T, int Mg, int r, float alpha, int transpose_out, int accumulate,
-                    void* stream) {
+                    long long out_bytes, void* stream) {
   if (!(r == 16 || r == 32 || r == 64) || T < 64 || Mg < 128 || Mg % 8 || lda % 8 || ldb % 8) return -100;
   if (!transpose_out && ldc % 8) return -100;
   if (((uintptr_t)a | (uintptr_t)b) & 15) return -100;
@@ -300,6 +305,7 @@ int eri_gemm_tokred(const void* a, long long lda, const void* b, long long ldb, 
   TokredParams p;
   p.Mg = Mg; p.r = r; p.T = T; p.ldc = ldc; p.ksteps_total = ksteps; p.splits = splits;
   p.transpose_out = transpose_out; p.accumulate = accumulate; p.alpha = alpha;
+  p.dbg_out_bytes = out_bytes;
   p.out = (bf16*)out; p.ws = s.ws; p.counters = s.counters; p.err = s.err;
   dim3 grid(m_tiles, splits);
   gemm_tokred_kernel<<<grid, 192, SMEM, st>>>(ta, tb, p);
@@ -307,3 +313,5 @@ int eri_gemm_tokred(const void* a, long long lda, const void* b, long long ldb, 
 }
 
 }  // extern "C"
+
+ERI_DEBUG_BOUNDS_EXPORT(tokred)

@@ -13,6 +13,7 @@
 // fused CUDA Adam (src/kernels/fused_adam.cu:14-254) is never built. Block-wise scaling bounds
 // the quantisation error per 256 values instead of per tensor.
 #include "ptx.cuh"
+#include "optim_codec.cuh"
 
 using namespace eri;
 typedef __nv_bfloat16 bf16;
@@ -21,27 +22,6 @@ namespace {
 
 constexpr int kBlock = 256;  // quantisation block, elements
 
-__device__ __forceinline__ float decode_m(int8_t q, float absmax) {
-  float a = (float)(q < 0 ? -q : q) * (1.f / 127.f);
-  float v = a * a * absmax;
-  return q < 0 ? -v : v;
-}
-__device__ __forceinline__ int8_t encode_m(float m, float inv_absmax) {
-  float a = sqrtf(fminf(fabsf(m) * inv_absmax, 1.f));
-  int q = __float2int_rn(a * 127.f);
-  return (int8_t)(m < 0.f ? -q : q);
-}
-__device__ __forceinline__ float decode_v(uint8_t q, float absmax) {
-  float a = (float)q * (1.f / 255.f);
-  a = a * a;
-  return a * a * absmax;
-}
-__device__ __forceinline__ uint8_t encode_v(float v, float inv_absmax) {
-  float a = sqrtf(sqrtf(fminf(v * inv_absmax, 1.f)));
-  int q = __float2int_rn(a * 255.f);
-  if (q == 0 && v > 0.f) q = 1;  // a positive second moment never collapses to zero
-  return (uint8_t)q;
-}
 __device__ __forceinline__ uint32_t hash_u32(uint32_t x) {
   x ^= x >> 16; x *= 0x7feb352dU; x ^= x >> 15; x *= 0x846ca68bU; x ^= x >> 16;
   return x;
@@ -107,6 +87,8 @@ __global__ void adamw8bit_kernel(bf16* __restrict__ param, const bf16* __restric
       for (int j = 0; j < 8; ++j) p[j] = g[j] = m[j] = v[j] = 0.f;
     }
     float mmax = 0.f, vmax = 0.f;
+    float sv[8];                       // sqrt(v): shared by Adam's denominator and the code of v
+    const float inv_bc1 = 1.f / a.bc1, rsqrt_bc2 = rsqrtf(a.bc2), decay = 1.f - lr * a.weight_decay;
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
       float gj = g[j] * gs;
@@ -114,13 +96,14 @@ __global__ void adamw8bit_kernel(bf16* __restrict__ param, const bf16* __restric
       v[j] = a.beta2 * v[j] + (1.f - a.beta2) * gj * gj;
       mmax = fmaxf(mmax, fabsf(m[j]));
       vmax = fmaxf(vmax, v[j]);
-      float upd = (m[j] / a.bc1) / (sqrtf(v[j] / a.bc2) + a.eps);
-      p[j] = p[j] * (1.f - lr * a.weight_decay) - lr * upd;
+      sv[j] = sqrtf(v[j]);
+      const float upd = __fdividef(m[j] * inv_bc1, sv[j] * rsqrt_bc2 + a.eps);
+      p[j] = p[j] * decay - lr * upd;
     }
     mmax = warp_max(mmax);
     vmax = warp_max(vmax);
     if (live) {
-      const float im = mmax > 0.f ? 1.f / mmax : 0.f, iv = vmax > 0.f ? 1.f / vmax : 0.f;
+      const float im = mmax > 0.f ? 1.f / mmax : 0.f, siv = vmax > 0.f ? rsqrtf(vmax) : 0.f;
       uint2 mraw, vraw;
       int8_t* mb = reinterpret_cast<int8_t*>(&mraw);
       uint8_t* vb = reinterpret_cast<uint8_t*>(&vraw);
@@ -129,7 +112,7 @@ __global__ void adamw8bit_kernel(bf16* __restrict__ param, const bf16* __restric
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
         mb[j] = encode_m(m[j], im);
-        vb[j] = encode_v(v[j], iv);
+        vb[j] = encode_v_from_sqrt(sv[j], siv);
         pb[j] = round_bf16(p[j], a.stochastic != 0, hash_u32(a.seed ^ (uint32_t)(e0 + j) * 0x9E3779B9u));
       }
       *reinterpret_cast<uint2*>(mq + e0) = mraw;

@@ -232,6 +232,89 @@ __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16
       : "memory");
 }
 
+// ----------------------------------------------------------------- CTA pairs (cta_group::2)
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t saddr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(saddr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr)
+               : "memory");
+}
+// TMA load whose completion bytes are credited to the barrier at `bar_cluster_addr`
+// (a shared::cluster address, here always the leader CTA's barrier).
+__device__ __forceinline__ void tma_load_2d_pair(void* smem_dst, const void* desc,
+                                                 uint32_t bar_cluster_addr, int32_t x, int32_t y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(desc)), "r"(bar_cluster_addr),
+      "r"(x), "r"(y)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_alloc2(uint32_t* smem_dst, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                   smem_u32(smem_dst)),
+               "r"(ncols)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish2() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc2(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols)
+               : "memory");
+}
+__device__ __forceinline__ void umma2_bf16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b,
+                                           uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}\n"
+      ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// Arrive (once all prior UMMAs of this thread are done) on a barrier given by its shared::cluster
+// address: used for the local CTA's barrier and, with the mapped address, for the peer's.
+__device__ __forceinline__ void umma2_commit_addr(uint32_t bar_cluster_addr) {
+  asm volatile(
+      "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
+          bar_cluster_addr)
+      : "memory");
+}
+
+__device__ __forceinline__ void tma_load_3d_pair(void* smem_dst, const void* desc,
+                                                 uint32_t bar_cluster_addr, int32_t x, int32_t y,
+                                                 int32_t z) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%3, %4, %5}], [%2];"
+      ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(desc)), "r"(bar_cluster_addr),
+      "r"(x), "r"(y), "r"(z)
+      : "memory");
+}
+// Pair MMA with the A operand read from tensor memory (each CTA's own lanes), B from the two CTAs'
+// shared memory.
+__device__ __forceinline__ void umma2_bf16_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t desc_b,
+                                              uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], [%1], %2, %3, p;\n\t}\n"
+      ::"r"(tmem_d), "r"(tmem_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
 // Shared-memory matrix descriptor for a K-major bf16 operand stored as rows of 128 bytes
 // (64 bf16) with the 128-byte swizzle that TMA's SWIZZLE_128B mode writes. Groups of 8 rows
 // are 1024 bytes apart (stride byte offset); the leading byte offset is unused for this mode.
@@ -292,6 +375,48 @@ __device__ __forceinline__ uint32_t ld_relaxed_sys(const uint32_t* p) {
   asm volatile("ld.relaxed.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
   return v;
 }
+
+// ----------------------------------------------------------------- bounds-checked debug build
+// Built with -DERI_DEBUG_BOUNDS (csrc/build.py, ERI_B200_DEBUG_BOUNDS=1) every guarded global or
+// peer access first checks its byte range against the extent the host passed for that buffer; a
+// violation is RECORDED (first code / count / source line / offending value, read through
+// eri_<file>_debug_bounds) and the access is SKIPPED, so an indexing bug shows up as a report
+// instead of a fault. In the normal build the macros expand to nothing / `true`. This is the
+// stand-in for a memory checker on machines where none can be run.
+#ifdef ERI_DEBUG_BOUNDS
+#define ERI_DEBUG_BOUNDS_DEFINE(tag)                                                              \
+  static __device__ int g_dbg_bounds[4];                                                          \
+  static __device__ __forceinline__ bool eri_dbg_violation(int code, long long value, int line) { \
+    if (atomicAdd(&g_dbg_bounds[1], 1) == 0) {                                                    \
+      g_dbg_bounds[0] = code;                                                                     \
+      g_dbg_bounds[2] = line;                                                                     \
+      g_dbg_bounds[3] = (int)value;                                                               \
+    }                                                                                             \
+    return false;                                                                                 \
+  }
+// the exported reader: placed at file scope (outside any unnamed namespace) so that it is visible
+#define ERI_DEBUG_BOUNDS_EXPORT(tag)                                                              \
+  extern "C" int eri_##tag##_debug_bounds(int* out4) {                                            \
+    int z[4] = {0, 0, 0, 0};                                                                      \
+    if (cudaMemcpyFromSymbol(out4, g_dbg_bounds, sizeof(z)) != cudaSuccess) return -1;            \
+    cudaMemcpyToSymbol(g_dbg_bounds, z, sizeof(z));                                               \
+    return out4[1];                                                                               \
+  }
+#define ERI_DBG_VIOLATION(code, value) eri_dbg_violation(code, (long long)(value), __LINE__)
+// true when [ptr, ptr + n) lies inside [base, base + extent) (extent 0: unknown, not checked)
+#define ERI_DBG_RANGE(base, extent, ptr, n, code)                                                 \
+  ((extent) == 0 ||                                                                               \
+   ((const char*)(ptr) >= (const char*)(base) &&                                                  \
+    (const char*)(ptr) + (n) <= (const char*)(base) + (extent)) ||                                \
+   ERI_DBG_VIOLATION(code, (const char*)(ptr) - (const char*)(base)))
+#define ERI_DBG_INDEX(i, n, code) (((i) >= 0 && (i) < (n)) || ERI_DBG_VIOLATION(code, i))
+#else
+#define ERI_DEBUG_BOUNDS_DEFINE(tag)
+#define ERI_DEBUG_BOUNDS_EXPORT(tag)
+#define ERI_DBG_VIOLATION(code, value) false
+#define ERI_DBG_RANGE(base, extent, ptr, n, code) true
+#define ERI_DBG_INDEX(i, n, code) true
+#endif
 
 // ----------------------------------------------------------------- small math helpers
 __device__ __forceinline__ float warp_sum(float v) {

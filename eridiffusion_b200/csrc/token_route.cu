@@ -72,12 +72,15 @@ __global__ void __launch_bounds__(1024) topk_desc_kernel(const float* __restrict
     idx_out[(size_t)b * k + j] = (int)(0xffffffffu - (unsigned)(keys[j] & 0xffffffffull));
 }
 
+ERI_DEBUG_BOUNDS_DEFINE(route)
+
 __global__ void build_inverse_kernel(const int* __restrict__ idx, int* __restrict__ inv, int B, int L,
                                      int k) {
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= B * k) return;
   const int b = i / k, j = i % k;
   const int l = idx[i];
+  if (!ERI_DBG_INDEX(l, L, 61)) return;       // debug build: an index outside [0, L) is recorded
   if (l >= 0 && l < L) inv[(size_t)b * L + l] = j;
 }
 
@@ -87,6 +90,7 @@ __global__ void gather_rows_kernel(const bf16* __restrict__ x, const int* __rest
   const int l = idx[(size_t)b * k + j];
   const bf16x8* src = reinterpret_cast<const bf16x8*>(x + ((size_t)b * L + l) * D);
   bf16x8* dst = reinterpret_cast<bf16x8*>(out + ((size_t)b * k + j) * D);
+  if (threadIdx.x == 0) (void)ERI_DBG_INDEX(l, L, 62);   // debug build: recorded; skipped in every build
   if (l < 0 || l >= L) return;
   for (int v = threadIdx.x; v < (D >> 3); v += blockDim.x) dst[v] = src[v];
 }
@@ -97,6 +101,10 @@ __global__ void reinject_rows_kernel(const bf16* __restrict__ full, const bf16* 
   const int l = blockIdx.x, b = blockIdx.y;
   const int j = inv[(size_t)b * L + l];
   bf16x8* dst = reinterpret_cast<bf16x8*>(out + ((size_t)b * L + l) * D);
+  if (j >= k) {                                  // never valid: skipped in every build, recorded in the debug build
+    if (threadIdx.x == 0) (void)ERI_DBG_VIOLATION(63, j);
+    return;
+  }
   if (j >= 0) {
     const bf16x8* src = reinterpret_cast<const bf16x8*>(routed + ((size_t)b * k + j) * D);
     for (int v = threadIdx.x; v < (D >> 3); v += blockDim.x) dst[v] = src[v];
@@ -164,3 +172,5 @@ int eri_reinject_rows(const void* full, const void* routed, const int* inv, void
 }
 
 }  // extern "C"
+
+ERI_DEBUG_BOUNDS_EXPORT(route)

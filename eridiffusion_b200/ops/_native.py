@@ -15,7 +15,9 @@ from pathlib import Path
 import torch
 
 _PKG = Path(__file__).resolve().parent.parent
-_LIB_PATH = _PKG / "lib" / "liberi_b200_kernels.so"
+# ERI_B200_DEBUG_BOUNDS=1 loads the bounds-checked debug variant (csrc/build.py builds it on demand)
+DEBUG_BOUNDS = os.environ.get("ERI_B200_DEBUG_BOUNDS") == "1"
+_LIB_PATH = _PKG / "lib" / ("liberi_b200_kernels_debug.so" if DEBUG_BOUNDS else "liberi_b200_kernels.so")
 _lock = threading.Lock()
 _lib = None
 _launches = 0  # number of kernel launches issued through this module (for bench accounting)
@@ -50,6 +52,8 @@ class GemmArgs(C.Structure):
         ("loc_mode", C.c_int), ("loc_lo", C.c_int), ("loc_hi", C.c_int), ("n_jobs_nl", C.c_int),
         ("jobs_nl", C.c_void_p), ("flag_target_nl", C.c_void_p),
         ("a_mn", C.c_int), ("glu", C.c_int),
+        ("dbg_out_bytes", C.c_longlong), ("dbg_out2_bytes", C.c_longlong), ("dbg_pre_bytes", C.c_longlong),
+        ("dbg_res_bytes", C.c_longlong), ("scatter_mode", C.c_int),
     ]
 
 
@@ -73,6 +77,7 @@ _SIGNATURES = {
                             _I, _I, _I, _P],
     "eri_gate_residual": [_P, _P, _P, _P, _L, _I, _I, _I, _P],
     "eri_gate_grad": [_P, _P, _P, _I, _I, _I, _P],
+    "eri_slot_reduce": [_P, _P, _I, _L, _F, _I, _P],
     "eri_act_fwd": [_P, _P, _L, _I, _P],
     "eri_act_bwd": [_P, _P, _P, _L, _I, _P],
     "eri_glu_fwd": [_P, _P, _I, _I, _I, _I, _P],
@@ -102,7 +107,7 @@ _SIGNATURES = {
     "eri_gemm_skinny": [_P, _L, _P, _L, _P, _I, _I, _I, _I, _F, _P],
     "eri_gemm_skinny_check_error": [],
     "eri_gemm_rank_stream": [_P, _L, _P, _L, _P, _I, _I, _I, _I, _F, _P],
-    "eri_gemm_tokred": [_P, _L, _P, _L, _P, _I, _I, _I, _I, _F, _I, _I, _P],
+    "eri_gemm_tokred": [_P, _L, _P, _L, _P, _I, _I, _I, _I, _F, _I, _I, _L, _P],
     "eri_gemm_tokred_check_error": [],
     "eri_gemm_tokred_set_target": [_I],
     "eri_gemm_init": [],
@@ -120,7 +125,7 @@ def _maybe_build() -> None:
         return
     try:
         from ..csrc import build as _b
-        _b.build_kernels()
+        _b.build_kernels(debug_bounds=DEBUG_BOUNDS)
     except Exception:
         if not _LIB_PATH.exists():
             raise
@@ -150,6 +155,35 @@ def lib():
             fn.restype = C.c_int
         _lib = handle
     return _lib
+
+
+def extent_bytes(t) -> int:
+    """Bytes from ``t``'s first element to the end of its storage (what a kernel may touch through a
+    pointer to ``t``); passed to the kernels for the bounds-checked debug build."""
+    if t is None:
+        return 0
+    return t.untyped_storage().nbytes() - t.storage_offset() * t.element_size()
+
+
+def debug_bounds_report() -> dict:
+    """Violations recorded by the bounds-checked debug build since the last call, per kernel file:
+    ``{file: {"code", "count", "line", "value"}}`` (empty: clean, or not the debug build). Reading
+    synchronises the device and clears the records."""
+    h = lib()
+    out = {}
+    if h is None:
+        return out
+    buf = (C.c_int * 4)()
+    for tag in ("gemm", "gemm2", "tokred", "fa", "route"):
+        fn = getattr(h, f"eri_{tag}_debug_bounds", None)
+        if fn is None:
+            if DEBUG_BOUNDS:
+                raise NativeLibraryError(f"the debug library does not export eri_{tag}_debug_bounds")
+            continue
+        fn.argtypes, fn.restype = [C.POINTER(C.c_int)], C.c_int
+        if fn(buf) > 0:
+            out[tag] = {"code": buf[0], "count": buf[1], "line": buf[2], "value": buf[3]}
+    return out
 
 
 def available() -> bool:

@@ -11,6 +11,7 @@ as one key tile whose padding is blanked by the same bias.
 from __future__ import annotations
 
 import math
+import os
 
 import torch
 
@@ -22,7 +23,9 @@ N._SIGNATURES.update({
     "eri_flash_attn_bwd": [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _P],
     "eri_flash_attn_fwd_masked": [_P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _P],
     "eri_flash_attn_bwd_masked": [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _P],
+    "eri_flash_attn_fwd_pair": [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _P],
     "eri_fa_check_error": [],
+    "eri_fa2_check_error": [],
     "eri_fa_bwd_check_error": [],
 })
 
@@ -33,7 +36,8 @@ _MASKED = -1.0e30      # bias of a masked key: its probability is exactly zero, 
 
 def _bind(lib):
     for name in ("eri_flash_attn_fwd", "eri_flash_attn_bwd", "eri_flash_attn_fwd_masked",
-                 "eri_flash_attn_bwd_masked", "eri_fa_check_error", "eri_fa_bwd_check_error"):
+                 "eri_flash_attn_bwd_masked", "eri_flash_attn_fwd_pair", "eri_fa_check_error",
+                 "eri_fa2_check_error", "eri_fa_bwd_check_error"):
         if hasattr(lib, name):
             fn = getattr(lib, name)
             fn.argtypes = N._SIGNATURES[name]
@@ -48,6 +52,56 @@ def has_forward() -> bool:
 def has_backward() -> bool:
     lib = N.lib()
     return lib is not None and hasattr(lib, "eri_flash_attn_bwd")
+
+
+# The forward for head size 128 without a mask runs on CTA pairs (csrc/flash_attn2.cu) once a
+# one-time self-check on the device has passed: the pair kernel's result on a small case must agree
+# with the one-CTA kernel and leave its error word clear. ERI_B200_FA_PAIR=0 keeps the one-CTA kernel.
+_PAIR_ENABLED = os.environ.get("ERI_B200_FA_PAIR", "0") == "1"
+_PAIR_OK = {}
+
+
+def _poly_pairs() -> int:
+    v = os.environ.get("ERI_B200_FA_POLY", "4")
+    return int(v) if v in ("0", "4", "8") else 4
+
+
+def _pair_call(lib, q, k, v, out, lse, scale):
+    B, Lq, H, D = q.shape
+    return lib.eri_flash_attn_fwd_pair(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), lse.data_ptr(),
+                                       B, H, Lq, k.shape[1], D, scale, _poly_pairs(), N.stream_ptr())
+
+
+def pair_forward_ok(device) -> bool:
+    """Whether the CTA-pair forward kernel may be used on ``device`` (checked once per device)."""
+    if not _PAIR_ENABLED:
+        return False
+    key = str(device)
+    if key in _PAIR_OK:
+        return _PAIR_OK[key]
+    lib = N.require()
+    _bind(lib)
+    ok = False
+    if hasattr(lib, "eri_flash_attn_fwd_pair"):
+        g = torch.Generator(device=device).manual_seed(1234)
+        q, k, v = (torch.randn(1, 384, 2, 128, device=device, generator=g).bfloat16() for _ in range(3))
+        scale = 1.0 / math.sqrt(128)
+        o1, o2 = torch.empty_like(q), torch.empty_like(q)
+        l1 = torch.empty(1, 2, 384, dtype=torch.float32, device=device)
+        l2 = torch.empty_like(l1)
+        c1 = lib.eri_flash_attn_fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), o1.data_ptr(), l1.data_ptr(), 1, 2, 384,
+                                    384, 128, scale, N.stream_ptr())
+        c2 = _pair_call(lib, q, k, v, o2, l2, scale)
+        torch.cuda.synchronize(device)
+        err = lib.eri_fa2_check_error()
+        ok = (c1 == 0 and c2 == 0 and err == 0
+              and (o1.float() - o2.float()).abs().max().item() < 2e-2 and (l1 - l2).abs().max().item() < 1e-2)
+        if not ok:
+            import warnings
+            warnings.warn(f"CTA-pair attention forward failed its self-check on {device} (codes {c1}/{c2}, error word "
+                          f"{err}); using the one-CTA kernel")
+    _PAIR_OK[key] = ok
+    return ok
 
 
 def supported(q, k, v) -> bool:
@@ -115,6 +169,11 @@ def fwd(q, k, v, scale=None, out=None, kbias=None):
                                               lse.data_ptr(), kbias.data_ptr(), B, H, Lq, Lk, D, scale,
                                               N.stream_ptr()), "flash_attn_fwd_masked")
         return out, lse
+    if D == 128 and Lq >= 256 and Lk >= 128 and pair_forward_ok(q.device):
+        code = _pair_call(lib, q, k, v, out, lse, scale)
+        if code != -100:
+            N.check(code, "flash_attn_fwd_pair")
+            return out, lse
     N.check(lib.eri_flash_attn_fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(),
                                    lse.data_ptr(), B, H, Lq, Lk, D, scale, N.stream_ptr()),
             "flash_attn_fwd")
@@ -152,6 +211,8 @@ def check_error() -> int:
     lib = N.require()
     _bind(lib)
     e = lib.eri_fa_check_error()
+    if not e and hasattr(lib, "eri_fa2_check_error"):
+        e = lib.eri_fa2_check_error()
     if not e and hasattr(lib, "eri_fa_bwd_check_error"):
         e = lib.eri_fa_bwd_check_error()
     return e

@@ -359,7 +359,8 @@ def gemm_native(a, b, *, out=None, alpha=1.0, bias=None, lora_h=None, lora_b=Non
     ``out`` may be row-strided views (last dim contiguous). ``gather``: dict built by
     ``parallel.gather_gemm`` (copy jobs + slab counters, fuses an operand gather into the launch).
     ``scatter``: dict(world, rank, part_cols, group_cols, local_rows, ptrs) routing column groups
-    to peer buffers (``out`` is then only used for its row stride). ``a_mn=True``: ``a`` is [K, M]
+    to peer buffers (``out`` is then only used for its row stride); with ``mode=1`` output ROW r goes to
+    rank ``r // local_rows`` into slot ``rank`` of that rank's receive buffer ``[world][local_rows, N]``. ``a_mn=True``: ``a`` is [K, M]
     used as is (with ``b_mn`` this is the weight-gradient product over token-major activations).
     ``glu`` 1-4: ``b`` is an up-projection [2*hidden, K] and the output is the gated product of its
     halves, [M, hidden] (1 a*gelu(g), 2 a*silu(g), 3 gelu(a)*g, 4 silu(a)*g); ``pre_out``
@@ -397,6 +398,10 @@ def gemm_native(a, b, *, out=None, alpha=1.0, bias=None, lora_h=None, lora_b=Non
     if out2 is not None:
         g.out2, g.ldc2 = out2.data_ptr(), out2.stride(0)
     g.force_bn = force_bn
+    if N.DEBUG_BOUNDS:
+        g.dbg_out_bytes = N.extent_bytes(out) if scatter is None else 0
+        g.dbg_out2_bytes, g.dbg_pre_bytes = N.extent_bytes(out2), N.extent_bytes(pre_out)
+        g.dbg_res_bytes = N.extent_bytes(residual)
     g.b_mn = 1 if b_mn else 0
     g.a_mn = 1 if a_mn else 0
     g.glu = int(glu)
@@ -416,6 +421,7 @@ def gemm_native(a, b, *, out=None, alpha=1.0, bias=None, lora_h=None, lora_b=Non
         g.scatter_world, g.scatter_rank = scatter["world"], scatter["rank"]
         g.scatter_part_cols, g.scatter_group_cols = scatter["part_cols"], scatter["group_cols"]
         g.scatter_local_rows = scatter["local_rows"]
+        g.scatter_mode = int(scatter.get("mode", 0))
         for i, ptr_ in enumerate(scatter["ptrs"]):
             g.scatter_out[i] = ptr_
         if scatter.get("rowsq") is not None:
@@ -482,7 +488,7 @@ def kernel_error_check() -> dict:
     family's bounded waits ran out, and cleared by the read). Empty dict = clean."""
     lib = N.require()
     out = {}
-    for name in ("gemm", "gemm2", "gemm_skinny", "gemm_tokred", "fa", "fa_bwd", "norm"):
+    for name in ("gemm", "gemm2", "gemm_skinny", "gemm_tokred", "fa", "fa2", "fa_bwd", "norm"):
         fn = getattr(lib, f"eri_{name}_check_error", None)
         if fn is not None:
             v = fn()
@@ -544,7 +550,8 @@ def lora_wgrad(a_tok, b_tok, out=None, transpose_out=False, accumulate=False):
             out, accumulate = torch.empty(shape, dtype=torch.bfloat16, device=a_tok.device), False
         code = lib.eri_gemm_tokred(a_tok.data_ptr(), a_tok.stride(0), b_tok.data_ptr(), b_tok.stride(0),
                                    out.data_ptr(), out.stride(0), T, Mg, r, 1.0, 1 if transpose_out else 0,
-                                   1 if accumulate else 0, N.stream_ptr())
+                                   1 if accumulate else 0, N.extent_bytes(out) if N.DEBUG_BOUNDS else 0,
+                                   N.stream_ptr())
         if code != -100:
             N.check(code, "gemm_tokred")
             return out

@@ -8,8 +8,12 @@ symmetric (peer-mapped) memory. Nothing is gathered ahead of time:
   per output-column tile on the slab counters (``GatherPlan.rows``);
 * backward ``dX = dY W``: the same landing data is the MN-major B operand, gathered again along
   the reduction dimension (``along_k=True``), no transposed copy;
-* ``dW``: local GEMM into a symmetric staging buffer, then a pull-based reduce-scatter kernel
-  delivers this rank's averaged slab (no NCCL);
+* ``dW``: the weight-gradient GEMM (tcgen05, both activations token-major) pushes every row slab of
+  its result straight into the owning rank's receive buffer from its epilogue (row-slab peer
+  scatter: the reduce-scatter's transfer runs tile by tile under the GEMM), one in-kernel barrier
+  later the owner adds the ``world`` slots (``eri_slot_reduce``); no NCCL, no staging pass.
+  ``ERI_B200_ZERO3_FUSED_RS=0`` restores the staged form (local GEMM, then a pull-based
+  reduce-scatter kernel);
 * conditioning-vector linears (adaLN modulation) are sharded too: every rank applies its row
   slab to the vectors of all ranks (tiny all-gather in, all-to-all out), so a third of a
   Qwen-Image block's weights never crosses NVLink at all.
@@ -39,11 +43,17 @@ class Zero3Context:
                  max_weight_elems: int = 64 << 20, n_copy: int = 16, wait_ms: float = 2000.0):
         self.pg = pg or ProcessGroup()
         self.rank, self.world = self.pg.rank, self.pg.world_size
-        self.heap = SymmetricHeap(heap_bytes + max_weight_elems * 2 + (1 << 20), group=self.pg.group)
+        # symmetric memory: parameter shards (heap_bytes), the dW staging buffer and two receive
+        # buffers of the fused weight-gradient reduce-scatter (alternating by layer)
+        self.fused_rs = os.environ.get("ERI_B200_ZERO3_FUSED_RS", "1") == "1"
+        self.heap = SymmetricHeap(heap_bytes + max_weight_elems * 2 * (3 if self.fused_rs else 1) + (1 << 20),
+                                  group=self.pg.group)
         self.comm = Communicator(self.heap, wait_ms)
         dev = torch.device("cuda", torch.cuda.current_device())
         self.landing = [torch.empty(max_weight_elems, dtype=torch.bfloat16, device=dev) for _ in range(2)]
         self.stage = self.heap.tensor((max_weight_elems,), torch.bfloat16)
+        self.recv = [self.heap.tensor((max_weight_elems,), torch.bfloat16) for _ in range(2)] if self.fused_rs else []
+        self._recv_flip = 0
         self.n_copy = n_copy
         # "sm": copy CTAs inside the GEMM launch pull the slabs; "ce": the copy engines do, on a side
         # stream, and the GEMM only waits on the landing counters (ERI_B200_ZERO3_GATHER overrides)
@@ -77,6 +87,15 @@ class Zero3Context:
             self._plans[key] = pl
         self.gathered_bytes += pl.bytes_from_peers()
         return pl, landing
+
+    def next_recv(self):
+        """Receive buffer of the next fused weight-gradient reduce-scatter. Two alternate: a fast
+        peer may already push layer l + 1's slabs while this rank still adds up layer l's (it cannot
+        be two layers ahead: it has to pass layer l + 1's barrier, which this rank enters only after
+        its reduction of layer l)."""
+        r = self.recv[self._recv_flip]
+        self._recv_flip ^= 1
+        return r
 
     def gather_args(self, pl):
         if self.copy_stream is not None:
@@ -133,13 +152,27 @@ class _Zero3LinearFn(torch.autograd.Function):
         dshard = None
         if ctx.needs_input_grad[1]:
             per = n_out // z3.world
-            stage = z3.stage.local[: n_out * K].view(n_out, K)
-            F.wgrad(dy2, x2, out=stage)
-            if z3.world > 1:
+            fused = (z3.world > 1 and z3.fused_rs and n_out >= 256 and K >= 256 and M >= 64 and K % 8 == 0
+                     and n_out % 8 == 0 and F._wgrad_ok(dy2, x2))
+            if fused:
+                # every rank's partial slab for rank d lands in slot `rank` of d's receive buffer while
+                # the GEMM is still running; one barrier, then the owner adds the slots
+                recv = z3.next_recv()
+                F.gemm_native(dy2, x2, a_mn=True, b_mn=True, out=recv.local[: n_out * K].view(n_out, K),
+                              scatter=dict(world=z3.world, rank=z3.rank, mode=1, local_rows=per, part_cols=0,
+                                           group_cols=0, ptrs=recv.peer_ptrs))
+                z3.barrier()
                 dshard = torch.empty(per, K, dtype=dy2.dtype, device=dy2.device)
-                z3.comm.collective("reduce_scatter", z3.stage, dst=dshard, count=per * K, avg=True)
+                F.N.check(F.N.require().eri_slot_reduce(recv.local.data_ptr(), dshard.data_ptr(), z3.world, per * K,
+                                                        1.0 / z3.world, 0, F.N.stream_ptr()), "slot_reduce")
             else:
-                dshard = stage.clone()
+                stage = z3.stage.local[: n_out * K].view(n_out, K)
+                F.wgrad(dy2, x2, out=stage)
+                if z3.world > 1:
+                    dshard = torch.empty(per, K, dtype=dy2.dtype, device=dy2.device)
+                    z3.comm.collective("reduce_scatter", z3.stage, dst=dshard, count=per * K, avg=True)
+                else:
+                    dshard = stage.clone()
         dbias = dy2.sum(0) if (has_bias and ctx.needs_input_grad[2]) else None
         return dx, dshard, dbias, None, None, None, d_res, None
 

@@ -158,3 +158,22 @@ def test_flash_headline_shape_against_fp32():
             rel = (got[:, :, h:h + 1].float() - want).abs().max().item() / want.abs().max().item()
             worst[name] = max(worst.get(name, 0.0), rel)
     assert worst["out"] < 1.5e-2 and worst["dq"] < 2.5e-2 and worst["dk"] < 2.5e-2 and worst["dv"] < 2.5e-2, worst
+
+
+@pytest.mark.parametrize("B,H,Lq,Lk", [(1, 2, 256, 128), (2, 3, 512, 384), (1, 2, 640, 333), (1, 4, 1152, 1152), (1, 2, 300, 256)])
+def test_flash_fwd_cta_pair_kernel(B, H, Lq, Lk):
+    """The CTA-pair forward (two CTAs share every K / V tile) against fp32 and against the one-CTA
+    kernel, including query counts that leave the pair's second tile partly or wholly empty."""
+    assert FA.pair_forward_ok(torch.device("cuda", 0)), "the CTA-pair forward failed its self-check"
+    lib = FA.N.require()
+    q, k, v = mk(B, Lq, H, 128, 1), mk(B, Lk, H, 128, 2), mk(B, Lk, H, 128, 3)
+    out = torch.full_like(q, float("nan"))
+    lse = torch.empty(B, H, Lq, dtype=torch.float32, device="cuda")
+    code = FA._pair_call(lib, q, k, v, out, lse, 1.0 / math.sqrt(128))
+    assert code == 0
+    torch.cuda.synchronize()
+    assert FA.check_error() == 0
+    ref = R.attention_fp32(q, k, v)
+    assert (out.float() - ref).abs().max().item() < 2e-2
+    s = torch.einsum("blhd,bmhd->bhlm", q.float(), k.float()) / math.sqrt(128)
+    assert (lse - torch.logsumexp(s, -1)).abs().max().item() < 2e-2

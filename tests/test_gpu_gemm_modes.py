@@ -147,3 +147,31 @@ def test_scatter_epilogue_pair_tiles_and_row_squares(pair, monkeypatch):
         assert got[:, 1 - rank].abs().max().item() == 0.0
     want_sq = yf.view(B * Ll, 3, part)[:, :2].pow(2).sum(-1).t()
     assert torch.allclose(rowsq, want_sq, rtol=2e-2, atol=1e-2)
+
+
+@pytest.mark.parametrize("rank", [0, 2])
+def test_row_slab_scatter_is_the_weight_gradient_reduce_scatter(rank):
+    """dW = dY^T X whose epilogue pushes row slab d of the result into slot `rank` of rank d's receive
+    buffer (peers emulated by local buffers); the owner then adds the slots."""
+    W, T, N, K = 4, 640, 1024, 512
+    per = N // W
+    dy, x = rnd(T, N, scale=0.5), rnd(T, K, seed=1)
+    recv = [torch.zeros(W, per, K, device=DEV, dtype=torch.bfloat16) for _ in range(W)]
+    F.gemm_native(dy, x, a_mn=True, b_mn=True, out=recv[0].view(N, K),
+                  scatter=dict(world=W, rank=rank, mode=1, local_rows=per, part_cols=0, group_cols=0,
+                               ptrs=[r.data_ptr() for r in recv]))
+    assert F.gemm_error_check() == 0
+    ref = dy.float().t() @ x.float()
+    for d in range(W):
+        close(recv[d][rank], ref[d * per:(d + 1) * per], 0.05 * (T / 128) ** 0.5)
+        others = [s for s in range(W) if s != rank]
+        assert recv[d][others].abs().max().item() == 0.0
+    # the owner's reduction over the slots (mean over ranks), here with every slot filled differently
+    slots = torch.stack([rnd(per, K, seed=40 + s) for s in range(W)])
+    out = torch.empty(per, K, device=DEV, dtype=torch.bfloat16)
+    lib = F.N.require()
+    F.N.check(lib.eri_slot_reduce(slots.data_ptr(), out.data_ptr(), W, per * K, 1.0 / W, 0, F.N.stream_ptr()), "slot_reduce")
+    close(out, slots.float().mean(0), 0.02)
+    acc = out.clone()
+    F.N.check(lib.eri_slot_reduce(slots.data_ptr(), acc.data_ptr(), W, per * K, 1.0 / W, 1, F.N.stream_ptr()), "slot_reduce")
+    close(acc, 2 * slots.float().mean(0), 0.04)

@@ -83,14 +83,43 @@ def _worker_body(rank, world, port, q):
     pers = 6 * 256 // world
     out["z3_small_dw"] = _rel(zs.weight.grad, sw.grad[rank * pers:(rank + 1) * pers])
     out["z3_small_dx"] = _rel(v.grad, vr[rank].grad * world)
+    # a second layer whose slabs (384 rows per rank) are not multiples of the 256-row pair tile:
+    # forward gather, input gradient (gather along K) and the fused weight-gradient reduce-scatter
+    torch.manual_seed(2)
+    lin2 = Linear(512, 384 * world, bias=False, device=dev)
+    zl2 = Zero3Linear(lin2, z3)
+    arena2 = ParamArena([zl2.weight], alloc=z3.arena_alloc)
+    z3.barrier()
+    x2s = [torch.randn(2, 192, 512, device=dev, generator=torch.Generator(device=dev).manual_seed(21 + r)).bfloat16()
+           for r in range(world)]
+    x2 = x2s[rank].clone().requires_grad_()
+    lib = F.N.require()
+    c0 = lib.eri_gemm2_gather_count()
+    y2 = zl2(x2)
+    y2.float().pow(2).mean().backward()
+    torch.cuda.synchronize()
+    out["z3_pair_launches"] = lib.eri_gemm2_gather_count() - c0          # forward + input-gradient gathers
+    w2 = lin2.weight.detach().float().requires_grad_()
+    x2r = [t.clone().float().requires_grad_() for t in x2s]
+    tot2 = 0
+    for r in range(world):
+        y2r = torch.nn.functional.linear(x2r[r], w2)
+        if r == rank:
+            out["z3u_fwd"] = _rel(y2, y2r)
+        tot2 = tot2 + y2r.pow(2).mean() / world
+    tot2.backward()
+    out["z3u_dx"] = _rel(x2.grad, x2r[rank].grad * world)
+    out["z3u_dw"] = _rel(zl2.weight.grad, w2.grad[rank * 384:(rank + 1) * 384])
     out["z3_status"] = z3.comm.status()
     out["gemm_err"] = F.gemm_error_check()
 
     # ---------------- Ulysses: LTX-style model, sequence sharded over ranks vs full sequence
     torch.manual_seed(1)
-    kw = dict(hidden=256, num_heads=4, depth=2, context_dim=256, caption_dim=128, in_channels=64)
+    # one rank's head group stays 128 columns wide and its sequence shard 128 tokens at every world size
+    hid, nh = (256, 4) if world == 2 else (128 * world, world)
+    kw = dict(hidden=hid, num_heads=nh, depth=2, context_dim=256, caption_dim=128, in_channels=64)
     model = build_model("ltx_video", device=dev, **kw)
-    frames, hh, ww = 2, 8, 16                       # 256 tokens
+    frames, hh, ww = 2, 8, 8 * world                # 128 tokens per rank
     L = frames * hh * ww
     Ll = L // world
     g = torch.Generator(device=dev).manual_seed(3)
@@ -103,7 +132,7 @@ def _worker_body(rank, world, port, q):
     (ref * wgt).sum().backward()
     ref_dx = full_in.grad.clone()
     ref_gw = model.blocks[0].attn1_qkv.weight.grad
-    u = UlyssesContext(pg, batch=1, l_local=Ll, hidden=256, heads=4, n_copy=4)
+    u = UlyssesContext(pg, batch=1, l_local=Ll, hidden=hid, heads=nh, n_copy=4)
     model.set_sequence_parallel(u)
     loc_in = tok[:, rank * Ll:(rank + 1) * Ll].clone().requires_grad_()
     for p in model.parameters():
@@ -126,13 +155,15 @@ def _worker_body(rank, world, port, q):
     dist.destroy_process_group()
 
 
-@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
-def test_zero3_and_ulysses_two_gpus():
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_zero3_and_ulysses_multi_gpu(world):
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
     import torch.multiprocessing as mp
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     port = _free_port()
-    procs = [ctx.Process(target=_worker, args=(r, 2, port, q)) for r in range(2)]
+    procs = [ctx.Process(target=_worker, args=(r, world, port, q)) for r in range(world)]
     for p in procs:
         p.start()
     out = q.get(timeout=300)
@@ -146,5 +177,7 @@ def test_zero3_and_ulysses_two_gpus():
         p.join(timeout=120)
         assert p.exitcode == 0
     assert out["z3_status"] == 0 and out["ul_status"] == 0 and out["gemm_err"] == 0 and out["gemm_err2"] == 0, out
-    for k in ("z3_fwd", "z3_small_fwd", "z3_dx", "z3_dw", "z3_small_dw", "z3_small_dx", "ul_fwd", "ul_dx", "ul_dw"):
+    for k in ("z3_fwd", "z3_small_fwd", "z3_dx", "z3_dw", "z3_small_dw", "z3_small_dx", "z3u_fwd", "z3u_dx", "z3u_dw",
+              "ul_fwd", "ul_dx", "ul_dw"):
         assert out[k] < 4e-2, (k, out)
+    assert out["z3_pair_launches"] == 2, out          # unaligned slabs stay on the two-CTA kernel
