@@ -175,6 +175,36 @@ def bench_zero3(a, pg, rank, world, dev):
                               **roofline_fields(flops, link_bytes, t_f, a.n_copy),
                               "n_copy": a.n_copy, "gemm_peak": tag, "status": z3.comm.status(), "gemm_err": F.gemm_error_check(),
                               "two_cta_gather_launches": N_.require().eri_gemm2_gather_count()}))
+        # forward + backward: two gathers inside GEMMs and the weight-gradient reduce-scatter inside the
+        # dW GEMM's epilogue, against all-gather + three library GEMMs + NCCL reduce-scatter
+        xg = x.clone().requires_grad_()
+        dy = torch.randn(1, M, n_out, device=dev).bfloat16()
+        zl.weight.requires_grad_(True)
+        dws = torch.empty(n_out // world, k_in, device=dev, dtype=torch.bfloat16)
+        dwf = torch.empty(n_out, k_in, device=dev, dtype=torch.bfloat16)
+
+        def fused_fb():
+            zl.weight.grad = None
+            xg.grad = None
+            zl(xg).backward(dy)
+
+        def nccl_fb():
+            with torch.no_grad():
+                dist.all_gather_into_tensor(full, zl.weight.data)
+                F.linear(x, full)
+                dist.all_gather_into_tensor(full, zl.weight.data)       # ZeRO-3 re-gathers for backward
+                torch.matmul(dy[0], full)
+                torch.matmul(dy[0].t(), x[0], out=dwf)
+                dist.reduce_scatter_tensor(dws, dwf, op=dist.ReduceOp.AVG)
+
+        t_f, t_n = timed(fused_fb), timed(nccl_fb)
+        if rank == 0:
+            print(json.dumps({"what": f"zero3 forward + backward (gather, gather, dW reduce-scatter) [{M}x{k_in}] x [{n_out}x{k_in}]^T",
+                              "world": world, "fused_ms": round(t_f, 4), "nccl_and_library_gemms_ms": round(t_n, 4),
+                              **roofline_fields(3 * flops, 3 * link_bytes, t_f, a.n_copy),
+                              "fused_reduce_scatter": bool(z3.fused_rs), "n_copy": a.n_copy, "gemm_peak": tag,
+                              "status": z3.comm.status(), "gemm_err": F.gemm_error_check()}))
+        zl.weight.requires_grad_(False)
 
 
 def bench_ulysses(a, pg, rank, world, dev):

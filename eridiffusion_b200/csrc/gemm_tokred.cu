@@ -12,15 +12,14 @@
 // operands are fed to tcgen05.mma as MN-major tiles straight from their row-major [T, *] layout
 // (no transposed copy exists anywhere): the A tile is two 64-column slabs of 64 token rows, the B
 // tile one slab whose columns beyond r are zero-filled by the TMA unit (box wider than the tensor),
-// so the instruction always runs with N = 64. The token dimension is split across CTAs
-// (grid = Mg / 128 tiles x splits); every CTA stores its partial tile into its own slot of an fp32
-// workspace (plain coalesced stores, no atomics) and the last CTA of a tile (an arrival counter)
-// adds the slots in split order, optionally adds the existing gradient (beta = 1) and writes bf16.
-// The summation order is fixed, so the result is bit-reproducible run to run. One launch per
-// gradient.
-//
-// The workspace is one buffer per device shared by all calls: calls whose GPU work may overlap
-// (different streams) must not use this entry point concurrently.
+// so the instruction always runs with N = 64. The token dimension is split across the CTAs of one
+// thread-block cluster (grid = Mg / 128 tiles x splits, cluster = 1 x splits, splits in {1, 2, 4, 8}):
+// every CTA leaves its fp32 partial tile in its own shared memory, and after one cluster barrier
+// each CTA adds a 128 / splits row band of all the partials, read over distributed shared memory in
+// split order, optionally adds the existing gradient (beta = 1) and writes bf16. No workspace in
+// global memory, no atomics, and a fixed summation order: the result is bit-reproducible run to
+// run. One launch per gradient; with programmatic dependent launch its prologue (barriers, TMEM
+// allocation, descriptor prefetch) overlaps the tail of the kernel before it.
 #include <cstdlib>
 
 #include "ptx.cuh"
@@ -44,8 +43,6 @@ struct TokredParams {
   float alpha;
   bf16* out;
   long long dbg_out_bytes;   // extent of `out` in bytes (debug build only; 0: unknown)
-  float* ws;           // [m_tiles][splits][r][128] fp32 partial tiles (every slot is rewritten per call)
-  int* counters;       // [m_tiles] arrivals (zero between calls)
   int* err;
 };
 
@@ -62,10 +59,9 @@ gemm_tokred_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
   uint64_t* empty = bars + STAGES;
   uint64_t* acc_full = bars + 2 * STAGES;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 1);
-  int* s_last = reinterpret_cast<int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int m_tile = blockIdx.x, split = blockIdx.y;
+  const int m_tile = blockIdx.x, split = (int)cluster_ctarank();   // cluster = (1, splits, 1): rank == blockIdx.y
   const int ks0 = (int)((long long)p.ksteps_total * split / p.splits);
   const int ks1 = (int)((long long)p.ksteps_total * (split + 1) / p.splits);
   const int nks = ks1 - ks0;
@@ -91,6 +87,7 @@ gemm_tokred_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
 
   if (warp == 0) {
     if (elect_one()) {
+      griddep_wait();                    // the operands are written by the kernels before this one
       for (int i = 0; i < nks; ++i) {
         const int s = i % STAGES;
         if (!mbar_wait(&empty[s], (uint32_t)(((i / STAGES) & 1) ^ 1))) { atomicExch(p.err, 71); break; }
@@ -120,85 +117,111 @@ gemm_tokred_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
       if (ok) umma_commit(acc_full);
     }
   } else {
+    // this CTA's partial tile -> shared memory as [r][128] floats (the stages are free: the commit
+    // that armed acc_full covers every MMA that read them)
     const int qd = warp & 3;
     const int r_in = qd * 32 + lane;
-    const int row = m_tile * BM + r_in;
     const uint32_t lane_addr = tmem_base + ((uint32_t)(qd * 32) << 16);
-    float acc[BN];
-    bool ok = nks > 0 ? mbar_wait(acc_full, 0) : true;
+    const bool ok = nks > 0 ? mbar_wait(acc_full, 0) : true;
     if (!ok && lane == 0) atomicExch(p.err, 73);
     tc_fence_after();
-    if (ok && nks > 0) {
+    float* part = reinterpret_cast<float*>(smem);
 #pragma unroll
-      for (int c = 0; c < BN / 16; ++c) {
+    for (int c = 0; c < BN / 16; ++c) {
+      if (c * 16 < p.r) {
         uint32_t rr[16];
-        tmem_ld16(lane_addr + c * 16, rr);
-        tmem_ld_wait();
-#pragma unroll
-        for (int j = 0; j < 16; ++j) acc[c * 16 + j] = __uint_as_float(rr[j]);
-      }
-    } else {
-#pragma unroll
-      for (int j = 0; j < BN; ++j) acc[j] = 0.f;
-    }
-    // slot of (tile, split): [r][128] floats, lanes along the row index -> coalesced
-    const size_t slot_elems = (size_t)p.r * BM;
-    float* tile_ws = p.ws + (size_t)m_tile * p.splits * slot_elems;
-    if (p.splits > 1) {
-      float* mine = tile_ws + (size_t)split * slot_elems + r_in;
-#pragma unroll
-      for (int j = 0; j < BN; ++j)
-        if (j < p.r) __stcg(mine + (size_t)j * BM, acc[j]);
-      __threadfence();
-      asm volatile("bar.sync 1, 128;" ::: "memory");
-      if (threadIdx.x == 64) *s_last = (atomicAdd(p.counters + m_tile, 1) == p.splits - 1) ? 1 : 0;
-      asm volatile("bar.sync 1, 128;" ::: "memory");
-    }
-    if (p.splits == 1 || *s_last) {
-      if (p.splits > 1) {
-        __threadfence();
-#pragma unroll
-        for (int j = 0; j < BN; ++j) acc[j] = 0.f;
-        for (int sp = 0; sp < p.splits; ++sp) {
-          const float* src = tile_ws + (size_t)sp * slot_elems + r_in;
-#pragma unroll
-          for (int j = 0; j < BN; ++j)
-            if (j < p.r) acc[j] += __ldcg(src + (size_t)j * BM);
-        }
-        if (threadIdx.x == 64) p.counters[m_tile] = 0;
-      }
-      if (row < p.Mg) {
-        if (p.transpose_out) {
-          // consecutive threads hold consecutive rows: column j of the tile is a contiguous run
-#pragma unroll
-          for (int j = 0; j < BN; ++j)
-            if (j < p.r) {
-              bf16* o = p.out + (size_t)j * p.ldc + row;
-              if (!ERI_DBG_RANGE(p.out, p.dbg_out_bytes, o, 2, 71)) continue;
-              float v = acc[j] * p.alpha;
-              if (p.accumulate) v += __bfloat162float(*o);
-              *o = __float2bfloat16(v);
-            }
+        if (ok && nks > 0) {
+          tmem_ld16(lane_addr + c * 16, rr);
+          tmem_ld_wait();
         } else {
-          bf16* o = p.out + (size_t)row * p.ldc;
 #pragma unroll
-          for (int g = 0; g < BN / 8; ++g)
-            if (g * 8 < p.r && ERI_DBG_RANGE(p.out, p.dbg_out_bytes, o + g * 8, 16, 72)) {
-              float v[8];
-#pragma unroll
-              for (int j = 0; j < 8; ++j) v[j] = acc[g * 8 + j] * p.alpha;
-              if (p.accumulate) {
-                float old[8];
-                unpack8(*reinterpret_cast<const bf16x8*>(o + g * 8), old);
-#pragma unroll
-                for (int j = 0; j < 8; ++j) v[j] += old[j];
-              }
-              *reinterpret_cast<bf16x8*>(o + g * 8) = pack8(v);
-            }
+          for (int j = 0; j < 16; ++j) rr[j] = 0u;
         }
+#pragma unroll
+        for (int j = 0; j < 16; ++j) part[(c * 16 + j) * BM + r_in] = __uint_as_float(rr[j]);
       }
     }
   }
+  // every CTA of the cluster has its partial in place (all threads of all CTAs arrive: the roles
+  // above always fall through to here, also after a wait that ran out)
+  __syncwarp();
+  cluster_sync_all();
+  if (warp >= 2) {
+    griddep_wait();                      // `out` may be read or written only after the kernel before
+    const int t = (int)threadIdx.x - 64;
+    const int band = BM / p.splits;      // rows of the tile this CTA reduces: 128, 64, 32 or 16
+    const uint32_t part_u32 = smem_u32(smem);
+    if (p.transpose_out) {
+      // item = (column j, 8 consecutive rows): out[j][row .. row + 7] is a contiguous run
+      const int items = p.r * (band / 8);
+      for (int it = t; it < items; it += 128) {
+        const int j = it / (band / 8), g = it % (band / 8);
+        const int rl = split * band + g * 8, row = m_tile * BM + rl;
+        if (row >= p.Mg) continue;       // Mg is a multiple of 8: a group is inside or outside
+        float v[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v[i] = 0.f;
+#pragma unroll 8
+        for (int sp = 0; sp < p.splits; ++sp) {
+          const uint32_t src = map_to_cta(part_u32 + (uint32_t)(j * BM + rl) * 4u, (uint32_t)sp);
+          const float4 lo = ld_shared_cluster_v4(src), hi = ld_shared_cluster_v4(src + 16);
+          v[0] += lo.x; v[1] += lo.y; v[2] += lo.z; v[3] += lo.w;
+          v[4] += hi.x; v[5] += hi.y; v[6] += hi.z; v[7] += hi.w;
+        }
+        bf16* o = p.out + (size_t)j * p.ldc + row;
+        if (!ERI_DBG_RANGE(p.out, p.dbg_out_bytes, o, 16, 71)) continue;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v[i] *= p.alpha;
+        if ((reinterpret_cast<uintptr_t>(o) & 15) == 0) {
+          if (p.accumulate) {
+            float old[8];
+            unpack8(*reinterpret_cast<const bf16x8*>(o), old);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) v[i] += old[i];
+          }
+          *reinterpret_cast<bf16x8*>(o) = pack8(v);
+        } else {
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            float w = v[i];
+            if (p.accumulate) w += __bfloat162float(o[i]);
+            o[i] = __float2bfloat16(w);
+          }
+        }
+      }
+    } else {
+      // item = (row, 8 consecutive columns): out[row][j0 .. j0 + 7]
+      const int items = band * (p.r / 8);
+      for (int it = t; it < items; it += 128) {
+        const int rl = split * band + it % band, j0 = (it / band) * 8;
+        const int row = m_tile * BM + rl;
+        if (row >= p.Mg) continue;
+        float v[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v[i] = 0.f;
+#pragma unroll 8
+        for (int sp = 0; sp < p.splits; ++sp) {
+          const uint32_t src = map_to_cta(part_u32 + (uint32_t)(j0 * BM + rl) * 4u, (uint32_t)sp);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) v[i] += ld_shared_cluster_f32(src + (uint32_t)(i * BM) * 4u);
+        }
+        bf16* o = p.out + (size_t)row * p.ldc + j0;
+        if (!ERI_DBG_RANGE(p.out, p.dbg_out_bytes, o, 16, 72)) continue;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v[i] *= p.alpha;
+        if (p.accumulate) {
+          float old[8];
+          unpack8(*reinterpret_cast<const bf16x8*>(o), old);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) v[i] += old[i];
+        }
+        *reinterpret_cast<bf16x8*>(o) = pack8(v);
+      }
+    }
+  }
+  // no CTA leaves (and frees its shared memory) while a peer may still read its partial
+  __syncwarp();
+  cluster_sync_all();
   tc_fence_before();
   __syncthreads();
   if (warp == 1) {
@@ -208,16 +231,12 @@ gemm_tokred_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
 }
 
 struct TokredState {
-  float* ws = nullptr;
-  int* counters = nullptr;
   int* err = nullptr;
-  long long ws_elems = 0;
-  int n_counters = 0;
   bool configured = false;
   int sms = 0;
 };
 TokredState g_tr[64];
-int g_tokred_target = 0;   // CTAs per launch to aim for (0: four per SM)
+int g_tokred_target = 0;   // CTAs per launch to aim for (0: one per SM)
 
 }  // namespace
 
@@ -262,32 +281,17 @@ int eri_gemm_tokred(const void* a, long long lda, const void* b, long long ldb, 
     cudaDeviceGetAttribute(&s.sms, cudaDevAttrMultiProcessorCount, dev);
     s.configured = true;
   }
-  const int m_tiles = (Mg + BM - 1) / BM;
-  const int ksteps = (T + BK - 1) / BK;
-  // About one CTA per SM measured best (every extra split adds a partial tile to store and re-read);
-  // at least four K steps per CTA pay for its prologue.
-  const int target = g_tokred_target > 0 ? g_tokred_target : s.sms;
-  int splits = (target + m_tiles / 2) / m_tiles;
-  if (splits > ksteps / 4) splits = ksteps / 4;
-  if (splits < 1) splits = 1;
-  if (splits > 64) splits = 64;
   if (!s.err) {
     if (cudaMalloc(&s.err, sizeof(int)) != cudaSuccess) return -3;
     cudaMemsetAsync(s.err, 0, sizeof(int), st);
   }
-  const long long need = splits > 1 ? (long long)m_tiles * splits * r * BM : 0;
-  if (need > s.ws_elems || m_tiles > s.n_counters) {
-    // grow the workspace (rare: first call and larger problems); the old buffers are released only
-    // after the stream has drained, since earlier launches may still use them
-    cudaStreamSynchronize(st);
-    if (s.ws) cudaFree(s.ws);
-    if (s.counters) cudaFree(s.counters);
-    s.ws_elems = need > (8ll << 20) ? need : (8ll << 20);
-    s.n_counters = m_tiles > 4096 ? m_tiles : 4096;
-    if (cudaMalloc(&s.ws, (size_t)s.ws_elems * sizeof(float)) != cudaSuccess) return -3;
-    if (cudaMalloc(&s.counters, (size_t)s.n_counters * sizeof(int)) != cudaSuccess) return -3;
-    cudaMemsetAsync(s.counters, 0, (size_t)s.n_counters * sizeof(int), st);
-  }
+  const int m_tiles = (Mg + BM - 1) / BM;
+  const int ksteps = (T + BK - 1) / BK;
+  // The token splits of one tile form a cluster (1, 2, 4 or 8 CTAs). Enough CTAs to cover the SMs,
+  // but at least four K steps each so that a CTA's prologue is paid for.
+  const int target = g_tokred_target > 0 ? g_tokred_target : s.sms;
+  int splits = 1;
+  while (splits < 8 && m_tiles * splits < target && ksteps / (splits * 2) >= 4) splits *= 2;
   CUtensorMap ta, tb;
   {
     uint64_t dims[2] = {(uint64_t)Mg, (uint64_t)T};
@@ -306,10 +310,20 @@ int eri_gemm_tokred(const void* a, long long lda, const void* b, long long ldb, 
   p.Mg = Mg; p.r = r; p.T = T; p.ldc = ldc; p.ksteps_total = ksteps; p.splits = splits;
   p.transpose_out = transpose_out; p.accumulate = accumulate; p.alpha = alpha;
   p.dbg_out_bytes = out_bytes;
-  p.out = (bf16*)out; p.ws = s.ws; p.counters = s.counters; p.err = s.err;
-  dim3 grid(m_tiles, splits);
-  gemm_tokred_kernel<<<grid, 192, SMEM, st>>>(ta, tb, p);
-  return (int)cudaGetLastError();
+  p.out = (bf16*)out; p.err = s.err;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(m_tiles, splits);
+  cfg.blockDim = dim3(192);
+  cfg.dynamicSmemBytes = SMEM;
+  cfg.stream = st;
+  cudaLaunchAttribute at[2];
+  at[0].id = cudaLaunchAttributeClusterDimension;
+  at[0].val.clusterDim.x = 1; at[0].val.clusterDim.y = splits; at[0].val.clusterDim.z = 1;
+  at[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  at[1].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = at;
+  cfg.numAttrs = 2;
+  return (int)cudaLaunchKernelEx(&cfg, gemm_tokred_kernel, ta, tb, p);
 }
 
 }  // extern "C"
