@@ -165,6 +165,13 @@ def bench_zero3(a, pg, rank, world, dev):
                 F.linear(x, full)
 
         t_f, t_n = timed(fused), timed(nccl)
+        # one more launch with the kernel's own %globaltimer record
+        z3.stamps = torch.zeros(8, dtype=torch.int64, device=dev)
+        dist.barrier()
+        fused()
+        torch.cuda.synchronize()
+        phases = z3.phase_times_us()
+        z3.stamps = None
         flops = 2.0 * M * n_out * k_in
         link_bytes = (world - 1) / world * n_out * k_in * 2
         if rank == 0:
@@ -174,7 +181,8 @@ def bench_zero3(a, pg, rank, world, dev):
                               "nvlink_bound_ms": round(link_bytes / (LINK_GBS * 1e9) * 1e3, 4),
                               **roofline_fields(flops, link_bytes, t_f, a.n_copy),
                               "n_copy": a.n_copy, "gemm_peak": tag, "status": z3.comm.status(), "gemm_err": F.gemm_error_check(),
-                              "two_cta_gather_launches": N_.require().eri_gemm2_gather_count()}))
+                              "two_cta_gather_launches": N_.require().eri_gemm2_gather_count(),
+                              "phases_us_rank0": {k: round(v, 1) for k, v in phases.items()}}))
         # forward + backward: two gathers inside GEMMs and the weight-gradient reduce-scatter inside the
         # dW GEMM's epilogue, against all-gather + three library GEMMs + NCCL reduce-scatter
         xg = x.clone().requires_grad_()
@@ -332,6 +340,65 @@ def bench_link(a, pg, rank, world, dev):
                           "ingress_gbs_per_gpu": round((world - 1) * nbytes / t / 1e6, 1)}))
 
 
+def bench_ring(a, pg, rank, world, dev):
+    """Context parallelism at the headline attention shape (B1, 4608 tokens, 24 heads of 128): ring
+    attention over NCCL send / recv (sequence sharded, keys and values travel) against Ulysses-style
+    head sharding (NCCL all-to-all, then the flash kernel over the full sequence with H / W heads) and
+    against one GPU doing the whole problem. Forward + backward; parity of the ring result against the
+    one-GPU flash kernel is printed with the times."""
+    from ..ops import flash_attn as FA
+    from ..parallel.ring_attention import ring_attention
+    B, L, H, D = 1, 4608, 24, 128
+    Ll, Hl = L // world, H // world
+    g = torch.Generator(device=dev).manual_seed(11)
+    full = [torch.randn(B, L, H, D, device=dev, generator=g).bfloat16() for _ in range(4)]     # same on every rank
+    q, k, v, do = (t[:, rank * Ll:(rank + 1) * Ll].contiguous() for t in full)
+
+    def ring():
+        ql, kl, vl = (t.clone().requires_grad_() for t in (q, k, v))
+        o = ring_attention(ql, kl, vl)
+        o.backward(do)
+        return o, ql.grad, kl.grad, vl.grad
+
+    def a2a(x, to_heads):
+        # [B, Ll, H, D] -> [B, L, Hl, D] (to_heads) or back
+        if to_heads:
+            src = x.view(B, Ll, world, Hl, D).permute(2, 0, 1, 3, 4).contiguous()
+            dst = torch.empty_like(src)
+            dist.all_to_all_single(dst, src)
+            return dst.permute(1, 0, 2, 3, 4).reshape(B, L, Hl, D)
+        src = x.view(B, world, Ll, Hl, D).permute(1, 0, 2, 3, 4).contiguous()
+        dst = torch.empty_like(src)
+        dist.all_to_all_single(dst, src)
+        return dst.permute(1, 2, 0, 3, 4).reshape(B, Ll, H, D)
+
+    def ulysses():
+        qh, kh, vh, doh = (a2a(t, True) for t in (q, k, v, do))
+        o, lse = FA.fwd(qh, kh, vh)
+        dq, dk, dv = FA.bwd(doh, qh, kh, vh, o, lse)
+        return [a2a(t, False) for t in (o, dq, dk, dv)]
+
+    def single():
+        o, lse = FA.fwd(full[0], full[1], full[2])
+        return (o,) + tuple(FA.bwd(full[3], full[0], full[1], full[2], o, lse))
+
+    ref = single()
+    got = ring()
+    err = max(float((got[i].float() - ref[i][:, rank * Ll:(rank + 1) * Ll].float()).abs().max() /
+                    ref[i].float().abs().max()) for i in range(4))
+    e = torch.tensor([err], device=dev)
+    dist.all_reduce(e, dist.ReduceOp.MAX)
+    t_r, t_u, t_s = timed(ring), timed(ulysses), timed(single)
+    if rank == 0:
+        flops = 3.5 * 4.0 * L * L * D * H * B                                  # forward + 2.5x backward
+        print(json.dumps({"what": f"context parallel attention fwd+bwd, B{B} L{L} H{H} Dh{D}", "world": world,
+                          "ring_nccl_ms": round(t_r, 4), "ulysses_all_to_all_ms": round(t_u, 4),
+                          "one_gpu_flash_ms": round(t_s, 4), "ideal_ms": round(t_s / world, 4),
+                          "ring_vs_one_gpu_max_err_rel": round(float(e), 5),
+                          "ring_tflops_per_gpu": round(flops / world / t_r / 1e9, 1),
+                          "fa_err": FA.check_error()}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--params", type=int, default=56_000_000)
@@ -344,9 +411,9 @@ def main():
     pg = ProcessGroup()
     sweep = [int(v) for v in str(a.n_copy).split(",")]
     for w in a.what.split(","):
-        for nc in (sweep if w not in ("fused_dp", "link") else sweep[:1]):
+        for nc in (sweep if w not in ("fused_dp", "link", "ring") else sweep[:1]):
             a.n_copy = nc
-            {"fused_dp": bench_fused_dp, "zero3": bench_zero3, "ulysses": bench_ulysses, "link": bench_link}[w](
+            {"fused_dp": bench_fused_dp, "zero3": bench_zero3, "ulysses": bench_ulysses, "link": bench_link, "ring": bench_ring}[w](
                 a, pg, rank, world, dev)
             dist.barrier()
             torch.cuda.empty_cache()

@@ -1,7 +1,7 @@
 """Training-step throughput of the multi-GPU configurations other than the headline one:
 
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 \
-        -m eridiffusion_b200.cli.config_bench --config sdxl_zero2|qwen_zero3|ltx_ulysses \
+        -m eridiffusion_b200.cli.config_bench --config sdxl_zero2|qwen_zero3|ltx_ulysses|ltx_av|sd15|sd35_medium \
         [--steps 4 --warmup 2] [--scale 1.0]
 
 * ``sdxl_zero2``   SDXL UNet (2.57 B parameters) full fine-tune, eps objective, 1024^2 (128 x 128
@@ -13,6 +13,12 @@
 * ``ltx_ulysses``  LTX-video-architecture DiT (48 blocks, hidden 4096) LoRA on a 19 008-token clip with
                    the sequence sharded over the ranks (Ulysses): both all-to-alls folded into the
                    QKV / output projections.
+
+* ``ltx_av``       LTX audio + video DiT (48 block pairs with cross-modal attention) LoRA r16 on a 9-frame
+                   16 x 16 clip (2304 video tokens) with 64 audio tokens; data parallel over the ranks.
+* ``sd15``         SD1.5 UNet LoRA r16, eps objective, 512^2 (head sizes 40 / 80 / 160); data parallel.
+* ``sd35_medium``  SD3.5-medium MMDiT (24 joint blocks, dual attention in the first 13) LoRA r16, 1024^2;
+                   data parallel.
 
 ``--scale`` shrinks the depth (number of blocks) for quick checks; the printed line says so. Times are
 CUDA events bracketed by barriers, max over ranks; synthetic N(0,1) inputs, random-init weights.
@@ -31,12 +37,12 @@ from ..data import synthetic_batch
 from ..models import build_model
 from ..ops import functional as F
 from ..parallel.dist import GradSync, ProcessGroup, init_from_env
-from ..train.trainer import Trainer, TrainerConfig, default_forward, ltx_forward
+from ..train.trainer import Trainer, TrainerConfig, default_forward, ltx_av_forward, ltx_forward
 
 
 def main(argv=None):
     ap = argparse.ArgumentParser()
-    ap.add_argument("--config", required=True, choices=["sdxl_zero2", "qwen_zero3", "ltx_ulysses"])
+    ap.add_argument("--config", required=True, choices=["sdxl_zero2", "qwen_zero3", "ltx_ulysses", "ltx_av", "sd15", "sd35_medium"])
     ap.add_argument("--steps", type=int, default=4)
     ap.add_argument("--warmup", type=int, default=2)
     ap.add_argument("--scale", type=float, default=1.0, help="fraction of the block count to build")
@@ -77,6 +83,40 @@ def main(argv=None):
         batch = lambda i: synthetic_batch("qwen_image", a.batch, dev, dt, 100 + i * world + rank)
         info = {"model": f"Qwen-Image-arch MMDiT ({depth} dual-stream blocks) full fine-tune",
                 "parallelism": f"zero3-{world} (gather-in-GEMM)", "tokens": 4096 + 256}
+    elif a.config in ("ltx_av", "sd15", "sd35_medium"):
+        lora = AdapterConfig(rank=16, alpha=16, dtype=dt)
+        gs = GradSync("fused") if world > 1 else None
+        if a.config == "ltx_av":
+            depth = max(1, int(round(48 * a.scale)))
+            model = build_model("ltx_av", device=dev, depth=depth)
+            frames, hh, ww, la = 9, 16, 16, 64
+            cfg = TrainerConfig(mode="lora", adapter=lora, objective="flow", optimizer="adamw8bit", lr=1e-4, patch=1,
+                                seed=0, guidance=None)
+            tr = Trainer(model, cfg, grad_sync=gs, forward_fn=ltx_av_forward)
+
+            def batch(i):
+                b = synthetic_batch("ltx", a.batch, dev, dt, 100 + i * world + rank, 512, 512, frames=frames)
+                g = torch.Generator().manual_seed(7 + i * world + rank)
+                audio = torch.randn(a.batch, 128, la, 1, generator=g).to(dt).to(dev)
+                b["latents"] = torch.cat([b["latents"], audio], dim=2)          # [video tokens | audio tokens]
+                b["grid_fhw"] = (frames, hh, ww)
+                return b
+            info = {"model": f"LTX audio+video DiT ({depth} block pairs) LoRA r16", "tokens": frames * hh * ww + la}
+        elif a.config == "sd15":
+            from ..models.sdxl_unet import sdxl_forward
+            model = build_model("sd15", device=dev)
+            cfg = TrainerConfig(mode="lora", adapter=lora, objective="eps", optimizer="adamw8bit", lr=1e-4, patch=1, seed=0)
+            tr = Trainer(model, cfg, grad_sync=gs, forward_fn=sdxl_forward)
+            batch = lambda i: synthetic_batch("sd15", a.batch, dev, dt, 100 + i * world + rank, 512, 512)
+            info = {"model": "SD1.5 UNet LoRA r16, 512^2", "tokens": 64 * 64}
+        else:
+            model = build_model("sd35_medium", device=dev)
+            cfg = TrainerConfig(mode="lora", adapter=lora, objective="flow", optimizer="adamw8bit", lr=1e-4, seed=0,
+                                guidance=None)
+            tr = Trainer(model, cfg, grad_sync=gs, forward_fn=default_forward)
+            batch = lambda i: synthetic_batch("sd35", a.batch, dev, dt, 100 + i * world + rank)
+            info = {"model": "SD3.5-medium MMDiT LoRA r16, 1024^2", "tokens": 4096 + 333}
+        info["parallelism"] = f"dp{world}"
     else:
         depth = max(1, int(round(48 * a.scale)))
         model = build_model("ltx_video", device=dev, depth=depth)
@@ -137,7 +177,7 @@ def main(argv=None):
                           "ms_per_step": round(ms / a.steps, 2),
                           "samples_per_s": round(samples * a.steps / (ms / 1e3), 4),
                           "loss": round(float(loss), 5), "depth_scale": a.scale, "dtype": "bf16",
-                          "data": "synthetic", "kernel_errors": errs,
+                          "data": "synthetic", "kernel_errors": errs, "attention_forward_calls": dict(F.ATTENTION_CALLS),
                           "peak_mem_gb": round(torch.cuda.max_memory_allocated() / 2 ** 30, 1)}))
     if world > 1:
         dist.barrier()

@@ -1,6 +1,6 @@
 """Per-kernel timing against the library equivalents and the measured roofline.
 
-    python -m eridiffusion_b200.cli.kernel_bench [--what gemm,skinny,attn,elementwise,optim,dequant,narrow,wgrad] [--small]
+    python -m eridiffusion_b200.cli.kernel_bench [--what gemm,skinny,attn,elementwise,optim,dequant,narrow,wgrad,small_m] [--small]
 
 Timing: CUDA events on the launching stream, >= 3 warm-up launches, L2 flushed between timed
 launches by writing a 256 MB buffer, median of the timed launches. Roofline denominators come from
@@ -75,6 +75,27 @@ def bench_gemm(small):
         t_mn = timeit(lambda: F.gemm_native(a, bt, out=out, b_mn=True))
         print(f"{M:6d} {N:6d} {K:6d} | {t_ours*1e6:9.1f} {fl_/t_ours/1e12:7.1f} {fl_/t_ours/fl:6.2f} | "
               f"{t_lib*1e6:9.1f} {fl_/t_lib/1e12:7.1f} | {t_lora*1e6:9.1f} | B[K,N]: {t_mn*1e6:9.1f}   ({tag})")
+    assert F.gemm_error_check() == 0
+
+
+def bench_small_m(small):
+    """Text-stream GEMMs (512 tokens): few 256 x 256 pair tiles, so the tile width decides how many SMs
+    work. Pair kernel (default route) against the one-CTA kernel at 128- and 64-column tiles and cuBLAS;
+    second line: the same with B given as [K, N] (the dX product)."""
+    bw, fl, tag = peaks()
+    for M, N, K in ([(512, 3072, 3072), (512, 3072, 12288), (512, 3072, 9216), (512, 9216, 3072), (512, 12288, 3072)]
+                    if not small else [(512, 1024, 1024)]):
+        a = torch.randn(M, K, device="cuda").bfloat16()
+        b = torch.randn(N, K, device="cuda").bfloat16()
+        bt = b.t().contiguous()
+        out = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+        fl_ = 2.0 * M * N * K
+        for mn, bb in ((False, b), (True, bt)):
+            ts = [timeit(lambda: F.gemm_native(a, bb, out=out, b_mn=mn, force_bn=f)) for f in (256, 128, 64)]
+            t_auto = timeit(lambda: F.gemm_native(a, bb, out=out, b_mn=mn))
+            t_lib = timeit(lambda: torch.matmul(a, b.t() if not mn else bt, out=out))
+            print(f"{M}x{N}x{K} {'B[K,N]' if mn else 'B[N,K]'}: pair {ts[0]*1e6:6.1f} | one-CTA bn128 {ts[1]*1e6:6.1f} | bn64 {ts[2]*1e6:6.1f} | "
+                  f"default route {t_auto*1e6:6.1f} us {fl_/t_auto/1e12:5.0f} TF/s | cuBLAS {t_lib*1e6:6.1f} us")
     assert F.gemm_error_check() == 0
 
 
@@ -250,7 +271,7 @@ def main():
     a = ap.parse_args()
     for w in a.what.split(","):
         {"gemm": bench_gemm, "skinny": bench_skinny, "elementwise": bench_elementwise, "optim": bench_optim,
-         "attn": bench_attn, "dequant": bench_dequant, "narrow": bench_narrow, "wgrad": bench_wgrad}[w](a.small)
+         "attn": bench_attn, "dequant": bench_dequant, "narrow": bench_narrow, "wgrad": bench_wgrad, "small_m": bench_small_m}[w](a.small)
 
 
 if __name__ == "__main__":

@@ -49,6 +49,7 @@ struct Gemm2Params {
   bf16* out2;
   bf16* pre_out;
   int* err;
+  unsigned long long* stamps;   // optional %globaltimer phase record of a gather launch (gemm_args.h)
   // gather mode (see gather_copy.cuh): the first n_copy CTAs (whole clusters) run copy jobs
   int n_copy, n_jobs;
   const GatherJob* jobs;
@@ -112,12 +113,17 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~uintptr_t(1023));
+  if (p.stamps && threadIdx.x == 0) atomicMin(p.stamps + 0, (unsigned long long)globaltimer_ns());
   if ((int)blockIdx.x < p.n_copy) {
     // copy clusters (n_copy is even): both CTAs move slabs and leave; they take no part in the
     // cluster barriers or the tensor-memory allocation of the compute clusters. The copy ring reuses
     // the operand stages' shared memory; its barriers sit where the GEMM's do.
     constexpr int RING = (STAGES * STAGE_BYTES) / kCopyStageBytes;
     copy_role(p, smem, RING < 6 ? RING : 6, (int)blockIdx.x);
+    if (p.stamps) {
+      __syncthreads();
+      if (threadIdx.x == 0) atomicMax(p.stamps + 1, (unsigned long long)globaltimer_ns());
+    }
     return;
   }
   uint64_t* full = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
@@ -166,6 +172,7 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
       uint32_t phase = 0;
       bool ok = true;
       bool dep_done = false;
+      unsigned long long waited = 0;   // ns spent on slab counters (recorded only with p.stamps)
       for (int t = cluster_id; t < tiles && ok; t += num_clusters) {
         int m_blk, n_blk;
         tile_coords(t, num_m, num_n, p.rot_n, m_blk, n_blk);
@@ -175,11 +182,13 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
         if (p.b_flag_rows && !b_rows_local) {
           // every slab that the B rows staged by THIS CTA touch must have landed
           const int f0 = n0 / p.b_flag_rows, f1 = (min(n0 + BNH, p.N) - 1) / p.b_flag_rows;
+          const unsigned long long tw = p.stamps ? globaltimer_ns() : 0ull;
           for (int f = f0; f <= f1 && ok; ++f)
             if (!wait_slab(p, f)) {
               atomicExch(p.err, 45);
               ok = false;
             }
+          if (p.stamps) waited += globaltimer_ns() - tw;
           if (!ok) break;
           fence_proxy_async_all();
         }
@@ -201,11 +210,13 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
               int f = (kk * BK) / p.a_flag_cols;
               if (p.a_flag_rows) f = f * p.a_row_groups + min(m0, p.M - 1) / p.a_flag_rows;
               if (f != a_ready) {
+                const unsigned long long tw = p.stamps ? globaltimer_ns() : 0ull;
                 if (!wait_slab(p, f)) {
                   atomicExch(p.err, 46);
                   ok = false;
                   break;
                 }
+                if (p.stamps) waited += globaltimer_ns() - tw;
                 fence_proxy_async_all();
                 a_ready = f;
               }
@@ -244,6 +255,11 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
             phase ^= 1;
           }
         }
+      }
+      if (p.stamps && waited) {
+        atomicAdd(p.stamps + 3, waited);
+        atomicMax(p.stamps + 4, waited);
+        atomicAdd(p.stamps + 5, 1ull);
       }
     }
   } else if (warp == 1) {
@@ -513,6 +529,7 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
   tc_fence_before();
   __syncthreads();
   cluster_sync_all();   // the peer may still read this CTA's shared memory / signal its barriers
+  if (p.stamps && threadIdx.x == 0) atomicMax(p.stamps + 2, (unsigned long long)globaltimer_ns());
   if (warp == 1) {
     __syncwarp();
     tmem_dealloc2(tmem_base, 512);
@@ -662,6 +679,7 @@ int eri_gemm2_bf16(const EriGemmArgs2* g, void* stream) {
   p.err = g2_err;
   p.dbg_out_bytes = g->dbg_out_bytes; p.dbg_out2_bytes = g->dbg_out2_bytes;
   p.dbg_pre_bytes = g->dbg_pre_bytes; p.dbg_res_bytes = g->dbg_res_bytes;
+  p.stamps = g->n_copy ? g->stamps : nullptr;
   p.n_copy = g->n_copy; p.n_jobs = g->n_jobs; p.jobs = (const GatherJob*)g->jobs;
   p.flags = (unsigned int*)g->flags; p.flag_target = (const unsigned int*)g->flag_target;
   p.b_flag_rows = g->b_flag_rows; p.a_flag_cols = g->a_flag_cols; p.a_flag_rows = g->a_flag_rows;

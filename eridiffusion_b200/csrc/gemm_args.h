@@ -67,6 +67,12 @@ struct EriGemmArgs {
   // receive buffer [world][scatter_local_rows, N] (the weight-gradient reduce-scatter of ZeRO-3
   // folded into the dW GEMM: every rank's partial slab lands at its owner as the tiles finish).
   int scatter_mode;
+  // Gather mode, optional: device array of 8 unsigned 64-bit words that the launch fills with
+  // %globaltimer readings (ns): [0] earliest CTA start (caller presets it to all ones), [1] latest
+  // end of a copy CTA (every slab has landed), [2] latest end of a compute CTA, [3] sum and [4]
+  // maximum over the compute CTAs' TMA producers of the time spent waiting for slab counters,
+  // [5] number of producers that waited at all. Null: nothing is recorded.
+  unsigned long long* stamps;
 };
 
 }  // extern "C"

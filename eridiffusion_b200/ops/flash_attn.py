@@ -72,9 +72,10 @@ def _pair_call(lib, q, k, v, out, lse, scale):
                                        B, H, Lq, k.shape[1], D, scale, _poly_pairs(), N.stream_ptr())
 
 
-def pair_forward_ok(device) -> bool:
-    """Whether the CTA-pair forward kernel may be used on ``device`` (checked once per device)."""
-    if not _PAIR_ENABLED:
+def pair_forward_ok(device, force: bool = False) -> bool:
+    """Whether the CTA-pair forward kernel may be used on ``device`` (checked once per device).
+    ``force`` runs the self-check although ``ERI_B200_FA_PAIR`` leaves the kernel off (tests, benchmarks)."""
+    if not (_PAIR_ENABLED or force):
         return False
     key = str(device)
     if key in _PAIR_OK:

@@ -17,6 +17,7 @@ _BACKEND = os.environ.get("ERI_B200_BACKEND", "fused")  # "fused" | "eager"
 _GEMM_NATIVE = os.environ.get("ERI_B200_GEMM", "native")  # "native" | "library"
 _ATTN_NATIVE = os.environ.get("ERI_B200_ATTN", "native")  # "native" | "library"
 _GEMM_PAIR = os.environ.get("ERI_B200_GEMM2", "1") == "1"  # two-CTA tiles for large problems
+_PAIR_MIN_TILES = int(os.environ.get("ERI_B200_PAIR_MIN_TILES", "36"))  # at most this many 256 x 256 tiles: one-CTA kernel
 _GATHER_PAIR = os.environ.get("ERI_B200_GATHER_PAIR", "1") == "1"  # gather-fused GEMMs on the two-CTA kernel
 _GATHER_LOCAL = os.environ.get("ERI_B200_GATHER_LOCAL", "1") == "1"  # own slab read in place, not copied
 _SCATTER_PAIR = os.environ.get("ERI_B200_SCATTER_PAIR", "1") == "1"  # peer-scatter epilogue on the two-CTA kernel
@@ -412,6 +413,8 @@ def gemm_native(a, b, *, out=None, alpha=1.0, bias=None, lora_h=None, lora_b=Non
         g.b_flag_rows, g.a_flag_cols = gather.get("b_flag_rows", 0), gather.get("a_flag_cols", 0)
         g.rot_n_rows, g.rot_k_cols = gather.get("rot_n_rows", 0), gather.get("rot_k_cols", 0)
         g.a_flag_rows = gather.get("a_flag_rows", 0)
+        st = gather.get("stamps")                 # optional uint64[8] phase record (see gemm_args.h)
+        g.stamps = st.data_ptr() if st is not None else None
         loc = gather.get("local") if _GATHER_LOCAL else None
         if loc is not None:
             g.b_local, g.ldb_local = loc["ptr"], loc["ld"]
@@ -426,8 +429,13 @@ def gemm_native(a, b, *, out=None, alpha=1.0, bias=None, lora_h=None, lora_b=Non
             g.scatter_out[i] = ptr_
         if scatter.get("rowsq") is not None:
             g.rowsq, g.rowsq_parts = scatter["rowsq"].data_ptr(), scatter["rowsq"].shape[0]
+    # Few pair tiles (the 512-token text stream against a 3072-wide weight: 24 tiles for 74 CTA pairs)
+    # leave most SMs idle; the one-CTA kernel's 128-column tiles spread the same work over four times
+    # as many CTAs (measured 22.5 against 30.7 us at 512 x 3072 x 3072, 61 against 78 us at K = 12288).
+    few_tiles = (force_bn == 0 and not (a_mn or glu) and gather is None and scatter is None
+                 and ((M + 255) // 256) * ((Nn + 255) // 256) <= _PAIR_MIN_TILES)
     if (_GEMM_PAIR or a_mn or glu) and (gather is None or _GATHER_PAIR) and (scatter is None or _SCATTER_PAIR) \
-            and force_bn in (0, 256) and M >= 256 and Nn >= 256:
+            and force_bn in (0, 256) and M >= 256 and Nn >= 256 and not few_tiles:
         # two-CTA 256x256 tiles; in gather mode with whole copy clusters in front (answers -30 when
         # the gather plan does not line up with pair tiles, and the one-CTA kernel takes over)
         code = lib.eri_gemm2_bf16(g, N.stream_ptr())
@@ -904,6 +912,10 @@ def small_linear(x, w, bias=None, silu_in=False):
 _ATTN_ENV_POLICY = any(os.environ.get(k) for k in ("ATTN_Q_CHUNK", "ATTN_KV_CHUNK", "ATTN_MAX_WS_MB", "ATTN_MIN_FREE_MB"))
 
 
+_HEAD_PAD = os.environ.get("ERI_B200_ATTN_HEAD_PAD", "1") == "1"
+ATTENTION_CALLS = {"native": 0, "library": 0}     # forward calls by path since import (benchmarks print it)
+
+
 def attention(q, k, v, scale=None, mask=None, out=None):
     """Non-causal attention over token-major [B, L, H, Dh] tensors. ``out``: optional destination
     buffer for the native kernel (ignored by the library path, which returns its own tensor)."""
@@ -911,7 +923,21 @@ def attention(q, k, v, scale=None, mask=None, out=None):
         from . import flash_attn as FA
         # key-only masks (text padding, [B, 1, 1, T]) ride on the native kernel as a per-key bias
         if FA.supported(q, k, v) and (mask is None or FA.mask_is_key_only(mask, q.shape[0], k.shape[1])):
+            ATTENTION_CALLS["native"] += 1
             return FA.flash_attention(q, k, v, scale, out, mask)
+        # other head sizes below 128 (SD1.5: 40 and 80) ride on the 64 / 128 kernels with zero columns
+        # appended: zero query / key columns leave the scores unchanged, zero value columns give zero
+        # output columns that are cut off again (the pad and the slice are differentiable copies)
+        D = q.shape[-1]
+        if _HEAD_PAD and D not in (64, 128) and 16 <= D < 128 and D % 8 == 0 and \
+                (mask is None or FA.mask_is_key_only(mask, q.shape[0], k.shape[1])):
+            pad = (64 if D < 64 else 128) - D
+            qp, kp, vp = (torch.nn.functional.pad(t, (0, pad)) for t in (q, k, v))
+            if FA.supported(qp, kp, vp):
+                ATTENTION_CALLS["native"] += 1
+                sc = scale if scale is not None else 1.0 / math.sqrt(D)
+                return FA.flash_attention(qp, kp, vp, sc, None, mask)[..., :D].contiguous()
+    ATTENTION_CALLS["library"] += 1
     if mask is None and _ATTN_ENV_POLICY:
         from ..utils.env_flags import library_attention
         o = library_attention(q, k, v, scale)

@@ -45,6 +45,7 @@ class Zero3Context:
         self.rank, self.world = self.pg.rank, self.pg.world_size
         # symmetric memory: parameter shards (heap_bytes), the dW staging buffer and two receive
         # buffers of the fused weight-gradient reduce-scatter (alternating by layer)
+        self.stamps = None
         self.fused_rs = os.environ.get("ERI_B200_ZERO3_FUSED_RS", "1") == "1"
         self.heap = SymmetricHeap(heap_bytes + max_weight_elems * 2 * (3 if self.fused_rs else 1) + (1 << 20),
                                   group=self.pg.group)
@@ -100,7 +101,22 @@ class Zero3Context:
     def gather_args(self, pl):
         if self.copy_stream is not None:
             return pl.launch_args_engine(self.copy_stream)
-        return pl.launch_args()
+        args = pl.launch_args()
+        if self.stamps is not None:
+            # phase record of the next gather launch: [0] is a minimum, so it starts at all ones
+            self.stamps.zero_()
+            self.stamps[0] = -1
+            args = dict(args, stamps=self.stamps)
+        return args
+
+    def phase_times_us(self):
+        """Phases of the last gather-fused launch recorded with ``stamps`` (a device int64[8] tensor
+        assigned by the caller), in microseconds from the first CTA's start."""
+        s = self.stamps.tolist()
+        t0 = s[0]
+        return {"all_slabs_landed": (s[1] - t0) / 1e3, "last_compute_cta_done": (s[2] - t0) / 1e3,
+                "producers_that_waited": s[5], "mean_wait_of_those": (s[3] / s[5] / 1e3) if s[5] else 0.0,
+                "longest_wait": s[4] / 1e3}
 
     def barrier(self):
         """Cross-GPU barrier on the current stream (a kernel; no host synchronisation)."""

@@ -341,3 +341,13 @@ def default_forward(model, xt, t, batch, cfg):
 def ltx_forward(model, xt, t, batch, cfg):
     """LTX-style call: model(tokens, text, t, (frames, h, w))."""
     return model(xt, batch["txt"], t, batch["grid_fhw"])
+
+
+def ltx_av_forward(model, xt, t, batch, cfg):
+    """LTX audio + video: the training latent is the token sequence [video tokens | audio tokens]
+    (both 128 channels), noised with one timestep; the prediction is the two streams' outputs in the
+    same order, so the loss covers both (joint forward of ltx2_model.rs:53-151)."""
+    f, h, w = batch["grid_fhw"]
+    lv = f * h * w
+    pv, pa = model(xt[:, :lv].contiguous(), xt[:, lv:].contiguous(), batch["txt"], t, batch["grid_fhw"])
+    return torch.cat([pv, pa], dim=1)

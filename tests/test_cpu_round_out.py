@@ -404,3 +404,26 @@ def test_ltx_diffusers_layout_round_trip(tmp_path):
     del ext["transformer_blocks.1.attn1.to_v.weight"]
     with pytest.raises(KeyError, match="expected"):
         remap_ltx_state_dict(ext)
+
+
+def test_ltx_audio_video_trains_through_the_trainer():
+    """[video tokens | audio tokens] as one noised latent sequence: the joint forward's two
+    predictions come back in the same order and both streams' adapters receive gradient."""
+    from eridiffusion_b200.adapters import AdapterConfig
+    from eridiffusion_b200.train.trainer import Trainer, TrainerConfig, ltx_av_forward
+    from eridiffusion_b200.models import build_model
+    torch.manual_seed(0)
+    m = build_model("ltx_av", dtype=torch.float32, hidden=48, num_heads=2, depth=2, in_channels=8,
+                    context_dim=24, caption_dim=12, audio=dict(audio_in_channels=8, audio_heads=2,
+                                                               audio_head_dim=8, audio_context_dim=16))
+    cfg = TrainerConfig(mode="lora", adapter=AdapterConfig(rank=4, alpha=4, dtype=torch.float32), objective="flow",
+                        optimizer="adamw", lr=1e-2, patch=1, seed=0, guidance=None)
+    tr = Trainer(m, cfg, forward_fn=ltx_av_forward)
+    grid, la = (2, 2, 3), 5
+    batch = {"latents": torch.randn(2, 8, 12 + la, 1), "txt": torch.randn(2, 5, 12), "grid_fhw": grid}
+    l0 = float(tr.train_step(batch))
+    for _ in range(5):
+        l1 = float(tr.train_step(batch))
+    assert l0 == l0 and l1 < l0
+    names = [n for n, p in m.named_parameters() if p.requires_grad]
+    assert any(".audio." in n for n in names) and any(".video." in n for n in names) and any("a2v" in n for n in names)

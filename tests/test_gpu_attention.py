@@ -164,7 +164,7 @@ def test_flash_headline_shape_against_fp32():
 def test_flash_fwd_cta_pair_kernel(B, H, Lq, Lk):
     """The CTA-pair forward (two CTAs share every K / V tile) against fp32 and against the one-CTA
     kernel, including query counts that leave the pair's second tile partly or wholly empty."""
-    assert FA.pair_forward_ok(torch.device("cuda", 0)), "the CTA-pair forward failed its self-check"
+    assert FA.pair_forward_ok(torch.device("cuda", 0), force=True), "the CTA-pair forward failed its self-check"
     lib = FA.N.require()
     q, k, v = mk(B, Lq, H, 128, 1), mk(B, Lk, H, 128, 2), mk(B, Lk, H, 128, 3)
     out = torch.full_like(q, float("nan"))
@@ -177,3 +177,25 @@ def test_flash_fwd_cta_pair_kernel(B, H, Lq, Lk):
     assert (out.float() - ref).abs().max().item() < 2e-2
     s = torch.einsum("blhd,bmhd->bhlm", q.float(), k.float()) / math.sqrt(128)
     assert (lse - torch.logsumexp(s, -1)).abs().max().item() < 2e-2
+
+
+@pytest.mark.parametrize("Dh,Lq,Lk", [(40, 1024, 1024), (80, 256, 256), (40, 1024, 77), (80, 320, 77)])
+def test_other_head_sizes_ride_on_the_native_kernels(Dh, Lq, Lk):
+    """SD1.5 head sizes (40 at 64 x 64, 80 at 32 x 32; self- and 77-key cross-attention): zero-padded to
+    64 / 128 columns for the tcgen05 kernels; output and gradients equal fp32 attention at the true size."""
+    from eridiffusion_b200.ops import functional as F
+    B, H = 2, 8
+    q, k, v = mk(B, Lq, H, Dh, 1), mk(B, Lk, H, Dh, 2), mk(B, Lk, H, Dh, 3)
+    q.requires_grad_(); k.requires_grad_(); v.requires_grad_()
+    n0 = F.ATTENTION_CALLS["native"]
+    o = F.attention(q, k, v)
+    assert F.ATTENTION_CALLS["native"] == n0 + 1 and o.shape == q.shape and o.is_contiguous()
+    do = mk(B, Lq, H, Dh, 4)
+    o.backward(do)
+    assert FA.check_error() == 0
+    qr, kr, vr = (t.detach().float().requires_grad_() for t in (q, k, v))
+    ref = R.attention_fp32(qr, kr, vr)
+    ref.backward(do.float())
+    rel = lambda a, b: (a.float() - b).abs().max().item() / b.abs().max().item()
+    assert rel(o, ref) < 1.5e-2
+    assert rel(q.grad, qr.grad) < 2.5e-2 and rel(k.grad, kr.grad) < 2.5e-2 and rel(v.grad, vr.grad) < 2.5e-2

@@ -44,8 +44,10 @@ def test_norm_modulate_fwd_bwd(rms, D):
     y.backward(g)
     yr.backward(g.float())
     close(x.grad, xr.grad, 3e-2, 3e-2)
-    close(mod.grad, modr.grad, 0.15, 3e-2)
-    close(w.grad, wr.grad, 0.3, 3e-2)
+    # parameter gradients are sums over B * L rows: bounded relative to the fp32 reference's own
+    # magnitude (measured: worst element 0.37 % of |ref| + 1 % of max|ref|)
+    close(mod.grad, modr.grad, 0.0, 1e-2, rel_to_max=1e-2)
+    close(w.grad, wr.grad, 0.0, 1e-2, rel_to_max=1e-2)
 
 
 @pytest.mark.parametrize("rms", [False, True])
@@ -90,7 +92,7 @@ def test_qknorm_rope_joint(Dh):
     for a, b in zip(ins, insr):
         close(a.grad, b.grad, 4e-2, 3e-2)
     for a, b in zip(scales, scr):
-        close(a.grad, b.grad, 0.5, 3e-2)
+        close(a.grad, b.grad, 0.0, 1e-2, rel_to_max=1e-2)
 
 
 def test_gate_residual_and_acts():
@@ -103,7 +105,7 @@ def test_gate_residual_and_acts():
     close(out, outr, 2e-2)
     g = rnd(B, L, D, seed=3)
     out.backward(g); outr.backward(g.float())
-    close(x.grad, xr.grad, 1e-2); close(y.grad, yr.grad, 2e-2); close(gate.grad, gr.grad, 0.2, 3e-2)
+    close(x.grad, xr.grad, 1e-2); close(y.grad, yr.grad, 2e-2); close(gate.grad, gr.grad, 0.0, 1e-2, rel_to_max=1e-2)
     for fn, rf in ((F.gelu_tanh, R.gelu_tanh), (F.silu, R.silu)):
         a = rnd(4, 1024).requires_grad_()
         ar = a.detach().float().requires_grad_()
