@@ -341,10 +341,16 @@ __global__ void qknorm_rope_bwd_kernel(const bf16* __restrict__ dq, const bf16* 
                                        int in_tok_stride, int in_part_stride,
                                        int grad_tok_stride) {
   constexpr int Dh = EPL * 32;
-  const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   const int lane = threadIdx.x & 31;
   const int total = B * L * H;
-  if (warp >= total) return;
+  const int nwarps_grid = (gridDim.x * blockDim.x) >> 5;
+  // Scale gradients: every warp keeps its share in registers over its (batch, token, head) items;
+  // the CTA adds its warps in shared memory and issues one global atomic per element. (One atomic
+  // per element per item put 100 k warps on the same 128 addresses: 1.2 ms per call.)
+  float acc_s[2][EPL];
+#pragma unroll
+  for (int j = 0; j < EPL; ++j) acc_s[0][j] = acc_s[1][j] = 0.f;
+  for (int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5; warp < total; warp += nwarps_grid) {
   const int h = warp % H;
   const int l = (warp / H) % L;
   const int b = warp / (H * L);
@@ -394,7 +400,7 @@ __global__ void qknorm_rope_bwd_kernel(const bf16* __restrict__ dq, const bf16* 
         for (int j = 0; j < EPL; ++j) {
           xh[j] = x[j] * r;
           float sj = __bfloat162float(sp[lane * EPL + j]);
-          if (dsp) atomicAdd(dsp + lane * EPL + j, g[j] * xh[j]);
+          if (dsp) acc_s[part][j] += g[j] * xh[j];
           g[j] *= sj;
           c2 += g[j] * xh[j];
         }
@@ -406,6 +412,22 @@ __global__ void qknorm_rope_bwd_kernel(const bf16* __restrict__ dq, const bf16* 
 #pragma unroll
     for (int j = 0; j < EPL; j += 2)
       *reinterpret_cast<__nv_bfloat162*>(dst + j) = __floats2bfloat162_rn(g[j], g[j + 1]);
+  }
+  }
+  if (dqs || dks) {
+    __shared__ float red[2][Dh];
+    for (int i = threadIdx.x; i < 2 * Dh; i += blockDim.x) (&red[0][0])[i] = 0.f;
+    __syncthreads();
+#pragma unroll
+    for (int j = 0; j < EPL; ++j) {
+      if (dqs) atomicAdd(&red[0][lane * EPL + j], acc_s[0][j]);
+      if (dks) atomicAdd(&red[1][lane * EPL + j], acc_s[1][j]);
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < Dh; i += blockDim.x) {
+      if (dqs) atomicAdd(dqs + i, red[0][i]);
+      if (dks) atomicAdd(dks + i, red[1][i]);
+    }
   }
 }
 
@@ -755,7 +777,9 @@ int eri_qknorm_rope_bwd(const void* dq, const void* dk, const void* dv, const vo
                         int grad_tok_stride, void* stream) {
   const int total = B * L * H;
   const int block = 256;
-  const int grid = (total * 32 + block - 1) / block;
+  int grid = (total * 32 + block - 1) / block;
+  // with scale gradients the grid is capped (a CTA then loops over its items and reduces once)
+  if ((dqs || dks) && grid > 148 * 8) grid = 148 * 8;
   if (Dh == 128)
     qknorm_rope_bwd_kernel<4><<<grid, block, 0, (cudaStream_t)stream>>>(
         (const bf16*)dq, (const bf16*)dk, (const bf16*)dv, (const bf16*)qkv, (const bf16*)qs,

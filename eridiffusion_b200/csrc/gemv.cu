@@ -96,3 +96,117 @@ extern "C" int eri_gemv_bf16(const void* x, const void* w, const void* bias, voi
 #undef ERI_GEMV_CASE
   return (int)cudaGetLastError();
 }
+
+// ---------------------------------------------------------------------------------------------
+// Backward of the small-M linear (T <= 8 rows of dy).
+//
+//   weight gradient  dW[n, k] (+)= sum_t dy[t, n] * x[t, k]        bound by writing dW once
+//   input gradient   part[s, t, k] = sum_{n in split s} dy[t, n] * W[n, k]   bound by reading W once;
+//                    the caller adds the `splits` partial planes (fixed order: deterministic)
+//
+// Reference: the modulation / embedder linears' backward is composed from tensor ops
+// (crates/training/src/flux/runtime.rs:401-463 forward; gradients through the autograd tape).
+namespace {
+
+__global__ void rows_wgrad_kernel(const bf16* __restrict__ dy, int ldy, const bf16* __restrict__ x,
+                                  int ldx, bf16* __restrict__ dw, int ldw, int T, int N, int K,
+                                  int accumulate, float scale) {
+  const int kv = blockIdx.x * blockDim.x + threadIdx.x;   // 8 columns per thread
+  if (kv * 8 >= K) return;
+  float xf[kMaxM][8];
+  for (int t = 0; t < kMaxM; ++t) {
+    if (t < T) unpack8(*reinterpret_cast<const bf16x8*>(x + (size_t)t * ldx + kv * 8), xf[t]);
+  }
+  for (int n = blockIdx.y; n < N; n += gridDim.y) {
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    for (int t = 0; t < kMaxM; ++t) {
+      if (t < T) {
+        const float d = __bfloat162float(dy[(size_t)t * ldy + n]) * scale;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[j] = fmaf(d, xf[t][j], acc[j]);
+      }
+    }
+    bf16x8* o = reinterpret_cast<bf16x8*>(dw + (size_t)n * ldw + kv * 8);
+    if (accumulate) {
+      float old[8];
+      unpack8(*o, old);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[j] += old[j];
+    }
+    *o = pack8(acc);
+  }
+}
+
+template <int T>
+__global__ void rows_dgrad_kernel(const bf16* __restrict__ dy, int ldy, const bf16* __restrict__ w,
+                                  int ldw, float* __restrict__ part, int N, int K, int rows_per_split) {
+  const int kv = blockIdx.x * blockDim.x + threadIdx.x;
+  if (kv * 8 >= K) return;
+  const int n0 = blockIdx.y * rows_per_split;
+  const int n1 = min(N, n0 + rows_per_split);
+  float acc[T][8];
+#pragma unroll
+  for (int t = 0; t < T; ++t)
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[t][j] = 0.f;
+#pragma unroll 4
+  for (int n = n0; n < n1; ++n) {
+    float wf[8];
+    unpack8(*reinterpret_cast<const bf16x8*>(w + (size_t)n * ldw + kv * 8), wf);
+#pragma unroll
+    for (int t = 0; t < T; ++t) {
+      const float d = __bfloat162float(dy[(size_t)t * ldy + n]);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[t][j] = fmaf(d, wf[j], acc[t][j]);
+    }
+  }
+#pragma unroll
+  for (int t = 0; t < T; ++t) {
+    float4* o = reinterpret_cast<float4*>(part + ((size_t)blockIdx.y * T + t) * K + kv * 8);
+    o[0] = make_float4(acc[t][0], acc[t][1], acc[t][2], acc[t][3]);
+    o[1] = make_float4(acc[t][4], acc[t][5], acc[t][6], acc[t][7]);
+  }
+}
+
+}  // namespace
+
+// dw[N, K] (row stride ldw) (+)= scale * dy[T, N]^T x[T, K]; T <= 8, K, ldx and ldw multiples of 8.
+extern "C" int eri_rows_wgrad(const void* dy, int ldy, const void* x, int ldx, void* dw, int ldw,
+                              int T, int N, int K, int accumulate, float scale, void* stream) {
+  if (T < 1 || T > kMaxM || K % 8 || ldx % 8 || ldw % 8 || N < 1) return -1;
+  if (((uintptr_t)x | (uintptr_t)dw) & 15) return -1;
+  const int block = 128;
+  dim3 grid((K / 8 + block - 1) / block, N < 65535 ? N : 65535);
+  rows_wgrad_kernel<<<grid, block, 0, (cudaStream_t)stream>>>((const bf16*)dy, ldy, (const bf16*)x, ldx,
+                                                              (bf16*)dw, ldw, T, N, K, accumulate, scale);
+  return (int)cudaGetLastError();
+}
+
+// part[splits, T, K] fp32 = per-split partial sums of dy[T, N] W[N, K]; returns the number of
+// splits (> 0) the caller must add, or a negative error. `max_splits`: planes available in `part`.
+extern "C" int eri_rows_dgrad(const void* dy, int ldy, const void* w, int ldw, float* part, int T,
+                              int N, int K, int max_splits, void* stream) {
+  if (T < 1 || T > kMaxM || K % 8 || ldw % 8 || N < 1 || max_splits < 1) return -1;
+  if (((uintptr_t)w | (uintptr_t)part) & 15) return -1;
+  const int block = 128;
+  const int gx = (K / 8 + block - 1) / block;
+  int splits = (148 * 6 + gx - 1) / gx;            // about six CTAs per SM
+  if (splits > max_splits) splits = max_splits;
+  if (splits > N) splits = N;
+  const int rows = (N + splits - 1) / splits;
+  splits = (N + rows - 1) / rows;
+  dim3 grid(gx, splits);
+  cudaStream_t st = (cudaStream_t)stream;
+#define ERI_DGRAD_CASE(TT)                                                                              \
+  case TT:                                                                                              \
+    rows_dgrad_kernel<TT><<<grid, block, 0, st>>>((const bf16*)dy, ldy, (const bf16*)w, ldw, part, N, K, \
+                                                  rows);                                                \
+    break;
+  switch (T) {
+    ERI_DGRAD_CASE(1) ERI_DGRAD_CASE(2) ERI_DGRAD_CASE(3) ERI_DGRAD_CASE(4)
+    ERI_DGRAD_CASE(5) ERI_DGRAD_CASE(6) ERI_DGRAD_CASE(7) ERI_DGRAD_CASE(8)
+  }
+#undef ERI_DGRAD_CASE
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? splits : -(int)e - 1000;
+}

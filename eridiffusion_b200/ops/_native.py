@@ -116,6 +116,8 @@ _SIGNATURES = {
     "eri_gemm2_bf16": [C.POINTER(GemmArgs), _P],
     "eri_gemm2_check_error": [],
     "eri_gemm2_gather_count": [],
+    "eri_rows_wgrad": [_P, _I, _P, _I, _P, _I, _I, _I, _I, _I, _F, _P],
+    "eri_rows_dgrad": [_P, _I, _P, _I, _P, _I, _I, _I, _I, _P],
     "eri_gemv_bf16": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P],
 }
 

@@ -861,6 +861,44 @@ def linear_glu(x, lin, mode="gelu", act_first=True):
     return glu(lin(x), mode, act_first)
 
 
+def _rows_ok(*ts):
+    return all(t.is_cuda and t.dtype == torch.bfloat16 and t.dim() == 2 and t.stride(1) == 1 and t.stride(0) % 8 == 0
+               and t.data_ptr() % 16 == 0 for t in ts)
+
+
+def small_wgrad(dy2, xin, scale: float = 1.0):
+    """dW[N, K] = scale * dy2[T, N]^T @ xin[T, K] for a handful of rows (T <= 8): one pass that is
+    bound by writing dW (native kernel); other shapes use ``torch``."""
+    T, Nn = dy2.shape
+    K = xin.shape[1]
+    lib = N.lib() if dy2.is_cuda else None
+    if lib is not None and _BACKEND == "fused" and hasattr(lib, "eri_rows_wgrad") and T <= 8 and K % 8 == 0 \
+            and _rows_ok(xin) and dy2.dtype == torch.bfloat16 and dy2.stride(1) == 1:
+        dw = torch.empty(Nn, K, dtype=torch.bfloat16, device=dy2.device)
+        N.check(lib.eri_rows_wgrad(dy2.data_ptr(), dy2.stride(0), xin.data_ptr(), xin.stride(0), dw.data_ptr(), K,
+                                   T, Nn, K, 0, float(scale), N.stream_ptr()), "rows_wgrad")
+        return dw
+    dw = dy2.t() @ xin
+    return dw if scale == 1.0 else dw * scale
+
+
+def small_dgrad(dy2, w):
+    """dx[T, K] = dy2[T, N] @ w[N, K] for T <= 8: one pass over w split across CTAs by rows of w; the
+    fp32 partial planes are added in split order (deterministic)."""
+    T, Nn = dy2.shape
+    K = w.shape[1]
+    lib = N.lib() if dy2.is_cuda else None
+    if lib is not None and _BACKEND == "fused" and hasattr(lib, "eri_rows_dgrad") and T <= 8 and K % 8 == 0 \
+            and _rows_ok(w) and dy2.dtype == torch.bfloat16 and dy2.stride(1) == 1:
+        max_splits = 1024
+        part = torch.empty(max_splits, T, K, dtype=torch.float32, device=dy2.device)
+        n = lib.eri_rows_dgrad(dy2.data_ptr(), dy2.stride(0), w.data_ptr(), w.stride(0), part.data_ptr(), T, Nn, K,
+                               max_splits, N.stream_ptr())
+        N.check(0 if n > 0 else (n or -1), "rows_dgrad")
+        return part[:n].sum(0).to(torch.bfloat16)
+    return dy2 @ w
+
+
 class _SmallLinear(torch.autograd.Function):
     """Conditioning-vector linear (M <= 8 rows): y = f_out(silu_in?(x) W^T + b)."""
 
@@ -885,14 +923,14 @@ class _SmallLinear(torch.autograd.Function):
         xin = torch.nn.functional.silu(x2.float()).to(x2.dtype) if silu_in else x2
         dx = dw = db = None
         if ctx.needs_input_grad[0]:
-            dx = dy2 @ w
+            dx = small_dgrad(dy2, w)
             if silu_in:
                 xf = x2.float()
                 sg = torch.sigmoid(xf)
                 dx = (dx.float() * (sg * (1 + xf * (1 - sg)))).to(x2.dtype)
             dx = dx.view(shp)
         if ctx.needs_input_grad[1]:
-            dw = dy2.t() @ xin
+            dw = small_wgrad(dy2, xin)
         if has_bias and ctx.needs_input_grad[2]:
             db = dy2.sum(0)
         return dx, dw, db, None

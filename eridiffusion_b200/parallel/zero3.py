@@ -47,12 +47,16 @@ class Zero3Context:
         # buffers of the fused weight-gradient reduce-scatter (alternating by layer)
         self.stamps = None
         self.fused_rs = os.environ.get("ERI_B200_ZERO3_FUSED_RS", "1") == "1"
-        self.heap = SymmetricHeap(heap_bytes + max_weight_elems * 2 * (3 if self.fused_rs else 1) + (1 << 20),
+        self.heap = SymmetricHeap(heap_bytes + max_weight_elems * 2 * (3 if self.fused_rs else 1) + (4 << 20),
                                   group=self.pg.group)
         self.comm = Communicator(self.heap, wait_ms)
         dev = torch.device("cuda", torch.cuda.current_device())
         self.landing = [torch.empty(max_weight_elems, dtype=torch.bfloat16, device=dev) for _ in range(2)]
         self.stage = self.heap.tensor((max_weight_elems,), torch.bfloat16)
+        # scratch of the conditioning-vector collectives (modulation linears): 256 K elements each
+        self.native_small = os.environ.get("ERI_B200_ZERO3_MOD", "native") != "nccl"
+        self.small_bf16 = self.heap.tensor((1 << 18,), torch.bfloat16)
+        self.small_f32 = self.heap.tensor((1 << 18,), torch.float32)
         self.recv = [self.heap.tensor((max_weight_elems,), torch.bfloat16) for _ in range(2)] if self.fused_rs else []
         self._recv_flip = 0
         self.n_copy = n_copy
@@ -117,6 +121,22 @@ class Zero3Context:
         return {"all_slabs_landed": (s[1] - t0) / 1e3, "last_compute_cta_done": (s[2] - t0) / 1e3,
                 "producers_that_waited": s[5], "mean_wait_of_those": (s[3] / s[5] / 1e3) if s[5] else 0.0,
                 "longest_wait": s[4] / 1e3}
+
+    def small_collective(self, op: str, src: torch.Tensor, dst: torch.Tensor, count: int) -> bool:
+        """``op`` (all_gather / all_to_all / reduce_scatter) on a conditioning-vector sized bf16 / fp32
+        tensor through the symmetric heap's collective kernel (flag barrier, peer loads, flag barrier:
+        one launch, no NCCL). Returns False when the tensor does not fit the scratch buffer or the
+        native path is switched off (``ERI_B200_ZERO3_MOD=nccl``); the caller then uses NCCL."""
+        if not self.native_small or src.dtype not in (torch.bfloat16, torch.float32):
+            return False
+        buf = self.small_bf16 if src.dtype == torch.bfloat16 else self.small_f32
+        n = src.numel()
+        if n > buf.local.numel() or not dst.is_contiguous() or dst.dtype != src.dtype or \
+                (count * src.element_size()) % 16 or dst.data_ptr() % 16:
+            return False
+        buf.local[:n].copy_(src.reshape(-1))
+        self.comm.collective(op, buf, dst=dst, count=count)
+        return True
 
     def barrier(self):
         """Cross-GPU barrier on the current stream (a kernel; no host synchronisation)."""
@@ -220,7 +240,8 @@ class _Zero3SmallFn(torch.autograd.Function):
         B, K = x.shape
         xs = torch.empty(W * B, K, dtype=x.dtype, device=x.device)
         if W > 1:
-            dist.all_gather_into_tensor(xs, x.contiguous(), group=z3.pg.group)
+            if not z3.small_collective("all_gather", x, xs, B * K):
+                dist.all_gather_into_tensor(xs, x.contiguous(), group=z3.pg.group)
         else:
             xs.copy_(x)
         ys = F.small_linear(xs, shard, bias_shard, silu_in=silu_in) if W * B <= 8 else \
@@ -228,7 +249,8 @@ class _Zero3SmallFn(torch.autograd.Function):
         per = shard.shape[0]
         out = torch.empty(W, B, per, dtype=x.dtype, device=x.device)
         if W > 1:
-            dist.all_to_all_single(out, ys.view(W, B, per).contiguous(), group=z3.pg.group)
+            if not z3.small_collective("all_to_all", ys, out, B * per):
+                dist.all_to_all_single(out, ys.view(W, B, per).contiguous(), group=z3.pg.group)
         else:
             out.copy_(ys.view(W, B, per))
         ctx.save_for_backward(xs, shard)
@@ -244,23 +266,25 @@ class _Zero3SmallFn(torch.autograd.Function):
         dyw = dy.reshape(B, W, per).permute(1, 0, 2).contiguous()
         dys = torch.empty_like(dyw)
         if W > 1:
-            dist.all_to_all_single(dys, dyw, group=z3.pg.group)
+            if not z3.small_collective("all_to_all", dyw, dys, B * per):
+                dist.all_to_all_single(dys, dyw, group=z3.pg.group)
         else:
             dys.copy_(dyw)
         dys = dys.view(W * B, per)
         xin = torch.nn.functional.silu(xs.float()).to(xs.dtype) if silu_in else xs
-        dshard = (dys.t() @ xin) / W if ctx.needs_input_grad[1] else None     # already summed over ranks
+        dshard = F.small_wgrad(dys, xin, 1.0 / W) if ctx.needs_input_grad[1] else None   # already summed over ranks
         dbias = dys.sum(0) / W if (has_bias and ctx.needs_input_grad[2]) else None
         dx = None
         if ctx.needs_input_grad[0]:
-            dxs = dys @ shard
+            dxs = F.small_dgrad(dys, shard)
             if silu_in:
                 xf = xs.float()
                 sg = torch.sigmoid(xf)
                 dxs = (dxs.float() * (sg * (1 + xf * (1 - sg)))).to(xs.dtype)
             dx = torch.empty(B, K, dtype=dxs.dtype, device=dxs.device)
             if W > 1:
-                dist.reduce_scatter_tensor(dx, dxs.contiguous(), group=z3.pg.group)
+                if not z3.small_collective("reduce_scatter", dxs, dx, B * K):
+                    dist.reduce_scatter_tensor(dx, dxs.contiguous(), group=z3.pg.group)
             else:
                 dx.copy_(dxs)
         return dx, dshard, dbias, None, None

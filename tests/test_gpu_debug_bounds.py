@@ -44,13 +44,19 @@ args = dict(out=big)
 import eridiffusion_b200.ops._native as NN
 real = NN.extent_bytes
 NN.extent_bytes = lambda t: real(t) if t is not big else small.numel() * 2
-F.gemm_native(x, w, out=big)                        # ... but computes 512
-NN.extent_bytes = real
+F.gemm_native(x, w, out=big, force_bn=256)          # ... but computes 512 (two-CTA kernel)
 torch.cuda.synchronize()
 rep = N.debug_bounds_report()
 out["violation"] = rep
 out["tail_untouched"] = bool((big[256:] == 7.0).all())
 out["head_written"] = bool((big[:256].float() - ref[:256]).abs().max() < 0.5)
+big[:256] = 7.0
+F.gemm_native(x, w, out=big, force_bn=128)          # the same on the one-CTA kernel
+NN.extent_bytes = real
+torch.cuda.synchronize()
+out["violation1"] = N.debug_bounds_report()
+out["tail_untouched1"] = bool((big[256:] == 7.0).all())
+out["head_written1"] = bool((big[:256].float() - ref[:256]).abs().max() < 0.5)
 # 3. a routing index outside the sequence: skipped and recorded
 bad = idx.clone(); bad[0, 0] = 10_000
 from eridiffusion_b200.ops import functional as FF
@@ -70,4 +76,6 @@ def test_debug_build_runs_clean_and_records_declared_overruns():
     assert res["clean"] == {} and res["err"] == {} and res["gemm_ok"]
     assert list(res["violation"]) == ["gemm2"] and res["violation"]["gemm2"]["code"] == 91 and res["violation"]["gemm2"]["count"] > 0
     assert res["tail_untouched"] and res["head_written"]
+    assert list(res["violation1"]) == ["gemm"] and res["violation1"]["gemm"]["code"] == 81 and res["violation1"]["gemm"]["count"] > 0
+    assert res["tail_untouched1"] and res["head_written1"]
     assert res["route"]["route"]["code"] == 62 and res["route"]["route"]["value"] == 10_000

@@ -300,3 +300,26 @@ def test_adamw8bit_moments_track_fp32_adamw_over_hundreds_of_steps():
     # adds up to half a step), so the 8-bit run's steps are a few per cent shorter than fp32 AdamW's:
     # measured 0.064 relative distance between the two parameter vectors after 300 steps, cosine 0.9985
     assert rel < 0.08 and cos > 0.998, (rel, cos)
+
+
+@pytest.mark.parametrize("T,N,K", [(1, 18432, 3072), (2, 1536, 256), (8, 777, 264), (3, 100000, 64)])
+def test_small_linear_backward_kernels(T, N, K):
+    """Weight and input gradients of the conditioning-vector linears (T <= 8 rows) on their own
+    kernels, against fp32; the linear's autograd path uses them."""
+    dy, x, w = rnd(T, N, scale=0.5), rnd(T, K, seed=1), rnd(N, K, scale=0.05, seed=2)
+    c0 = F.N.launch_count()
+    dw = F.small_wgrad(dy, x, 0.5)
+    dx = F.small_dgrad(dy, w)
+    assert F.N.launch_count() == c0 + 2, "the small-M backward left the native path"
+    close(dw, 0.5 * dy.float().t() @ x.float(), 0.0, 1e-2, rel_to_max=1e-2)
+    close(dx, dy.float() @ w.float(), 0.0, 1e-2, rel_to_max=1e-2)
+    # through autograd (SiLU on the input, bias)
+    xg, wg, b = x.clone().requires_grad_(), w.clone().requires_grad_(), rnd(N, seed=3).requires_grad_()
+    if T * K <= 50000:
+        y = F.small_linear(xg, wg, b, silu_in=True)
+        y.backward(dy)
+        xr, wr, br = (t.detach().float().requires_grad_() for t in (xg, wg, b))
+        torch.nn.functional.linear(torch.nn.functional.silu(xr), wr, br).backward(dy.float())
+        close(xg.grad, xr.grad, 0.0, 2e-2, rel_to_max=1e-2)
+        close(wg.grad, wr.grad, 0.0, 2e-2, rel_to_max=1e-2)
+        close(b.grad, br.grad, 0.0, 2e-2, rel_to_max=1e-2)
