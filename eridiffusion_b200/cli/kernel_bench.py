@@ -1,6 +1,6 @@
 """Per-kernel timing against the library equivalents and the measured roofline.
 
-    python -m eridiffusion_b200.cli.kernel_bench [--what gemm,skinny,attn,elementwise,optim,dequant,narrow,wgrad,small_m] [--small]
+    python -m eridiffusion_b200.cli.kernel_bench [--what gemm,skinny,attn,elementwise,optim,dequant,narrow,wgrad,small_m,gather_emul] [--small]
 
 Timing: CUDA events on the launching stream, >= 3 warm-up launches, L2 flushed between timed
 launches by writing a 256 MB buffer, median of the timed launches. Roofline denominators come from
@@ -96,6 +96,39 @@ def bench_small_m(small):
             t_lib = timeit(lambda: torch.matmul(a, b.t() if not mn else bt, out=out))
             print(f"{M}x{N}x{K} {'B[K,N]' if mn else 'B[N,K]'}: pair {ts[0]*1e6:6.1f} | one-CTA bn128 {ts[1]*1e6:6.1f} | bn64 {ts[2]*1e6:6.1f} | "
                   f"default route {t_auto*1e6:6.1f} us {fl_/t_auto/1e12:5.0f} TF/s | cuBLAS {t_lib*1e6:6.1f} us")
+    assert F.gemm_error_check() == 0
+
+
+def bench_gather_emul(small):
+    """The ZeRO-3 gather-in-GEMM launch with its eight ranks' shards all on THIS GPU (peer pointers are
+    local buffers): what the launch costs apart from NVLink - copy CTAs taking SMs, the extra pass of the
+    gathered operand through HBM, counter waits - against the plain GEMM on an already gathered weight."""
+    from ..parallel.gather_gemm import GatherPlan
+    bw, fl, tag = peaks()
+    W, M = 8, 4608 if not small else 512
+    for n_out, k_in in ([(12288, 3072), (9216, 3072), (3072, 12288)] if not small else [(2048, 512)]):
+        x = torch.randn(M, k_in, device="cuda").bfloat16()
+        shards = [torch.randn(n_out // W, k_in, device="cuda").bfloat16() for _ in range(W)]
+        full = torch.cat(shards, 0)
+        out = torch.empty(M, n_out, device="cuda", dtype=torch.bfloat16)
+        t_plain = timeit(lambda: F.gemm_native(x, full, out=out))
+        row = []
+        for n_copy in (8, 16, 32):
+            landing = torch.empty(n_out, k_in, device="cuda", dtype=torch.bfloat16)
+            plan = GatherPlan.rows(3, W, [s_.data_ptr() for s_ in shards], landing, n_copy=n_copy)
+            stamps = torch.zeros(8, dtype=torch.int64, device="cuda")
+
+            def run():
+                stamps.zero_()
+                stamps[0] = -1
+                F.gemm_native(x, landing, out=out, gather=dict(plan.launch_args(), stamps=stamps))
+            t = timeit(run)
+            s_ = stamps.tolist()
+            row.append(f"{n_copy} copy CTAs {t*1e6:.1f} us (slabs landed at {(s_[1]-s_[0])/1e3:.0f} us, compute done at "
+                       f"{(s_[2]-s_[0])/1e3:.0f} us, {s_[5]} producers waited, longest {s_[4]/1e3:.0f} us)")
+        fl_ = 2.0 * M * n_out * k_in
+        print(f"gather-in-GEMM, 8 emulated ranks on one GPU [{M}x{k_in}] x [{n_out}x{k_in}]^T: plain GEMM {t_plain*1e6:.1f} us "
+              f"({fl_/t_plain/fl:.2f} {tag}) | " + " | ".join(row))
     assert F.gemm_error_check() == 0
 
 
@@ -271,7 +304,7 @@ def main():
     a = ap.parse_args()
     for w in a.what.split(","):
         {"gemm": bench_gemm, "skinny": bench_skinny, "elementwise": bench_elementwise, "optim": bench_optim,
-         "attn": bench_attn, "dequant": bench_dequant, "narrow": bench_narrow, "wgrad": bench_wgrad, "small_m": bench_small_m}[w](a.small)
+         "attn": bench_attn, "dequant": bench_dequant, "narrow": bench_narrow, "wgrad": bench_wgrad, "small_m": bench_small_m, "gather_emul": bench_gather_emul}[w](a.small)
 
 
 if __name__ == "__main__":

@@ -176,7 +176,12 @@ extern "C" int eri_rows_wgrad(const void* dy, int ldy, const void* x, int ldx, v
   if (T < 1 || T > kMaxM || K % 8 || ldx % 8 || ldw % 8 || N < 1) return -1;
   if (((uintptr_t)x | (uintptr_t)dw) & 15) return -1;
   const int block = 128;
-  dim3 grid((K / 8 + block - 1) / block, N < 65535 ? N : 65535);
+  // about sixteen CTAs per SM, each looping over its rows of dW with the x rows held in registers
+  const int gx = (K / 8 + block - 1) / block;
+  int gy = (148 * 16 + gx - 1) / gx;
+  if (gy > N) gy = N;
+  if (gy > 65535) gy = 65535;
+  dim3 grid(gx, gy);
   rows_wgrad_kernel<<<grid, block, 0, (cudaStream_t)stream>>>((const bf16*)dy, ldy, (const bf16*)x, ldx,
                                                               (bf16*)dw, ldw, T, N, K, accumulate, scale);
   return (int)cudaGetLastError();
