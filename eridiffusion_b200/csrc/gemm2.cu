@@ -50,6 +50,7 @@ struct Gemm2Params {
   bf16* pre_out;
   int* err;
   unsigned long long* stamps;   // optional %globaltimer phase record of a gather launch (gemm_args.h)
+  int join_round;               // gather mode: > 0 = copy clusters compute tiles from this round on
   // gather mode (see gather_copy.cuh): the first n_copy CTAs (whole clusters) run copy jobs
   int n_copy, n_jobs;
   const GatherJob* jobs;
@@ -96,6 +97,19 @@ __device__ __forceinline__ void tile_coords(int t, int num_m, int num_n, int rot
     if (n_blk >= num_n) n_blk -= num_n;
   }
 }
+// Tile schedule of a persistent launch. Round r hands one tile to every participating cluster. In
+// gather mode the copy clusters take part from round `join` on (they move slabs first), so rounds
+// below `join` are `cc` tiles wide and later rounds `cc + cx`:
+//   compute cluster i: tile(r) = r * cc + i                               (r <  join)
+//                      tile(r) = join * cc + (r - join) * (cc + cx) + i   (r >= join)
+//   copy cluster j   : starts at r = join with slot cc + j.
+// Without copy clusters (cx = 0) this is the plain stride-cc walk.
+struct TileSched {
+  int cc, cx, join, slot, first_round;
+  __device__ __forceinline__ int tile(int r) const {
+    return r < join ? r * cc + slot : join * cc + (r - join) * (cc + cx) + slot;
+  }
+};
 __device__ __forceinline__ float apply_act(float v, int act) {
   return act == 1 ? gelu_tanh_f(v) : act == 2 ? silu_f(v) : v;
 }
@@ -124,7 +138,16 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
       __syncthreads();
       if (threadIdx.x == 0) atomicMax(p.stamps + 1, (unsigned long long)globaltimer_ns());
     }
-    return;
+    if (p.join_round <= 0) return;
+    // This cluster now joins the tile loop. The copy ring's barriers sit where the GEMM's are set up
+    // below: every copy of the ring has completed (each job ends with a full store drain), so they
+    // are invalidated before the memory becomes the GEMM's barriers.
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      uint64_t* rb = reinterpret_cast<uint64_t*>(smem + (size_t)(RING < 6 ? RING : 6) * kCopyStageBytes);
+      for (int i = 0; i < 2 * (RING < 6 ? RING : 6); ++i) mbar_inval(&rb[i]);
+    }
+    __syncthreads();
   }
   uint64_t* full = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
   uint64_t* empty = full + STAGES;
@@ -163,8 +186,13 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
   const int num_n = p.glu ? (p.glu_hidden + BNH - 1) / BNH : (p.N + BN - 1) / BN;
   const int tiles = num_m * num_n;
   const int k_iters = p.num_k + (p.lora_r > 0 ? 1 : 0);
-  const int cluster_id = ((int)blockIdx.x - p.n_copy) >> 1;
-  const int num_clusters = ((int)gridDim.x - p.n_copy) >> 1;
+  const bool was_copy = (int)blockIdx.x < p.n_copy;
+  TileSched sched;
+  sched.cc = ((int)gridDim.x - p.n_copy) >> 1;
+  sched.cx = p.join_round > 0 ? p.n_copy >> 1 : 0;
+  sched.join = p.join_round > 0 ? p.join_round : 0x3fffffff;
+  sched.slot = was_copy ? sched.cc + ((int)blockIdx.x >> 1) : ((int)blockIdx.x - p.n_copy) >> 1;
+  sched.first_round = was_copy ? sched.join : 0;
 
   if (warp == 0) {
     if (elect_one()) {
@@ -173,7 +201,9 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
       bool ok = true;
       bool dep_done = false;
       unsigned long long waited = 0;   // ns spent on slab counters (recorded only with p.stamps)
-      for (int t = cluster_id; t < tiles && ok; t += num_clusters) {
+      for (int r = sched.first_round; ok; ++r) {
+        const int t = sched.tile(r);
+        if (t >= tiles) break;
         int m_blk, n_blk;
         tile_coords(t, num_m, num_n, p.rot_n, m_blk, n_blk);
         const int m0 = m_blk * 2 * BM + (int)rank * BM;
@@ -270,7 +300,7 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
       int it = 0;
       const uint32_t idesc = umma_idesc_bf16(256, BN, p.a_mn, p.b_mn);
       const uint32_t idesc_lora = umma_idesc_bf16(256, BN, 0, 0);
-      for (int t = cluster_id; t < tiles && ok; t += num_clusters, ++it) {
+      for (int r = sched.first_round; ok && sched.tile(r) < tiles; ++r, ++it) {
         const int buf = it & 1;
         const uint32_t use = (uint32_t)(it >> 1);
         if (!mbar_wait(&acc_empty[buf], (use & 1) ^ 1)) {
@@ -333,7 +363,8 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
   } else {
     const int q = warp & 3;
     int it = 0;
-    for (int t = cluster_id; t < tiles; t += num_clusters, ++it) {
+    for (int r = sched.first_round; sched.tile(r) < tiles; ++r, ++it) {
+      const int t = sched.tile(r);
       int m_blk, n_blk;
       tile_coords(t, num_m, num_n, p.rot_n, m_blk, n_blk);
       const int m0 = m_blk * 2 * BM + (int)rank * BM, n0 = p.glu ? n_blk * BNH : n_blk * BN;
@@ -680,6 +711,7 @@ int eri_gemm2_bf16(const EriGemmArgs2* g, void* stream) {
   p.dbg_out_bytes = g->dbg_out_bytes; p.dbg_out2_bytes = g->dbg_out2_bytes;
   p.dbg_pre_bytes = g->dbg_pre_bytes; p.dbg_res_bytes = g->dbg_res_bytes;
   p.stamps = g->n_copy ? g->stamps : nullptr;
+  p.join_round = g->n_copy ? g->join_round : 0;
   p.n_copy = g->n_copy; p.n_jobs = g->n_jobs; p.jobs = (const GatherJob*)g->jobs;
   p.flags = (unsigned int*)g->flags; p.flag_target = (const unsigned int*)g->flag_target;
   p.b_flag_rows = g->b_flag_rows; p.a_flag_cols = g->a_flag_cols; p.a_flag_rows = g->a_flag_rows;

@@ -73,6 +73,10 @@ struct EriGemmArgs {
   // maximum over the compute CTAs' TMA producers of the time spent waiting for slab counters,
   // [5] number of producers that waited at all. Null: nothing is recorded.
   unsigned long long* stamps;
+  // Gather mode on the two-CTA kernel: > 0 = the copy clusters join the tile loop once their slabs
+  // have landed, taking tiles from this round of the persistent schedule on (the caller estimates how
+  // many rounds the compute clusters finish while the copies run); 0 = they leave after copying.
+  int join_round;
 };
 
 }  // extern "C"

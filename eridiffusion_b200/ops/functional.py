@@ -18,6 +18,7 @@ _GEMM_NATIVE = os.environ.get("ERI_B200_GEMM", "native")  # "native" | "library"
 _ATTN_NATIVE = os.environ.get("ERI_B200_ATTN", "native")  # "native" | "library"
 _GEMM_PAIR = os.environ.get("ERI_B200_GEMM2", "1") == "1"  # two-CTA tiles for large problems
 _PAIR_MIN_TILES = int(os.environ.get("ERI_B200_PAIR_MIN_TILES", "36"))  # at most this many 256 x 256 tiles: one-CTA kernel
+_GATHER_JOIN = os.environ.get("ERI_B200_GATHER_JOIN", "0") == "1"  # copy clusters compute tiles after copying
 _GATHER_PAIR = os.environ.get("ERI_B200_GATHER_PAIR", "1") == "1"  # gather-fused GEMMs on the two-CTA kernel
 _GATHER_LOCAL = os.environ.get("ERI_B200_GATHER_LOCAL", "1") == "1"  # own slab read in place, not copied
 _SCATTER_PAIR = os.environ.get("ERI_B200_SCATTER_PAIR", "1") == "1"  # peer-scatter epilogue on the two-CTA kernel
@@ -415,6 +416,18 @@ def gemm_native(a, b, *, out=None, alpha=1.0, bias=None, lora_h=None, lora_b=Non
         g.a_flag_rows = gather.get("a_flag_rows", 0)
         st = gather.get("stamps")                 # optional uint64[8] phase record (see gemm_args.h)
         g.stamps = st.data_ptr() if st is not None else None
+        # Copy clusters join the tile loop when their slabs have landed. The round from which the tile
+        # schedule counts them in is the number of tiles a compute cluster finishes meanwhile: a copy
+        # CTA moves ~35 GB/s (measured, bulk-copy ring), a K step of a pair tile is ~0.33 us.
+        # Off unless asked for (``join_round`` in the plan's arguments, or ERI_B200_GATHER_JOIN=1): with
+        # eight ranks emulated on one GPU it shortened the compute phase by one round of 13 but not the
+        # launch as a whole.
+        if gather.get("join_round") is not None:
+            g.join_round = int(gather["join_round"])
+        elif _GATHER_JOIN and g.n_copy > 0 and gather.get("copy_bytes"):
+            copy_us = gather["copy_bytes"] / g.n_copy / 35e3
+            tile_us = ((K + 63) // 64) * 0.33 + 2.0
+            g.join_round = max(1, int(math.ceil(copy_us / tile_us)))
         loc = gather.get("local") if _GATHER_LOCAL else None
         if loc is not None:
             g.b_local, g.ldb_local = loc["ptr"], loc["ld"]

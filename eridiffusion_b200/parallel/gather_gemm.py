@@ -78,22 +78,27 @@ class GatherPlan:
                 flag_rows = per
         pl = cls(rank, world, n_copy, landing.device, n_flags=Nn // flag_rows)
         rb = K * landing.element_size()
-        # interleave peers so that every slab makes progress; own slab first
+        # Slab after slab in ring order from this rank's own: the GEMM walks its tiles (or its K ranges)
+        # in the same order, so the copy CTAs fill the slab that is needed next instead of all slabs a
+        # little. (Interleaving the peers row group by row group made the LAST rows of the next slab land
+        # at the very end of the gather: every producer then waited ~70 % of the copy time in total.)
         order = [(rank + i) % world for i in range(world)]
-        r0 = 0
-        while r0 < per:
-            nr = min(rows_per_job, per - r0)
-            for p in order:
+        for p in order:
+            r0 = 0
+            while r0 < per:
+                nr = min(rows_per_job, per - r0)
                 pl._add(shard_ptrs[p] + r0 * rb, landing.data_ptr() + (p * per + r0) * landing.stride(0) * landing.element_size(),
                         nr, rb, rb, landing.stride(0) * landing.element_size(), (p * per + r0) // flag_rows, remote=p != rank)
-            r0 += nr
-        # The rotation only says where the tile / K order starts (at this rank's own slab); it is
-        # rounded down to whole 256-column pair tiles / 64-wide K blocks so that the two-CTA kernel
-        # accepts the plan on every rank, whatever the slab size.
+                r0 += nr
+        # The rotation only says where the tile / K order starts; it is a whole number of 256-column
+        # pair tiles / 64-wide K blocks so that the two-CTA kernel accepts the plan on every rank,
+        # whatever the slab size. It is rounded UP into this rank's own slab: rounded down, the first
+        # tile would begin in the previous rank's slab, which is the LAST one the copy CTAs fill, and
+        # every producer would sit out the whole gather before its first load.
         if along_k:
-            pl.kw = dict(a_flag_cols=flag_rows, rot_k_cols=(rank * per) // 64 * 64)
+            pl.kw = dict(a_flag_cols=flag_rows, rot_k_cols=(-(-(rank * per) // 64) * 64) % Nn)
         else:
-            pl.kw = dict(b_flag_rows=flag_rows, rot_n_rows=(rank * per) // 256 * 256)
+            pl.kw = dict(b_flag_rows=flag_rows, rot_n_rows=(-(-(rank * per) // 256) * 256) % Nn)
         # whole slabs in the same order, for the copy-engine variant of the gather
         sb = per * rb
         pl.slabs = [(shard_ptrs[p], landing.data_ptr() + p * per * landing.stride(0) * landing.element_size(), sb,
@@ -147,7 +152,8 @@ class GatherPlan:
         ``ops.functional.gemm_native``."""
         self.flags.zero_()
         d = dict(n_copy=self.n_copy, n_jobs=len(self.jobs), jobs=self._dev_jobs.data_ptr(),
-                 flags=self.flags.data_ptr(), flag_target=self._targets_dev.data_ptr(), **self.kw)
+                 flags=self.flags.data_ptr(), flag_target=self._targets_dev.data_ptr(),
+                 copy_bytes=self.remote_bytes, **self.kw)
         if self.local is not None:
             d["local"] = dict(self.local, n_jobs=len(self.jobs_nl), jobs=self._dev_jobs_nl.data_ptr(),
                               flag_target=self._targets_nl_dev.data_ptr())

@@ -158,11 +158,11 @@ class _UlyssesQKV(torch.autograd.Function):
         if la is not None:
             ts = F.gemm_native(dY, _t(lb), alpha=ctx.ls, gather=pl.launch_args())   # lands dY
             dx = F.gemm_native(dY, w, b_mn=True, lora_h=ts, lora_b=_t(la))
-            da = ts.t() @ x2 if ctx.needs_input_grad[3] else None
-            db_ = dY.t() @ h if ctx.needs_input_grad[4] else None
+            da = F.lora_wgrad(x2, ts, transpose_out=True) if ctx.needs_input_grad[3] else None
+            db_ = F.lora_wgrad(dY, h) if ctx.needs_input_grad[4] else None
         else:
             dx = F.gemm_native(dY, w, b_mn=True, gather=pl.launch_args())           # lands dY
-        dw = (dY.t() @ x2) if ctx.needs_input_grad[1] else None
+        dw = F.wgrad(dY, x2) if ctx.needs_input_grad[1] else None
         db = dY.sum(0) if (ctx.has_bias and ctx.needs_input_grad[2]) else None
         return dx.view(B, Ll, D), dw, db, da, db_, None, None, None
 
@@ -223,10 +223,10 @@ class _UlyssesOutProj(torch.autograd.Function):
                       lora_b=_t(la) if la is not None else None, scatter=u.scatter_args(u.d_attn_out))
         u.barrier()
         d_attn = u.d_attn_out.local.view(B, u.Lt, u.G).clone()
-        dw = (dy2.t() @ A) if ctx.needs_input_grad[1] else None
+        dw = F.wgrad(dy2, A) if ctx.needs_input_grad[1] else None
         db = dy2.sum(0) if (ctx.has_bias and ctx.needs_input_grad[2]) else None
-        da = ts.t() @ A if (la is not None and ctx.needs_input_grad[3]) else None
-        db_ = dy2.t() @ h if (la is not None and ctx.needs_input_grad[4]) else None
+        da = F.lora_wgrad(A, ts, transpose_out=True) if (la is not None and ctx.needs_input_grad[3]) else None
+        db_ = F.lora_wgrad(dy2, h) if (la is not None and ctx.needs_input_grad[4]) else None
         return d_attn, dw, db, da, db_, None, None, d_res, None, None
 
 

@@ -51,7 +51,12 @@ def test_rows_plan_rotation_is_a_whole_pair_tile_on_every_rank():
         for rank in range(W):
             pl = GatherPlan.rows(rank, W, _ptrs(W, per * K * 2), landing, n_copy=16)
             assert pl.kw["b_flag_rows"] == 128 and pl.kw["rot_n_rows"] % 256 == 0
-            assert pl.kw["rot_n_rows"] <= rank * per < pl.kw["rot_n_rows"] + 256
+            # the tile order starts INSIDE this rank's own slab (rounded up to the next pair tile), never
+            # in the previous rank's slab, which the copy CTAs fill last
+            assert rank * per <= pl.kw["rot_n_rows"] < rank * per + 256 and pl.kw["rot_n_rows"] < (rank + 1) * per
+            # copy jobs: slab after slab in ring order from the own slab
+            owners = [j.flag * 128 // per for j in pl.jobs]
+            assert owners == sorted(owners, key=lambda p: (p - rank) % W)
             assert pl.local["lo"] % 128 == 0 and pl.local["hi"] % 128 == 0
             # every counter is bumped by exactly the jobs that cover its rows
             rows_per_flag = [0] * len(pl.flags)

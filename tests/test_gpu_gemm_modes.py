@@ -45,6 +45,22 @@ def test_gather_rows_forward(rank):
     close(out, x.float() @ w.float().t(), 0.05)
 
 
+@pytest.mark.parametrize("join_round", [1, 2, 50])
+def test_gather_copy_clusters_join_the_tile_loop(join_round):
+    """Copy clusters that take tiles once their slabs have landed (from a given round of the persistent
+    schedule on; a round beyond the last leaves them idle): same result, every tile computed once."""
+    W, rank, M, N, K = 4, 1, 4096, 8192, 256          # 512 pair tiles: several rounds on 74 clusters
+    x = rnd(M, K)
+    shards = [rnd(N // W, K, seed=10 + p, scale=K ** -0.5) for p in range(W)]
+    landing = torch.full((N, K), float("nan"), device=DEV, dtype=torch.bfloat16)
+    plan = GatherPlan.rows(rank, W, [s.data_ptr() for s in shards], landing, n_copy=8)
+    out = torch.full((M, N), float("nan"), device=DEV, dtype=torch.bfloat16)
+    c0 = F.N.require().eri_gemm2_gather_count()
+    F.gemm_native(x, landing, out=out, gather=dict(plan.launch_args(), join_round=join_round))
+    assert F.gemm_error_check() == 0 and F.N.require().eri_gemm2_gather_count() == c0 + 1
+    close(out, x.float() @ torch.cat(shards, 0).float().t(), 0.05)
+
+
 @pytest.mark.parametrize("rank", [1, 3])
 def test_gather_rows_along_k_for_input_grad(rank):
     W, M, N, K = 4, 384, 1024, 512          # dX[M, K] = dY[M, N] @ W[N, K]
