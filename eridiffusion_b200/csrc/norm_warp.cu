@@ -51,20 +51,26 @@ __device__ __forceinline__ bf16x8 pack8_f2(const f32x2 (&p)[4]) {
   return o;
 }
 
-constexpr int kBarBytes = 1024;  // room for 32 warps x 2 stages of mbarriers
+constexpr int kBarBytes = 1024;  // room for 32 warps x 3 stages of mbarriers
+template <bool BWD>
+constexpr int kRingStages = BWD ? 2 : 3;
 
 template <int VPL, bool BWD>
 __global__ void __launch_bounds__(BWD ? 256 : 384, 1) norm_rows_kernel(const NormArgs a) {
   extern __shared__ __align__(128) uint8_t smem[];
   constexpr int NT = BWD ? 2 : 1;
+  // Ring depth per warp: the forward has one row per stage and room for three (at 4608 rows a warp
+  // owns two or three rows, so all of them are in flight from the start and the launch pays the DRAM
+  // latency once); the backward's stages hold two rows and stay at two.
+  constexpr int NS = kRingStages<BWD>;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
   const int D = a.D, nvec = D >> 3;
   const uint32_t row_bytes = (uint32_t)D * 2u;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem) + warp * 2;
-  uint8_t* ring = smem + kBarBytes + (size_t)warp * 2 * NT * row_bytes;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem) + warp * NS;
+  uint8_t* ring = smem + kBarBytes + (size_t)warp * NS * NT * row_bytes;
   if (lane == 0) {
-    mbar_init(&bars[0], 1);
-    mbar_init(&bars[1], 1);
+#pragma unroll
+    for (int s = 0; s < NS; ++s) mbar_init(&bars[s], 1);
     mbar_fence_init();
   }
   __syncwarp();
@@ -78,16 +84,17 @@ __global__ void __launch_bounds__(BWD ? 256 : 384, 1) norm_rows_kernel(const Nor
                &bars[st]);
   };
   if (lane == 0) {
-    if (row0 < a.rows) issue(row0, 0);
-    if (row0 + stride < a.rows) issue(row0 + stride, 1);
+#pragma unroll
+    for (int s = 0; s < NS; ++s)
+      if (row0 + s * stride < a.rows) issue(row0 + s * stride, s);
   }
   const bf16x8* wv = a.weight ? reinterpret_cast<const bf16x8*>(a.weight) : nullptr;
   const bf16x8* bv = a.bias ? reinterpret_cast<const bf16x8*>(a.bias) : nullptr;
   const float inv_d = 1.f / (float)D;
   int it = 0;
   for (int row = row0; row < a.rows; row += stride, ++it) {
-    const int st = it & 1;
-    if (!mbar_wait(&bars[st], (uint32_t)((it >> 1) & 1))) {
+    const int st = it % NS;
+    if (!mbar_wait(&bars[st], (uint32_t)((it / NS) & 1))) {
       if (lane == 0) atomicExch(a.err, 1);
       break;
     }
@@ -105,9 +112,9 @@ __global__ void __launch_bounds__(BWD ? 256 : 384, 1) norm_rows_kernel(const Nor
       }
     }
     __syncwarp();
-    if (lane == 0 && row + 2 * stride < a.rows) {
+    if (lane == 0 && row + NS * stride < a.rows) {
       fence_proxy_async_smem();  // the warp's reads of this stage precede the copy engine's writes
-      issue(row + 2 * stride, st);
+      issue(row + NS * stride, st);
     }
     const int b = row / a.rows_per_batch;
     const bf16x8* sc =
@@ -240,8 +247,8 @@ template <bool BWD>
 int launch_rows(const NormArgs& a, cudaStream_t st) {
   constexpr int NT = BWD ? 2 : 1;
   const int D = a.D;
-  const int per_warp = 2 * NT * D * 2;
-  int warps = (200 * 1024 - kBarBytes) / per_warp;
+  const int per_warp = kRingStages<BWD> * NT * D * 2;
+  int warps = (220 * 1024 - kBarBytes) / per_warp;
   if (warps > (BWD ? 8 : 12)) warps = BWD ? 8 : 12;
   if (warps < 1) return -100;
   const int smem = kBarBytes + warps * per_warp;
@@ -253,7 +260,7 @@ int launch_rows(const NormArgs& a, cudaStream_t st) {
     static bool configured = false;                                                             \
     if (!configured) {                                                                          \
       if (cudaFuncSetAttribute(norm_rows_kernel<V, BWD>,                                        \
-                               cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) !=      \
+                               cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024) !=      \
           cudaSuccess)                                                                          \
         return -101;                                                                            \
       configured = true;                                                                        \

@@ -87,8 +87,13 @@ class Zero3Context:
         key = (shard.data_ptr(), n, k, along_k, li)
         pl = self._plans.get(key)
         if pl is None:
+            # A weight with few output tiles (N <= 4096: at most 16 column tiles) is needed almost
+            # whole by the first wave of tiles, so the gather has to finish early: twice the copy CTAs
+            # (emulated 8-rank launch of [4608 x 12288] x [3072 x 12288]^T: compute done at 317 us
+            # against 360 us).
+            n_copy = self.n_copy * 2 if (not along_k and n <= 4096 and self.n_copy <= 16) else self.n_copy
             pl = GatherPlan.rows(self.rank, self.world, self.peer_ptrs_of(shard), landing,
-                                 along_k=along_k, n_copy=self.n_copy)
+                                 along_k=along_k, n_copy=n_copy)
             self._plans[key] = pl
         self.gathered_bytes += pl.bytes_from_peers()
         return pl, landing
