@@ -130,6 +130,23 @@ def bench_gather_emul(small):
         fl_ = 2.0 * M * n_out * k_in
         print(f"gather-in-GEMM, 8 emulated ranks on one GPU [{M}x{k_in}] x [{n_out}x{k_in}]^T: plain GEMM {t_plain*1e6:.1f} us "
               f"({fl_/t_plain/fl:.2f} {tag}) | " + " | ".join(row))
+        # input gradient dX[M, k_in] = dY[M, n_out] W[n_out, k_in]: the gathered rows are the reduction dimension
+        dy = torch.randn(M, n_out, device="cuda").bfloat16()
+        dx = torch.empty(M, k_in, device="cuda", dtype=torch.bfloat16)
+        t_plain = timeit(lambda: F.gemm_native(dy, full, out=dx, b_mn=True))
+        row = []
+        for n_copy in (16, 32):
+            landing = torch.empty(n_out, k_in, device="cuda", dtype=torch.bfloat16)
+            plan = GatherPlan.rows(3, W, [s_.data_ptr() for s_ in shards], landing, along_k=True, n_copy=n_copy)
+            t = timeit(lambda: F.gemm_native(dy, landing, out=dx, b_mn=True, gather=plan.launch_args()))
+            stamps = torch.zeros(8, dtype=torch.int64, device="cuda")
+            stamps[0] = -1
+            F.gemm_native(dy, landing, out=dx, b_mn=True, gather=dict(plan.launch_args(), stamps=stamps))
+            torch.cuda.synchronize()
+            s_ = stamps.tolist()
+            row.append(f"{n_copy} copy CTAs {t*1e6:.1f} us (landed at {(s_[1]-s_[0])/1e3:.0f} us, compute done at "
+                       f"{(s_[2]-s_[0])/1e3:.0f} us, longest wait {s_[4]/1e3:.0f} us)")
+        print(f"   input gradient [{M}x{n_out}] x [{n_out}x{k_in}]: plain GEMM {t_plain*1e6:.1f} us | " + " | ".join(row))
     assert F.gemm_error_check() == 0
 
 

@@ -330,7 +330,7 @@ __global__ void qknorm_rope_fwd_kernel(const bf16* __restrict__ qkv, const bf16*
   }
 }
 
-template <int EPL>
+template <int EPL, bool SGRAD>
 __global__ void qknorm_rope_bwd_kernel(const bf16* __restrict__ dq, const bf16* __restrict__ dk,
                                        const bf16* __restrict__ dv, const bf16* __restrict__ qkv,
                                        const bf16* __restrict__ qs, const bf16* __restrict__ ks,
@@ -347,10 +347,14 @@ __global__ void qknorm_rope_bwd_kernel(const bf16* __restrict__ dq, const bf16* 
   // Scale gradients: every warp keeps its share in registers over its (batch, token, head) items;
   // the CTA adds its warps in shared memory and issues one global atomic per element. (One atomic
   // per element per item put 100 k warps on the same 128 addresses: 1.2 ms per call.)
-  float acc_s[2][EPL];
+  // SGRAD = false (frozen scales: LoRA training) keeps the accumulators out of the register budget
+  float acc_s[2][SGRAD ? EPL : 1];
+  if constexpr (SGRAD) {
 #pragma unroll
-  for (int j = 0; j < EPL; ++j) acc_s[0][j] = acc_s[1][j] = 0.f;
-  for (int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5; warp < total; warp += nwarps_grid) {
+    for (int j = 0; j < EPL; ++j) acc_s[0][j] = acc_s[1][j] = 0.f;
+  }
+  for (int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5; warp < total;
+       warp += SGRAD ? nwarps_grid : total) {   // frozen scales: one item per warp, as many warps as items
   const int h = warp % H;
   const int l = (warp / H) % L;
   const int b = warp / (H * L);
@@ -400,7 +404,9 @@ __global__ void qknorm_rope_bwd_kernel(const bf16* __restrict__ dq, const bf16* 
         for (int j = 0; j < EPL; ++j) {
           xh[j] = x[j] * r;
           float sj = __bfloat162float(sp[lane * EPL + j]);
-          if (dsp) acc_s[part][j] += g[j] * xh[j];
+          if constexpr (SGRAD) {
+            if (dsp) acc_s[part][j] += g[j] * xh[j];
+          }
           g[j] *= sj;
           c2 += g[j] * xh[j];
         }
@@ -414,7 +420,7 @@ __global__ void qknorm_rope_bwd_kernel(const bf16* __restrict__ dq, const bf16* 
       *reinterpret_cast<__nv_bfloat162*>(dst + j) = __floats2bfloat162_rn(g[j], g[j + 1]);
   }
   }
-  if (dqs || dks) {
+  if constexpr (SGRAD) {
     __shared__ float red[2][Dh];
     for (int i = threadIdx.x; i < 2 * Dh; i += blockDim.x) (&red[0][0])[i] = 0.f;
     __syncthreads();
@@ -780,18 +786,20 @@ int eri_qknorm_rope_bwd(const void* dq, const void* dk, const void* dv, const vo
   int grid = (total * 32 + block - 1) / block;
   // with scale gradients the grid is capped (a CTA then loops over its items and reduces once)
   if ((dqs || dks) && grid > 148 * 8) grid = 148 * 8;
-  if (Dh == 128)
-    qknorm_rope_bwd_kernel<4><<<grid, block, 0, (cudaStream_t)stream>>>(
-        (const bf16*)dq, (const bf16*)dk, (const bf16*)dv, (const bf16*)qkv, (const bf16*)qs,
-        (const bf16*)ks, cosT, sinT, (bf16*)dqkv, dqs, dks, B, L, H, Ltot, l_off, eps,
-        in_tok_stride, in_part_stride, grad_tok_stride);
-  else if (Dh == 64)
-    qknorm_rope_bwd_kernel<2><<<grid, block, 0, (cudaStream_t)stream>>>(
-        (const bf16*)dq, (const bf16*)dk, (const bf16*)dv, (const bf16*)qkv, (const bf16*)qs,
-        (const bf16*)ks, cosT, sinT, (bf16*)dqkv, dqs, dks, B, L, H, Ltot, l_off, eps,
-        in_tok_stride, in_part_stride, grad_tok_stride);
-  else
+#define ERI_QKN_BWD(E, SG)                                                                       \
+  qknorm_rope_bwd_kernel<E, SG><<<grid, block, 0, (cudaStream_t)stream>>>(                       \
+      (const bf16*)dq, (const bf16*)dk, (const bf16*)dv, (const bf16*)qkv, (const bf16*)qs,      \
+      (const bf16*)ks, cosT, sinT, (bf16*)dqkv, dqs, dks, B, L, H, Ltot, l_off, eps,             \
+      in_tok_stride, in_part_stride, grad_tok_stride)
+  const bool sg = dqs || dks;
+  if (Dh == 128) {
+    if (sg) ERI_QKN_BWD(4, true); else ERI_QKN_BWD(4, false);
+  } else if (Dh == 64) {
+    if (sg) ERI_QKN_BWD(2, true); else ERI_QKN_BWD(2, false);
+  } else {
     return -1;
+  }
+#undef ERI_QKN_BWD
   ERI_LAUNCH_CHECK();
 }
 

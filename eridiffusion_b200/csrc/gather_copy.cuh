@@ -3,7 +3,7 @@
 // A gather-fused launch reserves its first n_copy CTAs for copy jobs: each job moves a slab (rows of
 // row_bytes, source possibly on a peer GPU) into a local landing buffer and bumps the slab's
 // counter; the TMA producers of the compute CTAs wait (bounded) on the counters of the slabs they
-// are about to load. The parameter type P provides n_copy, n_jobs, jobs, flags, flag_target, err.
+// are about to load. The parameter type P provides n_copy, n_jobs, jobs, flags, flag_target, all_flag, err.
 #pragma once
 #include "ptx.cuh"
 
@@ -186,6 +186,7 @@ __device__ void copy_role(const P& p, uint8_t* smem, int ring_stages, int cta) {
         __threadfence();
         fence_proxy_async_all();
         atomicAdd(p.flags + job.flag, 1u);
+        if (p.all_flag) atomicAdd(p.flags + (p.all_flag - 1), 1u);
       }
     }
   }

@@ -59,6 +59,7 @@ struct GemmParams {
   bf16* pre_out;        // indexed with (col - n_split)
   int* err;
   // gather mode
+  int all_flag;               // 1 + index of the counter every copy job bumps (0: none)
   int n_copy;                 // leading CTAs that run copy jobs
   int n_jobs;
   const GatherJob* jobs;
@@ -553,6 +554,7 @@ int eri_gemm_bf16(const EriGemmArgs* g, void* stream) {
   p.err = g_err_flag;
   p.dbg_out_bytes = g->dbg_out_bytes; p.dbg_out2_bytes = g->dbg_out2_bytes;
   p.dbg_pre_bytes = g->dbg_pre_bytes; p.dbg_res_bytes = g->dbg_res_bytes;
+  p.all_flag = g->n_copy ? g->all_flag : 0;
   p.n_copy = g->n_copy; p.n_jobs = g->n_jobs; p.jobs = (const GatherJob*)g->jobs;
   p.flags = (unsigned int*)g->flags; p.flag_target = (const unsigned int*)g->flag_target;
   p.b_flag_rows = g->b_flag_rows; p.a_flag_cols = g->a_flag_cols;

@@ -51,6 +51,7 @@ struct Gemm2Params {
   int* err;
   unsigned long long* stamps;   // optional %globaltimer phase record of a gather launch (gemm_args.h)
   int join_round;               // gather mode: > 0 = copy clusters compute tiles from this round on
+  int all_flag;                 // gather mode: 1 + index of the counter every copy job bumps (0: none)
   // gather mode (see gather_copy.cuh): the first n_copy CTAs (whole clusters) run copy jobs
   int n_copy, n_jobs;
   const GatherJob* jobs;
@@ -201,6 +202,7 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
       bool ok = true;
       bool dep_done = false;
       unsigned long long waited = 0;   // ns spent on slab counters (recorded only with p.stamps)
+      bool all_landed = false;         // sticky: the gather has finished, no slab counter needs a look
       for (int r = sched.first_round; ok; ++r) {
         const int t = sched.tile(r);
         if (t >= tiles) break;
@@ -209,7 +211,11 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
         const int m0 = m_blk * 2 * BM + (int)rank * BM;
         const int n0 = p.glu ? n_blk * BNH + (int)rank * p.glu_hidden : n_blk * BN + (int)rank * BNH;
         const bool b_rows_local = p.loc_mode == 1 && n0 >= p.loc_lo && n0 + BNH <= p.loc_hi;
-        if (p.b_flag_rows && !b_rows_local) {
+        if (p.all_flag && !all_landed) {
+          all_landed = ld_acquire_gpu(p.flags + (p.all_flag - 1)) >= p.flag_target[p.all_flag - 1];
+          if (all_landed) fence_proxy_async_all();
+        }
+        if (p.b_flag_rows && !b_rows_local && !all_landed) {
           // every slab that the B rows staged by THIS CTA touch must have landed
           const int f0 = n0 / p.b_flag_rows, f1 = (min(n0 + BNH, p.N) - 1) / p.b_flag_rows;
           const unsigned long long tw = p.stamps ? globaltimer_ns() : 0ull;
@@ -236,7 +242,7 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
             int kk = k + p.rot_k;
             if (kk >= p.num_k) kk -= p.num_k;
             const bool k_local = p.loc_mode >= 2 && kk * BK >= p.loc_lo && kk * BK + BK <= p.loc_hi;
-            if (p.a_flag_cols && !k_local) {
+            if (p.a_flag_cols && !k_local && !all_landed) {
               int f = (kk * BK) / p.a_flag_cols;
               if (p.a_flag_rows) f = f * p.a_row_groups + min(m0, p.M - 1) / p.a_flag_rows;
               if (f != a_ready) {
@@ -712,6 +718,7 @@ int eri_gemm2_bf16(const EriGemmArgs2* g, void* stream) {
   p.dbg_pre_bytes = g->dbg_pre_bytes; p.dbg_res_bytes = g->dbg_res_bytes;
   p.stamps = g->n_copy ? g->stamps : nullptr;
   p.join_round = g->n_copy ? g->join_round : 0;
+  p.all_flag = g->n_copy ? g->all_flag : 0;
   p.n_copy = g->n_copy; p.n_jobs = g->n_jobs; p.jobs = (const GatherJob*)g->jobs;
   p.flags = (unsigned int*)g->flags; p.flag_target = (const unsigned int*)g->flag_target;
   p.b_flag_rows = g->b_flag_rows; p.a_flag_cols = g->a_flag_cols; p.a_flag_rows = g->a_flag_rows;

@@ -77,6 +77,10 @@ struct EriGemmArgs {
   // have landed, taking tiles from this round of the persistent schedule on (the caller estimates how
   // many rounds the compute clusters finish while the copies run); 0 = they leave after copying.
   int join_round;
+  // Gather mode: 1 + index of a counter in `flags` that every finished copy job bumps (its target in
+  // `flag_target` is the number of jobs); 0 = none. A producer that finds it at its target stops
+  // checking slab counters: after the gather has finished, a tile costs one counter load.
+  int all_flag;
 };
 
 }  // extern "C"

@@ -15,7 +15,7 @@ using namespace eri;
 namespace {
 
 struct ProbeParams {
-  int n_copy, n_jobs;
+  int n_copy, n_jobs, all_flag;
   const GatherJob* jobs;
   unsigned int* flags;
   const unsigned int* flag_target;
@@ -72,7 +72,7 @@ int eri_link_probe(int mode, const void* src, void* dst, long long bytes, int n_
       configured = 6 * kCopyStageBytes + 1280;
     }
     ProbeParams p;
-    p.n_copy = n_ctas; p.n_jobs = n_jobs; p.jobs = (const GatherJob*)jobs;
+    p.n_copy = n_ctas; p.n_jobs = n_jobs; p.all_flag = 0; p.jobs = (const GatherJob*)jobs;
     p.flags = (unsigned int*)flags; p.flag_target = (const unsigned int*)flag_target; p.err = g_probe_err;
     probe_bulk_kernel<<<n_ctas, 192, SMEM, st>>>(p, ring);
     return (int)cudaGetLastError();

@@ -52,16 +52,15 @@ __device__ __forceinline__ bf16x8 pack8_f2(const f32x2 (&p)[4]) {
 }
 
 constexpr int kBarBytes = 1024;  // room for 32 warps x 3 stages of mbarriers
+// Ring depth per warp. Three stages for the forward (all rows of a warp in flight at 4608 rows) were
+// measured slower in the training step (25.2 against 22.1 us per launch): two it is.
 template <bool BWD>
-constexpr int kRingStages = BWD ? 2 : 3;
+constexpr int kRingStages = 2;
 
 template <int VPL, bool BWD>
 __global__ void __launch_bounds__(BWD ? 256 : 384, 1) norm_rows_kernel(const NormArgs a) {
   extern __shared__ __align__(128) uint8_t smem[];
   constexpr int NT = BWD ? 2 : 1;
-  // Ring depth per warp: the forward has one row per stage and room for three (at 4608 rows a warp
-  // owns two or three rows, so all of them are in flight from the start and the launch pays the DRAM
-  // latency once); the backward's stages hold two rows and stay at two.
   constexpr int NS = kRingStages<BWD>;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
   const int D = a.D, nvec = D >> 3;
@@ -248,7 +247,7 @@ int launch_rows(const NormArgs& a, cudaStream_t st) {
   constexpr int NT = BWD ? 2 : 1;
   const int D = a.D;
   const int per_warp = kRingStages<BWD> * NT * D * 2;
-  int warps = (220 * 1024 - kBarBytes) / per_warp;
+  int warps = (200 * 1024 - kBarBytes) / per_warp;
   if (warps > (BWD ? 8 : 12)) warps = BWD ? 8 : 12;
   if (warps < 1) return -100;
   const int smem = kBarBytes + warps * per_warp;
@@ -260,7 +259,7 @@ int launch_rows(const NormArgs& a, cudaStream_t st) {
     static bool configured = false;                                                             \
     if (!configured) {                                                                          \
       if (cudaFuncSetAttribute(norm_rows_kernel<V, BWD>,                                        \
-                               cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024) !=      \
+                               cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) !=      \
           cudaSuccess)                                                                          \
         return -101;                                                                            \
       configured = true;                                                                        \

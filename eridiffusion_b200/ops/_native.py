@@ -53,7 +53,7 @@ class GemmArgs(C.Structure):
         ("jobs_nl", C.c_void_p), ("flag_target_nl", C.c_void_p),
         ("a_mn", C.c_int), ("glu", C.c_int),
         ("dbg_out_bytes", C.c_longlong), ("dbg_out2_bytes", C.c_longlong), ("dbg_pre_bytes", C.c_longlong),
-        ("dbg_res_bytes", C.c_longlong), ("scatter_mode", C.c_int), ("stamps", C.c_void_p), ("join_round", C.c_int),
+        ("dbg_res_bytes", C.c_longlong), ("scatter_mode", C.c_int), ("stamps", C.c_void_p), ("join_round", C.c_int), ("all_flag", C.c_int),
     ]
 
 

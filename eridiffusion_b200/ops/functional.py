@@ -414,6 +414,7 @@ def gemm_native(a, b, *, out=None, alpha=1.0, bias=None, lora_h=None, lora_b=Non
         g.b_flag_rows, g.a_flag_cols = gather.get("b_flag_rows", 0), gather.get("a_flag_cols", 0)
         g.rot_n_rows, g.rot_k_cols = gather.get("rot_n_rows", 0), gather.get("rot_k_cols", 0)
         g.a_flag_rows = gather.get("a_flag_rows", 0)
+        g.all_flag = int(gather.get("all_flag", 0))
         st = gather.get("stamps")                 # optional uint64[8] phase record (see gemm_args.h)
         g.stamps = st.data_ptr() if st is not None else None
         # Copy clusters join the tile loop when their slabs have landed. The round from which the tile

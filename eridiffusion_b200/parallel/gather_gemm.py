@@ -31,6 +31,10 @@ class GatherPlan:
         self.jobs = []
         self.jobs_nl = []                 # the same jobs without this rank's own slab
         n_flags = n_flags or world
+        self.n_slab_flags = n_flags
+        # one more counter after the slab counters: every finished job bumps it, so a producer reads
+        # "everything has landed" with one load per tile and then skips the per-slab checks
+        n_flags += 1
         self.targets = [0] * n_flags
         self.targets_nl = [0] * n_flags
         self.local = None                 # dict(ptr, ld, mode, lo, hi): own slab readable in place
@@ -51,9 +55,11 @@ class GatherPlan:
         j.src_stride, j.dst_stride, j.flag = src_stride, dst_stride, flag
         self.jobs.append(j)
         self.targets[flag] += 1
+        self.targets[-1] += 1
         if remote:
             self.jobs_nl.append(j)
             self.targets_nl[flag] += 1
+            self.targets_nl[-1] += 1
 
     @classmethod
     def rows(cls, rank, world, shard_ptrs, landing: torch.Tensor, along_k=False, n_copy=16,
@@ -64,10 +70,15 @@ class GatherPlan:
         Nn, K = landing.shape
         assert Nn % world == 0
         per = Nn // world
+        # (For dX = dY W, where every output tile needs every slab, moving W by 256-wide column blocks in
+        # tile order was tried: the 512-byte row pieces copy at a third of the rate of whole slabs, and
+        # the emulated 8-rank launch took 511 us against ~360 us. Whole slabs in ring order it is.)
         # A slab that is not a multiple of 256 rows (9216 / 8 = 1152, 3072 / 8 = 384) keeps counters
         # INSIDE the slab at the largest granule that divides it; one counter per whole slab would
         # hold every tile of a slab back until its last byte has landed.
-        for cand in (flag_rows, 128, 64):
+        # Along K (dX = dY W) every tile walks all slabs, and each new counter costs its producer a
+        # global load in the middle of the K loop: one counter per whole slab there.
+        for cand in ((per,) if along_k else ()) + (flag_rows, 128, 64):
             if per % cand == 0 and cand % rows_per_job == 0:
                 flag_rows = cand
                 break
@@ -153,7 +164,7 @@ class GatherPlan:
         self.flags.zero_()
         d = dict(n_copy=self.n_copy, n_jobs=len(self.jobs), jobs=self._dev_jobs.data_ptr(),
                  flags=self.flags.data_ptr(), flag_target=self._targets_dev.data_ptr(),
-                 copy_bytes=self.remote_bytes, **self.kw)
+                 copy_bytes=self.remote_bytes, all_flag=self.n_slab_flags + 1, **self.kw)
         if self.local is not None:
             d["local"] = dict(self.local, n_jobs=len(self.jobs_nl), jobs=self._dev_jobs_nl.data_ptr(),
                               flag_target=self._targets_nl_dev.data_ptr())

@@ -14,11 +14,12 @@ def test_rows_plan_counters_and_local_slab():
     landing = torch.empty(Nn, K, dtype=torch.bfloat16)
     per = Nn // W
     pl = GatherPlan.rows(rank, W, _ptrs(W, per * K * 2), landing, n_copy=8, rows_per_job=64, flag_rows=256)
-    assert len(pl.flags) == Nn // 256 and pl.kw == dict(b_flag_rows=256, rot_n_rows=rank * per)
+    # one counter per 256 rows plus the counter that every job bumps ("everything has landed")
+    assert len(pl.flags) == Nn // 256 + 1 and pl.kw == dict(b_flag_rows=256, rot_n_rows=rank * per)
     # every 256-row counter expects its four 64-row jobs; without the local slab its counters expect none
-    assert pl.targets == [4] * 8
+    assert pl.targets == [4] * 8 + [32]
     own = [f for f in range(8) if rank * per <= f * 256 < (rank + 1) * per]
-    assert [pl.targets_nl[f] for f in own] == [0, 0] and sum(pl.targets_nl) == 4 * 6
+    assert [pl.targets_nl[f] for f in own] == [0, 0] and pl.targets_nl[-1] == 4 * 6 == sum(pl.targets_nl[:-1])
     assert len(pl.jobs) == W * per // 64 and len(pl.jobs_nl) == (W - 1) * per // 64
     assert pl.bytes_from_peers() == (W - 1) * per * K * 2
     assert pl.local == dict(ptr=_ptrs(W, per * K * 2)[rank], ld=K, mode=1, lo=rank * per, hi=(rank + 1) * per)
@@ -31,15 +32,17 @@ def test_rows_plan_counters_and_local_slab():
     assert args["n_jobs"] == len(pl.jobs) and args["local"]["n_jobs"] == len(pl.jobs_nl) and args["local"]["mode"] == 1
 
 
-def test_rows_plan_along_k_keeps_counters_inside_an_unaligned_slab():
-    W, rank, Nn, K = 8, 5, 9216, 256
+def test_rows_plan_along_k_has_one_counter_per_slab():
+    W, rank, Nn, K = 8, 5, 9216, 136               # K_in not a multiple of 256: counters per range of the reduction
     landing = torch.empty(Nn, K, dtype=torch.bfloat16)
     per = Nn // W                                  # 1152 rows: not a multiple of 256 -> 128-row counters
     pl = GatherPlan.rows(rank, W, _ptrs(W, per * K * 2), landing, along_k=True, n_copy=16)
-    assert len(pl.flags) == Nn // 128 and pl.kw == dict(a_flag_cols=128, rot_k_cols=rank * per)
-    assert pl.targets == [2] * (Nn // 128)         # two 64-row jobs per counter
-    own = range(rank * per // 128, (rank + 1) * per // 128)
-    assert all(pl.targets_nl[f] == 0 for f in own) and pl.local["mode"] == 2
+    # along the reduction dimension every tile walks all slabs: one counter per slab (a counter costs
+    # the producer a global load in the middle of its K loop), plus the "everything has landed" counter
+    assert len(pl.flags) == W + 1 and pl.kw == dict(a_flag_cols=per, rot_k_cols=rank * per)
+    assert pl.targets[:-1] == [per // 64] * W      # eighteen 64-row jobs per slab
+    assert pl.targets[-1] == len(pl.jobs) and pl.targets_nl[-1] == len(pl.jobs_nl)
+    assert pl.targets_nl[rank] == 0 and pl.local["mode"] == 2
 
 
 def test_rows_plan_rotation_is_a_whole_pair_tile_on_every_rank():
@@ -59,12 +62,12 @@ def test_rows_plan_rotation_is_a_whole_pair_tile_on_every_rank():
             assert owners == sorted(owners, key=lambda p: (p - rank) % W)
             assert pl.local["lo"] % 128 == 0 and pl.local["hi"] % 128 == 0
             # every counter is bumped by exactly the jobs that cover its rows
-            rows_per_flag = [0] * len(pl.flags)
+            rows_per_flag = [0] * (len(pl.flags) - 1)
             for j in pl.jobs:
                 rows_per_flag[j.flag] += j.rows
             assert rows_per_flag == [128] * (Nn // 128)
             pk = GatherPlan.rows(rank, W, _ptrs(W, per * K * 2), landing, along_k=True, n_copy=16)
-            assert pk.kw["rot_k_cols"] % 64 == 0 and pk.kw["a_flag_cols"] % 64 == 0
+            assert pk.kw["rot_k_cols"] % 64 == 0 and pk.kw["a_flag_cols"] == per
 
 
 def test_cols_plan_row_groups_and_local_block():
@@ -73,7 +76,7 @@ def test_cols_plan_row_groups_and_local_block():
     src = _ptrs(W, W * L * Cc * 2)
     pl = GatherPlan.cols(rank, W, src, rank * L, Cc * 2, landing, n_copy=4, rows_per_job=128)
     groups = L // 128
-    assert len(pl.flags) == W * groups and pl.targets == [1] * (W * groups)
+    assert len(pl.flags) == W * groups + 1 and pl.targets == [1] * (W * groups) + [W * groups]
     assert pl.kw == dict(a_flag_cols=Cc, rot_k_cols=rank * Cc, a_flag_rows=128)
     assert [pl.targets_nl[rank * groups + g] for g in range(groups)] == [0] * groups
     assert pl.local["mode"] == 3 and pl.local["ptr"] == src[rank] + rank * L * Cc * 2 and pl.local["ld"] == Cc
