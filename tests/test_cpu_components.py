@@ -389,3 +389,17 @@ def test_tread_and_checkpoint_policies():
         if pol == "none":
             ref = xin.grad.clone()
         assert torch.allclose(xin.grad, ref)
+
+
+def test_small_linear_backward_helpers_and_attention_counters_on_cpu():
+    """The conditioning-vector backward helpers and the head-size padding fall back to plain
+    PyTorch statements without the native library; the attention call counter moves."""
+    import torch
+    from eridiffusion_b200.ops import functional as F
+    dy, x, w = torch.randn(3, 40), torch.randn(3, 16), torch.randn(40, 16)
+    assert torch.allclose(F.small_wgrad(dy, x, 0.5), 0.5 * dy.t() @ x)
+    assert torch.allclose(F.small_dgrad(dy, w), dy @ w)
+    before = dict(F.ATTENTION_CALLS)
+    q = torch.randn(1, 32, 2, 40)
+    o = F.attention(q, q, q)
+    assert o.shape == q.shape and F.ATTENTION_CALLS["library"] == before["library"] + 1
