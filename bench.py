@@ -39,6 +39,8 @@ def parse():
     ap.add_argument("--sync", default=None, choices=[None, "allreduce", "zero1", "fused"])
     ap.add_argument("--batch", type=int, default=1)
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--keep-gc", action="store_true", help="leave Python's cyclic collector as it is (default: "
+                    "gc.freeze() after warm-up)")
     return ap.parse_args()
 
 
@@ -216,6 +218,13 @@ def main():
     for i in range(args.warmup):
         trainer.train_step(dev_pool[i % 4])
     barrier()
+    if not args.keep_gc:
+        # Long-lived objects (model, adapters, plans) leave the collector's generations: a full
+        # collection in the middle of a step costs tens of milliseconds of host time, which the
+        # end-to-end loop (one device -> host read per step) cannot hide behind queued launches.
+        import gc
+        gc.collect()
+        gc.freeze()
 
     sampler = ClockSampler(local) if cuda else None
     if sampler:

@@ -78,6 +78,9 @@ class Zero3Context:
         return [p + off for p in self.heap.peer_ptrs]
 
     def next_landing(self, n, k):
+        if n * k > self.landing[0].numel():
+            raise ValueError(f"a [{n}, {k}] weight does not fit the landing buffers "
+                             f"(max_weight_elems={self.landing[0].numel()}): raise it in Zero3Context")
         i = self._flip
         self._flip ^= 1
         return self.landing[i][: n * k].view(n, k), i

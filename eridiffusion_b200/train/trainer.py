@@ -59,6 +59,11 @@ class TrainerConfig:
     seed: int = 0
     out_dir: str | None = None
     ckpt_every: int = 0
+    # After this many optimizer steps the objects alive so far (model, adapters, arena views, launch
+    # plans) are moved out of the cyclic collector's generations (gc.freeze): a full collection in the
+    # middle of a step costs tens of milliseconds of host time, which shows as soon as something reads a
+    # result back every step. 0 leaves the collector alone.
+    gc_freeze_after: int = 3
     keep_last: int = 0
     lr_if_contains: dict = field(default_factory=dict)   # {name substring: LR multiplier}
     rotate_window: int = 0                  # >0: train only this many consecutive blocks at a time
@@ -188,6 +193,11 @@ class Trainer:
                 out = self._train_step(batch)
             self.strict_events = c.snapshot()
             return out
+        if self.cfg.gc_freeze_after and self.step == self.cfg.gc_freeze_after and not getattr(self, "_gc_frozen", False):
+            import gc
+            gc.collect()
+            gc.freeze()
+            self._gc_frozen = True
         return self._train_step(batch)
 
     def _train_step(self, batch: dict):

@@ -46,7 +46,7 @@ def _worker_body(rank, world, port, q):
     torch.manual_seed(0)
     lin = Linear(256, 512, device=dev)
     small = SmallLinear(256, 6 * 256, device=dev)
-    z3 = Zero3Context(pg, heap_bytes=8 << 20, max_weight_elems=1 << 20, n_copy=4)
+    z3 = Zero3Context(pg, heap_bytes=8 << 20, max_weight_elems=2 << 20, n_copy=4)
     zl, zs = Zero3Linear(lin, z3), Zero3SmallLinear(small, z3)
     # move the shards into the symmetric heap, as the trainer's arena does
     from eridiffusion_b200.optim import ParamArena
