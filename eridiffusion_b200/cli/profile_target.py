@@ -2,7 +2,7 @@
 the device, a handful of launches), one per hot kernel:
 
     python -m eridiffusion_b200.cli.profile_target gemm|gemm_lora|rank_stream|attn_fwd|attn_bwd|norm|qknorm|adamw|gemv|
-        elementwise|groupnorm|token_route|dequant
+        elementwise|groupnorm|token_route|dequant|attn_masked|small_linear_bwd|slot_reduce|gemm_small_m
 
 Meant to be run as ``ncu --set full --clock-control none -k regex:<kernel> -s 2 -c 1 ... python -m
 eridiffusion_b200.cli.profile_target <what>`` after the same command line exited 0 without ncu.
@@ -113,6 +113,49 @@ def main():
         for _ in range(iters):
             for q in qs:
                 dequantize(q)
+    elif what == "attn_masked":
+        # joint sequence with a text-padding mask (keys 300..511 of the text part hidden) and the SDXL
+        # cross-attention shape (77 keys): the MASK variants of the forward and backward kernels
+        from ..ops import functional as Fn
+        B, L, H, D = 1, 4608, 24, 128
+        q, k, v = (r(B, L, H, D).requires_grad_() for _ in range(3))
+        vis = torch.ones(B, 1, 1, L, dtype=torch.bool, device=dev)
+        vis[..., 300:512] = False
+        for _ in range(iters):
+            o = Fn.attention(q, k, v, mask=vis)
+            o.backward(torch.ones_like(o))
+        q2, k2, v2 = r(2, 4096, 10, 64).requires_grad_(), r(2, 77, 10, 64).requires_grad_(), r(2, 77, 10, 64).requires_grad_()
+        for _ in range(iters):
+            o = Fn.attention(q2, k2, v2)
+            o.backward(torch.ones_like(o))
+        assert FA.check_error() == 0
+    elif what == "small_linear_bwd":
+        # modulation linear [18432 x 3072] on one conditioning vector: dW (bound by writing 113 MB) and dx
+        # (bound by reading it); three weights so that every launch goes to DRAM
+        ws = [r(18432, 3072) for _ in range(3)]
+        dy, x = r(1, 18432), r(1, 3072)
+        for _ in range(iters):
+            for w in ws:
+                F.small_dgrad(dy, w)
+                F.small_wgrad(dy, x)
+    elif what == "slot_reduce":
+        # owner-side sum of the 8 ranks' slots of a [1536 x 3072] weight-gradient slab (ZeRO-3 fused reduce-scatter)
+        lib = F.N.require()
+        world, n = 8, 1536 * 3072
+        slots = [r(world * n) for _ in range(3)]
+        out = torch.empty(n, device=dev, dtype=torch.bfloat16)
+        for _ in range(iters):
+            for s_ in slots:
+                F.N.check(lib.eri_slot_reduce(s_.data_ptr(), out.data_ptr(), world, n, 1.0 / world, 0, F.N.stream_ptr()),
+                          "slot_reduce")
+    elif what == "gemm_small_m":
+        # text-stream GEMMs (512 tokens) on the one-CTA kernel's 128-column tiles
+        a1, a2 = r(512, 3072), r(512, 12288)
+        b1, b2 = r(3072, 3072), r(3072, 12288)
+        for _ in range(iters):
+            F.gemm_native(a1, b1)
+            F.gemm_native(a2, b2)
+        assert F.gemm_error_check() == 0
     else:
         raise SystemExit(f"unknown target {what}")
     torch.cuda.synchronize()

@@ -317,7 +317,7 @@ fa_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
               f2_unpack(v, lo, hi);
               v = f2_pack(ex2_mufu(lo), ex2_mufu(hi));
             } else {
-              v = ex2_poly2(v);
+              v = MASK ? ex2_poly2_z(v) : ex2_poly2(v);
             }
             pr[x] = v;
             pk[x] = f2_to_bf162(v);
@@ -658,7 +658,7 @@ fa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
               f2_unpack(v, lo, hi);
               v = f2_pack(ex2_mufu(lo), ex2_mufu(hi));
             } else {
-              v = ex2_poly2(v);
+              v = MASK ? ex2_poly2_z(v) : ex2_poly2(v);
             }
             pr[x] = v;
           }
@@ -796,7 +796,7 @@ int bwd_poly_pairs() {
 template <int DH>
 int launch_bwd(const CUtensorMap& q, const CUtensorMap& k, const CUtensorMap& v,
                const CUtensorMap& d, const FaBwdParams& p, cudaStream_t st) {
-  if (p.kbias) return launch_bwd_v<DH, 0, true>(q, k, v, d, p, st);
+  if (p.kbias) return launch_bwd_v<DH, 4, true>(q, k, v, d, p, st);
   const int poly = bwd_poly_pairs();
   if (poly == 0) return launch_bwd_v<DH, 0, false>(q, k, v, d, p, st);
   if (poly == 8) return launch_bwd_v<DH, 8, false>(q, k, v, d, p, st);

@@ -108,32 +108,49 @@ extern "C" int eri_gemv_bf16(const void* x, const void* w, const void* bias, voi
 // (crates/training/src/flux/runtime.rs:401-463 forward; gradients through the autograd tape).
 namespace {
 
-__global__ void rows_wgrad_kernel(const bf16* __restrict__ dy, int ldy, const bf16* __restrict__ x,
-                                  int ldx, bf16* __restrict__ dw, int ldw, int T, int N, int K,
-                                  int accumulate, float scale) {
+__global__ void __launch_bounds__(128) rows_wgrad_kernel(const bf16* __restrict__ dy, int ldy, const bf16* __restrict__ x,
+                                                         int ldx, bf16* __restrict__ dw, int ldw, int T, int N, int K,
+                                                         int accumulate, float scale) {
+  // a CTA owns 128 x 8 columns of dW and walks its rows in chunks of kChunk: the chunk's dy values are
+  // staged in shared memory first, so that the row loop has no dependent global load in it
+  constexpr int kChunk = 64;
+  __shared__ float sdy[kMaxM][kChunk];
   const int kv = blockIdx.x * blockDim.x + threadIdx.x;   // 8 columns per thread
-  if (kv * 8 >= K) return;
+  const bool live = kv * 8 < K;
   float xf[kMaxM][8];
+#pragma unroll
   for (int t = 0; t < kMaxM; ++t) {
-    if (t < T) unpack8(*reinterpret_cast<const bf16x8*>(x + (size_t)t * ldx + kv * 8), xf[t]);
+    if (t < T && live) unpack8(*reinterpret_cast<const bf16x8*>(x + (size_t)t * ldx + kv * 8), xf[t]);
   }
-  for (int n = blockIdx.y; n < N; n += gridDim.y) {
-    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-    for (int t = 0; t < kMaxM; ++t) {
-      if (t < T) {
-        const float d = __bfloat162float(dy[(size_t)t * ldy + n]) * scale;
+  for (int n0 = blockIdx.y * kChunk; n0 < N; n0 += gridDim.y * kChunk) {
+    const int nc = min(kChunk, N - n0);
+    __syncthreads();
+    for (int i = threadIdx.x; i < T * kChunk; i += blockDim.x) {
+      const int t = i / kChunk, j = i - t * kChunk;
+      sdy[t][j] = j < nc ? __bfloat162float(dy[(size_t)t * ldy + n0 + j]) * scale : 0.f;
+    }
+    __syncthreads();
+    if (!live) continue;
+#pragma unroll 4
+    for (int j = 0; j < nc; ++j) {
+      float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-        for (int j = 0; j < 8; ++j) acc[j] = fmaf(d, xf[t][j], acc[j]);
+      for (int t = 0; t < kMaxM; ++t) {
+        if (t < T) {
+          const float d = sdy[t][j];
+#pragma unroll
+          for (int q = 0; q < 8; ++q) acc[q] = fmaf(d, xf[t][q], acc[q]);
+        }
       }
-    }
-    bf16x8* o = reinterpret_cast<bf16x8*>(dw + (size_t)n * ldw + kv * 8);
-    if (accumulate) {
-      float old[8];
-      unpack8(*o, old);
+      bf16x8* o = reinterpret_cast<bf16x8*>(dw + (size_t)(n0 + j) * ldw + kv * 8);
+      if (accumulate) {
+        float old[8];
+        unpack8(*o, old);
 #pragma unroll
-      for (int j = 0; j < 8; ++j) acc[j] += old[j];
+        for (int q = 0; q < 8; ++q) acc[q] += old[q];
+      }
+      *o = pack8(acc);
     }
-    *o = pack8(acc);
   }
 }
 
@@ -179,7 +196,8 @@ extern "C" int eri_rows_wgrad(const void* dy, int ldy, const void* x, int ldx, v
   // about sixteen CTAs per SM, each looping over its rows of dW with the x rows held in registers
   const int gx = (K / 8 + block - 1) / block;
   int gy = (148 * 16 + gx - 1) / gx;
-  if (gy > N) gy = N;
+  const int chunks = (N + 63) / 64;
+  if (gy > chunks) gy = chunks;
   if (gy > 65535) gy = 65535;
   dim3 grid(gx, gy);
   rows_wgrad_kernel<<<grid, block, 0, (cudaStream_t)stream>>>((const bf16*)dy, ldy, (const bf16*)x, ldx,

@@ -568,6 +568,15 @@ __device__ __forceinline__ f32x2 ex2_poly2(f32x2 x) {
   p1 += t1 << 23;
   return f2_pack_bits(p0, p1);
 }
+// Same, with an exact zero where x < -125 (a masked key carries a bias of -1e30: its probability and
+// therefore its gradients must be exactly zero, as the special-function unit gives them).
+__device__ __forceinline__ f32x2 ex2_poly2_z(f32x2 x) {
+  float x0, x1;
+  f2_unpack(x, x0, x1);
+  float r0, r1;
+  f2_unpack(ex2_poly2(x), r0, r1);
+  return f2_pack(x0 < -125.f ? 0.f : r0, x1 < -125.f ? 0.f : r1);
+}
 // round a pair to packed bf16 (low half = lo)
 __device__ __forceinline__ uint32_t f2_to_bf162(f32x2 v) {
   float lo, hi;
