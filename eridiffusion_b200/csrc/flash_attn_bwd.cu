@@ -37,7 +37,8 @@ struct FaBwdParams {
   bf16* dk;              // [B, Lk, H, DH]
   bf16* dv;
   int* err;
-  const float* kbias;    // MASK variants: [B, Lkb] additive key bias in log2 units (-1e30 = masked)
+  const float* kbias;    // MASK variants: [B, Lkb] additive key bias in log2 units (-1e30 = masked),
+                         // followed by one int per (batch, 128-key tile): 1 = the tile has a non-zero bias
   int Lkb;               // ceil(Lk / 128) * 128
 };
 
@@ -636,7 +637,9 @@ fa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(s_read);  // S is in registers: the next S may overwrite it
-        if constexpr (MASK) {
+        const bool use_bias =
+            MASK && reinterpret_cast<const int*>(p.kbias + (size_t)p.B * p.Lkb)[b * (p.Lkb / T) + j] != 0;
+        if (use_bias) {
           // the 32 keys of this warp's chunk: every lane reads the same bias values
           const float4* kb4 = reinterpret_cast<const float4*>(p.kbias + (size_t)b * p.Lkb + j * T + c * 32);
 #pragma unroll

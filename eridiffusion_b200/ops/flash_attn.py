@@ -125,8 +125,18 @@ def mask_is_key_only(mask, B, Lk) -> bool:
     return len(shp) == 4 and shp[1] == 1 and shp[2] == 1 and shp[3] == Lk and shp[0] in (1, B)
 
 
+def _with_tile_flags(kb):
+    """[B, Lkb] bias rows -> one flat fp32 buffer: the rows, then one int32 per (batch, 128-key tile)
+    that is 1 when any key of the tile carries a non-zero bias. The kernels run their unmasked fast
+    path on the tiles whose flag is 0 (all but the text-padding tiles of a joint sequence)."""
+    B, Lkb = kb.shape
+    flags = (kb.view(B, Lkb // 128, 128) != 0).any(-1).to(torch.int32)
+    return torch.cat([kb.reshape(-1), flags.reshape(-1).view(torch.float32)])
+
+
 def key_bias(mask, B, Lk, device):
-    """[B, ceil(Lk/128)*128] fp32 additive key bias in log2 units for the masked kernels. ``mask``:
+    """Additive key bias in log2 units for the masked kernels: a flat fp32 buffer holding
+    [B, ceil(Lk/128)*128] rows followed by the per-tile flags (see ``_with_tile_flags``). ``mask``:
     None (only the padding beyond Lk is blanked), boolean (True = visible) or additive (natural-log
     units; -inf allowed), of a shape accepted by ``mask_is_key_only``."""
     Lkb = (Lk + 127) // 128 * 128
@@ -135,18 +145,19 @@ def key_bias(mask, B, Lk, device):
         key = (B, Lk, str(device))
         kb = _PAD_BIAS.get(key)
         if kb is None:
-            kb = torch.full((B, Lkb), _MASKED, dtype=torch.float32, device=device)
-            kb[:, :Lk] = 0.0
+            rows = torch.full((B, Lkb), _MASKED, dtype=torch.float32, device=device)
+            rows[:, :Lk] = 0.0
+            kb = _with_tile_flags(rows)
             _PAD_BIAS[key] = kb
         return kb
-    kb = torch.full((B, Lkb), _MASKED, dtype=torch.float32, device=device)
+    rows = torch.full((B, Lkb), _MASKED, dtype=torch.float32, device=device)
     m = mask.reshape(mask.shape[0], Lk).to(device)
     if m.dtype == torch.bool:
         row = torch.where(m, 0.0, _MASKED).float()
     else:
         row = (m.float() * _LOG2E).clamp_min(_MASKED)
-    kb[:, :Lk] = row.expand(B, Lk)
-    return kb
+    rows[:, :Lk] = row.expand(B, Lk)
+    return _with_tile_flags(rows)
 
 
 def fwd(q, k, v, scale=None, out=None, kbias=None):

@@ -403,3 +403,29 @@ def test_small_linear_backward_helpers_and_attention_counters_on_cpu():
     q = torch.randn(1, 32, 2, 40)
     o = F.attention(q, q, q)
     assert o.shape == q.shape and F.ATTENTION_CALLS["library"] == before["library"] + 1
+
+
+def test_key_bias_rows_are_followed_by_per_tile_flags():
+    """The masked attention kernels read [B, ceil(Lk/128)*128] bias rows and, behind them, one int per
+    (batch, 128-key tile) that tells whether any key of the tile is biased (only those tiles leave the
+    unmasked fast path)."""
+    import torch
+    from eridiffusion_b200.ops import flash_attn as FA
+    B, Lk = 2, 300                                   # three tiles per sample, the last one partly padding
+    vis = torch.ones(B, 1, 1, Lk, dtype=torch.bool)
+    vis[1, ..., 130:140] = False                     # sample 1 hides ten keys of its second tile
+    kb = FA.key_bias(vis, B, Lk, torch.device("cpu"))
+    Lkb = 384
+    assert kb.dtype == torch.float32 and kb.numel() == B * Lkb + B * 3
+    rows = kb[: B * Lkb].view(B, Lkb)
+    flags = kb[B * Lkb:].view(torch.int32).view(B, 3)
+    assert float(rows[0, :Lk].abs().max()) == 0.0 and bool((rows[:, Lk:] < -1e29).all())
+    assert bool((rows[1, 130:140] < -1e29).all()) and float(rows[1, :130].abs().max()) == 0.0
+    assert flags.tolist() == [[0, 0, 1], [0, 1, 1]]
+    # padding only (no mask): every full tile is plain
+    kb2 = FA.key_bias(None, 1, 256 + 77, torch.device("cpu"))
+    assert kb2[384:].view(torch.int32).tolist() == [0, 0, 1]
+    # an additive mask in natural-log units lands in log2 units
+    add = torch.zeros(1, 1, 1, 128); add[..., 5] = -1.0
+    kb3 = FA.key_bias(add, 1, 128, torch.device("cpu"))
+    assert abs(float(kb3[5]) + 1.4426950408889634) < 1e-6 and kb3[128:].view(torch.int32).tolist() == [1]
