@@ -72,6 +72,10 @@ struct Gemm2Params {
   float* rowsq;
   int rowsq_parts;
   long long dbg_out_bytes, dbg_out2_bytes, dbg_pre_bytes, dbg_res_bytes;   // debug build only
+  // Grouped launch (two plain products with the same N, K, operand majors, LoRA rank and epilogue
+  // kind, e.g. the image and the text stream of a dual-stream block): tiles [0, group_tiles0) belong
+  // to this problem, the rest to the second parameter block. 0: a single problem. total_tiles: all.
+  int group_tiles0, total_tiles;
 };
 
 ERI_DEBUG_BOUNDS_DEFINE(gemm2)
@@ -122,9 +126,15 @@ __device__ __forceinline__ float apply_act_grad(float pre, int act) {
 // asynchronous copy (the peer scatter, whose destination rows live on other GPUs).
 template <int STAGES, bool STAGED>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(192, 1)
-gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                  const __grid_constant__ CUtensorMap tmA2, const __grid_constant__ CUtensorMap tmB2,
-                  const __grid_constant__ CUtensorMap tmBL, const __grid_constant__ Gemm2Params p) {
+gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA_0, const __grid_constant__ CUtensorMap tmB_0,
+                  const __grid_constant__ CUtensorMap tmA2_0, const __grid_constant__ CUtensorMap tmB2_0,
+                  const __grid_constant__ CUtensorMap tmBL, const __grid_constant__ Gemm2Params p0,
+                  const __grid_constant__ CUtensorMap tmA_1, const __grid_constant__ CUtensorMap tmB_1,
+                  const __grid_constant__ CUtensorMap tmA2_1, const __grid_constant__ CUtensorMap tmB2_1,
+                  const __grid_constant__ Gemm2Params p1) {
+  // Launch-wide state comes from the first parameter block; inside the tile loops `p` and the
+  // operand maps are re-bound per tile to the problem the tile belongs to (grouped launch).
+  const Gemm2Params& p = p0;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~uintptr_t(1023));
@@ -182,10 +192,9 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-  const int num_m = (p.M + 2 * BM - 1) / (2 * BM);
   // GLU: a tile is 128 output columns (value rows from the first half of B, gate rows from the second)
   const int num_n = p.glu ? (p.glu_hidden + BNH - 1) / BNH : (p.N + BN - 1) / BN;
-  const int tiles = num_m * num_n;
+  const int tiles = p.total_tiles;     // both problems of a grouped launch
   const int k_iters = p.num_k + (p.lora_r > 0 ? 1 : 0);
   const bool was_copy = (int)blockIdx.x < p.n_copy;
   TileSched sched;
@@ -206,8 +215,16 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
       for (int r = sched.first_round; ok; ++r) {
         const int t = sched.tile(r);
         if (t >= tiles) break;
+        // grouped launch: this tile's problem, its operand maps and its tile index within the problem
+        const bool g1 = p0.group_tiles0 > 0 && t >= p0.group_tiles0;
+        const Gemm2Params& p = g1 ? p1 : p0;
+        const CUtensorMap& tmA = g1 ? tmA_1 : tmA_0;
+        const CUtensorMap& tmB = g1 ? tmB_1 : tmB_0;
+        const CUtensorMap& tmA2 = g1 ? tmA2_1 : tmA2_0;
+        const CUtensorMap& tmB2 = g1 ? tmB2_1 : tmB2_0;
+        const int num_m = (p.M + 2 * BM - 1) / (2 * BM);
         int m_blk, n_blk;
-        tile_coords(t, num_m, num_n, p.rot_n, m_blk, n_blk);
+        tile_coords(g1 ? t - p0.group_tiles0 : t, num_m, num_n, p.rot_n, m_blk, n_blk);
         const int m0 = m_blk * 2 * BM + (int)rank * BM;
         const int n0 = p.glu ? n_blk * BNH + (int)rank * p.glu_hidden : n_blk * BN + (int)rank * BNH;
         const bool b_rows_local = p.loc_mode == 1 && n0 >= p.loc_lo && n0 + BNH <= p.loc_hi;
@@ -371,8 +388,11 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     int it = 0;
     for (int r = sched.first_round; sched.tile(r) < tiles; ++r, ++it) {
       const int t = sched.tile(r);
+      const bool g1 = p0.group_tiles0 > 0 && t >= p0.group_tiles0;
+      const Gemm2Params& p = g1 ? p1 : p0;     // this tile's problem (grouped launch)
+      const int num_m = (p.M + 2 * BM - 1) / (2 * BM);
       int m_blk, n_blk;
-      tile_coords(t, num_m, num_n, p.rot_n, m_blk, n_blk);
+      tile_coords(g1 ? t - p0.group_tiles0 : t, num_m, num_n, p.rot_n, m_blk, n_blk);
       const int m0 = m_blk * 2 * BM + (int)rank * BM, n0 = p.glu ? n_blk * BNH : n_blk * BN;
       const int buf = it & 1;
       const uint32_t use = (uint32_t)(it >> 1);
@@ -577,9 +597,18 @@ int g2_num_sms = 0;
 int* g2_err = nullptr;
 long long g2_gather_launches = 0;   // gather-mode launches that ran on this kernel (host counter)
 
+// Operand maps of one problem: A, B, LoRA rank-r operands (H, up-matrix) and the in-place local slab.
+struct Gemm2Maps {
+  CUtensorMap ta, tb, ta2, tb2, tbl;
+};
+
+// p / m: the (first) problem; pg / mg: the second problem of a grouped launch (the same objects as
+// p / m for a single problem: the kernel never looks at them then).
 template <int STAGES, bool STAGED>
-int launch2(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& ta2, const CUtensorMap& tb2,
-            const CUtensorMap& tbl, Gemm2Params& p, int tiles, int pdl, cudaStream_t st) {
+int launch2(const Gemm2Maps& m, Gemm2Params& p, const Gemm2Maps& mg, const Gemm2Params& pg, int tiles, int pdl,
+            cudaStream_t st) {
+  const CUtensorMap &ta = m.ta, &tb = m.tb, &ta2 = m.ta2, &tb2 = m.tb2, &tbl = m.tbl;
+  p.total_tiles = tiles;
   constexpr int SMEM = STAGES * STAGE_BYTES + 1024 + 256 + (STAGED ? BM * STG_PITCH : 0);
   auto kern = gemm2_bf16_kernel<STAGES, STAGED>;
   int dev = 0;
@@ -616,7 +645,8 @@ int launch2(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& ta2
     const int room = coop_clusters - p.n_copy / 2;
     if (room < 8) return -30;
     const int clusters = tiles < room ? tiles : room;
-    void* args[] = {(void*)&ta, (void*)&tb, (void*)&ta2, (void*)&tb2, (void*)&tbl, (void*)&p};
+    void* args[] = {(void*)&ta, (void*)&tb, (void*)&ta2, (void*)&tb2, (void*)&tbl, (void*)&p,
+                    (void*)&mg.ta, (void*)&mg.tb, (void*)&mg.ta2, (void*)&mg.tb2, (void*)&pg};
     cudaError_t e = cudaLaunchCooperativeKernel((const void*)kern, dim3(p.n_copy + clusters * 2),
                                                 dim3(192), args, SMEM, st);
     if (e != cudaSuccess) {
@@ -639,9 +669,9 @@ int launch2(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& ta2
     at[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = at;
     cfg.numAttrs = 1;
-    return (int)cudaLaunchKernelEx(&cfg, kern, ta, tb, ta2, tb2, tbl, p);
+    return (int)cudaLaunchKernelEx(&cfg, kern, ta, tb, ta2, tb2, tbl, p, mg.ta, mg.tb, mg.ta2, mg.tb2, pg);
   }
-  kern<<<clusters * 2, 192, SMEM, st>>>(ta, tb, ta2, tb2, tbl, p);
+  kern<<<clusters * 2, 192, SMEM, st>>>(ta, tb, ta2, tb2, tbl, p, mg.ta, mg.tb, mg.ta2, mg.tb2, pg);
   return (int)cudaGetLastError();
 }
 
@@ -661,8 +691,13 @@ int eri_gemm2_check_error() {
   return h;
 }
 
-// Returns -30 when the problem does not fit this kernel (caller falls back to eri_gemm_bf16).
-int eri_gemm2_bf16(const EriGemmArgs2* g, void* stream) {
+}  // extern "C"
+
+namespace {
+
+// Validates one problem and fills its parameter block and operand maps. Returns 0, or the negative
+// code the entry points hand back (-30: the problem does not fit this kernel). `tiles_out`: its tiles.
+int build_problem(const EriGemmArgs* g, Gemm2Params& p, Gemm2Maps& m, int& tiles_out) {
   const bool scatter = g->scatter_world != 0;
   if (g->rowsq && !scatter) return -30;
   if (scatter && g->scatter_mode == 1) {
@@ -702,7 +737,6 @@ int eri_gemm2_bf16(const EriGemmArgs2* g, void* stream) {
     if (cudaMalloc(&g2_err, sizeof(int)) != cudaSuccess) return -31;
     cudaMemset(g2_err, 0, sizeof(int));
   }
-  Gemm2Params p;
   memset(&p, 0, sizeof(p));
   p.M = g->M; p.N = g->N; p.K = g->K; p.num_k = (g->K + BK - 1) / BK;
   p.lora_r = g->lora_r; p.act = g->act; p.n_split = g->n_split > 0 ? g->n_split : -1;
@@ -743,7 +777,7 @@ int eri_gemm2_bf16(const EriGemmArgs2* g, void* stream) {
     p.flag_target = (const unsigned int*)g->flag_target_nl;
   }
 
-  CUtensorMap ta, tb, ta2, tb2;
+  CUtensorMap &ta = m.ta, &tb = m.tb, &ta2 = m.ta2, &tb2 = m.tb2, &tbl = m.tbl;
   if (!g->a_mn) {
     uint64_t d[2] = {(uint64_t)g->K, (uint64_t)g->M};
     uint64_t s[1] = {(uint64_t)g->lda * 2};
@@ -779,7 +813,7 @@ int eri_gemm2_bf16(const EriGemmArgs2* g, void* stream) {
     ta2 = ta;
     tb2 = tb;
   }
-  CUtensorMap tbl = tb;
+  tbl = tb;
   if (use_local) {
     const uint64_t rows = (uint64_t)(g->loc_hi - g->loc_lo);
     uint64_t s[1] = {(uint64_t)g->ldb_local * 2};
@@ -798,11 +832,49 @@ int eri_gemm2_bf16(const EriGemmArgs2* g, void* stream) {
     }
   }
   const int n_tiles = g->glu ? (g->N / 2 + BNH - 1) / BNH : (g->N + BN - 1) / BN;
-  const int tiles = ((g->M + 2 * BM - 1) / (2 * BM)) * n_tiles;
+  tiles_out = ((g->M + 2 * BM - 1) / (2 * BM)) * n_tiles;
+  return 0;
+}
+
+}  // namespace
+
+extern "C" {
+
+// Returns -30 when the problem does not fit this kernel (caller falls back to eri_gemm_bf16).
+int eri_gemm2_bf16(const EriGemmArgs2* g, void* stream) {
+  Gemm2Params p;
+  Gemm2Maps m;
+  int tiles = 0;
+  const int code = build_problem(g, p, m, tiles);
+  if (code) return code;
   cudaStream_t st = (cudaStream_t)stream;
   // four operand stages leave room for the 128 staged accumulator rows of the peer scatter
-  if (scatter) return launch2<4, true>(ta, tb, ta2, tb2, tbl, p, tiles, 0, st);
-  return launch2<6, false>(ta, tb, ta2, tb2, tbl, p, tiles, g->pdl && g->lora_r, st);
+  if (g->scatter_world) return launch2<4, true>(m, p, m, p, tiles, 0, st);
+  return launch2<6, false>(m, p, m, p, tiles, g->pdl && g->lora_r, st);
+}
+
+// Two plain products in ONE launch: the tiles of the second follow the tiles of the first in the
+// persistent schedule, so a small second problem (the 512-token text stream of a dual-stream block:
+// 24-96 tiles) runs in the last, partly empty round of the first instead of as a launch of its own
+// that leaves most SMs idle. Both must have the same N, K, operand majors, LoRA rank, activation and
+// column split, and neither may use gather, scatter, GLU or token-major A. Returns -30 when the pair
+// does not qualify (the caller then launches them one by one).
+int eri_gemm2_bf16_group2(const EriGemmArgs2* g0, const EriGemmArgs2* g1, void* stream) {
+  const EriGemmArgs2* gs[2] = {g0, g1};
+  for (const EriGemmArgs2* g : gs)
+    if (g->scatter_world || g->n_copy || g->glu || g->a_mn || g->rowsq) return -30;
+  if (g0->N != g1->N || g0->K != g1->K || g0->b_mn != g1->b_mn || g0->lora_r != g1->lora_r || g0->act != g1->act ||
+      g0->n_split != g1->n_split || g0->alpha != g1->alpha || (g0->out2 != nullptr) != (g1->out2 != nullptr))
+    return -30;
+  Gemm2Params p0, p1;
+  Gemm2Maps m0, m1;
+  int t0 = 0, t1 = 0;
+  int code = build_problem(g0, p0, m0, t0);
+  if (code) return code;
+  code = build_problem(g1, p1, m1, t1);
+  if (code) return code;
+  p0.group_tiles0 = t0;
+  return launch2<6, false>(m0, p0, m1, p1, t0 + t1, g0->pdl && g1->pdl && g0->lora_r, (cudaStream_t)stream);
 }
 
 }  // extern "C"

@@ -114,6 +114,7 @@ _SIGNATURES = {
     "eri_gemm_check_error": [],
     "eri_gemm_bf16": [C.POINTER(GemmArgs), _P],
     "eri_gemm2_bf16": [C.POINTER(GemmArgs), _P],
+    "eri_gemm2_bf16_group2": [C.POINTER(GemmArgs), C.POINTER(GemmArgs), _P],
     "eri_gemm2_check_error": [],
     "eri_gemm2_gather_count": [],
     "eri_rows_wgrad": [_P, _I, _P, _I, _P, _I, _I, _I, _I, _I, _F, _P],

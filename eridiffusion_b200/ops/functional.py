@@ -354,7 +354,7 @@ _ACT_CODE = {None: 0, "gelu": 1, "silu": 2, "gelu_bwd": 3, "silu_bwd": 4}
 def gemm_native(a, b, *, out=None, alpha=1.0, bias=None, lora_h=None, lora_b=None, act=None,
                 pre_out=None, pre_in=None, residual=None, gate=None, rows_per_batch=0,
                 n_split=0, out2=None, force_bn=0, b_mn=False, gather=None, scatter=None, pdl=False,
-                a_mn=False, glu=0):
+                a_mn=False, glu=0, _prepare_only=False):
     """out[M,N] = epilogue(a[M,K] @ op(b) (+ lora_h[M,r] @ lora_b[N,r]^T)) on the tcgen05 kernel.
 
     ``b`` is [N, K] (``op`` = transpose) or, with ``b_mn=True``, [K, N] used as is. ``a``/``b``/
@@ -443,6 +443,14 @@ def gemm_native(a, b, *, out=None, alpha=1.0, bias=None, lora_h=None, lora_b=Non
             g.scatter_out[i] = ptr_
         if scatter.get("rowsq") is not None:
             g.rowsq, g.rowsq_parts = scatter["rowsq"].data_ptr(), scatter["rowsq"].shape[0]
+    route = (M, Nn, K, a_mn, glu, gather, scatter, force_bn)
+    if _prepare_only:
+        return g, out, route          # ``gemm_native_pair`` launches it, alone or grouped
+    return _launch_gemm(lib, g, out, route)
+
+
+def _launch_gemm(lib, g, out, route):
+    M, Nn, K, a_mn, glu, gather, scatter, force_bn = route
     # Few pair tiles (the 512-token text stream against a 3072-wide weight: 24 tiles for 74 CTA pairs)
     # leave most SMs idle; the one-CTA kernel's 128-column tiles spread the same work over four times
     # as many CTAs (measured 22.5 against 30.7 us at 512 x 3072 x 3072, 61 against 78 us at K = 12288).
@@ -461,6 +469,29 @@ def gemm_native(a, b, *, out=None, alpha=1.0, bias=None, lora_h=None, lora_b=Non
     code = lib.eri_gemm_bf16(g, N.stream_ptr())
     N.check(code, "gemm_bf16")
     return out
+
+
+_GEMM_GROUP = os.environ.get("ERI_B200_GEMM_GROUP", "1") == "1"
+
+
+def gemm_native_pair(kw0: dict, kw1: dict):
+    """Two independent products (keyword arguments of ``gemm_native`` each) in ONE launch of the two-CTA
+    kernel when they qualify: same N, K, operand majors, LoRA rank and epilogue kind, plain modes. The
+    second problem's tiles follow the first's in the persistent schedule, so a small second problem
+    (the text stream of a dual-stream block) runs in the first one's last, partly empty round instead of
+    as a launch that leaves most SMs idle. Otherwise the two are launched one after the other.
+    Returns (out0, out1)."""
+    lib = N.require()
+    g0, out0, r0 = gemm_native(**kw0, _prepare_only=True)
+    g1, out1, r1 = gemm_native(**kw1, _prepare_only=True)
+    plain = all(not (r[3] or r[4]) and r[5] is None and r[6] is None and r[7] == 0 and r[0] >= 256 and r[1] >= 256
+                for r in (r0, r1))
+    if _GEMM_GROUP and _GEMM_PAIR and plain and hasattr(lib, "eri_gemm2_bf16_group2"):
+        code = lib.eri_gemm2_bf16_group2(g0, g1, N.stream_ptr())
+        if code != -30:
+            N.check(code, "gemm2_bf16_group2")
+            return out0, out1
+    return _launch_gemm(lib, g0, out0, r0), _launch_gemm(lib, g1, out1, r1)
 
 
 def skinny_gemm(a, b, alpha=1.0):

@@ -63,3 +63,41 @@ def test_pair_lora_epilogues(r):
     pf = pre2.float().requires_grad_()
     gd = torch.autograd.grad(torch.nn.functional.gelu(pf, approximate="tanh").sum(), pf)[0]
     close(out2, full[:, n_split:] * gd, 0.06)
+
+
+@pytest.mark.parametrize("M0,M1,N,K", [(4096, 512, 3072, 320), (1024, 256, 768, 512), (768, 300, 1024, 256)])
+@pytest.mark.parametrize("mn", [False, True])
+def test_grouped_launch_of_two_problems(M0, M1, N, K, mn):
+    """Two products with the same N and K (image and text stream of a dual-stream block) in one launch:
+    each with its own weight, bias, LoRA pair, residual and gate; results equal the separate launches."""
+    F.set_gemm_pair(True)
+    lib = F.N.require()
+    r = 16
+    outs = []
+    kws = []
+    for i, M in enumerate((M0, M1)):
+        x = rnd(M, K, seed=10 * i)
+        w = rnd(N, K, scale=K ** -0.5, seed=10 * i + 1)
+        b_op = w.t().contiguous() if mn else w
+        bias, res = rnd(N, seed=10 * i + 2), rnd(M, N, seed=10 * i + 3)
+        gate = rnd(1, N, seed=10 * i + 4)
+        A, Bm = rnd(r, K, scale=K ** -0.5, seed=10 * i + 5), rnd(N, r, scale=0.1, seed=10 * i + 6)
+        h = F.gemm_native(x, A, alpha=0.5)
+        kw = dict(a=x, b=b_op, bias=bias, lora_h=h, lora_b=Bm, residual=res, gate=gate, rows_per_batch=M, b_mn=mn)
+        kws.append(kw)
+        outs.append(F.gemm_native(**kw).clone())
+        ref = res.float() + gate.float() * (x.float() @ w.float().t() + bias.float() + h.float() @ Bm.float().t())
+        close(outs[-1], ref, 0.06)
+    c0 = F.N.launch_count()
+    y0, y1 = F.gemm_native_pair(kws[0], kws[1])
+    assert F.N.launch_count() == c0 + 1, "the two products did not share one launch"
+    assert F.gemm_error_check() == 0
+    # the separate launches may have run on another kernel (few tiles: one-CTA route), so compare values
+    for y, o in ((y0, outs[0]), (y1, outs[1])):
+        assert (y.float() - o.float()).abs().max().item() <= 0.02 * o.float().abs().max().item()
+    # a pair that does not qualify (different K) is launched one by one and still right
+    x2, w2 = rnd(M1, K + 64, seed=77), rnd(N, K + 64, seed=78)
+    z0, z1 = F.gemm_native_pair(dict(a=kws[0]["a"], b=kws[0]["b"], b_mn=mn),
+                                dict(a=x2, b=w2.t().contiguous() if mn else w2, b_mn=mn))
+    close(z1, x2.float() @ w2.float().t(), 0.06)
+    assert F.gemm_error_check() == 0
