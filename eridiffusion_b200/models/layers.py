@@ -62,6 +62,33 @@ class Linear(nn.Module):
         return f"in={self.in_features}, out={self.out_features}, bias={self.bias is not None}"
 
 
+def _pair_spec(lin):
+    """(weight, bias, lora triple or None) of a layer whose forward is exactly one fused linear: a plain
+    ``Linear`` without hooks, bare or with a plain LoRA adapter that applies no dropout. None otherwise."""
+    if type(lin) is not Linear or lin._forward_hooks or lin._forward_pre_hooks or _KEEP_TRANSPOSE:
+        return None
+    ad = lin.adapter
+    if ad is None:
+        return lin.weight, lin.bias, None
+    if getattr(ad, "kind", None) != "lora" or type(ad).__name__ != "LoRA" or ad._forward_hooks:
+        return None
+    if ad.dropout > 0 and ad.training:
+        return None
+    return lin.weight, lin.bias, (ad.lora_A, ad.lora_B, ad.scale)
+
+
+def linear_pair(lin0, x0, lin1, x1, act=None, residual=(None, None), gate=(None, None)):
+    """``(lin0(x0), lin1(x1))`` for two layers of equal shape (the image and the text projection of a
+    dual-stream block). When both are plain or plain-LoRA layers their main GEMMs run as one grouped launch
+    (``F.linear_pair``), so the small text-stream product fills the last, partly empty round of the image
+    one instead of leaving most SMs idle in a launch of its own."""
+    s0, s1 = _pair_spec(lin0), _pair_spec(lin1)
+    if s0 is None or s1 is None or not F._GEMM_GROUP:
+        return (lin0(x0, act=act, residual=residual[0], gate=gate[0]),
+                lin1(x1, act=act, residual=residual[1], gate=gate[1]))
+    return F.linear_pair(x0, (*s0, residual[0], gate[0]), x1, (*s1, residual[1], gate[1]), act=act)
+
+
 class SmallLinear(Linear):
     """Linear applied to a few conditioning rows (adaLN modulation, embedders)."""
 

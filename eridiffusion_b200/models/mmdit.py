@@ -24,7 +24,7 @@ import torch.nn as nn
 
 from ..ops import functional as F
 from .layers import (Linear, MLPEmbedder, Modulation, RMSNormScale, SmallLinear, image_ids,
-                     rope_table, timestep_embedding)
+                     linear_pair, rope_table, timestep_embedding)
 from .registry import register_model
 
 
@@ -84,20 +84,20 @@ class DoubleStreamBlock(nn.Module):
         i_sh1, i_sc1, i_g1, i_sh2, i_sc2, i_g2 = self.img_mod(vec)
         t_sh1, t_sc1, t_g1, t_sh2, t_sc2, t_g2 = self.txt_mod(vec)
         Lt = txt.shape[1]
-        img_qkv = self.img_attn.qkv(F.norm_modulate(img, i_sc1, i_sh1))
-        txt_qkv = self.txt_attn.qkv(F.norm_modulate(txt, t_sc1, t_sh1))
+        img_qkv, txt_qkv = linear_pair(self.img_attn.qkv, F.norm_modulate(img, i_sc1, i_sh1),
+                                       self.txt_attn.qkv, F.norm_modulate(txt, t_sc1, t_sh1))
         q, k, v = F.qknorm_rope_joint(
             [(txt_qkv, self.txt_attn.q_norm.scale, self.txt_attn.k_norm.scale),
              (img_qkv, self.img_attn.q_norm.scale, self.img_attn.k_norm.scale)],
             cos, sin, self.heads)
         attn = F.attention(q, k, v).flatten(2)               # [B, Lt+Li, D]
         txt_a, img_a = attn[:, :Lt], attn[:, Lt:]
-        img = self.img_attn.proj(img_a, residual=img, gate=i_g1)
-        img = self.img_mlp_2(self.img_mlp_0(F.norm_modulate(img, i_sc2, i_sh2), act="gelu"),
-                             residual=img, gate=i_g2)
-        txt = self.txt_attn.proj(txt_a, residual=txt, gate=t_g1)
-        txt = self.txt_mlp_2(self.txt_mlp_0(F.norm_modulate(txt, t_sc2, t_sh2), act="gelu"),
-                             residual=txt, gate=t_g2)
+        img, txt = linear_pair(self.img_attn.proj, img_a, self.txt_attn.proj, txt_a,
+                               residual=(img, txt), gate=(i_g1, t_g1))
+        img_h, txt_h = linear_pair(self.img_mlp_0, F.norm_modulate(img, i_sc2, i_sh2),
+                                   self.txt_mlp_0, F.norm_modulate(txt, t_sc2, t_sh2), act="gelu")
+        img, txt = linear_pair(self.img_mlp_2, img_h, self.txt_mlp_2, txt_h,
+                               residual=(img, txt), gate=(i_g2, t_g2))
         return img, txt
 
 

@@ -115,10 +115,13 @@ class _NormModulate(torch.autograd.Function):
         N.check(code, "norm_modulate_fwd")
         ctx.save_for_backward(x, scale_v, weight, bias, mean, rstd)
         ctx.meta = (B, L, D, stride, rms, scale is not None, shift is not None)
+        ctx.set_materialize_grads(False)
         return y
 
     @staticmethod
     def backward(ctx, dy):
+        if dy is None:          # the consumer had no gradient for this input (an unused stream)
+            return None, None, None, None, None, None, None
         x, scale_v, weight, bias, mean, rstd = ctx.saved_tensors
         B, L, D, stride, rms, has_scale, has_shift = ctx.meta
         dy = _c(dy)
@@ -844,6 +847,138 @@ def linear(x, w, bias=None, lora=None, act=None, residual=None, gate=None, wt=No
     if gate is not None or residual is not None:
         y = R.gate_residual(residual, y, gate)
     return y
+
+
+class _FusedLinearPair(torch.autograd.Function):
+    """Two fused linears with the same shape of weight (the image and the text stream of a dual-stream
+    block): y_i = [residual_i + gate_i *] act(x_i W_i^T + b_i + s_i (x_i A_i^T) B_i^T). The two main GEMMs
+    share one launch in the forward, and the two input-gradient GEMMs one in the backward
+    (``gemm_native_pair``); everything else is what ``_FusedLinear`` does per stream. Only for the
+    native path with rank-16/32/64 adapters (or none) on both streams; ``linear_pair`` checks that."""
+
+    @staticmethod
+    def forward(ctx, act, x0, w0, b0, la0, lb0, s0, res0, gate0, x1, w1, b1, la1, lb1, s1, res1, gate1):
+        streams = ((x0, w0, b0, la0, lb0, s0, res0, gate0), (x1, w1, b1, la1, lb1, s1, res1, gate1))
+        need_any = (any(ctx.needs_input_grad[1:6]), any(ctx.needs_input_grad[9:14]))
+        kws, saved, metas = [], [], []
+        for i, (x, w, b, la, lb, sc, res, gate) in enumerate(streams):
+            shp = x.shape
+            K, Nn = shp[-1], w.shape[0]
+            x2 = _c(x).view(-1, K)
+            M, L = x2.shape[0], shp[-2]
+            r = 0 if la is None else la.shape[0]
+            pre = torch.empty(M, Nn, dtype=x.dtype, device=x.device) if (act is not None and need_any[i]) else None
+            res2 = None if res is None else _c(res).view(-1, Nn)
+            gate_v = _mod_view(gate, Nn)[0] if gate is not None else None
+            h = skinny_gemm(x2, la, alpha=sc) if r else None
+            kws.append(dict(a=x2, b=w, bias=b, lora_h=h, lora_b=lb if r else None, act=act, pre_out=pre,
+                            residual=res2, gate=gate_v, rows_per_batch=L, pdl=_pdl_ok()))
+            saved += [x2, w, la, lb, h, pre, gate_v]
+            metas.append((shp, Nn, L, sc, res is not None, b is not None))
+        y0, y1 = gemm_native_pair(kws[0], kws[1])
+        ctx.save_for_backward(*saved)
+        ctx.meta = (act, metas)
+        ctx.set_materialize_grads(False)       # an unused output (None gradient) costs nothing in backward
+        return y0.view(*metas[0][0][:-1], metas[0][1]), y1.view(*metas[1][0][:-1], metas[1][1])
+
+    @staticmethod
+    def backward(ctx, dy0, dy1):
+        act, metas = ctx.meta
+        sv = ctx.saved_tensors
+        lib = N.require()
+        need = ctx.needs_input_grad
+        parts = []
+        kws = []
+        for i, dy in enumerate((dy0, dy1)):
+            if dy is None:
+                kws.append(None)
+                parts.append(None)
+                continue
+            x2, w, la, lb, h, pre, gate_v = sv[7 * i: 7 * i + 7]
+            shp, Nn, L, sc, has_res, has_bias = metas[i]
+            M, K = x2.shape
+            dy2 = _c(dy).view(M, Nn)
+            d_res = dy.reshape(*shp[:-1], Nn) if has_res else None
+            if gate_v is not None:
+                g = torch.empty_like(dy2)
+                N.check(lib.eri_gate_residual(None, dy2.data_ptr(), gate_v.data_ptr(), g.data_ptr(), M, Nn, L,
+                                              gate_v.stride(0), N.stream_ptr()), "gate_bwd")
+                dy2 = g
+            if act is not None:
+                g = torch.empty_like(dy2)
+                N.check(lib.eri_act_bwd(dy2.data_ptr(), pre.data_ptr(), g.data_ptr(), dy2.numel(),
+                                        0 if act == "gelu" else 1, N.stream_ptr()), "act_bwd")
+                dy2 = g
+            r = 0 if la is None else la.shape[0]
+            ts = la_t = None
+            if r:
+                lb_t, la_t = _lora_transposed(lb), _lora_transposed(la)
+                ts = skinny_gemm(dy2, lb_t, alpha=sc)
+            kws.append(dict(a=dy2, b=w, b_mn=True, lora_h=ts, lora_b=la_t, pdl=_pdl_ok()))
+            parts.append((dy2, ts, d_res))
+        base = (1, 9)                      # positions of x0 / x1 among the forward's arguments
+        dxs = [None, None]
+        want = [need[base[0]] and kws[0] is not None, need[base[1]] and kws[1] is not None]
+        if all(want):
+            dxs = list(gemm_native_pair(kws[0], kws[1]))
+        else:
+            for i in range(2):
+                if want[i]:
+                    dxs[i] = gemm_native(**kws[i])
+        grads = [None]
+        for i in range(2):
+            if parts[i] is None:
+                grads += [None] * 8
+                continue
+            x2, w, la, lb, h, pre, gate_v = sv[7 * i: 7 * i + 7]
+            shp, Nn, L, sc, has_res, has_bias = metas[i]
+            dy2, ts, d_res = parts[i]
+            nd = need[base[i]: base[i] + 5]
+            dw = dbias = da = db = None
+            if nd[1]:
+                if _ACCUM_INTO_GRAD and w.grad is not None and w.grad.dtype == x2.dtype and w.grad.is_contiguous():
+                    wgrad(dy2, x2, accum=w.grad)
+                else:
+                    dw = wgrad(dy2, x2)
+            if has_bias and nd[2]:
+                dbias = dy2.sum(0)
+            if la is not None and nd[3]:
+                if _ACCUM_INTO_GRAD and la.grad is not None and la.grad.dtype == x2.dtype:
+                    lora_wgrad(x2, ts, out=la.grad, transpose_out=True, accumulate=True)
+                else:
+                    da = lora_wgrad(x2, ts, transpose_out=True)
+            if la is not None and nd[4]:
+                if _ACCUM_INTO_GRAD and lb.grad is not None and lb.grad.dtype == h.dtype:
+                    lora_wgrad(dy2, h, out=lb.grad, accumulate=True)
+                else:
+                    db = lora_wgrad(dy2, h)
+            dx = None if dxs[i] is None else dxs[i].view(shp)
+            grads += [dx, dw, dbias, da, db, None, d_res, None]
+        return tuple(grads)
+
+
+def linear_pair(x0, lin0, x1, lin1, act=None):
+    """``lin_i`` = (w, bias, lora or None, residual or None, gate or None). Returns (y0, y1) of two fused
+    linears whose main GEMMs (and input-gradient GEMMs) share one launch when both run on the native path
+    with matching shapes; otherwise exactly ``linear`` twice."""
+    (w0, b0, lo0, r0, g0), (w1, b1, lo1, r1, g1) = lin0, lin1
+
+    def rank_ok(lo):
+        return lo is None or lo[0].shape[0] in (16, 32, 64)
+    ok = (_GEMM_GROUP and _GEMM_NATIVE == "native" and _native_ok(x0, w0, b0) and _native_ok(x1, w1, b1)
+          and w0.shape == w1.shape and x0.shape[-1] % 8 == 0 and rank_ok(lo0) and rank_ok(lo1)
+          and (lo0 is None) == (lo1 is None) and (lo0 is None or lo0[0].shape[0] == lo1[0].shape[0])
+          and (b0 is None) == (b1 is None)
+          and not (g0 is not None and g0.requires_grad) and not (g1 is not None and g1.requires_grad)
+          and x0.numel() // x0.shape[-1] >= 256 and x1.numel() // x1.shape[-1] >= 256
+          and gemm_supported(x0.numel() // x0.shape[-1], w0.shape[0], x0.shape[-1])
+          and gemm_supported(x1.numel() // x1.shape[-1], w1.shape[0], x1.shape[-1]))
+    if not ok:
+        return (linear(x0, w0, b0, lora=lo0, act=act, residual=r0, gate=g0),
+                linear(x1, w1, b1, lora=lo1, act=act, residual=r1, gate=g1))
+    a0, bb0, s0 = lo0 if lo0 is not None else (None, None, 1.0)
+    a1, bb1, s1 = lo1 if lo1 is not None else (None, None, 1.0)
+    return _FusedLinearPair.apply(act, x0, w0, b0, a0, bb0, float(s0), r0, g0, x1, w1, b1, a1, bb1, float(s1), r1, g1)
 
 
 _GLU_FUSED = os.environ.get("ERI_B200_GLU_FUSED", "1") == "1"

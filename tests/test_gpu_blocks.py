@@ -49,3 +49,61 @@ def test_fused_model_matches_library_path(dd, ds):
         a, b = g1[k], g2[k]
         e = (a - b).abs().max().item()
         assert e < 0.06 * b.abs().max().item() + 1e-5, (k, e, b.abs().max().item())
+
+
+def _double_block(group, full_ft=False, depth_single=1):
+    from eridiffusion_b200.adapters import AdapterConfig, inject_adapters
+    from eridiffusion_b200.models import build_model
+    from eridiffusion_b200.ops import functional as F
+    old = F._GEMM_GROUP
+    F._GEMM_GROUP = group
+    try:
+        torch.manual_seed(0)
+        dev = "cuda"
+        m = build_model("flux", device=dev, hidden=512, num_heads=4, depth_double=2, depth_single=depth_single,
+                        context_dim=256, vec_dim=64)
+        params = {}
+        if full_ft:
+            params = {n: p for n, p in m.named_parameters() if "double_blocks" in n and p.dim() == 2}
+        else:
+            m.requires_grad_(False)
+            ads = inject_adapters(m, AdapterConfig(rank=16, alpha=16, target=m.lora_targets()), seed=1)
+            g = torch.Generator(device=dev).manual_seed(5)
+            for path, a in sorted(ads.items()):
+                a.lora_B.data.copy_(torch.randn(a.lora_B.shape, device=dev, generator=g).mul_(0.05))
+                for p_n, p in a.named_parameters():
+                    params[f"{path}.{p_n}"] = p
+        g = torch.Generator(device=dev).manual_seed(6)
+        img = torch.randn(2, 1024, 64, device=dev, generator=g).bfloat16()
+        txt = torch.randn(2, 256, 256, device=dev, generator=g).bfloat16()
+        t = torch.tensor([0.3, 0.6], device=dev)
+        y = torch.randn(2, 64, device=dev, generator=g).bfloat16()
+        c0 = F.N.launch_count()
+        out = m(img, txt, t, y, torch.tensor([3.5, 3.5], device=dev))
+        w = torch.randn(out.shape, device=dev, generator=g).bfloat16()
+        (out.float() * w.float()).mean().backward()
+        n = F.N.launch_count() - c0
+        assert F.gemm_error_check() == 0
+        return out.float(), {k: p.grad.float().clone() for k, p in params.items() if p.grad is not None}, n
+    finally:
+        F._GEMM_GROUP = old
+
+
+@pytest.mark.parametrize("full_ft,depth_single", [(False, 1), (True, 1), (False, 0)])
+def test_grouped_stream_linears_match_separate_launches(full_ft, depth_single):
+    """Dual-stream blocks with the image and the text projection of each pair in one grouped launch
+    (forward GEMM and input-gradient GEMM) against the same blocks with one launch per projection.
+    Without single-stream blocks the last block's text output is unused: its gradient is None and the
+    paired backward runs the image stream alone."""
+    o1, g1, n1 = _double_block(True, full_ft, depth_single)
+    o0, g0, n0 = _double_block(False, full_ft, depth_single)
+    # two blocks x four projection pairs, one launch fewer per grouped pair in forward and in backward.
+    # LoRA: the first pair of the first block has no input gradient to compute (frozen input projections),
+    # and without single-stream blocks three text projections of the last block have no gradient at all.
+    # Full fine-tune: the gates are trainable, so only the un-gated pairs (qkv, mlp_0) group.
+    assert n0 - n1 == (8 if full_ft else 15 if depth_single else 12), (n0, n1)
+    assert (o1 - o0).abs().max().item() <= 0.02 * o0.abs().max().item()
+    assert g0.keys() == g1.keys() and len(g0) > 0
+    for k in g0:
+        e = (g1[k] - g0[k]).abs().max().item()
+        assert e <= 0.03 * g0[k].abs().max().item() + 1e-6, (k, e)
