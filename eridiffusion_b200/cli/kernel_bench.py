@@ -202,18 +202,29 @@ def bench_wgrad(small):
 def bench_elementwise(small):
     bw, fl, tag = peaks()
     B, L, D = 1, 4608, 3072
+    lib = F.N.require()
+    # both row kernels (rows resident in shared memory / in registers) at the step's size and at eight times it
+    for Bn in (1, 8):
+        xb = torch.randn(Bn, L, D, device="cuda").bfloat16()
+        modb = torch.randn(Bn, 2 * D, device="cuda").bfloat16()
+        shb, scb = modb.split(D, -1)
+        xg = xb.clone().requires_grad_()
+        for variant, name in ((1, "shared-memory rows"), (0, "register rows")):
+            if not hasattr(lib, "eri_norm_set_smem_variant"):
+                continue
+            prev = lib.eri_norm_set_smem_variant(variant)
+            t = timeit(lambda: F.norm_modulate(xb, scb, shb))
+            nb = 2 * xb.numel() * 2
+            yg = F.norm_modulate(xg, scb, shb)
+            go = torch.randn_like(yg)
+            tb = timeit(lambda: torch.autograd.grad(yg, xg, go, retain_graph=True))
+            nbb = 3 * xb.numel() * 2
+            print(f"norm_modulate [{Bn * L}x{D}] {name}: fwd {t*1e6:.1f} us {nb/t/bw:.2f}, "
+                  f"bwd (dx only) {tb*1e6:.1f} us {nbb/tb/bw:.2f} {tag}")
+            lib.eri_norm_set_smem_variant(prev)
     x = torch.randn(B, L, D, device="cuda").bfloat16()
     mod = torch.randn(B, 3 * D, device="cuda").bfloat16()
     sh, sc, g = mod.split(D, -1)
-    t = timeit(lambda: F.norm_modulate(x, sc, sh))
-    nb = 2 * x.numel() * 2
-    print(f"norm_modulate fwd [{L}x{D}]: {t*1e6:.1f} us  {nb/t/1e9:.0f} GB/s  {nb/t/bw:.2f} {tag}")
-    xg = x.clone().requires_grad_()
-    yg = F.norm_modulate(xg, sc, sh)
-    go = torch.randn_like(yg)
-    t = timeit(lambda: torch.autograd.grad(yg, xg, go, retain_graph=True))
-    nb = 3 * x.numel() * 2
-    print(f"norm_modulate bwd (dx only) [{L}x{D}]: {t*1e6:.1f} us  {nb/t/1e9:.0f} GB/s  {nb/t/bw:.2f} {tag}")
     F.set_backend("eager")
     t2 = timeit(lambda: R.norm_modulate(x, sc, sh))
     F.set_backend("fused")

@@ -36,7 +36,8 @@ namespace {
 struct FaParams {
   int B, H, Lq, Lk;
   float scale_log2;  // softmax scale * log2(e)
-  bf16* out;         // [B, Lq, H, DH]
+  bf16* out;         // [B, Lq, H, DH]; consecutive tokens are out_ld elements apart
+  long long out_ld;  // >= H * DH (larger when the output is a column block of a wider matrix)
   float* lse;        // [B, H, Lq] natural-log log-sum-exp (may be null)
   int* err;
   const float* kbias;  // MASK variant: [B, Lkb] additive key bias in log2 units (-1e30 = masked),
@@ -360,7 +361,7 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
     if (ok) {
       tc_fence_after();
       const float inv_l = 1.f / l;
-      bf16* orow = p.out + (((size_t)b * p.Lq + row) * p.H + h) * DH + half * (DH / 2);
+      bf16* orow = p.out + ((size_t)b * p.Lq + row) * p.out_ld + h * DH + half * (DH / 2);
 #pragma unroll 1
       for (int c = 0; c < DH / 64; ++c) {
         uint32_t r[32];
@@ -372,7 +373,7 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
             float v[8];
 #pragma unroll
             for (int i = 0; i < 8; ++i) v[i] = __uint_as_float(r[g * 8 + i]) * inv_l;
-            if (ERI_DBG_RANGE(p.out, (size_t)p.B * p.Lq * p.H * DH * 2, orow + c * 32 + g * 8, 16, 51))
+            if (ERI_DBG_RANGE(p.out, (((size_t)p.B * p.Lq - 1) * p.out_ld + (size_t)p.H * DH) * 2, orow + c * 32 + g * 8, 16, 51))
               *reinterpret_cast<bf16x8*>(orow + c * 32 + g * 8) = pack8(v);
           }
         }
@@ -428,8 +429,11 @@ int make_qkv_map(CUtensorMap* m, const void* ptr, int B, int L, int H, int DH) {
 }
 
 int fwd_entry(const void* q, const void* k, const void* v, void* out, float* lse, const float* kbias,
-              int B, int H, int Lq, int Lk, int DH, float scale, void* stream) {
+              int B, int H, int Lq, int Lk, int DH, float scale, void* stream, long long out_ld = 0) {
   if (DH != 64 && DH != 128) return -1;
+  if (out_ld == 0) out_ld = (long long)H * DH;
+  // rows are written as 16-byte words
+  if (out_ld < (long long)H * DH || out_ld % 8 || (((uintptr_t)out) & 15)) return -7;
   // Fewer than 128 keys (one mostly empty tile) need the key bias to blank the padding; queries are
   // tiled by 128 rows and a short last tile is simply not written back.
   if (Lq < 1 || Lk < 1 || (Lk < 128 && !kbias)) return -2;
@@ -446,7 +450,7 @@ int fwd_entry(const void* q, const void* k, const void* v, void* out, float* lse
   FaParams p;
   p.B = B; p.H = H; p.Lq = Lq; p.Lk = Lk;
   p.scale_log2 = scale * 1.4426950408889634f;
-  p.out = (bf16*)out; p.lse = lse; p.err = g_fa_err[dev];
+  p.out = (bf16*)out; p.out_ld = out_ld; p.lse = lse; p.err = g_fa_err[dev];
   p.kbias = kbias; p.Lkb = (Lk + BKV - 1) / BKV * BKV;
   cudaStream_t st = (cudaStream_t)stream;
   if (kbias) {
@@ -484,6 +488,14 @@ int eri_fa_check_error() {
 int eri_flash_attn_fwd(const void* q, const void* k, const void* v, void* out, float* lse, int B,
                        int H, int Lq, int Lk, int DH, float scale, void* stream) {
   return fwd_entry(q, k, v, out, lse, nullptr, B, H, Lq, Lk, DH, scale, stream);
+}
+
+// The same with the output's token stride given: out_ld elements between consecutive tokens (a
+// multiple of 8, at least H * DH), batches Lq * out_ld apart. Lets the attention write a column block
+// of a wider matrix (the attention half of a single-stream block's second linear's input) in place.
+int eri_flash_attn_fwd_ld(const void* q, const void* k, const void* v, void* out, float* lse, int B,
+                          int H, int Lq, int Lk, int DH, float scale, long long out_ld, void* stream) {
+  return fwd_entry(q, k, v, out, lse, nullptr, B, H, Lq, Lk, DH, scale, stream, out_ld);
 }
 
 // The same with an additive key bias: kbias [B, ceil(Lk/128)*128] fp32 in log2 units (the caller

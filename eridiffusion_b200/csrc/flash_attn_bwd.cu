@@ -46,7 +46,8 @@ constexpr int T = 128;  // tile edge (queries and keys)
 
 __global__ void fa_bwd_prep_kernel(const bf16* __restrict__ o, const bf16* __restrict__ dout,
                                    const float* __restrict__ lse, float* __restrict__ lse2,
-                                   float* __restrict__ delta, int B, int H, int Lq, int Lp, int DH) {
+                                   float* __restrict__ delta, int B, int H, int Lq, int Lp, int DH,
+                                   long long o_ld) {
   // 16 lanes per (b, h, l) row, one 16-byte load of O and of dO per lane per 128 columns
   const long long gid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   const long long rowid = gid >> 4;
@@ -57,9 +58,10 @@ __global__ void fa_bwd_prep_kernel(const bf16* __restrict__ o, const bf16* __res
   float acc = 0.f;
   if (l < Lq) {
     const size_t base = (((size_t)b * Lq + l) * H + h) * DH;
+    const size_t obase = ((size_t)b * Lq + l) * o_ld + (size_t)h * DH;   // O may be a column block
     for (int d = sub * 8; d < DH; d += 128) {
       float a[8], g[8];
-      unpack8(*reinterpret_cast<const bf16x8*>(o + base + d), a);
+      unpack8(*reinterpret_cast<const bf16x8*>(o + obase + d), a);
       unpack8(*reinterpret_cast<const bf16x8*>(dout + base + d), g);
 #pragma unroll
       for (int j = 0; j < 8; ++j) acc = fmaf(a[j], g[j], acc);
@@ -807,20 +809,23 @@ int launch_bwd(const CUtensorMap& q, const CUtensorMap& k, const CUtensorMap& v,
 }
 
 void launch_prep(const void* out, const void* dout, const float* lse, float* lse2, float* delta, int B,
-                 int H, int Lq, int Lp, int DH, cudaStream_t st) {
+                 int H, int Lq, int Lp, int DH, cudaStream_t st, long long out_ld = 0) {
+  if (out_ld == 0) out_ld = (long long)H * DH;
   const long long rows = (long long)B * H * Lp;
   const int block = 256;
   const long long grid = (rows * 16 + block - 1) / block;
   fa_bwd_prep_kernel<<<(unsigned)grid, block, 0, st>>>((const bf16*)out, (const bf16*)dout, lse, lse2,
-                                                       delta, B, H, Lq, Lp, DH);
+                                                       delta, B, H, Lq, Lp, DH, out_ld);
 }
 
 int bwd_entry(const void* dout, const void* q, const void* k, const void* v, const void* out,
               const float* lse, float* lse2, float* delta, void* dq, void* dk, void* dv,
-              const float* kbias, int B, int H, int Lq, int Lk, int DH, float scale, void* stream) {
+              const float* kbias, int B, int H, int Lq, int Lk, int DH, float scale, void* stream,
+              long long out_ld = 0) {
   if (DH != 64 && DH != 128) return -1;
   if (Lq < 1 || Lk < 1 || (Lk < 128 && !kbias)) return -2;
   if (kbias && (((uintptr_t)kbias) & 15)) return -6;
+  if (out_ld && (out_ld < (long long)H * DH || out_ld % 8 || (((uintptr_t)out) & 15))) return -7;
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return -3;
   if (!g_fab_err[dev]) {
@@ -833,7 +838,7 @@ int bwd_entry(const void* dout, const void* q, const void* k, const void* v, con
   if (make_map(&tq, q, B, Lq, H, DH) || make_map(&tk, k, B, Lk, H, DH) ||
       make_map(&tv, v, B, Lk, H, DH) || make_map(&td, dout, B, Lq, H, DH))
     return -4;
-  launch_prep(out, dout, lse, lse2, delta, B, H, Lq, Lp, DH, st);
+  launch_prep(out, dout, lse, lse2, delta, B, H, Lq, Lp, DH, st, out_ld);
   FaBwdParams p;
   p.B = B; p.H = H; p.Lq = Lq; p.Lk = Lk; p.Lp = Lp;
   p.scale = scale; p.scale_log2 = scale * 1.4426950408889634f;
@@ -876,6 +881,16 @@ int eri_flash_attn_bwd(const void* dout, const void* q, const void* k, const voi
                        void* stream) {
   return bwd_entry(dout, q, k, v, out, lse, lse2, delta, dq, dk, dv, nullptr, B, H, Lq, Lk, DH, scale,
                    stream);
+}
+
+// The same with the forward output's token stride given (see eri_flash_attn_fwd_ld); only the
+// row-sum preparation reads the forward output.
+int eri_flash_attn_bwd_ld(const void* dout, const void* q, const void* k, const void* v,
+                          const void* out, const float* lse, float* lse2, float* delta, void* dq,
+                          void* dk, void* dv, int B, int H, int Lq, int Lk, int DH, float scale,
+                          long long out_ld, void* stream) {
+  return bwd_entry(dout, q, k, v, out, lse, lse2, delta, dq, dk, dv, nullptr, B, H, Lq, Lk, DH, scale,
+                   stream, out_ld);
 }
 
 // The same with the additive key bias of eri_flash_attn_fwd_masked (the forward's lse already

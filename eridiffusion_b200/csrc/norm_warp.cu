@@ -239,13 +239,221 @@ __global__ void __launch_bounds__(BWD ? 256 : 384, 1) norm_rows_kernel(const Nor
   }
 }
 
+// Shared-memory-resident variant: one row buffer per warp and up to 32 warps per CTA, the passes read
+// the row from shared memory instead of holding it in registers as fp32. Thirty-two warps of ~60
+// registers instead of twelve of ~160: every row of a 4608-row problem is in flight at once (31 rows
+// per SM), and on long problems the issue slots are shared by eight warps per scheduler instead of
+// three, which is what the register-resident kernel above lacks (it issues 0.4 instructions per cycle
+// and scheduler). Statistics in one pass over values shifted by the row's first element (the variance
+// as E[(x-k)^2] - E[x-k]^2 does not cancel unless that element is a far outlier); the backward uses
+// dx = g*rstd + (x-mean)*(-c2*rstd^2) - c1*rstd with c2 = rstd^2 * mean(g*(x-mean)) folded in.
+template <bool BWD>
+__global__ void __launch_bounds__(1024, 1) norm_rows_smem_kernel(const NormArgs a) {
+  extern __shared__ __align__(128) uint8_t smem[];
+  constexpr int NT = BWD ? 2 : 1;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
+  const int D = a.D, nvec = D >> 3;
+  const uint32_t row_bytes = (uint32_t)D * 2u;
+  uint64_t* bar = reinterpret_cast<uint64_t*>(smem) + warp;
+  uint8_t* buf = smem + kBarBytes + (size_t)warp * NT * row_bytes;
+  if (lane == 0) {
+    mbar_init(bar, 1);
+    mbar_fence_init();
+  }
+  __syncwarp();
+  const int stride = gridDim.x * nwarps;
+  auto issue = [&](int row) {
+    mbar_expect_tx(bar, NT * row_bytes);
+    bulk_g2s(buf, a.x + (size_t)row * D, row_bytes, bar);
+    if (BWD) bulk_g2s(buf + row_bytes, a.dy + (size_t)row * D, row_bytes, bar);
+  };
+  int row = blockIdx.x * nwarps + warp;
+  if (lane == 0 && row < a.rows) issue(row);
+  const bf16x8* wv = a.weight ? reinterpret_cast<const bf16x8*>(a.weight) : nullptr;
+  const bf16x8* bv = a.bias ? reinterpret_cast<const bf16x8*>(a.bias) : nullptr;
+  const bf16x8* sx = reinterpret_cast<const bf16x8*>(buf);
+  const float inv_d = 1.f / (float)D;
+  const f32x2 zero2 = f2_pack(0.f, 0.f);
+  uint32_t phase = 0;
+  for (; row < a.rows; row += stride, phase ^= 1u) {
+    if (!mbar_wait(bar, phase)) {
+      if (lane == 0) atomicExch(a.err, 1);
+      break;
+    }
+    const int b = row / a.rows_per_batch;
+    const bf16x8* sc =
+        a.scale ? reinterpret_cast<const bf16x8*>(a.scale + (size_t)b * a.mod_stride) : nullptr;
+    bf16x8* orow = reinterpret_cast<bf16x8*>(a.out + (size_t)row * D);
+    if (!BWD) {
+      const bf16x8* sh =
+          a.shift ? reinterpret_cast<const bf16x8*>(a.shift + (size_t)b * a.mod_stride) : nullptr;
+      const float kshift = a.rms ? 0.f : __bfloat162float(reinterpret_cast<const bf16*>(buf)[0]);
+      const f32x2 k2 = f2_pack(kshift, kshift);
+      f32x2 s1a = zero2, s1b = zero2, s2a = zero2, s2b = zero2;
+#pragma unroll 4
+      for (int v = lane; v < nvec; v += 32) {
+        f32x2 p[4];
+        unpack8_f2(sx[v], p);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) p[j] = f2_sub(p[j], k2);
+        s1a = f2_add(s1a, f2_add(p[0], p[1]));
+        s1b = f2_add(s1b, f2_add(p[2], p[3]));
+        s2a = f2_fma(p[0], p[0], s2a);
+        s2b = f2_fma(p[1], p[1], s2b);
+        s2a = f2_fma(p[2], p[2], s2a);
+        s2b = f2_fma(p[3], p[3], s2b);
+      }
+      float lo, hi;
+      f2_unpack(f2_add(s1a, s1b), lo, hi);
+      const float m1 = warp_sum(lo + hi) * inv_d;
+      f2_unpack(f2_add(s2a, s2b), lo, hi);
+      const float m2 = warp_sum(lo + hi) * inv_d;
+      const float mean = a.rms ? 0.f : kshift + m1;
+      const float var = a.rms ? m2 : fmaxf(m2 - m1 * m1, 0.f);
+      const float rstd = rsqrtf(var + a.eps);
+      if (lane == 0) {
+        if (a.mean) a.mean[row] = mean;
+        if (a.rstd) a.rstd[row] = rstd;
+      }
+      const f32x2 a2 = f2_pack(rstd, rstd), b2 = f2_pack(-mean * rstd, -mean * rstd);
+#pragma unroll 2
+      for (int v = lane; v < nvec; v += 32) {
+        f32x2 o[4], t[4];
+        unpack8_f2(sx[v], o);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) o[j] = f2_fma(o[j], a2, b2);
+        if (wv) {
+          unpack8_f2(wv[v], t);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) o[j] = f2_mul(o[j], t[j]);
+        }
+        if (bv) {
+          unpack8_f2(bv[v], t);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) o[j] = f2_add(o[j], t[j]);
+        }
+        if (sc) {
+          unpack8_f2(sc[v], t);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) o[j] = f2_fma(o[j], t[j], o[j]);
+        }
+        if (sh) {
+          unpack8_f2(sh[v], t);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) o[j] = f2_add(o[j], t[j]);
+        }
+        orow[v] = pack8_f2(o);
+      }
+    } else {
+      const float mean = a.rms ? 0.f : a.mean[row];
+      const float rstd = a.rstd[row];
+      const f32x2 nm2 = f2_pack(-mean, -mean);
+      const bf16x8* sg = sx + nvec;
+      // pass 1: sum of g = dy * (1 + scale) * weight and of g * (x - mean)
+      f32x2 s1a = zero2, s1b = zero2, s2a = zero2, s2b = zero2;
+#pragma unroll 2
+      for (int v = lane; v < nvec; v += 32) {
+        f32x2 x[4], g[4], t[4];
+        unpack8_f2(sx[v], x);
+        unpack8_f2(sg[v], g);
+        if (sc) {
+          unpack8_f2(sc[v], t);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) g[j] = f2_fma(g[j], t[j], g[j]);
+        }
+        if (wv) {
+          unpack8_f2(wv[v], t);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) g[j] = f2_mul(g[j], t[j]);
+        }
+#pragma unroll
+        for (int j = 0; j < 4; ++j) x[j] = f2_add(x[j], nm2);
+        s1a = f2_add(s1a, f2_add(g[0], g[1]));
+        s1b = f2_add(s1b, f2_add(g[2], g[3]));
+        s2a = f2_fma(g[0], x[0], s2a);
+        s2b = f2_fma(g[1], x[1], s2b);
+        s2a = f2_fma(g[2], x[2], s2a);
+        s2b = f2_fma(g[3], x[3], s2b);
+      }
+      float lo, hi;
+      f2_unpack(f2_add(s1a, s1b), lo, hi);
+      const float c1 = a.rms ? 0.f : warp_sum(lo + hi) * inv_d;
+      f2_unpack(f2_add(s2a, s2b), lo, hi);
+      const float c2 = warp_sum(lo + hi) * inv_d * rstd;            // mean(g * xhat)
+      // dx = rstd * (g - c1 - xhat * c2) = g * rstd + (x - mean) * (-c2 * rstd^2) - c1 * rstd
+      const f32x2 ka = f2_pack(rstd, rstd), kb = f2_pack(-c2 * rstd * rstd, -c2 * rstd * rstd),
+                  kc = f2_pack(-c1 * rstd, -c1 * rstd);
+#pragma unroll 2
+      for (int v = lane; v < nvec; v += 32) {
+        f32x2 x[4], g[4], t[4];
+        unpack8_f2(sx[v], x);
+        unpack8_f2(sg[v], g);
+        if (sc) {
+          unpack8_f2(sc[v], t);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) g[j] = f2_fma(g[j], t[j], g[j]);
+        }
+        if (wv) {
+          unpack8_f2(wv[v], t);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) g[j] = f2_mul(g[j], t[j]);
+        }
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          x[j] = f2_fma(f2_add(x[j], nm2), kb, f2_fma(g[j], ka, kc));
+        orow[v] = pack8_f2(x);
+      }
+    }
+    __syncwarp();
+    if (lane == 0 && row + stride < a.rows) {
+      fence_proxy_async_smem();  // the warp's reads of the buffer precede the copy engine's writes
+      issue(row + stride);
+    }
+  }
+}
+
 int* g_norm_err = nullptr;
 int g_norm_sms = 0;
+
+// ERI_B200_NORM_SMEM=0 (or eri_norm_set_smem_variant(0)) keeps the register-resident kernel.
+int g_norm_smem = -1;
+bool norm_smem_variant() {
+  if (g_norm_smem < 0) {
+    const char* e = getenv("ERI_B200_NORM_SMEM");
+    g_norm_smem = (e && e[0] == '0') ? 0 : 1;
+  }
+  return g_norm_smem == 1;
+}
+
+template <bool BWD>
+int launch_rows_smem(const NormArgs& a, cudaStream_t st) {
+  constexpr int NT = BWD ? 2 : 1;
+  const int per_warp = NT * a.D * 2;
+  int warps = (216 * 1024 - kBarBytes) / per_warp;
+  if (warps > 32) warps = 32;
+  if (warps < 4) return -100;
+  const int smem = kBarBytes + warps * per_warp;
+  int grid = (a.rows + warps - 1) / warps;
+  if (grid > g_norm_sms) grid = g_norm_sms;
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(norm_rows_smem_kernel<BWD>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             216 * 1024) != cudaSuccess)
+      return -101;
+    configured = true;
+  }
+  norm_rows_smem_kernel<BWD><<<grid, warps * 32, smem, st>>>(a);
+  return (int)cudaGetLastError();
+}
 
 template <bool BWD>
 int launch_rows(const NormArgs& a, cudaStream_t st) {
   constexpr int NT = BWD ? 2 : 1;
   const int D = a.D;
+  if (norm_smem_variant()) {
+    const int code = launch_rows_smem<BWD>(a, st);
+    if (code != -100) return code;
+  }
   const int per_warp = kRingStages<BWD> * NT * D * 2;
   int warps = (200 * 1024 - kBarBytes) / per_warp;
   if (warps > (BWD ? 8 : 12)) warps = BWD ? 8 : 12;
@@ -286,6 +494,14 @@ int norm_setup() {
 }  // namespace
 
 extern "C" {
+
+// Chooses between the shared-memory-resident (1) and the register-resident (0) row kernels; returns
+// the previous choice.
+int eri_norm_set_smem_variant(int on) {
+  const int prev = norm_smem_variant() ? 1 : 0;
+  g_norm_smem = on ? 1 : 0;
+  return prev;
+}
 
 // 0, or 1 when a bounded wait for a row copy ran out (the word is cleared by the read).
 int eri_norm_check_error() {

@@ -21,6 +21,8 @@ _P, _I, _F = N.C.c_void_p, N.C.c_int, N.C.c_float
 N._SIGNATURES.update({
     "eri_flash_attn_fwd": [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _P],
     "eri_flash_attn_bwd": [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _P],
+    "eri_flash_attn_fwd_ld": [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, N.C.c_longlong, _P],
+    "eri_flash_attn_bwd_ld": [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, N.C.c_longlong, _P],
     "eri_flash_attn_fwd_masked": [_P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _P],
     "eri_flash_attn_bwd_masked": [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _P],
     "eri_flash_attn_fwd_pair": [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _P],
@@ -35,7 +37,8 @@ _MASKED = -1.0e30      # bias of a masked key: its probability is exactly zero, 
 
 
 def _bind(lib):
-    for name in ("eri_flash_attn_fwd", "eri_flash_attn_bwd", "eri_flash_attn_fwd_masked",
+    for name in ("eri_flash_attn_fwd", "eri_flash_attn_bwd", "eri_flash_attn_fwd_ld", "eri_flash_attn_bwd_ld",
+                 "eri_flash_attn_fwd_masked",
                  "eri_flash_attn_bwd_masked", "eri_flash_attn_fwd_pair", "eri_fa_check_error",
                  "eri_fa2_check_error", "eri_fa_bwd_check_error"):
         if hasattr(lib, name):
@@ -160,22 +163,42 @@ def key_bias(mask, B, Lk, device):
     return _with_tile_flags(rows)
 
 
+def _token_stride(t):
+    """Elements between consecutive tokens of a [B, L, H, Dh] view whose heads are packed (a column block
+    of a wider [B * L, ld] matrix); raises for any other layout."""
+    B, L, H, D = t.shape
+    ld = t.stride(1)
+    if t.stride(3) != 1 or t.stride(2) != D or ld < H * D or ld % 8 or (B > 1 and t.stride(0) != L * ld):
+        raise ValueError(f"flash attention: unsupported output strides {t.stride()} for shape {tuple(t.shape)}")
+    return ld
+
+
 def fwd(q, k, v, scale=None, out=None, kbias=None):
-    """Returns (out [B, Lq, H, Dh] bf16, lse [B, H, Lq] fp32). ``out``: optional contiguous
-    destination of q's shape (e.g. a buffer that peers can read). ``kbias``: key bias from
+    """Returns (out [B, Lq, H, Dh] bf16, lse [B, H, Lq] fp32). ``out``: optional destination of q's shape,
+    contiguous (e.g. a buffer that peers can read) or a column block of a wider row-major matrix. ``kbias``: key bias from
     ``key_bias`` (required when there are fewer than 128 keys)."""
     lib = N.require()
     _bind(lib)
     B, Lq, H, D = q.shape
     Lk = k.shape[1]
     scale = scale if scale is not None else 1.0 / math.sqrt(D)
+    ld = 0
     if out is None:
         out = torch.empty_like(q)
-    elif out.shape != q.shape or out.dtype != q.dtype or not out.is_contiguous():
-        raise ValueError("flash attention: out must be contiguous with q's shape and dtype")
+    elif out.shape != q.shape or out.dtype != q.dtype:
+        raise ValueError("flash attention: out must have q's shape and dtype")
+    elif not out.is_contiguous():
+        ld = _token_stride(out)
     lse = torch.empty(B, H, Lq, dtype=torch.float32, device=q.device)
     if kbias is None and Lk < 128:
         kbias = key_bias(None, B, Lk, q.device)
+    if ld:
+        if kbias is not None:
+            raise ValueError("flash attention: a strided output is not supported together with a key bias")
+        N.check(lib.eri_flash_attn_fwd_ld(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(),
+                                          lse.data_ptr(), B, H, Lq, Lk, D, scale, ld, N.stream_ptr()),
+                "flash_attn_fwd_ld")
+        return out, lse
     if kbias is not None:
         N.check(lib.eri_flash_attn_fwd_masked(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(),
                                               lse.data_ptr(), kbias.data_ptr(), B, H, Lq, Lk, D, scale,
@@ -205,6 +228,15 @@ def bwd(do, q, k, v, out, lse, scale=None, kbias=None):
     delta = torch.empty_like(lse2)
     if kbias is None and Lk < 128:
         kbias = key_bias(None, B, Lk, q.device)
+    if not out.is_contiguous():
+        if kbias is not None:
+            raise ValueError("flash attention: a strided forward output is not supported together with a key bias")
+        N.check(lib.eri_flash_attn_bwd_ld(do.data_ptr(), q.data_ptr(), k.data_ptr(), v.data_ptr(),
+                                          out.data_ptr(), lse.data_ptr(), lse2.data_ptr(),
+                                          delta.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(),
+                                          B, H, Lq, Lk, D, scale, _token_stride(out), N.stream_ptr()),
+                "flash_attn_bwd_ld")
+        return dq, dk, dv
     if kbias is not None:
         N.check(lib.eri_flash_attn_bwd_masked(do.data_ptr(), q.data_ptr(), k.data_ptr(), v.data_ptr(),
                                               out.data_ptr(), lse.data_ptr(), lse2.data_ptr(),

@@ -46,21 +46,22 @@ class _SingleStream(torch.autograd.Function):
         N.check(lib.eri_qknorm_rope_fwd(qkv.data_ptr(), N.ptr(qs), N.ptr(ks), N.ptr(cos), N.ptr(sin),
                                         q.data_ptr(), k.data_ptr(), v.data_ptr(), B, L, heads, Dh, L, 0,
                                         1e-6, 3 * D, D, N.stream_ptr()), "qknorm_rope_fwd")
-        o, lse = FA.fwd(q, k, v)
-        cat[:, :D].copy_(o.view(M, D))
+        # the attention writes its output straight into the left column block of the second linear's input
+        o, lse = FA.fwd(q, k, v, out=cat.view(B, L, D + Fm)[:, :, :D].unflatten(-1, (heads, Dh)))
         h2 = F.skinny_gemm(cat, a2, alpha=s2) if a2 is not None else None
         y = F.gemm_native(cat, w2, bias=b2, lora_h=h2, lora_b=bb2, residual=x2,
                           gate=gate_v, rows_per_batch=L, pdl=F._pdl_ok())
-        ctx.save_for_backward(xm2, qkv, pre, cat, q, k, v, o, lse, h1, h2, gate_v, w1, w2, a1, bb1, a2,
+        ctx.save_for_backward(xm2, qkv, pre, cat, q, k, v, lse, h1, h2, gate_v, w1, w2, a1, bb1, a2,
                               bb2, qs, ks, cos, sin)
         ctx.meta = (B, L, D, Fm, heads, Dh, s1, s2)
         return y.view(B, L, D)
 
     @staticmethod
     def backward(ctx, dy):
-        (xm2, qkv, pre, cat, q, k, v, o, lse, h1, h2, gate_v, w1, w2, a1, bb1, a2, bb2, qs, ks, cos,
+        (xm2, qkv, pre, cat, q, k, v, lse, h1, h2, gate_v, w1, w2, a1, bb1, a2, bb2, qs, ks, cos,
          sin) = ctx.saved_tensors
         B, L, D, Fm, heads, Dh, s1, s2 = ctx.meta
+        o = cat.view(B, L, D + Fm)[:, :, :D].unflatten(-1, (heads, Dh))    # the forward's attention output
         M = B * L
         dev, dt = dy.device, dy.dtype
         lib = N.require()

@@ -78,6 +78,26 @@ def test_flash_attention_into_caller_buffer():
     assert FA.check_error() == 0
 
 
+@pytest.mark.parametrize("B,L,H,D", [(1, 384, 2, 128), (2, 300, 4, 64)])
+def test_flash_output_as_column_block_of_a_wider_matrix(B, L, H, D):
+    """The forward writes its output into the left column block of a wider row-major matrix (the input of
+    a single-stream block's second linear) and the backward reads it there: bit-equal to the contiguous
+    path, and the columns to the right stay untouched."""
+    q, k, v = (mk(B, L, H, D, s) for s in (21, 22, 23))
+    go = mk(B, L, H, D, 24)
+    o_ref, lse_ref = FA.fwd(q, k, v)
+    wide = torch.full((B * L, H * D + 136), 7.0, device="cuda", dtype=torch.bfloat16)
+    view = wide.view(B, L, H * D + 136)[:, :, : H * D].unflatten(-1, (H, D))
+    o, lse = FA.fwd(q, k, v, out=view)
+    assert o.data_ptr() == wide.data_ptr() and torch.equal(o, o_ref) and torch.equal(lse, lse_ref)
+    assert (wide[:, H * D:] == 7.0).all()
+    for a, b in zip(FA.bwd(go, q, k, v, o_ref, lse_ref), FA.bwd(go, q, k, v, o, lse)):
+        assert torch.equal(a, b)
+    with pytest.raises(ValueError):                       # heads not packed inside a token
+        FA.fwd(q, k, v, out=torch.empty(B, H, L, D, device="cuda", dtype=torch.bfloat16).transpose(1, 2))
+    assert FA.check_error() == 0
+
+
 def _ref_masked(q, k, v, bias):
     """fp32 softmax(QK^T / sqrt(D) + bias[b, key]) V with autograd, bias [B, Lk] additive."""
     D = q.shape[-1]

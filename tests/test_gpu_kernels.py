@@ -50,13 +50,25 @@ def test_norm_modulate_fwd_bwd(rms, D):
     close(w.grad, wr.grad, 0.0, 1e-2, rel_to_max=1e-2)
 
 
+@pytest.mark.parametrize("variant", [1, 0])
 @pytest.mark.parametrize("rms", [False, True])
-@pytest.mark.parametrize("L,D", [(67, 256), (2500, 3072), (5000, 264), (700, 4096)])
-def test_norm_modulate_row_kernels(rms, L, D):
+@pytest.mark.parametrize("L,D", [(67, 256), (2500, 3072), (5000, 264), (700, 4096), (9000, 3072)])
+def test_norm_modulate_row_kernels(rms, L, D, variant):
     """Input-gradient-only case (frozen modulation and weight): the persistent warp-per-row
-    kernels fed by bulk copies; the long cases make every warp cycle its two-stage ring."""
+    kernels fed by bulk copies, rows resident in shared memory (variant 1) or in registers (0); the
+    long cases make every warp cycle its row buffers several times. The rows carry a mean of several
+    standard deviations, which the shifted one-pass statistics of variant 1 must survive."""
+    lib = F.N.require()
+    prev = lib.eri_norm_set_smem_variant(variant)
+    try:
+        _norm_rows_case(rms, L, D)
+    finally:
+        lib.eri_norm_set_smem_variant(prev)
+
+
+def _norm_rows_case(rms, L, D):
     B = 2
-    x = rnd(B, L, D).requires_grad_()
+    x = (rnd(B, L, D) + 4.0).bfloat16().requires_grad_()
     mod = rnd(B, 2 * D, scale=0.3)
     w = rnd(D, scale=0.5)
     sh, sc = mod.split(D, dim=-1)
