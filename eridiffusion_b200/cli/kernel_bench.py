@@ -250,9 +250,19 @@ def bench_optim(small):
     opt = AdamW8bit([p])
     opt.arena.grad.normal_()
     ss = F.sumsq(opt.arena.grad)
-    t = timeit(lambda: opt.step(grad_sumsq=ss, max_grad_norm=1.0))
     nb = opt.arena.numel * (2 + 2 + 2 + 1 + 1 + 1 + 1)
-    print(f"adamw8bit [{n/1e6:.0f}M params]: {t*1e6:.1f} us  {nb/t/1e9:.0f} GB/s  {nb/t/bw:.2f} {tag}")
+    lib = F.N.require()
+    for variant, name in ((1, "packed pairs"), (0, "element-wise")):
+        if not hasattr(lib, "eri_adamw8bit_set_pair_variant"):
+            continue
+        prev = lib.eri_adamw8bit_set_pair_variant(variant)
+        for sr in (True, False):
+            opt.stochastic_rounding = sr
+            t = timeit(lambda: opt.step(grad_sumsq=ss, max_grad_norm=1.0))
+            print(f"adamw8bit [{n/1e6:.0f}M params] {name}, stochastic rounding {'on' if sr else 'off'}: "
+                  f"{t*1e6:.1f} us  {nb/t/1e9:.0f} GB/s  {nb/t/bw:.2f} {tag}")
+        lib.eri_adamw8bit_set_pair_variant(prev)
+    opt.stochastic_rounding = True
     t = timeit(lambda: F.sumsq(opt.arena.grad, ss))
     print(f"sumsq: {t*1e6:.1f} us  {opt.arena.numel*2/t/1e9:.0f} GB/s")
 

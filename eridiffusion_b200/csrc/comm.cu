@@ -193,50 +193,28 @@ fused_dp_step_kernel(CommCtx c, FusedDpArgs a) {
 
   // phase 3: 8-bit AdamW on the shard, push new parameters to every rank
   if (finite && comm_ok) {
+    Adam8Consts k;
+    adam8_consts(k, a.beta1, a.beta2, a.eps, a.bc1, a.bc2, gs);
     for (long long blk = gwarp; blk < nblocks; blk += warps) {
       const long long e = blk * kBlock + lane * 8;
-      float p[8], g[8], m[8], v[8];
       bf16* own = reinterpret_cast<bf16*>(a.params.ptr[c.rank]) + shard_off + e;
-      unpack8(*reinterpret_cast<const bf16x8*>(own), p);
+      const uint4 pw = *reinterpret_cast<const uint4*>(own);
       const float4* gp = reinterpret_cast<const float4*>(a.reduced + e);
-      float4 g0 = gp[0], g1 = gp[1];
-      g[0] = g0.x; g[1] = g0.y; g[2] = g0.z; g[3] = g0.w; g[4] = g1.x; g[5] = g1.y; g[6] = g1.z; g[7] = g1.w;
-      const float ma = a.m_absmax[blk], va = a.v_absmax[blk];
-      uint2 mraw = *reinterpret_cast<const uint2*>(a.mq + e);
-      uint2 vraw = *reinterpret_cast<const uint2*>(a.vq + e);
-      const int8_t* mb = reinterpret_cast<const int8_t*>(&mraw);
-      const uint8_t* vb = reinterpret_cast<const uint8_t*>(&vraw);
-      float mmax = 0.f, vmax = 0.f;
-      float sv[8];                     // sqrt(v): shared by Adam's denominator and the code of v
-      const float inv_bc1 = 1.f / a.bc1, rsqrt_bc2 = rsqrtf(a.bc2), decay = 1.f - a.lr * a.weight_decay;
-#pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        m[j] = decode_m(mb[j], ma);
-        v[j] = decode_v(vb[j], va);
-        const float gj = g[j] * gs;
-        m[j] = a.beta1 * m[j] + (1.f - a.beta1) * gj;
-        v[j] = a.beta2 * v[j] + (1.f - a.beta2) * gj * gj;
-        mmax = fmaxf(mmax, fabsf(m[j]));
-        vmax = fmaxf(vmax, v[j]);
-        sv[j] = sqrtf(v[j]);
-        const float upd = __fdividef(m[j] * inv_bc1, sv[j] * rsqrt_bc2 + a.eps);
-        p[j] = p[j] * decay - a.lr * upd;
-      }
+      const float4 g0 = gp[0], g1 = gp[1];
+      const f32x2 g2[4] = {f2_pack(g0.x, g0.y), f2_pack(g0.z, g0.w), f2_pack(g1.x, g1.y), f2_pack(g1.z, g1.w)};
+      const uint2 mraw = *reinterpret_cast<const uint2*>(a.mq + e);
+      const uint2 vraw = *reinterpret_cast<const uint2*>(a.vq + e);
+      f32x2 m2[4], sv2[4], p2[4];
+      float mmax, vmax;
+      adam8_update8(k, g2, pw, mraw, vraw, a.m_absmax[blk], a.v_absmax[blk], a.lr, a.weight_decay, m2, sv2,
+                    p2, mmax, vmax);
       mmax = warp_max(mmax);
       vmax = warp_max(vmax);
-      const float im = mmax > 0.f ? 1.f / mmax : 0.f, siv = vmax > 0.f ? rsqrtf(vmax) : 0.f;
       uint2 mo, vo;
-      int8_t* mob = reinterpret_cast<int8_t*>(&mo);
-      uint8_t* vob = reinterpret_cast<uint8_t*>(&vo);
+      uint4 pq;
+      adam8_encode8(m2, sv2, p2, mmax, vmax, a.stochastic != 0, a.seed, (uint32_t)(shard_off + e), mo, vo, pq);
       bf16x8 po;
-      bf16* pb = reinterpret_cast<bf16*>(&po);
-#pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        mob[j] = encode_m(m[j], im);
-        vob[j] = encode_v_from_sqrt(sv[j], siv);
-        pb[j] = round_bf16(p[j], a.stochastic != 0,
-                           hash_u32(a.seed ^ (uint32_t)(shard_off + e + j) * 0x9E3779B9u));
-      }
+      po.u = pq;
       *reinterpret_cast<uint2*>(a.mq + e) = mo;
       *reinterpret_cast<uint2*>(a.vq + e) = vo;
       if (lane == 0) {

@@ -73,6 +73,7 @@ _SIGNATURES = {
     "eri_norm_modulate_bwd_warp": [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P],
     "eri_norm_check_error": [],
     "eri_norm_set_smem_variant": [C.c_int],
+    "eri_adamw8bit_set_pair_variant": [C.c_int],
     "eri_qknorm_rope_fwd": [_P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _I, _I, _P],
     "eri_qknorm_rope_bwd": [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F,
                             _I, _I, _I, _P],

@@ -244,7 +244,41 @@ def test_small_linear():
     close(y, yr, 0.03)
 
 
-def test_adamw8bit_kernel_matches_reference():
+@pytest.fixture(params=[1, 0], ids=["pair-kernel", "element-kernel"])
+def adamw8_variant(request):
+    """Both 8-bit AdamW kernels: packed pairs (the default) and the element-wise one."""
+    lib = F.N.require()
+    prev = lib.eri_adamw8bit_set_pair_variant(request.param)
+    yield request.param
+    lib.eri_adamw8bit_set_pair_variant(prev)
+
+
+def test_adamw8bit_stochastic_rounding_is_unbiased(adamw8_variant):
+    """One step from p = 1 with a constant gradient moves every element to 1 - 2^-10, a quarter of the
+    way down to the next bf16 value (1 - 2^-8): round-to-nearest leaves all of them at 1, stochastic
+    rounding puts a quarter of them on the lower value, so that the mean keeps the update."""
+    from eridiffusion_b200.optim import AdamW8bit
+    n = 256 * 1024
+    for stochastic in (False, True):
+        p = [torch.nn.Parameter(torch.ones(n, device="cuda", dtype=torch.bfloat16))]
+        opt = AdamW8bit(p, lr=2.0 ** -10, weight_decay=0.0, stochastic_rounding=stochastic)
+        opt.arena.grad.fill_(1.0)
+        opt.step()
+        got = opt.arena.data[:n].float()
+        if not stochastic:
+            assert (got == 1.0).all()
+            continue
+        lower = (got == 1.0 - 2.0 ** -8)
+        assert ((got == 1.0) | lower).all()
+        frac = lower.float().mean().item()
+        assert abs(frac - 0.25) < 0.01, frac                       # sigma = 0.00085
+        assert abs(got.mean().item() - (1.0 - 2.0 ** -10)) < 4e-5
+        # neighbouring elements share one hash (its two halves): they must still be independent
+        both = (lower[0::2] & lower[1::2]).float().mean().item()
+        assert abs(both - 0.0625) < 0.005, both
+
+
+def test_adamw8bit_kernel_matches_reference(adamw8_variant):
     from eridiffusion_b200.optim import AdamW8bit
     torch.manual_seed(0)
     p1 = [torch.nn.Parameter(rnd(1000, 33)), torch.nn.Parameter(rnd(4099, seed=1))]
@@ -267,7 +301,7 @@ def test_adamw8bit_kernel_matches_reference():
     assert abs(ss.sqrt().item() - o1.arena.grad.float().norm().item()) < 1e-2 * ss.sqrt().item()
 
 
-def test_adamw8bit_moments_track_fp32_adamw_over_hundreds_of_steps():
+def test_adamw8bit_moments_track_fp32_adamw_over_hundreds_of_steps(adamw8_variant):
     """The 8-bit kernel (fast-math build, shared square root, magic-number rounding) against a plain
     fp32 AdamW over 300 steps of a gradient stream with a persistent component: the moments stay
     within the quantisation error of their block and the parameter trajectory does not drift."""
