@@ -540,6 +540,7 @@ ENV_VARS = {
     "ERI_B200_ATTN_HEAD_PAD": "1 | 0: head sizes other than 64 / 128 (below 128) zero-padded onto the native attention kernels",
     "ERI_B200_PAIR_MIN_TILES": "GEMMs with at most this many 256 x 256 tiles use the one-CTA kernel's 128-column tiles (default 36)",
     "ERI_B200_NORM_SMEM": "1 | 0: norm + modulate rows resident in shared memory (32 warps per SM) or in registers",
+    "ERI_B200_ADAMW8_PAIR": "1 | 0: 8-bit AdamW on packed fp32 pairs (default) or the element-wise kernel",
     "ERI_B200_GEMM_GROUP": "1 | 0: image and text projection of a dual-stream block in one grouped launch of the two-CTA GEMM",
     "ERI_B200_GATHER_JOIN": "1: copy clusters of a gather-fused GEMM take tiles after their last slab (default 0)",
     "ERI_B200_ZERO3_FUSED_RS": "1 | 0: ZeRO-3 weight-gradient reduce-scatter in the dW GEMM's epilogue",
