@@ -969,7 +969,6 @@ def linear_pair(x0, lin0, x1, lin1, act=None):
           and w0.shape == w1.shape and x0.shape[-1] % 8 == 0 and rank_ok(lo0) and rank_ok(lo1)
           and (lo0 is None) == (lo1 is None) and (lo0 is None or lo0[0].shape[0] == lo1[0].shape[0])
           and (b0 is None) == (b1 is None)
-          and not (g0 is not None and g0.requires_grad) and not (g1 is not None and g1.requires_grad)
           and x0.numel() // x0.shape[-1] >= 256 and x1.numel() // x1.shape[-1] >= 256
           and gemm_supported(x0.numel() // x0.shape[-1], w0.shape[0], x0.shape[-1])
           and gemm_supported(x1.numel() // x1.shape[-1], w1.shape[0], x1.shape[-1]))
@@ -978,6 +977,11 @@ def linear_pair(x0, lin0, x1, lin1, act=None):
                 linear(x1, w1, b1, lora=lo1, act=act, residual=r1, gate=g1))
     a0, bb0, s0 = lo0 if lo0 is not None else (None, None, 1.0)
     a1, bb1, s1 = lo1 if lo1 is not None else (None, None, 1.0)
+    if (g0 is not None and g0.requires_grad) or (g1 is not None and g1.requires_grad):
+        # trainable modulation: the gates stay outside the GEMM epilogue so that their gradients are produced
+        y0, y1 = _FusedLinearPair.apply(act, x0, w0, b0, a0, bb0, float(s0), None, None,
+                                        x1, w1, b1, a1, bb1, float(s1), None, None)
+        return gate_residual(r0, y0, g0), gate_residual(r1, y1, g1)
     return _FusedLinearPair.apply(act, x0, w0, b0, a0, bb0, float(s0), r0, g0, x1, w1, b1, a1, bb1, float(s1), r1, g1)
 
 

@@ -100,8 +100,8 @@ def test_grouped_stream_linears_match_separate_launches(full_ft, depth_single):
     # two blocks x four projection pairs, one launch fewer per grouped pair in forward and in backward.
     # LoRA: the first pair of the first block has no input gradient to compute (frozen input projections),
     # and without single-stream blocks three text projections of the last block have no gradient at all.
-    # Full fine-tune: the gates are trainable, so only the un-gated pairs (qkv, mlp_0) group.
-    assert n0 - n1 == (8 if full_ft else 15 if depth_single else 12), (n0, n1)
+    # Full fine-tune: all four pairs group as well (trainable gates are applied outside the GEMM in both paths).
+    assert n0 - n1 == (16 if full_ft else 15 if depth_single else 12), (n0, n1)
     assert (o1 - o0).abs().max().item() <= 0.02 * o0.abs().max().item()
     assert g0.keys() == g1.keys() and len(g0) > 0
     for k in g0:
