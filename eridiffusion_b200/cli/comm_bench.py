@@ -213,6 +213,47 @@ def bench_zero3(a, pg, rank, world, dev):
                               "fused_reduce_scatter": bool(z3.fused_rs), "n_copy": a.n_copy, "gemm_peak": tag,
                               "status": z3.comm.status(), "gemm_err": F.gemm_error_check()}))
         zl.weight.requires_grad_(False)
+    # A stack: three MLPs (3072 -> 12288 -> 3072) forward and backward as one step, with the next layer's slabs
+    # pulled by the copy engines while the current GEMM runs (prefetch), and without.
+    torch.manual_seed(1)
+    layers = []
+    for i in range(6):
+        k_in, n_out = (3072, 12288) if i % 2 == 0 else (12288, 3072)
+        zl = Zero3Linear(Linear(k_in, n_out, bias=False, device=dev), z3)
+        shard = z3.arena_alloc(zl.weight.numel(), torch.bfloat16, dev).view_as(zl.weight)
+        shard.copy_(zl.weight.data)
+        zl.weight.data = shard
+        zl.weight.requires_grad_(True)
+        layers.append(zl)
+    z3.barrier()
+    x = torch.randn(1, M, 3072, device=dev).bfloat16()
+    dy = torch.randn(1, M, 3072, device=dev).bfloat16()
+
+    def step():
+        z3.begin_step()
+        h = x.clone().requires_grad_()
+        y = h
+        for zl in layers:
+            zl.weight.grad = None
+            y = zl(y)
+        y.backward(dy)
+
+    res = {}
+    for on in (True, False):
+        z3.prefetch = on and world > 1 and z3.prefetch_stream is not None
+        step()                                    # records the order for the following steps
+        n0 = z3.prefetched_launches
+        res[on] = timed(step)
+        res[(on, "n")] = z3.prefetched_launches - n0
+    z3.begin_step()
+    flops = 3 * 6 * 2.0 * M * 3072 * 12288
+    link_bytes = 2 * 6 * (world - 1) / world * 3072 * 12288 * 2 + 6 * (world - 1) / world * 3072 * 12288 * 2
+    if rank == 0:
+        print(json.dumps({"what": "zero3 stack of six linears (3072 <-> 12288) forward + backward as one step", "world": world,
+                          "prefetch_ms": round(res[True], 4), "no_prefetch_ms": round(res[False], 4),
+                          "prefetched_launches_timed": res[(True, "n")],
+                          **roofline_fields(flops, link_bytes, res[True], 0),
+                          "status": z3.comm.status(), "gemm_err": F.gemm_error_check()}))
 
 
 def bench_ulysses(a, pg, rank, world, dev):

@@ -543,6 +543,7 @@ ENV_VARS = {
     "ERI_B200_ADAMW8_PAIR": "1 | 0: 8-bit AdamW on packed fp32 pairs (default) or the element-wise kernel",
     "ERI_B200_GEMM_GROUP": "1 | 0: image and text projection of a dual-stream block in one grouped launch of the two-CTA GEMM",
     "ERI_B200_GATHER_JOIN": "1: copy clusters of a gather-fused GEMM take tiles after their last slab (default 0)",
+    "ERI_B200_ZERO3_PREFETCH": "1 | 0: ZeRO-3 next-layer prefetch (copy engines pull layer i + 1's shards while GEMM i runs)",
     "ERI_B200_ZERO3_FUSED_RS": "1 | 0: ZeRO-3 weight-gradient reduce-scatter in the dW GEMM's epilogue",
     "ERI_B200_ZERO3_MOD": "native | nccl: collectives of the ZeRO-3 conditioning-vector linears",
     "TRAIN_LOG_CSV": "per-step CSV path (step,loss,grad_norm,sec_per_it,alloc_mb,ckpt_path)",

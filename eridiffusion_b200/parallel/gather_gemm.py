@@ -63,7 +63,7 @@ class GatherPlan:
 
     @classmethod
     def rows(cls, rank, world, shard_ptrs, landing: torch.Tensor, along_k=False, n_copy=16,
-             rows_per_job=64, flag_rows=256):
+             rows_per_job=64, flag_rows=256, slab_flags=False):
         """landing [N, K]; shard_ptrs[p] -> peer p's [N/W, K] contiguous shard. One counter per
         ``flag_rows`` landing rows, so a tile (or K range) starts as soon as its own rows are
         there instead of waiting for a peer's whole slab."""
@@ -78,7 +78,9 @@ class GatherPlan:
         # hold every tile of a slab back until its last byte has landed.
         # Along K (dX = dY W) every tile walks all slabs, and each new counter costs its producer a
         # global load in the middle of the K loop: one counter per whole slab there.
-        for cand in ((per,) if along_k else ()) + (flag_rows, 128, 64):
+        # ``slab_flags``: one counter per slab in every case (copy-engine prefetch: a whole slab is one copy
+        # and every counter costs the host one stream memory write).
+        for cand in ((per,) if (along_k or slab_flags) else ()) + (flag_rows, 128, 64):
             if per % cand == 0 and cand % rows_per_job == 0:
                 flag_rows = cand
                 break
@@ -195,6 +197,31 @@ class GatherPlan:
                 raise RuntimeError(f"copy-engine gather failed with code {code}")
         return dict(n_copy=0, n_jobs=0, jobs=0, flags=self.flags.data_ptr(),
                     flag_target=self._targets_dev.data_ptr(), **self.kw)
+
+    def issue_engine(self, side_stream):
+        """Copy-engine gather on ``side_stream``: counters zeroed, one asynchronous copy per slab in ring
+        order followed by stream memory writes that set the slab's counters, then the "everything has
+        landed" counter. The caller orders ``side_stream`` behind the landing buffer's last reader."""
+        lib = N.require()
+        if not hasattr(lib.eri_peer_copy_flags, "_bound"):
+            lib.eri_peer_copy_flags.argtypes = [C.c_void_p, C.c_void_p, C.c_longlong, C.c_void_p, C.c_int,
+                                                C.c_uint, C.c_void_p]
+            lib.eri_peer_copy_flags.restype = C.c_int
+            lib.eri_peer_copy_flags._bound = True
+        with torch.cuda.stream(side_stream):
+            self.flags.zero_()
+        jobs = list(self.slabs) + [(0, 0, 0, self.n_slab_flags, 1)]
+        for src, dst, nbytes, f0, nfl in jobs:
+            code = lib.eri_peer_copy_flags(dst, src, nbytes, self.flags.data_ptr() + 4 * f0, nfl,
+                                           self.targets[f0], side_stream.cuda_stream)
+            if code:
+                raise RuntimeError(f"copy-engine gather failed with code {code}")
+
+    def engine_args(self):
+        """``gather=`` dict of a launch whose slabs were (or are being) delivered by ``issue_engine``: no
+        copy CTAs, the tiles only look at the counters."""
+        return dict(n_copy=0, n_jobs=0, jobs=0, flags=self.flags.data_ptr(),
+                    flag_target=self._targets_dev.data_ptr(), all_flag=self.n_slab_flags + 1, **self.kw)
 
     def bytes_from_peers(self):
         return self.remote_bytes

@@ -67,6 +67,14 @@ class Zero3Context:
         self._flip = 0
         self._plans = {}
         self.gathered_bytes = 0
+        # Next-layer prefetch: the order of the gathers of a step is recorded; from the second step on,
+        # while layer i's GEMM runs, the copy engines pull layer i + 1's slabs into the other landing
+        # buffer on a side stream, so that launch i + 1 has no copy CTAs and finds its counters set.
+        self.prefetch = os.environ.get("ERI_B200_ZERO3_PREFETCH", "1") == "1" and self.world > 1
+        self.prefetch_stream = torch.cuda.Stream(device=dev) if self.prefetch else None
+        self._seq, self._rec, self._pos, self._follow = [], [], 0, False
+        self._pf = self._pf_done = None
+        self.prefetched_launches = 0
 
     # allocator handed to ParamArena so that the shards live in peer-mapped memory
     def arena_alloc(self, n, dtype, device):
@@ -85,8 +93,62 @@ class Zero3Context:
         self._flip ^= 1
         return self.landing[i][: n * k].view(n, k), i
 
+    def begin_step(self):
+        """Marks the start of a step (forward + backward between two optimizer updates). The gathers of
+        the step that just ended become the order that the next one is expected to follow; nothing is
+        ever prefetched across this call, because the shards change under the optimizer."""
+        self._drain_prefetch()
+        if self._rec:
+            self._seq = self._rec
+        self._rec, self._pos, self._flip = [], 0, 0
+        self._follow = self.prefetch and bool(self._seq)
+
+    def _drain_prefetch(self):
+        if self._pf is not None:
+            # a prefetch nobody consumed still writes a landing buffer: the current stream waits for it
+            torch.cuda.current_stream().wait_event(self._pf_done)
+            self._pf = None
+
+    def _issue_prefetch(self, key, li):
+        ptr, n, k, along_k = key
+        pk = (key, li, "engine")
+        pl = self._plans.get(pk)
+        if pl is None:
+            off = ptr - self.heap.local_ptr
+            landing = self.landing[li][: n * k].view(n, k)
+            pl = GatherPlan.rows(self.rank, self.world, [p + off for p in self.heap.peer_ptrs], landing,
+                                 along_k=along_k, n_copy=self.n_copy, slab_flags=True)
+            self._plans[pk] = pl
+        # the other landing buffer's last reader is the GEMM launched before the current one: both are
+        # already on this stream, the copies start behind the earlier one
+        ev = torch.cuda.Event()
+        ev.record()
+        self.prefetch_stream.wait_event(ev)
+        pl.issue_engine(self.prefetch_stream)
+        self._pf_done = torch.cuda.Event()
+        self._pf_done.record(self.prefetch_stream)
+        self._pf = (key, li, pl)
+
     def plan(self, shard: torch.Tensor, n, k, along_k: bool):
         landing, li = self.next_landing(n, k)
+        skey = (shard.data_ptr(), n, k, along_k)
+        ready = None
+        if self._pf is not None:
+            if self._pf[0] == skey and self._pf[1] == li:
+                ready, self._pf = self._pf[2], None
+            else:
+                self._drain_prefetch()
+        if self._follow and (self._pos >= len(self._seq) or self._seq[self._pos] != skey):
+            self._follow = False                      # this step leaves the recorded order: no more prefetching
+        self._rec.append(skey)
+        self._pos += 1
+        if self._follow and self._pos < len(self._seq):
+            self._issue_prefetch(self._seq[self._pos], li ^ 1)
+        if ready is not None:
+            self.gathered_bytes += ready.bytes_from_peers()
+            self.prefetched_launches += 1
+            ready.prefetched = True
+            return ready, landing
         key = (shard.data_ptr(), n, k, along_k, li)
         pl = self._plans.get(key)
         if pl is None:
@@ -113,6 +175,8 @@ class Zero3Context:
         return r
 
     def gather_args(self, pl):
+        if getattr(pl, "prefetched", False):
+            return pl.engine_args()
         if self.copy_stream is not None:
             return pl.launch_args_engine(self.copy_stream)
         args = pl.launch_args()
@@ -369,6 +433,7 @@ class Zero3Sync:
         if self.world_size > 1 and self.n_shard < arena.numel:
             self.pg.broadcast(arena.data[self.n_shard:], 0)
         self.z3.barrier()
+        self.z3.begin_step()
 
     def reduce_grads(self):
         if self.world_size > 1 and self.n_shard < self.arena.numel:
@@ -389,3 +454,4 @@ class Zero3Sync:
 
     def gather_params(self):
         self.z3.barrier()          # all shards updated before anyone gathers for the next forward
+        self.z3.begin_step()

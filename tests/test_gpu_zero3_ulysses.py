@@ -110,6 +110,27 @@ def _worker_body(rank, world, port, q):
     tot2.backward()
     out["z3u_dx"] = _rel(x2.grad, x2r[rank].grad * world)
     out["z3u_dw"] = _rel(zl2.weight.grad, w2.grad[rank * 384:(rank + 1) * 384])
+    # next-layer prefetch: the same two layers as a repeated step (forward of both, backward of both). The
+    # first step records the order of the gathers, later steps have every gather but the step's first one
+    # delivered by the copy engines while the GEMM before it runs; results equal the unprefetched step's.
+    def step():
+        z3.begin_step()
+        xa = xs[rank].clone().requires_grad_()
+        ya = zl(xa, act="gelu")                       # [2, 128, 512]
+        yb = zl2(ya)                                  # [2, 128, 384 * world]
+        yb.float().pow(2).mean().backward()
+        return yb.detach().clone(), xa.grad.clone(), zl.weight.grad.clone(), zl2.weight.grad.clone()
+    zl.weight.grad = zl2.weight.grad = None
+    base = step()                                     # records the order; nothing prefetched yet
+    n0 = z3.prefetched_launches
+    got = None
+    for _ in range(3):
+        zl.weight.grad = zl2.weight.grad = None
+        got = step()
+    z3.begin_step()
+    torch.cuda.synchronize()
+    out["z3_prefetched"] = z3.prefetched_launches - n0   # 3 steps x (4 gathers - the first of the step)
+    out["z3_prefetch_diff"] = max(_rel(a, b) for a, b in zip(got, base))
     out["z3_status"] = z3.comm.status()
     out["gemm_err"] = F.gemm_error_check()
 
@@ -181,3 +202,5 @@ def test_zero3_and_ulysses_multi_gpu(world):
               "ul_fwd", "ul_dx", "ul_dw"):
         assert out[k] < 4e-2, (k, out)
     assert out["z3_pair_launches"] == 2, out          # unaligned slabs stay on the two-CTA kernel
+    # three steps, four gathers each, all but the first of a step delivered ahead by the copy engines
+    assert out["z3_prefetched"] == 9 and out["z3_prefetch_diff"] < 1e-3, out
