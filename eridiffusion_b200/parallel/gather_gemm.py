@@ -24,6 +24,29 @@ import torch
 from ..ops import _native as N
 
 
+class GatherOrder:
+    """Order of a step's weight gathers, recorded in one step and followed in the next (ZeRO-3 next-layer
+    prefetch). ``begin`` closes a step: what was recorded becomes the expected order. ``advance(key)``
+    takes the gather that is about to run and returns the key of the one expected AFTER it, or None when
+    the step has left the recorded order, the order ends here, or nothing has been recorded yet."""
+
+    def __init__(self):
+        self.seq, self.rec, self.pos, self.follow = [], [], 0, False
+
+    def begin(self, enabled=True):
+        if self.rec:
+            self.seq = self.rec
+        self.rec, self.pos = [], 0
+        self.follow = bool(enabled) and bool(self.seq)
+
+    def advance(self, key):
+        if self.follow and (self.pos >= len(self.seq) or self.seq[self.pos] != key):
+            self.follow = False                       # this step leaves the recorded order
+        self.rec.append(key)
+        self.pos += 1
+        return self.seq[self.pos] if (self.follow and self.pos < len(self.seq)) else None
+
+
 class GatherPlan:
     def __init__(self, rank: int, world: int, n_copy: int = 16, device=None, n_flags: int | None = None):
         self.rank, self.world, self.n_copy = rank, world, n_copy

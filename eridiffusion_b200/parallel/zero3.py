@@ -34,7 +34,7 @@ from ..models.layers import Linear, SmallLinear
 from ..ops import functional as F
 from ..ops import reference as R
 from .dist import ProcessGroup, ReduceOp
-from .gather_gemm import GatherPlan
+from .gather_gemm import GatherOrder, GatherPlan
 from .symm import Communicator, SymmetricHeap
 
 
@@ -72,7 +72,7 @@ class Zero3Context:
         # buffer on a side stream, so that launch i + 1 has no copy CTAs and finds its counters set.
         self.prefetch = os.environ.get("ERI_B200_ZERO3_PREFETCH", "1") == "1" and self.world > 1
         self.prefetch_stream = torch.cuda.Stream(device=dev) if self.prefetch else None
-        self._seq, self._rec, self._pos, self._follow = [], [], 0, False
+        self._order = GatherOrder()
         self._pf = self._pf_done = None
         self.prefetched_launches = 0
 
@@ -98,10 +98,8 @@ class Zero3Context:
         the step that just ended become the order that the next one is expected to follow; nothing is
         ever prefetched across this call, because the shards change under the optimizer."""
         self._drain_prefetch()
-        if self._rec:
-            self._seq = self._rec
-        self._rec, self._pos, self._flip = [], 0, 0
-        self._follow = self.prefetch and bool(self._seq)
+        self._flip = 0
+        self._order.begin(self.prefetch)
 
     def _drain_prefetch(self):
         if self._pf is not None:
@@ -138,12 +136,9 @@ class Zero3Context:
                 ready, self._pf = self._pf[2], None
             else:
                 self._drain_prefetch()
-        if self._follow and (self._pos >= len(self._seq) or self._seq[self._pos] != skey):
-            self._follow = False                      # this step leaves the recorded order: no more prefetching
-        self._rec.append(skey)
-        self._pos += 1
-        if self._follow and self._pos < len(self._seq):
-            self._issue_prefetch(self._seq[self._pos], li ^ 1)
+        nxt = self._order.advance(skey)
+        if nxt is not None:
+            self._issue_prefetch(nxt, li ^ 1)
         if ready is not None:
             self.gathered_bytes += ready.bytes_from_peers()
             self.prefetched_launches += 1

@@ -2,7 +2,7 @@
 slab, built on CPU tensors with made-up peer addresses (nothing is launched)."""
 import torch
 
-from eridiffusion_b200.parallel.gather_gemm import GatherPlan
+from eridiffusion_b200.parallel.gather_gemm import GatherOrder, GatherPlan
 
 
 def _ptrs(world, stride):
@@ -82,3 +82,30 @@ def test_cols_plan_row_groups_and_local_block():
     assert pl.local["mode"] == 3 and pl.local["ptr"] == src[rank] + rank * L * Cc * 2 and pl.local["ld"] == Cc
     j = pl.jobs_nl[0]
     assert j.row_bytes == Cc * 2 and j.src_stride == Cc * 2 and j.dst_stride == W * Cc * 2
+
+
+def test_gather_order_records_a_step_and_follows_it():
+    o = GatherOrder()
+    o.begin()
+    step = ["qkv", "proj", "mlp0", "mlp2", "mlp2'", "mlp0'", "proj'", "qkv'"]
+    assert [o.advance(k) for k in step] == [None] * 8          # first step: nothing recorded yet
+    o.begin()
+    # second step: every gather names its successor, the last one has none (the shards change after it)
+    assert [o.advance(k) for k in step] == step[1:] + [None]
+    # a step that leaves the order (a validation forward in between) stops following at once ...
+    o.begin()
+    got = [o.advance(k) for k in ["qkv", "proj", "other", "mlp0"]]
+    assert got == ["proj", "mlp0", None, None]
+    # ... and what it did becomes the next expectation
+    o.begin()
+    assert [o.advance(k) for k in ["qkv", "proj", "other", "mlp0"]] == ["proj", "other", "mlp0", None]
+    # a step longer than the recorded one: no successor beyond the record, no error
+    o.begin()
+    assert [o.advance(k) for k in ["qkv", "proj", "other", "mlp0", "extra"]] == ["proj", "other", "mlp0", None, None]
+    # switched off: records, never names a successor
+    o.begin(enabled=False)
+    assert [o.advance(k) for k in ["qkv", "proj"]] == [None, None]
+    # an empty step keeps the last recorded order
+    o.begin()
+    o.begin()
+    assert o.advance("qkv") == "proj"
