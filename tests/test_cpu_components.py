@@ -429,3 +429,37 @@ def test_key_bias_rows_are_followed_by_per_tile_flags():
     add = torch.zeros(1, 1, 1, 128); add[..., 5] = -1.0
     kb3 = FA.key_bias(add, 1, 128, torch.device("cpu"))
     assert abs(float(kb3[5]) + 1.4426950408889634) < 1e-6 and kb3[128:].view(torch.int32).tolist() == [1]
+
+
+def test_linear_pair_falls_back_to_two_linears_off_the_native_path():
+    """The image / text projection pair of a dual-stream block: without the native backend (CPU tensors), with
+    a layer that is not a plain Linear, or with LoRA dropout in training, it is exactly the two separate calls."""
+    import torch
+    from eridiffusion_b200.adapters import AdapterConfig, inject_adapters
+    from eridiffusion_b200.models.layers import Linear, linear_pair, _pair_spec
+    from eridiffusion_b200.ops import functional as F
+    torch.manual_seed(0)
+    a, b = Linear(32, 48, dtype=torch.float32), Linear(32, 48, dtype=torch.float32)
+    x0, x1 = torch.randn(2, 5, 32), torch.randn(2, 3, 32)
+    r0, r1 = torch.randn(2, 5, 48), torch.randn(2, 3, 48)
+    g0, g1 = torch.randn(2, 48), torch.randn(2, 48)
+    y0, y1 = linear_pair(a, x0, b, x1, act="gelu")
+    assert torch.equal(y0, a(x0, act="gelu")) and torch.equal(y1, b(x1, act="gelu"))
+    z0, z1 = linear_pair(a, x0, b, x1, residual=(r0, r1), gate=(g0, g1))
+    assert torch.equal(z0, a(x0, residual=r0, gate=g0)) and torch.equal(z1, b(x1, residual=r1, gate=g1))
+    # the functional form on CPU tensors is two fused linears as well
+    f0, f1 = F.linear_pair(x0, (a.weight, a.bias, None, r0, g0), x1, (b.weight, b.bias, None, r1, g1))
+    assert torch.allclose(f0, z0) and torch.allclose(f1, z1)
+    # which layers qualify for the grouped launch at all
+    assert _pair_spec(a) == (a.weight, a.bias, None)
+    holder = torch.nn.Module()
+    holder.lin = a
+    ads = inject_adapters(holder, AdapterConfig(rank=4, alpha=4, target=["lin$"], dropout=0.1), seed=0)
+    ad = next(iter(ads.values()))
+    ad.train()
+    assert _pair_spec(a) is None                     # dropout in training: the adapter's own forward runs
+    ad.eval()
+    spec = _pair_spec(a)
+    assert spec is not None and spec[2][0] is ad.lora_A and spec[2][2] == ad.scale
+    a.register_forward_hook(lambda m, i, o: o)
+    assert _pair_spec(a) is None                     # hooks must see their module's own call
