@@ -2,7 +2,7 @@
 the device, a handful of launches), one per hot kernel:
 
     python -m eridiffusion_b200.cli.profile_target gemm|gemm_lora|rank_stream|attn_fwd|attn_bwd|norm|qknorm|adamw|gemv|
-        elementwise|groupnorm|token_route|dequant|attn_masked|small_linear_bwd|slot_reduce|gemm_small_m
+        elementwise|groupnorm|token_route|dequant|attn_masked|small_linear_bwd|slot_reduce|gemm_small_m|gemm_group
 
 Meant to be run as ``ncu --set full --clock-control none -k regex:<kernel> -s 2 -c 1 ... python -m
 eridiffusion_b200.cli.profile_target <what>`` after the same command line exited 0 without ncu.
@@ -155,6 +155,21 @@ def main():
         for _ in range(iters):
             F.gemm_native(a1, b1)
             F.gemm_native(a2, b2)
+        assert F.gemm_error_check() == 0
+    elif what == "gemm_group":
+        # image (4096 tokens) and text (512 tokens) projection of a dual-stream block, 3072 -> 3072 with
+        # rank-16 adapters: one grouped launch, then the two separate launches (pair kernel for the
+        # image stream, one-CTA kernel for the text stream)
+        kws = []
+        for M in (4096, 512):
+            x, w, hh, lb = r(M, 3072), r(3072, 3072), r(M, 16), r(3072, 16)
+            kws.append(dict(a=x, b=w, bias=r(3072), lora_h=hh, lora_b=lb, residual=r(M, 3072), gate=r(1, 3072),
+                            rows_per_batch=M))
+        for _ in range(iters):
+            F.gemm_native_pair(kws[0], kws[1])
+        for _ in range(iters):
+            F.gemm_native(**kws[0])
+            F.gemm_native(**kws[1])
         assert F.gemm_error_check() == 0
     else:
         raise SystemExit(f"unknown target {what}")
