@@ -48,17 +48,36 @@ __device__ __forceinline__ void mma16816(float (&c)[4], uint32_t a0, uint32_t a1
 constexpr int kWarps = 8;
 
 // NT: 8-column tiles of the output (N = 8 * NT); U: 32-column steps whose loads are issued together.
+// One problem of a launch. A launch may carry two with the same K and N (the image and the text stream of a
+// dual-stream block): CTAs [0, ceil(M0 / 16)) work on the first, the rest on the second.
+struct RankProb {
+  const bf16* a;
+  long long lda;
+  const bf16* b;
+  long long ldb;
+  bf16* out;
+  int ldc, M;
+  float alpha;
+};
+
 template <int NT, int U>
 __global__ void __launch_bounds__(kWarps * 32)
-rank_stream_kernel(const bf16* __restrict__ a, long long lda, const bf16* __restrict__ b,
-                   long long ldb, bf16* __restrict__ out, int ldc, int M, int K, float alpha) {
+rank_stream_kernel(const RankProb p0, const RankProb p1, int grid0, int K) {
   constexpr int N = NT * 8;
+  const bool second = (int)blockIdx.x >= grid0;
+  const RankProb& pr = second ? p1 : p0;
+  const bf16* __restrict__ a = pr.a;
+  const bf16* __restrict__ b = pr.b;
+  bf16* __restrict__ out = pr.out;
+  const long long lda = pr.lda, ldb = pr.ldb;
+  const int ldc = pr.ldc, M = pr.M;
+  const float alpha = pr.alpha;
   __shared__ float red[kWarps][16][N + 1];
   // the GEMM that consumes this kernel's output may be scheduled now; it waits for this kernel's
   // completion only before it reads the output (programmatic dependent launch)
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
-  const int m0 = blockIdx.x * 16;
+  const int m0 = ((int)blockIdx.x - (second ? grid0 : 0)) * 16;
   // rows past the end read the last row (valid memory) and are never stored
   const int r0 = min(m0 + g, M - 1), r1 = min(m0 + g + 8, M - 1);
   const int nsteps = K >> 5;
@@ -132,6 +151,17 @@ rank_stream_kernel(const bf16* __restrict__ a, long long lda, const bf16* __rest
   }
 }
 
+int launch_rank(const RankProb& p0, const RankProb& p1, int grid0, int grid1, int N, int K, cudaStream_t st) {
+  const int grid = grid0 + grid1;
+  if (N == 16)
+    rank_stream_kernel<2, 4><<<grid, kWarps * 32, 0, st>>>(p0, p1, grid0, K);
+  else if (N == 32)
+    rank_stream_kernel<4, 4><<<grid, kWarps * 32, 0, st>>>(p0, p1, grid0, K);
+  else
+    rank_stream_kernel<8, 2><<<grid, kWarps * 32, 0, st>>>(p0, p1, grid0, K);
+  return (int)cudaGetLastError();
+}
+
 }  // namespace
 
 extern "C" {
@@ -143,18 +173,24 @@ int eri_gemm_rank_stream(const void* a, long long lda, const void* b, long long 
   if (!(N == 16 || N == 32 || N == 64) || M < 1 || K < 256 || K % 32 || lda % 8 || ldb % 8 || ldc % 2)
     return -100;
   if ((((uintptr_t)a | (uintptr_t)b) & 15) || ((uintptr_t)out & 3)) return -100;
-  cudaStream_t st = (cudaStream_t)stream;
-  const bf16* pa = (const bf16*)a;
-  const bf16* pb = (const bf16*)b;
-  bf16* po = (bf16*)out;
-  const int grid = (M + 15) / 16;
-  if (N == 16)
-    rank_stream_kernel<2, 4><<<grid, kWarps * 32, 0, st>>>(pa, lda, pb, ldb, po, ldc, M, K, alpha);
-  else if (N == 32)
-    rank_stream_kernel<4, 4><<<grid, kWarps * 32, 0, st>>>(pa, lda, pb, ldb, po, ldc, M, K, alpha);
-  else
-    rank_stream_kernel<8, 2><<<grid, kWarps * 32, 0, st>>>(pa, lda, pb, ldb, po, ldc, M, K, alpha);
-  return (int)cudaGetLastError();
+  const RankProb p{(const bf16*)a, lda, (const bf16*)b, ldb, (bf16*)out, ldc, M, alpha};
+  return launch_rank(p, p, (M + 15) / 16, 0, N, K, (cudaStream_t)stream);
+}
+
+// Two products with the same N and K in one launch (out_i = alpha_i * a_i b_i^T): the small second one (the
+// 512-token text stream) costs a few more CTAs instead of a launch of its own.
+int eri_gemm_rank_stream2(const void* a0, long long lda0, const void* b0, long long ldb0, void* out0, int ldc0,
+                          int M0, float alpha0, const void* a1, long long lda1, const void* b1, long long ldb1,
+                          void* out1, int ldc1, int M1, float alpha1, int N, int K, void* stream) {
+  if (!(N == 16 || N == 32 || N == 64) || M0 < 1 || M1 < 1 || K < 256 || K % 32 || lda0 % 8 || ldb0 % 8 || ldc0 % 2 ||
+      lda1 % 8 || ldb1 % 8 || ldc1 % 2)
+    return -100;
+  if ((((uintptr_t)a0 | (uintptr_t)b0 | (uintptr_t)a1 | (uintptr_t)b1) & 15) ||
+      (((uintptr_t)out0 | (uintptr_t)out1) & 3))
+    return -100;
+  const RankProb p0{(const bf16*)a0, lda0, (const bf16*)b0, ldb0, (bf16*)out0, ldc0, M0, alpha0};
+  const RankProb p1{(const bf16*)a1, lda1, (const bf16*)b1, ldb1, (bf16*)out1, ldc1, M1, alpha1};
+  return launch_rank(p0, p1, (M0 + 15) / 16, (M1 + 15) / 16, N, K, (cudaStream_t)stream);
 }
 
 }  // extern "C"

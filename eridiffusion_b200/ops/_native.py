@@ -109,6 +109,7 @@ _SIGNATURES = {
     "eri_gemm_skinny": [_P, _L, _P, _L, _P, _I, _I, _I, _I, _F, _P],
     "eri_gemm_skinny_check_error": [],
     "eri_gemm_rank_stream": [_P, _L, _P, _L, _P, _I, _I, _I, _I, _F, _P],
+    "eri_gemm_rank_stream2": [_P, _L, _P, _L, _P, _I, _I, _F, _P, _L, _P, _L, _P, _I, _I, _F, _I, _I, _P],
     "eri_gemm_tokred": [_P, _L, _P, _L, _P, _I, _I, _I, _I, _F, _I, _I, _L, _P],
     "eri_gemm_tokred_check_error": [],
     "eri_gemm_tokred_set_target": [_I],

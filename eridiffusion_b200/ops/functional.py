@@ -521,6 +521,26 @@ def skinny_gemm(a, b, alpha=1.0):
     return gemm_native(a, b, alpha=alpha)
 
 
+def skinny_gemm_pair(a0, b0, alpha0, a1, b1, alpha1):
+    """(alpha0 * a0 b0^T, alpha1 * a1 b1^T) for two rank-r products with the same K and r (the adapters of the
+    image and the text projection of a dual-stream block) in one launch of the streaming kernel; two
+    launches when the shapes do not allow it."""
+    lib = N.require()
+    if (_RANK_STREAM and _GEMM_GROUP and hasattr(lib, "eri_gemm_rank_stream2") and a0.shape[1] == a1.shape[1]
+            and b0.shape[0] == b1.shape[0] and all(t.stride(1) == 1 for t in (a0, b0, a1, b1))):
+        r, K = b0.shape[0], a0.shape[1]
+        o0 = torch.empty(a0.shape[0], r, dtype=torch.bfloat16, device=a0.device)
+        o1 = torch.empty(a1.shape[0], r, dtype=torch.bfloat16, device=a1.device)
+        code = lib.eri_gemm_rank_stream2(a0.data_ptr(), a0.stride(0), b0.data_ptr(), b0.stride(0), o0.data_ptr(), r,
+                                         a0.shape[0], float(alpha0), a1.data_ptr(), a1.stride(0), b1.data_ptr(),
+                                         b1.stride(0), o1.data_ptr(), r, a1.shape[0], float(alpha1), r, K,
+                                         N.stream_ptr())
+        if code != -100:
+            N.check(code, "gemm_rank_stream2")
+            return o0, o1
+    return skinny_gemm(a0, b0, alpha=alpha0), skinny_gemm(a1, b1, alpha=alpha1)
+
+
 def gemm_supported(M, Nn, K) -> bool:
     return M >= 128 and Nn >= 16 and K >= 8 and K % 8 == 0 and Nn % 8 == 0
 
@@ -870,11 +890,15 @@ class _FusedLinearPair(torch.autograd.Function):
             pre = torch.empty(M, Nn, dtype=x.dtype, device=x.device) if (act is not None and need_any[i]) else None
             res2 = None if res is None else _c(res).view(-1, Nn)
             gate_v = _mod_view(gate, Nn)[0] if gate is not None else None
-            h = skinny_gemm(x2, la, alpha=sc) if r else None
-            kws.append(dict(a=x2, b=w, bias=b, lora_h=h, lora_b=lb if r else None, act=act, pre_out=pre,
+            kws.append(dict(a=x2, b=w, bias=b, lora_h=None, lora_b=lb if r else None, act=act, pre_out=pre,
                             residual=res2, gate=gate_v, rows_per_batch=L, pdl=_pdl_ok()))
-            saved += [x2, w, la, lb, h, pre, gate_v]
+            saved += [x2, w, la, lb, None, pre, gate_v]
             metas.append((shp, Nn, L, sc, res is not None, b is not None))
+        if la0 is not None:
+            # both rank-r products in one launch, right before the grouped GEMM that consumes them
+            h0, h1 = skinny_gemm_pair(kws[0]["a"], la0, s0, kws[1]["a"], la1, s1)
+            kws[0]["lora_h"], kws[1]["lora_h"] = h0, h1
+            saved[4], saved[11] = h0, h1
         y0, y1 = gemm_native_pair(kws[0], kws[1])
         ctx.save_for_backward(*saved)
         ctx.meta = (act, metas)
@@ -910,12 +934,22 @@ class _FusedLinearPair(torch.autograd.Function):
                                         0 if act == "gelu" else 1, N.stream_ptr()), "act_bwd")
                 dy2 = g
             r = 0 if la is None else la.shape[0]
-            ts = la_t = None
+            lb_t = la_t = None
             if r:
                 lb_t, la_t = _lora_transposed(lb), _lora_transposed(la)
-                ts = skinny_gemm(dy2, lb_t, alpha=sc)
-            kws.append(dict(a=dy2, b=w, b_mn=True, lora_h=ts, lora_b=la_t, pdl=_pdl_ok()))
-            parts.append((dy2, ts, d_res))
+            kws.append(dict(a=dy2, b=w, b_mn=True, lora_h=None, lora_b=la_t, pdl=_pdl_ok()))
+            parts.append([dy2, None, d_res, lb_t, sc])
+        # Ts_i = s_i * dY_i B_i: one launch for both streams when both have a gradient, right before the
+        # grouped input-gradient GEMM
+        live = [i for i in range(2) if parts[i] is not None and parts[i][3] is not None]
+        if len(live) == 2:
+            t0, t1 = skinny_gemm_pair(parts[0][0], parts[0][3], parts[0][4], parts[1][0], parts[1][3], parts[1][4])
+            parts[0][1], parts[1][1] = t0, t1
+        else:
+            for i in live:
+                parts[i][1] = skinny_gemm(parts[i][0], parts[i][3], alpha=parts[i][4])
+        for i in live:
+            kws[i]["lora_h"] = parts[i][1]
         base = (1, 9)                      # positions of x0 / x1 among the forward's arguments
         dxs = [None, None]
         want = [need[base[0]] and kws[0] is not None, need[base[1]] and kws[1] is not None]
@@ -932,7 +966,7 @@ class _FusedLinearPair(torch.autograd.Function):
                 continue
             x2, w, la, lb, h, pre, gate_v = sv[7 * i: 7 * i + 7]
             shp, Nn, L, sc, has_res, has_bias = metas[i]
-            dy2, ts, d_res = parts[i]
+            dy2, ts, d_res = parts[i][:3]
             nd = need[base[i]: base[i] + 5]
             dw = dbias = da = db = None
             if nd[1]:

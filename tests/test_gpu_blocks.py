@@ -97,11 +97,14 @@ def test_grouped_stream_linears_match_separate_launches(full_ft, depth_single):
     paired backward runs the image stream alone."""
     o1, g1, n1 = _double_block(True, full_ft, depth_single)
     o0, g0, n0 = _double_block(False, full_ft, depth_single)
-    # two blocks x four projection pairs, one launch fewer per grouped pair in forward and in backward.
-    # LoRA: the first pair of the first block has no input gradient to compute (frozen input projections),
-    # and without single-stream blocks three text projections of the last block have no gradient at all.
-    # Full fine-tune: all four pairs group as well (trainable gates are applied outside the GEMM in both paths).
-    assert n0 - n1 == (16 if full_ft else 15 if depth_single else 12), (n0, n1)
+    # two blocks x four projection pairs. Per grouped pair one GEMM launch fewer in forward and one in backward
+    # (input gradient), and with adapters one rank-r launch fewer each way as well (both streams' x A^T, and
+    # both streams' dY B, in one launch).
+    # LoRA: the first pair of the first block has no input gradient to compute (frozen input projections):
+    # 16 + 8 + 7. Without single-stream blocks three text projections of the last block have no gradient at
+    # all: 16 + (1 + 4) + (1 + 3). Full fine-tune (no adapters; trainable gates are applied outside the GEMM in
+    # both paths): 8 + 8.
+    assert n0 - n1 == (16 if full_ft else 31 if depth_single else 25), (n0, n1)
     assert (o1 - o0).abs().max().item() <= 0.02 * o0.abs().max().item()
     assert g0.keys() == g1.keys() and len(g0) > 0
     for k in g0:

@@ -50,3 +50,29 @@ def test_rank_stream_strided_rows_and_fallback():
     out2 = F.skinny_gemm(a2, b2)
     ref2 = a2.float() @ b2.float().t()
     assert (out2.float() - ref2).abs().max().item() <= 2e-2 * ref2.abs().max().item() + 1e-3
+
+
+@pytest.mark.parametrize("M0,M1,N,K", [(4096, 512, 16, 3072), (301, 77, 32, 1056), (4096, 512, 64, 12288), (16, 5000, 16, 288)])
+def test_rank_stream_two_problems_in_one_launch(M0, M1, N, K):
+    """The adapters of the image and the text projection in one launch: each problem with its own operands,
+    scale and row tail; equal to the single-problem launches bit for bit."""
+    g = torch.Generator(device="cuda").manual_seed(M0 + M1 + N + K)
+    mk = lambda m: torch.randn(m, K, device="cuda", generator=g).bfloat16()
+    a0, a1 = mk(M0), mk(M1)
+    b0, b1 = (torch.randn(N, K, device="cuda", generator=g) / K ** 0.5).bfloat16(), \
+        (torch.randn(N, K, device="cuda", generator=g) / K ** 0.5).bfloat16()
+    c0 = NAT.launch_count()
+    o0, o1 = F.skinny_gemm_pair(a0, b0, 0.5, a1, b1, 2.0)
+    assert NAT.launch_count() == c0 + 1
+    _, r0 = _call(a0, b0, 0.5)
+    _, r1 = _call(a1, b1, 2.0)
+    assert torch.equal(o0, r0) and torch.equal(o1, r1)
+    ref1 = (a1.float() @ b1.float().t()) * 2.0
+    assert (o1.float() - ref1).abs().max().item() <= 1e-2 * ref1.abs().max().item() + 1e-3
+    # different K: two launches, same results
+    a2 = torch.randn(M1, K + 32, device="cuda", generator=g).bfloat16()
+    b2 = (torch.randn(N, K + 32, device="cuda", generator=g) / K ** 0.5).bfloat16()
+    p0, p2 = F.skinny_gemm_pair(a0, b0, 0.5, a2, b2, 1.0)
+    assert torch.equal(p0, r0)
+    ref2 = a2.float() @ b2.float().t()
+    assert (p2.float() - ref2).abs().max().item() <= 1e-2 * ref2.abs().max().item() + 1e-3
