@@ -541,6 +541,9 @@ ENV_VARS = {
     "ERI_B200_PAIR_MIN_TILES": "GEMMs with at most this many 256 x 256 tiles use the one-CTA kernel's 128-column tiles (default 36)",
     "ERI_B200_NORM_SMEM": "1 | 0: norm + modulate rows resident in shared memory (32 warps per SM) or in registers",
     "ERI_B200_ADAMW8_PAIR": "1 | 0: 8-bit AdamW on packed fp32 pairs (default) or the element-wise kernel",
+    "ERI_B200_MLP_FUSE": "1: dual-stream MLP pairs apply the activation derivative in the down-projection's input-gradient epilogue (measured slower; default 0)",
+    "ERI_B200_ACT_EPILOGUE": "1: activation + stored pre-activation in the GEMM epilogue during training (default 0: the GEMM writes the pre-activation, a separate pass applies the activation)",
+    "ERI_B200_SS_ACT_EPILOGUE": "1: single-stream blocks keep GELU (forward) and its derivative (backward) in GEMM epilogues (default 0: separate row-strided passes)",
     "ERI_B200_GEMM_GROUP": "1 | 0: image and text projection of a dual-stream block in one grouped launch of the two-CTA GEMM",
     "ERI_B200_GATHER_JOIN": "1: copy clusters of a gather-fused GEMM take tiles after their last slab (default 0)",
     "ERI_B200_ZERO3_PREFETCH": "1 | 0: ZeRO-3 next-layer prefetch (copy engines pull layer i + 1's shards while GEMM i runs)",

@@ -521,6 +521,37 @@ __global__ void act_bwd_kernel(const bf16* __restrict__ dy, const bf16* __restri
     reinterpret_cast<bf16x8*>(dx)[i] = pack8(g);
   }
 }
+// y[r, c] = act(x[r, c]) on row-strided [rows, cols] views.
+__global__ void act_fwd_rows_kernel(const bf16* __restrict__ x, long long ld_x, bf16* __restrict__ y, long long ld_y,
+                                    int rows, int cols, int mode) {
+  const int cv = cols >> 3;
+  const size_t n = (size_t)rows * cv;
+  for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+    const size_t row = i / cv;
+    const int c = (int)(i - row * cv) * 8;
+    float a[8];
+    unpack8(*reinterpret_cast<const bf16x8*>(x + row * ld_x + c), a);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) a[j] = mode == 0 ? gelu_tanh_f(a[j]) : silu_f(a[j]);
+    *reinterpret_cast<bf16x8*>(y + row * ld_y + c) = pack8(a);
+  }
+}
+// The same on row-strided views (a column block of a wider matrix), in place when dx == dy.
+__global__ void act_bwd_rows_kernel(const bf16* dy, long long ld_dy, const bf16* __restrict__ x, long long ld_x,
+                                    bf16* dx, long long ld_dx, int rows, int cols, int mode) {
+  const int cv = cols >> 3;
+  const size_t n = (size_t)rows * cv;
+  for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+    const size_t row = i / cv;
+    const int c = (int)(i - row * cv) * 8;
+    float a[8], g[8];
+    unpack8(*reinterpret_cast<const bf16x8*>(x + row * ld_x + c), a);
+    unpack8(*reinterpret_cast<const bf16x8*>(dy + row * ld_dy + c), g);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) g[j] *= mode == 0 ? gelu_tanh_grad_f(a[j]) : silu_grad_f(a[j]);
+    *reinterpret_cast<bf16x8*>(dx + row * ld_dx + c) = pack8(g);
+  }
+}
 // Gated linear units on h = [rows, 2F]: out = act(h[:, :F]) * h[:, F:] when act_first,
 // else h[:, :F] * act(h[:, F:]).  mode 0 = GELU(tanh) (GEGLU), 1 = SiLU (SwiGLU).
 __global__ void glu_fwd_kernel(const bf16* __restrict__ h, bf16* __restrict__ out, int rows, int F,
@@ -832,6 +863,23 @@ int eri_act_bwd(const void* dy, const void* x, void* dx, long long n, int mode, 
   if (n % 8 != 0) return -1;
   act_bwd_kernel<<<grid_for(n / 8, 256), 256, 0, (cudaStream_t)stream>>>(
       (const bf16*)dy, (const bf16*)x, (bf16*)dx, n / 8, mode);
+  ERI_LAUNCH_CHECK();
+}
+int eri_act_fwd_rows(const void* x, long long ld_x, void* y, long long ld_y, int rows, int cols, int mode,
+                     void* stream) {
+  if (cols % 8 || ld_x % 8 || ld_y % 8 || ((((uintptr_t)x | (uintptr_t)y) & 15) != 0)) return -1;
+  act_fwd_rows_kernel<<<grid_for((size_t)rows * cols / 8, 256), 256, 0, (cudaStream_t)stream>>>(
+      (const bf16*)x, ld_x, (bf16*)y, ld_y, rows, cols, mode);
+  ERI_LAUNCH_CHECK();
+}
+// dx[r, c] = dy[r, c] * act'(x[r, c]) on row-strided [rows, cols] views (strides in elements, multiples of 8;
+// 16-byte aligned bases); dx may be dy.
+int eri_act_bwd_rows(const void* dy, long long ld_dy, const void* x, long long ld_x, void* dx, long long ld_dx,
+                     int rows, int cols, int mode, void* stream) {
+  if (cols % 8 || ld_dy % 8 || ld_x % 8 || ld_dx % 8) return -1;
+  if ((((uintptr_t)dy | (uintptr_t)x | (uintptr_t)dx) & 15) != 0) return -1;
+  act_bwd_rows_kernel<<<grid_for((size_t)rows * cols / 8, 256), 256, 0, (cudaStream_t)stream>>>(
+      (const bf16*)dy, ld_dy, (const bf16*)x, ld_x, (bf16*)dx, ld_dx, rows, cols, mode);
   ERI_LAUNCH_CHECK();
 }
 int eri_glu_fwd(const void* h, void* out, int rows, int F, int mode, int act_first, void* stream) {

@@ -496,10 +496,36 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA_0, const __grid_consta
         if (it > 0) tma_store_wait_read<0>();
       }
       float sq = 0.f;
+      // The residual / stored pre-activation of a row chunk is fetched one chunk ahead: a 16-byte load per
+      // thread from its own row has nothing to overlap with when it is issued in the middle of the
+      // chunk's arithmetic, and with a short K loop (K = 3072) the epilogue is on the critical path.
+      const bf16* ex_res = (p.residual && row_ok) ? p.residual + (size_t)row * p.ldr : nullptr;
+      const bf16* ex_pre = ((act == 3 || act == 4) && row_ok) ? p.pre_in + (size_t)row * p.ld_pre - coff : nullptr;
+      uint4 nx_res[4], nx_pre[4];
+      auto fetch = [&](int c) {
+        const int col0 = n0 + c * 32;
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+          const int col = col0 + g * 8;
+          if (col < p.N) {
+            if (ex_res && ERI_DBG_RANGE(p.residual, p.dbg_res_bytes, ex_res + col, 16, 93))
+              nx_res[g] = *reinterpret_cast<const uint4*>(ex_res + col);
+            if (ex_pre) nx_pre[g] = *reinterpret_cast<const uint4*>(ex_pre + col);
+          }
+        }
+      };
+      if (ex_res || ex_pre) fetch(0);
 #pragma unroll 1
       for (int c = 0; c < BN / 32; ++c) {
         const int col0 = n0 + c * 32;
         if (col0 >= p.N) break;
+        uint4 cur_res[4], cur_pre[4];
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+          cur_res[g] = nx_res[g];
+          cur_pre[g] = nx_pre[g];
+        }
+        if ((ex_res || ex_pre) && c + 1 < BN / 32 && col0 + 32 < p.N) fetch(c + 1);
         uint32_t r[32];
         tmem_ld32(acc_addr + c * 32, r);
         tmem_ld_wait();
@@ -526,9 +552,9 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA_0, const __grid_consta
                 for (int j = 0; j < 8; ++j) v[j] = apply_act(v[j], act);
               } else if (act == 3 || act == 4) {
                 float pr[8];
-                unpack8(*reinterpret_cast<const bf16x8*>(p.pre_in + (size_t)row * p.ld_pre +
-                                                         (col - coff)),
-                        pr);
+                bf16x8 pv;
+                pv.u = cur_pre[g];
+                unpack8(pv, pr);
 #pragma unroll
                 for (int j = 0; j < 8; ++j) v[j] *= apply_act_grad(pr[j], act);
               }
@@ -541,8 +567,9 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA_0, const __grid_consta
               if (p.residual && ERI_DBG_RANGE(p.residual, p.dbg_res_bytes,
                                               p.residual + (size_t)row * p.ldr + col, 16, 93)) {
                 float rs[8];
-                unpack8(*reinterpret_cast<const bf16x8*>(p.residual + (size_t)row * p.ldr + col),
-                        rs);
+                bf16x8 rv;
+                rv.u = cur_res[g];
+                unpack8(rv, rs);
 #pragma unroll
                 for (int j = 0; j < 8; ++j) v[j] += rs[j];
               }

@@ -24,7 +24,7 @@ import torch.nn as nn
 
 from ..ops import functional as F
 from .layers import (Linear, MLPEmbedder, Modulation, RMSNormScale, SmallLinear, image_ids,
-                     linear_pair, rope_table, timestep_embedding)
+                     linear_pair, mlp_pair, rope_table, timestep_embedding)
 from .registry import register_model
 
 
@@ -94,10 +94,9 @@ class DoubleStreamBlock(nn.Module):
         txt_a, img_a = attn[:, :Lt], attn[:, Lt:]
         img, txt = linear_pair(self.img_attn.proj, img_a, self.txt_attn.proj, txt_a,
                                residual=(img, txt), gate=(i_g1, t_g1))
-        img_h, txt_h = linear_pair(self.img_mlp_0, F.norm_modulate(img, i_sc2, i_sh2),
-                                   self.txt_mlp_0, F.norm_modulate(txt, t_sc2, t_sh2), act="gelu")
-        img, txt = linear_pair(self.img_mlp_2, img_h, self.txt_mlp_2, txt_h,
-                               residual=(img, txt), gate=(i_g2, t_g2))
+        img, txt = mlp_pair(self.img_mlp_0, self.img_mlp_2, F.norm_modulate(img, i_sc2, i_sh2),
+                            self.txt_mlp_0, self.txt_mlp_2, F.norm_modulate(txt, t_sc2, t_sh2), act="gelu",
+                            residual=(img, txt), gate=(i_g2, t_g2))
         return img, txt
 
 

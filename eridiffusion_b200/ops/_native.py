@@ -82,6 +82,8 @@ _SIGNATURES = {
     "eri_slot_reduce": [_P, _P, _I, _L, _F, _I, _P],
     "eri_act_fwd": [_P, _P, _L, _I, _P],
     "eri_act_bwd": [_P, _P, _P, _L, _I, _P],
+    "eri_act_bwd_rows": [_P, _L, _P, _L, _P, _L, _I, _I, _I, _P],
+    "eri_act_fwd_rows": [_P, _L, _P, _L, _I, _I, _I, _P],
     "eri_glu_fwd": [_P, _P, _I, _I, _I, _I, _P],
     "eri_glu_bwd": [_P, _P, _P, _I, _I, _I, _I, _P],
     "eri_noise_mix": [_P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _U64, _U64, _P],

@@ -475,6 +475,7 @@ def _launch_gemm(lib, g, out, route):
 
 
 _GEMM_GROUP = os.environ.get("ERI_B200_GEMM_GROUP", "1") == "1"
+_ACT_EPILOGUE = os.environ.get("ERI_B200_ACT_EPILOGUE", "0") == "1"   # activation + stored pre-activation in the GEMM epilogue
 
 
 def gemm_native_pair(kw0: dict, kw1: dict):
@@ -798,6 +799,13 @@ class _FusedLinear(torch.autograd.Function):
                 if gate_v is not None or res2 is not None:
                     y = R.gate_residual(None if res2 is None else res2.view(-1, L, Nn),
                                         y.view(-1, L, Nn), gate_v).view(M, Nn)
+            elif pre is not None and not _ACT_EPILOGUE and res2 is None and gate_v is None:
+                # training keeps the pre-activation anyway: the GEMM writes it as its output and the
+                # activation is a pass of its own (cheaper than storing both from the epilogue)
+                gemm_native(x2, w, bias=bias, lora_h=h, lora_b=lora_b if r else None, out=pre, pdl=_pdl_ok())
+                y = torch.empty_like(pre)
+                N.check(N.require().eri_act_fwd(pre.data_ptr(), y.data_ptr(), pre.numel(), 0 if act == "gelu" else 1,
+                                                N.stream_ptr()), "act_fwd")
             else:
                 y = gemm_native(x2, w, bias=bias, lora_h=h, lora_b=lora_b if r else None,
                                 act=act, pre_out=pre, residual=res2, gate=gate_v,
@@ -873,44 +881,78 @@ class _FusedLinearPair(torch.autograd.Function):
     """Two fused linears with the same shape of weight (the image and the text stream of a dual-stream
     block): y_i = [residual_i + gate_i *] act(x_i W_i^T + b_i + s_i (x_i A_i^T) B_i^T). The two main GEMMs
     share one launch in the forward, and the two input-gradient GEMMs one in the backward
-    (``gemm_native_pair``); everything else is what ``_FusedLinear`` does per stream. Only for the
-    native path with rank-16/32/64 adapters (or none) on both streams; ``linear_pair`` checks that."""
+    (``gemm_native_pair``), as do the rank-r products of both streams (``skinny_gemm_pair``); everything
+    else is what ``_FusedLinear`` does per stream. Only for the native path with rank-16/32/64 adapters
+    (or none) on both streams; ``linear_pair`` checks that.
+
+    Two more modes chain an MLP without a separate activation-gradient pass. ``emit_pre``: the outputs
+    are (pre_0, pre_1, u_0, u_1) with u_i = act(pre_i) marked non-differentiable, i.e. the layer is the
+    plain linear that produces the pre-activation and the activation is a by-product of its epilogue.
+    ``act_in`` with ``xp_i``: x_i is act_in(xp_i) (such a by-product), the layer is linear-of-activation
+    as a function of xp_i, and its input-gradient GEMM applies the activation's derivative at xp_i in its
+    epilogue, so the gradient it returns is already the one of the pre-activation."""
 
     @staticmethod
-    def forward(ctx, act, x0, w0, b0, la0, lb0, s0, res0, gate0, x1, w1, b1, la1, lb1, s1, res1, gate1):
-        streams = ((x0, w0, b0, la0, lb0, s0, res0, gate0), (x1, w1, b1, la1, lb1, s1, res1, gate1))
-        need_any = (any(ctx.needs_input_grad[1:6]), any(ctx.needs_input_grad[9:14]))
+    def forward(ctx, act, emit_pre, act_in, x0, xp0, w0, b0, la0, lb0, s0, res0, gate0,
+                x1, xp1, w1, b1, la1, lb1, s1, res1, gate1):
+        streams = ((x0, xp0, w0, b0, la0, lb0, s0, res0, gate0), (x1, xp1, w1, b1, la1, lb1, s1, res1, gate1))
+        need = ctx.needs_input_grad
+        need_any = (any(need[3:9]), any(need[12:18]))
         kws, saved, metas = [], [], []
-        for i, (x, w, b, la, lb, sc, res, gate) in enumerate(streams):
+        for i, (x, xp, w, b, la, lb, sc, res, gate) in enumerate(streams):
             shp = x.shape
             K, Nn = shp[-1], w.shape[0]
             x2 = _c(x).view(-1, K)
             M, L = x2.shape[0], shp[-2]
             r = 0 if la is None else la.shape[0]
-            pre = torch.empty(M, Nn, dtype=x.dtype, device=x.device) if (act is not None and need_any[i]) else None
+            pre = None
+            if act is not None and (need_any[i] or emit_pre):
+                pre = torch.empty(M, Nn, dtype=x.dtype, device=x.device)
             res2 = None if res is None else _c(res).view(-1, Nn)
             gate_v = _mod_view(gate, Nn)[0] if gate is not None else None
+            xp2 = None if xp is None else _c(xp).view(-1, K)
             kws.append(dict(a=x2, b=w, bias=b, lora_h=None, lora_b=lb if r else None, act=act, pre_out=pre,
                             residual=res2, gate=gate_v, rows_per_batch=L, pdl=_pdl_ok()))
-            saved += [x2, w, la, lb, None, pre, gate_v]
+            saved += [x2, w, la, lb, None, None if emit_pre else pre, gate_v, xp2]
             metas.append((shp, Nn, L, sc, res is not None, b is not None))
         if la0 is not None:
             # both rank-r products in one launch, right before the grouped GEMM that consumes them
             h0, h1 = skinny_gemm_pair(kws[0]["a"], la0, s0, kws[1]["a"], la1, s1)
             kws[0]["lora_h"], kws[1]["lora_h"] = h0, h1
-            saved[4], saved[11] = h0, h1
+            saved[4], saved[12] = h0, h1
+        # Training keeps the pre-activation anyway: the GEMM then writes it as its output and the activation
+        # is a pass of its own (storing both from the epilogue costs the GEMM more than that pass does).
+        unfuse = (act is not None and not _ACT_EPILOGUE and all(k["pre_out"] is not None and k["residual"] is None
+                                                                 and k["gate"] is None for k in kws))
+        if unfuse:
+            for k in kws:
+                k.update(out=k["pre_out"], act=None, pre_out=None)
         y0, y1 = gemm_native_pair(kws[0], kws[1])
+        if unfuse:
+            pres = (y0, y1)
+            y0, y1 = torch.empty_like(y0), torch.empty_like(y1)
+            for pr, yy in zip(pres, (y0, y1)):
+                N.check(N.require().eri_act_fwd(pr.data_ptr(), yy.data_ptr(), pr.numel(), 0 if act == "gelu" else 1,
+                                                N.stream_ptr()), "act_fwd")
+            for k, pr in zip(kws, pres):
+                k["pre_out"] = pr
         ctx.save_for_backward(*saved)
-        ctx.meta = (act, metas)
+        ctx.meta = (act, emit_pre, act_in, metas)
         ctx.set_materialize_grads(False)       # an unused output (None gradient) costs nothing in backward
-        return y0.view(*metas[0][0][:-1], metas[0][1]), y1.view(*metas[1][0][:-1], metas[1][1])
+        y0, y1 = y0.view(*metas[0][0][:-1], metas[0][1]), y1.view(*metas[1][0][:-1], metas[1][1])
+        if emit_pre:
+            ctx.mark_non_differentiable(y0, y1)
+            return kws[0]["pre_out"].view_as(y0), kws[1]["pre_out"].view_as(y1), y0, y1
+        return y0, y1
 
     @staticmethod
-    def backward(ctx, dy0, dy1):
-        act, metas = ctx.meta
+    def backward(ctx, *douts):
+        act, emit_pre, act_in, metas = ctx.meta
+        dy0, dy1 = douts[0], douts[1]      # emit_pre: the gradients of the pre-activations
         sv = ctx.saved_tensors
         lib = N.require()
         need = ctx.needs_input_grad
+        base = (3, 12)                     # positions of x0 / x1 among the forward's arguments
         parts = []
         kws = []
         for i, dy in enumerate((dy0, dy1)):
@@ -918,7 +960,7 @@ class _FusedLinearPair(torch.autograd.Function):
                 kws.append(None)
                 parts.append(None)
                 continue
-            x2, w, la, lb, h, pre, gate_v = sv[7 * i: 7 * i + 7]
+            x2, w, la, lb, h, pre, gate_v, xp2 = sv[8 * i: 8 * i + 8]
             shp, Nn, L, sc, has_res, has_bias = metas[i]
             M, K = x2.shape
             dy2 = _c(dy).view(M, Nn)
@@ -928,7 +970,7 @@ class _FusedLinearPair(torch.autograd.Function):
                 N.check(lib.eri_gate_residual(None, dy2.data_ptr(), gate_v.data_ptr(), g.data_ptr(), M, Nn, L,
                                               gate_v.stride(0), N.stream_ptr()), "gate_bwd")
                 dy2 = g
-            if act is not None:
+            if act is not None and not emit_pre:
                 g = torch.empty_like(dy2)
                 N.check(lib.eri_act_bwd(dy2.data_ptr(), pre.data_ptr(), g.data_ptr(), dy2.numel(),
                                         0 if act == "gelu" else 1, N.stream_ptr()), "act_bwd")
@@ -937,7 +979,10 @@ class _FusedLinearPair(torch.autograd.Function):
             lb_t = la_t = None
             if r:
                 lb_t, la_t = _lora_transposed(lb), _lora_transposed(la)
-            kws.append(dict(a=dy2, b=w, b_mn=True, lora_h=None, lora_b=la_t, pdl=_pdl_ok()))
+            kw = dict(a=dy2, b=w, b_mn=True, lora_h=None, lora_b=la_t, pdl=_pdl_ok())
+            if act_in is not None:
+                kw.update(act=act_in + "_bwd", pre_in=xp2)     # the input's activation derivative in the epilogue
+            kws.append(kw)
             parts.append([dy2, None, d_res, lb_t, sc])
         # Ts_i = s_i * dY_i B_i: one launch for both streams when both have a gradient, right before the
         # grouped input-gradient GEMM
@@ -950,24 +995,24 @@ class _FusedLinearPair(torch.autograd.Function):
                 parts[i][1] = skinny_gemm(parts[i][0], parts[i][3], alpha=parts[i][4])
         for i in live:
             kws[i]["lora_h"] = parts[i][1]
-        base = (1, 9)                      # positions of x0 / x1 among the forward's arguments
         dxs = [None, None]
-        want = [need[base[0]] and kws[0] is not None, need[base[1]] and kws[1] is not None]
+        xin = 1 if act_in is not None else 0          # the differentiable input: xp_i or x_i
+        want = [need[base[0] + xin] and kws[0] is not None, need[base[1] + xin] and kws[1] is not None]
         if all(want):
             dxs = list(gemm_native_pair(kws[0], kws[1]))
         else:
             for i in range(2):
                 if want[i]:
                     dxs[i] = gemm_native(**kws[i])
-        grads = [None]
+        grads = [None, None, None]
         for i in range(2):
             if parts[i] is None:
-                grads += [None] * 8
+                grads += [None] * 9
                 continue
-            x2, w, la, lb, h, pre, gate_v = sv[7 * i: 7 * i + 7]
+            x2, w, la, lb, h, pre, gate_v, xp2 = sv[8 * i: 8 * i + 8]
             shp, Nn, L, sc, has_res, has_bias = metas[i]
             dy2, ts, d_res = parts[i][:3]
-            nd = need[base[i]: base[i] + 5]
+            nd = need[base[i] + 1: base[i] + 6]      # (xp,) w, bias, A, B at offsets 1..4 of this slice
             dw = dbias = da = db = None
             if nd[1]:
                 if _ACCUM_INTO_GRAD and w.grad is not None and w.grad.dtype == x2.dtype and w.grad.is_contiguous():
@@ -987,36 +1032,54 @@ class _FusedLinearPair(torch.autograd.Function):
                 else:
                     db = lora_wgrad(dy2, h)
             dx = None if dxs[i] is None else dxs[i].view(shp)
-            grads += [dx, dw, dbias, da, db, None, d_res, None]
+            grads += [None if xin else dx, dx if xin else None, dw, dbias, da, db, None, d_res, None]
         return tuple(grads)
 
 
-def linear_pair(x0, lin0, x1, lin1, act=None):
-    """``lin_i`` = (w, bias, lora or None, residual or None, gate or None). Returns (y0, y1) of two fused
-    linears whose main GEMMs (and input-gradient GEMMs) share one launch when both run on the native path
-    with matching shapes; otherwise exactly ``linear`` twice."""
+def _linear_pair_ok(x0, lin0, x1, lin1) -> bool:
     (w0, b0, lo0, r0, g0), (w1, b1, lo1, r1, g1) = lin0, lin1
 
     def rank_ok(lo):
         return lo is None or lo[0].shape[0] in (16, 32, 64)
-    ok = (_GEMM_GROUP and _GEMM_NATIVE == "native" and _native_ok(x0, w0, b0) and _native_ok(x1, w1, b1)
-          and w0.shape == w1.shape and x0.shape[-1] % 8 == 0 and rank_ok(lo0) and rank_ok(lo1)
-          and (lo0 is None) == (lo1 is None) and (lo0 is None or lo0[0].shape[0] == lo1[0].shape[0])
-          and (b0 is None) == (b1 is None)
-          and x0.numel() // x0.shape[-1] >= 256 and x1.numel() // x1.shape[-1] >= 256
-          and gemm_supported(x0.numel() // x0.shape[-1], w0.shape[0], x0.shape[-1])
-          and gemm_supported(x1.numel() // x1.shape[-1], w1.shape[0], x1.shape[-1]))
-    if not ok:
+    return bool(_GEMM_GROUP and _GEMM_NATIVE == "native" and _native_ok(x0, w0, b0) and _native_ok(x1, w1, b1)
+                and w0.shape == w1.shape and x0.shape[-1] % 8 == 0 and rank_ok(lo0) and rank_ok(lo1)
+                and (lo0 is None) == (lo1 is None) and (lo0 is None or lo0[0].shape[0] == lo1[0].shape[0])
+                and (b0 is None) == (b1 is None)
+                and x0.numel() // x0.shape[-1] >= 256 and x1.numel() // x1.shape[-1] >= 256
+                and gemm_supported(x0.numel() // x0.shape[-1], w0.shape[0], x0.shape[-1])
+                and gemm_supported(x1.numel() // x1.shape[-1], w1.shape[0], x1.shape[-1]))
+
+
+def linear_pair_ok(x0, lin0, x1, lin1) -> bool:
+    """Whether ``linear_pair`` would run the two layers as grouped launches."""
+    return _linear_pair_ok(x0, lin0, x1, lin1)
+
+
+def linear_pair(x0, lin0, x1, lin1, act=None, emit_pre=False, act_in=None, x_pre=(None, None)):
+    """``lin_i`` = (w, bias, lora or None, residual or None, gate or None). Returns (y0, y1) of two fused
+    linears whose main GEMMs (and input-gradient GEMMs) share one launch when both run on the native path
+    with matching shapes; otherwise exactly ``linear`` twice. ``emit_pre`` / ``act_in`` + ``x_pre`` (only
+    when ``linear_pair_ok``): see ``_FusedLinearPair``; with ``emit_pre`` the result is
+    (pre_0, pre_1, act(pre_0), act(pre_1))."""
+    (w0, b0, lo0, r0, g0), (w1, b1, lo1, r1, g1) = lin0, lin1
+    if emit_pre or act_in is not None:
+        a0, bb0, s0 = lo0 if lo0 is not None else (None, None, 1.0)
+        a1, bb1, s1 = lo1 if lo1 is not None else (None, None, 1.0)
+        return _FusedLinearPair.apply(act, emit_pre, act_in, x0, x_pre[0], w0, b0, a0, bb0, float(s0), r0, g0,
+                                      x1, x_pre[1], w1, b1, a1, bb1, float(s1), r1, g1)
+
+    if not _linear_pair_ok(x0, lin0, x1, lin1):
         return (linear(x0, w0, b0, lora=lo0, act=act, residual=r0, gate=g0),
                 linear(x1, w1, b1, lora=lo1, act=act, residual=r1, gate=g1))
     a0, bb0, s0 = lo0 if lo0 is not None else (None, None, 1.0)
     a1, bb1, s1 = lo1 if lo1 is not None else (None, None, 1.0)
     if (g0 is not None and g0.requires_grad) or (g1 is not None and g1.requires_grad):
         # trainable modulation: the gates stay outside the GEMM epilogue so that their gradients are produced
-        y0, y1 = _FusedLinearPair.apply(act, x0, w0, b0, a0, bb0, float(s0), None, None,
-                                        x1, w1, b1, a1, bb1, float(s1), None, None)
+        y0, y1 = _FusedLinearPair.apply(act, False, None, x0, None, w0, b0, a0, bb0, float(s0), None, None,
+                                        x1, None, w1, b1, a1, bb1, float(s1), None, None)
         return gate_residual(r0, y0, g0), gate_residual(r1, y1, g1)
-    return _FusedLinearPair.apply(act, x0, w0, b0, a0, bb0, float(s0), r0, g0, x1, w1, b1, a1, bb1, float(s1), r1, g1)
+    return _FusedLinearPair.apply(act, False, None, x0, None, w0, b0, a0, bb0, float(s0), r0, g0,
+                                  x1, None, w1, b1, a1, bb1, float(s1), r1, g1)
 
 
 _GLU_FUSED = os.environ.get("ERI_B200_GLU_FUSED", "1") == "1"

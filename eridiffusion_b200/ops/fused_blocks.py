@@ -21,6 +21,9 @@ from . import flash_attn as FA
 from . import functional as F
 
 
+_ACT_BWD_IN_EPILOGUE = __import__("os").environ.get("ERI_B200_SS_ACT_EPILOGUE", "0") == "1"
+
+
 class _SingleStream(torch.autograd.Function):
     @staticmethod
     def forward(ctx, xm, x, gate, w1, b1, w2, b2, a1, bb1, s1, a2, bb2, s2, qs, ks, cos, sin, heads):
@@ -39,8 +42,17 @@ class _SingleStream(torch.autograd.Function):
         # each rank-r product is the launch right before the GEMM that consumes it, so that GEMM can
         # start while it still runs (programmatic dependent launch)
         h1 = F.skinny_gemm(xm2, a1, alpha=s1) if a1 is not None else None
-        F.gemm_native(xm2, w1, bias=b1, lora_h=h1, lora_b=bb1, out=qkv, n_split=3 * D,
-                      out2=cat[:, D:], act="gelu", pre_out=pre, pdl=F._pdl_ok())
+        if _ACT_BWD_IN_EPILOGUE:
+            F.gemm_native(xm2, w1, bias=b1, lora_h=h1, lora_b=bb1, out=qkv, n_split=3 * D,
+                          out2=cat[:, D:], act="gelu", pre_out=pre, pdl=F._pdl_ok())
+        else:
+            # the MLP half's pre-activation goes straight to its buffer and GELU is a pass of its own into
+            # the second linear's input: storing both from the epilogue costs the GEMM more than that pass
+            F.gemm_native(xm2, w1, bias=b1, lora_h=h1, lora_b=bb1, out=qkv, n_split=3 * D, out2=pre,
+                          pdl=F._pdl_ok())
+            mlp_in = cat[:, D:]
+            N.check(lib.eri_act_fwd_rows(pre.data_ptr(), pre.stride(0), mlp_in.data_ptr(), cat.stride(0), M, Fm, 0,
+                                         N.stream_ptr()), "act_fwd_rows")
         q = torch.empty(B, L, heads, Dh, dtype=dt, device=dev)
         k, v = torch.empty_like(q), torch.empty_like(q)
         N.check(lib.eri_qknorm_rope_fwd(qkv.data_ptr(), N.ptr(qs), N.ptr(ks), N.ptr(cos), N.ptr(sin),
@@ -76,8 +88,17 @@ class _SingleStream(torch.autograd.Function):
         d_attn = torch.empty(M, D, dtype=dt, device=dev)
         d_h = torch.empty(M, 3 * D + Fm, dtype=dt, device=dev)
         ts2 = F.skinny_gemm(g, bb2_t, alpha=s2) if a2 is not None else None
-        F.gemm_native(g, w2, b_mn=True, lora_h=ts2, lora_b=a2_t,
-                      out=d_attn, n_split=D, out2=d_h[:, 3 * D:], act="gelu_bwd", pre_in=pre, pdl=F._pdl_ok())
+        if _ACT_BWD_IN_EPILOGUE:
+            F.gemm_native(g, w2, b_mn=True, lora_h=ts2, lora_b=a2_t,
+                          out=d_attn, n_split=D, out2=d_h[:, 3 * D:], act="gelu_bwd", pre_in=pre, pdl=F._pdl_ok())
+        else:
+            # the GELU derivative as a pass of its own over the MLP half of d_h, in place: the epilogue's
+            # row-strided reads of the pre-activation cost the GEMM more than this pass does
+            F.gemm_native(g, w2, b_mn=True, lora_h=ts2, lora_b=a2_t,
+                          out=d_attn, n_split=D, out2=d_h[:, 3 * D:], pdl=F._pdl_ok())
+            mlp_g = d_h[:, 3 * D:]
+            N.check(lib.eri_act_bwd_rows(mlp_g.data_ptr(), d_h.stride(0), pre.data_ptr(), pre.stride(0),
+                                         mlp_g.data_ptr(), d_h.stride(0), M, Fm, 0, N.stream_ptr()), "act_bwd_rows")
         da2 = F.lora_wgrad(cat, ts2, transpose_out=True) if (a2 is not None and need[10]) else None
         db2 = F.lora_wgrad(g, h2) if (a2 is not None and need[11]) else None
         dq, dk, dv = FA.bwd(d_attn.view(B, L, heads, Dh), q, k, v, o, lse)

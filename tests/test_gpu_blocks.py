@@ -51,12 +51,13 @@ def test_fused_model_matches_library_path(dd, ds):
         assert e < 0.06 * b.abs().max().item() + 1e-5, (k, e, b.abs().max().item())
 
 
-def _double_block(group, full_ft=False, depth_single=1):
+def _double_block(group, full_ft=False, depth_single=1, mlp_fuse=False):
     from eridiffusion_b200.adapters import AdapterConfig, inject_adapters
     from eridiffusion_b200.models import build_model
     from eridiffusion_b200.ops import functional as F
-    old = F._GEMM_GROUP
-    F._GEMM_GROUP = group
+    from eridiffusion_b200.models import layers as LY
+    old, old_fuse = F._GEMM_GROUP, LY._MLP_FUSE
+    F._GEMM_GROUP, LY._MLP_FUSE = group, mlp_fuse
     try:
         torch.manual_seed(0)
         dev = "cuda"
@@ -86,16 +87,17 @@ def _double_block(group, full_ft=False, depth_single=1):
         assert F.gemm_error_check() == 0
         return out.float(), {k: p.grad.float().clone() for k, p in params.items() if p.grad is not None}, n
     finally:
-        F._GEMM_GROUP = old
+        F._GEMM_GROUP, LY._MLP_FUSE = old, old_fuse
 
 
-@pytest.mark.parametrize("full_ft,depth_single", [(False, 1), (True, 1), (False, 0)])
-def test_grouped_stream_linears_match_separate_launches(full_ft, depth_single):
+@pytest.mark.parametrize("full_ft,depth_single,mlp_fuse", [(False, 1, False), (True, 1, False), (False, 0, False),
+                                                           (False, 1, True), (False, 0, True)])
+def test_grouped_stream_linears_match_separate_launches(full_ft, depth_single, mlp_fuse):
     """Dual-stream blocks with the image and the text projection of each pair in one grouped launch
     (forward GEMM and input-gradient GEMM) against the same blocks with one launch per projection.
     Without single-stream blocks the last block's text output is unused: its gradient is None and the
     paired backward runs the image stream alone."""
-    o1, g1, n1 = _double_block(True, full_ft, depth_single)
+    o1, g1, n1 = _double_block(True, full_ft, depth_single, mlp_fuse)
     o0, g0, n0 = _double_block(False, full_ft, depth_single)
     # two blocks x four projection pairs. Per grouped pair one GEMM launch fewer in forward and one in backward
     # (input gradient), and with adapters one rank-r launch fewer each way as well (both streams' x A^T, and
@@ -103,8 +105,11 @@ def test_grouped_stream_linears_match_separate_launches(full_ft, depth_single):
     # LoRA: the first pair of the first block has no input gradient to compute (frozen input projections):
     # 16 + 8 + 7. Without single-stream blocks three text projections of the last block have no gradient at
     # all: 16 + (1 + 4) + (1 + 3). Full fine-tune (no adapters; trainable gates are applied outside the GEMM in
-    # both paths): 8 + 8.
-    assert n0 - n1 == (16 if full_ft else 31 if depth_single else 25), (n0, n1)
+    # both paths): 8 + 8. ``mlp_fuse`` (opt-in): the MLP pairs also drop their activation-gradient launches (the
+    # derivative is applied in the down-projections' input-gradient epilogue): 4, or 3 when the last block's
+    # text MLP has no gradient.
+    extra = (4 if depth_single else 3) if mlp_fuse else 0
+    assert n0 - n1 == (16 if full_ft else 31 if depth_single else 25) + extra, (n0, n1)
     assert (o1 - o0).abs().max().item() <= 0.02 * o0.abs().max().item()
     assert g0.keys() == g1.keys() and len(g0) > 0
     for k in g0:
