@@ -478,6 +478,15 @@ _GEMM_GROUP = os.environ.get("ERI_B200_GEMM_GROUP", "1") == "1"
 _ACT_EPILOGUE = os.environ.get("ERI_B200_ACT_EPILOGUE", "0") == "1"   # activation + stored pre-activation in the GEMM epilogue
 
 
+def _act_outside_epilogue(M, Nn, K) -> bool:
+    """Whether a training-time linear + activation writes its pre-activation from the GEMM and applies the
+    activation in a pass of its own. With a short reduction (K <= 4096) the epilogue of a pair tile is on the
+    critical path and storing both tensors from it costs a large GEMM more than the separate pass
+    ([4096 x 12288 x 3072]: 282 against 225 + 39 us); with a long reduction the epilogue is hidden, and a small
+    problem is bound by its launches, so both keep the fused form."""
+    return not _ACT_EPILOGUE and K <= 4096 and M * Nn >= (1 << 25)
+
+
 def gemm_native_pair(kw0: dict, kw1: dict):
     """Two independent products (keyword arguments of ``gemm_native`` each) in ONE launch of the two-CTA
     kernel when they qualify: same N, K, operand majors, LoRA rank and epilogue kind, plain modes. The
@@ -799,7 +808,7 @@ class _FusedLinear(torch.autograd.Function):
                 if gate_v is not None or res2 is not None:
                     y = R.gate_residual(None if res2 is None else res2.view(-1, L, Nn),
                                         y.view(-1, L, Nn), gate_v).view(M, Nn)
-            elif pre is not None and not _ACT_EPILOGUE and res2 is None and gate_v is None:
+            elif pre is not None and res2 is None and gate_v is None and _act_outside_epilogue(M, Nn, K):
                 # training keeps the pre-activation anyway: the GEMM writes it as its output and the
                 # activation is a pass of its own (cheaper than storing both from the epilogue)
                 gemm_native(x2, w, bias=bias, lora_h=h, lora_b=lora_b if r else None, out=pre, pdl=_pdl_ok())
@@ -922,8 +931,9 @@ class _FusedLinearPair(torch.autograd.Function):
             saved[4], saved[12] = h0, h1
         # Training keeps the pre-activation anyway: the GEMM then writes it as its output and the activation
         # is a pass of its own (storing both from the epilogue costs the GEMM more than that pass does).
-        unfuse = (act is not None and not _ACT_EPILOGUE and all(k["pre_out"] is not None and k["residual"] is None
-                                                                 and k["gate"] is None for k in kws))
+        unfuse = (act is not None and all(k["pre_out"] is not None and k["residual"] is None and k["gate"] is None
+                                          for k in kws)
+                  and _act_outside_epilogue(kws[0]["a"].shape[0], kws[0]["b"].shape[0], kws[0]["a"].shape[1]))
         if unfuse:
             for k in kws:
                 k.update(out=k["pre_out"], act=None, pre_out=None)

@@ -101,3 +101,43 @@ def test_grouped_launch_of_two_problems(M0, M1, N, K, mn):
                                 dict(a=x2, b=w2.t().contiguous() if mn else w2, b_mn=mn))
     close(z1, x2.float() @ w2.float().t(), 0.06)
     assert F.gemm_error_check() == 0
+
+
+@pytest.mark.parametrize("paired", [False, True])
+def test_activation_outside_the_epilogue_matches_the_fused_form(paired):
+    """A large linear + GELU with a short reduction writes its pre-activation from the GEMM and applies GELU in
+    a pass of its own during training; outputs and gradients equal the form with everything in the epilogue."""
+    M, N, K, r = 4096, 8192, 512, 16
+    assert F._act_outside_epilogue(M, N, K)
+
+    def run(fused):
+        old = F._ACT_EPILOGUE
+        F._ACT_EPILOGUE = fused
+        try:
+            outs = []
+            xs = [rnd(1, M, K, seed=1).requires_grad_(), rnd(1, 512, K, seed=2).requires_grad_()]
+            ws = [rnd(N, K, scale=K ** -0.5, seed=3), rnd(N, K, scale=K ** -0.5, seed=4)]
+            As = [rnd(r, K, scale=K ** -0.5, seed=5).requires_grad_(), rnd(r, K, scale=K ** -0.5, seed=6).requires_grad_()]
+            Bs = [rnd(N, r, scale=0.1, seed=7).requires_grad_(), rnd(N, r, scale=0.1, seed=8).requires_grad_()]
+            bias = [rnd(N, seed=9), rnd(N, seed=10)]
+            if paired:
+                ys = F.linear_pair(xs[0], (ws[0], bias[0], (As[0], Bs[0], 0.5), None, None),
+                                   xs[1], (ws[1], bias[1], (As[1], Bs[1], 0.5), None, None), act="gelu")
+            else:
+                ys = [F.linear(xs[i], ws[i], bias[i], lora=(As[i], Bs[i], 0.5), act="gelu") for i in range(2)]
+            c0 = F.N.launch_count()
+            sum((y.float() * 0.01).sum() for y in ys).backward()
+            for i in range(2):
+                outs += [ys[i].detach().float(), xs[i].grad.float(), As[i].grad.float(), Bs[i].grad.float()]
+            return outs
+        finally:
+            F._ACT_EPILOGUE = old
+    a, b = run(False), run(True)
+    for u, v in zip(a, b):
+        assert (u - v).abs().max().item() <= 0.02 * v.abs().max().item() + 1e-6
+    assert F.gemm_error_check() == 0
+    # against fp32 for the first stream's output
+    x, w, bi = rnd(1, M, K, seed=1).float(), rnd(N, K, scale=K ** -0.5, seed=3).float(), rnd(N, seed=9).float()
+    A, B = rnd(r, K, scale=K ** -0.5, seed=5).float(), rnd(N, r, scale=0.1, seed=7).float()
+    ref = torch.nn.functional.gelu(x @ w.t() + bi + 0.5 * (x @ A.t()) @ B.t(), approximate="tanh")
+    close(a[0], ref, 0.05)
