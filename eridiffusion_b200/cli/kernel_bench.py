@@ -1,6 +1,6 @@
 """Per-kernel timing against the library equivalents and the measured roofline.
 
-    python -m eridiffusion_b200.cli.kernel_bench [--what gemm,skinny,attn,elementwise,optim,dequant,narrow,wgrad,small_m,gather_emul] [--small]
+    python -m eridiffusion_b200.cli.kernel_bench [--what gemm,skinny,attn,elementwise,optim,dequant,narrow,wgrad,small_m,gather_emul,epilogue] [--small]
 
 Timing: CUDA events on the launching stream, >= 3 warm-up launches, L2 flushed between timed
 launches by writing a 256 MB buffer, median of the timed launches. Roofline denominators come from
@@ -303,6 +303,36 @@ def bench_narrow(small):
               f"torch {t_lib*1e6:.1f} us")
 
 
+def bench_epilogue(small):
+    """What the GEMM epilogue's extra operands cost at the training step's shapes, against the same work as a
+    separate bandwidth-bound pass: residual + gate, GELU with a stored pre-activation, the GELU derivative read
+    from a stored pre-activation."""
+    r = lambda *s: torch.randn(*s, device="cuda").bfloat16()
+    shapes = [("single-stream second linear", 4608, 3072, 15360), ("attention out-projection", 4096, 3072, 3072),
+              ("MLP down-projection", 4096, 3072, 12288), ("MLP up-projection / its input gradient", 4096, 12288, 3072)]
+    for tag, M, Nn, K in (shapes[1:2] if small else shapes):
+        a, w, wt = r(M, K), r(Nn, K), r(K, Nn)
+        h, lb = r(M, 16), r(Nn, 16)
+        res, gate, bias = r(M, Nn), r(1, Nn), r(Nn)
+        pre = torch.empty(M, Nn, device="cuda", dtype=torch.bfloat16)
+        out = torch.empty(M, Nn, device="cuda", dtype=torch.bfloat16)
+        y = r(1, M, Nn)
+        t = {
+            "plain (bias + rank-16 K step)": timeit(lambda: F.gemm_native(a, w, out=out, bias=bias, lora_h=h, lora_b=lb)),
+            "+ residual + gate": timeit(lambda: F.gemm_native(a, w, out=out, bias=bias, lora_h=h, lora_b=lb, residual=res,
+                                                              gate=gate, rows_per_batch=M)),
+            "+ GELU + stored pre-activation": timeit(lambda: F.gemm_native(a, w, out=out, bias=bias, lora_h=h, lora_b=lb,
+                                                                           act="gelu", pre_out=pre)),
+            "input gradient, plain": timeit(lambda: F.gemm_native(a, wt, b_mn=True, out=out, lora_h=h, lora_b=lb)),
+            "input gradient + GELU derivative": timeit(lambda: F.gemm_native(a, wt, b_mn=True, out=out, lora_h=h, lora_b=lb,
+                                                                             act="gelu_bwd", pre_in=pre)),
+            "gate + residual as a pass": timeit(lambda: F.gate_residual(res.view(1, M, Nn), y, gate)),
+            "GELU as a pass": timeit(lambda: F.gelu_tanh(y)),
+        }
+        print(f"epilogue extras, {tag} [{M} x {Nn} x {K}]: " + "; ".join(f"{k} {v*1e6:.1f} us" for k, v in t.items()))
+    assert F.gemm_error_check() == 0
+
+
 def bench_attn(small):
     bw, fl, tag = peaks()
     for (B, L, H, D) in ([(1, 4608, 24, 128)] if not small else [(1, 1024, 8, 128)]):
@@ -343,6 +373,7 @@ def main():
     a = ap.parse_args()
     for w in a.what.split(","):
         {"gemm": bench_gemm, "skinny": bench_skinny, "elementwise": bench_elementwise, "optim": bench_optim,
+         "epilogue": bench_epilogue,
          "attn": bench_attn, "dequant": bench_dequant, "narrow": bench_narrow, "wgrad": bench_wgrad, "small_m": bench_small_m, "gather_emul": bench_gather_emul}[w](a.small)
 
 
