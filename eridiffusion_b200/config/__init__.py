@@ -543,7 +543,9 @@ ENV_VARS = {
     "ERI_B200_ADAMW8_PAIR": "1 | 0: 8-bit AdamW on packed fp32 pairs (default) or the element-wise kernel",
     "ERI_B200_MLP_FUSE": "1: dual-stream MLP pairs apply the activation derivative in the down-projection's input-gradient epilogue (measured slower; default 0)",
     "ERI_B200_ACT_EPILOGUE": "1: activation + stored pre-activation in the GEMM epilogue during training (default 0: the GEMM writes the pre-activation, a separate pass applies the activation)",
-    "ERI_B200_SS_ACT_EPILOGUE": "1: single-stream blocks keep GELU (forward) and its derivative (backward) in GEMM epilogues (default 0: separate row-strided passes)",
+    "ERI_B200_SS_ACT_EPILOGUE": "1: single-stream blocks apply GELU in the first linear's epilogue (default 0: the GEMM writes the pre-activation, a row pass applies GELU)",
+    "ERI_B200_SS_ACT_BWD_EPILOGUE": "1 | 0: single-stream blocks apply the GELU derivative in the second linear's input-gradient epilogue (default 1)",
+    "ERI_B200_GEMM_EPI_WARPS": "8 | 4: epilogue warps of a plain two-CTA GEMM launch (gather / scatter launches always use 4)",
     "ERI_B200_GEMM_GROUP": "1 | 0: image and text projection of a dual-stream block in one grouped launch of the two-CTA GEMM",
     "ERI_B200_GATHER_JOIN": "1: copy clusters of a gather-fused GEMM take tiles after their last slab (default 0)",
     "ERI_B200_ZERO3_PREFETCH": "1 | 0: ZeRO-3 next-layer prefetch (copy engines pull layer i + 1's shards while GEMM i runs)",

@@ -125,7 +125,7 @@ __device__ __forceinline__ float apply_act_grad(float pre, int act) {
 // STAGED: the epilogue writes each accumulator row to shared memory and sends it with one bulk
 // asynchronous copy (the peer scatter, whose destination rows live on other GPUs).
 template <int STAGES, bool STAGED>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(192, 1)
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(320, 1)
 gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA_0, const __grid_constant__ CUtensorMap tmB_0,
                   const __grid_constant__ CUtensorMap tmA2_0, const __grid_constant__ CUtensorMap tmB2_0,
                   const __grid_constant__ CUtensorMap tmBL, const __grid_constant__ Gemm2Params p0,
@@ -178,7 +178,7 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA_0, const __grid_consta
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(&acc_full[b], 1);
-      mbar_init(&acc_empty[b], 8);  // 4 epilogue warps x 2 CTAs (used on the leader only)
+      mbar_init(&acc_empty[b], 2 * ((blockDim.x >> 5) - 2));  // epilogue warps x 2 CTAs (used on the leader only)
     }
     mbar_fence_init();
   }
@@ -384,7 +384,14 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA_0, const __grid_consta
       }
     }
   } else {
+    // Four epilogue warps (one per 32-row TMEM quadrant) or eight: with eight, warps w and w + 4 share a
+    // quadrant and split the tile's columns in halves, which halves the time a tile spends in the epilogue
+    // (~10 us with four warps: with K = 3072 that is close to the main loop's ~19 us as soon as the epilogue
+    // reads or writes a second tensor). Plain launches run with eight, gather / scatter launches with four.
     const int q = warp & 3;
+    const int n_half = ((int)(blockDim.x >> 5) - 2) >> 2;        // 1 or 2
+    const int half = (warp - 2) >> 2;                            // 0, or 1 for the second set of four warps
+    const int c_lo = n_half == 2 ? half * (BN / 64) : 0, c_hi = n_half == 2 ? c_lo + BN / 64 : BN / 32;
     int it = 0;
     for (int r = sched.first_round; sched.tile(r) < tiles; ++r, ++it) {
       const int t = sched.tile(r);
@@ -410,7 +417,7 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA_0, const __grid_consta
         const bool act_first = p.glu >= 3;
         const int amode = (p.glu == 1 || p.glu == 3) ? 1 : 2;
 #pragma unroll 1
-        for (int c = 0; c < BNH / 32; ++c) {
+        for (int c = (n_half == 2 ? half * (BNH / 64) : 0); c < (n_half == 2 ? (half + 1) * (BNH / 64) : BNH / 32); ++c) {
           const int col0 = n0 + c * 32;
           if (col0 >= p.glu_hidden) break;
           uint32_t ra[32], rb[32];
@@ -514,9 +521,9 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA_0, const __grid_consta
           }
         }
       };
-      if (ex_res || ex_pre) fetch(0);
+      if ((ex_res || ex_pre) && n0 + c_lo * 32 < p.N) fetch(c_lo);
 #pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
+      for (int c = c_lo; c < c_hi; ++c) {
         const int col0 = n0 + c * 32;
         if (col0 >= p.N) break;
         uint4 cur_res[4], cur_pre[4];
@@ -525,7 +532,7 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA_0, const __grid_consta
           cur_res[g] = nx_res[g];
           cur_pre[g] = nx_pre[g];
         }
-        if ((ex_res || ex_pre) && c + 1 < BN / 32 && col0 + 32 < p.N) fetch(c + 1);
+        if ((ex_res || ex_pre) && c + 1 < c_hi && col0 + 32 < p.N) fetch(c + 1);
         uint32_t r[32];
         tmem_ld32(acc_addr + c * 32, r);
         tmem_ld_wait();
@@ -685,10 +692,18 @@ int launch2(const Gemm2Maps& m, Gemm2Params& p, const Gemm2Maps& mg, const Gemm2
   }
   const int max_clusters = g2_num_sms / 2;
   const int clusters = tiles < max_clusters ? tiles : max_clusters;
+  // plain launches: eight epilogue warps (ERI_B200_GEMM_EPI_WARPS=4 keeps four); the staged epilogue of the
+  // peer scatter keeps one thread per accumulator row
+  static int epi_warps = 0;
+  if (!epi_warps) {
+    const char* e = getenv("ERI_B200_GEMM_EPI_WARPS");
+    epi_warps = (e && e[0] == '4') ? 4 : 8;
+  }
+  const int threads = (STAGED || p.scatter_world) ? 192 : 64 + 32 * epi_warps;
   if (pdl) {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(clusters * 2);
-    cfg.blockDim = dim3(192);
+    cfg.blockDim = dim3(threads);
     cfg.dynamicSmemBytes = SMEM;
     cfg.stream = st;
     cudaLaunchAttribute at[1];
@@ -698,7 +713,7 @@ int launch2(const Gemm2Maps& m, Gemm2Params& p, const Gemm2Maps& mg, const Gemm2
     cfg.numAttrs = 1;
     return (int)cudaLaunchKernelEx(&cfg, kern, ta, tb, ta2, tb2, tbl, p, mg.ta, mg.tb, mg.ta2, mg.tb2, pg);
   }
-  kern<<<clusters * 2, 192, SMEM, st>>>(ta, tb, ta2, tb2, tbl, p, mg.ta, mg.tb, mg.ta2, mg.tb2, pg);
+  kern<<<clusters * 2, threads, SMEM, st>>>(ta, tb, ta2, tb2, tbl, p, mg.ta, mg.tb, mg.ta2, mg.tb2, pg);
   return (int)cudaGetLastError();
 }
 
