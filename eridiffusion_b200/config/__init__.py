@@ -539,6 +539,7 @@ ENV_VARS = {
     "ERI_B200_FA_PAIR": "1: attention forward for head size 128 on CTA pairs (measured slower; default 0)",
     "ERI_B200_ATTN_HEAD_PAD": "1 | 0: head sizes other than 64 / 128 (below 128) zero-padded onto the native attention kernels",
     "ERI_B200_PAIR_MIN_TILES": "GEMMs with at most this many 256 x 256 tiles use the one-CTA kernel's 128-column tiles (default 36)",
+    "ERI_B200_NORM_SKIP": "1: the gradient of the residual branch around a norm is added inside the norm's backward kernel (no measurable gain; default 0)",
     "ERI_B200_NORM_SMEM": "1 | 0: norm + modulate rows resident in shared memory (32 warps per SM) or in registers",
     "ERI_B200_ADAMW8_PAIR": "1 | 0: 8-bit AdamW on packed fp32 pairs (default) or the element-wise kernel",
     "ERI_B200_MLP_FUSE": "1: dual-stream MLP pairs apply the activation derivative in the down-projection's input-gradient epilogue (measured slower; default 0)",

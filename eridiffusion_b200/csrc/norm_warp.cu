@@ -21,6 +21,7 @@ namespace {
 
 struct NormArgs {
   const bf16 *x, *dy, *scale, *shift, *weight, *bias;
+  const bf16* addend;  // backward only (may be null): added to dx, e.g. the gradient of a residual branch of x
   bf16* out;  // y (forward) or dx (backward)
   float *mean, *rstd;
   int rows, D, rows_per_batch, mod_stride;
@@ -401,6 +402,11 @@ __global__ void __launch_bounds__(1024, 1) norm_rows_smem_kernel(const NormArgs 
 #pragma unroll
         for (int j = 0; j < 4; ++j)
           x[j] = f2_fma(f2_add(x[j], nm2), kb, f2_fma(g[j], ka, kc));
+        if (a.addend) {
+          unpack8_f2(reinterpret_cast<const bf16x8*>(a.addend + (size_t)row * D)[v], t);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) x[j] = f2_add(x[j], t[j]);
+        }
         orow[v] = pack8_f2(x);
       }
     }
@@ -454,6 +460,7 @@ int launch_rows(const NormArgs& a, cudaStream_t st) {
     const int code = launch_rows_smem<BWD>(a, st);
     if (code != -100) return code;
   }
+  if (a.addend) return -100;   // only the shared-memory-resident kernel adds a second gradient
   const int per_warp = kRingStages<BWD> * NT * D * 2;
   int warps = (200 * 1024 - kBarBytes) / per_warp;
   if (warps > (BWD ? 8 : 12)) warps = BWD ? 8 : 12;
@@ -521,19 +528,34 @@ int eri_norm_modulate_fwd_warp(const void* x, const void* scale, const void* shi
   if (norm_setup()) return -3;
   NormArgs a;
   a.x = (const bf16*)x; a.dy = nullptr; a.scale = (const bf16*)scale; a.shift = (const bf16*)shift;
-  a.weight = (const bf16*)weight; a.bias = (const bf16*)bias; a.out = (bf16*)y;
+  a.weight = (const bf16*)weight; a.bias = (const bf16*)bias; a.out = (bf16*)y; a.addend = nullptr;
   a.mean = mean; a.rstd = rstd; a.rows = rows; a.D = D; a.rows_per_batch = rows_per_batch;
   a.mod_stride = mod_stride; a.eps = eps; a.rms = rms; a.err = g_norm_err;
   return launch_rows<false>(a, (cudaStream_t)stream);
 }
 
+// addend (may be null): a [rows, D] bf16 tensor added to dx, e.g. the gradient that reached x through a
+// residual branch, so that autograd has no separate sum to launch.
+int eri_norm_modulate_bwd_warp_add(const void* dy, const void* x, const void* scale, const void* weight,
+                                   const float* mean, const float* rstd, void* dx, const void* addend, int rows,
+                                   int D, int rows_per_batch, int mod_stride, int rms, void* stream);
+
 int eri_norm_modulate_bwd_warp(const void* dy, const void* x, const void* scale, const void* weight,
                                const float* mean, const float* rstd, void* dx, int rows, int D,
                                int rows_per_batch, int mod_stride, int rms, void* stream) {
+  return eri_norm_modulate_bwd_warp_add(dy, x, scale, weight, mean, rstd, dx, nullptr, rows, D, rows_per_batch,
+                                        mod_stride, rms, stream);
+}
+
+int eri_norm_modulate_bwd_warp_add(const void* dy, const void* x, const void* scale, const void* weight,
+                                   const float* mean, const float* rstd, void* dx, const void* addend, int rows,
+                                   int D, int rows_per_batch, int mod_stride, int rms, void* stream) {
   if (D % 8 || D > 4096 || D < 256) return -100;
-  if (((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(dy)) & 15) != 0) return -100;
+  if (((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(dy) | reinterpret_cast<uintptr_t>(addend)) & 15) != 0)
+    return -100;
   if (norm_setup()) return -3;
   NormArgs a;
+  a.addend = (const bf16*)addend;
   a.x = (const bf16*)x; a.dy = (const bf16*)dy; a.scale = (const bf16*)scale; a.shift = nullptr;
   a.weight = (const bf16*)weight; a.bias = nullptr; a.out = (bf16*)dx;
   a.mean = const_cast<float*>(mean); a.rstd = const_cast<float*>(rstd); a.rows = rows; a.D = D;

@@ -84,8 +84,11 @@ class DoubleStreamBlock(nn.Module):
         i_sh1, i_sc1, i_g1, i_sh2, i_sc2, i_g2 = self.img_mod(vec)
         t_sh1, t_sc1, t_g1, t_sh2, t_sc2, t_g2 = self.txt_mod(vec)
         Lt = txt.shape[1]
-        img_qkv, txt_qkv = linear_pair(self.img_attn.qkv, F.norm_modulate(img, i_sc1, i_sh1),
-                                       self.txt_attn.qkv, F.norm_modulate(txt, t_sc1, t_sh1))
+        # each norm also hands back its input for the residual branch around it: the two gradients of the
+        # stream are then summed inside the norm's backward kernel
+        img_n, img = F.norm_modulate_skip(img, i_sc1, i_sh1)
+        txt_n, txt = F.norm_modulate_skip(txt, t_sc1, t_sh1)
+        img_qkv, txt_qkv = linear_pair(self.img_attn.qkv, img_n, self.txt_attn.qkv, txt_n)
         q, k, v = F.qknorm_rope_joint(
             [(txt_qkv, self.txt_attn.q_norm.scale, self.txt_attn.k_norm.scale),
              (img_qkv, self.img_attn.q_norm.scale, self.img_attn.k_norm.scale)],
@@ -94,8 +97,9 @@ class DoubleStreamBlock(nn.Module):
         txt_a, img_a = attn[:, :Lt], attn[:, Lt:]
         img, txt = linear_pair(self.img_attn.proj, img_a, self.txt_attn.proj, txt_a,
                                residual=(img, txt), gate=(i_g1, t_g1))
-        img, txt = mlp_pair(self.img_mlp_0, self.img_mlp_2, F.norm_modulate(img, i_sc2, i_sh2),
-                            self.txt_mlp_0, self.txt_mlp_2, F.norm_modulate(txt, t_sc2, t_sh2), act="gelu",
+        img_n, img = F.norm_modulate_skip(img, i_sc2, i_sh2)
+        txt_n, txt = F.norm_modulate_skip(txt, t_sc2, t_sh2)
+        img, txt = mlp_pair(self.img_mlp_0, self.img_mlp_2, img_n, self.txt_mlp_0, self.txt_mlp_2, txt_n, act="gelu",
                             residual=(img, txt), gate=(i_g2, t_g2))
         return img, txt
 
@@ -115,7 +119,7 @@ class SingleStreamBlock(nn.Module):
     def forward(self, x, vec, cos, sin):
         shift, scale, gate = self.modulation(vec)
         from ..ops import fused_blocks as FB
-        xm = F.norm_modulate(x, scale, shift)
+        xm, x = F.norm_modulate_skip(x, scale, shift)
         if FB.single_stream_supported(xm, gate, self.linear1, self.linear2, self.heads):
             return FB.single_stream(xm, x, gate, self.linear1, self.linear2, self.q_norm.scale,
                                     self.k_norm.scale, cos, sin, self.heads)

@@ -71,6 +71,7 @@ _SIGNATURES = {
     "eri_norm_modulate_bwd": [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P],
     "eri_norm_modulate_fwd_warp": [_P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _F, _I, _P],
     "eri_norm_modulate_bwd_warp": [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P],
+    "eri_norm_modulate_bwd_warp_add": [_P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P],
     "eri_norm_check_error": [],
     "eri_norm_set_smem_variant": [C.c_int],
     "eri_adamw8bit_set_pair_variant": [C.c_int],

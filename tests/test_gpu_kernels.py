@@ -66,6 +66,45 @@ def test_norm_modulate_row_kernels(rms, L, D, variant):
         lib.eri_norm_set_smem_variant(prev)
 
 
+@pytest.mark.parametrize("rms", [False, True])
+def test_norm_modulate_skip_adds_the_residual_gradient_in_the_kernel(rms, request):
+    """``norm_modulate_skip`` returns the normalised tensor and its input for the residual branch; the backward
+    kernel adds the gradient of that branch to dx. Same result as the two-branch formulation left to autograd."""
+    B, L, D = 2, 700, 3072
+    x0 = (rnd(B, L, D) + 1.5).bfloat16()
+    mod = rnd(B, 2 * D, scale=0.3)
+    sh, sc = mod.split(D, dim=-1)
+    g1, g2 = rnd(B, L, D, seed=5), rnd(B, L, D, seed=6)
+
+    F._NORM_SKIP, old_skip = True, F._NORM_SKIP            # opt-in switch (ERI_B200_NORM_SKIP)
+    request.addfinalizer(lambda: setattr(F, "_NORM_SKIP", old_skip))
+
+    def run(skip):
+        x = x0.clone().requires_grad_()
+        if skip:
+            y, xr = F.norm_modulate_skip(x, sc, sh, None, None, 1e-6, rms)
+            assert xr.data_ptr() == x.data_ptr()
+        else:
+            y, xr = F.norm_modulate(x, sc, sh, None, None, 1e-6, rms), x
+        c0 = F.N.launch_count()
+        ((y.float() * g1.float()).sum() + (xr.float() * g2.float()).sum()).backward()
+        return y.detach().float(), x.grad.float(), F.N.launch_count() - c0
+    y1, d1, n1 = run(True)
+    y0, d0, n0 = run(False)
+    assert torch.equal(y1, y0) and n1 == n0 == 1
+    close(d1, d0, 2e-2, 2e-2)
+    xr = x0.float().requires_grad_()
+    yr = R.norm_modulate(xr, sc.float(), sh.float(), None, None, 1e-6, rms)
+    ((yr * g1.float()).sum() + (xr * g2.float()).sum()).backward()
+    close(d1, xr.grad, 3e-2, 3e-2)
+    # only the residual branch has a gradient: it passes through untouched
+    x = x0.clone().requires_grad_()
+    y, xs = F.norm_modulate_skip(x, sc, sh, None, None, 1e-6, rms)
+    (xs.float() * g2.float()).sum().backward()
+    assert torch.equal(x.grad, g2)
+    assert F.kernel_error_check() == {}
+
+
 def _norm_rows_case(rms, L, D):
     B = 2
     x = (rnd(B, L, D) + 4.0).bfloat16().requires_grad_()
