@@ -94,7 +94,7 @@ class DoubleStreamBlock(nn.Module):
              (img_qkv, self.img_attn.q_norm.scale, self.img_attn.k_norm.scale)],
             cos, sin, self.heads)
         attn = F.attention(q, k, v).flatten(2)               # [B, Lt+Li, D]
-        txt_a, img_a = attn[:, :Lt], attn[:, Lt:]
+        txt_a, img_a = F.split_tokens(attn, Lt)
         img, txt = linear_pair(self.img_attn.proj, img_a, self.txt_attn.proj, txt_a,
                                residual=(img, txt), gate=(i_g1, t_g1))
         img_n, img = F.norm_modulate_skip(img, i_sc2, i_sh2)

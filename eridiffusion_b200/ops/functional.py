@@ -316,6 +316,37 @@ def gate_residual(x, y, gate=None):
     return R.gate_residual(x, y, gate)
 
 
+class _SplitTokens(torch.autograd.Function):
+    """(x[:, :n], x[:, n:]) as views. Autograd's own slice backward allocates a zero tensor of x's size per
+    slice, copies the slice's gradient into it and sums the two (two fills, two copies and an add per
+    dual-stream block); here the backward is one concatenation."""
+
+    @staticmethod
+    def forward(ctx, x, n):
+        ctx.n, ctx.shape = n, x.shape
+        ctx.set_materialize_grads(False)
+        return x[:, :n], x[:, n:]
+
+    @staticmethod
+    def backward(ctx, d0, d1):
+        if d0 is None and d1 is None:
+            return None, None
+        B, L = ctx.shape[0], ctx.shape[1]
+        ref = d0 if d0 is not None else d1
+        if d0 is None:
+            d0 = ref.new_zeros((B, ctx.n, *ctx.shape[2:]))
+        if d1 is None:
+            d1 = ref.new_zeros((B, L - ctx.n, *ctx.shape[2:]))
+        return torch.cat((d0, d1), dim=1), None
+
+
+def split_tokens(x, n):
+    """``(x[:, :n], x[:, n:])`` whose backward is a single concatenation."""
+    if x.requires_grad and torch.is_grad_enabled():
+        return _SplitTokens.apply(x, n)
+    return x[:, :n], x[:, n:]
+
+
 # ---------------------------------------------------------------------------- activations
 class _Act(torch.autograd.Function):
     @staticmethod

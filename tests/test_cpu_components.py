@@ -463,3 +463,22 @@ def test_linear_pair_falls_back_to_two_linears_off_the_native_path():
     assert spec is not None and spec[2][0] is ad.lora_A and spec[2][2] == ad.scale
     a.register_forward_hook(lambda m, i, o: o)
     assert _pair_spec(a) is None                     # hooks must see their module's own call
+
+
+def test_split_tokens_backward_is_one_concatenation():
+    import torch
+    from eridiffusion_b200.ops import functional as F
+    x = torch.randn(2, 7, 4, requires_grad=True)
+    a, b = F.split_tokens(x, 3)
+    assert a.shape == (2, 3, 4) and b.shape == (2, 4, 4) and torch.equal(a, x[:, :3]) and torch.equal(b, x[:, 3:])
+    ga, gb = torch.randn_like(a), torch.randn_like(b)
+    (a * ga).sum().add((b * gb).sum()).backward()
+    assert torch.equal(x.grad, torch.cat((ga, gb), 1))
+    # one side unused: its part of the gradient is zero
+    x2 = torch.randn(2, 7, 4, requires_grad=True)
+    a2, b2 = F.split_tokens(x2, 3)
+    (b2 * gb).sum().backward()
+    assert torch.equal(x2.grad[:, 3:], gb) and (x2.grad[:, :3] == 0).all()
+    # no gradient tracking: plain views
+    a3, b3 = F.split_tokens(x.detach(), 3)
+    assert a3.data_ptr() == x.data_ptr()
