@@ -482,3 +482,11 @@ def test_split_tokens_backward_is_one_concatenation():
     # no gradient tracking: plain views
     a3, b3 = F.split_tokens(x.detach(), 3)
     assert a3.data_ptr() == x.data_ptr()
+
+
+def test_activation_leaves_the_epilogue_only_for_large_products_with_a_short_reduction():
+    from eridiffusion_b200.ops import functional as F
+    assert F._act_outside_epilogue(4096, 12288, 3072)          # FLUX MLP up-projection
+    assert not F._act_outside_epilogue(4096, 3072, 12288)      # long reduction: the epilogue is hidden
+    assert not F._act_outside_epilogue(512, 12288, 3072)       # small problem: launch-bound
+    assert not F._act_outside_epilogue(4429, 6144, 1536)       # SD3.5-medium: measured a tie, stays fused
